@@ -1,0 +1,124 @@
+"""ctypes binding of libd2conv3d.so (the C ABI declared in include/d2conv3d.h).
+
+PyTorch is used only for device memory and the current stream: every call passes
+raw device pointers, sizes and a cudaStream_t across the C boundary.  There is no
+CPU or PyTorch fallback -- if the library is missing or a call fails, an error is
+raised.
+"""
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libd2conv3d.so")
+
+F32, F64, F16 = 0, 1, 2
+MATH_MODES = {"auto": 0, "fp32": 1, "bf16x3": 2, "bf16": 3}
+FIELD_MODES = {"x": 0, "xy": 1, "xxz": 2, "xyz": 3}
+FIELD_CHANNELS = {"x": 1, "xy": 2, "xxz": 2, "xyz": 3}
+OP_DEFORM_FWD, OP_DEFORM_BWD, OP_DYNDIL_FWD, OP_DYNDIL_BWD, OP_DW_FWD, OP_DW_BWD = range(6)
+
+_DTYPES = {torch.float32: F32, torch.float64: F64, torch.float16: F16}
+
+
+class ConvDesc(ctypes.Structure):
+    """d2c_conv_desc"""
+
+    _fields_ = [(n, ctypes.c_int32) for n in (
+        "dtype", "batch", "in_channels", "out_channels", "in_d", "in_h", "in_w",
+        "kd", "kh", "kw", "stride_d", "stride_h", "stride_w", "pad_d", "pad_h", "pad_w",
+        "dil_d", "dil_h", "dil_w", "groups", "offset_groups")]
+
+
+_lib = None
+
+
+def lib():
+    """The loaded library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m d2conv3d_b200.build` "
+                "(there is no fallback implementation)")
+        L = ctypes.CDLL(LIB_PATH)
+        vp, sz, i32 = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int
+        dp = ctypes.POINTER(ConvDesc)
+        L.d2c_output_dims.argtypes = [dp, ctypes.POINTER(ctypes.c_int32)]
+        L.d2c_deform_conv3d_check.argtypes = [dp, ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int64)]
+        L.d2c_workspace_bytes.argtypes = [i32, dp]
+        L.d2c_workspace_bytes.restype = sz
+        L.d2c_status_string.argtypes = [i32]
+        L.d2c_status_string.restype = ctypes.c_char_p
+        L.d2c_last_cuda_error.restype = ctypes.c_char_p
+        L.d2c_set_math_mode.argtypes = [i32]
+        L.d2c_get_max_intermediate_elements.restype = ctypes.c_uint64
+        L.d2c_set_max_intermediate_elements.argtypes = [ctypes.c_uint64]
+        L.d2c_set_max_intermediate_elements.restype = None
+        L.d2c_deform_conv3d_fwd.argtypes = [dp] + [vp] * 7 + [sz, vp]
+        L.d2c_deform_conv3d_bwd.argtypes = [dp] + [vp] * 11 + [sz, vp]
+        L.d2c_deform_conv3d_corners.argtypes = [dp, vp, vp, vp]
+        L.d2c_dyn_dilated_conv3d_fwd.argtypes = [dp, i32] + [vp] * 7 + [sz, vp]
+        L.d2c_dyn_dilated_conv3d_bwd.argtypes = [dp, i32] + [vp] * 11 + [sz, vp]
+        L.d2c_dyn_dilated_conv3d_corners.argtypes = [dp, i32, vp, vp, vp]
+        L.d2c_depthwise_conv3d_fwd.argtypes = [dp] + [vp] * 4 + [vp]
+        L.d2c_depthwise_conv3d_bwd.argtypes = [dp] + [vp] * 7 + [sz, vp]
+        _lib = L
+    return _lib
+
+
+def check(status, what):
+    if status == 0:
+        return
+    L = lib()
+    msg = L.d2c_status_string(status).decode()
+    if status > 0:
+        msg += ": " + L.d2c_last_cuda_error().decode()
+    raise RuntimeError(f"{what}: {msg} (status {status})")
+
+
+def dtype_code(t):
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise RuntimeError(f"unsupported dtype {t.dtype}") from None
+
+
+def make_desc(x, w, stride, padding, dilation, groups, offset_groups):
+    return ConvDesc(dtype_code(x), x.shape[0], x.shape[1], w.shape[0], x.shape[2], x.shape[3], x.shape[4],
+                    w.shape[2], w.shape[3], w.shape[4], stride[0], stride[1], stride[2],
+                    padding[0], padding[1], padding[2], dilation[0], dilation[1], dilation[2],
+                    groups, offset_groups)
+
+
+def output_dims(desc, what="conv3d"):
+    out = (ctypes.c_int32 * 3)()
+    check(lib().d2c_output_dims(ctypes.byref(desc), out), what)
+    return tuple(out)
+
+
+def ptr(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def stream_of(t):
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def workspace(op, desc, device):
+    n = lib().d2c_workspace_bytes(op, ctypes.byref(desc))
+    if n == 0:
+        return None, 0
+    ws = torch.empty(n, dtype=torch.uint8, device=device)
+    return ws, n
+
+
+def set_math_mode(mode):
+    """'auto' | 'fp32' | 'bf16x3' | 'bf16' -- how the Cin*K x Cout contraction is evaluated."""
+    check(lib().d2c_set_math_mode(MATH_MODES[mode]), "set_math_mode")
+
+
+def get_math_mode():
+    code = lib().d2c_get_math_mode()
+    return {v: k for k, v in MATH_MODES.items()}[code]

@@ -1,0 +1,367 @@
+// C ABI of libd2conv3d.so: argument validation, tier selection and launch
+// sequencing.  See include/d2conv3d.h for the contract of every entry point.
+#include <atomic>
+#include <cstring>
+
+#include "d2c_common.cuh"
+#include "deform_generic.cuh"
+#include "deform_sm100.h"
+
+namespace d2c {
+
+static thread_local char g_last_cuda_error[256] = "";
+void set_last_cuda_error(cudaError_t e) {
+  std::strncpy(g_last_cuda_error, cudaGetErrorString(e), sizeof(g_last_cuda_error) - 1);
+  cudaGetLastError();  // clear the sticky-free error state
+}
+
+static std::atomic<int> g_math_mode{D2C_MATH_AUTO};
+// Default of the reference's MAX_INTERMEDIATE_ELEMENTS (csrc/ops/dconv3d_gpu.cu:12).
+static std::atomic<unsigned long long> g_max_intermediate{1ull << 32};
+
+int depthwise_fwd(const Geom& g, int dtype, const void* x, const void* w, const void* bias, void* y,
+                  cudaStream_t st);
+int depthwise_bwd(const Geom& g, int dtype, const void* gy, const void* x, const void* w, void* gx,
+                  void* gw, void* gbias, void* ws, cudaStream_t st);
+size_t depthwise_bwd_workspace(const Geom& g);
+
+static size_t dtype_size(int dtype) { return dtype == D2C_F64 ? 8 : (dtype == D2C_F16 ? 2 : 4); }
+
+// torch.linspace(-dil*(k/2), dil*(k/2), k) as get_kernel_grid of the reference
+// evaluates it (utils/grid.py:21-25): in float32 whatever the field's dtype,
+// ascending from `start` in the first half, descending from `end` in the second.
+template <typename T>
+static void kernel_axis(int k, int dil, T* out) {
+  const float start = (float)(-dil * (k / 2)), end = (float)(dil * (k / 2));
+  if (k == 1) { out[0] = (T)start; return; }
+  const float step = (end - start) / (float)(k - 1);
+  const int half = k / 2;
+  for (int i = 0; i < k; ++i)
+    out[i] = (T)((i < half) ? start + step * (float)i : end - step * (float)(k - i - 1));
+}
+
+static int field_channels(int mode) {
+  switch (mode) {
+    case D2C_FIELD_X: return 1;
+    case D2C_FIELD_XY: case D2C_FIELD_XXZ: return 2;
+    case D2C_FIELD_XYZ: return 3;
+    default: return -1;
+  }
+}
+
+// size_map channel feeding dim d (0:z 1:y 2:x), -1 = constant one (utils/grid.py:79-92)
+static int field_channel(int mode, int d) {
+  switch (mode) {
+    case D2C_FIELD_X: return d == 0 ? -1 : 0;
+    case D2C_FIELD_XY: return d == 0 ? -1 : d - 1;
+    case D2C_FIELD_XXZ: return d == 0 ? 0 : 1;
+    default: return d;
+  }
+}
+
+template <typename T>
+static int make_field_coords(const Geom& g, int mode, const void* size_map, FieldCoords<T>* fc) {
+  const int nch = field_channels(mode);
+  if (nch < 0) return D2C_ERR_MODE;
+  if (g.kd > kMaxFieldKernelDim || g.kh > kMaxFieldKernelDim || g.kw > kMaxFieldKernelDim) return D2C_ERR_SHAPE;
+  std::memset(fc, 0, sizeof(*fc));
+  fc->size_map = (const T*)size_map;
+  fc->nch = nch;
+  for (int d = 0; d < 3; ++d) fc->ch[d] = field_channel(mode, d);
+  kernel_axis<T>(g.kd, g.dd, fc->axis[0]);
+  kernel_axis<T>(g.kh, g.dh, fc->axis[1]);
+  kernel_axis<T>(g.kw, g.dw, fc->axis[2]);
+  return D2C_OK;
+}
+
+static bool ws_ok(const void* ws, size_t have, size_t need) {
+  if (need == 0) return true;
+  return ws != nullptr && (reinterpret_cast<uintptr_t>(ws) % 256) == 0 && have >= need;
+}
+
+static size_t generic_bwd_workspace(const Geom& g, int dtype) {
+  const int nb = bwd_slice_clips(g, g_max_intermediate.load());
+  return align_up(dtype_size(dtype) * (size_t)nb * g.Cin * g.K * g.V, 256);
+}
+
+}  // namespace d2c
+
+using namespace d2c;
+
+extern "C" {
+
+int d2c_output_dims(const d2c_conv_desc* desc, int32_t out_dhw[3]) {
+  if (!desc || !out_dhw) return D2C_ERR_NULL;
+  Geom g;
+  // groups do not influence the output size; validate them only in the op calls
+  d2c_conv_desc d = *desc;
+  d.groups = 1; d.offset_groups = 1;
+  int rc = make_geom(&d, &g, false);
+  if (rc) return rc;
+  out_dhw[0] = g.Do; out_dhw[1] = g.Ho; out_dhw[2] = g.Wo;
+  return D2C_OK;
+}
+
+int d2c_deform_conv3d_check(const d2c_conv_desc* desc, const int64_t offset_dims[4],
+                            const int64_t mask_dims[4]) {
+  if (!desc || !offset_dims) return D2C_ERR_NULL;
+  if (desc->dtype != D2C_F32 && desc->dtype != D2C_F64) return D2C_ERR_DTYPE;
+  Geom g;
+  int rc = make_geom(desc, &g, false);
+  if (rc) return rc;
+  if (offset_dims[0] != (int64_t)g.G * 3 * g.K || offset_dims[1] != g.Do || offset_dims[2] != g.Ho ||
+      offset_dims[3] != g.Wo)
+    return D2C_ERR_OFFSET_SHAPE;
+  if (mask_dims && (mask_dims[0] != (int64_t)g.G * g.K || mask_dims[1] != g.Do || mask_dims[2] != g.Ho ||
+                    mask_dims[3] != g.Wo))
+    return D2C_ERR_MASK_SHAPE;
+  return D2C_OK;
+}
+
+size_t d2c_workspace_bytes(int op, const d2c_conv_desc* desc) {
+  Geom g;
+  const bool dw = (op == D2C_OP_DEPTHWISE_FWD || op == D2C_OP_DEPTHWISE_BWD);
+  if (make_geom(desc, &g, dw)) return 0;
+  switch (op) {
+    case D2C_OP_DEFORM_FWD:
+    case D2C_OP_DYNDIL_FWD:
+      return sm100_fwd_workspace(g, desc->dtype, g_math_mode.load());
+    case D2C_OP_DEFORM_BWD:
+    case D2C_OP_DYNDIL_BWD: {
+      const size_t fast = sm100_bwd_workspace(g, desc->dtype, g_math_mode.load());
+      const size_t gen = generic_bwd_workspace(g, desc->dtype);
+      return fast > gen ? fast : gen;
+    }
+    case D2C_OP_DEPTHWISE_BWD:
+      return depthwise_bwd_workspace(g);
+    default:
+      return 0;
+  }
+}
+
+const char* d2c_status_string(int status) {
+  switch (status) {
+    case D2C_OK: return "ok";
+    case D2C_ERR_NULL: return "a required pointer is NULL";
+    case D2C_ERR_DTYPE: return "dtype not supported by this op";
+    case D2C_ERR_SHAPE: return "sizes, strides and dilations must be positive and padding non-negative";
+    case D2C_ERR_GROUPS: return "channel counts must be divisible by groups and offset_groups";
+    case D2C_ERR_OUT_DIMS: return "computed output size is not positive";
+    case D2C_ERR_OFFSET_SHAPE: return "offset must have offset_groups*3*K channels and the output's spatial dims";
+    case D2C_ERR_MASK_SHAPE: return "mask must have offset_groups*K channels and the output's spatial dims";
+    case D2C_ERR_WORKSPACE: return "workspace is NULL, not 256-byte aligned or too small";
+    case D2C_ERR_TOO_LARGE: return "tensor too large for this op";
+    case D2C_ERR_MODE: return "unknown math or field mode";
+    case D2C_ERR_WEIGHT_SHAPE: return "weight shape does not match the channel counts";
+    case D2C_ERR_CUDA: return "CUDA runtime error";
+    case D2C_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait gave up";
+    default: return "unknown status";
+  }
+}
+
+const char* d2c_last_cuda_error(void) { return g_last_cuda_error; }
+
+int d2c_set_math_mode(int mode) {
+  if (mode < D2C_MATH_AUTO || mode > D2C_MATH_BF16) return D2C_ERR_MODE;
+  g_math_mode.store(mode);
+  return D2C_OK;
+}
+int d2c_get_math_mode(void) { return g_math_mode.load(); }
+
+uint64_t d2c_get_max_intermediate_elements(void) { return g_max_intermediate.load(); }
+void d2c_set_max_intermediate_elements(uint64_t n) { g_max_intermediate.store(n ? n : 1); }
+
+// ---- deformable conv ---------------------------------------------------------------------------
+
+int d2c_deform_conv3d_fwd(const d2c_conv_desc* desc, const void* x, const void* offset,
+                          const void* mask, const void* w, const void* bias, void* y,
+                          void* workspace, size_t workspace_bytes, d2c_stream_t stream) {
+  if (!desc || !x || !offset || !w || !y) return D2C_ERR_NULL;
+  Geom g;
+  int rc = make_geom(desc, &g, false);
+  if (rc) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (desc->dtype == D2C_F32) {
+    OffsetCoords<float> oc{(const float*)offset};
+    const int mode = g_math_mode.load();
+    if (sm100_fwd_supported(g, desc->dtype, mode)) {
+      if (!ws_ok(workspace, workspace_bytes, sm100_fwd_workspace(g, desc->dtype, mode))) return D2C_ERR_WORKSPACE;
+      return sm100_fwd_offsets(g, mode, (const float*)x, (const float*)offset, (const float*)mask,
+                               (const float*)w, (const float*)bias, (float*)y, workspace, st);
+    }
+    return launch_fwd_generic<float>(g, oc, (const float*)x, (const float*)mask, (const float*)w,
+                                     (const float*)bias, (float*)y, st);
+  } else if (desc->dtype == D2C_F64) {
+    OffsetCoords<double> oc{(const double*)offset};
+    return launch_fwd_generic<double>(g, oc, (const double*)x, (const double*)mask, (const double*)w,
+                                      (const double*)bias, (double*)y, st);
+  }
+  return D2C_ERR_DTYPE;
+}
+
+int d2c_deform_conv3d_bwd(const d2c_conv_desc* desc, const void* grad_y, const void* x,
+                          const void* offset, const void* mask, const void* w, void* grad_x,
+                          void* grad_offset, void* grad_mask, void* grad_w, void* grad_bias,
+                          void* workspace, size_t workspace_bytes, d2c_stream_t stream) {
+  if (!desc || !grad_y || !x || !offset || !w || !grad_x || !grad_offset || !grad_w) return D2C_ERR_NULL;
+  if (mask && !grad_mask) return D2C_ERR_NULL;
+  Geom g;
+  int rc = make_geom(desc, &g, false);
+  if (rc) return rc;
+  if (desc->dtype != D2C_F32 && desc->dtype != D2C_F64) return D2C_ERR_DTYPE;
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t need = generic_bwd_workspace(g, desc->dtype);
+  if (!ws_ok(workspace, workspace_bytes, need)) return D2C_ERR_WORKSPACE;
+  const int nb = bwd_slice_clips(g, g_max_intermediate.load());
+  if (desc->dtype == D2C_F32) {
+    OffsetCoords<float> oc{(const float*)offset};
+    return launch_bwd_generic<float, OffsetCoords<float>, false>(
+        g, oc, (const float*)grad_y, (const float*)x, (const float*)mask, (const float*)w,
+        (float*)grad_x, (float*)grad_offset, 0, (float*)grad_mask, (float*)grad_w, (float*)grad_bias,
+        (float*)workspace, nb, st);
+  }
+  OffsetCoords<double> oc{(const double*)offset};
+  return launch_bwd_generic<double, OffsetCoords<double>, false>(
+      g, oc, (const double*)grad_y, (const double*)x, (const double*)mask, (const double*)w,
+      (double*)grad_x, (double*)grad_offset, 0, (double*)grad_mask, (double*)grad_w,
+      (double*)grad_bias, (double*)workspace, nb, st);
+}
+
+int d2c_deform_conv3d_corners(const d2c_conv_desc* desc, const void* offset, int32_t* corners,
+                              d2c_stream_t stream) {
+  if (!desc || !offset || !corners) return D2C_ERR_NULL;
+  Geom g;
+  int rc = make_geom(desc, &g, false);
+  if (rc) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  const long long total = (long long)g.B * g.G * g.K * g.V;
+  if (desc->dtype == D2C_F32) {
+    OffsetCoords<float> oc{(const float*)offset};
+    corners_kernel<float><<<grid_1d(total, 256), 256, 0, st>>>(g, oc, corners);
+  } else if (desc->dtype == D2C_F64) {
+    OffsetCoords<double> oc{(const double*)offset};
+    corners_kernel<double><<<grid_1d(total, 256), 256, 0, st>>>(g, oc, corners);
+  } else {
+    return D2C_ERR_DTYPE;
+  }
+  D2C_LAUNCH_CHECK();
+  return D2C_OK;
+}
+
+// ---- dynamic-dilated conv ------------------------------------------------------------------------
+
+int d2c_dyn_dilated_conv3d_fwd(const d2c_conv_desc* desc, int field_mode, const void* x,
+                               const void* size_map, const void* mask, const void* w,
+                               const void* bias, void* y, void* workspace, size_t workspace_bytes,
+                               d2c_stream_t stream) {
+  if (!desc || !x || !size_map || !w || !y) return D2C_ERR_NULL;
+  Geom g;
+  int rc = make_geom(desc, &g, false);
+  if (rc) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (desc->dtype == D2C_F32) {
+    FieldCoords<float> fc;
+    if ((rc = make_field_coords<float>(g, field_mode, size_map, &fc))) return rc;
+    const int mode = g_math_mode.load();
+    if (sm100_fwd_supported(g, desc->dtype, mode)) {
+      if (!ws_ok(workspace, workspace_bytes, sm100_fwd_workspace(g, desc->dtype, mode))) return D2C_ERR_WORKSPACE;
+      return sm100_fwd_field(g, mode, fc, (const float*)x, (const float*)mask, (const float*)w,
+                             (const float*)bias, (float*)y, workspace, st);
+    }
+    return launch_fwd_generic<float>(g, fc, (const float*)x, (const float*)mask, (const float*)w,
+                                     (const float*)bias, (float*)y, st);
+  } else if (desc->dtype == D2C_F64) {
+    FieldCoords<double> fc;
+    if ((rc = make_field_coords<double>(g, field_mode, size_map, &fc))) return rc;
+    return launch_fwd_generic<double>(g, fc, (const double*)x, (const double*)mask, (const double*)w,
+                                      (const double*)bias, (double*)y, st);
+  }
+  return D2C_ERR_DTYPE;
+}
+
+int d2c_dyn_dilated_conv3d_bwd(const d2c_conv_desc* desc, int field_mode, const void* grad_y,
+                               const void* x, const void* size_map, const void* mask,
+                               const void* w, void* grad_x, void* grad_size_map, void* grad_mask,
+                               void* grad_w, void* grad_bias, void* workspace,
+                               size_t workspace_bytes, d2c_stream_t stream) {
+  if (!desc || !grad_y || !x || !size_map || !w || !grad_x || !grad_size_map || !grad_w) return D2C_ERR_NULL;
+  if (mask && !grad_mask) return D2C_ERR_NULL;
+  Geom g;
+  int rc = make_geom(desc, &g, false);
+  if (rc) return rc;
+  if (desc->dtype != D2C_F32 && desc->dtype != D2C_F64) return D2C_ERR_DTYPE;
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t need = generic_bwd_workspace(g, desc->dtype);
+  if (!ws_ok(workspace, workspace_bytes, need)) return D2C_ERR_WORKSPACE;
+  const int nb = bwd_slice_clips(g, g_max_intermediate.load());
+  const int nch = field_channels(field_mode);
+  if (nch < 0) return D2C_ERR_MODE;
+  const size_t gs_elems = (size_t)g.B * nch * g.V;
+  if (desc->dtype == D2C_F32) {
+    FieldCoords<float> fc;
+    if ((rc = make_field_coords<float>(g, field_mode, size_map, &fc))) return rc;
+    return launch_bwd_generic<float, FieldCoords<float>, true>(
+        g, fc, (const float*)grad_y, (const float*)x, (const float*)mask, (const float*)w,
+        (float*)grad_x, (float*)grad_size_map, gs_elems, (float*)grad_mask, (float*)grad_w,
+        (float*)grad_bias, (float*)workspace, nb, st);
+  }
+  FieldCoords<double> fc;
+  if ((rc = make_field_coords<double>(g, field_mode, size_map, &fc))) return rc;
+  return launch_bwd_generic<double, FieldCoords<double>, true>(
+      g, fc, (const double*)grad_y, (const double*)x, (const double*)mask, (const double*)w,
+      (double*)grad_x, (double*)grad_size_map, gs_elems, (double*)grad_mask, (double*)grad_w,
+      (double*)grad_bias, (double*)workspace, nb, st);
+}
+
+int d2c_dyn_dilated_conv3d_corners(const d2c_conv_desc* desc, int field_mode, const void* size_map,
+                                   int32_t* corners, d2c_stream_t stream) {
+  if (!desc || !size_map || !corners) return D2C_ERR_NULL;
+  Geom g;
+  int rc = make_geom(desc, &g, false);
+  if (rc) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  const long long total = (long long)g.B * g.G * g.K * g.V;
+  if (desc->dtype == D2C_F32) {
+    FieldCoords<float> fc;
+    if ((rc = make_field_coords<float>(g, field_mode, size_map, &fc))) return rc;
+    corners_kernel<float><<<grid_1d(total, 256), 256, 0, st>>>(g, fc, corners);
+  } else if (desc->dtype == D2C_F64) {
+    FieldCoords<double> fc;
+    if ((rc = make_field_coords<double>(g, field_mode, size_map, &fc))) return rc;
+    corners_kernel<double><<<grid_1d(total, 256), 256, 0, st>>>(g, fc, corners);
+  } else {
+    return D2C_ERR_DTYPE;
+  }
+  D2C_LAUNCH_CHECK();
+  return D2C_OK;
+}
+
+// ---- depthwise -----------------------------------------------------------------------------------
+
+int d2c_depthwise_conv3d_fwd(const d2c_conv_desc* desc, const void* x, const void* w,
+                             const void* bias, void* y, d2c_stream_t stream) {
+  if (!desc || !x || !w || !y) return D2C_ERR_NULL;
+  Geom g;
+  int rc = make_geom(desc, &g, true);
+  if (rc) return rc;
+  // int32 range rule of the reference (csrc/grouped_conv3d.cu:431-440)
+  if ((long long)g.B * g.Cin * g.Vin > 0x7fffffffLL || (long long)g.B * g.Cout * g.V > 0x7fffffffLL)
+    return D2C_ERR_TOO_LARGE;
+  return depthwise_fwd(g, desc->dtype, x, w, bias, y, (cudaStream_t)stream);
+}
+
+int d2c_depthwise_conv3d_bwd(const d2c_conv_desc* desc, const void* grad_y, const void* x,
+                             const void* w, void* grad_x, void* grad_w, void* grad_bias,
+                             void* workspace, size_t workspace_bytes, d2c_stream_t stream) {
+  if (!desc || !grad_y || !x || !w) return D2C_ERR_NULL;
+  Geom g;
+  int rc = make_geom(desc, &g, true);
+  if (rc) return rc;
+  if ((long long)g.B * g.Cin * g.Vin > 0x7fffffffLL || (long long)g.B * g.Cout * g.V > 0x7fffffffLL)
+    return D2C_ERR_TOO_LARGE;
+  if (grad_w && !ws_ok(workspace, workspace_bytes, depthwise_bwd_workspace(g))) return D2C_ERR_WORKSPACE;
+  return depthwise_bwd(g, desc->dtype, grad_y, x, w, grad_x, grad_w, grad_bias, workspace,
+                       (cudaStream_t)stream);
+}
+
+}  // extern "C"

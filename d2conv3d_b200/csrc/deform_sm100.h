@@ -1,0 +1,21 @@
+// Tensor-core (tcgen05 / TMEM) tier of the deformable conv3d path for sm_100a.
+// The API layer asks *_supported() first; unsupported geometries use the generic
+// CUDA-core kernels.
+#pragma once
+
+#include "d2c_common.cuh"
+
+namespace d2c {
+
+bool sm100_fwd_supported(const Geom& g, int dtype, int math_mode);
+size_t sm100_fwd_workspace(const Geom& g, int dtype, int math_mode);
+size_t sm100_bwd_workspace(const Geom& g, int dtype, int math_mode);
+
+int sm100_fwd_offsets(const Geom& g, int math_mode, const float* x, const float* offset,
+                      const float* mask, const float* w, const float* bias, float* y, void* ws,
+                      cudaStream_t st);
+int sm100_fwd_field(const Geom& g, int math_mode, const FieldCoords<float>& fc, const float* x,
+                    const float* mask, const float* w, const float* bias, float* y, void* ws,
+                    cudaStream_t st);
+
+}  // namespace d2c

@@ -1,0 +1,204 @@
+/*
+ * d2conv3d.h -- C ABI of libd2conv3d.so
+ *
+ * B200 (sm_100a) implementation of the D2Conv3D hot path: modulated deformable
+ * conv3d, dynamic-dilated ("size conditioned") conv3d and channel-separated
+ * depthwise conv3d, forward and backward.
+ *
+ * Conventions shared by every entry point
+ *   - All tensor pointers are DEVICE pointers owned by the caller, contiguous
+ *     NCDHW, element type given by `dtype`.  Nullable pointers are marked.
+ *   - Nothing here allocates device memory: scratch is a caller-supplied
+ *     workspace of at least d2c_workspace_bytes() bytes (256-byte aligned).
+ *   - Every launch goes to the caller-supplied stream; calls are asynchronous.
+ *   - Return value: 0 = ok, negative = invalid argument (nothing launched),
+ *     positive = CUDA runtime / device-side failure.  Nothing throws or aborts.
+ *     d2c_status_string() turns a code into text.
+ *
+ * Each declaration cites the interface of the reference extension
+ * (Schmiddo/d2conv3d, paths relative to that project) that it stands in for.
+ */
+#ifndef D2CONV3D_H_
+#define D2CONV3D_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Opaque to this header so that C callers need no CUDA headers. */
+typedef void* d2c_stream_t; /* a cudaStream_t */
+
+enum d2c_dtype { D2C_F32 = 0, D2C_F64 = 1, D2C_F16 = 2 /* depthwise only */ };
+
+/* How the Cin*K x Cout contraction of the deformable ops is evaluated.
+ *   D2C_MATH_FP32   fp32 (or fp64) FMA pipeline; matches a cuBLAS S/Dgemm up to
+ *                   summation order.  Always used for fp64.
+ *   D2C_MATH_BF16X3 tcgen05 bf16 tensor cores, each fp32 operand split into
+ *                   hi+lo bf16 (3 MMA passes, fp32 accumulate): ~2^-16 relative
+ *                   operand error, keeps the 1e-4 parity bound.
+ *   D2C_MATH_BF16   single-pass bf16 operands, fp32 accumulate (looser bound).
+ *   D2C_MATH_AUTO   BF16X3 where the tensor-core kernels apply, else FP32.
+ */
+enum d2c_math_mode { D2C_MATH_AUTO = 0, D2C_MATH_FP32 = 1, D2C_MATH_BF16X3 = 2, D2C_MATH_BF16 = 3 };
+
+/* Dilation-field layouts; names follow utils/grid.py:72-98 (`mode`). */
+enum d2c_field_mode {
+  D2C_FIELD_X = 0,   /* 1 channel  s      -> (1, s, s)       "xx1" scripts */
+  D2C_FIELD_XY = 1,  /* 2 channels (y,x)  -> (1, s_y, s_x)   "xy1" scripts */
+  D2C_FIELD_XXZ = 2, /* 2 channels (z,x)  -> (s_z, s_x, s_x)               */
+  D2C_FIELD_XYZ = 3  /* 3 channels (z,y,x)                                 */
+};
+
+enum d2c_status {
+  D2C_OK = 0,
+  D2C_ERR_NULL = -1,          /* required pointer is NULL */
+  D2C_ERR_DTYPE = -2,         /* dtype not supported by this op */
+  D2C_ERR_SHAPE = -3,         /* non-positive size / stride / dilation, negative pad */
+  D2C_ERR_GROUPS = -4,        /* channel counts not divisible by groups / offset_groups */
+  D2C_ERR_OUT_DIMS = -5,      /* computed output size is not positive */
+  D2C_ERR_OFFSET_SHAPE = -6,  /* offset channels != G*3*K or spatial dims != output dims */
+  D2C_ERR_MASK_SHAPE = -7,    /* mask channels != G*K or spatial dims != output dims */
+  D2C_ERR_WORKSPACE = -8,     /* workspace NULL, misaligned or too small */
+  D2C_ERR_TOO_LARGE = -9,     /* a tensor exceeds the 2^31-1 element index range of the op */
+  D2C_ERR_MODE = -10,         /* unknown math / field mode */
+  D2C_ERR_WEIGHT_SHAPE = -11, /* weight.size(1)*groups != Cin, or depthwise weight rule */
+  D2C_ERR_CUDA = 1,           /* a CUDA runtime call failed (see d2c_last_cuda_error) */
+  D2C_ERR_DEVICE_TIMEOUT = 2  /* a bounded device-side wait gave up */
+};
+
+/* Geometry of one convolution call.
+ * Stands in for the positional int arguments of
+ * dconv_native._ops.deform_conv3d (csrc/ops/dconv3d.h:188-205) plus the sizes
+ * the reference reads from its tensors (csrc/ops/dconv3d_gpu.cu:477-502). */
+typedef struct d2c_conv_desc {
+  int32_t dtype;                /* d2c_dtype */
+  int32_t batch;                /* B  (clips) */
+  int32_t in_channels;          /* Cin */
+  int32_t out_channels;         /* Cout */
+  int32_t in_d, in_h, in_w;     /* input D,H,W */
+  int32_t kd, kh, kw;           /* weight.size(2..4) */
+  int32_t stride_d, stride_h, stride_w;
+  int32_t pad_d, pad_h, pad_w;
+  int32_t dil_d, dil_h, dil_w;
+  int32_t groups;               /* weight groups  (n_weight_groups) */
+  int32_t offset_groups;        /* deformable groups (n_offset_groups) */
+} d2c_conv_desc;
+
+enum d2c_op {
+  D2C_OP_DEFORM_FWD = 0,
+  D2C_OP_DEFORM_BWD = 1,
+  D2C_OP_DYNDIL_FWD = 2,
+  D2C_OP_DYNDIL_BWD = 3,
+  D2C_OP_DEPTHWISE_FWD = 4,
+  D2C_OP_DEPTHWISE_BWD = 5
+};
+
+/* ---- helpers ------------------------------------------------------------ */
+
+/* get_output_size, csrc/ops/dconv_gpu_common.h:13-15, for the three dims. */
+int d2c_output_dims(const d2c_conv_desc* desc, int32_t out_dhw[3]);
+
+/* The argument checks of deform_conv3d_forward_cuda
+ * (csrc/ops/dconv_gpu_common.h:17-51, csrc/ops/dconv3d_gpu.cu:472-527) on
+ * sizes only.  offset_dims / mask_dims are {channels, D, H, W} of the offset
+ * and mask tensors; mask_dims may be NULL when no mask is given. */
+int d2c_deform_conv3d_check(const d2c_conv_desc* desc, const int64_t offset_dims[4],
+                            const int64_t mask_dims[4]);
+
+/* Scratch bytes needed by `op` (enum d2c_op) for this geometry under the
+ * current math mode and intermediate-element cap. */
+size_t d2c_workspace_bytes(int op, const d2c_conv_desc* desc);
+
+const char* d2c_status_string(int status);
+/* Text of the last CUDA runtime error seen by this thread ("" if none). */
+const char* d2c_last_cuda_error(void);
+
+/* Process-wide math mode (enum d2c_math_mode); returns status. */
+int d2c_set_math_mode(int mode);
+int d2c_get_math_mode(void);
+
+/* dconv_native._ops.config.{get,set}_max_intermediate_elements
+ * (csrc/ops/dconv.cpp:9-11, csrc/ops/dconv3d_gpu.cu:12-14).  Here it caps the
+ * element count of the backward's gradient-column scratch; larger problems are
+ * processed in batch slices. */
+uint64_t d2c_get_max_intermediate_elements(void);
+void d2c_set_max_intermediate_elements(uint64_t n);
+
+/* ---- modulated deformable conv3d ----------------------------------------- */
+
+/* deform_conv3d_forward_cuda, csrc/ops/dconv3d_gpu.cu:460-560.
+ *   x      [B, Cin, D, H, W]
+ *   offset [B, G*3*K, Do, Ho, Wo]   channel 3*(g*K+tap)+{0:z,1:y,2:x}
+ *   mask   [B, G*K,   Do, Ho, Wo]   nullable (== all ones)
+ *   w      [Cout, Cin/groups, kd, kh, kw]
+ *   bias   [Cout]                   nullable
+ *   y      [B, Cout, Do, Ho, Wo]    fully overwritten */
+int d2c_deform_conv3d_fwd(const d2c_conv_desc* desc, const void* x, const void* offset,
+                          const void* mask, const void* w, const void* bias, void* y,
+                          void* workspace, size_t workspace_bytes, d2c_stream_t stream);
+
+/* deform_conv3d_backward_cuda, csrc/ops/dconv3d_gpu.cu:1261-1332.
+ * All five gradients are fully overwritten (no pre-zeroing needed).
+ * grad_mask is ignored when mask is NULL; grad_bias may be NULL. */
+int d2c_deform_conv3d_bwd(const d2c_conv_desc* desc, const void* grad_y, const void* x,
+                          const void* offset, const void* mask, const void* w, void* grad_x,
+                          void* grad_offset, void* grad_mask, void* grad_w, void* grad_bias,
+                          void* workspace, size_t workspace_bytes, d2c_stream_t stream);
+
+/* Parity probe: the integer corner (floor) coordinates the kernels use.
+ * Same coordinate formation as csrc/ops/dconv3d_gpu.cu:192-194 followed by the
+ * floor of :63-65.  corners is int32 [B, G*K, 3, Do*Ho*Wo] (z0, y0, x0). */
+int d2c_deform_conv3d_corners(const d2c_conv_desc* desc, const void* offset, int32_t* corners,
+                              d2c_stream_t stream);
+
+/* ---- dynamic-dilated conv3d (dilation field instead of offsets) ---------- */
+
+/* Fuses offsets_from_size_map (utils/grid.py:72-98; older copy
+ * ops/dconv-native/src/dconv_native/grid.py:62-80) into the deformable conv:
+ *   offset[b, 3*tap+d, v] = base[d][tap] * (s_d[b, v] - 1)
+ * with base = linspace(-dil*(k/2), dil*(k/2), k) per dim, evaluated with the
+ * same two roundings, and never materialised.
+ *   size_map [B, {1,2,2,3}, Do, Ho, Wo] per `field_mode`; one field shared by
+ *   all offset groups; mask [B, G*K, Do,Ho,Wo] nullable. */
+int d2c_dyn_dilated_conv3d_fwd(const d2c_conv_desc* desc, int field_mode, const void* x,
+                               const void* size_map, const void* mask, const void* w,
+                               const void* bias, void* y, void* workspace,
+                               size_t workspace_bytes, d2c_stream_t stream);
+
+/* Backward of the above; grad_size_map has the shape of size_map and equals
+ * the autograd gradient through offsets_from_size_map of the reference's
+ * grad_offset (sum over taps, offset groups and shared dims). */
+int d2c_dyn_dilated_conv3d_bwd(const d2c_conv_desc* desc, int field_mode, const void* grad_y,
+                               const void* x, const void* size_map, const void* mask,
+                               const void* w, void* grad_x, void* grad_size_map,
+                               void* grad_mask, void* grad_w, void* grad_bias, void* workspace,
+                               size_t workspace_bytes, d2c_stream_t stream);
+
+/* Corner probe for the field path (see d2c_deform_conv3d_corners). */
+int d2c_dyn_dilated_conv3d_corners(const d2c_conv_desc* desc, int field_mode,
+                                   const void* size_map, int32_t* corners, d2c_stream_t stream);
+
+/* ---- depthwise conv3d ------------------------------------------------------ */
+
+/* For the depthwise entry points desc->groups is ignored (groups == Cin),
+ * out_channels must be a multiple of in_channels (channel multiplier) and
+ * w is [Cout, 1, kd, kh, kw]; dtype may be F16/F32/F64. */
+
+/* conv_depthwise3d_cuda, csrc/grouped_conv3d.cu:385-449
+ * (fast_depthwise_conv3d._ops.depthwise_separable_conv3d forward). */
+int d2c_depthwise_conv3d_fwd(const d2c_conv_desc* desc, const void* x, const void* w,
+                             const void* bias, void* y, d2c_stream_t stream);
+
+/* conv_depthwise3d_backward_cuda, csrc/grouped_conv3d.cu:513-678.  Any of
+ * grad_x / grad_w / grad_bias may be NULL (the reference's output_mask). */
+int d2c_depthwise_conv3d_bwd(const d2c_conv_desc* desc, const void* grad_y, const void* x,
+                             const void* w, void* grad_x, void* grad_w, void* grad_bias,
+                             void* workspace, size_t workspace_bytes, d2c_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* D2CONV3D_H_ */
