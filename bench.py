@@ -1,0 +1,364 @@
+"""Benchmark of the deformable-conv3d hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--mode auto|fp32|bf16x3|bf16] [--impl reference]
+
+One "step" is one pass of the hot path over one batch of synthetic input: forward plus full
+backward (all five gradients) of the modulated deformable conv3d layer of the headline
+configuration -- B=2 clips per GPU, Cin=Cout=512, T=8, H=30, W=54, 3x3x3, pad 1, 8 deformable
+groups, offsets ~ N(0, 2 voxels), mask = sigmoid(N(0,1)), Kaiming-normal weights, fp32 tensors.
+With N > 1 (launched by torchrun, one rank per GPU) every rank owns its own clips (weak scaling,
+no data-path collective) and only grad_weight/grad_bias are all-reduced over NCCL inside the step.
+
+Prints ONE JSON line (rank 0).  `value` = contraction TFLOP/s of the whole job with inputs
+resident in HBM (3 x 2*B*V*Cout*Cin*K flops per step: forward, dcol and dW contractions);
+`e2e` = the same metric with host buffers (pinned H2D of the step's inputs, D2H of its results,
+inside the timed region); `roofline` describes the dominant kernel phase as timed by the
+library's own CUDA events during the timed steps; `cpu_baseline` is the CPU restatement of the
+reference algorithm (oracle/) on a bounded sample of the same workload.
+
+`--impl reference` times that CPU restatement alone on the host cores (the reference op has no
+CPU implementation and cannot be built without its GPU toolchain here), rank 0 only.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOAD = dict(name="C2 modulated deformable conv3d 512->512, 8x30x54, 3x3x3 pad 1, G=8, B=2 clips/GPU, fwd+bwd",
+                B=2, Cin=512, Cout=512, dims=(8, 30, 54), k=3, pad=1, G=8, offset_std=2.0)
+METRIC = "deform_conv3d_layer_fwd_bwd_tflops"
+UNIT = "TFLOP/s"
+
+
+def fwd_flops(B, Cin, Cout, V, K, groups=1):
+    return 2.0 * B * V * Cout * (Cin // groups) * K
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm_gbs=p["hbm_gbs"], tensor_burst=p["bf16_tflops"], tensor_sustained=p["bf16_tflops_sustained"],
+                    source="measured")
+    return dict(hbm_gbs=6650.0, tensor_burst=1590.0, tensor_sustained=1400.0, source="fallback")
+
+
+def make_inputs(seed, wl, B=None, dims=None):
+    """Seeded synthetic inputs generated on the host in fp32 (same bits for CPU and GPU paths)."""
+    from tests._util import make_problem
+    p = make_problem(seed, B or wl["B"], wl["Cin"], wl["Cout"], dims or wl["dims"], k=wl["k"], padding=wl["pad"],
+                     G=wl["G"], dtype=np.float32, offset_std=wl["offset_std"])
+    p["bias"] = np.zeros_like(p["bias"])
+    return p
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [s.strip() for s in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx = float(f[2])
+            except ValueError:
+                continue
+            for nm, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ---- CPU arm (oracle) ----------------------------------------------------------------------------
+
+SAMPLE_LADDER = [(8, 30), (4, 30), (2, 30), (2, 15), (2, 8), (2, 4)]
+
+
+def cpu_step(orc, p):
+    kw = dict(stride=1, padding=1, dilation=1, groups=1, offset_groups=WORKLOAD["G"])
+    orc.deform_conv3d_fwd(p["x"], p["geo"], p["mask"], p["weight"], p["bias"], **kw)
+    orc.deform_conv3d_bwd(p["gy"], p["x"], p["geo"], p["mask"], p["weight"], True, **kw)
+
+
+def cpu_arm(steps, warmup, budget_s):
+    """Times the oracle (forward + backward) on a slab of one clip of the workload, picked from a
+    ladder so that warmup+steps fit the time budget.  Returns (TFLOP/s, ms per step, sample text)."""
+    from oracle import oracle as orc
+    wl = WORKLOAD
+    cores = os.cpu_count() or 1
+    probe = make_inputs(5, wl, B=1, dims=(2, 4, wl["dims"][2]))
+    cpu_step(orc, probe)
+    t0 = time.perf_counter(); cpu_step(orc, probe); tp = time.perf_counter() - t0
+    per_voxel = tp / (2 * 4 * wl["dims"][2])
+    target = budget_s / max(1, steps + warmup)
+    d, h = SAMPLE_LADDER[-1]
+    for dd, hh in SAMPLE_LADDER:
+        if per_voxel * dd * hh * wl["dims"][2] <= target:
+            d, h = dd, hh
+            break
+    p = make_inputs(6, wl, B=1, dims=(d, h, wl["dims"][2]))
+    for _ in range(warmup):
+        cpu_step(orc, p)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu_step(orc, p)
+    dt = (time.perf_counter() - t0) / steps
+    V = d * h * wl["dims"][2]
+    flops = 3 * fwd_flops(1, wl["Cin"], wl["Cout"], V, 27)
+    sample = (f"1 clip, {d}x{h}x{wl['dims'][2]} slab of the workload volume (same channels, groups, kernel), "
+              f"fwd+bwd, fp32, OpenMP on {cores} threads")
+    return flops / dt / 1e12, dt * 1e3, sample, cores
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    val, ms, sample, cores = cpu_arm(args.steps, args.warmup, budget_s=150.0)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": {"workload": WORKLOAD["name"], "l2": "host run"},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+        "note": "the reference op is CUDA-only; this arm times the CPU restatement of its algorithm (oracle/)",
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---- GPU arm ---------------------------------------------------------------------------------------
+
+PHASE_WORK = {
+    # phase-name prefix -> (bound, work per launch as a function of (F, bytes...))
+    "fwd": ("tensor", "F"), "bwd_dcol": ("tensor", "F"), "bwd_dw": ("tensor", "F"), "bwd_fused": ("tensor", "2F"),
+    "bwd_coord_grad": ("hbm", "coord_bytes"), "bwd_col2im": ("hbm", "col2im_bytes"),
+}
+
+
+def run_gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+
+    import d2conv3d_b200
+    from d2conv3d_b200 import _lib, dconv_native
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.gpus != world:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch N>1 with torchrun (one rank per GPU)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.lib()
+    d2conv3d_b200.set_math_mode(args.mode)
+    wl = WORKLOAD
+    peaks = measured_peaks()
+
+    p = make_inputs(1002 + rank, wl)
+    host = {k: torch.from_numpy(p[k]).pin_memory() for k in ("x", "geo", "mask", "gy")}
+    x, off, mask, gy = (host[k].to(dev) for k in ("x", "geo", "mask", "gy"))
+    w = torch.from_numpy(make_inputs(1002, wl)["weight"]).to(dev)      # weights replicated across ranks
+    bias = torch.zeros(wl["Cout"], device=dev)
+    for t in (x, off, mask, w, bias):
+        t.requires_grad_(True)
+    V = wl["dims"][0] * wl["dims"][1] * wl["dims"][2]
+    F = fwd_flops(wl["B"], wl["Cin"], wl["Cout"], V, 27)
+    s = 4
+    coord_bytes = s * (wl["B"] * wl["Cin"] * 27 * V + wl["B"] * wl["Cin"] * V + 2 * wl["B"] * wl["G"] * 4 * 27 * V)
+    col2im_bytes = s * (wl["B"] * wl["Cin"] * 27 * V + wl["B"] * wl["G"] * 4 * 27 * V + wl["B"] * wl["Cin"] * V)
+    work = {"F": F, "2F": 2 * F, "coord_bytes": coord_bytes, "col2im_bytes": col2im_bytes}
+
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)      # 256 MB > 126 MB L2
+
+    def step():
+        for t in (x, off, mask, w, bias):
+            t.grad = None
+        y = dconv_native.deform_conv3d(x, off, mask, w, bias, 1, wl["pad"], 1, 1, wl["G"])
+        y.backward(gy)
+        if world > 1:
+            dist.all_reduce(w.grad)
+            dist.all_reduce(bias.grad)
+        return y
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        flush.zero_()
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    _lib.profile_read()
+    _lib.profile_enable(True)
+    launches0 = _lib.launch_count()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    barrier()
+    for i in range(args.steps):
+        flush.zero_()                      # L2 flush between timed iterations, outside the event pair
+        ev[i][0].record()
+        step()
+        ev[i][1].record()
+    barrier()
+    launches = _lib.launch_count() - launches0
+    _lib.profile_enable(False)
+    phases = _lib.profile_read()
+    clocks = sampler.stop() if rank == 0 else None
+    total_ms = sum(a.elapsed_time(b) for a, b in ev)
+    tt = torch.tensor([total_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+    total_ms = float(tt.item())
+    ms_per_step = total_ms / args.steps
+    value = 3 * F * world / (ms_per_step * 1e-3) / 1e12
+
+    # ---- end-to-end with host buffers: pinned H2D of the step's inputs, D2H of its results ----
+    outs = {k: torch.empty_like(v, device="cpu").pin_memory() for k, v in
+            (("y", gy), ("gx", x), ("goff", off), ("gmask", mask), ("gw", w))}
+    h2d = sum(host[k].numel() * 4 for k in host)
+    d2h = sum(outs[k].numel() * 4 for k in outs)
+
+    def e2e_step():
+        xs, os_, ms_, gys = (host[k].to(dev, non_blocking=True) for k in ("x", "geo", "mask", "gy"))
+        for t in (xs, os_, ms_):
+            t.requires_grad_(True)
+        w.grad = None
+        y = dconv_native.deform_conv3d(xs, os_, ms_, w, bias, 1, wl["pad"], 1, 1, wl["G"])
+        y.backward(gys)
+        if world > 1:
+            dist.all_reduce(w.grad)
+        outs["y"].copy_(y.detach(), non_blocking=True)
+        outs["gx"].copy_(xs.grad, non_blocking=True)
+        outs["goff"].copy_(os_.grad, non_blocking=True)
+        outs["gmask"].copy_(ms_.grad, non_blocking=True)
+        outs["gw"].copy_(w.grad, non_blocking=True)
+
+    e2e_steps = max(1, min(args.steps, 10))
+    e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    te = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_ms = float(te.item()) / e2e_steps
+    e2e_value = 3 * F * world / (e2e_ms * 1e-3) / 1e12
+
+    if rank == 0:
+        # ---- roofline of the dominant kernel phase (library events over the timed steps) ----
+        agg = {}
+        for name, ms in phases:
+            a = agg.setdefault(name, [0, 0.0])
+            a[0] += 1; a[1] += ms
+        phase_summary = {n: {"launches": c, "ms_total": round(t, 4), "ms_avg": round(t / c, 4)} for n, (c, t) in agg.items()}
+        roofline = None
+        if agg:
+            dom = max(agg, key=lambda n: agg[n][1])
+            avg_ms = agg[dom][1] / agg[dom][0]
+            bound, key = "hbm", None
+            for prefix, (bnd, k) in PHASE_WORK.items():
+                if dom.startswith(prefix):
+                    bound, key = bnd, k
+            if key is not None:
+                if bound == "tensor":
+                    achieved = work[key] / (avg_ms * 1e-3) / 1e12
+                    peak, unit = peaks["tensor_sustained"], "TFLOP/s"
+                else:
+                    achieved = work[key] / (avg_ms * 1e-3) / 1e9
+                    peak, unit = peaks["hbm_gbs"], "GB/s"
+                roofline = {"kernel": dom, "bound": bound, "achieved": achieved, "peak": peak, "unit": unit,
+                            "frac": achieved / peak, "traffic": None, "ms_per_launch": avg_ms,
+                            "peak_source": peaks["source"] + (" (bf16 dense, sustained)" if bound == "tensor" else " (copy)")}
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            val, ms, sample, cores = cpu_arm(1, 1, budget_s=40.0)
+            cpu = {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample, "ms_per_sample_step": ms}
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "math_mode": _lib.get_math_mode(), "data": "synthetic",
+            "config": {"workload": wl["name"], "l2": "256 MB buffer written between timed iterations",
+                       "collective": "all-reduce of grad_weight+grad_bias (NCCL)" if world > 1 else "none"},
+            "clips_per_s": wl["B"] * world / (ms_per_step * 1e-3),
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms},
+            "gpu_launches": int(launches), "roofline": roofline, "phases": phase_summary, "cpu_baseline": cpu,
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--mode", default="auto", choices=["auto", "fp32", "bf16x3", "bf16"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

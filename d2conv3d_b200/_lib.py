@@ -31,6 +31,12 @@ class ConvDesc(ctypes.Structure):
         "dil_d", "dil_h", "dil_w", "groups", "offset_groups")]
 
 
+class ProfileRecord(ctypes.Structure):
+    """d2c_profile_record"""
+
+    _fields_ = [("name", ctypes.c_char_p), ("ms", ctypes.c_float)]
+
+
 _lib = None
 
 
@@ -52,6 +58,9 @@ def lib():
         L.d2c_status_string.argtypes = [i32]
         L.d2c_status_string.restype = ctypes.c_char_p
         L.d2c_last_cuda_error.restype = ctypes.c_char_p
+        L.d2c_launch_count.restype = ctypes.c_uint64
+        L.d2c_profile_enable.argtypes = [i32]
+        L.d2c_profile_read.argtypes = [ctypes.POINTER(ProfileRecord), i32, ctypes.POINTER(i32)]
         L.d2c_set_math_mode.argtypes = [i32]
         L.d2c_get_max_intermediate_elements.restype = ctypes.c_uint64
         L.d2c_set_max_intermediate_elements.argtypes = [ctypes.c_uint64]
@@ -122,3 +131,20 @@ def set_math_mode(mode):
 def get_math_mode():
     code = lib().d2c_get_math_mode()
     return {v: k for k, v in MATH_MODES.items()}[code]
+
+
+def launch_count():
+    """Kernels launched by the library in this process so far."""
+    return int(lib().d2c_launch_count())
+
+
+def profile_enable(on=True):
+    check(lib().d2c_profile_enable(1 if on else 0), "profile_enable")
+
+
+def profile_read(max_records=65536):
+    """[(phase name, milliseconds)] since the last read; synchronises with the device."""
+    recs = (ProfileRecord * max_records)()
+    n = ctypes.c_int(0)
+    check(lib().d2c_profile_read(recs, max_records, ctypes.byref(n)), "profile_read")
+    return [(recs[i].name.decode(), float(recs[i].ms)) for i in range(n.value)]

@@ -2,6 +2,8 @@
 // sequencing.  See include/d2conv3d.h for the contract of every entry point.
 #include <atomic>
 #include <cstring>
+#include <mutex>
+#include <vector>
 
 #include "d2c_common.cuh"
 #include "deform_generic.cuh"
@@ -13,6 +15,23 @@ static thread_local char g_last_cuda_error[256] = "";
 void set_last_cuda_error(cudaError_t e) {
   std::strncpy(g_last_cuda_error, cudaGetErrorString(e), sizeof(g_last_cuda_error) - 1);
   cudaGetLastError();  // clear the sticky-free error state
+}
+
+static std::atomic<unsigned long long> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+struct ProfMark { const char* name; cudaEvent_t ev; };
+static std::atomic<bool> g_prof_on{false};
+static std::mutex g_prof_mu;
+static std::vector<ProfMark> g_prof;
+void prof_mark(cudaStream_t st, const char* name) {
+  if (!g_prof_on.load(std::memory_order_relaxed)) return;
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  if (g_prof.size() >= 65536) return;
+  cudaEvent_t ev;
+  if (cudaEventCreate(&ev) != cudaSuccess) return;
+  cudaEventRecord(ev, st);
+  g_prof.push_back({name, ev});
 }
 
 static std::atomic<int> g_math_mode{D2C_MATH_AUTO};
@@ -160,6 +179,30 @@ const char* d2c_status_string(int status) {
 }
 
 const char* d2c_last_cuda_error(void) { return g_last_cuda_error; }
+
+uint64_t d2c_launch_count(void) { return g_launches.load(); }
+
+int d2c_profile_enable(int on) {
+  g_prof_on.store(on != 0);
+  return D2C_OK;
+}
+
+int d2c_profile_read(d2c_profile_record* records, int max_records, int* n_records) {
+  if (!n_records || (max_records > 0 && !records)) return D2C_ERR_NULL;
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  int n = 0, rc = D2C_OK;
+  if (!g_prof.empty()) rc = check_cuda(cudaEventSynchronize(g_prof.back().ev));
+  for (size_t i = 0; i + 1 < g_prof.size() && rc == D2C_OK; ++i) {
+    if (!g_prof[i].name) continue;
+    float ms = 0.f;
+    rc = check_cuda(cudaEventElapsedTime(&ms, g_prof[i].ev, g_prof[i + 1].ev));
+    if (n < max_records) records[n++] = {g_prof[i].name, ms};
+  }
+  for (auto& m : g_prof) cudaEventDestroy(m.ev);
+  g_prof.clear();
+  *n_records = n;
+  return rc;
+}
 
 int d2c_set_math_mode(int mode) {
   if (mode < D2C_MATH_AUTO || mode > D2C_MATH_BF16) return D2C_ERR_MODE;

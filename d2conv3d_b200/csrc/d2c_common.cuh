@@ -211,7 +211,18 @@ inline int check_cuda(cudaError_t e) {
     int _rc = ::d2c::check_cuda((expr));                  \
     if (_rc) return _rc;                                  \
   } while (0)
-#define D2C_LAUNCH_CHECK() D2C_CUDA_TRY(cudaGetLastError())
+// Every kernel launch of the library goes through this: counts it and checks it.
+void count_launch();
+#define D2C_LAUNCH_CHECK()               \
+  do {                                   \
+    ::d2c::count_launch();               \
+    D2C_CUDA_TRY(cudaGetLastError());    \
+  } while (0)
+
+// Phase profiling (off by default): when enabled, a CUDA event is recorded on the
+// caller's stream at every mark; the phase `name` lasts until the next mark.
+// name == nullptr closes the current phase.
+void prof_mark(cudaStream_t st, const char* name);
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 

@@ -372,8 +372,10 @@ int launch_fwd_generic(const Geom& g, const Coords& coords, const T* x, const T*
                        const T* bias, T* y, cudaStream_t st) {
   dim3 grid((g.V + kTileV - 1) / kTileV, (g.cout_g + kTileN - 1) / kTileN, g.B * g.groups);
   if (grid.y > 65535 || grid.z > 65535) return D2C_ERR_TOO_LARGE;
+  prof_mark(st, "fwd_generic");
   fwd_generic_kernel<T, Coords><<<grid, kGemmThreads, 0, st>>>(g, coords, x, mask, w, bias, y);
   D2C_LAUNCH_CHECK();
+  prof_mark(st, nullptr);
   return D2C_OK;
 }
 
@@ -391,6 +393,7 @@ int launch_bwd_generic(const Geom& g, const Coords& coords, const T* gy, const T
                        const T* w, T* grad_x, T* grad_coord, size_t grad_coord_elems, T* grad_mask,
                        T* grad_w, T* grad_bias, T* dcol, int slice_clips, cudaStream_t st) {
   const int R = g.cin_g * g.K;
+  prof_mark(st, "bwd_zero_fill");
   D2C_CUDA_TRY(cudaMemsetAsync(grad_x, 0, sizeof(T) * (size_t)g.B * g.Cin * g.Vin, st));
   D2C_CUDA_TRY(cudaMemsetAsync(grad_w, 0, sizeof(T) * (size_t)g.Cout * R, st));
   if (FieldOut) D2C_CUDA_TRY(cudaMemsetAsync(grad_coord, 0, sizeof(T) * grad_coord_elems, st));
@@ -398,12 +401,15 @@ int launch_bwd_generic(const Geom& g, const Coords& coords, const T* gy, const T
     const int nb = (g.B - b0 < slice_clips) ? g.B - b0 : slice_clips;
     dim3 grid((g.V + kTileV - 1) / kTileV, (R + kTileN - 1) / kTileN, nb * g.groups);
     if (grid.y > 65535 || grid.z > 65535) return D2C_ERR_TOO_LARGE;
+    prof_mark(st, "bwd_dcol_generic");
     dcol_generic_kernel<T><<<grid, kGemmThreads, 0, st>>>(g, b0, gy, w, dcol);
     D2C_LAUNCH_CHECK();
+    prof_mark(st, "bwd_coord_grad_generic");
     coord_grad_generic_kernel<T, Coords, FieldOut>
         <<<grid_1d((long long)nb * g.G * g.K * g.V, 256), 256, 0, st>>>(g, coords, b0, nb, dcol, x, mask,
                                                                        grad_coord, grad_mask);
     D2C_LAUNCH_CHECK();
+    prof_mark(st, "bwd_col2im_generic");
     col2im_generic_kernel<T, Coords>
         <<<grid_1d((long long)nb * g.Cin * g.K * g.V, 256), 256, 0, st>>>(g, coords, b0, nb, dcol, mask, grad_x);
     D2C_LAUNCH_CHECK();
@@ -420,13 +426,16 @@ int launch_bwd_generic(const Geom& g, const Coords& coords, const T* gy, const T
     nsplit = (g.V + v_per_split - 1) / v_per_split;
     dim3 grid((R + kTileV - 1) / kTileV, (g.cout_g + kTileN - 1) / kTileN, g.B * g.groups * nsplit);
     if (grid.y > 65535 || grid.z > 65535) return D2C_ERR_TOO_LARGE;
+    prof_mark(st, "bwd_dw_generic");
     dw_generic_kernel<T, Coords><<<grid, kGemmThreads, 0, st>>>(g, coords, v_per_split, gy, x, mask, grad_w);
     D2C_LAUNCH_CHECK();
   }
   if (grad_bias) {
+    prof_mark(st, "bwd_grad_bias");
     grad_bias_kernel<T><<<g.Cout, 256, 0, st>>>(g.B, g.Cout, g.V, gy, grad_bias);
     D2C_LAUNCH_CHECK();
   }
+  prof_mark(st, nullptr);
   return D2C_OK;
 }
 

@@ -232,11 +232,13 @@ static unsigned blocks_for(long long total) {
 template <typename T>
 static int dw_fwd_t(const Geom& g, const void* x, const void* w, const void* bias, void* y, cudaStream_t st) {
   const long long total = (long long)g.B * g.Cout * g.V;
+  prof_mark(st, "depthwise_fwd");
   if (g.kd == 3 && g.kh == 3 && g.kw == 3)
     dw_fwd_kernel<T, 3, 3, 3><<<blocks_for(total), 256, 0, st>>>(g, (const T*)x, (const T*)w, (const T*)bias, (T*)y);
   else
     dw_fwd_kernel<T, 0, 0, 0><<<blocks_for(total), 256, 0, st>>>(g, (const T*)x, (const T*)w, (const T*)bias, (T*)y);
   D2C_LAUNCH_CHECK();
+  prof_mark(st, nullptr);
   return D2C_OK;
 }
 
@@ -247,6 +249,7 @@ static int dw_bwd_t(const Geom& g, const void* gy, const void* x, const void* w,
   const bool k333 = g.kd == 3 && g.kh == 3 && g.kw == 3;
   if (gx) {
     const long long total = (long long)g.B * g.Cin * g.Vin;
+    prof_mark(st, "depthwise_bwd_input");
     if (k333)
       dw_bwd_input_kernel<T, 3, 3, 3><<<blocks_for(total), 256, 0, st>>>(g, (const T*)gy, (const T*)w, (T*)gx);
     else
@@ -256,6 +259,7 @@ static int dw_bwd_t(const Geom& g, const void* gy, const void* x, const void* w,
   if (gw) {
     A* partial = (A*)ws;
     const long long n = (long long)g.Cout * g.K;
+    prof_mark(st, "depthwise_bwd_weight");
     if (k333) {
       D2C_CUDA_TRY(cudaMemsetAsync(partial, 0, sizeof(A) * (size_t)n, st));
       // enough (channel, clip-slice) blocks to fill the GPU a few times over
@@ -273,9 +277,11 @@ static int dw_bwd_t(const Geom& g, const void* gy, const void* x, const void* w,
     D2C_LAUNCH_CHECK();
   }
   if (gbias) {
+    prof_mark(st, "depthwise_bwd_bias");
     dw_grad_bias_kernel<T><<<g.Cout, 256, 0, st>>>(g.B, g.Cout, g.V, (const T*)gy, (T*)gbias);
     D2C_LAUNCH_CHECK();
   }
+  prof_mark(st, nullptr);
   return D2C_OK;
 }
 

@@ -120,6 +120,22 @@ const char* d2c_last_cuda_error(void);
 int d2c_set_math_mode(int mode);
 int d2c_get_math_mode(void);
 
+/* Number of kernels this library has launched in this process so far. */
+uint64_t d2c_launch_count(void);
+
+/* Phase timing, the library's counterpart of the reference's `Timer` helper
+ * (utils/util.py:27-53) and benchmark loop (csrc/benchmark.cpp:13-25): while
+ * enabled, every entry point brackets its phases (kernels or kernel groups) with
+ * CUDA events recorded on the caller's stream.  d2c_profile_read synchronises with
+ * the last event, writes up to `max_records` {name, milliseconds} pairs in launch
+ * order, stores the count in *n_records and clears the log. */
+typedef struct d2c_profile_record {
+  const char* name; /* static string owned by the library */
+  float ms;
+} d2c_profile_record;
+int d2c_profile_enable(int on);
+int d2c_profile_read(d2c_profile_record* records, int max_records, int* n_records);
+
 /* dconv_native._ops.config.{get,set}_max_intermediate_elements
  * (csrc/ops/dconv.cpp:9-11, csrc/ops/dconv3d_gpu.cu:12-14).  Here it caps the
  * element count of the backward's gradient-column scratch; larger problems are

@@ -1,0 +1,78 @@
+"""GPU parity tests of the depthwise conv3d kernels (through the C ABI) against the CPU
+oracle, following ops/fast-depthwise-conv3d/test/test_conv3d_depthwise.py:25-96:
+stride x dilation in {1,2}^2, channel multiplier {1,2}, float/double/half with
+atol 1e-5 / 1e-5 / 1e-2."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+ATOL = {torch.float32: 1e-5, torch.float64: 1e-5, torch.float16: 1e-2}
+
+
+@pytest.fixture(scope="module")
+def dw():
+    from d2conv3d_b200 import _lib, fast_depthwise_conv3d
+    _lib.lib()
+    return fast_depthwise_conv3d
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64, torch.float16])
+@pytest.mark.parametrize("stride,dilation", [(1, 1), (2, 1), (1, 2), (2, 2)])
+@pytest.mark.parametrize("mult,bias", [(1, True), (2, False)])
+def test_depthwise_vs_oracle(dw, dtype, stride, dilation, mult, bias):
+    torch.manual_seed(0)
+    pad = dilation
+    m = dw.DepthwiseConv3d(2, 2 * mult, kernel_size=3, bias=bias, stride=stride, padding=pad, dilation=dilation).to("cuda", dtype)
+    x = torch.randn(2, 2, 6, 6, 6, device="cuda", dtype=dtype).div_(2).requires_grad_()
+    y = m(x)
+    gy = torch.randn_like(y) / 2
+    y.backward(gy)
+    np64 = lambda t: t.detach().double().cpu().numpy()
+    wy = orc.depthwise_conv3d_fwd(np64(x), np64(m.weight), np64(m.bias) if bias else None, stride, pad, dilation)
+    wgx, wgw, wgb = orc.depthwise_conv3d_bwd(np64(gy), np64(x), np64(m.weight), bias, stride, pad, dilation)
+    atol = ATOL[dtype]
+    assert y.dtype == dtype
+    assert np.abs(np64(y) - wy).max() <= atol
+    assert np.abs(np64(x.grad) - wgx).max() <= atol
+    assert np.abs(np64(m.weight.grad) - wgw).max() <= atol * (10 if dtype == torch.float16 else 1)
+    if bias:
+        assert np.abs(np64(m.bias.grad) - wgb).max() <= atol * (10 if dtype == torch.float16 else 1)
+
+
+def test_depthwise_other_kernel_shapes_and_larger_tile(dw):
+    torch.manual_seed(1)
+    for k, pad in (((1, 3, 3), (0, 1, 1)), ((3, 5, 3), (1, 2, 1)), (3, 1)):
+        m = dw.DepthwiseConv3d(5, 5, kernel_size=k, padding=pad).to("cuda", torch.float32)
+        x = torch.randn(3, 5, 4, 9, 13, device="cuda").requires_grad_()
+        y = m(x)
+        gy = torch.randn_like(y)
+        y.backward(gy)
+        np32 = lambda t: t.detach().cpu().numpy()
+        wy = orc.depthwise_conv3d_fwd(np32(x), np32(m.weight), np32(m.bias), 1, pad, 1)
+        wgx, wgw, wgb = orc.depthwise_conv3d_bwd(np32(gy), np32(x), np32(m.weight), True, 1, pad, 1)
+        assert np.abs(np32(y) - wy).max() <= 1e-5
+        assert np.abs(np32(x.grad) - wgx).max() <= 1e-5
+        assert np.abs(np32(m.weight.grad) - wgw).max() <= 1e-4 * max(1.0, np.abs(wgw).max())
+        assert np.abs(np32(m.bias.grad) - wgb).max() <= 1e-4 * max(1.0, np.abs(wgb).max())
+
+
+def test_autocast_keeps_half(dw):
+    inp = torch.randn(2, 2, 5, 5, 5).to(dtype=torch.half, device="cuda")
+    conv = dw.DepthwiseConv3d(2, 2, kernel_size=3).cuda()
+    with torch.autocast("cuda"):
+        assert conv(inp).dtype == torch.half
+
+
+def test_padding_mode_replicate(dw):
+    torch.manual_seed(3)
+    conv = dw.DepthwiseConv3d(3, 3, kernel_size=3, padding=1, padding_mode="replicate").cuda()
+    ref = torch.nn.Conv3d(3, 3, 3, padding=1, padding_mode="replicate", groups=3).cuda()
+    ref.load_state_dict(conv.state_dict())
+    x = torch.randn(2, 3, 4, 5, 6, device="cuda")
+    xp = torch.nn.functional.pad(x, (1, 1, 1, 1, 1, 1), mode="replicate")
+    want = orc.depthwise_conv3d_fwd(xp.cpu().numpy(), conv.weight.detach().cpu().numpy(), conv.bias.detach().cpu().numpy())
+    assert np.abs(conv(x).detach().cpu().numpy() - want).max() <= 1e-5
