@@ -133,6 +133,11 @@ def get_math_mode():
     return {v: k for k, v in MATH_MODES.items()}[code]
 
 
+def device_status():
+    """Synchronises and raises if a device-side bounded wait gave up."""
+    check(lib().d2c_device_status(), "device status")
+
+
 def launch_count():
     """Kernels launched by the library in this process so far."""
     return int(lib().d2c_launch_count())

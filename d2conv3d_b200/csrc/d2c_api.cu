@@ -180,6 +180,14 @@ const char* d2c_status_string(int status) {
 
 const char* d2c_last_cuda_error(void) { return g_last_cuda_error; }
 
+int d2c_device_status(void) {
+  int rc = check_cuda(cudaDeviceSynchronize());
+  if (rc) return rc;
+  const int v = sm100_device_status();
+  if (v < 0) return D2C_ERR_CUDA;
+  return v ? D2C_ERR_DEVICE_TIMEOUT : D2C_OK;
+}
+
 uint64_t d2c_launch_count(void) { return g_launches.load(); }
 
 int d2c_profile_enable(int on) {

@@ -18,4 +18,7 @@ int sm100_fwd_field(const Geom& g, int math_mode, const FieldCoords<float>& fc, 
                     const float* mask, const float* w, const float* bias, float* y, void* ws,
                     cudaStream_t st);
 
+// 0 = healthy; 1 = some kernel's bounded wait gave up (sticky); -1 = could not be read.
+int sm100_device_status();
+
 }  // namespace d2c

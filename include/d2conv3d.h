@@ -120,6 +120,11 @@ const char* d2c_last_cuda_error(void);
 int d2c_set_math_mode(int mode);
 int d2c_get_math_mode(void);
 
+/* Synchronises with the device and reports whether any tensor-core kernel of this
+ * process gave up a bounded device-side wait (D2C_ERR_DEVICE_TIMEOUT) since the
+ * library was loaded.  Results of calls made after such an event are undefined. */
+int d2c_device_status(void);
+
 /* Number of kernels this library has launched in this process so far. */
 uint64_t d2c_launch_count(void);
 
