@@ -147,7 +147,7 @@ size_t d2c_workspace_bytes(int op, const d2c_conv_desc* desc) {
       return sm100_fwd_workspace(g, desc->dtype, g_math_mode.load());
     case D2C_OP_DEFORM_BWD:
     case D2C_OP_DYNDIL_BWD: {
-      const size_t fast = sm100_bwd_workspace(g, desc->dtype, g_math_mode.load());
+      const size_t fast = sm100_bwd_workspace(g, desc->dtype, g_math_mode.load(), g_max_intermediate.load());
       const size_t gen = generic_bwd_workspace(g, desc->dtype);
       return fast > gen ? fast : gen;
     }
@@ -183,8 +183,9 @@ const char* d2c_last_cuda_error(void) { return g_last_cuda_error; }
 int d2c_device_status(void) {
   int rc = check_cuda(cudaDeviceSynchronize());
   if (rc) return rc;
-  const int v = sm100_device_status();
-  if (v < 0) return D2C_ERR_CUDA;
+  const int v1 = sm100_device_status(), v2 = sm100_bwd_device_status();
+  if (v1 < 0 || v2 < 0) return D2C_ERR_CUDA;
+  const int v = v1 | v2;
   return v ? D2C_ERR_DEVICE_TIMEOUT : D2C_OK;
 }
 
@@ -261,9 +262,17 @@ int d2c_deform_conv3d_bwd(const d2c_conv_desc* desc, const void* grad_y, const v
   if (rc) return rc;
   if (desc->dtype != D2C_F32 && desc->dtype != D2C_F64) return D2C_ERR_DTYPE;
   cudaStream_t st = (cudaStream_t)stream;
+  const unsigned long long cap = g_max_intermediate.load();
+  if (sm100_bwd_supported(g, desc->dtype, g_math_mode.load(), cap)) {
+    if (!ws_ok(workspace, workspace_bytes, sm100_bwd_workspace(g, desc->dtype, g_math_mode.load(), cap)))
+      return D2C_ERR_WORKSPACE;
+    return sm100_bwd_offsets(g, cap, (const float*)grad_y, (const float*)x, (const float*)offset,
+                             (const float*)mask, (const float*)w, (float*)grad_x, (float*)grad_offset,
+                             (float*)grad_mask, (float*)grad_w, (float*)grad_bias, workspace, st);
+  }
   const size_t need = generic_bwd_workspace(g, desc->dtype);
   if (!ws_ok(workspace, workspace_bytes, need)) return D2C_ERR_WORKSPACE;
-  const int nb = bwd_slice_clips(g, g_max_intermediate.load());
+  const int nb = bwd_slice_clips(g, cap);
   if (desc->dtype == D2C_F32) {
     OffsetCoords<float> oc{(const float*)offset};
     return launch_bwd_generic<float, OffsetCoords<float>, false>(
@@ -351,6 +360,14 @@ int d2c_dyn_dilated_conv3d_bwd(const d2c_conv_desc* desc, int field_mode, const 
   if (desc->dtype == D2C_F32) {
     FieldCoords<float> fc;
     if ((rc = make_field_coords<float>(g, field_mode, size_map, &fc))) return rc;
+    const unsigned long long cap = g_max_intermediate.load();
+    if (sm100_bwd_supported(g, desc->dtype, g_math_mode.load(), cap)) {
+      if (!ws_ok(workspace, workspace_bytes, sm100_bwd_workspace(g, desc->dtype, g_math_mode.load(), cap)))
+        return D2C_ERR_WORKSPACE;
+      return sm100_bwd_field(g, cap, fc, (const float*)grad_y, (const float*)x, (const float*)mask,
+                             (const float*)w, (float*)grad_x, (float*)grad_size_map, gs_elems,
+                             (float*)grad_mask, (float*)grad_w, (float*)grad_bias, workspace, st);
+    }
     return launch_bwd_generic<float, FieldCoords<float>, true>(
         g, fc, (const float*)grad_y, (const float*)x, (const float*)mask, (const float*)w,
         (float*)grad_x, (float*)grad_size_map, gs_elems, (float*)grad_mask, (float*)grad_w,

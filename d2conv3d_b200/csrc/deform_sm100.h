@@ -9,8 +9,6 @@ namespace d2c {
 
 bool sm100_fwd_supported(const Geom& g, int dtype, int math_mode);
 size_t sm100_fwd_workspace(const Geom& g, int dtype, int math_mode);
-size_t sm100_bwd_workspace(const Geom& g, int dtype, int math_mode);
-
 int sm100_fwd_offsets(const Geom& g, int math_mode, const float* x, const float* offset,
                       const float* mask, const float* w, const float* bias, float* y, void* ws,
                       cudaStream_t st);
@@ -18,7 +16,19 @@ int sm100_fwd_field(const Geom& g, int math_mode, const FieldCoords<float>& fc, 
                     const float* mask, const float* w, const float* bias, float* y, void* ws,
                     cudaStream_t st);
 
+// `cap` = maximum number of gradient-column elements held at once (clips are processed in chunks).
+bool sm100_bwd_supported(const Geom& g, int dtype, int math_mode, unsigned long long cap);
+size_t sm100_bwd_workspace(const Geom& g, int dtype, int math_mode, unsigned long long cap);
+int sm100_bwd_offsets(const Geom& g, unsigned long long cap, const float* gy, const float* x, const float* offset,
+                      const float* mask, const float* w, float* grad_x, float* grad_offset, float* grad_mask,
+                      float* grad_w, float* grad_bias, void* ws, cudaStream_t st);
+int sm100_bwd_field(const Geom& g, unsigned long long cap, const FieldCoords<float>& fc, const float* gy,
+                    const float* x, const float* mask, const float* w, float* grad_x, float* grad_size_map,
+                    size_t grad_size_elems, float* grad_mask, float* grad_w, float* grad_bias, void* ws,
+                    cudaStream_t st);
+
 // 0 = healthy; 1 = some kernel's bounded wait gave up (sticky); -1 = could not be read.
 int sm100_device_status();
+int sm100_bwd_device_status();
 
 }  // namespace d2c

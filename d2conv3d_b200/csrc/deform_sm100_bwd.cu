@@ -1,0 +1,512 @@
+// Tensor-core backward of the modulated deformable conv3d for sm_100a (data side):
+//
+//   (a) dcol_sm100_kernel   gradient columns dcol[b, v, (slice, c)] = sum_co grad_out[b, co, v] * W[co, c, tap]
+//                           as a tcgen05 GEMM (bf16 operands, fp32 accumulate in TMEM), voxel-major
+//                           rows so that the 64 channels of one (offset group, tap) slice are contiguous.
+//                           Replaces the reference's cuBLAS call at csrc/ops/dconv3d_gpu.cu:981-999.
+//   (b) sample_grad_kernel  one pass over dcol that produces grad_offset / grad_mask (8 corner dot-products
+//                           per (voxel, group, tap), reduced over channels by warp shuffles) AND scatters
+//                           grad_input with 16-byte vector reductions into a channels-last fp32 buffer.
+//                           Replaces deformable_col2im_coord_gpu_kernel (:756-864) and
+//                           deformable_col2im_gpu_kernel (:562-643).
+//   (c) unstage_grad_input_kernel  channels-last fp32 -> NCDHW.
+//
+// The weight gradient is in deform_sm100_dw.cu.
+#include "deform_generic.cuh"
+#include "deform_sm100.h"
+#include "sm100_ptx.cuh"
+#include "sm100_stage.cuh"
+
+namespace d2c {
+
+namespace {
+
+constexpr int kBM = 128;
+constexpr int kABlockBytes = kBM * 128;       // one 64-wide K block of the grad_out tile: 16 KB
+constexpr int kNBlock = 256;                  // dcol columns per accumulator (4 slices of 64 channels)
+constexpr int kBStageBytes = kNBlock * 128;   // 32 KB
+constexpr int kBStages = 3;
+constexpr int kDcolThreads = 192;             // warps 0-3 epilogue, warp 4 MMA, warp 5 loader
+constexpr int kSmemLimit = 227 * 1024;
+
+__device__ int g_sm100_bwd_status = 0;
+
+// ---- staging ------------------------------------------------------------------------------------
+
+// grad_out [B][Cout][V] fp32 -> per (tile, 64-wide co block) images of 128 rows (voxels) x 128 B (64 co,
+// bf16), 16-byte chunks XOR-swizzled by (row & 7): the byte image of a K-major SW128 A tile.
+// Rows past the end of the clip are zero.
+__global__ void __launch_bounds__(256)
+stage_gy_img_kernel(int Cout, int V, int tiles_per_clip, int b0, const float* __restrict__ gy,
+                    uint8_t* __restrict__ img) {
+  __shared__ float tile[64][129];
+  const int tile_id = blockIdx.x, kb = blockIdx.y, KB = gridDim.y;
+  const int bl = tile_id / tiles_per_clip, v0 = (tile_id % tiles_per_clip) * kBM;
+  const int b = b0 + bl;
+  for (int e = threadIdx.x; e < 64 * 128; e += 256) {
+    const int co = e >> 7, r = e & 127, v = v0 + r;
+    tile[co][r] = (v < V) ? __ldg(gy + ((long long)b * Cout + kb * 64 + co) * V + v) : 0.f;
+  }
+  __syncthreads();
+  uint8_t* dst = img + ((long long)tile_id * KB + kb) * kABlockBytes;
+  for (int e = threadIdx.x; e < 128 * 8; e += 256) {
+    const int r = e >> 3, j = e & 7;
+    uint4 o;
+    o.x = ptx::pack_bf16x2(tile[j * 8 + 0][r], tile[j * 8 + 1][r]);
+    o.y = ptx::pack_bf16x2(tile[j * 8 + 2][r], tile[j * 8 + 3][r]);
+    o.z = ptx::pack_bf16x2(tile[j * 8 + 4][r], tile[j * 8 + 5][r]);
+    o.w = ptx::pack_bf16x2(tile[j * 8 + 6][r], tile[j * 8 + 7][r]);
+    *reinterpret_cast<uint4*>(dst + (r >> 3) * 1024 + (r & 7) * 128 + ((j ^ (r & 7)) << 4)) = o;
+  }
+}
+
+// W [Cout][Cin][K] fp32 -> per (N block of 4 slices, 64-wide co block) images of 256 rows x 128 B:
+// row = slice_local*64 + c, 64 co (bf16) per row, swizzled as above (K-major SW128 B tile, K = co).
+__global__ void __launch_bounds__(256)
+stage_wt_img_kernel(int Cout, int Cin, int K, int cpg, int nh, int S, const float* __restrict__ w,
+                    uint8_t* __restrict__ img) {
+  const int KB = Cout / 64;
+  const long long total = (long long)S * 64 * KB * 8;   // 16-byte chunks
+  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total;
+       e += (long long)gridDim.x * blockDim.x) {
+    const int j = (int)(e & 7);
+    const int kb = (int)((e >> 3) % KB);
+    const long long rowg = (e >> 3) / KB;          // global row = slice*64 + c
+    const int c = (int)(rowg & 63), s = (int)(rowg >> 6);
+    const int h = s % nh, gt = s / nh, tap = gt % K, grp = gt / K;
+    const int cin = grp * cpg + h * 64 + c;
+    float v[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q)
+      v[q] = __ldg(w + ((long long)(kb * 64 + j * 8 + q) * Cin + cin) * K + tap);
+    uint4 o;
+    o.x = ptx::pack_bf16x2(v[0], v[1]); o.y = ptx::pack_bf16x2(v[2], v[3]);
+    o.z = ptx::pack_bf16x2(v[4], v[5]); o.w = ptx::pack_bf16x2(v[6], v[7]);
+    const int nb = s >> 2, row = (s & 3) * 64 + c;
+    uint8_t* dst = img + ((long long)nb * KB + kb) * kBStageBytes + (row >> 3) * 1024 + (row & 7) * 128 +
+                   ((j ^ (row & 7)) << 4);
+    *reinterpret_cast<uint4*>(dst) = o;
+  }
+}
+
+// ---- (a) dcol GEMM ------------------------------------------------------------------------------
+
+struct DcolParams {
+  const uint8_t* gy_img;   // [n_tiles][KB][16 KB]
+  const uint8_t* wt_img;   // [NB][KB][32 KB]
+  float* dcol;             // [clips_in_chunk * V][NT]
+  int V, NT, KB, NB, S;
+  int tiles_per_clip, n_tiles;
+  int tmem_cols;
+};
+
+__global__ void __launch_bounds__(kDcolThreads, 1)
+dcol_sm100_kernel(const DcolParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = ptx::smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - raw);
+  const int a_bytes = p.KB * kABlockBytes;
+  const uint32_t a_base = base, b_base = base + a_bytes, bar_base = b_base + kBStages * kBStageBytes;
+  auto b_full = [&](int s) { return bar_base + 8u * s; };
+  auto b_empty = [&](int s) { return bar_base + 8u * (kBStages + s); };
+  auto acc_full = [&](int a) { return bar_base + 8u * (2 * kBStages + a); };
+  auto acc_empty = [&](int a) { return bar_base + 8u * (2 * kBStages + 2 + a); };
+  const uint32_t a_full = bar_base + 8u * (2 * kBStages + 4), a_empty = bar_base + 8u * (2 * kBStages + 5);
+  const int slot_off = a_bytes + kBStages * kBStageBytes + 8 * (2 * kBStages + 6);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + slot_off);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + slot_off + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kBStages; ++s) { ptx::mbar_init(b_full(s), 1); ptx::mbar_init(b_empty(s), 1); }
+    for (int a = 0; a < 2; ++a) { ptx::mbar_init(acc_full(a), 1); ptx::mbar_init(acc_empty(a), 4); }
+    ptx::mbar_init(a_full, 1);
+    ptx::mbar_init(a_empty, 1);
+    *abort_flag = 0;
+    ptx::fence_mbar_init();
+  }
+  if (warp == 0) {
+    __syncwarp();
+    ptx::tmem_alloc(ptx::smem_u32((const void*)tmem_slot), (uint32_t)p.tmem_cols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp < 4) {
+    // ---- epilogue: TMEM -> dcol (each thread owns one voxel row; 128 B contiguous per 32 columns)
+    uint32_t q = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < p.n_tiles; tile += gridDim.x) {
+      const int bl = tile / p.tiles_per_clip, v0 = (tile % p.tiles_per_clip) * kBM;
+      const int v = v0 + warp * 32 + lane;
+      float* row = p.dcol + ((long long)bl * p.V + v) * p.NT;
+      for (int nb = 0; nb < p.NB; ++nb, ++q) {
+        const int acc = q & 1;
+        const int ncols = min(kNBlock, p.NT - nb * kNBlock);
+        if (!ptx::mbar_wait(acc_full(acc), (q >> 1) & 1, abort_flag)) { ok = false; break; }
+        ptx::tc_fence_after();
+        for (int c0 = 0; c0 < ncols; c0 += 32) {
+          uint32_t r[32];
+          ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(acc * kNBlock + c0), r);
+          ptx::tmem_ld_wait();
+          if (v < p.V) {
+            float4* dst = reinterpret_cast<float4*>(row + nb * kNBlock + c0);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              dst[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
+                                   __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+          }
+        }
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(acc_empty(acc));
+      }
+    }
+  } else if (warp == 4) {
+    if (lane == 0) {
+      uint32_t q = 0, kbc = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < p.n_tiles; tile += gridDim.x, ++it) {
+        if (!ptx::mbar_wait(a_full, it & 1, abort_flag)) break;
+        ptx::tc_fence_after();
+        for (int nb = 0; ok && nb < p.NB; ++nb, ++q) {
+          const int acc = q & 1;
+          const int ncols = min(kNBlock, p.NT - nb * kNBlock);
+          if (!ptx::mbar_wait(acc_empty(acc), ((q >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+          ptx::tc_fence_after();
+          const uint32_t idesc = ptx::umma_idesc_bf16_f32(kBM, ncols);
+          for (int kb = 0; kb < p.KB; ++kb, ++kbc) {
+            const int sb = kbc % kBStages;
+            if (!ptx::mbar_wait(b_full(sb), (kbc / kBStages) & 1, abort_flag)) { ok = false; break; }
+            ptx::tc_fence_after();
+            const uint64_t adesc = ptx::umma_desc_kmajor_sw128(a_base + kb * kABlockBytes);
+            const uint64_t bdesc = ptx::umma_desc_kmajor_sw128(b_base + sb * kBStageBytes);
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              ptx::umma_bf16(tmem_base + (uint32_t)(acc * kNBlock), adesc + (uint64_t)(2 * k),
+                             bdesc + (uint64_t)(2 * k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            ptx::umma_commit(b_empty(sb));
+          }
+          if (ok) ptx::umma_commit(acc_full(acc));
+        }
+        if (ok) ptx::umma_commit(a_empty);
+      }
+    }
+  } else {
+    if (lane == 0) {
+      uint32_t kbc = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < p.n_tiles; tile += gridDim.x, ++it) {
+        if (!ptx::mbar_wait(a_empty, (it & 1) ^ 1, abort_flag)) break;
+        ptx::mbar_arrive_expect_tx(a_full, (uint32_t)a_bytes);
+        const uint8_t* asrc = p.gy_img + (long long)tile * a_bytes;
+        for (int off = 0; off < a_bytes; off += 32768)
+          ptx::bulk_g2s(a_base + off, asrc + off, (uint32_t)min(32768, a_bytes - off), a_full);
+        for (int nb = 0; ok && nb < p.NB; ++nb) {
+          const int ncols = min(kNBlock, p.NT - nb * kNBlock);
+          for (int kb = 0; kb < p.KB; ++kb, ++kbc) {
+            const int sb = kbc % kBStages;
+            if (!ptx::mbar_wait(b_empty(sb), ((kbc / kBStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
+            ptx::mbar_arrive_expect_tx(b_full(sb), (uint32_t)(ncols * 128));
+            ptx::bulk_g2s(b_base + sb * kBStageBytes, p.wt_img + ((long long)nb * p.KB + kb) * kBStageBytes,
+                          (uint32_t)(ncols * 128), b_full(sb));
+          }
+        }
+      }
+      // drain: never exit with a bulk copy in flight
+      const uint32_t issued = kbc;
+      for (uint32_t qq = (issued > (uint32_t)kBStages ? issued - kBStages : 0); qq < issued; ++qq) {
+        const long long t0 = clock64();
+        while (!ptx::mbar_try_wait(b_full(qq % kBStages), (qq / kBStages) & 1))
+          if (clock64() - t0 > ptx::kWaitBudgetCycles) break;
+      }
+      if (it > 0) {
+        const long long t0 = clock64();
+        while (!ptx::mbar_try_wait(a_full, (it - 1) & 1))
+          if (clock64() - t0 > ptx::kWaitBudgetCycles) break;
+      }
+    }
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(&g_sm100_bwd_status, 1);
+  if (warp == 0) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+  }
+}
+
+// ---- (b) sampling gradient + scatter ---------------------------------------------------------------
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+
+// 8 threads per (clip, offset group, tap, voxel): thread j owns channels [8j, 8j+8) of each 64-channel slice.
+// Voxels are the fastest-varying item index, so offset / mask reads and gradient writes coalesce.
+template <typename Coords, bool FieldOut>
+__global__ void __launch_bounds__(256)
+sample_grad_kernel(Geom g, Coords coords, int b0, int nbc, int nh, int NT, const float* __restrict__ dcol,
+                   const __nv_bfloat16* __restrict__ x_cl, const float* __restrict__ mask,
+                   float* __restrict__ grad_coord, float* __restrict__ grad_mask, float* __restrict__ gx_cl) {
+  const long long n_items = (long long)nbc * g.G * g.K * g.V;
+  const int j = threadIdx.x & 7;
+  const long long items_per_sweep = (long long)gridDim.x * 32;
+  for (long long item0 = (long long)blockIdx.x * 32; item0 < n_items; item0 += items_per_sweep) {
+    const long long item = item0 + (threadIdx.x >> 3);
+    const bool active = item < n_items;
+    float G[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) G[q] = 0.f;
+    Sample<float> s;
+    float a[8], m = 1.f;
+    int v = 0, tap = 0, grp = 0, b = b0;
+    if (active) {
+      v = (int)(item % g.V);
+      tap = (int)((item / g.V) % g.K);
+      grp = (int)((item / ((long long)g.V * g.K)) % g.G);
+      const int bl = (int)(item / ((long long)g.V * g.K * g.G));
+      b = b0 + bl;
+      int bz, by, bx;
+      voxel_tap_base(g, v, tap, bz, by, bx);
+      float z, y, x;
+      coords.get(g, b, grp, tap, v, bz, by, bx, z, y, x);
+      s = make_sample(g, z, y, x);
+      sample_weights(s, a);
+      if (mask) m = __ldg(mask + (((long long)b * g.G + grp) * g.K + tap) * g.V + v);
+      // scatter weights of the reference's col2im: (1-|z-zp|)(1-|y-yp|)(1-|x-xp|), corners at distance
+      // exactly 1 excluded (dconv3d_gpu.cu:626-637)
+      const float wz[2] = {sub_rn(1.f, s.fz), sub_rn(1.f, s.gz)};
+      const float wy[2] = {sub_rn(1.f, s.fy), sub_rn(1.f, s.gy)};
+      const float wx[2] = {sub_rn(1.f, s.fx), sub_rn(1.f, s.gx)};
+      const bool okz[2] = {true, s.gz < 1.f}, oky[2] = {true, s.gy < 1.f}, okx[2] = {true, s.gx < 1.f};
+      long long vox[8];
+      float sw[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const int dz = q >> 2, dy = (q >> 1) & 1, dx = q & 1;
+        vox[q] = (((long long)b * g.D + (s.z0 + dz)) * g.H + (s.y0 + dy)) * g.W + (s.x0 + dx);
+        sw[q] = (okz[dz] && oky[dy] && okx[dx]) ? mul_rn(mul_rn(wz[dz], wy[dy]), wx[dx]) * m : 0.f;
+      }
+      const float* drow = dcol + ((long long)bl * g.V + v) * NT + (long long)((grp * g.K + tap) * nh) * 64 + j * 8;
+      for (int h = 0; h < nh; ++h) {
+        const int ch0 = grp * g.cpg + h * 64 + j * 8;
+        const float4 d0 = __ldg(reinterpret_cast<const float4*>(drow + h * 64));
+        const float4 d1 = __ldg(reinterpret_cast<const float4*>(drow + h * 64) + 1);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          if (!((s.valid >> q) & 1u)) continue;
+          const uint4 c = ptx::ldg_nc_v4(x_cl + vox[q] * g.Cin + ch0);
+          G[q] += d0.x * ptx::bf16_lo(c.x) + d0.y * ptx::bf16_hi(c.x) + d0.z * ptx::bf16_lo(c.y) +
+                  d0.w * ptx::bf16_hi(c.y) + d1.x * ptx::bf16_lo(c.z) + d1.y * ptx::bf16_hi(c.z) +
+                  d1.z * ptx::bf16_lo(c.w) + d1.w * ptx::bf16_hi(c.w);
+          if (sw[q] != 0.f) {
+            float* dst = gx_cl + vox[q] * g.Cin + ch0;
+            red_add_v4(dst, sw[q] * d0.x, sw[q] * d0.y, sw[q] * d0.z, sw[q] * d0.w);
+            red_add_v4(dst + 4, sw[q] * d1.x, sw[q] * d1.y, sw[q] * d1.z, sw[q] * d1.w);
+          }
+        }
+      }
+    }
+    // channel reduction of the 8 corner dot-products across the item's 8 threads
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      G[q] += __shfl_xor_sync(0xffffffffu, G[q], 1);
+      G[q] += __shfl_xor_sync(0xffffffffu, G[q], 2);
+      G[q] += __shfl_xor_sync(0xffffffffu, G[q], 4);
+    }
+    if (active && j == 0) {
+      float wts[3];
+      coord_weights(G, s, wts);    // linear in the corner values: applies to the channel-summed corners
+      const long long mi = (((long long)b * g.G + grp) * g.K + tap) * g.V + v;
+      if (mask && grad_mask) grad_mask[mi] = s.inside ? blend(G, a) : 0.f;
+      if constexpr (!FieldOut) {
+        float* go = grad_coord + (((long long)b * g.G + grp) * 3 * g.K + 3 * tap) * g.V + v;
+        go[0] = m * wts[0];
+        go[g.V] = m * wts[1];
+        go[2 * (long long)g.V] = m * wts[2];
+      } else {
+        const int k = tap % g.kw, jj = (tap / g.kw) % g.kh, i = tap / (g.kw * g.kh);
+        float* gs = grad_coord + (long long)b * coords.nch * g.V + v;
+        if (coords.ch[0] >= 0) atomicAdd(gs + (long long)coords.ch[0] * g.V, coords.axis[0][i] * (m * wts[0]));
+        if (coords.ch[1] >= 0) atomicAdd(gs + (long long)coords.ch[1] * g.V, coords.axis[1][jj] * (m * wts[1]));
+        if (coords.ch[2] >= 0) atomicAdd(gs + (long long)coords.ch[2] * g.V, coords.axis[2][k] * (m * wts[2]));
+      }
+    }
+  }
+}
+
+// ---- (c) channels-last fp32 -> NCDHW ----------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+unstage_grad_input_kernel(int C, long long Vin, const float* __restrict__ gx_cl, float* __restrict__ gx) {
+  __shared__ float tile[32][33];
+  const int b = blockIdx.z, c0 = blockIdx.y * 32;
+  const long long v0 = (long long)blockIdx.x * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int vv = ty; vv < 32; vv += 8) {
+    const long long v = v0 + vv;
+    tile[vv][tx] = (v < Vin && c0 + tx < C) ? __ldg(gx_cl + ((long long)b * Vin + v) * C + c0 + tx) : 0.f;
+  }
+  __syncthreads();
+  for (int cc = ty; cc < 32; cc += 8) {
+    const long long v = v0 + tx;
+    if (v < Vin && c0 + cc < C) gx[((long long)b * C + c0 + cc) * Vin + v] = tile[tx][cc];
+  }
+}
+
+struct BwdPlan {
+  int nh, S, NT, KB, NB, tiles_per_clip, tmem_cols, smem_bytes, clips_per_chunk;
+  size_t x_cl_bytes, gy_img_bytes, wt_img_bytes, dcol_bytes, gx_cl_bytes;
+};
+
+bool make_bwd_plan(const Geom& g, unsigned long long cap, BwdPlan* pl) {
+  if (g.groups != 1 || g.cpg % 64 != 0 || g.Cout % 64 != 0 || g.Cout > 512 || g.Cin % 32 != 0) return false;
+  pl->nh = g.cpg / 64;
+  pl->S = g.G * g.K * pl->nh;
+  pl->NT = pl->S * 64;
+  pl->KB = g.Cout / 64;
+  pl->NB = (pl->NT + kNBlock - 1) / kNBlock;
+  pl->tiles_per_clip = (g.V + kBM - 1) / kBM;
+  pl->tmem_cols = 512;
+  pl->smem_bytes = pl->KB * kABlockBytes + kBStages * kBStageBytes + 256 + 1024;
+  if (pl->smem_bytes > kSmemLimit) return false;
+  pl->clips_per_chunk = bwd_slice_clips(g, cap);
+  pl->x_cl_bytes = align_up((size_t)g.B * g.Vin * g.Cin * 2, 256);
+  pl->gy_img_bytes = align_up((size_t)pl->clips_per_chunk * pl->tiles_per_clip * pl->KB * kABlockBytes, 256);
+  pl->wt_img_bytes = align_up((size_t)pl->NB * pl->KB * kBStageBytes, 256);
+  pl->dcol_bytes = align_up((size_t)pl->clips_per_chunk * g.V * pl->NT * 4, 256);
+  pl->gx_cl_bytes = align_up((size_t)g.B * g.Vin * g.Cin * 4, 256);
+  return true;
+}
+
+template <typename Coords, bool FieldOut>
+int run_bwd(const Geom& g, const Coords& coords, unsigned long long cap, const float* gy, const float* x,
+            const float* mask, const float* w, float* grad_x, float* grad_coord, size_t grad_coord_elems,
+            float* grad_mask, float* grad_w, float* grad_bias, void* ws, cudaStream_t st) {
+  BwdPlan pl;
+  if (!make_bwd_plan(g, cap, &pl)) return D2C_ERR_MODE;
+  uint8_t* wsp = reinterpret_cast<uint8_t*>(ws);
+  __nv_bfloat16* x_cl = reinterpret_cast<__nv_bfloat16*>(wsp); wsp += pl.x_cl_bytes;
+  uint8_t* gy_img = wsp; wsp += pl.gy_img_bytes;
+  uint8_t* wt_img = wsp; wsp += pl.wt_img_bytes;
+  float* dcol = reinterpret_cast<float*>(wsp); wsp += pl.dcol_bytes;
+  float* gx_cl = reinterpret_cast<float*>(wsp);
+
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    D2C_CUDA_TRY(cudaGetDevice(&dev));
+    D2C_CUDA_TRY(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
+  }
+
+  prof_mark(st, "bwd_stage_operands");
+  D2C_CUDA_TRY(cudaMemsetAsync(gx_cl, 0, (size_t)g.B * g.Vin * g.Cin * 4, st));
+  if (FieldOut) D2C_CUDA_TRY(cudaMemsetAsync(grad_coord, 0, sizeof(float) * grad_coord_elems, st));
+  {
+    dim3 grid((unsigned)((g.Vin + 31) / 32), (unsigned)((g.Cin + 63) / 64), (unsigned)g.B);
+    stage_input_cl_bf16_kernel<<<grid, 256, 0, st>>>(g.Cin, g.Vin, x, x_cl);
+    D2C_LAUNCH_CHECK();
+    stage_wt_img_kernel<<<sm_count * 8, 256, 0, st>>>(g.Cout, g.Cin, g.K, g.cpg, pl.nh, pl.S, w, wt_img);
+    D2C_LAUNCH_CHECK();
+  }
+  D2C_CUDA_TRY(cudaFuncSetAttribute(dcol_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes));
+
+  for (int b0 = 0; b0 < g.B; b0 += pl.clips_per_chunk) {
+    const int nbc = (g.B - b0 < pl.clips_per_chunk) ? g.B - b0 : pl.clips_per_chunk;
+    const int n_tiles = nbc * pl.tiles_per_clip;
+    prof_mark(st, "bwd_stage_grad_out");
+    stage_gy_img_kernel<<<dim3((unsigned)n_tiles, (unsigned)pl.KB), 256, 0, st>>>(g.Cout, g.V, pl.tiles_per_clip, b0, gy,
+                                                                                 gy_img);
+    D2C_LAUNCH_CHECK();
+    DcolParams p;
+    p.gy_img = gy_img; p.wt_img = wt_img; p.dcol = dcol;
+    p.V = g.V; p.NT = pl.NT; p.KB = pl.KB; p.NB = pl.NB; p.S = pl.S;
+    p.tiles_per_clip = pl.tiles_per_clip; p.n_tiles = n_tiles; p.tmem_cols = pl.tmem_cols;
+    prof_mark(st, "bwd_dcol_sm100");
+    dcol_sm100_kernel<<<n_tiles < sm_count ? n_tiles : sm_count, kDcolThreads, pl.smem_bytes, st>>>(p);
+    D2C_LAUNCH_CHECK();
+    prof_mark(st, "bwd_sample_grad");
+    const long long items = (long long)nbc * g.G * g.K * g.V;
+    long long blocks = (items + 31) / 32;
+    if (blocks > (long long)sm_count * 16) blocks = (long long)sm_count * 16;
+    sample_grad_kernel<Coords, FieldOut><<<(unsigned)blocks, 256, 0, st>>>(g, coords, b0, nbc, pl.nh, pl.NT, dcol, x_cl,
+                                                                          mask, grad_coord, grad_mask, gx_cl);
+    D2C_LAUNCH_CHECK();
+  }
+  prof_mark(st, "bwd_unstage_grad_input");
+  {
+    dim3 grid((unsigned)((g.Vin + 31) / 32), (unsigned)((g.Cin + 31) / 32), (unsigned)g.B);
+    unstage_grad_input_kernel<<<grid, 256, 0, st>>>(g.Cin, g.Vin, gx_cl, grad_x);
+    D2C_LAUNCH_CHECK();
+  }
+  // weight gradient: CUDA-core implicit GEMM of the generic tier (fp32)
+  {
+    const int R = g.cin_g * g.K;
+    prof_mark(st, "bwd_dw_generic");
+    D2C_CUDA_TRY(cudaMemsetAsync(grad_w, 0, sizeof(float) * (size_t)g.Cout * R, st));
+    const int tiles = ((R + kTileV - 1) / kTileV) * ((g.cout_g + kTileN - 1) / kTileN) * g.groups * g.B;
+    int nsplit = (148 * 4 + tiles - 1) / tiles;
+    const int max_split = (g.V + 4 * kTileR - 1) / (4 * kTileR);
+    if (nsplit > max_split) nsplit = max_split;
+    if (nsplit < 1) nsplit = 1;
+    int v_per_split = (g.V + nsplit - 1) / nsplit;
+    v_per_split = (v_per_split + kTileR - 1) / kTileR * kTileR;
+    nsplit = (g.V + v_per_split - 1) / v_per_split;
+    dim3 grid((R + kTileV - 1) / kTileV, (g.cout_g + kTileN - 1) / kTileN, g.B * g.groups * nsplit);
+    dw_generic_kernel<float, Coords><<<grid, kGemmThreads, 0, st>>>(g, coords, v_per_split, gy, x, mask, grad_w);
+    D2C_LAUNCH_CHECK();
+  }
+  if (grad_bias) {
+    prof_mark(st, "bwd_grad_bias");
+    grad_bias_kernel<float><<<g.Cout, 256, 0, st>>>(g.B, g.Cout, g.V, gy, grad_bias);
+    D2C_LAUNCH_CHECK();
+  }
+  prof_mark(st, nullptr);
+  return D2C_OK;
+}
+
+}  // namespace
+
+bool sm100_bwd_supported(const Geom& g, int dtype, int math_mode, unsigned long long cap) {
+  if (dtype != D2C_F32 || math_mode != D2C_MATH_BF16) return false;
+  BwdPlan pl;
+  return make_bwd_plan(g, cap, &pl);
+}
+
+size_t sm100_bwd_workspace(const Geom& g, int dtype, int math_mode, unsigned long long cap) {
+  if (!sm100_bwd_supported(g, dtype, math_mode, cap)) return 0;
+  BwdPlan pl;
+  make_bwd_plan(g, cap, &pl);
+  return pl.x_cl_bytes + pl.gy_img_bytes + pl.wt_img_bytes + pl.dcol_bytes + pl.gx_cl_bytes;
+}
+
+int sm100_bwd_offsets(const Geom& g, unsigned long long cap, const float* gy, const float* x, const float* offset,
+                      const float* mask, const float* w, float* grad_x, float* grad_offset, float* grad_mask,
+                      float* grad_w, float* grad_bias, void* ws, cudaStream_t st) {
+  OffsetCoords<float> oc{offset};
+  return run_bwd<OffsetCoords<float>, false>(g, oc, cap, gy, x, mask, w, grad_x, grad_offset, 0, grad_mask, grad_w,
+                                             grad_bias, ws, st);
+}
+
+int sm100_bwd_field(const Geom& g, unsigned long long cap, const FieldCoords<float>& fc, const float* gy,
+                    const float* x, const float* mask, const float* w, float* grad_x, float* grad_size_map,
+                    size_t grad_size_elems, float* grad_mask, float* grad_w, float* grad_bias, void* ws,
+                    cudaStream_t st) {
+  return run_bwd<FieldCoords<float>, true>(g, fc, cap, gy, x, mask, w, grad_x, grad_size_map, grad_size_elems,
+                                           grad_mask, grad_w, grad_bias, ws, st);
+}
+
+int sm100_bwd_device_status() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_sm100_bwd_status, sizeof(int)) != cudaSuccess) return -1;
+  return v;
+}
+
+}  // namespace d2c

@@ -20,6 +20,7 @@
 // Stage hand-off is by mbarriers; every wait is bounded (sm100_ptx.cuh).
 #include "deform_sm100.h"
 #include "sm100_ptx.cuh"
+#include "sm100_stage.cuh"
 
 namespace d2c {
 
@@ -285,27 +286,6 @@ fwd_sm100_kernel(const FwdParams p, const Coords coords) {
 
 // ---- staging kernels -------------------------------------------------------------------------
 
-// x [B][C][Vin] fp32 -> x_cl [B][Vin][C] bf16.  Block: 64 channels x 32 voxels.
-__global__ void __launch_bounds__(256)
-stage_input_cl_bf16_kernel(int C, long long Vin, const float* __restrict__ x, __nv_bfloat16* __restrict__ x_cl) {
-  __shared__ float tile[64][33];
-  const int b = blockIdx.z, c0 = blockIdx.y * 64;
-  const long long v0 = (long long)blockIdx.x * 32;
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;   // 8 warps
-  for (int cc = ty; cc < 64; cc += 8) {
-    const long long v = v0 + tx;
-    tile[cc][tx] = (v < Vin && c0 + cc < C) ? __ldg(x + ((long long)b * C + c0 + cc) * Vin + v) : 0.f;
-  }
-  __syncthreads();
-  for (int vv = ty; vv < 32; vv += 8) {
-    const long long v = v0 + vv;
-    if (v < Vin && c0 + 2 * tx + 1 < C) {
-      const uint32_t pk = ptx::pack_bf16x2(tile[2 * tx][vv], tile[2 * tx + 1][vv]);
-      *reinterpret_cast<uint32_t*>(x_cl + ((long long)b * Vin + v) * C + c0 + 2 * tx) = pk;
-    }
-  }
-}
-
 // w [Cout][Cin][K] fp32 (weight groups == 1) -> w_sw [S][Cout rows x 128 B] bf16, slice
 // s = (grp*K + tap)*nh + h holding channels grp*cpg + h*64 .. +63, each row's 16-byte
 // chunks XOR-swizzled by (row & 7) -- the byte image of the shared-memory B tile.
@@ -418,8 +398,6 @@ size_t sm100_fwd_workspace(const Geom& g, int dtype, int math_mode) {
   make_plan(g, &pl);
   return pl.x_cl_bytes + pl.w_sw_bytes;
 }
-
-size_t sm100_bwd_workspace(const Geom&, int, int) { return 0; }
 
 int sm100_fwd_offsets(const Geom& g, int /*math_mode*/, const float* x, const float* offset, const float* mask,
                       const float* w, const float* bias, float* y, void* ws, cudaStream_t st) {

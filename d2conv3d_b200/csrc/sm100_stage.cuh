@@ -1,0 +1,32 @@
+// Operand staging kernels shared by the tensor-core forward and backward.
+#pragma once
+
+#include "sm100_ptx.cuh"
+
+namespace d2c {
+namespace {
+
+// x [B][C][Vin] fp32 -> x_cl [B][Vin][C] bf16.  Block: 64 channels x 32 voxels.
+static __global__ void __launch_bounds__(256)
+stage_input_cl_bf16_kernel(int C, long long Vin, const float* __restrict__ x, __nv_bfloat16* __restrict__ x_cl) {
+  __shared__ float tile[64][33];
+  const int b = blockIdx.z, c0 = blockIdx.y * 64;
+  const long long v0 = (long long)blockIdx.x * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;   // 8 warps
+  for (int cc = ty; cc < 64; cc += 8) {
+    const long long v = v0 + tx;
+    tile[cc][tx] = (v < Vin && c0 + cc < C) ? __ldg(x + ((long long)b * C + c0 + cc) * Vin + v) : 0.f;
+  }
+  __syncthreads();
+  for (int vv = ty; vv < 32; vv += 8) {
+    const long long v = v0 + vv;
+    if (v < Vin && c0 + 2 * tx + 1 < C) {
+      const uint32_t pk = ptx::pack_bf16x2(tile[2 * tx][vv], tile[2 * tx + 1][vv]);
+      *reinterpret_cast<uint32_t*>(x_cl + ((long long)b * Vin + v) * C + c0 + 2 * tx) = pk;
+    }
+  }
+}
+
+
+}  // namespace
+}  // namespace d2c
