@@ -16,6 +16,13 @@ int sm100_fwd_field(const Geom& g, int math_mode, const FieldCoords<float>& fc, 
                     const float* mask, const float* w, const float* bias, float* y, void* ws,
                     cudaStream_t st);
 
+// Weight gradient (implicit GEMM over the sampled tile); x_cl = channels-last bf16 staging of x.
+size_t sm100_dw_workspace(const Geom& g);
+int sm100_dw_offsets(const Geom& g, const float* offset, const float* gy, const void* x_cl, const float* mask,
+                     float* grad_w, void* ws, cudaStream_t st);
+int sm100_dw_field(const Geom& g, const FieldCoords<float>& fc, const float* gy, const void* x_cl,
+                   const float* mask, float* grad_w, void* ws, cudaStream_t st);
+
 // `cap` = maximum number of gradient-column elements held at once (clips are processed in chunks).
 bool sm100_bwd_supported(const Geom& g, int dtype, int math_mode, unsigned long long cap);
 size_t sm100_bwd_workspace(const Geom& g, int dtype, int math_mode, unsigned long long cap);

@@ -12,7 +12,7 @@
 //   (c) unstage_grad_input_kernel  channels-last fp32 -> NCDHW.
 //
 // The weight gradient is in deform_sm100_dw.cu.
-#include "deform_generic.cuh"
+#include "deform_generic.cuh"   // grad_bias_kernel, bwd_slice_clips
 #include "deform_sm100.h"
 #include "sm100_ptx.cuh"
 #include "sm100_stage.cuh"
@@ -397,7 +397,8 @@ int run_bwd(const Geom& g, const Coords& coords, unsigned long long cap, const f
   uint8_t* gy_img = wsp; wsp += pl.gy_img_bytes;
   uint8_t* wt_img = wsp; wsp += pl.wt_img_bytes;
   float* dcol = reinterpret_cast<float*>(wsp); wsp += pl.dcol_bytes;
-  float* gx_cl = reinterpret_cast<float*>(wsp);
+  float* gx_cl = reinterpret_cast<float*>(wsp); wsp += pl.gx_cl_bytes;
+  void* dw_ws = wsp;
 
   static int sm_count = 0;
   if (sm_count == 0) {
@@ -446,22 +447,12 @@ int run_bwd(const Geom& g, const Coords& coords, unsigned long long cap, const f
     unstage_grad_input_kernel<<<grid, 256, 0, st>>>(g.Cin, g.Vin, gx_cl, grad_x);
     D2C_LAUNCH_CHECK();
   }
-  // weight gradient: CUDA-core implicit GEMM of the generic tier (fp32)
+  // weight gradient: tensor-core implicit GEMM over the re-sampled tile
   {
-    const int R = g.cin_g * g.K;
-    prof_mark(st, "bwd_dw_generic");
-    D2C_CUDA_TRY(cudaMemsetAsync(grad_w, 0, sizeof(float) * (size_t)g.Cout * R, st));
-    const int tiles = ((R + kTileV - 1) / kTileV) * ((g.cout_g + kTileN - 1) / kTileN) * g.groups * g.B;
-    int nsplit = (148 * 4 + tiles - 1) / tiles;
-    const int max_split = (g.V + 4 * kTileR - 1) / (4 * kTileR);
-    if (nsplit > max_split) nsplit = max_split;
-    if (nsplit < 1) nsplit = 1;
-    int v_per_split = (g.V + nsplit - 1) / nsplit;
-    v_per_split = (v_per_split + kTileR - 1) / kTileR * kTileR;
-    nsplit = (g.V + v_per_split - 1) / v_per_split;
-    dim3 grid((R + kTileV - 1) / kTileV, (g.cout_g + kTileN - 1) / kTileN, g.B * g.groups * nsplit);
-    dw_generic_kernel<float, Coords><<<grid, kGemmThreads, 0, st>>>(g, coords, v_per_split, gy, x, mask, grad_w);
-    D2C_LAUNCH_CHECK();
+    int rc;
+    if constexpr (FieldOut) rc = sm100_dw_field(g, coords, gy, x_cl, mask, grad_w, dw_ws, st);
+    else rc = sm100_dw_offsets(g, coords.offset, gy, x_cl, mask, grad_w, dw_ws, st);
+    if (rc) return rc;
   }
   if (grad_bias) {
     prof_mark(st, "bwd_grad_bias");
@@ -477,14 +468,14 @@ int run_bwd(const Geom& g, const Coords& coords, unsigned long long cap, const f
 bool sm100_bwd_supported(const Geom& g, int dtype, int math_mode, unsigned long long cap) {
   if (dtype != D2C_F32 || math_mode != D2C_MATH_BF16) return false;
   BwdPlan pl;
-  return make_bwd_plan(g, cap, &pl);
+  return make_bwd_plan(g, cap, &pl) && sm100_dw_workspace(g) > 0;
 }
 
 size_t sm100_bwd_workspace(const Geom& g, int dtype, int math_mode, unsigned long long cap) {
   if (!sm100_bwd_supported(g, dtype, math_mode, cap)) return 0;
   BwdPlan pl;
   make_bwd_plan(g, cap, &pl);
-  return pl.x_cl_bytes + pl.gy_img_bytes + pl.wt_img_bytes + pl.dcol_bytes + pl.gx_cl_bytes;
+  return pl.x_cl_bytes + pl.gy_img_bytes + pl.wt_img_bytes + pl.dcol_bytes + pl.gx_cl_bytes + sm100_dw_workspace(g);
 }
 
 int sm100_bwd_offsets(const Geom& g, unsigned long long cap, const float* gy, const float* x, const float* offset,

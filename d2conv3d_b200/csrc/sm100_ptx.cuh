@@ -124,6 +124,15 @@ __device__ __forceinline__ uint64_t umma_desc_kmajor_sw128(uint32_t smem_addr) {
   return (static_cast<uint64_t>(hi) << 32) | lo;
 }
 
+// Descriptor of an MN-major operand (the M/N index is the contiguous one) with the 128-byte swizzle:
+// atoms of 64 elements (128 B) along MN by 8 rows along K; `lbo` = byte distance between atoms
+// along MN, `sbo` = byte distance between 8-row groups along K.
+__device__ __forceinline__ uint64_t umma_desc_mnmajor_sw128(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+  const uint32_t lo = ((smem_addr >> 4) & 0x3FFFu) | (((lbo >> 4) & 0x3FFFu) << 16);
+  const uint32_t hi = ((sbo >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
+  return (static_cast<uint64_t>(hi) << 32) | lo;
+}
+
 // Instruction descriptor, kind::f16: bf16 A and B (both K-major), fp32 accumulator, M x N.
 __device__ __forceinline__ uint32_t umma_idesc_bf16_f32(uint32_t M, uint32_t N) {
   return (1u << 4) /* D = f32 */ | (1u << 7) /* A = bf16 */ | (1u << 10) /* B = bf16 */ | ((N >> 3) << 17) |
