@@ -73,6 +73,7 @@ def lib():
         L.d2c_dyn_dilated_conv3d_corners.argtypes = [dp, i32, vp, vp, vp]
         L.d2c_depthwise_conv3d_fwd.argtypes = [dp] + [vp] * 4 + [vp]
         L.d2c_depthwise_conv3d_bwd.argtypes = [dp] + [vp] * 7 + [sz, vp]
+        L.d2c_depthwise_conv3d_bwd_noalloc.argtypes = [dp] + [vp] * 6 + [vp]
         _lib = L
     return _lib
 

@@ -172,6 +172,8 @@ const char* d2c_status_string(int status) {
     case D2C_ERR_TOO_LARGE: return "tensor too large for this op";
     case D2C_ERR_MODE: return "unknown math or field mode";
     case D2C_ERR_WEIGHT_SHAPE: return "weight shape does not match the channel counts";
+    case D2C_ERR_SCRATCH_LIMIT:
+      return "out_channels * kernel taps exceeds the 32768 accumulator slots of the built-in scratch buffer";
     case D2C_ERR_CUDA: return "CUDA runtime error";
     case D2C_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait gave up";
     default: return "unknown status";

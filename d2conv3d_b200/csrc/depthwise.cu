@@ -7,6 +7,8 @@
 // gradient, :609 bias gradient).
 #include <cuda_fp16.h>
 
+#include <mutex>
+
 #include "d2c_common.cuh"
 
 namespace d2c {
@@ -307,4 +309,56 @@ int depthwise_bwd(const Geom& g, int dtype, const void* gy, const void* x, const
   }
 }
 
+// ---- depthwise backward without any device allocation -----------------------------------------------
+//
+// Some users of this C ABI cannot hand the library a workspace: a host program that sizes all of its
+// device memory once at start-up and then runs under a fixed budget (a serving process that shares the
+// GPU with other tenants, an embedded pipeline with a static memory plan) has nothing left to allocate
+// from, and a latency-critical loop cannot afford cudaMalloc/cudaFree at all because they synchronise the
+// whole device.  For those callers the weight-gradient accumulators of the depthwise backward live in
+// the fixed array below instead of a caller-supplied workspace.
+//
+// The array is part of the library image: every GPU that loads libd2conv3d.so holds these 256 KB from
+// load until the process exits.  All calls on a device share it and it keeps the last call's contents, so
+// (a) the kernels' launch sequence clears it on the stream before accumulating and (b) two calls whose
+// GPU work overlaps (different streams, or host threads racing on one device) corrupt each other.
+constexpr size_t kNoAllocScratchElems = 32768;   // accumulator slots: out_channels * kd*kh*kw must fit
+static __device__ __align__(256) double g_dw_noalloc_scratch[kNoAllocScratchElems];
+
+constexpr int kMaxDevices = 64;
+static void* g_dw_noalloc_ptr[kMaxDevices];      // device address of the array, per device (0 = not set up)
+static std::mutex g_dw_noalloc_mu;
+
+// In host code the array's name is only a handle; the address a kernel can use has to be asked for,
+// per device, with that device current.
+static int dw_noalloc_scratch(void** out) {
+  int dev = -1;
+  D2C_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return D2C_ERR_TOO_LARGE;
+  std::lock_guard<std::mutex> lk(g_dw_noalloc_mu);
+  if (!g_dw_noalloc_ptr[dev]) {
+    void* ptr = nullptr;
+    D2C_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_dw_noalloc_scratch));
+    g_dw_noalloc_ptr[dev] = ptr;
+  }
+  *out = g_dw_noalloc_ptr[dev];
+  return D2C_OK;
+}
+
 }  // namespace d2c
+
+extern "C" int d2c_depthwise_conv3d_bwd_noalloc(const d2c_conv_desc* desc, const void* grad_y, const void* x,
+                                                const void* w, void* grad_x, void* grad_w, void* grad_bias,
+                                                d2c_stream_t stream) {
+  using namespace d2c;
+  if (!desc || !grad_y || !x || !w) return D2C_ERR_NULL;
+  Geom g;
+  int rc = make_geom(desc, &g, true);
+  if (rc) return rc;
+  if ((long long)g.B * g.Cin * g.Vin > 0x7fffffffLL || (long long)g.B * g.Cout * g.V > 0x7fffffffLL)
+    return D2C_ERR_TOO_LARGE;
+  if (grad_w && (size_t)g.Cout * g.K > kNoAllocScratchElems) return D2C_ERR_SCRATCH_LIMIT;
+  void* scratch = nullptr;
+  if ((rc = dw_noalloc_scratch(&scratch))) return rc;
+  return depthwise_bwd(g, desc->dtype, grad_y, x, w, grad_x, grad_w, grad_bias, scratch, (cudaStream_t)stream);
+}

@@ -65,6 +65,7 @@ enum d2c_status {
   D2C_ERR_TOO_LARGE = -9,     /* a tensor exceeds the 2^31-1 element index range of the op */
   D2C_ERR_MODE = -10,         /* unknown math / field mode */
   D2C_ERR_WEIGHT_SHAPE = -11, /* weight.size(1)*groups != Cin, or depthwise weight rule */
+  D2C_ERR_SCRATCH_LIMIT = -12,/* problem needs more scratch than the library's built-in buffer holds */
   D2C_ERR_CUDA = 1,           /* a CUDA runtime call failed (see d2c_last_cuda_error) */
   D2C_ERR_DEVICE_TIMEOUT = 2  /* a bounded device-side wait gave up */
 };
@@ -218,6 +219,22 @@ int d2c_depthwise_conv3d_fwd(const d2c_conv_desc* desc, const void* x, const voi
 int d2c_depthwise_conv3d_bwd(const d2c_conv_desc* desc, const void* grad_y, const void* x,
                              const void* w, void* grad_x, void* grad_w, void* grad_bias,
                              void* workspace, size_t workspace_bytes, d2c_stream_t stream);
+
+/* No counterpart in the reference.  Same results as d2c_depthwise_conv3d_bwd, for callers that
+ * have no device memory to give and may not allocate any: a process that planned its whole device-memory
+ * budget at start-up (e.g. a server sharing the GPU with other tenants) or a latency-critical loop in
+ * which cudaMalloc/cudaFree, which synchronise the device, are not acceptable.  The weight-gradient
+ * accumulators live in a 256 KB array inside the library (held by every GPU that loads the library,
+ * until the process exits) instead of a workspace; the call itself allocates nothing.
+ *   - Limit: out_channels * kd*kh*kw <= 32768 when grad_w is requested, else D2C_ERR_SCRATCH_LIMIT.
+ *   - The first call on each device looks up the array's device address (one-time set-up); make that
+ *     first call before any stream capture is started on that device.
+ *   - All calls on a device share the array: calls whose GPU work can overlap (different streams, or
+ *     several host threads) race on it.  Issue them on one stream, or otherwise order them.
+ *   - Keep phase profiling (d2c_profile_enable) off: it creates CUDA events. */
+int d2c_depthwise_conv3d_bwd_noalloc(const d2c_conv_desc* desc, const void* grad_y, const void* x,
+                                     const void* w, void* grad_x, void* grad_w, void* grad_bias,
+                                     d2c_stream_t stream);
 
 #ifdef __cplusplus
 }
