@@ -64,7 +64,8 @@ def make_inputs(seed, wl, B=None, dims=None):
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks / throttle reasons while the timed region runs."""
+    """Samples nvidia-smi clocks / throttle reasons; `summary(t0, t1)` keeps the samples that arrived
+    inside the timed window (host clock)."""
 
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -76,8 +77,8 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
-                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True, bufsize=1)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
@@ -85,31 +86,51 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
+
+    def wait_for_samples(self, n=2, timeout=5.0):
+        t0 = time.time()
+        while self.proc is not None and len(self.lines) < n and time.time() - t0 < timeout:
+            time.sleep(0.05)
 
     def stop(self):
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            return
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        sm, mx, reasons = [], None, set()
+
+    def summary(self, t0, t1):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"], "samples": 0}
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
-            f = [s.strip() for s in ln.split(",")]
-            if len(f) < 9:
-                continue
-            try:
-                sm.append(float(f[1])); mx = float(f[2])
-            except ValueError:
-                continue
-            for nm, val in zip(names, f[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(nm)
+
+        def collect(lo, hi):
+            sm, mx, reasons, power = [], None, set(), []
+            for ts, ln in self.lines:
+                if not (lo <= ts <= hi):
+                    continue
+                f = [x.strip() for x in ln.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1])); mx = float(f[2]); power.append(float(f[3]))
+                except ValueError:
+                    continue
+                for nm, val in zip(names, f[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(nm)
+            return sm, mx, reasons, power
+
+        sm, mx, reasons, power = collect(t0, t1 + 0.06)
+        window = "timed region"
+        if len(sm) < 2:   # very short timed region: fall back to everything sampled under load
+            sm, mx, reasons, power = collect(0, float("inf"))
+            window = "warm-up + timed region (timed region shorter than the sampling period)"
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
-                "samples": len(sm)}
+                "samples": len(sm), "power_w_max": max(power) if power else None, "window": window}
 
 
 # ---- CPU arm (oracle) ----------------------------------------------------------------------------
@@ -172,10 +193,17 @@ def run_reference_arm(args):
 
 # ---- GPU arm ---------------------------------------------------------------------------------------
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised in profiles/
+# (same workload); None where no capture has been taken.
+TRAFFIC_PER_LAUNCH = {}
+
 PHASE_WORK = {
-    # phase-name prefix -> (bound, work per launch as a function of (F, bytes...))
-    "fwd": ("tensor", "F"), "bwd_dcol": ("tensor", "F"), "bwd_dw": ("tensor", "F"), "bwd_fused": ("tensor", "2F"),
-    "bwd_coord_grad": ("hbm", "coord_bytes"), "bwd_col2im": ("hbm", "col2im_bytes"),
+    # phase name -> (bound, key of the algorithmic work of one launch)
+    "fwd_sm100_fused": ("tensor", "F"), "fwd_generic": ("tensor", "F"),
+    "bwd_dcol_sm100": ("tensor", "F"), "bwd_dcol_generic": ("tensor", "F"),
+    "bwd_dw_sm100": ("tensor", "F"), "bwd_dw_generic": ("tensor", "F"),
+    "bwd_sample_grad": ("hbm", "sample_grad_bytes"),
+    "bwd_coord_grad_generic": ("hbm", "coord_bytes"), "bwd_col2im_generic": ("hbm", "col2im_bytes"),
 }
 
 
@@ -213,7 +241,9 @@ def run_gpu_arm(args):
     s = 4
     coord_bytes = s * (wl["B"] * wl["Cin"] * 27 * V + wl["B"] * wl["Cin"] * V + 2 * wl["B"] * wl["G"] * 4 * 27 * V)
     col2im_bytes = s * (wl["B"] * wl["Cin"] * 27 * V + wl["B"] * wl["G"] * 4 * 27 * V + wl["B"] * wl["Cin"] * V)
-    work = {"F": F, "2F": 2 * F, "coord_bytes": coord_bytes, "col2im_bytes": col2im_bytes}
+    # fused offset/mask-gradient + scatter: dcol read once, x read, offsets+mask read, their gradients and grad_x written
+    sample_grad_bytes = s * (wl["B"] * wl["Cin"] * 27 * V + 2 * wl["B"] * wl["Cin"] * V + 2 * wl["B"] * wl["G"] * 4 * 27 * V)
+    work = {"F": F, "coord_bytes": coord_bytes, "col2im_bytes": col2im_bytes, "sample_grad_bytes": sample_grad_bytes}
 
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)      # 256 MB > 126 MB L2
 
@@ -232,28 +262,36 @@ def run_gpu_arm(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
     for _ in range(args.warmup):
         flush.zero_()
         step()
     barrier()
-    sampler = ClockSampler(local_rank)
     if rank == 0:
-        sampler.start()
+        sampler.wait_for_samples()
     _lib.profile_read()
     _lib.profile_enable(True)
     launches0 = _lib.launch_count()
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     barrier()
+    t_start = time.time()
     for i in range(args.steps):
         flush.zero_()                      # L2 flush between timed iterations, outside the event pair
         ev[i][0].record()
         step()
         ev[i][1].record()
     barrier()
+    t_end = time.time()
     launches = _lib.launch_count() - launches0
     _lib.profile_enable(False)
     phases = _lib.profile_read()
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = None
+    if rank == 0:
+        sampler.stop()
+        clocks = sampler.summary(t_start, t_end)
+    _lib.device_status()               # raises if a bounded device-side wait gave up
     total_ms = sum(a.elapsed_time(b) for a, b in ev)
     tt = torch.tensor([total_ms], device=dev, dtype=torch.float64)
     if world > 1:
@@ -283,20 +321,23 @@ def run_gpu_arm(args):
         outs["gmask"].copy_(ms_.grad, non_blocking=True)
         outs["gw"].copy_(w.grad, non_blocking=True)
 
-    e2e_steps = max(1, min(args.steps, 10))
-    e2e_step()
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(e2e_steps):
+    e2e = None
+    if not args.no_e2e:
+        e2e_steps = max(1, min(args.steps, 10))
         e2e_step()
-    e1.record()
-    barrier()
-    te = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(te, op=dist.ReduceOp.MAX)
-    e2e_ms = float(te.item()) / e2e_steps
-    e2e_value = 3 * F * world / (e2e_ms * 1e-3) / 1e12
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(e2e_steps):
+            e2e_step()
+        e1.record()
+        barrier()
+        te = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        e2e_ms = float(te.item()) / e2e_steps
+        e2e = {"value": 3 * F * world / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps}
 
     if rank == 0:
         # ---- roofline of the dominant kernel phase (library events over the timed steps) ----
@@ -304,25 +345,29 @@ def run_gpu_arm(args):
         for name, ms in phases:
             a = agg.setdefault(name, [0, 0.0])
             a[0] += 1; a[1] += ms
-        phase_summary = {n: {"launches": c, "ms_total": round(t, 4), "ms_avg": round(t / c, 4)} for n, (c, t) in agg.items()}
+        def phase_roofline(name, avg_ms):
+            if name not in PHASE_WORK:
+                return None
+            bound, key = PHASE_WORK[name]
+            if bound == "tensor":
+                achieved, peak, unit = work[key] / (avg_ms * 1e-3) / 1e12, peaks["tensor_sustained"], "TFLOP/s"
+            else:
+                achieved, peak, unit = work[key] / (avg_ms * 1e-3) / 1e9, peaks["hbm_gbs"], "GB/s"
+            return {"kernel": name, "bound": bound, "achieved": achieved, "peak": peak, "unit": unit,
+                    "frac": achieved / peak, "traffic": TRAFFIC_PER_LAUNCH.get(name), "ms_per_launch": avg_ms,
+                    "peak_source": peaks["source"] + (" (bf16 dense, sustained)" if bound == "tensor" else " (copy)")}
+
+        phase_summary = {}
+        for n, (c, t) in agg.items():
+            phase_summary[n] = {"launches": c, "ms_total": round(t, 4), "ms_avg": round(t / c, 4)}
+            r = phase_roofline(n, t / c)
+            if r:
+                phase_summary[n]["frac_of_peak"] = round(r["frac"], 4)
         roofline = None
-        if agg:
-            dom = max(agg, key=lambda n: agg[n][1])
-            avg_ms = agg[dom][1] / agg[dom][0]
-            bound, key = "hbm", None
-            for prefix, (bnd, k) in PHASE_WORK.items():
-                if dom.startswith(prefix):
-                    bound, key = bnd, k
-            if key is not None:
-                if bound == "tensor":
-                    achieved = work[key] / (avg_ms * 1e-3) / 1e12
-                    peak, unit = peaks["tensor_sustained"], "TFLOP/s"
-                else:
-                    achieved = work[key] / (avg_ms * 1e-3) / 1e9
-                    peak, unit = peaks["hbm_gbs"], "GB/s"
-                roofline = {"kernel": dom, "bound": bound, "achieved": achieved, "peak": peak, "unit": unit,
-                            "frac": achieved / peak, "traffic": None, "ms_per_launch": avg_ms,
-                            "peak_source": peaks["source"] + (" (bf16 dense, sustained)" if bound == "tensor" else " (copy)")}
+        candidates = [n for n in agg if n in PHASE_WORK]
+        if candidates:
+            dom = max(candidates, key=lambda n: agg[n][1])
+            roofline = phase_roofline(dom, agg[dom][1] / agg[dom][0])
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
             val, ms, sample, cores = cpu_arm(1, 1, budget_s=40.0)
@@ -330,12 +375,12 @@ def run_gpu_arm(args):
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f32", "math_mode": _lib.get_math_mode(), "data": "synthetic",
+            "dtype": "bf16" if _lib.get_math_mode() == "bf16" else "f32", "math_mode": _lib.get_math_mode(),
+            "tensor_dtype": "f32", "data": "synthetic",
             "config": {"workload": wl["name"], "l2": "256 MB buffer written between timed iterations",
                        "collective": "all-reduce of grad_weight+grad_bias (NCCL)" if world > 1 else "none"},
             "clips_per_s": wl["B"] * world / (ms_per_step * 1e-3),
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": e2e_ms},
+            "e2e": e2e,
             "gpu_launches": int(launches), "roofline": roofline, "phases": phase_summary, "cpu_baseline": cpu,
             "clocks": clocks,
         }
@@ -347,11 +392,12 @@ def run_gpu_arm(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--mode", default="auto", choices=["auto", "fp32", "bf16x3", "bf16"])
+    ap.add_argument("--mode", default="bf16", choices=["auto", "fp32", "bf16x3", "bf16"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
