@@ -207,6 +207,47 @@ PHASE_WORK = {
 }
 
 
+def time_reference_cuda_op(host, w, bias, wl, F):
+    """The reference's own CUDA op (unmodified sources built into baseline/_ref), same inputs, same GPU:
+    the kernel to beat.  Its kernels launch on the legacy default stream, so every measurement is
+    bracketed by device-wide synchronisation.  Returns None when the build is absent."""
+    import torch
+    from tests import _reference
+    ref = _reference.load("dconv_native")
+    if ref is None:
+        return None
+    try:
+        torch.backends.cuda.matmul.allow_tf32 = False
+        dev = w.device
+        x, off, mask, gy = (host[k].to(dev) for k in ("x", "geo", "mask", "gy"))
+        ts = [t.detach().clone().requires_grad_() for t in (x, off, mask, w, bias)]
+        torch.cuda.reset_peak_memory_stats()
+
+        def one():
+            for t in ts:
+                t.grad = None
+            torch.cuda.synchronize()
+            e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+            e[0].record()
+            y = ref.deform_conv3d(*ts, 1, wl["pad"], 1, 1, wl["G"])
+            e[1].record()
+            y.backward(gy)
+            e[2].record()
+            torch.cuda.synchronize()
+            return e[0].elapsed_time(e[1]), e[1].elapsed_time(e[2])
+
+        for _ in range(2):
+            one()
+        runs = [one() for _ in range(5)]
+        fwd = statistics.median(r[0] for r in runs)
+        bwd = statistics.median(r[1] for r in runs)
+        return {"fwd_ms": fwd, "bwd_ms": bwd, "ms_per_step": fwd + bwd, "value": 3 * F / ((fwd + bwd) * 1e-3) / 1e12,
+                "unit": UNIT, "peak_mem_gb": torch.cuda.max_memory_allocated() / 1e9,
+                "what": "unmodified reference dconv_native (im2col + cuBLAS fp32, allow_tf32=False), median of 5"}
+    except Exception as exc:  # the reference op is outside our control; report instead of failing the bench
+        return {"error": f"{type(exc).__name__}: {exc}"}
+
+
 def run_gpu_arm(args):
     import torch
     import torch.distributed as dist
@@ -372,6 +413,9 @@ def run_gpu_arm(args):
         if world == 1 and not args.no_cpu_baseline:
             val, ms, sample, cores = cpu_arm(1, 1, budget_s=40.0)
             cpu = {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample, "ms_per_sample_step": ms}
+        ref_gpu = None
+        if world == 1 and not args.no_reference_gpu:
+            ref_gpu = time_reference_cuda_op(host, w, bias, wl, F)
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -382,7 +426,7 @@ def run_gpu_arm(args):
             "clips_per_s": wl["B"] * world / (ms_per_step * 1e-3),
             "e2e": e2e,
             "gpu_launches": int(launches), "roofline": roofline, "phases": phase_summary, "cpu_baseline": cpu,
-            "clocks": clocks,
+            "clocks": clocks, "reference_cuda_op": ref_gpu,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -398,6 +442,7 @@ def main():
     ap.add_argument("--mode", default="bf16", choices=["auto", "fp32", "bf16x3", "bf16"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-reference-gpu", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":

@@ -1,0 +1,68 @@
+"""Multi-GPU plumbing of the path: one process per GPU, clips (the batch dimension) sharded across
+ranks, weights replicated, and a single collective -- the sum of grad_weight / grad_bias -- for
+training-style runs.  Forward, grad_input, grad_offset and grad_mask depend only on a rank's own
+clips (reference csrc/ops/dconv3d_gpu.cu:147,158-178 offsets every pointer by the clip index), so the
+data path needs no exchange; the reference's DDP wrapper (trainer.py:111) all-reduces parameter
+gradients the same way.
+
+Works with any torch.distributed backend: NCCL on GPUs, gloo in the CPU tests.
+"""
+import torch
+import torch.distributed as dist
+
+
+def clip_range(n_clips, rank, world_size):
+    """Contiguous slice [begin, end) of the batch owned by `rank`; sizes differ by at most one."""
+    if not (0 <= rank < world_size):
+        raise ValueError(f"rank {rank} outside world of {world_size}")
+    base, extra = divmod(n_clips, world_size)
+    begin = rank * base + min(rank, extra)
+    return begin, begin + base + (1 if rank < extra else 0)
+
+
+def shard_clips(tensors, rank=None, world_size=None):
+    """Slices every tensor (or None) of `tensors` along dim 0 to this rank's clips."""
+    rank = dist.get_rank() if rank is None else rank
+    world_size = dist.get_world_size() if world_size is None else world_size
+    out = []
+    for t in tensors:
+        if t is None:
+            out.append(None)
+            continue
+        b, e = clip_range(t.shape[0], rank, world_size)
+        out.append(t[b:e])
+    return out
+
+
+def all_reduce_param_grads(grads, group=None, async_op=False):
+    """Sums parameter gradients (grad_weight, grad_bias; None entries skipped) over all ranks in place.
+    One flat bucket, so small gradients cost a single collective.  Returns the work handle when
+    async_op (call .wait() and then `unflatten()` on the returned tuple's second element)."""
+    live = [g for g in grads if g is not None]
+    if not live or not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return None
+    if len(live) == 1:
+        return dist.all_reduce(live[0], op=dist.ReduceOp.SUM, group=group, async_op=async_op)
+    flat = torch.cat([g.reshape(-1) for g in live])
+    work = dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group, async_op=async_op)
+
+    def unflatten():
+        off = 0
+        for g in live:
+            n = g.numel()
+            g.copy_(flat[off:off + n].view_as(g))
+            off += n
+
+    if async_op:
+        return work, unflatten
+    unflatten()
+    return None
+
+
+def broadcast_params(params, src=0, group=None):
+    """Replicates weights / bias from `src` at start-up."""
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return
+    for p in params:
+        if p is not None:
+            dist.broadcast(p.data if hasattr(p, "data") else p, src=src, group=group)
