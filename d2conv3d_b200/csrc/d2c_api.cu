@@ -185,7 +185,7 @@ const char* d2c_last_cuda_error(void) { return g_last_cuda_error; }
 int d2c_device_status(void) {
   int rc = check_cuda(cudaDeviceSynchronize());
   if (rc) return rc;
-  const int v1 = sm100_device_status(), v2 = sm100_bwd_device_status();
+  const int v1 = sm100_device_status(), v2 = sm100_bwd_device_status() | sm100_dw_device_status();
   if (v1 < 0 || v2 < 0) return D2C_ERR_CUDA;
   const int v = v1 | v2;
   return v ? D2C_ERR_DEVICE_TIMEOUT : D2C_OK;

@@ -16,12 +16,11 @@ int sm100_fwd_field(const Geom& g, int math_mode, const FieldCoords<float>& fc, 
                     const float* mask, const float* w, const float* bias, float* y, void* ws,
                     cudaStream_t st);
 
-// Weight gradient (implicit GEMM over the sampled tile); x_cl = channels-last bf16 staging of x.
+// Weight gradient (implicit GEMM over the sampled tile).  x_cl = channels-last bf16 staging of x,
+// recs = the call's sampling records (float4 {z, y, x, mask} per (clip, group, tap, voxel)).
 size_t sm100_dw_workspace(const Geom& g);
-int sm100_dw_offsets(const Geom& g, const float* offset, const float* gy, const void* x_cl, const float* mask,
-                     float* grad_w, void* ws, cudaStream_t st);
-int sm100_dw_field(const Geom& g, const FieldCoords<float>& fc, const float* gy, const void* x_cl,
-                   const float* mask, float* grad_w, void* ws, cudaStream_t st);
+int sm100_dw(const Geom& g, const float* gy, const void* x_cl, const void* recs, float* grad_w, void* ws,
+             cudaStream_t st);
 
 // `cap` = maximum number of gradient-column elements held at once (clips are processed in chunks).
 bool sm100_bwd_supported(const Geom& g, int dtype, int math_mode, unsigned long long cap);
@@ -37,5 +36,6 @@ int sm100_bwd_field(const Geom& g, unsigned long long cap, const FieldCoords<flo
 // 0 = healthy; 1 = some kernel's bounded wait gave up (sticky); -1 = could not be read.
 int sm100_device_status();
 int sm100_bwd_device_status();
+int sm100_dw_device_status();
 
 }  // namespace d2c

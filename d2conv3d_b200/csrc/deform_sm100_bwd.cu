@@ -11,9 +11,11 @@
 //                           deformable_col2im_gpu_kernel (:562-643).
 //   (c) unstage_grad_input_kernel  channels-last fp32 -> NCDHW.
 //
-// The weight gradient is in deform_sm100_dw.cu.
+// The weight gradient is in deform_sm100_dw.cu; sampling positions come from the records of
+// sm100_gather.cuh, computed once per backward call.
 #include "deform_generic.cuh"   // grad_bias_kernel, bwd_slice_clips
 #include "deform_sm100.h"
+#include "sm100_gather.cuh"
 #include "sm100_ptx.cuh"
 #include "sm100_stage.cuh"
 
@@ -26,7 +28,9 @@ constexpr int kABlockBytes = kBM * 128;       // one 64-wide K block of the grad
 constexpr int kNBlock = 256;                  // dcol columns per accumulator (4 slices of 64 channels)
 constexpr int kBStageBytes = kNBlock * 128;   // 32 KB
 constexpr int kBStages = 3;
-constexpr int kDcolThreads = 192;             // warps 0-3 epilogue, warp 4 MMA, warp 5 loader
+constexpr int kDcolEpiWarps = 8;              // warp w: TMEM lane quarter w%4, column half w/4
+constexpr int kDcolMmaWarp = 8, kDcolLoadWarp = 9;
+constexpr int kDcolThreads = 320;
 constexpr int kSmemLimit = 227 * 1024;
 
 __device__ int g_sm100_bwd_status = 0;
@@ -90,13 +94,18 @@ stage_wt_img_kernel(int Cout, int Cin, int K, int cpg, int nh, int S, const floa
 }
 
 // ---- (a) dcol GEMM ------------------------------------------------------------------------------
+// Work units are (tile, 256-column block); each CTA takes one contiguous range of them, so the last wave
+// is as full as the others.  Within a range the grad_out tile (A, up to 128 KB) is loaded once per tile
+// segment; B blocks stream through a 3-stage ring; two accumulators alternate so that the store epilogue
+// (8 warps) overlaps the next block's MMAs.
 
 struct DcolParams {
   const uint8_t* gy_img;   // [n_tiles][KB][16 KB]
   const uint8_t* wt_img;   // [NB][KB][32 KB]
   float* dcol;             // [clips_in_chunk * V][NT]
-  int V, NT, KB, NB, S;
+  int V, NT, KB, NB;
   int tiles_per_clip, n_tiles;
+  long long n_units;       // n_tiles * NB
   int tmem_cols;
 };
 
@@ -118,9 +127,11 @@ dcol_sm100_kernel(const DcolParams p) {
   volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + slot_off + 4);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long u_beg = p.n_units * blockIdx.x / gridDim.x, u_end = p.n_units * (blockIdx.x + 1) / gridDim.x;
+
   if (threadIdx.x == 0) {
     for (int s = 0; s < kBStages; ++s) { ptx::mbar_init(b_full(s), 1); ptx::mbar_init(b_empty(s), 1); }
-    for (int a = 0; a < 2; ++a) { ptx::mbar_init(acc_full(a), 1); ptx::mbar_init(acc_empty(a), 4); }
+    for (int a = 0; a < 2; ++a) { ptx::mbar_init(acc_full(a), 1); ptx::mbar_init(acc_empty(a), kDcolEpiWarps); }
     ptx::mbar_init(a_full, 1);
     ptx::mbar_init(a_empty, 1);
     *abort_flag = 0;
@@ -136,45 +147,47 @@ dcol_sm100_kernel(const DcolParams p) {
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp < 4) {
-    // ---- epilogue: TMEM -> dcol (each thread owns one voxel row; 128 B contiguous per 32 columns)
+  if (warp < kDcolEpiWarps) {
+    // ---- epilogue: TMEM -> dcol (a thread owns one voxel row and a 128-column half of the block)
+    const int quarter = warp & 3, half = warp >> 2;
     uint32_t q = 0;
-    bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < p.n_tiles; tile += gridDim.x) {
+    for (long long u = u_beg; u < u_end; ++u, ++q) {
+      const int tile = (int)(u / p.NB), nb = (int)(u % p.NB);
       const int bl = tile / p.tiles_per_clip, v0 = (tile % p.tiles_per_clip) * kBM;
-      const int v = v0 + warp * 32 + lane;
-      float* row = p.dcol + ((long long)bl * p.V + v) * p.NT;
-      for (int nb = 0; nb < p.NB; ++nb, ++q) {
-        const int acc = q & 1;
-        const int ncols = min(kNBlock, p.NT - nb * kNBlock);
-        if (!ptx::mbar_wait(acc_full(acc), (q >> 1) & 1, abort_flag)) { ok = false; break; }
-        ptx::tc_fence_after();
-        for (int c0 = 0; c0 < ncols; c0 += 32) {
-          uint32_t r[32];
-          ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(acc * kNBlock + c0), r);
-          ptx::tmem_ld_wait();
-          if (v < p.V) {
-            float4* dst = reinterpret_cast<float4*>(row + nb * kNBlock + c0);
+      const int v = v0 + quarter * 32 + lane;
+      float* row = p.dcol + ((long long)bl * p.V + v) * p.NT + nb * kNBlock;
+      const int acc = q & 1;
+      const int ncols = min(kNBlock, p.NT - nb * kNBlock);
+      if (!ptx::mbar_wait(acc_full(acc), (q >> 1) & 1, abort_flag)) break;
+      ptx::tc_fence_after();
+      for (int c0 = half * 128; c0 < min(ncols, half * 128 + 128); c0 += 32) {
+        uint32_t r[32];
+        ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * kNBlock + c0), r);
+        ptx::tmem_ld_wait();
+        if (v < p.V) {
+          float4* dst = reinterpret_cast<float4*>(row + c0);
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
-              dst[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
-                                   __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
-          }
+          for (int i = 0; i < 8; ++i)
+            dst[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
+                                 __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
         }
-        ptx::tc_fence_before();
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(acc_empty(acc));
       }
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(acc_empty(acc));
     }
-  } else if (warp == 4) {
+  } else if (warp == kDcolMmaWarp) {
     if (lane == 0) {
       uint32_t q = 0, kbc = 0;
-      int it = 0;
+      int seg = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < p.n_tiles; tile += gridDim.x, ++it) {
-        if (!ptx::mbar_wait(a_full, it & 1, abort_flag)) break;
+      for (long long u = u_beg; ok && u < u_end; ++seg) {
+        const int nb_beg = (int)(u % p.NB);
+        const int nb_end = (int)min((long long)p.NB, nb_beg + (u_end - u));
+        u += nb_end - nb_beg;
+        if (!ptx::mbar_wait(a_full, seg & 1, abort_flag)) break;
         ptx::tc_fence_after();
-        for (int nb = 0; ok && nb < p.NB; ++nb, ++q) {
+        for (int nb = nb_beg; ok && nb < nb_end; ++nb, ++q) {
           const int acc = q & 1;
           const int ncols = min(kNBlock, p.NT - nb * kNBlock);
           if (!ptx::mbar_wait(acc_empty(acc), ((q >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
@@ -197,18 +210,21 @@ dcol_sm100_kernel(const DcolParams p) {
         if (ok) ptx::umma_commit(a_empty);
       }
     }
-  } else {
+  } else if (warp == kDcolLoadWarp) {
     if (lane == 0) {
       uint32_t kbc = 0;
-      int it = 0;
+      int seg = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < p.n_tiles; tile += gridDim.x, ++it) {
-        if (!ptx::mbar_wait(a_empty, (it & 1) ^ 1, abort_flag)) break;
+      for (long long u = u_beg; ok && u < u_end; ++seg) {
+        const int tile = (int)(u / p.NB), nb_beg = (int)(u % p.NB);
+        const int nb_end = (int)min((long long)p.NB, nb_beg + (u_end - u));
+        u += nb_end - nb_beg;
+        if (!ptx::mbar_wait(a_empty, (seg & 1) ^ 1, abort_flag)) break;
         ptx::mbar_arrive_expect_tx(a_full, (uint32_t)a_bytes);
         const uint8_t* asrc = p.gy_img + (long long)tile * a_bytes;
         for (int off = 0; off < a_bytes; off += 32768)
           ptx::bulk_g2s(a_base + off, asrc + off, (uint32_t)min(32768, a_bytes - off), a_full);
-        for (int nb = 0; ok && nb < p.NB; ++nb) {
+        for (int nb = nb_beg; ok && nb < nb_end; ++nb) {
           const int ncols = min(kNBlock, p.NT - nb * kNBlock);
           for (int kb = 0; kb < p.KB; ++kb, ++kbc) {
             const int sb = kbc % kBStages;
@@ -226,9 +242,9 @@ dcol_sm100_kernel(const DcolParams p) {
         while (!ptx::mbar_try_wait(b_full(qq % kBStages), (qq / kBStages) & 1))
           if (clock64() - t0 > ptx::kWaitBudgetCycles) break;
       }
-      if (it > 0) {
+      if (seg > 0) {
         const long long t0 = clock64();
-        while (!ptx::mbar_try_wait(a_full, (it - 1) & 1))
+        while (!ptx::mbar_try_wait(a_full, (seg - 1) & 1))
           if (clock64() - t0 > ptx::kWaitBudgetCycles) break;
       }
     }
@@ -249,96 +265,87 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
                : "memory");
 }
 
-// 8 threads per (clip, offset group, tap, voxel): thread j owns channels [8j, 8j+8) of each 64-channel slice.
-// Voxels are the fastest-varying item index, so offset / mask reads and gradient writes coalesce.
-template <typename Coords, bool FieldOut>
+// Block = 32 voxels of one (clip, offset group, tap) -- blockIdx.y -- times 8 threads per voxel; thread j owns
+// channels [8j, 8j+8) of each 64-channel slice.  The sampling position comes from the call's records, so
+// there is no integer division and no strided offset read in here.
+template <bool FieldOut>
 __global__ void __launch_bounds__(256)
-sample_grad_kernel(Geom g, Coords coords, int b0, int nbc, int nh, int NT, const float* __restrict__ dcol,
-                   const __nv_bfloat16* __restrict__ x_cl, const float* __restrict__ mask,
-                   float* __restrict__ grad_coord, float* __restrict__ grad_mask, float* __restrict__ gx_cl) {
-  const long long n_items = (long long)nbc * g.G * g.K * g.V;
+sample_grad_kernel(Geom g, ClStrides cs, int b0, int nh, int NT, const float4* __restrict__ recs,
+                   const float* __restrict__ dcol, const __nv_bfloat16* __restrict__ x_cl, bool has_mask,
+                   float* __restrict__ grad_coord, float* __restrict__ grad_mask, float* __restrict__ gx_cl,
+                   int field_nch, int3 field_ch, const float* __restrict__ field_axes) {
   const int j = threadIdx.x & 7;
-  const long long items_per_sweep = (long long)gridDim.x * 32;
-  for (long long item0 = (long long)blockIdx.x * 32; item0 < n_items; item0 += items_per_sweep) {
-    const long long item = item0 + (threadIdx.x >> 3);
-    const bool active = item < n_items;
-    float G[8];
+  const int v = blockIdx.x * 32 + (threadIdx.x >> 3);
+  const int tap = blockIdx.y % g.K, grp = (blockIdx.y / g.K) % g.G, bl = blockIdx.y / (g.K * g.G);
+  const int b = b0 + bl;
+  const bool active = v < g.V;
+  float G[8];
 #pragma unroll
-    for (int q = 0; q < 8; ++q) G[q] = 0.f;
-    Sample<float> s;
-    float a[8], m = 1.f;
-    int v = 0, tap = 0, grp = 0, b = b0;
-    if (active) {
-      v = (int)(item % g.V);
-      tap = (int)((item / g.V) % g.K);
-      grp = (int)((item / ((long long)g.V * g.K)) % g.G);
-      const int bl = (int)(item / ((long long)g.V * g.K * g.G));
-      b = b0 + bl;
-      int bz, by, bx;
-      voxel_tap_base(g, v, tap, bz, by, bx);
-      float z, y, x;
-      coords.get(g, b, grp, tap, v, bz, by, bx, z, y, x);
-      s = make_sample(g, z, y, x);
-      sample_weights(s, a);
-      if (mask) m = __ldg(mask + (((long long)b * g.G + grp) * g.K + tap) * g.V + v);
-      // scatter weights of the reference's col2im: (1-|z-zp|)(1-|y-yp|)(1-|x-xp|), corners at distance
-      // exactly 1 excluded (dconv3d_gpu.cu:626-637)
-      const float wz[2] = {sub_rn(1.f, s.fz), sub_rn(1.f, s.gz)};
-      const float wy[2] = {sub_rn(1.f, s.fy), sub_rn(1.f, s.gy)};
-      const float wx[2] = {sub_rn(1.f, s.fx), sub_rn(1.f, s.gx)};
-      const bool okz[2] = {true, s.gz < 1.f}, oky[2] = {true, s.gy < 1.f}, okx[2] = {true, s.gx < 1.f};
-      long long vox[8];
-      float sw[8];
+  for (int q = 0; q < 8; ++q) G[q] = 0.f;
+  Sample<float> s;
+  float m = 1.f;
+  const long long ri = (((long long)b * g.G + grp) * g.K + tap) * g.V + v;
+  if (active) {
+    const float4 rec = __ldg(recs + ri);
+    m = rec.w;
+    s = make_sample(g, rec.x, rec.y, rec.z);
+    // scatter weights of the reference's col2im: (1-|z-zp|)(1-|y-yp|)(1-|x-xp|), corners at distance
+    // exactly 1 excluded (dconv3d_gpu.cu:626-637)
+    const float wz[2] = {sub_rn(1.f, s.fz), sub_rn(1.f, s.gz)};
+    const float wy[2] = {sub_rn(1.f, s.fy), sub_rn(1.f, s.gy)};
+    const float wx[2] = {sub_rn(1.f, s.fx), sub_rn(1.f, s.gx)};
+    const bool okz[2] = {true, s.gz < 1.f}, oky[2] = {true, s.gy < 1.f}, okx[2] = {true, s.gx < 1.f};
+    const int off0 = ((s.z0 * g.H + s.y0) * g.W + s.x0) * g.Cin + grp * g.cpg + j * 8;
+    const __nv_bfloat16* xb = x_cl + (long long)b * g.Vin * g.Cin;
+    float* gxb = gx_cl + (long long)b * g.Vin * g.Cin;
+    const float* drow = dcol + ((long long)bl * g.V + v) * NT + (long long)((grp * g.K + tap) * nh) * 64 + j * 8;
+    for (int h = 0; h < nh; ++h) {
+      const float4 d0 = __ldg(reinterpret_cast<const float4*>(drow + h * 64));
+      const float4 d1 = __ldg(reinterpret_cast<const float4*>(drow + h * 64) + 1);
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
+        if (!((s.valid >> q) & 1u)) continue;
         const int dz = q >> 2, dy = (q >> 1) & 1, dx = q & 1;
-        vox[q] = (((long long)b * g.D + (s.z0 + dz)) * g.H + (s.y0 + dy)) * g.W + (s.x0 + dx);
-        sw[q] = (okz[dz] && oky[dy] && okx[dx]) ? mul_rn(mul_rn(wz[dz], wy[dy]), wx[dx]) * m : 0.f;
-      }
-      const float* drow = dcol + ((long long)bl * g.V + v) * NT + (long long)((grp * g.K + tap) * nh) * 64 + j * 8;
-      for (int h = 0; h < nh; ++h) {
-        const int ch0 = grp * g.cpg + h * 64 + j * 8;
-        const float4 d0 = __ldg(reinterpret_cast<const float4*>(drow + h * 64));
-        const float4 d1 = __ldg(reinterpret_cast<const float4*>(drow + h * 64) + 1);
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          if (!((s.valid >> q) & 1u)) continue;
-          const uint4 c = ptx::ldg_nc_v4(x_cl + vox[q] * g.Cin + ch0);
-          G[q] += d0.x * ptx::bf16_lo(c.x) + d0.y * ptx::bf16_hi(c.x) + d0.z * ptx::bf16_lo(c.y) +
-                  d0.w * ptx::bf16_hi(c.y) + d1.x * ptx::bf16_lo(c.z) + d1.y * ptx::bf16_hi(c.z) +
-                  d1.z * ptx::bf16_lo(c.w) + d1.w * ptx::bf16_hi(c.w);
-          if (sw[q] != 0.f) {
-            float* dst = gx_cl + vox[q] * g.Cin + ch0;
-            red_add_v4(dst, sw[q] * d0.x, sw[q] * d0.y, sw[q] * d0.z, sw[q] * d0.w);
-            red_add_v4(dst + 4, sw[q] * d1.x, sw[q] * d1.y, sw[q] * d1.z, sw[q] * d1.w);
-          }
+        const int off = off0 + h * 64 + dz * cs.dz + dy * cs.dy + dx * cs.dx;
+        const uint4 c = ptx::ldg_nc_v4(xb + off);
+        G[q] += d0.x * ptx::bf16_lo(c.x) + d0.y * ptx::bf16_hi(c.x) + d0.z * ptx::bf16_lo(c.y) +
+                d0.w * ptx::bf16_hi(c.y) + d1.x * ptx::bf16_lo(c.z) + d1.y * ptx::bf16_hi(c.z) +
+                d1.z * ptx::bf16_lo(c.w) + d1.w * ptx::bf16_hi(c.w);
+        if (okz[dz] && oky[dy] && okx[dx]) {
+          const float sw = mul_rn(mul_rn(wz[dz], wy[dy]), wx[dx]) * m;
+          float* dst = gxb + off;
+          red_add_v4(dst, sw * d0.x, sw * d0.y, sw * d0.z, sw * d0.w);
+          red_add_v4(dst + 4, sw * d1.x, sw * d1.y, sw * d1.z, sw * d1.w);
         }
       }
     }
-    // channel reduction of the 8 corner dot-products across the item's 8 threads
+  }
+  // channel reduction of the 8 corner dot-products across the voxel's 8 threads
 #pragma unroll
-    for (int q = 0; q < 8; ++q) {
-      G[q] += __shfl_xor_sync(0xffffffffu, G[q], 1);
-      G[q] += __shfl_xor_sync(0xffffffffu, G[q], 2);
-      G[q] += __shfl_xor_sync(0xffffffffu, G[q], 4);
+  for (int q = 0; q < 8; ++q) {
+    G[q] += __shfl_xor_sync(0xffffffffu, G[q], 1);
+    G[q] += __shfl_xor_sync(0xffffffffu, G[q], 2);
+    G[q] += __shfl_xor_sync(0xffffffffu, G[q], 4);
+  }
+  if (active && j == 0) {
+    float wts[3];
+    coord_weights(G, s, wts);    // linear in the corner values: applies to the channel-summed corners
+    if (has_mask && grad_mask) {
+      float a[8];
+      sample_weights(s, a);
+      grad_mask[ri] = s.inside ? blend(G, a) : 0.f;
     }
-    if (active && j == 0) {
-      float wts[3];
-      coord_weights(G, s, wts);    // linear in the corner values: applies to the channel-summed corners
-      const long long mi = (((long long)b * g.G + grp) * g.K + tap) * g.V + v;
-      if (mask && grad_mask) grad_mask[mi] = s.inside ? blend(G, a) : 0.f;
-      if constexpr (!FieldOut) {
-        float* go = grad_coord + (((long long)b * g.G + grp) * 3 * g.K + 3 * tap) * g.V + v;
-        go[0] = m * wts[0];
-        go[g.V] = m * wts[1];
-        go[2 * (long long)g.V] = m * wts[2];
-      } else {
-        const int k = tap % g.kw, jj = (tap / g.kw) % g.kh, i = tap / (g.kw * g.kh);
-        float* gs = grad_coord + (long long)b * coords.nch * g.V + v;
-        if (coords.ch[0] >= 0) atomicAdd(gs + (long long)coords.ch[0] * g.V, coords.axis[0][i] * (m * wts[0]));
-        if (coords.ch[1] >= 0) atomicAdd(gs + (long long)coords.ch[1] * g.V, coords.axis[1][jj] * (m * wts[1]));
-        if (coords.ch[2] >= 0) atomicAdd(gs + (long long)coords.ch[2] * g.V, coords.axis[2][k] * (m * wts[2]));
-      }
+    if constexpr (!FieldOut) {
+      float* go = grad_coord + (((long long)b * g.G + grp) * 3 * g.K + 3 * tap) * g.V + v;
+      go[0] = m * wts[0];
+      go[g.V] = m * wts[1];
+      go[2 * (long long)g.V] = m * wts[2];
+    } else {
+      const int k = tap % g.kw, jj = (tap / g.kw) % g.kh, i = tap / (g.kw * g.kh);
+      float* gs = grad_coord + (long long)b * field_nch * g.V + v;
+      if (field_ch.x >= 0) atomicAdd(gs + (long long)field_ch.x * g.V, field_axes[i] * (m * wts[0]));
+      if (field_ch.y >= 0) atomicAdd(gs + (long long)field_ch.y * g.V, field_axes[kMaxFieldKernelDim + jj] * (m * wts[1]));
+      if (field_ch.z >= 0) atomicAdd(gs + (long long)field_ch.z * g.V, field_axes[2 * kMaxFieldKernelDim + k] * (m * wts[2]));
     }
   }
 }
@@ -363,11 +370,13 @@ unstage_grad_input_kernel(int C, long long Vin, const float* __restrict__ gx_cl,
 
 struct BwdPlan {
   int nh, S, NT, KB, NB, tiles_per_clip, tmem_cols, smem_bytes, clips_per_chunk;
-  size_t x_cl_bytes, gy_img_bytes, wt_img_bytes, dcol_bytes, gx_cl_bytes;
+  size_t x_cl_bytes, rec_bytes, gy_img_bytes, wt_img_bytes, dcol_bytes, gx_cl_bytes, axes_bytes;
 };
 
 bool make_bwd_plan(const Geom& g, unsigned long long cap, BwdPlan* pl) {
-  if (g.groups != 1 || g.cpg % 64 != 0 || g.Cout % 64 != 0 || g.Cout > 512 || g.Cin % 32 != 0) return false;
+  if (g.groups != 1 || g.cpg % 64 != 0 || g.Cout % 64 != 0 || g.Cout > 512) return false;
+  if (g.Vin * g.Cin > 0x7fffffffLL) return false;
+  if ((long long)g.G * g.K * g.B > 65535) return false;
   pl->nh = g.cpg / 64;
   pl->S = g.G * g.K * pl->nh;
   pl->NT = pl->S * 64;
@@ -379,10 +388,12 @@ bool make_bwd_plan(const Geom& g, unsigned long long cap, BwdPlan* pl) {
   if (pl->smem_bytes > kSmemLimit) return false;
   pl->clips_per_chunk = bwd_slice_clips(g, cap);
   pl->x_cl_bytes = align_up((size_t)g.B * g.Vin * g.Cin * 2, 256);
+  pl->rec_bytes = coord_records_bytes(g);
   pl->gy_img_bytes = align_up((size_t)pl->clips_per_chunk * pl->tiles_per_clip * pl->KB * kABlockBytes, 256);
   pl->wt_img_bytes = align_up((size_t)pl->NB * pl->KB * kBStageBytes, 256);
   pl->dcol_bytes = align_up((size_t)pl->clips_per_chunk * g.V * pl->NT * 4, 256);
   pl->gx_cl_bytes = align_up((size_t)g.B * g.Vin * g.Cin * 4, 256);
+  pl->axes_bytes = 256;
   return true;
 }
 
@@ -394,10 +405,12 @@ int run_bwd(const Geom& g, const Coords& coords, unsigned long long cap, const f
   if (!make_bwd_plan(g, cap, &pl)) return D2C_ERR_MODE;
   uint8_t* wsp = reinterpret_cast<uint8_t*>(ws);
   __nv_bfloat16* x_cl = reinterpret_cast<__nv_bfloat16*>(wsp); wsp += pl.x_cl_bytes;
+  float4* recs = reinterpret_cast<float4*>(wsp); wsp += pl.rec_bytes;
   uint8_t* gy_img = wsp; wsp += pl.gy_img_bytes;
   uint8_t* wt_img = wsp; wsp += pl.wt_img_bytes;
   float* dcol = reinterpret_cast<float*>(wsp); wsp += pl.dcol_bytes;
   float* gx_cl = reinterpret_cast<float*>(wsp); wsp += pl.gx_cl_bytes;
+  float* axes_dev = reinterpret_cast<float*>(wsp); wsp += pl.axes_bytes;
   void* dw_ws = wsp;
 
   static int sm_count = 0;
@@ -405,6 +418,19 @@ int run_bwd(const Geom& g, const Coords& coords, unsigned long long cap, const f
     int dev = 0;
     D2C_CUDA_TRY(cudaGetDevice(&dev));
     D2C_CUDA_TRY(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
+  }
+  int rc;
+  ClStrides cs;
+  cs.dz = g.H * g.W * g.Cin; cs.dy = g.W * g.Cin; cs.dx = g.Cin;
+
+  // dilation-field variant: tap positions per dim, read by the kernel that accumulates grad_size_map
+  int field_nch = 0;
+  int3 field_ch = make_int3(-1, -1, -1);
+  if constexpr (FieldOut) {
+    field_nch = coords.nch;
+    field_ch = make_int3(coords.ch[0], coords.ch[1], coords.ch[2]);
+    D2C_CUDA_TRY(cudaMemcpyAsync(axes_dev, &coords.axis[0][0], sizeof(float) * 3 * kMaxFieldKernelDim,
+                                 cudaMemcpyHostToDevice, st));
   }
 
   prof_mark(st, "bwd_stage_operands");
@@ -416,6 +442,7 @@ int run_bwd(const Geom& g, const Coords& coords, unsigned long long cap, const f
     D2C_LAUNCH_CHECK();
     stage_wt_img_kernel<<<sm_count * 8, 256, 0, st>>>(g.Cout, g.Cin, g.K, g.cpg, pl.nh, pl.S, w, wt_img);
     D2C_LAUNCH_CHECK();
+    if ((rc = launch_coord_records(g, coords, mask, recs, st))) return rc;
   }
   D2C_CUDA_TRY(cudaFuncSetAttribute(dcol_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes));
 
@@ -428,17 +455,20 @@ int run_bwd(const Geom& g, const Coords& coords, unsigned long long cap, const f
     D2C_LAUNCH_CHECK();
     DcolParams p;
     p.gy_img = gy_img; p.wt_img = wt_img; p.dcol = dcol;
-    p.V = g.V; p.NT = pl.NT; p.KB = pl.KB; p.NB = pl.NB; p.S = pl.S;
-    p.tiles_per_clip = pl.tiles_per_clip; p.n_tiles = n_tiles; p.tmem_cols = pl.tmem_cols;
+    p.V = g.V; p.NT = pl.NT; p.KB = pl.KB; p.NB = pl.NB;
+    p.tiles_per_clip = pl.tiles_per_clip; p.n_tiles = n_tiles; p.n_units = (long long)n_tiles * pl.NB;
+    p.tmem_cols = pl.tmem_cols;
+    long long grid = p.n_units / 4;
+    if (grid > sm_count) grid = sm_count;
+    if (grid < 1) grid = 1;
     prof_mark(st, "bwd_dcol_sm100");
-    dcol_sm100_kernel<<<n_tiles < sm_count ? n_tiles : sm_count, kDcolThreads, pl.smem_bytes, st>>>(p);
+    dcol_sm100_kernel<<<(unsigned)grid, kDcolThreads, pl.smem_bytes, st>>>(p);
     D2C_LAUNCH_CHECK();
     prof_mark(st, "bwd_sample_grad");
-    const long long items = (long long)nbc * g.G * g.K * g.V;
-    long long blocks = (items + 31) / 32;
-    if (blocks > (long long)sm_count * 16) blocks = (long long)sm_count * 16;
-    sample_grad_kernel<Coords, FieldOut><<<(unsigned)blocks, 256, 0, st>>>(g, coords, b0, nbc, pl.nh, pl.NT, dcol, x_cl,
-                                                                          mask, grad_coord, grad_mask, gx_cl);
+    dim3 sgrid((unsigned)((g.V + 31) / 32), (unsigned)(nbc * g.G * g.K));
+    sample_grad_kernel<FieldOut><<<sgrid, 256, 0, st>>>(g, cs, b0, pl.nh, pl.NT, recs, dcol, x_cl, mask != nullptr,
+                                                        grad_coord, grad_mask, gx_cl, field_nch, field_ch,
+                                                        axes_dev);
     D2C_LAUNCH_CHECK();
   }
   prof_mark(st, "bwd_unstage_grad_input");
@@ -448,12 +478,7 @@ int run_bwd(const Geom& g, const Coords& coords, unsigned long long cap, const f
     D2C_LAUNCH_CHECK();
   }
   // weight gradient: tensor-core implicit GEMM over the re-sampled tile
-  {
-    int rc;
-    if constexpr (FieldOut) rc = sm100_dw_field(g, coords, gy, x_cl, mask, grad_w, dw_ws, st);
-    else rc = sm100_dw_offsets(g, coords.offset, gy, x_cl, mask, grad_w, dw_ws, st);
-    if (rc) return rc;
-  }
+  if ((rc = sm100_dw(g, gy, x_cl, recs, grad_w, dw_ws, st))) return rc;
   if (grad_bias) {
     prof_mark(st, "bwd_grad_bias");
     grad_bias_kernel<float><<<g.Cout, 256, 0, st>>>(g.B, g.Cout, g.V, gy, grad_bias);
@@ -475,7 +500,8 @@ size_t sm100_bwd_workspace(const Geom& g, int dtype, int math_mode, unsigned lon
   if (!sm100_bwd_supported(g, dtype, math_mode, cap)) return 0;
   BwdPlan pl;
   make_bwd_plan(g, cap, &pl);
-  return pl.x_cl_bytes + pl.gy_img_bytes + pl.wt_img_bytes + pl.dcol_bytes + pl.gx_cl_bytes + sm100_dw_workspace(g);
+  return pl.x_cl_bytes + pl.rec_bytes + pl.gy_img_bytes + pl.wt_img_bytes + pl.dcol_bytes + pl.gx_cl_bytes +
+         pl.axes_bytes + sm100_dw_workspace(g);
 }
 
 int sm100_bwd_offsets(const Geom& g, unsigned long long cap, const float* gy, const float* x, const float* offset,

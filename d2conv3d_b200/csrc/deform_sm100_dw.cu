@@ -1,0 +1,353 @@
+// Weight gradient of the deformable conv3d for sm_100a as an implicit GEMM over voxels that consumes
+// the SAME sampled tile as the forward:
+//   dW[(slice, c), co] = sum_{b, v} sample[b, v, (slice, c)] * grad_out[b, co, v]
+// (reference: re-im2col + cuBLAS gemmStridedBatched + sum over the batch, csrc/ops/dconv3d_gpu.cu:1037-1088).
+//
+// One CTA owns a PAIR of K slices (2 x 64 channels = the 128 rows of the accumulator) and a contiguous
+// range of voxel tiles; its accumulator [128 x Cout] fp32 lives in tensor memory for the whole range.
+//   A operand: the two sampled [128 voxels x 64 ch] tiles, read MN-major (M = channel is the contiguous
+//              dimension, K = voxel): byte-identical to the forward's K-major A tile.
+//   B operand: grad_out as bf16 [co rows x 64 voxels], K-major, staged per 64-voxel block.
+// The partial results of different voxel ranges are combined with vector reductions into a [S*64, Cout]
+// fp32 buffer that a last kernel permutes into the [Cout, Cin, kd, kh, kw] layout of grad_weight.
+#include "deform_sm100.h"
+#include "sm100_gather.cuh"
+#include "sm100_ptx.cuh"
+
+namespace d2c {
+
+namespace {
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;
+constexpr int kTileBytes = kBM * kBK * 2;            // one sampled slice tile: 16 KB
+constexpr int kAStages = 2;
+constexpr int kAStageBytes = 2 * kTileBytes;         // two slices
+constexpr int kBStages = 2;
+constexpr int kChunkBytes = 256 * 128;               // one 256-row (co) x 64-voxel image
+constexpr int kThreads = 448;
+constexpr int kEpiWarps = 4, kMmaWarp = 4, kLoadWarp = 5, kGatherWarp0 = 6, kGatherWarps = 8;
+constexpr int kSmemLimit = 227 * 1024;
+
+__device__ int g_sm100_dw_status = 0;
+
+struct DwParams {
+  Geom g;
+  const __nv_bfloat16* x_cl;
+  const float4* recs;
+  const uint8_t* gyk_img;    // [n_tiles][2 voxel blocks][NCH][32 KB]
+  float* dws;                // [S*64][Cout] fp32, zero-initialised
+  ClStrides cs;
+  int N, nh, S, tiles_per_clip, n_tiles, tmem_cols;
+  int n_pairs, tiles_per_split, NCH, b_stage_bytes;
+};
+
+// grad_out [B][Cout][V] fp32 -> per (tile, 64-voxel block, 256-co chunk) images: 256 rows (co) x 128 B
+// (64 voxels, bf16), chunks XOR-swizzled by (row & 7).  Voxels past the clip are zero.
+__global__ void __launch_bounds__(256)
+stage_gy_kmajor_kernel(int Cout, int V, int tiles_per_clip, int NCH, const float* __restrict__ gy,
+                       uint8_t* __restrict__ img) {
+  const int tile = blockIdx.x, coblk = blockIdx.y;        // coblk: 64 rows of co
+  const int b = tile / tiles_per_clip, v0 = (tile % tiles_per_clip) * kBM;
+  for (int e = threadIdx.x; e < 64 * 16; e += 256) {
+    const int rl = e >> 4, q = e & 15;                    // row within block, 8-voxel chunk (0..15)
+    const int co = coblk * 64 + rl;
+    if (co >= Cout) continue;
+    const int v = v0 + q * 8;
+    float f[8];
+    const float* src = gy + ((long long)b * Cout + co) * V;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = (v + i < V) ? __ldg(src + v + i) : 0.f;
+    uint4 o;
+    o.x = ptx::pack_bf16x2(f[0], f[1]); o.y = ptx::pack_bf16x2(f[2], f[3]);
+    o.z = ptx::pack_bf16x2(f[4], f[5]); o.w = ptx::pack_bf16x2(f[6], f[7]);
+    const int kblk = q >> 3, j = q & 7, chunk = co >> 8, row = co & 255;
+    uint8_t* dst = img + (((long long)tile * 2 + kblk) * NCH + chunk) * kChunkBytes + (row >> 3) * 1024 +
+                   (row & 7) * 128 + ((j ^ (row & 7)) << 4);
+    *reinterpret_cast<uint4*>(dst) = o;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+dw_sm100_kernel(const DwParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = ptx::smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - raw);
+  const uint32_t a_base = base, b_base = base + kAStages * kAStageBytes;
+  const int bar_off = kAStages * kAStageBytes + kBStages * p.b_stage_bytes;
+  const uint32_t bar_base = base + bar_off;
+  auto a_full = [&](int s) { return bar_base + 8u * s; };
+  auto a_empty = [&](int s) { return bar_base + 8u * (2 + s); };
+  auto b_full = [&](int s) { return bar_base + 8u * (4 + s); };
+  auto b_empty = [&](int s) { return bar_base + 8u * (6 + s); };
+  const uint32_t acc_full = bar_base + 8u * 8;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + bar_off + 8 * 9);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + bar_off + 8 * 9 + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const Geom& g = p.g;
+  const int pair = blockIdx.x % p.n_pairs, split = blockIdx.x / p.n_pairs;
+  const int tile_beg = split * p.tiles_per_split;
+  const int tile_end = min(p.n_tiles, tile_beg + p.tiles_per_split);
+  const int n_my_tiles = tile_end - tile_beg;          // may be <= 0 for a trailing split
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kAStages; ++s) { ptx::mbar_init(a_full(s), kGatherWarps); ptx::mbar_init(a_empty(s), 1); }
+    for (int s = 0; s < kBStages; ++s) { ptx::mbar_init(b_full(s), 1); ptx::mbar_init(b_empty(s), 1); }
+    ptx::mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    ptx::fence_mbar_init();
+  }
+  if (warp == 0) {
+    __syncwarp();
+    ptx::tmem_alloc(ptx::smem_u32((const void*)tmem_slot), (uint32_t)p.tmem_cols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (n_my_tiles > 0) {
+    if (warp < kEpiWarps) {
+      // ---- epilogue (once): accumulator rows (slice_local*64 + c) x columns co -> dws, vector reductions
+      if (ptx::mbar_wait(acc_full, 0, abort_flag)) {
+        ptx::tc_fence_after();
+        const int m = warp * 32 + lane;
+        const int s = 2 * pair + (m >> 6);
+        float* row = p.dws + ((long long)s * 64 + (m & 63)) * p.N;
+        for (int c0 = 0; c0 < p.N; c0 += 32) {
+          uint32_t r[32];
+          ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);
+          ptx::tmem_ld_wait();
+          if (s < p.S) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(row + c0 + 4 * i),
+                           "f"(__uint_as_float(r[4 * i])), "f"(__uint_as_float(r[4 * i + 1])),
+                           "f"(__uint_as_float(r[4 * i + 2])), "f"(__uint_as_float(r[4 * i + 3]))
+                           : "memory");
+          }
+        }
+        ptx::tc_fence_before();
+      }
+    } else if (warp == kMmaWarp) {
+      if (lane == 0) {
+        uint32_t kb = 0;
+        bool ok = true;
+        for (int t = 0; ok && t < n_my_tiles; ++t) {
+          const int sa = t % kAStages;
+          if (!ptx::mbar_wait(a_full(sa), (t / kAStages) & 1, abort_flag)) break;
+          for (int kblk = 0; kblk < 2; ++kblk, ++kb) {
+            const int sb = kb % kBStages;
+            if (!ptx::mbar_wait(b_full(sb), (kb / kBStages) & 1, abort_flag)) { ok = false; break; }
+            ptx::tc_fence_after();
+#pragma unroll
+            for (int k4 = 0; k4 < 4; ++k4) {
+              // A: 16 voxels starting at voxel kblk*64 + k4*16 -> two 8-row groups of 1024 bytes;
+              //    the second slice's tile (rows 64..127 of M) sits kTileBytes further (LBO)
+              const uint64_t adesc = ptx::umma_desc_mnmajor_sw128(
+                  a_base + sa * kAStageBytes + (kblk * 8 + k4 * 2) * 1024, kTileBytes, 1024);
+              for (int n0 = 0; n0 < p.N; n0 += 256) {
+                const int nc = min(256, p.N - n0);
+                const uint64_t bdesc =
+                    ptx::umma_desc_kmajor_sw128(b_base + sb * p.b_stage_bytes + (n0 >> 8) * kChunkBytes) +
+                    (uint64_t)(2 * k4);
+                ptx::umma_bf16(tmem_base + (uint32_t)n0, adesc, bdesc,
+                               ptx::umma_idesc_bf16_f32(kBM, nc) | (1u << 15) /* A is MN-major */,
+                               (t > 0 || kblk > 0 || k4 > 0) ? 1u : 0u);
+              }
+            }
+            ptx::umma_commit(b_empty(sb));
+          }
+          if (ok) ptx::umma_commit(a_empty(sa));
+        }
+        if (ok) ptx::umma_commit(acc_full);
+      }
+    } else if (warp == kLoadWarp) {
+      if (lane == 0) {
+        uint32_t kb = 0;
+        bool ok = true;
+        for (int t = 0; ok && t < n_my_tiles; ++t) {
+          for (int kblk = 0; kblk < 2; ++kblk, ++kb) {
+            const int sb = kb % kBStages;
+            if (!ptx::mbar_wait(b_empty(sb), ((kb / kBStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
+            ptx::mbar_arrive_expect_tx(b_full(sb), (uint32_t)p.b_stage_bytes);
+            const uint8_t* src = p.gyk_img + ((long long)(tile_beg + t) * 2 + kblk) * p.b_stage_bytes;
+            for (int off = 0; off < p.b_stage_bytes; off += 32768)
+              ptx::bulk_g2s(b_base + sb * p.b_stage_bytes + off, src + off, 32768u, b_full(sb));
+          }
+        }
+        const uint32_t issued = kb;
+        for (uint32_t q = (issued > (uint32_t)kBStages ? issued - kBStages : 0); q < issued; ++q) {
+          const long long t0 = clock64();
+          while (!ptx::mbar_try_wait(b_full(q % kBStages), (q / kBStages) & 1))
+            if (clock64() - t0 > ptx::kWaitBudgetCycles) break;
+        }
+      }
+    } else {
+      // ---- gather producers: the forward's producer, two slices per stage; records one tile ahead
+      const int tt = threadIdx.x - kGatherWarp0 * 32;
+      const int j = tt & 7, r0 = tt >> 3;
+      uint32_t row_dst[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int r = r0 + 32 * i;
+        row_dst[i] = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((j ^ (r & 7)) << 4));
+      }
+      int grp_[2], tap_[2], ch0_[2];
+#pragma unroll
+      for (int sl = 0; sl < 2; ++sl) {
+        const int s = min(2 * pair + sl, p.S - 1);      // an odd last slice is produced twice, second copy unused
+        const int h = s % p.nh, gt = s / p.nh;
+        tap_[sl] = gt % g.K; grp_[sl] = gt / g.K;
+        ch0_[sl] = grp_[sl] * g.cpg + h * kBK + j * 8;
+      }
+      // half-units q = 2*t + sl (tile t of the range, slice sl of the pair); records one half-unit ahead
+      auto load_q = [&](int q, float4 (&out)[4]) {
+        const int tile = tile_beg + (q >> 1), sl = q & 1;
+        const int b = tile / p.tiles_per_clip, v0 = (tile % p.tiles_per_clip) * kBM;
+        load_row_records(p.recs, g, b, sl ? grp_[1] : grp_[0], sl ? tap_[1] : tap_[0], v0, r0, out);
+      };
+      float4 rec[4];
+      load_q(0, rec);
+      const int nq = 2 * n_my_tiles;
+      for (int q = 0; q < nq; ++q) {
+        float4 rec_next[4];
+        if (q + 1 < nq) load_q(q + 1, rec_next);
+        const int t = q >> 1, sl = q & 1, sa = t % kAStages;
+        const int tile = tile_beg + t;
+        const int b = tile / p.tiles_per_clip;
+        if (sl == 0 && !ptx::mbar_wait(a_empty(sa), ((t / kAStages) & 1) ^ 1, abort_flag)) break;
+        const __nv_bfloat16* xb = p.x_cl + (long long)b * g.Vin * g.Cin;
+        const uint32_t stage = a_base + sa * kAStageBytes + sl * kTileBytes;
+        const int ch0 = sl ? ch0_[1] : ch0_[0];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) produce_item_rec(g, xb, p.cs, rec[i], ch0, stage + row_dst[i]);
+        if (sl == 1) {
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(a_full(sa));
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) rec[i] = rec_next[i];
+      }
+    }
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(&g_sm100_dw_status, 1);
+  if (warp == 0) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+  }
+}
+
+// dws [(slice, c)][co] -> grad_w [co][cin][tap]   (cin = grp*cpg + h*64 + c)
+__global__ void __launch_bounds__(256)
+unstage_dw_kernel(int Cout, int Cin, int K, int cpg, int nh, int S, const float* __restrict__ dws,
+                  float* __restrict__ grad_w) {
+  __shared__ float tile[32][33];
+  const int r0 = blockIdx.x * 32, co0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int rr = ty; rr < 32; rr += 8) {
+    const int r = r0 + rr;
+    tile[rr][tx] = (r < S * 64 && co0 + tx < Cout) ? __ldg(dws + (long long)r * Cout + co0 + tx) : 0.f;
+  }
+  __syncthreads();
+  for (int cc = ty; cc < 32; cc += 8) {
+    const int r = r0 + tx, co = co0 + cc;
+    if (r < S * 64 && co < Cout) {
+      const int c = r & 63, s = r >> 6;
+      const int h = s % nh, gt = s / nh, tap = gt % K, grp = gt / K;
+      grad_w[((long long)co * Cin + grp * cpg + h * 64 + c) * K + tap] = tile[tx][cc];
+    }
+  }
+}
+
+struct DwPlan {
+  int nh, S, tiles_per_clip, n_tiles, tmem_cols;
+  int n_pairs, nsplit, tiles_per_split, NCH, b_stage_bytes, smem_bytes;
+  size_t gyk_bytes, dws_bytes;
+};
+
+bool make_dw_plan(const Geom& g, int sm_count, DwPlan* dp) {
+  if (g.groups != 1 || g.cpg % kBK != 0 || g.Cout % 64 != 0 || g.Cout > 512) return false;
+  if (g.Vin * g.Cin > 0x7fffffffLL) return false;
+  dp->nh = g.cpg / kBK;
+  dp->S = g.G * g.K * dp->nh;
+  dp->tiles_per_clip = (g.V + kBM - 1) / kBM;
+  dp->n_tiles = dp->tiles_per_clip * g.B;
+  int cols = 32;
+  while (cols < g.Cout) cols <<= 1;
+  dp->tmem_cols = cols;
+  dp->n_pairs = (dp->S + 1) / 2;
+  dp->NCH = (g.Cout + 255) / 256;
+  dp->b_stage_bytes = dp->NCH * kChunkBytes;
+  dp->smem_bytes = kAStages * kAStageBytes + kBStages * dp->b_stage_bytes + 256 + 1024;
+  if (dp->smem_bytes > kSmemLimit) return false;
+  // enough (pair, voxel-range) work items for ~3 waves, but at least 8 tiles per item
+  int nsplit = (3 * sm_count + dp->n_pairs - 1) / dp->n_pairs;
+  const int max_split = (dp->n_tiles + 7) / 8;
+  if (nsplit > max_split) nsplit = max_split;
+  if (nsplit < 1) nsplit = 1;
+  dp->tiles_per_split = (dp->n_tiles + nsplit - 1) / nsplit;
+  dp->nsplit = (dp->n_tiles + dp->tiles_per_split - 1) / dp->tiles_per_split;
+  dp->gyk_bytes = align_up((size_t)dp->n_tiles * 2 * dp->b_stage_bytes, 256);
+  dp->dws_bytes = align_up((size_t)dp->S * 64 * g.Cout * 4, 256);
+  return true;
+}
+
+}  // namespace
+
+size_t sm100_dw_workspace(const Geom& g) {
+  DwPlan dp;
+  if (!make_dw_plan(g, 148, &dp)) return 0;
+  return dp.gyk_bytes + dp.dws_bytes;
+}
+
+int sm100_dw(const Geom& g, const float* gy, const void* x_cl, const void* recs, float* grad_w, void* ws,
+             cudaStream_t st) {
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    D2C_CUDA_TRY(cudaGetDevice(&dev));
+    D2C_CUDA_TRY(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
+  }
+  DwPlan dp;
+  if (!make_dw_plan(g, sm_count, &dp)) return D2C_ERR_MODE;
+  uint8_t* gyk = reinterpret_cast<uint8_t*>(ws);
+  float* dws = reinterpret_cast<float*>(gyk + dp.gyk_bytes);
+
+  prof_mark(st, "bwd_dw_stage");
+  D2C_CUDA_TRY(cudaMemsetAsync(dws, 0, (size_t)dp.S * 64 * g.Cout * 4, st));
+  stage_gy_kmajor_kernel<<<dim3((unsigned)dp.n_tiles, (unsigned)((g.Cout + 63) / 64)), 256, 0, st>>>(
+      g.Cout, g.V, dp.tiles_per_clip, dp.NCH, gy, gyk);
+  D2C_LAUNCH_CHECK();
+
+  DwParams p;
+  p.g = g; p.x_cl = reinterpret_cast<const __nv_bfloat16*>(x_cl); p.recs = reinterpret_cast<const float4*>(recs);
+  p.gyk_img = gyk; p.dws = dws;
+  p.cs.dz = g.H * g.W * g.Cin; p.cs.dy = g.W * g.Cin; p.cs.dx = g.Cin;
+  p.N = g.Cout; p.nh = dp.nh; p.S = dp.S; p.tiles_per_clip = dp.tiles_per_clip; p.n_tiles = dp.n_tiles;
+  p.tmem_cols = dp.tmem_cols;
+  p.n_pairs = dp.n_pairs; p.tiles_per_split = dp.tiles_per_split; p.NCH = dp.NCH; p.b_stage_bytes = dp.b_stage_bytes;
+  D2C_CUDA_TRY(cudaFuncSetAttribute(dw_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dp.smem_bytes));
+  prof_mark(st, "bwd_dw_sm100");
+  dw_sm100_kernel<<<dp.n_pairs * dp.nsplit, kThreads, dp.smem_bytes, st>>>(p);
+  D2C_LAUNCH_CHECK();
+  prof_mark(st, "bwd_dw_unstage");
+  unstage_dw_kernel<<<dim3((unsigned)((dp.S * 64 + 31) / 32), (unsigned)((g.Cout + 31) / 32)), 256, 0, st>>>(
+      g.Cout, g.Cin, g.K, g.cpg, dp.nh, dp.S, dws, grad_w);
+  D2C_LAUNCH_CHECK();
+  return D2C_OK;
+}
+
+int sm100_dw_device_status() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_sm100_dw_status, sizeof(int)) != cudaSuccess) return -1;
+  return v;
+}
+
+}  // namespace d2c
