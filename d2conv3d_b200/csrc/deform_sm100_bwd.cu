@@ -155,7 +155,10 @@ dcol_sm100_kernel(const DcolParams p) {
       const int tile = (int)(u / p.NB), nb = (int)(u % p.NB);
       const int bl = tile / p.tiles_per_clip, v0 = (tile % p.tiles_per_clip) * kBM;
       const int v = v0 + quarter * 32 + lane;
-      float* row = p.dcol + ((long long)bl * p.V + v) * p.NT + nb * kNBlock;
+      // dcol is slice-major: [clip][slice][voxel][64 channels]; a 256-column block is 4 slices
+      const long long S = p.NT / 64;
+      float* row = p.dcol + (((long long)bl * S + nb * 4) * p.V + v) * 64;
+      const long long slice_stride = (long long)p.V * 64;
       const int acc = q & 1;
       const int ncols = min(kNBlock, p.NT - nb * kNBlock);
       if (!ptx::mbar_wait(acc_full(acc), (q >> 1) & 1, abort_flag)) break;
@@ -165,7 +168,7 @@ dcol_sm100_kernel(const DcolParams p) {
         ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * kNBlock + c0), r);
         ptx::tmem_ld_wait();
         if (v < p.V) {
-          float4* dst = reinterpret_cast<float4*>(row + c0);
+          float4* dst = reinterpret_cast<float4*>(row + (c0 >> 6) * slice_stride + (c0 & 63));
 #pragma unroll
           for (int i = 0; i < 8; ++i)
             dst[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
@@ -261,91 +264,117 @@ dcol_sm100_kernel(const DcolParams p) {
 // ---- (b) sampling gradient + scatter ---------------------------------------------------------------
 
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
-               : "memory");
+  // volatile (must not be dropped) but no memory clobber: read-only loads may move across it
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d));
 }
 
-// Block = 32 voxels of one (clip, offset group, tap) -- blockIdx.y -- times 8 threads per voxel; thread j owns
-// channels [8j, 8j+8) of each 64-channel slice.  The sampling position comes from the call's records, so
-// there is no integer division and no strided offset read in here.
+// Block = 32 voxels of one (clip, offset group) -- blockIdx.y -- times 8 threads per voxel; thread j owns
+// channels [8j, 8j+8) of each 64-channel slice.  The block walks the K taps; the record and the gradient
+// columns of tap t+1 are requested before tap t is processed, so the HBM stream of dcol (slice-major:
+// 8 KB contiguous per block and slice) stays in flight behind the L2 gathers and reductions.
 template <bool FieldOut>
-__global__ void __launch_bounds__(256)
-sample_grad_kernel(Geom g, ClStrides cs, int b0, int nh, int NT, const float4* __restrict__ recs,
-                   const float* __restrict__ dcol, const __nv_bfloat16* __restrict__ x_cl, bool has_mask,
-                   float* __restrict__ grad_coord, float* __restrict__ grad_mask, float* __restrict__ gx_cl,
-                   int field_nch, int3 field_ch, const float* __restrict__ field_axes) {
+__global__ void __launch_bounds__(256, 3)
+sample_grad_taps_kernel(Geom g, ClStrides cs, int b0, int nh, const float4* __restrict__ recs,
+                        const float* __restrict__ dcol, const __nv_bfloat16* __restrict__ x_cl, bool has_mask,
+                        float* __restrict__ grad_coord, float* __restrict__ grad_mask, float* __restrict__ gx_cl,
+                        int field_nch, int3 field_ch, const float* __restrict__ field_axes) {
   const int j = threadIdx.x & 7;
   const int v = blockIdx.x * 32 + (threadIdx.x >> 3);
-  const int tap = blockIdx.y % g.K, grp = (blockIdx.y / g.K) % g.G, bl = blockIdx.y / (g.K * g.G);
+  const int grp = blockIdx.y % g.G, bl = blockIdx.y / g.G;
   const int b = b0 + bl;
   const bool active = v < g.V;
-  float G[8];
-#pragma unroll
-  for (int q = 0; q < 8; ++q) G[q] = 0.f;
-  Sample<float> s;
-  float m = 1.f;
-  const long long ri = (((long long)b * g.G + grp) * g.K + tap) * g.V + v;
-  if (active) {
-    const float4 rec = __ldg(recs + ri);
-    m = rec.w;
-    s = make_sample(g, rec.x, rec.y, rec.z);
+  const int vc = active ? v : g.V - 1;                       // clamped: inactive threads load valid memory
+  const long long S = (long long)g.G * g.K * nh;
+  const float4* recp = recs + (((long long)b * g.G + grp) * g.K) * g.V + vc;
+  // thread j owns channels [4j, 4j+4) and [32+4j, 32+4j+4) of a slice: one warp-wide 16-byte access then
+  // covers whole 32-byte sectors (two lanes each), which halves the sector operations of the reductions
+  const float* dp = dcol + (((long long)bl * S + (long long)grp * g.K * nh) * g.V + vc) * 64 + j * 4;
+  const long long slice_stride = (long long)g.V * 64;
+  const __nv_bfloat16* xb = x_cl + (long long)b * g.Vin * g.Cin;
+  float* gxb = gx_cl + (long long)b * g.Vin * g.Cin;
+  const int chbase = grp * g.cpg + j * 4;
+
+  float4 rec_n = __ldg(recp);
+  float4 d0_n = __ldg(reinterpret_cast<const float4*>(dp)), d1_n = __ldg(reinterpret_cast<const float4*>(dp + 32));
+  for (int tap = 0; tap < g.K; ++tap) {
+    const float4 rec = rec_n;
+    float4 d0 = d0_n, d1 = d1_n;
+    if (tap + 1 < g.K) {
+      rec_n = __ldg(recp + (long long)(tap + 1) * g.V);
+      const float4* nx = reinterpret_cast<const float4*>(dp + (long long)(tap + 1) * nh * slice_stride);
+      d0_n = __ldg(nx); d1_n = __ldg(nx + 8);
+    }
+    const float m = rec.w;
+    const Sample<float> s = make_sample(g, rec.x, rec.y, rec.z);
     // scatter weights of the reference's col2im: (1-|z-zp|)(1-|y-yp|)(1-|x-xp|), corners at distance
     // exactly 1 excluded (dconv3d_gpu.cu:626-637)
     const float wz[2] = {sub_rn(1.f, s.fz), sub_rn(1.f, s.gz)};
     const float wy[2] = {sub_rn(1.f, s.fy), sub_rn(1.f, s.gy)};
     const float wx[2] = {sub_rn(1.f, s.fx), sub_rn(1.f, s.gx)};
     const bool okz[2] = {true, s.gz < 1.f}, oky[2] = {true, s.gy < 1.f}, okx[2] = {true, s.gx < 1.f};
-    const int off0 = ((s.z0 * g.H + s.y0) * g.W + s.x0) * g.Cin + grp * g.cpg + j * 8;
-    const __nv_bfloat16* xb = x_cl + (long long)b * g.Vin * g.Cin;
-    float* gxb = gx_cl + (long long)b * g.Vin * g.Cin;
-    const float* drow = dcol + ((long long)bl * g.V + v) * NT + (long long)((grp * g.K + tap) * nh) * 64 + j * 8;
+    const unsigned valid = active ? s.valid : 0u;
+    const int off0 = ((s.z0 * g.H + s.y0) * g.W + s.x0) * g.Cin + chbase;
+    float G[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) G[q] = 0.f;
     for (int h = 0; h < nh; ++h) {
-      const float4 d0 = __ldg(reinterpret_cast<const float4*>(drow + h * 64));
-      const float4 d1 = __ldg(reinterpret_cast<const float4*>(drow + h * 64) + 1);
+      if (h > 0) {
+        const float4* cur = reinterpret_cast<const float4*>(dp + ((long long)tap * nh + h) * slice_stride);
+        d0 = __ldg(cur); d1 = __ldg(cur + 8);
+      }
+      uint4 c[8];
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
-        if (!((s.valid >> q) & 1u)) continue;
+        const int off = off0 + h * 64 + (q >> 2) * cs.dz + ((q >> 1) & 1) * cs.dy + (q & 1) * cs.dx;
+        if ((valid >> q) & 1u) {
+          const uint2 lo = ptx::ldg_nc_v2(xb + off), hi = ptx::ldg_nc_v2(xb + off + 32);
+          c[q] = make_uint4(lo.x, lo.y, hi.x, hi.y);
+        } else {
+          c[q] = make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
         const int dz = q >> 2, dy = (q >> 1) & 1, dx = q & 1;
-        const int off = off0 + h * 64 + dz * cs.dz + dy * cs.dy + dx * cs.dx;
-        const uint4 c = ptx::ldg_nc_v4(xb + off);
-        G[q] += d0.x * ptx::bf16_lo(c.x) + d0.y * ptx::bf16_hi(c.x) + d0.z * ptx::bf16_lo(c.y) +
-                d0.w * ptx::bf16_hi(c.y) + d1.x * ptx::bf16_lo(c.z) + d1.y * ptx::bf16_hi(c.z) +
-                d1.z * ptx::bf16_lo(c.w) + d1.w * ptx::bf16_hi(c.w);
-        if (okz[dz] && oky[dy] && okx[dx]) {
+        G[q] += d0.x * ptx::bf16_lo(c[q].x) + d0.y * ptx::bf16_hi(c[q].x) + d0.z * ptx::bf16_lo(c[q].y) +
+                d0.w * ptx::bf16_hi(c[q].y) + d1.x * ptx::bf16_lo(c[q].z) + d1.y * ptx::bf16_hi(c[q].z) +
+                d1.z * ptx::bf16_lo(c[q].w) + d1.w * ptx::bf16_hi(c[q].w);
+        if (((valid >> q) & 1u) && okz[dz] && oky[dy] && okx[dx]) {
           const float sw = mul_rn(mul_rn(wz[dz], wy[dy]), wx[dx]) * m;
-          float* dst = gxb + off;
+          float* dst = gxb + (off0 + h * 64 + dz * cs.dz + dy * cs.dy + dx * cs.dx);
           red_add_v4(dst, sw * d0.x, sw * d0.y, sw * d0.z, sw * d0.w);
-          red_add_v4(dst + 4, sw * d1.x, sw * d1.y, sw * d1.z, sw * d1.w);
+          red_add_v4(dst + 32, sw * d1.x, sw * d1.y, sw * d1.z, sw * d1.w);
         }
       }
     }
-  }
-  // channel reduction of the 8 corner dot-products across the voxel's 8 threads
+    // channel reduction of the 8 corner dot-products across the voxel's 8 threads
 #pragma unroll
-  for (int q = 0; q < 8; ++q) {
-    G[q] += __shfl_xor_sync(0xffffffffu, G[q], 1);
-    G[q] += __shfl_xor_sync(0xffffffffu, G[q], 2);
-    G[q] += __shfl_xor_sync(0xffffffffu, G[q], 4);
-  }
-  if (active && j == 0) {
-    float wts[3];
-    coord_weights(G, s, wts);    // linear in the corner values: applies to the channel-summed corners
-    if (has_mask && grad_mask) {
-      float a[8];
-      sample_weights(s, a);
-      grad_mask[ri] = s.inside ? blend(G, a) : 0.f;
+    for (int q = 0; q < 8; ++q) {
+      G[q] += __shfl_xor_sync(0xffffffffu, G[q], 1);
+      G[q] += __shfl_xor_sync(0xffffffffu, G[q], 2);
+      G[q] += __shfl_xor_sync(0xffffffffu, G[q], 4);
     }
-    if constexpr (!FieldOut) {
-      float* go = grad_coord + (((long long)b * g.G + grp) * 3 * g.K + 3 * tap) * g.V + v;
-      go[0] = m * wts[0];
-      go[g.V] = m * wts[1];
-      go[2 * (long long)g.V] = m * wts[2];
-    } else {
-      const int k = tap % g.kw, jj = (tap / g.kw) % g.kh, i = tap / (g.kw * g.kh);
-      float* gs = grad_coord + (long long)b * field_nch * g.V + v;
-      if (field_ch.x >= 0) atomicAdd(gs + (long long)field_ch.x * g.V, field_axes[i] * (m * wts[0]));
-      if (field_ch.y >= 0) atomicAdd(gs + (long long)field_ch.y * g.V, field_axes[kMaxFieldKernelDim + jj] * (m * wts[1]));
-      if (field_ch.z >= 0) atomicAdd(gs + (long long)field_ch.z * g.V, field_axes[2 * kMaxFieldKernelDim + k] * (m * wts[2]));
+    if (active && j == 0) {
+      float wts[3];
+      coord_weights(G, s, wts);    // linear in the corner values: applies to the channel-summed corners
+      const long long ri = (((long long)b * g.G + grp) * g.K + tap) * g.V + v;
+      if (has_mask && grad_mask) {
+        float a[8];
+        sample_weights(s, a);
+        grad_mask[ri] = s.inside ? blend(G, a) : 0.f;
+      }
+      if constexpr (!FieldOut) {
+        float* go = grad_coord + (((long long)b * g.G + grp) * 3 * g.K + 3 * tap) * g.V + v;
+        go[0] = m * wts[0];
+        go[g.V] = m * wts[1];
+        go[2 * (long long)g.V] = m * wts[2];
+      } else {
+        const int k = tap % g.kw, jj = (tap / g.kw) % g.kh, i = tap / (g.kw * g.kh);
+        float* gs = grad_coord + (long long)b * field_nch * g.V + v;
+        if (field_ch.x >= 0) atomicAdd(gs + (long long)field_ch.x * g.V, field_axes[i] * (m * wts[0]));
+        if (field_ch.y >= 0) atomicAdd(gs + (long long)field_ch.y * g.V, field_axes[kMaxFieldKernelDim + jj] * (m * wts[1]));
+        if (field_ch.z >= 0) atomicAdd(gs + (long long)field_ch.z * g.V, field_axes[2 * kMaxFieldKernelDim + k] * (m * wts[2]));
+      }
     }
   }
 }
@@ -465,10 +494,10 @@ int run_bwd(const Geom& g, const Coords& coords, unsigned long long cap, const f
     dcol_sm100_kernel<<<(unsigned)grid, kDcolThreads, pl.smem_bytes, st>>>(p);
     D2C_LAUNCH_CHECK();
     prof_mark(st, "bwd_sample_grad");
-    dim3 sgrid((unsigned)((g.V + 31) / 32), (unsigned)(nbc * g.G * g.K));
-    sample_grad_kernel<FieldOut><<<sgrid, 256, 0, st>>>(g, cs, b0, pl.nh, pl.NT, recs, dcol, x_cl, mask != nullptr,
-                                                        grad_coord, grad_mask, gx_cl, field_nch, field_ch,
-                                                        axes_dev);
+    dim3 sgrid((unsigned)((g.V + 31) / 32), (unsigned)(nbc * g.G));
+    sample_grad_taps_kernel<FieldOut><<<sgrid, 256, 0, st>>>(g, cs, b0, pl.nh, recs, dcol, x_cl, mask != nullptr,
+                                                             grad_coord, grad_mask, gx_cl, field_nch, field_ch,
+                                                             axes_dev);
     D2C_LAUNCH_CHECK();
   }
   prof_mark(st, "bwd_unstage_grad_input");
