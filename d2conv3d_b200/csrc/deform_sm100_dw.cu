@@ -25,8 +25,10 @@ constexpr int kAStages = 2;
 constexpr int kAStageBytes = 2 * kTileBytes;         // two slices
 constexpr int kBStages = 2;
 constexpr int kChunkBytes = 256 * 128;               // one 256-row (co) x 64-voxel image
-constexpr int kThreads = 448;
-constexpr int kEpiWarps = 4, kMmaWarp = 4, kLoadWarp = 5, kGatherWarp0 = 6, kGatherWarps = 8;
+constexpr int kThreads = (6 + 16) * 32;   // 4 epilogue + MMA + loader + 16 gather warps
+constexpr int kEpiWarps = 4, kMmaWarp = 4, kLoadWarp = 5, kGatherWarp0 = 6, kGatherWarps = 16;
+constexpr int kRowStride = kGatherWarps * 4;          // 8 threads per row -> rows handled per pass
+constexpr int kRowsPerThread = kBM / kRowStride;
 constexpr int kSmemLimit = 227 * 1024;
 
 __device__ int g_sm100_dw_status = 0;
@@ -190,10 +192,10 @@ dw_sm100_kernel(const DwParams p) {
       // ---- gather producers: the forward's producer, two slices per stage; records one tile ahead
       const int tt = threadIdx.x - kGatherWarp0 * 32;
       const int j = tt & 7, r0 = tt >> 3;
-      uint32_t row_dst[4];
+      uint32_t row_dst[kRowsPerThread];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int r = r0 + 32 * i;
+      for (int i = 0; i < kRowsPerThread; ++i) {
+        const int r = r0 + kRowStride * i;
         row_dst[i] = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((j ^ (r & 7)) << 4));
       }
       int grp_[2], tap_[2], ch0_[2];
@@ -205,16 +207,16 @@ dw_sm100_kernel(const DwParams p) {
         ch0_[sl] = grp_[sl] * g.cpg + h * kBK + j * 8;
       }
       // half-units q = 2*t + sl (tile t of the range, slice sl of the pair); records one half-unit ahead
-      auto load_q = [&](int q, float4 (&out)[4]) {
+      auto load_q = [&](int q, float4 (&out)[kRowsPerThread]) {
         const int tile = tile_beg + (q >> 1), sl = q & 1;
         const int b = tile / p.tiles_per_clip, v0 = (tile % p.tiles_per_clip) * kBM;
-        load_row_records(p.recs, g, b, sl ? grp_[1] : grp_[0], sl ? tap_[1] : tap_[0], v0, r0, out);
+        load_row_records<kRowsPerThread, kRowStride>(p.recs, g, b, sl ? grp_[1] : grp_[0], sl ? tap_[1] : tap_[0], v0, r0, out);
       };
-      float4 rec[4];
+      float4 rec[kRowsPerThread];
       load_q(0, rec);
       const int nq = 2 * n_my_tiles;
       for (int q = 0; q < nq; ++q) {
-        float4 rec_next[4];
+        float4 rec_next[kRowsPerThread];
         if (q + 1 < nq) load_q(q + 1, rec_next);
         const int t = q >> 1, sl = q & 1, sa = t % kAStages;
         const int tile = tile_beg + t;
@@ -224,14 +226,14 @@ dw_sm100_kernel(const DwParams p) {
         const uint32_t stage = a_base + sa * kAStageBytes + sl * kTileBytes;
         const int ch0 = sl ? ch0_[1] : ch0_[0];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) produce_item_rec(g, xb, p.cs, rec[i], ch0, stage + row_dst[i]);
+        for (int i = 0; i < kRowsPerThread; ++i) produce_item_rec(g, xb, p.cs, rec[i], ch0, stage + row_dst[i]);
         if (sl == 1) {
           ptx::fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(a_full(sa));
         }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) rec[i] = rec_next[i];
+        for (int i = 0; i < kRowsPerThread; ++i) rec[i] = rec_next[i];
       }
     }
   }

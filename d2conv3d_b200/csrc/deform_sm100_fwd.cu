@@ -38,8 +38,10 @@ constexpr int kBK = 64;             // channels per K slice (128 bytes of bf16: 
 constexpr int kAStages = 4;
 constexpr int kAStageBytes = kBM * kBK * 2;   // 16 KB
 constexpr int kMaxN = 512;
-constexpr int kThreads = 448;
-constexpr int kEpiWarps = 4, kMmaWarp = 4, kLoadWarp = 5, kGatherWarp0 = 6, kGatherWarps = 8;
+constexpr int kThreads = (6 + 16) * 32;   // 4 epilogue + MMA + loader + 16 gather warps
+constexpr int kEpiWarps = 4, kMmaWarp = 4, kLoadWarp = 5, kGatherWarp0 = 6, kGatherWarps = 16;
+constexpr int kRowStride = kGatherWarps * 4;          // 8 threads per row -> rows handled per pass
+constexpr int kRowsPerThread = kBM / kRowStride;
 constexpr int kSmemLimit = 227 * 1024;
 constexpr int kMinUnitsPerCta = 16;
 
@@ -203,11 +205,11 @@ fwd_sm100_kernel(const FwdParams p) {
     // ===================== gather producers =====================
     const int t = threadIdx.x - kGatherWarp0 * 32;
     const int j = t & 7;             // 16-byte chunk (8 channels) of the 128-byte row
-    const int r0 = t >> 3;           // rows r0, r0+32, r0+64, r0+96
-    uint32_t row_dst[4];
+    const int r0 = t >> 3;           // rows r0, r0+kRowStride, ...
+    uint32_t row_dst[kRowsPerThread];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int r = r0 + 32 * i;
+    for (int i = 0; i < kRowsPerThread; ++i) {
+      const int r = r0 + kRowStride * i;
       row_dst[i] = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((j ^ (r & 7)) << 4));
     }
     auto unit_coords = [&](long long u, int& b, int& v0, int& grp, int& tap, int& h) {
@@ -217,19 +219,19 @@ fwd_sm100_kernel(const FwdParams p) {
       const int gt = s / p.nh;
       tap = gt % g.K; grp = gt / g.K;
     };
-    float4 rec[4];
+    float4 rec[kRowsPerThread];
     int b, v0, grp, tap, h;
     if (u_beg < u_end) {
       unit_coords(u_beg, b, v0, grp, tap, h);
-      load_row_records(p.recs, g, b, grp, tap, v0, r0, rec);
+      load_row_records<kRowsPerThread, kRowStride>(p.recs, g, b, grp, tap, v0, r0, rec);
     }
     uint32_t k = 0;
     for (long long u = u_beg; u < u_end; ++u, ++k) {
-      float4 rec_next[4];
+      float4 rec_next[kRowsPerThread];
       int nb = b, nv0 = v0, ngrp = grp, ntap = tap, nh_ = h;
       if (u + 1 < u_end) {
         unit_coords(u + 1, nb, nv0, ngrp, ntap, nh_);
-        load_row_records(p.recs, g, nb, ngrp, ntap, nv0, r0, rec_next);   // in flight while this unit is produced
+        load_row_records<kRowsPerThread, kRowStride>(p.recs, g, nb, ngrp, ntap, nv0, r0, rec_next);   // in flight while this unit is produced
       }
       const int sa = k % kAStages;
       if (!ptx::mbar_wait(a_empty(sa), ((k / kAStages) & 1) ^ 1, abort_flag)) break;
@@ -237,12 +239,12 @@ fwd_sm100_kernel(const FwdParams p) {
       const __nv_bfloat16* xb = p.x_cl + (long long)b * g.Vin * g.Cin;
       const int ch0 = grp * g.cpg + h * kBK + j * 8;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) produce_item_rec(g, xb, p.cs, rec[i], ch0, stage + row_dst[i]);
+      for (int i = 0; i < kRowsPerThread; ++i) produce_item_rec(g, xb, p.cs, rec[i], ch0, stage + row_dst[i]);
       ptx::fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(a_full(sa));
 #pragma unroll
-      for (int i = 0; i < 4; ++i) rec[i] = rec_next[i];
+      for (int i = 0; i < kRowsPerThread; ++i) rec[i] = rec_next[i];
       b = nb; v0 = nv0; grp = ngrp; tap = ntap; h = nh_;
     }
   }

@@ -91,14 +91,15 @@ __device__ __forceinline__ void produce_item_rec(const Geom& g, const __nv_bfloa
   ptx::sts_v4(dst, out);
 }
 
-// Records of the 4 rows (r0, r0+32, r0+64, r0+96) a gather thread owns in the tile starting at voxel v0.
+// Records of the kRows rows (r0, r0+kStride, ...) a gather thread owns in the tile starting at voxel v0.
 // Rows past the end of the clip get {0,0,0,0}: a valid position with modulation 0, i.e. a zero row.
+template <int kRows, int kStride>
 __device__ __forceinline__ void load_row_records(const float4* __restrict__ recs, const Geom& g, int b, int grp,
-                                                 int tap, int v0, int r0, float4 (&out)[4]) {
+                                                 int tap, int v0, int r0, float4 (&out)[kRows]) {
   const float4* p = recs + (((long long)b * g.G + grp) * g.K + tap) * g.V;
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int v = v0 + r0 + 32 * i;
+  for (int i = 0; i < kRows; ++i) {
+    const int v = v0 + r0 + kStride * i;
     out[i] = (v < g.V) ? __ldg(p + v) : make_float4(0.f, 0.f, 0.f, 0.f);
   }
 }
