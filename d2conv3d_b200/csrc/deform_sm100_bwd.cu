@@ -275,7 +275,7 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
 template <bool FieldOut>
 __global__ void __launch_bounds__(256, 3)
 sample_grad_taps_kernel(Geom g, ClStrides cs, int b0, int nh, const float4* __restrict__ recs,
-                        const float* __restrict__ dcol, const __nv_bfloat16* __restrict__ x_cl, bool has_mask,
+                        const float* __restrict__ dcol, const __half* __restrict__ x_cl, bool has_mask,
                         float* __restrict__ grad_coord, float* __restrict__ grad_mask, float* __restrict__ gx_cl,
                         int field_nch, int3 field_ch, const float* __restrict__ field_axes) {
   const int j = threadIdx.x & 7;
@@ -290,7 +290,7 @@ sample_grad_taps_kernel(Geom g, ClStrides cs, int b0, int nh, const float4* __re
   // covers whole 32-byte sectors (two lanes each), which halves the sector operations of the reductions
   const float* dp = dcol + (((long long)bl * S + (long long)grp * g.K * nh) * g.V + vc) * 64 + j * 4;
   const long long slice_stride = (long long)g.V * 64;
-  const __nv_bfloat16* xb = x_cl + (long long)b * g.Vin * g.Cin;
+  const __half* xb = x_cl + (long long)b * g.Vin * g.Cin;
   float* gxb = gx_cl + (long long)b * g.Vin * g.Cin;
   const int chbase = grp * g.cpg + j * 4;
 
@@ -336,9 +336,10 @@ sample_grad_taps_kernel(Geom g, ClStrides cs, int b0, int nh, const float4* __re
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
         const int dz = q >> 2, dy = (q >> 1) & 1, dx = q & 1;
-        G[q] += d0.x * ptx::bf16_lo(c[q].x) + d0.y * ptx::bf16_hi(c[q].x) + d0.z * ptx::bf16_lo(c[q].y) +
-                d0.w * ptx::bf16_hi(c[q].y) + d1.x * ptx::bf16_lo(c[q].z) + d1.y * ptx::bf16_hi(c[q].z) +
-                d1.z * ptx::bf16_lo(c[q].w) + d1.w * ptx::bf16_hi(c[q].w);
+        const float2 x0 = __half22float2(bits_h2(c[q].x)), x1 = __half22float2(bits_h2(c[q].y));
+        const float2 x2 = __half22float2(bits_h2(c[q].z)), x3 = __half22float2(bits_h2(c[q].w));
+        G[q] += d0.x * x0.x + d0.y * x0.y + d0.z * x1.x + d0.w * x1.y + d1.x * x2.x + d1.y * x2.y + d1.z * x3.x +
+                d1.w * x3.y;
         if (((valid >> q) & 1u) && okz[dz] && oky[dy] && okx[dx]) {
           const float sw = mul_rn(mul_rn(wz[dz], wy[dy]), wx[dx]) * m;
           float* dst = gxb + (off0 + h * 64 + dz * cs.dz + dy * cs.dy + dx * cs.dx);
@@ -399,7 +400,7 @@ unstage_grad_input_kernel(int C, long long Vin, const float* __restrict__ gx_cl,
 
 struct BwdPlan {
   int nh, S, NT, KB, NB, tiles_per_clip, tmem_cols, smem_bytes, clips_per_chunk;
-  size_t x_cl_bytes, rec_bytes, gy_img_bytes, wt_img_bytes, dcol_bytes, gx_cl_bytes, axes_bytes;
+  size_t x_cl_bytes, rec_bytes, gat_bytes, gy_img_bytes, wt_img_bytes, dcol_bytes, gx_cl_bytes, axes_bytes;
 };
 
 bool make_bwd_plan(const Geom& g, unsigned long long cap, BwdPlan* pl) {
@@ -417,7 +418,8 @@ bool make_bwd_plan(const Geom& g, unsigned long long cap, BwdPlan* pl) {
   if (pl->smem_bytes > kSmemLimit) return false;
   pl->clips_per_chunk = bwd_slice_clips(g, cap);
   pl->x_cl_bytes = align_up((size_t)g.B * g.Vin * g.Cin * 2, 256);
-  pl->rec_bytes = coord_records_bytes(g);
+  pl->rec_bytes = pos_records_bytes(g);
+  pl->gat_bytes = gather_records_bytes(g);
   pl->gy_img_bytes = align_up((size_t)pl->clips_per_chunk * pl->tiles_per_clip * pl->KB * kABlockBytes, 256);
   pl->wt_img_bytes = align_up((size_t)pl->NB * pl->KB * kBStageBytes, 256);
   pl->dcol_bytes = align_up((size_t)pl->clips_per_chunk * g.V * pl->NT * 4, 256);
@@ -433,8 +435,9 @@ int run_bwd(const Geom& g, const Coords& coords, unsigned long long cap, const f
   BwdPlan pl;
   if (!make_bwd_plan(g, cap, &pl)) return D2C_ERR_MODE;
   uint8_t* wsp = reinterpret_cast<uint8_t*>(ws);
-  __nv_bfloat16* x_cl = reinterpret_cast<__nv_bfloat16*>(wsp); wsp += pl.x_cl_bytes;
+  __half* x_cl = reinterpret_cast<__half*>(wsp); wsp += pl.x_cl_bytes;
   float4* recs = reinterpret_cast<float4*>(wsp); wsp += pl.rec_bytes;
+  uint4* gat = reinterpret_cast<uint4*>(wsp); wsp += pl.gat_bytes;
   uint8_t* gy_img = wsp; wsp += pl.gy_img_bytes;
   uint8_t* wt_img = wsp; wsp += pl.wt_img_bytes;
   float* dcol = reinterpret_cast<float*>(wsp); wsp += pl.dcol_bytes;
@@ -467,11 +470,11 @@ int run_bwd(const Geom& g, const Coords& coords, unsigned long long cap, const f
   if (FieldOut) D2C_CUDA_TRY(cudaMemsetAsync(grad_coord, 0, sizeof(float) * grad_coord_elems, st));
   {
     dim3 grid((unsigned)((g.Vin + 31) / 32), (unsigned)((g.Cin + 63) / 64), (unsigned)g.B);
-    stage_input_cl_bf16_kernel<<<grid, 256, 0, st>>>(g.Cin, g.Vin, x, x_cl);
+    stage_input_cl_f16_kernel<<<grid, 256, 0, st>>>(g.Cin, g.Vin, x, x_cl);
     D2C_LAUNCH_CHECK();
     stage_wt_img_kernel<<<sm_count * 8, 256, 0, st>>>(g.Cout, g.Cin, g.K, g.cpg, pl.nh, pl.S, w, wt_img);
     D2C_LAUNCH_CHECK();
-    if ((rc = launch_coord_records(g, coords, mask, recs, st))) return rc;
+    if ((rc = launch_sample_records(g, coords, mask, recs, gat, st))) return rc;
   }
   D2C_CUDA_TRY(cudaFuncSetAttribute(dcol_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes));
 
@@ -507,7 +510,7 @@ int run_bwd(const Geom& g, const Coords& coords, unsigned long long cap, const f
     D2C_LAUNCH_CHECK();
   }
   // weight gradient: tensor-core implicit GEMM over the re-sampled tile
-  if ((rc = sm100_dw(g, gy, x_cl, recs, grad_w, dw_ws, st))) return rc;
+  if ((rc = sm100_dw(g, gy, x_cl, gat, grad_w, dw_ws, st))) return rc;
   if (grad_bias) {
     prof_mark(st, "bwd_grad_bias");
     grad_bias_kernel<float><<<g.Cout, 256, 0, st>>>(g.B, g.Cout, g.V, gy, grad_bias);
@@ -529,7 +532,7 @@ size_t sm100_bwd_workspace(const Geom& g, int dtype, int math_mode, unsigned lon
   if (!sm100_bwd_supported(g, dtype, math_mode, cap)) return 0;
   BwdPlan pl;
   make_bwd_plan(g, cap, &pl);
-  return pl.x_cl_bytes + pl.rec_bytes + pl.gy_img_bytes + pl.wt_img_bytes + pl.dcol_bytes + pl.gx_cl_bytes +
+  return pl.x_cl_bytes + pl.rec_bytes + pl.gat_bytes + pl.gy_img_bytes + pl.wt_img_bytes + pl.dcol_bytes + pl.gx_cl_bytes +
          pl.axes_bytes + sm100_dw_workspace(g);
 }
 

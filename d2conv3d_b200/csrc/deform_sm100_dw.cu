@@ -35,8 +35,8 @@ __device__ int g_sm100_dw_status = 0;
 
 struct DwParams {
   Geom g;
-  const __nv_bfloat16* x_cl;
-  const float4* recs;
+  const __half* x_cl;        // channels-last fp16 staging of x
+  const uint4* recs;         // gather records (sm100_gather.cuh)
   const uint8_t* gyk_img;    // [n_tiles][2 voxel blocks][NCH][32 KB]
   float* dws;                // [S*64][Cout] fp32, zero-initialised
   ClStrides cs;
@@ -207,26 +207,26 @@ dw_sm100_kernel(const DwParams p) {
         ch0_[sl] = grp_[sl] * g.cpg + h * kBK + j * 8;
       }
       // half-units q = 2*t + sl (tile t of the range, slice sl of the pair); records one half-unit ahead
-      auto load_q = [&](int q, float4 (&out)[kRowsPerThread]) {
+      auto load_q = [&](int q, GatherRec (&out)[kRowsPerThread]) {
         const int tile = tile_beg + (q >> 1), sl = q & 1;
         const int b = tile / p.tiles_per_clip, v0 = (tile % p.tiles_per_clip) * kBM;
         load_row_records<kRowsPerThread, kRowStride>(p.recs, g, b, sl ? grp_[1] : grp_[0], sl ? tap_[1] : tap_[0], v0, r0, out);
       };
-      float4 rec[kRowsPerThread];
+      GatherRec rec[kRowsPerThread];
       load_q(0, rec);
       const int nq = 2 * n_my_tiles;
       for (int q = 0; q < nq; ++q) {
-        float4 rec_next[kRowsPerThread];
+        GatherRec rec_next[kRowsPerThread];
         if (q + 1 < nq) load_q(q + 1, rec_next);
         const int t = q >> 1, sl = q & 1, sa = t % kAStages;
         const int tile = tile_beg + t;
         const int b = tile / p.tiles_per_clip;
         if (sl == 0 && !ptx::mbar_wait(a_empty(sa), ((t / kAStages) & 1) ^ 1, abort_flag)) break;
-        const __nv_bfloat16* xb = p.x_cl + (long long)b * g.Vin * g.Cin;
+        const __half* xb = p.x_cl + (long long)b * g.Vin * g.Cin;
         const uint32_t stage = a_base + sa * kAStageBytes + sl * kTileBytes;
         const int ch0 = sl ? ch0_[1] : ch0_[0];
 #pragma unroll
-        for (int i = 0; i < kRowsPerThread; ++i) produce_item_rec(g, xb, p.cs, rec[i], ch0, stage + row_dst[i]);
+        for (int i = 0; i < kRowsPerThread; ++i) produce_item(xb, p.cs, rec[i], ch0, stage + row_dst[i]);
         if (sl == 1) {
           ptx::fence_proxy_async_smem();
           __syncwarp();
@@ -329,7 +329,7 @@ int sm100_dw(const Geom& g, const float* gy, const void* x_cl, const void* recs,
   D2C_LAUNCH_CHECK();
 
   DwParams p;
-  p.g = g; p.x_cl = reinterpret_cast<const __nv_bfloat16*>(x_cl); p.recs = reinterpret_cast<const float4*>(recs);
+  p.g = g; p.x_cl = reinterpret_cast<const __half*>(x_cl); p.recs = reinterpret_cast<const uint4*>(recs);
   p.gyk_img = gyk; p.dws = dws;
   p.cs.dz = g.H * g.W * g.Cin; p.cs.dy = g.W * g.Cin; p.cs.dx = g.Cin;
   p.N = g.Cout; p.nh = dp.nh; p.S = dp.S; p.tiles_per_clip = dp.tiles_per_clip; p.n_tiles = dp.n_tiles;

@@ -8,7 +8,7 @@
 // GEMM view: M = output voxels (tiles of 128 consecutive voxels of one clip), N = Cout
 // (whole, <= 512, in tensor memory), K = Cin*27 walked as slices of 64 input channels of
 // one (offset group, tap).  All channels of a slice share their 8 trilinear corners, so
-// with the input staged channels-last in bf16 each corner of a slice is ONE contiguous
+// with the input staged channels-last in fp16 each corner of a slice is ONE contiguous
 // 128-byte line.
 //
 // Work decomposition: the (tile, slice) units are cut into one contiguous range per CTA
@@ -16,13 +16,13 @@
 // covers a whole tile stores it; partial tiles are combined with fp32 reductions into the
 // zero-initialised output.
 //
-// Per CTA, 14 warps:
+// Per CTA, 22 warps:
 //   warps 0-3   epilogue: tcgen05.ld the 128 x N accumulator, add bias, store / reduce NCDHW
 //   warp  4     one thread issues tcgen05.mma and the commits that free the stages
 //   warp  5     one thread streams pre-swizzled weight slices with cp.async.bulk
-//   warps 6-13  gather producers: sampling records (prefetched one unit ahead), predicated
-//               corner loads (16 B per thread), fp32 blend, modulation, bf16 pack, swizzled
-//               st.shared of the A tile
+//   warps 6-21  gather producers: gather records (prefetched one unit ahead), predicated
+//               corner loads (16 B per thread), packed-fp16 blend with pre-modulated weights,
+//               bf16 pack, swizzled st.shared of the A tile
 // Stage hand-off is by mbarriers; every wait is bounded (sm100_ptx.cuh).
 #include "deform_sm100.h"
 #include "sm100_gather.cuh"
@@ -49,9 +49,9 @@ __device__ int g_sm100_status = 0;   // sticky: set when a bounded wait gave up
 
 struct FwdParams {
   Geom g;
-  const __nv_bfloat16* x_cl;   // [B][Vin][Cin] bf16 (channels-last staging of x)
+  const __half* x_cl;          // [B][Vin][Cin] fp16 (channels-last staging of x)
   const uint8_t* w_sw;         // [S][N rows x 128 B], rows swizzled exactly as the smem B tile
-  const float4* recs;          // [B][G][K][V] sampling records {z, y, x, mask}
+  const uint4* recs;           // [B][G][K][V] gather records (3 x uint4 each, sm100_gather.cuh)
   const float* bias;           // [Cout] or nullptr
   float* y;                    // [B, Cout, V]
   ClStrides cs;
@@ -219,7 +219,7 @@ fwd_sm100_kernel(const FwdParams p) {
       const int gt = s / p.nh;
       tap = gt % g.K; grp = gt / g.K;
     };
-    float4 rec[kRowsPerThread];
+    GatherRec rec[kRowsPerThread];
     int b, v0, grp, tap, h;
     if (u_beg < u_end) {
       unit_coords(u_beg, b, v0, grp, tap, h);
@@ -227,7 +227,7 @@ fwd_sm100_kernel(const FwdParams p) {
     }
     uint32_t k = 0;
     for (long long u = u_beg; u < u_end; ++u, ++k) {
-      float4 rec_next[kRowsPerThread];
+      GatherRec rec_next[kRowsPerThread];
       int nb = b, nv0 = v0, ngrp = grp, ntap = tap, nh_ = h;
       if (u + 1 < u_end) {
         unit_coords(u + 1, nb, nv0, ngrp, ntap, nh_);
@@ -236,10 +236,10 @@ fwd_sm100_kernel(const FwdParams p) {
       const int sa = k % kAStages;
       if (!ptx::mbar_wait(a_empty(sa), ((k / kAStages) & 1) ^ 1, abort_flag)) break;
       const uint32_t stage = a_base + sa * kAStageBytes;
-      const __nv_bfloat16* xb = p.x_cl + (long long)b * g.Vin * g.Cin;
+      const __half* xb = p.x_cl + (long long)b * g.Vin * g.Cin;
       const int ch0 = grp * g.cpg + h * kBK + j * 8;
 #pragma unroll
-      for (int i = 0; i < kRowsPerThread; ++i) produce_item_rec(g, xb, p.cs, rec[i], ch0, stage + row_dst[i]);
+      for (int i = 0; i < kRowsPerThread; ++i) produce_item(xb, p.cs, rec[i], ch0, stage + row_dst[i]);
       ptx::fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(a_full(sa));
@@ -315,7 +315,7 @@ bool make_plan(const Geom& g, Plan* pl) {
   pl->smem_bytes = kAStages * kAStageBytes + pl->b_stages * pl->b_stage_bytes + 256 + 1024;
   pl->x_cl_bytes = align_up((size_t)g.B * g.Vin * g.Cin * 2, 256);
   pl->w_sw_bytes = align_up((size_t)pl->S * pl->b_stage_bytes, 256);
-  pl->rec_bytes = coord_records_bytes(g);
+  pl->rec_bytes = gather_records_bytes(g);
   return true;
 }
 
@@ -336,9 +336,9 @@ int run_fwd(const Geom& g, const Coords& coords, const float* x, const float* ma
   Plan pl;
   if (!make_plan(g, &pl)) return D2C_ERR_MODE;
   uint8_t* wsp = reinterpret_cast<uint8_t*>(ws);
-  __nv_bfloat16* x_cl = reinterpret_cast<__nv_bfloat16*>(wsp); wsp += pl.x_cl_bytes;
+  __half* x_cl = reinterpret_cast<__half*>(wsp); wsp += pl.x_cl_bytes;
   uint8_t* w_sw = wsp; wsp += pl.w_sw_bytes;
-  float4* recs = reinterpret_cast<float4*>(wsp);
+  uint4* recs = reinterpret_cast<uint4*>(wsp);
   int sm_count = 0, rc;
   if ((rc = sm_count_cached(&sm_count))) return rc;
 
@@ -351,12 +351,12 @@ int run_fwd(const Geom& g, const Coords& coords, const float* x, const float* ma
   prof_mark(st, "fwd_stage_operands");
   {
     dim3 sgrid((unsigned)((g.Vin + 31) / 32), (unsigned)((g.Cin + 63) / 64), (unsigned)g.B);
-    stage_input_cl_bf16_kernel<<<sgrid, 256, 0, st>>>(g.Cin, g.Vin, x, x_cl);
+    stage_input_cl_f16_kernel<<<sgrid, 256, 0, st>>>(g.Cin, g.Vin, x, x_cl);
     D2C_LAUNCH_CHECK();
     dim3 wgrid((unsigned)g.Cout, (unsigned)(g.Cin / 64));
     stage_weight_sw128_kernel<<<wgrid, 64, 64 * g.K * sizeof(float), st>>>(g.Cout, g.Cin, g.K, g.cpg, pl.nh, w, w_sw);
     D2C_LAUNCH_CHECK();
-    if ((rc = launch_coord_records(g, coords, mask, recs, st))) return rc;
+    if ((rc = launch_sample_records(g, coords, mask, nullptr, recs, st))) return rc;
     if (!whole_tiles_only) D2C_CUDA_TRY(cudaMemsetAsync(y, 0, sizeof(float) * (size_t)g.B * g.Cout * g.V, st));
   }
 

@@ -1,15 +1,22 @@
-// Sampling-coordinate records and the gather producer shared by the tensor-core forward, the
-// weight-gradient and the sampling-gradient kernels.
+// Sampling records and the gather producer shared by the tensor-core forward, the weight-gradient and
+// the sampling-gradient kernels.
 //
-// A record is the float4 {z, y, x, mask} of one (clip, offset group, tap, output voxel): the sampling
-// position exactly as the reference forms it (integer base converted once + offset, one fp add;
-// csrc/ops/dconv3d_gpu.cu:192-194 -- or the dilation-field synthesis of utils/grid.py:97) and the
-// modulation value (1 when there is no mask).  They are computed ONCE per call by
-// coord_records_kernel; consumers re-derive floor corners / validity / weights from (z, y, x) with the
-// same make_sample() as every other kernel, so integer corners stay bit-identical across tiers while the
-// integer div/mod and the strided offset reads leave the inner loops.
-// Layout: [B][G][K][V] float4, i.e. the 128 records of a voxel tile of one (group, tap) are 2 KB contiguous.
+// Everything that depends only on (clip, offset group, tap, output voxel) -- the sampling position exactly
+// as the reference forms it (integer base converted once + offset, one fp add; csrc/ops/dconv3d_gpu.cu:192-194,
+// or the dilation-field synthesis of utils/grid.py:97), its floor corners, which corners are readable, the
+// eight trilinear weights and the modulation value -- is computed ONCE per call by sample_records_kernel with
+// the same make_sample() as every other kernel (so integer corners stay bit-identical across tiers), and the
+// inner loops of the consumers contain no integer division, no strided offset read and no weight arithmetic.
+//
+// Two record streams, both [B][G][K][V]:
+//   pos  float4 {z, y, x, mask}                                    -> sampling-gradient kernel
+//   gat  3 x uint4 (48 B): {voff, valid, -, -}, w0..w3, w4..w7      -> gather producers (forward, dW)
+//        voff  = element offset of corner 000 inside the clip's channels-last staging (no channel term)
+//        valid = bit j set when corner j (order 000..111) contributes to the forward sample
+//        wj    = half2 {a_j*mask, a_j*mask}: trilinear weight x modulation, rounded to fp16, duplicated
 #pragma once
+
+#include <cuda_fp16.h>
 
 #include "d2c_common.cuh"
 #include "sm100_ptx.cuh"
@@ -17,9 +24,18 @@
 namespace d2c {
 namespace {
 
+struct GatherRec {
+  uint4 head;   // x: voff, y: valid bits, z/w: unused
+  uint4 w03, w47;
+};
+
+__device__ __forceinline__ uint32_t h2_bits(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
+__device__ __forceinline__ __half2 bits_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
+
 template <typename Coords>
 static __global__ void __launch_bounds__(256)
-coord_records_kernel(Geom g, Coords coords, const float* __restrict__ mask, float4* __restrict__ recs) {
+sample_records_kernel(Geom g, Coords coords, const float* __restrict__ mask, float4* __restrict__ pos,
+                      uint4* __restrict__ gat) {
   const int v = blockIdx.x * 256 + threadIdx.x;
   if (v >= g.V) return;
   const int tap = blockIdx.y % g.K, grp = blockIdx.y / g.K, b = blockIdx.z;
@@ -29,21 +45,38 @@ coord_records_kernel(Geom g, Coords coords, const float* __restrict__ mask, floa
   coords.get(g, b, grp, tap, v, bz, by, bx, z, y, x);
   const long long i = (((long long)b * g.G + grp) * g.K + tap) * g.V + v;
   const float m = mask ? __ldg(mask + i) : 1.f;
-  recs[i] = make_float4(z, y, x, m);
+  if (pos) pos[i] = make_float4(z, y, x, m);
+  if (gat) {
+    const Sample<float> s = make_sample(g, z, y, x);
+    float a[8];
+    sample_weights(s, a);
+    uint32_t w[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) w[j] = h2_bits(__float2half2_rn(a[j] * m));
+    const unsigned valid = s.inside ? s.valid : 0u;
+    const int voff = ((s.z0 * g.H + s.y0) * g.W + s.x0) * g.Cin;
+    uint4* o = gat + 3 * i;
+    o[0] = make_uint4((uint32_t)voff, valid, 0u, 0u);
+    o[1] = make_uint4(w[0], w[1], w[2], w[3]);
+    o[2] = make_uint4(w[4], w[5], w[6], w[7]);
+  }
 }
 
 template <typename Coords>
-static int launch_coord_records(const Geom& g, const Coords& coords, const float* mask, float4* recs,
-                                cudaStream_t st) {
+static int launch_sample_records(const Geom& g, const Coords& coords, const float* mask, float4* pos, uint4* gat,
+                                 cudaStream_t st) {
   dim3 grid((unsigned)((g.V + 255) / 256), (unsigned)(g.G * g.K), (unsigned)g.B);
   if (grid.y > 65535 || grid.z > 65535) return D2C_ERR_TOO_LARGE;
-  coord_records_kernel<Coords><<<grid, 256, 0, st>>>(g, coords, mask, recs);
+  sample_records_kernel<Coords><<<grid, 256, 0, st>>>(g, coords, mask, pos, gat);
   D2C_LAUNCH_CHECK();
   return D2C_OK;
 }
 
-inline size_t coord_records_bytes(const Geom& g) {
+inline size_t pos_records_bytes(const Geom& g) {
   return align_up((size_t)g.B * g.G * g.K * g.V * sizeof(float4), 256);
+}
+inline size_t gather_records_bytes(const Geom& g) {
+  return align_up((size_t)g.B * g.G * g.K * g.V * 3 * sizeof(uint4), 256);
 }
 
 // Element strides of the channels-last staging of x within one clip.
@@ -51,56 +84,57 @@ struct ClStrides {
   int dz, dy, dx;   // H*W*Cin, W*Cin, Cin
 };
 
-// One A-tile item: the 8 channels [ch0, ch0+8) of the modulated trilinear sample described by `rec`,
-// packed to bf16 and stored (16 bytes) at shared-memory address `dst`.
-//   xb: channels-last bf16 staging of the clip ([Vin][Cin]).
-// Corners outside the volume (or a position failing the forward's early-out) are not loaded.
-__device__ __forceinline__ void produce_item_rec(const Geom& g, const __nv_bfloat16* __restrict__ xb, ClStrides cs,
-                                                 float4 rec, int ch0, uint32_t dst) {
-  const Sample<float> s = make_sample(g, rec.x, rec.y, rec.z);
-  float a[8];
-  sample_weights(s, a);
-  const unsigned valid = s.inside ? s.valid : 0u;
-  const int off0 = ((s.z0 * g.H + s.y0) * g.W + s.x0) * g.Cin + ch0;
+// One A-tile item: the 8 channels [ch0, ch0+8) of the modulated trilinear sample described by `r`,
+// blended in packed fp16 (the weights already carry the modulation), converted to bf16 and stored
+// (16 bytes) at shared-memory address `dst`.   xb: channels-last fp16 staging of the clip ([Vin][Cin]).
+// Corners that do not contribute are not loaded.
+__device__ __forceinline__ void produce_item(const __half* __restrict__ xb, ClStrides cs, const GatherRec& r,
+                                             int ch0, uint32_t dst) {
+  const unsigned valid = r.head.y;
+  const int off0 = (int)r.head.x + ch0;
   uint4 c[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     const int off = off0 + (j >> 2) * cs.dz + ((j >> 1) & 1) * cs.dy + (j & 1) * cs.dx;
     c[j] = ((valid >> j) & 1u) ? ptx::ldg_nc_v4(xb + off) : make_uint4(0u, 0u, 0u, 0u);
   }
-  float acc[8];
+  const uint32_t w[8] = {r.w03.x, r.w03.y, r.w03.z, r.w03.w, r.w47.x, r.w47.y, r.w47.z, r.w47.w};
+  __half2 acc[4];
 #pragma unroll
-  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+  for (int e = 0; e < 4; ++e) acc[e] = __float2half2_rn(0.f);
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {   // corner order 000..111, fma chain as the reference's interpolation
-    acc[0] = fmaf(ptx::bf16_lo(c[j].x), a[j], acc[0]);
-    acc[1] = fmaf(ptx::bf16_hi(c[j].x), a[j], acc[1]);
-    acc[2] = fmaf(ptx::bf16_lo(c[j].y), a[j], acc[2]);
-    acc[3] = fmaf(ptx::bf16_hi(c[j].y), a[j], acc[3]);
-    acc[4] = fmaf(ptx::bf16_lo(c[j].z), a[j], acc[4]);
-    acc[5] = fmaf(ptx::bf16_hi(c[j].z), a[j], acc[5]);
-    acc[6] = fmaf(ptx::bf16_lo(c[j].w), a[j], acc[6]);
-    acc[7] = fmaf(ptx::bf16_hi(c[j].w), a[j], acc[7]);
+  for (int j = 0; j < 8; ++j) {   // corner order 000..111, as the reference's interpolation chain
+    const __half2 wj = bits_h2(w[j]);
+    acc[0] = __hfma2(bits_h2(c[j].x), wj, acc[0]);
+    acc[1] = __hfma2(bits_h2(c[j].y), wj, acc[1]);
+    acc[2] = __hfma2(bits_h2(c[j].z), wj, acc[2]);
+    acc[3] = __hfma2(bits_h2(c[j].w), wj, acc[3]);
   }
-  const float m = rec.w;
   uint4 out;
-  out.x = ptx::pack_bf16x2(m * acc[0], m * acc[1]);
-  out.y = ptx::pack_bf16x2(m * acc[2], m * acc[3]);
-  out.z = ptx::pack_bf16x2(m * acc[4], m * acc[5]);
-  out.w = ptx::pack_bf16x2(m * acc[6], m * acc[7]);
+  float2 f;
+  f = __half22float2(acc[0]); out.x = ptx::pack_bf16x2(f.x, f.y);
+  f = __half22float2(acc[1]); out.y = ptx::pack_bf16x2(f.x, f.y);
+  f = __half22float2(acc[2]); out.z = ptx::pack_bf16x2(f.x, f.y);
+  f = __half22float2(acc[3]); out.w = ptx::pack_bf16x2(f.x, f.y);
   ptx::sts_v4(dst, out);
 }
 
-// Records of the kRows rows (r0, r0+kStride, ...) a gather thread owns in the tile starting at voxel v0.
-// Rows past the end of the clip get {0,0,0,0}: a valid position with modulation 0, i.e. a zero row.
+// Gather records of the kRows rows (r0, r0+kStride, ...) a gather thread owns in the tile starting at voxel
+// v0.  Rows past the end of the clip get an all-zero record (no corner contributes -> a zero row).
 template <int kRows, int kStride>
-__device__ __forceinline__ void load_row_records(const float4* __restrict__ recs, const Geom& g, int b, int grp,
-                                                 int tap, int v0, int r0, float4 (&out)[kRows]) {
-  const float4* p = recs + (((long long)b * g.G + grp) * g.K + tap) * g.V;
+__device__ __forceinline__ void load_row_records(const uint4* __restrict__ gat, const Geom& g, int b, int grp,
+                                                 int tap, int v0, int r0, GatherRec (&out)[kRows]) {
+  const uint4* p = gat + 3 * ((((long long)b * g.G + grp) * g.K + tap) * g.V);
 #pragma unroll
   for (int i = 0; i < kRows; ++i) {
     const int v = v0 + r0 + kStride * i;
-    out[i] = (v < g.V) ? __ldg(p + v) : make_float4(0.f, 0.f, 0.f, 0.f);
+    if (v < g.V) {
+      out[i].head = __ldg(p + 3 * (long long)v);
+      out[i].w03 = __ldg(p + 3 * (long long)v + 1);
+      out[i].w47 = __ldg(p + 3 * (long long)v + 2);
+    } else {
+      out[i].head = out[i].w03 = out[i].w47 = make_uint4(0u, 0u, 0u, 0u);
+    }
   }
 }
 
