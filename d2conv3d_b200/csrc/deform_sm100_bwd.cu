@@ -66,26 +66,29 @@ stage_gy_img_kernel(int Cout, int V, int tiles_per_clip, int b0, const float* __
 
 // W [Cout][Cin][K] fp32 -> per (N block of 4 slices, 64-wide co block) images of 256 rows x 128 B:
 // row = slice_local*64 + c, 64 co (bf16) per row, swizzled as above (K-major SW128 B tile, K = co).
-__global__ void __launch_bounds__(256)
-stage_wt_img_kernel(int Cout, int Cin, int K, int cpg, int nh, int S, const float* __restrict__ w,
+// Block = (64-wide co block kb, input channel cin): the 64 x K weights W[kb*64 + q][cin][0..K) are read
+// as 64 contiguous runs of K floats into shared memory, then each tap's 64 co values are written as one
+// 128-byte row (8 swizzled 16-byte chunks).
+__global__ void __launch_bounds__(64)
+stage_wt_img_kernel(int Cout, int Cin, int K, int cpg, int nh, const float* __restrict__ w,
                     uint8_t* __restrict__ img) {
-  const int KB = Cout / 64;
-  const long long total = (long long)S * 64 * KB * 8;   // 16-byte chunks
-  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total;
-       e += (long long)gridDim.x * blockDim.x) {
-    const int j = (int)(e & 7);
-    const int kb = (int)((e >> 3) % KB);
-    const long long rowg = (e >> 3) / KB;          // global row = slice*64 + c
-    const int c = (int)(rowg & 63), s = (int)(rowg >> 6);
-    const int h = s % nh, gt = s / nh, tap = gt % K, grp = gt / K;
-    const int cin = grp * cpg + h * 64 + c;
+  extern __shared__ float wsm[];                    // [64 co][K]
+  const int kb = blockIdx.x, cin = blockIdx.y, KB = gridDim.x;
+  for (int i = threadIdx.x; i < 64 * K; i += 64) {
+    const int q = i / K, t = i - q * K;
+    wsm[i] = __ldg(w + ((long long)(kb * 64 + q) * Cin + cin) * K + t);
+  }
+  __syncthreads();
+  const int grp = cin / cpg, h = (cin % cpg) / 64, c = cin & 63;
+  for (int item = threadIdx.x; item < K * 8; item += 64) {
+    const int tap = item >> 3, j = item & 7;
     float v[8];
 #pragma unroll
-    for (int q = 0; q < 8; ++q)
-      v[q] = __ldg(w + ((long long)(kb * 64 + j * 8 + q) * Cin + cin) * K + tap);
+    for (int q = 0; q < 8; ++q) v[q] = wsm[(j * 8 + q) * K + tap];
     uint4 o;
     o.x = ptx::pack_bf16x2(v[0], v[1]); o.y = ptx::pack_bf16x2(v[2], v[3]);
     o.z = ptx::pack_bf16x2(v[4], v[5]); o.w = ptx::pack_bf16x2(v[6], v[7]);
+    const int s = (grp * K + tap) * nh + h;
     const int nb = s >> 2, row = (s & 3) * 64 + c;
     uint8_t* dst = img + ((long long)nb * KB + kb) * kBStageBytes + (row >> 3) * 1024 + (row & 7) * 128 +
                    ((j ^ (row & 7)) << 4);
@@ -407,6 +410,7 @@ bool make_bwd_plan(const Geom& g, unsigned long long cap, BwdPlan* pl) {
   if (g.groups != 1 || g.cpg % 64 != 0 || g.Cout % 64 != 0 || g.Cout > 512) return false;
   if (g.Vin * g.Cin > 0x7fffffffLL) return false;
   if ((long long)g.G * g.K * g.B > 65535) return false;
+  if (g.K * 64 * (int)sizeof(float) > 48 * 1024 || g.Cin > 65535) return false;   // weight staging kernel
   pl->nh = g.cpg / 64;
   pl->S = g.G * g.K * pl->nh;
   pl->NT = pl->S * 64;
@@ -472,7 +476,8 @@ int run_bwd(const Geom& g, const Coords& coords, unsigned long long cap, const f
     dim3 grid((unsigned)((g.Vin + 31) / 32), (unsigned)((g.Cin + 63) / 64), (unsigned)g.B);
     stage_input_cl_f16_kernel<<<grid, 256, 0, st>>>(g.Cin, g.Vin, x, x_cl);
     D2C_LAUNCH_CHECK();
-    stage_wt_img_kernel<<<sm_count * 8, 256, 0, st>>>(g.Cout, g.Cin, g.K, g.cpg, pl.nh, pl.S, w, wt_img);
+    stage_wt_img_kernel<<<dim3((unsigned)pl.KB, (unsigned)g.Cin), 64, 64 * g.K * sizeof(float), st>>>(
+        g.Cout, g.Cin, g.K, g.cpg, pl.nh, w, wt_img);
     D2C_LAUNCH_CHECK();
     if ((rc = launch_sample_records(g, coords, mask, recs, gat, st))) return rc;
   }
