@@ -433,6 +433,84 @@ def run_gpu_arm(args):
         dist.destroy_process_group()
 
 
+EXTRA_WORKLOADS = {
+    # BASELINE config 3: dynamic-dilation conv3d, one field shared by all taps, optional 27-channel mask
+    "c3-xyz": dict(kind="dyndil", mode="xyz", B=4, Cin=256, Cout=256, dims=(8, 60, 108), G=1),
+    "c3-xy": dict(kind="dyndil", mode="xy", B=4, Cin=256, Cout=256, dims=(8, 60, 108), G=1),
+    "c3-x": dict(kind="dyndil", mode="x", B=4, Cin=256, Cout=256, dims=(8, 60, 108), G=1),
+    # BASELINE config 4: depthwise 3x3x3 of an ir-CSN bottleneck, then the modulated deformable 1024->256 stage
+    "c4-depthwise": dict(kind="depthwise", B=8, C=1024, dims=(8, 30, 54)),
+    "c4-md": dict(kind="deform", B=8, Cin=1024, Cout=256, dims=(8, 30, 54), G=8),
+}
+
+
+def run_extra_workload(args):
+    """Secondary configurations (not the headline line): prints one JSON line with forward / backward
+    milliseconds from CUDA events, contraction TFLOP/s or GB/s against the measured peaks."""
+    import torch
+
+    import d2conv3d_b200
+    from d2conv3d_b200 import _lib, dconv_native, fast_depthwise_conv3d
+    from tests._util import make_problem
+
+    wl = EXTRA_WORKLOADS[args.workload]
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    _lib.lib()
+    d2conv3d_b200.set_math_mode(args.mode)
+    peaks = measured_peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    V = wl["dims"][0] * wl["dims"][1] * wl["dims"][2]
+
+    if wl["kind"] == "depthwise":
+        g = torch.Generator().manual_seed(1004)
+        x = torch.randn((wl["B"], wl["C"]) + wl["dims"], generator=g).to(dev).requires_grad_()
+        w = (torch.randn((wl["C"], 1, 3, 3, 3), generator=g) * 0.1).to(dev).requires_grad_()
+        gy = torch.randn((wl["B"], wl["C"]) + wl["dims"], generator=g).to(dev)
+        fwd = lambda: fast_depthwise_conv3d._ops.depthwise_separable_conv3d(x, w, None, 1, 1, 1)
+        params = [x, w]
+        work_f = 2 * 4 * wl["B"] * wl["C"] * V      # bytes: read x, write y
+        work_b = 3 * 4 * wl["B"] * wl["C"] * V      # read grad_out + x, write grad_x
+        unit, peak = "GB/s", peaks["hbm_gbs"]
+    else:
+        p = make_problem(1003, wl["B"], wl["Cin"], wl["Cout"], wl["dims"], k=3, padding=1, G=wl["G"],
+                         dtype=np.float32, offset_std=2.0, field_mode=wl.get("mode"))
+        ts = [torch.from_numpy(p[k]).to(dev).requires_grad_() for k in ("x", "geo", "mask", "weight", "bias")]
+        gy = torch.from_numpy(p["gy"]).to(dev)
+        if wl["kind"] == "dyndil":
+            fwd = lambda: dconv_native.dyn_dilated_conv3d(*ts, wl["mode"], 1, 1, 1, 1, wl["G"])
+        else:
+            fwd = lambda: dconv_native.deform_conv3d(*ts, 1, 1, 1, 1, wl["G"])
+        params = ts
+        work_f = fwd_flops(wl["B"], wl["Cin"], wl["Cout"], V, 27)
+        work_b = 2 * work_f
+        unit, peak = "TFLOP/s", peaks["tensor_sustained"]
+
+    def one():
+        for t in params:
+            t.grad = None
+        flush.zero_()
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        e[0].record(); y = fwd(); e[1].record(); y.backward(gy); e[2].record()
+        torch.cuda.synchronize()
+        return e[0].elapsed_time(e[1]), e[1].elapsed_time(e[2])
+
+    for _ in range(max(3, args.warmup)):
+        one()
+    runs = [one() for _ in range(args.steps)]
+    f_ms = statistics.median(r[0] for r in runs)
+    b_ms = statistics.median(r[1] for r in runs)
+    scale = 1e9 if unit == "GB/s" else 1e12
+    _lib.device_status()
+    print(json.dumps({
+        "workload": args.workload, "config": wl, "math_mode": _lib.get_math_mode(), "steps": args.steps,
+        "fwd_ms": f_ms, "bwd_ms": b_ms, "clips_per_s_fwd_bwd": wl["B"] / ((f_ms + b_ms) * 1e-3),
+        "fwd": {"achieved": work_f / (f_ms * 1e-3) / scale, "unit": unit, "frac_of_measured_peak": work_f / (f_ms * 1e-3) / scale / peak},
+        "bwd": {"achieved": work_b / (b_ms * 1e-3) / scale, "unit": unit, "frac_of_measured_peak": work_b / (b_ms * 1e-3) / scale / peak},
+        "note": "times include operand staging and (backward) all gradients; L2 flushed between iterations",
+    }), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -443,10 +521,14 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-reference-gpu", action="store_true")
+    ap.add_argument("--workload", default="c2", choices=["c2"] + sorted(EXTRA_WORKLOADS),
+                    help="c2 = the headline line (default); the others print a secondary line for one GPU")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.workload != "c2":
+        run_extra_workload(args)
     else:
         run_gpu_arm(args)
 

@@ -10,6 +10,7 @@
 #include <mutex>
 
 #include "d2c_common.cuh"
+#include "depthwise_tile.cuh"
 
 namespace d2c {
 
@@ -235,6 +236,13 @@ template <typename T>
 static int dw_fwd_t(const Geom& g, const void* x, const void* w, const void* bias, void* y, cudaStream_t st) {
   const long long total = (long long)g.B * g.Cout * g.V;
   prof_mark(st, "depthwise_fwd");
+  DwTilePlan plan;
+  if (dw_tile_plan(g, sizeof(typename AccOf<T>::type), &plan)) {
+    const int rc = dw_tile_conv<T, typename AccOf<T>::type>(g, plan, (const T*)x, (const T*)w, (const T*)bias, (T*)y,
+                                                            0, st);
+    prof_mark(st, nullptr);
+    return rc;
+  }
   if (g.kd == 3 && g.kh == 3 && g.kw == 3)
     dw_fwd_kernel<T, 3, 3, 3><<<blocks_for(total), 256, 0, st>>>(g, (const T*)x, (const T*)w, (const T*)bias, (T*)y);
   else
@@ -249,10 +257,16 @@ static int dw_bwd_t(const Geom& g, const void* gy, const void* x, const void* w,
                     void* gbias, void* ws, cudaStream_t st) {
   using A = typename AccOf<T>::type;
   const bool k333 = g.kd == 3 && g.kh == 3 && g.kw == 3;
+  DwTilePlan plan;
+  const bool tiled = dw_tile_plan(g, sizeof(A), &plan);
   if (gx) {
     const long long total = (long long)g.B * g.Cin * g.Vin;
     prof_mark(st, "depthwise_bwd_input");
-    if (k333)
+    if (tiled) {
+      // grad_x = correlation of grad_out with the point-reflected kernel
+      const int rc = dw_tile_conv<T, A>(g, plan, (const T*)gy, (const T*)w, (const T*)nullptr, (T*)gx, 1, st);
+      if (rc) return rc;
+    } else if (k333)
       dw_bwd_input_kernel<T, 3, 3, 3><<<blocks_for(total), 256, 0, st>>>(g, (const T*)gy, (const T*)w, (T*)gx);
     else
       dw_bwd_input_kernel<T, 0, 0, 0><<<blocks_for(total), 256, 0, st>>>(g, (const T*)gy, (const T*)w, (T*)gx);
@@ -262,7 +276,11 @@ static int dw_bwd_t(const Geom& g, const void* gy, const void* x, const void* w,
     A* partial = (A*)ws;
     const long long n = (long long)g.Cout * g.K;
     prof_mark(st, "depthwise_bwd_weight");
-    if (k333) {
+    if (tiled) {
+      D2C_CUDA_TRY(cudaMemsetAsync(partial, 0, sizeof(A) * (size_t)n, st));
+      const int rc = dw_tile_wgrad<T, A>(g, plan, (const T*)gy, (const T*)x, partial, st);
+      if (rc) return rc;
+    } else if (k333) {
       D2C_CUDA_TRY(cudaMemsetAsync(partial, 0, sizeof(A) * (size_t)n, st));
       // enough (channel, clip-slice) blocks to fill the GPU a few times over
       int slices = (148 * 8 + g.Cout - 1) / g.Cout;
