@@ -43,6 +43,7 @@ int depthwise_fwd(const Geom& g, int dtype, const void* x, const void* w, const 
 int depthwise_bwd(const Geom& g, int dtype, const void* gy, const void* x, const void* w, void* gx,
                   void* gw, void* gbias, void* ws, cudaStream_t st);
 size_t depthwise_bwd_workspace(const Geom& g);
+int depthwise_device_status();
 
 static size_t dtype_size(int dtype) { return dtype == D2C_F64 ? 8 : (dtype == D2C_F16 ? 2 : 4); }
 
@@ -185,7 +186,7 @@ const char* d2c_last_cuda_error(void) { return g_last_cuda_error; }
 int d2c_device_status(void) {
   int rc = check_cuda(cudaDeviceSynchronize());
   if (rc) return rc;
-  const int v1 = sm100_device_status(), v2 = sm100_bwd_device_status() | sm100_dw_device_status();
+  const int v1 = sm100_device_status() | depthwise_device_status(), v2 = sm100_bwd_device_status() | sm100_dw_device_status();
   if (v1 < 0 || v2 < 0) return D2C_ERR_CUDA;
   const int v = v1 | v2;
   return v ? D2C_ERR_DEVICE_TIMEOUT : D2C_OK;

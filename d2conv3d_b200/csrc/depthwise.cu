@@ -10,6 +10,7 @@
 #include <mutex>
 
 #include "d2c_common.cuh"
+#include "depthwise_bulk.cuh"
 #include "depthwise_tile.cuh"
 
 namespace d2c {
@@ -226,6 +227,8 @@ dw_grad_bias_kernel(int B, int Cout, int V, const T* __restrict__ gy, T* __restr
   if (threadIdx.x == 0) grad_bias[co] = cvt<T, A>(red[0]);
 }
 
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
 static unsigned blocks_for(long long total) {
   long long n = (total + 255) / 256;
   const long long cap = 148LL * 32;
@@ -238,8 +241,11 @@ static int dw_fwd_t(const Geom& g, const void* x, const void* w, const void* bia
   prof_mark(st, "depthwise_fwd");
   DwTilePlan plan;
   if (dw_tile_plan(g, sizeof(typename AccOf<T>::type), &plan)) {
-    const int rc = dw_tile_conv<T, typename AccOf<T>::type>(g, plan, (const T*)x, (const T*)w, (const T*)bias, (T*)y,
-                                                            0, st);
+    using A = typename AccOf<T>::type;
+    DwBulkPlan bulk;
+    const int rc = (aligned16(x) && dw_bulk_plan(g, sizeof(T), 1, plan, &bulk))
+                       ? dw_bulk_conv<T, A>(g, plan, bulk, (const T*)x, (const T*)w, (const T*)bias, (T*)y, 0, st)
+                       : dw_tile_conv<T, A>(g, plan, (const T*)x, (const T*)w, (const T*)bias, (T*)y, 0, st);
     prof_mark(st, nullptr);
     return rc;
   }
@@ -264,7 +270,10 @@ static int dw_bwd_t(const Geom& g, const void* gy, const void* x, const void* w,
     prof_mark(st, "depthwise_bwd_input");
     if (tiled) {
       // grad_x = correlation of grad_out with the point-reflected kernel
-      const int rc = dw_tile_conv<T, A>(g, plan, (const T*)gy, (const T*)w, (const T*)nullptr, (T*)gx, 1, st);
+      DwBulkPlan bulk;
+      const int rc = (aligned16(gy) && dw_bulk_plan(g, sizeof(T), 1, plan, &bulk))
+                         ? dw_bulk_conv<T, A>(g, plan, bulk, (const T*)gy, (const T*)w, (const T*)nullptr, (T*)gx, 1, st)
+                         : dw_tile_conv<T, A>(g, plan, (const T*)gy, (const T*)w, (const T*)nullptr, (T*)gx, 1, st);
       if (rc) return rc;
     } else if (k333)
       dw_bwd_input_kernel<T, 3, 3, 3><<<blocks_for(total), 256, 0, st>>>(g, (const T*)gy, (const T*)w, (T*)gx);
@@ -278,7 +287,10 @@ static int dw_bwd_t(const Geom& g, const void* gy, const void* x, const void* w,
     prof_mark(st, "depthwise_bwd_weight");
     if (tiled) {
       D2C_CUDA_TRY(cudaMemsetAsync(partial, 0, sizeof(A) * (size_t)n, st));
-      const int rc = dw_tile_wgrad<T, A>(g, plan, (const T*)gy, (const T*)x, partial, st);
+      DwBulkPlan bulk;
+      const int rc = (aligned16(gy) && aligned16(x) && dw_bulk_plan(g, sizeof(T), 2, plan, &bulk))
+                         ? dw_bulk_wgrad<T, A>(g, plan, bulk, (const T*)gy, (const T*)x, partial, st)
+                         : dw_tile_wgrad<T, A>(g, plan, (const T*)gy, (const T*)x, partial, st);
       if (rc) return rc;
     } else if (k333) {
       D2C_CUDA_TRY(cudaMemsetAsync(partial, 0, sizeof(A) * (size_t)n, st));
@@ -303,6 +315,12 @@ static int dw_bwd_t(const Geom& g, const void* gy, const void* x, const void* w,
   }
   prof_mark(st, nullptr);
   return D2C_OK;
+}
+
+int depthwise_device_status() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_dw_status, sizeof(int)) != cudaSuccess) return -1;
+  return v;
 }
 
 size_t depthwise_bwd_workspace(const Geom& g) { return align_up(sizeof(double) * (size_t)g.Cout * g.K, 256); }

@@ -60,6 +60,45 @@ def test_depthwise_other_kernel_shapes_and_larger_tile(dw):
         assert np.abs(np32(m.bias.grad) - wgb).max() <= 1e-4 * max(1.0, np.abs(wgb).max())
 
 
+@pytest.mark.parametrize("shape,dtype,misalign", [
+    ((2, 8, 4, 6, 8), torch.float32, False),      # whole volumes staged by bulk copies, one per chunk
+    ((2, 640, 2, 5, 7), torch.float32, False),    # 280-byte volumes: two per chunk to reach 16-byte multiples
+    ((2, 640, 2, 5, 7), torch.float16, False),    # 140-byte volumes: four per chunk
+    ((1, 3, 3, 5, 7), torch.float32, False),      # volume count not divisible by the chunk: register-window march
+    ((1, 2, 8, 56, 56), torch.float32, False),    # forward fits shared memory single-block, weight gradient does not
+    ((2, 8, 4, 6, 8), torch.float32, True),       # tensors at a 4-byte offset: no bulk copy possible
+    ((1, 4, 1, 9, 33), torch.float64, False),     # single plane, double
+])
+def test_depthwise_3x3x3_fast_paths(dw, shape, dtype, misalign):
+    """The 3x3x3 / stride 1 / padding 1 case has three implementations chosen by size and alignment
+    (bulk-copy pipeline, register-window march, generic); every one must match the oracle."""
+    from d2conv3d_b200 import _lib
+    torch.manual_seed(11)
+    B, C = shape[:2]
+
+    def make(*sh):
+        n = int(np.prod(sh))
+        if misalign:
+            return torch.randn(n + 1, device="cuda", dtype=dtype)[1:].view(*sh)
+        return torch.randn(*sh, device="cuda", dtype=dtype)
+
+    x = make(*shape).div_(2).requires_grad_()
+    w = (torch.randn(C, 1, 3, 3, 3, device="cuda", dtype=dtype) / 4).requires_grad_()
+    b = torch.randn(C, device="cuda", dtype=dtype).requires_grad_()
+    y = dw._ops.depthwise_separable_conv3d(x, w, b, 1, 1, 1)
+    gy = make(*shape).div_(2)
+    y.backward(gy)
+    np64 = lambda t: t.detach().double().cpu().numpy()
+    wy = orc.depthwise_conv3d_fwd(np64(x), np64(w), np64(b), 1, 1, 1)
+    wgx, wgw, wgb = orc.depthwise_conv3d_bwd(np64(gy), np64(x), np64(w), True, 1, 1, 1)
+    atol = ATOL[dtype]
+    assert np.abs(np64(y) - wy).max() <= atol
+    assert np.abs(np64(x.grad) - wgx).max() <= atol
+    scale = max(1.0, float(np.abs(wgw).max()))
+    assert np.abs(np64(w.grad) - wgw).max() <= (1e-2 if dtype == torch.float16 else 1e-4) * scale
+    _lib.device_status()
+
+
 def test_autocast_keeps_half(dw):
     inp = torch.randn(2, 2, 5, 5, 5).to(dtype=torch.half, device="cuda")
     conv = dw.DepthwiseConv3d(2, 2, kernel_size=3).cuda()
