@@ -61,13 +61,15 @@ def test_depthwise_other_kernel_shapes_and_larger_tile(dw):
 
 
 @pytest.mark.parametrize("shape,dtype,misalign", [
-    ((2, 8, 4, 6, 8), torch.float32, False),      # whole volumes staged by bulk copies, one per chunk
-    ((2, 640, 2, 5, 7), torch.float32, False),    # 280-byte volumes: two per chunk to reach 16-byte multiples
-    ((2, 640, 2, 5, 7), torch.float16, False),    # 140-byte volumes: four per chunk
-    ((1, 3, 3, 5, 7), torch.float32, False),      # volume count not divisible by the chunk: register-window march
-    ((1, 2, 8, 56, 56), torch.float32, False),    # forward fits shared memory single-block, weight gradient does not
+    ((2, 8, 4, 6, 8), torch.float32, False),      # planes staged by bulk copies, one volume per chunk
+    ((2, 640, 2, 4, 8), torch.float32, False),    # small volumes: two per chunk
+    ((2, 640, 2, 4, 8), torch.float16, False),    # half: 64-byte planes
+    ((2, 8, 5, 6, 8), torch.float32, False),      # depth not a multiple of the march's unroll
+    ((2, 64, 2, 5, 7), torch.float32, False),     # 140-byte planes cannot be bulk-copied: register-window march
+    ((1, 3, 3, 5, 7), torch.float32, False),      # odd everything
+    ((1, 2, 8, 56, 56), torch.float32, False),    # forward fits shared memory with one block per SM, weight gradient does not
     ((2, 8, 4, 6, 8), torch.float32, True),       # tensors at a 4-byte offset: no bulk copy possible
-    ((1, 4, 1, 9, 33), torch.float64, False),     # single plane, double
+    ((1, 4, 1, 9, 32), torch.float64, False),     # single plane, double, odd height
 ])
 def test_depthwise_3x3x3_fast_paths(dw, shape, dtype, misalign):
     """The 3x3x3 / stride 1 / padding 1 case has three implementations chosen by size and alignment
