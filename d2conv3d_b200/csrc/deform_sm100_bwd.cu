@@ -170,12 +170,36 @@ dcol_sm100_kernel(const DcolParams p) {
         uint32_t r[32];
         ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * kNBlock + c0), r);
         ptx::tmem_ld_wait();
-        if (v < p.V) {
-          float4* dst = reinterpret_cast<float4*>(row + (c0 >> 6) * slice_stride + (c0 & 63));
+        // Lanes 2i / 2i+1 hold rows v, v+1 (256 bytes apart).  They swap every other 16-byte chunk so that
+        // each store instruction has the pair write one full 32-byte sector of ONE row (first the even
+        // lane's row, then the odd lane's) instead of two half sectors of two rows.
+        {
+          const bool odd = lane & 1;
+          float* row_even = row - (odd ? 64 : 0) + (c0 >> 6) * slice_stride + (c0 & 63);
+          const bool ok_even = (v - (odd ? 1 : 0)) < p.V, ok_odd = (v + (odd ? 0 : 1)) < p.V;
 #pragma unroll
-          for (int i = 0; i < 8; ++i)
-            dst[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
-                                 __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+          for (int i = 0; i < 4; ++i) {
+            uint32_t send[4], recv[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) send[e] = odd ? r[8 * i + e] : r[8 * i + 4 + e];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) recv[e] = __shfl_xor_sync(0xffffffffu, send[e], 1);
+            float4 first, second;   // first: even row's chunk (2i + odd); second: odd row's chunk (2i + odd)
+            if (odd) {
+              first = make_float4(__uint_as_float(recv[0]), __uint_as_float(recv[1]), __uint_as_float(recv[2]),
+                                  __uint_as_float(recv[3]));
+              second = make_float4(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]),
+                                   __uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+            } else {
+              first = make_float4(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1]),
+                                  __uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
+              second = make_float4(__uint_as_float(recv[0]), __uint_as_float(recv[1]), __uint_as_float(recv[2]),
+                                   __uint_as_float(recv[3]));
+            }
+            float4* dst = reinterpret_cast<float4*>(row_even + (2 * i + (odd ? 1 : 0)) * 4);
+            if (ok_even) dst[0] = first;
+            if (ok_odd) dst[16] = second;    // next row: + 64 floats
+          }
         }
       }
       ptx::tc_fence_before();
