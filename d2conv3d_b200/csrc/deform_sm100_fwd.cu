@@ -38,8 +38,10 @@ constexpr int kBK = 64;             // channels per K slice (128 bytes of bf16: 
 constexpr int kAStages = 4;
 constexpr int kAStageBytes = kBM * kBK * 2;   // 16 KB
 constexpr int kMaxN = 512;
-constexpr int kThreads = (6 + 16) * 32;   // 4 epilogue + MMA + loader + 16 gather warps
-constexpr int kEpiWarps = 4, kMmaWarp = 4, kLoadWarp = 5, kGatherWarp0 = 6, kGatherWarps = 16;
+constexpr int kThreads = (6 + 16 + 1) * 32;   // 4 epilogue + MMA + weight loader + 16 gather + record loader warps
+constexpr int kEpiWarps = 4, kMmaWarp = 4, kLoadWarp = 5, kGatherWarp0 = 6, kGatherWarps = 16, kRecWarp = 22;
+constexpr int kRStages = 4;                       // gather-record ring: one stage = the records of a unit's 128 rows
+constexpr int kRStageBytes = kBM * 48;            // 6 KB
 constexpr int kRowStride = kGatherWarps * 4;          // 8 threads per row -> rows handled per pass
 constexpr int kRowsPerThread = kBM / kRowStride;
 constexpr int kSmemLimit = 227 * 1024;
@@ -76,14 +78,18 @@ fwd_sm100_kernel(const FwdParams p) {
   const uint32_t raw = ptx::smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - raw);
-  const int bar_off = kAStages * kAStageBytes + p.b_stages * p.b_stage_bytes;
-  const uint32_t a_base = base, b_base = base + kAStages * kAStageBytes, bar_base = base + bar_off;
+  const int rec_off = kAStages * kAStageBytes + p.b_stages * p.b_stage_bytes;
+  const int bar_off = rec_off + kRStages * kRStageBytes;
+  const uint32_t a_base = base, b_base = base + kAStages * kAStageBytes, rec_base = base + rec_off,
+                 bar_base = base + bar_off;
   auto a_full = [&](int s) { return bar_base + 8u * s; };
   auto a_empty = [&](int s) { return bar_base + 8u * (kAStages + s); };
   auto b_full = [&](int s) { return bar_base + 8u * (2 * kAStages + s); };
   auto b_empty = [&](int s) { return bar_base + 8u * (2 * kAStages + 4 + s); };
   const uint32_t acc_full = bar_base + 8u * (2 * kAStages + 8);
   const uint32_t acc_empty = bar_base + 8u * (2 * kAStages + 9);
+  auto r_full = [&](int s) { return bar_base + 8u * (2 * kAStages + 11 + s); };
+  auto r_empty = [&](int s) { return bar_base + 8u * (2 * kAStages + 11 + kRStages + s); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + bar_off + 8 * (2 * kAStages + 10));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + bar_off + 8 * (2 * kAStages + 10) + 4);
 
@@ -95,6 +101,7 @@ fwd_sm100_kernel(const FwdParams p) {
   if (threadIdx.x == 0) {
     for (int s = 0; s < kAStages; ++s) { ptx::mbar_init(a_full(s), kGatherWarps); ptx::mbar_init(a_empty(s), 1); }
     for (int s = 0; s < p.b_stages; ++s) { ptx::mbar_init(b_full(s), 1); ptx::mbar_init(b_empty(s), 1); }
+    for (int s = 0; s < kRStages; ++s) { ptx::mbar_init(r_full(s), 1); ptx::mbar_init(r_empty(s), kGatherWarps); }
     ptx::mbar_init(acc_full, 1);
     ptx::mbar_init(acc_empty, kEpiWarps);
     *abort_flag = 0;
@@ -119,7 +126,7 @@ fwd_sm100_kernel(const FwdParams p) {
       u += s_end - s_beg;
       const bool whole = (s_beg == 0 && s_end == p.S);
       const int b = tile / p.tiles_per_clip, v0 = (tile % p.tiles_per_clip) * kBM;
-      if (!ptx::mbar_wait(acc_full, seg & 1, abort_flag)) break;
+      if (!ptx::mbar_wait(acc_full, seg & 1, abort_flag, 2000)) break;
       ptx::tc_fence_after();
       const int v = v0 + warp * 32 + lane;
       float* yb = p.y + (long long)b * g.Cout * g.V + v;
@@ -186,7 +193,7 @@ fwd_sm100_kernel(const FwdParams p) {
       uint32_t k = 0;
       for (long long u = u_beg; u < u_end; ++u, ++k) {
         const int s = (int)(u % p.S), sb = k % p.b_stages;
-        if (!ptx::mbar_wait(b_empty(sb), ((k / p.b_stages) & 1) ^ 1, abort_flag)) break;
+        if (!ptx::mbar_wait(b_empty(sb), ((k / p.b_stages) & 1) ^ 1, abort_flag, 200)) break;
         ptx::mbar_arrive_expect_tx(b_full(sb), (uint32_t)p.b_stage_bytes);
         const uint8_t* src = p.w_sw + (long long)s * p.b_stage_bytes;
         const uint32_t dst = b_base + sb * p.b_stage_bytes;
@@ -201,6 +208,30 @@ fwd_sm100_kernel(const FwdParams p) {
           if (clock64() - t0 > ptx::kWaitBudgetCycles) break;
       }
     }
+  } else if (warp == kRecWarp) {
+    // ===================== gather-record loader =====================
+    // The records of a unit's rows are one contiguous run of the [B][G][K][V] stream: one bulk copy per unit,
+    // kRStages units ahead of the gather warps, so the producers read them from shared memory.
+    if (lane == 0) {
+      uint32_t k = 0;
+      for (long long u = u_beg; u < u_end; ++u, ++k) {
+        const int tile = (int)(u / p.S), s = (int)(u % p.S);
+        const int b = tile / p.tiles_per_clip, v0 = (tile % p.tiles_per_clip) * kBM;
+        const int gt = s / p.nh, tap = gt % g.K, grp = gt / g.K;
+        const int sr = k % kRStages;
+        if (!ptx::mbar_wait(r_empty(sr), ((k / kRStages) & 1) ^ 1, abort_flag, 200)) break;
+        const uint32_t bytes = (uint32_t)min(kBM, g.V - v0) * 48u;
+        ptx::mbar_arrive_expect_tx(r_full(sr), bytes);
+        ptx::bulk_g2s(rec_base + sr * kRStageBytes, p.recs + 3 * ((((long long)b * g.G + grp) * g.K + tap) * g.V + v0),
+                      bytes, r_full(sr));
+      }
+      const uint32_t issued = k;
+      for (uint32_t q = (issued > (uint32_t)kRStages ? issued - kRStages : 0); q < issued; ++q) {
+        const long long t0 = clock64();
+        while (!ptx::mbar_try_wait(r_full(q % kRStages), (q / kRStages) & 1))
+          if (clock64() - t0 > ptx::kWaitBudgetCycles) break;
+      }
+    }
   } else {
     // ===================== gather producers =====================
     const int t = threadIdx.x - kGatherWarp0 * 32;
@@ -212,40 +243,42 @@ fwd_sm100_kernel(const FwdParams p) {
       const int r = r0 + kRowStride * i;
       row_dst[i] = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((j ^ (r & 7)) << 4));
     }
-    auto unit_coords = [&](long long u, int& b, int& v0, int& grp, int& tap, int& h) {
-      const int tile = (int)(u / p.S), s = (int)(u % p.S);
-      b = tile / p.tiles_per_clip; v0 = (tile % p.tiles_per_clip) * kBM;
-      h = s % p.nh;
-      const int gt = s / p.nh;
-      tap = gt % g.K; grp = gt / g.K;
-    };
-    GatherRec rec[kRowsPerThread];
-    int b, v0, grp, tap, h;
-    if (u_beg < u_end) {
-      unit_coords(u_beg, b, v0, grp, tap, h);
-      load_row_records<kRowsPerThread, kRowStride>(p.recs, g, b, grp, tap, v0, r0, rec);
-    }
     uint32_t k = 0;
     for (long long u = u_beg; u < u_end; ++u, ++k) {
-      GatherRec rec_next[kRowsPerThread];
-      int nb = b, nv0 = v0, ngrp = grp, ntap = tap, nh_ = h;
-      if (u + 1 < u_end) {
-        unit_coords(u + 1, nb, nv0, ngrp, ntap, nh_);
-        load_row_records<kRowsPerThread, kRowStride>(p.recs, g, nb, ngrp, ntap, nv0, r0, rec_next);   // in flight while this unit is produced
+      const int tile = (int)(u / p.S), s = (int)(u % p.S);
+      const int b = tile / p.tiles_per_clip, v0 = (tile % p.tiles_per_clip) * kBM;
+      const int h = s % p.nh, grp = (s / p.nh) / g.K;
+      const int sr = k % kRStages, sa = k % kAStages;
+      if (!ptx::mbar_wait(r_full(sr), (k / kRStages) & 1, abort_flag)) break;
+      const uint8_t* rec_stage = base_ptr + rec_off + sr * kRStageBytes;
+      const __half* xb = p.x_cl + (long long)b * g.Vin * g.Cin + grp * g.cpg + h * kBK + j * 8;
+      // every corner of every row this thread owns goes in flight before the first blend
+      uint4 c[kRowsPerThread][8];
+#pragma unroll
+      for (int i = 0; i < kRowsPerThread; ++i) {
+        const int r = r0 + kRowStride * i;
+        uint2 head = make_uint2(0u, 0u);
+        if (v0 + r < g.V) head = *reinterpret_cast<const uint2*>(rec_stage + r * 48);
+        load_corners(xb, p.cs, head.x, head.y, c[i]);
       }
-      const int sa = k % kAStages;
       if (!ptx::mbar_wait(a_empty(sa), ((k / kAStages) & 1) ^ 1, abort_flag)) break;
       const uint32_t stage = a_base + sa * kAStageBytes;
-      const __half* xb = p.x_cl + (long long)b * g.Vin * g.Cin;
-      const int ch0 = grp * g.cpg + h * kBK + j * 8;
 #pragma unroll
-      for (int i = 0; i < kRowsPerThread; ++i) produce_item(xb, p.cs, rec[i], ch0, stage + row_dst[i]);
+      for (int i = 0; i < kRowsPerThread; ++i) {
+        const int r = r0 + kRowStride * i;
+        uint4 w03 = make_uint4(0u, 0u, 0u, 0u), w47 = w03;   // rows past the clip end: stage bytes are stale
+        if (v0 + r < g.V) {
+          w03 = *reinterpret_cast<const uint4*>(rec_stage + r * 48 + 16);
+          w47 = *reinterpret_cast<const uint4*>(rec_stage + r * 48 + 32);
+        }
+        blend_store(c[i], w03, w47, stage + row_dst[i]);
+      }
       ptx::fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(a_full(sa));
-#pragma unroll
-      for (int i = 0; i < kRowsPerThread; ++i) rec[i] = rec_next[i];
-      b = nb; v0 = nv0; grp = ngrp; tap = ntap; h = nh_;
+      if (lane == 0) {
+        ptx::mbar_arrive(a_full(sa));
+        ptx::mbar_arrive(r_empty(sr));
+      }
     }
   }
 
@@ -305,14 +338,14 @@ bool make_plan(const Geom& g, Plan* pl) {
   pl->tiles_per_clip = (g.V + kBM - 1) / kBM;
   pl->n_tiles = pl->tiles_per_clip * g.B;
   pl->b_stage_bytes = g.Cout * 128;
-  int nb = (kSmemLimit - 1024 - 256 - kAStages * kAStageBytes) / pl->b_stage_bytes;
+  int nb = (kSmemLimit - 1024 - 256 - kAStages * kAStageBytes - kRStages * kRStageBytes) / pl->b_stage_bytes;
   if (nb > 4) nb = 4;
   if (nb < 2) return false;
   pl->b_stages = nb;
   int cols = 32;
   while (cols < g.Cout) cols <<= 1;
   pl->tmem_cols = cols;
-  pl->smem_bytes = kAStages * kAStageBytes + pl->b_stages * pl->b_stage_bytes + 256 + 1024;
+  pl->smem_bytes = kAStages * kAStageBytes + pl->b_stages * pl->b_stage_bytes + kRStages * kRStageBytes + 256 + 1024;
   pl->x_cl_bytes = align_up((size_t)g.B * g.Vin * g.Cin * 2, 256);
   pl->w_sw_bytes = align_up((size_t)pl->S * pl->b_stage_bytes, 256);
   pl->rec_bytes = gather_records_bytes(g);

@@ -119,6 +119,39 @@ __device__ __forceinline__ void produce_item(const __half* __restrict__ xb, ClSt
   ptx::sts_v4(dst, out);
 }
 
+// The same work split in two so that a producer can put the corners of several items in flight before the
+// first blend: load_corners issues the (up to) 8 corner loads of one item, blend_store consumes them.
+__device__ __forceinline__ void load_corners(const __half* __restrict__ xb_ch, ClStrides cs, uint32_t voff,
+                                             uint32_t valid, uint4 (&c)[8]) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int off = (int)voff + (j >> 2) * cs.dz + ((j >> 1) & 1) * cs.dy + (j & 1) * cs.dx;
+    c[j] = ((valid >> j) & 1u) ? ptx::ldg_nc_v4(xb_ch + off) : make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
+__device__ __forceinline__ void blend_store(const uint4 (&c)[8], uint4 w03, uint4 w47, uint32_t dst) {
+  const uint32_t w[8] = {w03.x, w03.y, w03.z, w03.w, w47.x, w47.y, w47.z, w47.w};
+  __half2 acc[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) acc[e] = __float2half2_rn(0.f);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {   // corner order 000..111, as the reference's interpolation chain
+    const __half2 wj = bits_h2(w[j]);
+    acc[0] = __hfma2(bits_h2(c[j].x), wj, acc[0]);
+    acc[1] = __hfma2(bits_h2(c[j].y), wj, acc[1]);
+    acc[2] = __hfma2(bits_h2(c[j].z), wj, acc[2]);
+    acc[3] = __hfma2(bits_h2(c[j].w), wj, acc[3]);
+  }
+  uint4 out;
+  float2 f;
+  f = __half22float2(acc[0]); out.x = ptx::pack_bf16x2(f.x, f.y);
+  f = __half22float2(acc[1]); out.y = ptx::pack_bf16x2(f.x, f.y);
+  f = __half22float2(acc[2]); out.z = ptx::pack_bf16x2(f.x, f.y);
+  f = __half22float2(acc[3]); out.w = ptx::pack_bf16x2(f.x, f.y);
+  ptx::sts_v4(dst, out);
+}
+
 // Gather records of the kRows rows (r0, r0+kStride, ...) a gather thread owns in the tile starting at voxel
 // v0.  Rows past the end of the clip get an all-zero record (no corner contributes -> a zero row).
 template <int kRows, int kStride>

@@ -48,13 +48,18 @@ constexpr long long kWaitBudgetCycles = 4000000000LL;
 
 // Returns false (and raises *abort_flag) if the phase did not complete in time or
 // another role already aborted.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+// backoff_ns > 0: sleep between polls (for roles whose waits are long and not latency-critical, so that
+// their polling does not take issue slots from the producers).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          unsigned backoff_ns = 0) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
 #pragma unroll 1
-    for (int i = 0; i < 64; ++i)
+    for (int i = 0; i < 64; ++i) {
       if (mbar_try_wait(bar, parity)) return true;
+      if (backoff_ns) __nanosleep(backoff_ns);
+    }
     if (*abort_flag) return false;
     if (clock64() - t0 > kWaitBudgetCycles) {
       *abort_flag = 1;
