@@ -29,6 +29,9 @@
 #include "sm100_ptx.cuh"
 #include "sm100_stage.cuh"
 
+#include <cstdio>
+#include <cstdlib>
+
 namespace d2c {
 
 namespace {
@@ -41,7 +44,8 @@ constexpr int kMaxN = 512;
 constexpr int kThreads = (6 + 16 + 1) * 32;   // 4 epilogue + MMA + weight loader + 16 gather + record loader warps
 constexpr int kEpiWarps = 4, kMmaWarp = 4, kLoadWarp = 5, kGatherWarp0 = 6, kGatherWarps = 16, kRecWarp = 22;
 constexpr int kRStages = 4;                       // gather-record ring: one stage = the records of a unit's 128 rows
-constexpr int kRStageBytes = kBM * 48;            // 6 KB
+constexpr int kRecBytes = kBM * 48;               // 6 KB of records ...
+constexpr int kRStageBytes = kRecBytes + 16;      // ... + unit header {int64 x_cl element offset of the slice, int rows}
 constexpr int kRowStride = kGatherWarps * 4;          // 8 threads per row -> rows handled per pass
 constexpr int kRowsPerThread = kBM / kRowStride;
 constexpr int kSmemLimit = 227 * 1024;
@@ -220,7 +224,13 @@ fwd_sm100_kernel(const FwdParams p) {
         const int gt = s / p.nh, tap = gt % g.K, grp = gt / g.K;
         const int sr = k % kRStages;
         if (!ptx::mbar_wait(r_empty(sr), ((k / kRStages) & 1) ^ 1, abort_flag, 200)) break;
-        const uint32_t bytes = (uint32_t)min(kBM, g.V - v0) * 48u;
+        const int rows = min(kBM, g.V - v0), h = s % p.nh;
+        // unit header for the gather warps (no index arithmetic there); ordered before their reads by the
+        // release of the arrive below and the acquire of their wait
+        uint8_t* hdr = base_ptr + rec_off + sr * kRStageBytes + kRecBytes;
+        *reinterpret_cast<long long*>(hdr) = (long long)b * g.Vin * g.Cin + grp * g.cpg + h * kBK;
+        *reinterpret_cast<int*>(hdr + 8) = rows;
+        const uint32_t bytes = (uint32_t)rows * 48u;
         ptx::mbar_arrive_expect_tx(r_full(sr), bytes);
         ptx::bulk_g2s(rec_base + sr * kRStageBytes, p.recs + 3 * ((((long long)b * g.G + grp) * g.K + tap) * g.V + v0),
                       bytes, r_full(sr));
@@ -244,21 +254,20 @@ fwd_sm100_kernel(const FwdParams p) {
       row_dst[i] = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((j ^ (r & 7)) << 4));
     }
     uint32_t k = 0;
-    for (long long u = u_beg; u < u_end; ++u, ++k) {
-      const int tile = (int)(u / p.S), s = (int)(u % p.S);
-      const int b = tile / p.tiles_per_clip, v0 = (tile % p.tiles_per_clip) * kBM;
-      const int h = s % p.nh, grp = (s / p.nh) / g.K;
+    const uint32_t n_my_units = (uint32_t)(u_end - u_beg);
+    for (; k < n_my_units; ++k) {
       const int sr = k % kRStages, sa = k % kAStages;
       if (!ptx::mbar_wait(r_full(sr), (k / kRStages) & 1, abort_flag)) break;
       const uint8_t* rec_stage = base_ptr + rec_off + sr * kRStageBytes;
-      const __half* xb = p.x_cl + (long long)b * g.Vin * g.Cin + grp * g.cpg + h * kBK + j * 8;
+      const __half* xb = p.x_cl + *reinterpret_cast<const long long*>(rec_stage + kRecBytes) + j * 8;
+      const int rows = *reinterpret_cast<const int*>(rec_stage + kRecBytes + 8);
       // every corner of every row this thread owns goes in flight before the first blend
       uint4 c[kRowsPerThread][8];
 #pragma unroll
       for (int i = 0; i < kRowsPerThread; ++i) {
         const int r = r0 + kRowStride * i;
         uint2 head = make_uint2(0u, 0u);
-        if (v0 + r < g.V) head = *reinterpret_cast<const uint2*>(rec_stage + r * 48);
+        if (r < rows) head = *reinterpret_cast<const uint2*>(rec_stage + r * 48);
         load_corners(xb, p.cs, head.x, head.y, c[i]);
       }
       if (!ptx::mbar_wait(a_empty(sa), ((k / kAStages) & 1) ^ 1, abort_flag)) break;
@@ -267,7 +276,7 @@ fwd_sm100_kernel(const FwdParams p) {
       for (int i = 0; i < kRowsPerThread; ++i) {
         const int r = r0 + kRowStride * i;
         uint4 w03 = make_uint4(0u, 0u, 0u, 0u), w47 = w03;   // rows past the clip end: stage bytes are stale
-        if (v0 + r < g.V) {
+        if (r < rows) {
           w03 = *reinterpret_cast<const uint4*>(rec_stage + r * 48 + 16);
           w47 = *reinterpret_cast<const uint4*>(rec_stage + r * 48 + 32);
         }
@@ -291,6 +300,8 @@ fwd_sm100_kernel(const FwdParams p) {
     ptx::tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
   }
 }
+
+#include "deform_sm100_fwd_pair.cuh"
 
 // ---- staging kernels -------------------------------------------------------------------------
 
@@ -379,7 +390,44 @@ int run_fwd(const Geom& g, const Coords& coords, const float* x, const float* ma
   long long grid = n_units / kMinUnitsPerCta;
   if (grid > sm_count) grid = sm_count;
   if (grid < 1) grid = 1;
-  const bool whole_tiles_only = (pl.n_tiles % grid == 0);
+  bool whole_tiles_only = (pl.n_tiles % grid == 0);
+
+  // CTA pairs (deform_sm100_fwd_pair.cuh) whenever there are at least two tiles and the device can co-schedule
+  // clusters of 2 with this kernel's shared memory.  Opt-in (D2C_SM100_PAIR=1): measured slower than the
+  // single-CTA kernel so far.
+  const int n_tile_pairs = (pl.n_tiles + 1) / 2;
+  const long long n_pair_units = (long long)n_tile_pairs * pl.S;
+  int pair_b_stages = (kSmemLimit - 1024 - 256 - kAStages * kAStageBytes - kRStages * kRStageBytes) / (pl.b_stage_bytes / 2);
+  if (pair_b_stages > 4) pair_b_stages = 4;
+  const int pair_smem = kAStages * kAStageBytes + pair_b_stages * (pl.b_stage_bytes / 2) + kRStages * kRStageBytes + 256 + 1024;
+  long long pair_clusters = 0;
+  {
+    static int pair_enabled = -1;
+    if (pair_enabled < 0) {
+      const char* e = getenv("D2C_SM100_PAIR");
+      pair_enabled = (e && e[0] == '1') ? 1 : 0;
+    }
+    if (pair_enabled && pl.n_tiles >= 2 && pair_b_stages >= 2) {
+      D2C_CUDA_TRY(cudaFuncSetAttribute(pair::fwd_sm100_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pair_smem));
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(2 * (unsigned)sm_count, 1, 1);
+      cfg.blockDim = dim3(kThreads, 1, 1);
+      cfg.dynamicSmemBytes = (size_t)pair_smem;
+      cudaLaunchAttribute attr;
+      attr.id = cudaLaunchAttributeClusterDimension;
+      attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+      cfg.attrs = &attr; cfg.numAttrs = 1;
+      int max_clusters = 0;
+      if (cudaOccupancyMaxActiveClusters(&max_clusters, pair::fwd_sm100_pair_kernel, &cfg) == cudaSuccess && max_clusters > 0) {
+        pair_clusters = n_pair_units / kMinUnitsPerCta;
+        if (pair_clusters > max_clusters) pair_clusters = max_clusters;
+        if (pair_clusters < 1) pair_clusters = 1;
+        whole_tiles_only = (n_tile_pairs % pair_clusters == 0);
+      } else {
+        (void)cudaGetLastError();
+      }
+    }
+  }
 
   prof_mark(st, "fwd_stage_operands");
   {
@@ -400,6 +448,17 @@ int run_fwd(const Geom& g, const Coords& coords, const float* x, const float* ma
   p.n_units = n_units;
   p.b_stages = pl.b_stages; p.b_stage_bytes = pl.b_stage_bytes; p.tmem_cols = pl.tmem_cols;
 
+  if (pair_clusters > 0) {
+    pair::PairParams pp;
+    pp.f = p;
+    pp.n_tile_pairs = n_tile_pairs; pp.n_pair_units = n_pair_units;
+    pp.b_stages = pair_b_stages; pp.b_half_bytes = pl.b_stage_bytes / 2;
+    prof_mark(st, "fwd_sm100_fused");
+    pair::fwd_sm100_pair_kernel<<<(unsigned)(2 * pair_clusters), kThreads, pair_smem, st>>>(pp);
+    D2C_LAUNCH_CHECK();
+    prof_mark(st, nullptr);
+    return D2C_OK;
+  }
   D2C_CUDA_TRY(cudaFuncSetAttribute(fwd_sm100_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes));
   prof_mark(st, "fwd_sm100_fused");
   fwd_sm100_kernel<0><<<(unsigned)grid, kThreads, pl.smem_bytes, st>>>(p);

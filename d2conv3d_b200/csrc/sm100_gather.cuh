@@ -10,10 +10,17 @@
 //
 // Two record streams, both [B][G][K][V]:
 //   pos  float4 {z, y, x, mask}                                    -> sampling-gradient kernel
-//   gat  3 x uint4 (48 B): {voff, valid, -, -}, w0..w3, w4..w7      -> gather producers (forward, dW)
-//        voff  = element offset of corner 000 inside the clip's channels-last staging (no channel term)
-//        valid = bit j set when corner j (order 000..111) contributes to the forward sample
-//        wj    = half2 {a_j*mask, a_j*mask}: trilinear weight x modulation, rounded to fp16, duplicated
+//   gat  3 x uint4 (48 B): {voff, steps, -, -}, w0..w3, w4..w7      -> gather producers (forward, dW)
+//        voff  = element offset (no channel term) of the CLAMPED corner 000 inside the clip's channels-last
+//                staging: per axis the floor index if it is inside the volume, else the ceil index if that is,
+//                else 0
+//        steps = bit 0/1/2 set when the x/y/z neighbour (+1) exists AND the floor index is inside, i.e. when
+//                corner 1 of that axis is a different, readable voxel; otherwise both corners of the axis read
+//                the same (readable) voxel
+//        wj    = half2 {a_j*mask, a_j*mask}: trilinear weight x modulation, rounded to fp16, duplicated; ZERO
+//                for every corner that does not contribute to the forward sample
+//   so a producer issues 8 unconditional loads of readable addresses and lets the zero weights discard the
+//   stand-ins (the staging is saturated fp16, hence finite, so 0 x stand-in = 0): no predicate, no zero-fill.
 #pragma once
 
 #include <cuda_fp16.h>
@@ -54,9 +61,23 @@ sample_records_kernel(Geom g, Coords coords, const float* __restrict__ mask, flo
 #pragma unroll
     for (int j = 0; j < 8; ++j) w[j] = h2_bits(__float2half2_rn(a[j] * m));
     const unsigned valid = s.inside ? s.valid : 0u;
-    const int voff = ((s.z0 * g.H + s.y0) * g.W + s.x0) * g.Cin;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (!((valid >> j) & 1u)) w[j] = 0u;
+    int cz, cy, cx;
+    unsigned steps = 0;
+    {
+      const bool z0ok = s.z0 >= 0 && s.z0 < g.D, z1ok = s.z0 + 1 >= 0 && s.z0 + 1 < g.D;
+      const bool y0ok = s.y0 >= 0 && s.y0 < g.H, y1ok = s.y0 + 1 >= 0 && s.y0 + 1 < g.H;
+      const bool x0ok = s.x0 >= 0 && s.x0 < g.W, x1ok = s.x0 + 1 >= 0 && s.x0 + 1 < g.W;
+      cz = z0ok ? s.z0 : (z1ok ? s.z0 + 1 : 0);
+      cy = y0ok ? s.y0 : (y1ok ? s.y0 + 1 : 0);
+      cx = x0ok ? s.x0 : (x1ok ? s.x0 + 1 : 0);
+      steps = (x0ok && x1ok ? 1u : 0u) | (y0ok && y1ok ? 2u : 0u) | (z0ok && z1ok ? 4u : 0u);
+    }
+    const int voff = ((cz * g.H + cy) * g.W + cx) * g.Cin;
     uint4* o = gat + 3 * i;
-    o[0] = make_uint4((uint32_t)voff, valid, 0u, 0u);
+    o[0] = make_uint4((uint32_t)voff, steps, 0u, 0u);
     o[1] = make_uint4(w[0], w[1], w[2], w[3]);
     o[2] = make_uint4(w[4], w[5], w[6], w[7]);
   }
@@ -84,50 +105,24 @@ struct ClStrides {
   int dz, dy, dx;   // H*W*Cin, W*Cin, Cin
 };
 
-// One A-tile item: the 8 channels [ch0, ch0+8) of the modulated trilinear sample described by `r`,
-// blended in packed fp16 (the weights already carry the modulation), converted to bf16 and stored
-// (16 bytes) at shared-memory address `dst`.   xb: channels-last fp16 staging of the clip ([Vin][Cin]).
-// Corners that do not contribute are not loaded.
-__device__ __forceinline__ void produce_item(const __half* __restrict__ xb, ClStrides cs, const GatherRec& r,
-                                             int ch0, uint32_t dst) {
-  const unsigned valid = r.head.y;
-  const int off0 = (int)r.head.x + ch0;
-  uint4 c[8];
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const int off = off0 + (j >> 2) * cs.dz + ((j >> 1) & 1) * cs.dy + (j & 1) * cs.dx;
-    c[j] = ((valid >> j) & 1u) ? ptx::ldg_nc_v4(xb + off) : make_uint4(0u, 0u, 0u, 0u);
-  }
-  const uint32_t w[8] = {r.w03.x, r.w03.y, r.w03.z, r.w03.w, r.w47.x, r.w47.y, r.w47.z, r.w47.w};
-  __half2 acc[4];
-#pragma unroll
-  for (int e = 0; e < 4; ++e) acc[e] = __float2half2_rn(0.f);
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {   // corner order 000..111, as the reference's interpolation chain
-    const __half2 wj = bits_h2(w[j]);
-    acc[0] = __hfma2(bits_h2(c[j].x), wj, acc[0]);
-    acc[1] = __hfma2(bits_h2(c[j].y), wj, acc[1]);
-    acc[2] = __hfma2(bits_h2(c[j].z), wj, acc[2]);
-    acc[3] = __hfma2(bits_h2(c[j].w), wj, acc[3]);
-  }
-  uint4 out;
-  float2 f;
-  f = __half22float2(acc[0]); out.x = ptx::pack_bf16x2(f.x, f.y);
-  f = __half22float2(acc[1]); out.y = ptx::pack_bf16x2(f.x, f.y);
-  f = __half22float2(acc[2]); out.z = ptx::pack_bf16x2(f.x, f.y);
-  f = __half22float2(acc[3]); out.w = ptx::pack_bf16x2(f.x, f.y);
-  ptx::sts_v4(dst, out);
-}
-
-// The same work split in two so that a producer can put the corners of several items in flight before the
-// first blend: load_corners issues the (up to) 8 corner loads of one item, blend_store consumes them.
+// One A-tile item = the 8 channels [ch0, ch0+8) of one modulated trilinear sample, blended in packed fp16
+// (the weights already carry the modulation), converted to bf16 and stored (16 bytes) in the swizzled A tile.
+// The work is split in two so that a producer can put the corners of several items in flight before the first
+// blend: load_corners issues the 8 corner loads of one item (all unconditional, see the record format above),
+// blend_store consumes them.   xb_ch: channels-last fp16 staging of the clip, advanced to the item's channel.
 __device__ __forceinline__ void load_corners(const __half* __restrict__ xb_ch, ClStrides cs, uint32_t voff,
-                                             uint32_t valid, uint4 (&c)[8]) {
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const int off = (int)voff + (j >> 2) * cs.dz + ((j >> 1) & 1) * cs.dy + (j & 1) * cs.dx;
-    c[j] = ((valid >> j) & 1u) ? ptx::ldg_nc_v4(xb_ch + off) : make_uint4(0u, 0u, 0u, 0u);
-  }
+                                             uint32_t steps, uint4 (&c)[8]) {
+  const int dx = (steps & 1u) ? cs.dx : 0, dy = (steps & 2u) ? cs.dy : 0, dz = (steps & 4u) ? cs.dz : 0;
+  const __half* p0 = xb_ch + voff;
+  const __half* p1 = p0 + dz;
+  c[0] = ptx::ldg_nc_v4(p0);
+  c[1] = ptx::ldg_nc_v4(p0 + dx);
+  c[2] = ptx::ldg_nc_v4(p0 + dy);
+  c[3] = ptx::ldg_nc_v4(p0 + dy + dx);
+  c[4] = ptx::ldg_nc_v4(p1);
+  c[5] = ptx::ldg_nc_v4(p1 + dx);
+  c[6] = ptx::ldg_nc_v4(p1 + dy);
+  c[7] = ptx::ldg_nc_v4(p1 + dy + dx);
 }
 
 __device__ __forceinline__ void blend_store(const uint4 (&c)[8], uint4 w03, uint4 w47, uint32_t dst) {
@@ -152,8 +147,15 @@ __device__ __forceinline__ void blend_store(const uint4 (&c)[8], uint4 w03, uint
   ptx::sts_v4(dst, out);
 }
 
+__device__ __forceinline__ void produce_item(const __half* __restrict__ xb, ClStrides cs, const GatherRec& r,
+                                             int ch0, uint32_t dst) {
+  uint4 c[8];
+  load_corners(xb + ch0, cs, r.head.x, r.head.y, c);
+  blend_store(c, r.w03, r.w47, dst);
+}
+
 // Gather records of the kRows rows (r0, r0+kStride, ...) a gather thread owns in the tile starting at voxel
-// v0.  Rows past the end of the clip get an all-zero record (no corner contributes -> a zero row).
+// v0.  Rows past the end of the clip get an all-zero record (zero weights -> a zero row).
 template <int kRows, int kStride>
 __device__ __forceinline__ void load_row_records(const uint4* __restrict__ gat, const Geom& g, int b, int grp,
                                                  int tap, int v0, int r0, GatherRec (&out)[kRows]) {
