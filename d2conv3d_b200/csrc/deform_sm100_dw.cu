@@ -25,8 +25,11 @@ constexpr int kAStages = 2;
 constexpr int kAStageBytes = 2 * kTileBytes;         // two slices
 constexpr int kBStages = 2;
 constexpr int kChunkBytes = 256 * 128;               // one 256-row (co) x 64-voxel image
-constexpr int kThreads = (6 + 16) * 32;   // 4 epilogue + MMA + loader + 16 gather warps
-constexpr int kEpiWarps = 4, kMmaWarp = 4, kLoadWarp = 5, kGatherWarp0 = 6, kGatherWarps = 16;
+constexpr int kThreads = (6 + 16 + 1) * 32;   // 4 epilogue + MMA + grad_out loader + 16 gather + record loader warps
+constexpr int kEpiWarps = 4, kMmaWarp = 4, kLoadWarp = 5, kGatherWarp0 = 6, kGatherWarps = 16, kRecWarp = 22;
+constexpr int kRStages = 4;                       // gather-record ring, one stage per (tile, slice) half-unit
+constexpr int kRecBytes = kBM * 48;               // 6 KB of records ...
+constexpr int kRStageBytes = kRecBytes + 16;      // ... + header {int64 x_cl element offset of the slice, int rows}
 constexpr int kRowStride = kGatherWarps * 4;          // 8 threads per row -> rows handled per pass
 constexpr int kRowsPerThread = kBM / kRowStride;
 constexpr int kSmemLimit = 227 * 1024;
@@ -77,13 +80,16 @@ dw_sm100_kernel(const DwParams p) {
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - raw);
   const uint32_t a_base = base, b_base = base + kAStages * kAStageBytes;
-  const int bar_off = kAStages * kAStageBytes + kBStages * p.b_stage_bytes;
-  const uint32_t bar_base = base + bar_off;
+  const int rec_off = kAStages * kAStageBytes + kBStages * p.b_stage_bytes;
+  const int bar_off = rec_off + kRStages * kRStageBytes;
+  const uint32_t rec_base = base + rec_off, bar_base = base + bar_off;
   auto a_full = [&](int s) { return bar_base + 8u * s; };
   auto a_empty = [&](int s) { return bar_base + 8u * (2 + s); };
   auto b_full = [&](int s) { return bar_base + 8u * (4 + s); };
   auto b_empty = [&](int s) { return bar_base + 8u * (6 + s); };
   const uint32_t acc_full = bar_base + 8u * 8;
+  auto r_full = [&](int s) { return bar_base + 8u * (10 + s); };
+  auto r_empty = [&](int s) { return bar_base + 8u * (10 + kRStages + s); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + bar_off + 8 * 9);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + bar_off + 8 * 9 + 4);
 
@@ -97,6 +103,7 @@ dw_sm100_kernel(const DwParams p) {
   if (threadIdx.x == 0) {
     for (int s = 0; s < kAStages; ++s) { ptx::mbar_init(a_full(s), kGatherWarps); ptx::mbar_init(a_empty(s), 1); }
     for (int s = 0; s < kBStages; ++s) { ptx::mbar_init(b_full(s), 1); ptx::mbar_init(b_empty(s), 1); }
+    for (int s = 0; s < kRStages; ++s) { ptx::mbar_init(r_full(s), 1); ptx::mbar_init(r_empty(s), kGatherWarps); }
     ptx::mbar_init(acc_full, 1);
     *abort_flag = 0;
     ptx::fence_mbar_init();
@@ -188,8 +195,38 @@ dw_sm100_kernel(const DwParams p) {
             if (clock64() - t0 > ptx::kWaitBudgetCycles) break;
         }
       }
+    } else if (warp == kRecWarp) {
+      // ---- gather-record loader: half-units q = 2*t + sl (tile t of the range, slice sl of the pair); the
+      //      records of a half-unit's rows are one contiguous run, copied kRStages half-units ahead together
+      //      with a header that spares the gather warps all index arithmetic
+      if (lane == 0) {
+        const int nq = 2 * n_my_tiles;
+        int q = 0;
+        for (; q < nq; ++q) {
+          const int tile = tile_beg + (q >> 1), sl = q & 1;
+          const int b = tile / p.tiles_per_clip, v0 = (tile % p.tiles_per_clip) * kBM;
+          const int s = min(2 * pair + sl, p.S - 1);    // an odd last slice is produced twice, second copy unused
+          const int h = s % p.nh, gt = s / p.nh, tap = gt % g.K, grp = gt / g.K;
+          const int sr = q % kRStages;
+          if (!ptx::mbar_wait(r_empty(sr), ((q / kRStages) & 1) ^ 1, abort_flag, 200)) break;
+          const int rows = min(kBM, g.V - v0);
+          uint8_t* hdr = base_ptr + rec_off + sr * kRStageBytes + kRecBytes;
+          *reinterpret_cast<long long*>(hdr) = (long long)b * g.Vin * g.Cin + grp * g.cpg + h * kBK;
+          *reinterpret_cast<int*>(hdr + 8) = rows;
+          ptx::mbar_arrive_expect_tx(r_full(sr), (uint32_t)rows * 48u);
+          ptx::bulk_g2s(rec_base + sr * kRStageBytes,
+                        p.recs + 3 * ((((long long)b * g.G + grp) * g.K + tap) * g.V + v0), (uint32_t)rows * 48u,
+                        r_full(sr));
+        }
+        const int issued = q;
+        for (int w = (issued > kRStages ? issued - kRStages : 0); w < issued; ++w) {
+          const long long t0 = clock64();
+          while (!ptx::mbar_try_wait(r_full(w % kRStages), (w / kRStages) & 1))
+            if (clock64() - t0 > ptx::kWaitBudgetCycles) break;
+        }
+      }
     } else {
-      // ---- gather producers: the forward's producer, two slices per stage; records one tile ahead
+      // ---- gather producers: the forward's producer, two slices per stage
       const int tt = threadIdx.x - kGatherWarp0 * 32;
       const int j = tt & 7, r0 = tt >> 3;
       uint32_t row_dst[kRowsPerThread];
@@ -198,42 +235,40 @@ dw_sm100_kernel(const DwParams p) {
         const int r = r0 + kRowStride * i;
         row_dst[i] = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((j ^ (r & 7)) << 4));
       }
-      int grp_[2], tap_[2], ch0_[2];
-#pragma unroll
-      for (int sl = 0; sl < 2; ++sl) {
-        const int s = min(2 * pair + sl, p.S - 1);      // an odd last slice is produced twice, second copy unused
-        const int h = s % p.nh, gt = s / p.nh;
-        tap_[sl] = gt % g.K; grp_[sl] = gt / g.K;
-        ch0_[sl] = grp_[sl] * g.cpg + h * kBK + j * 8;
-      }
-      // half-units q = 2*t + sl (tile t of the range, slice sl of the pair); records one half-unit ahead
-      auto load_q = [&](int q, GatherRec (&out)[kRowsPerThread]) {
-        const int tile = tile_beg + (q >> 1), sl = q & 1;
-        const int b = tile / p.tiles_per_clip, v0 = (tile % p.tiles_per_clip) * kBM;
-        load_row_records<kRowsPerThread, kRowStride>(p.recs, g, b, sl ? grp_[1] : grp_[0], sl ? tap_[1] : tap_[0], v0, r0, out);
-      };
-      GatherRec rec[kRowsPerThread];
-      load_q(0, rec);
       const int nq = 2 * n_my_tiles;
       for (int q = 0; q < nq; ++q) {
-        GatherRec rec_next[kRowsPerThread];
-        if (q + 1 < nq) load_q(q + 1, rec_next);
-        const int t = q >> 1, sl = q & 1, sa = t % kAStages;
-        const int tile = tile_beg + t;
-        const int b = tile / p.tiles_per_clip;
-        if (sl == 0 && !ptx::mbar_wait(a_empty(sa), ((t / kAStages) & 1) ^ 1, abort_flag)) break;
-        const __half* xb = p.x_cl + (long long)b * g.Vin * g.Cin;
-        const uint32_t stage = a_base + sa * kAStageBytes + sl * kTileBytes;
-        const int ch0 = sl ? ch0_[1] : ch0_[0];
+        const int t = q >> 1, sl = q & 1, sa = t % kAStages, sr = q % kRStages;
+        if (!ptx::mbar_wait(r_full(sr), (q / kRStages) & 1, abort_flag)) break;
+        const uint8_t* rec_stage = base_ptr + rec_off + sr * kRStageBytes;
+        const __half* xb = p.x_cl + *reinterpret_cast<const long long*>(rec_stage + kRecBytes) + j * 8;
+        const int rows = *reinterpret_cast<const int*>(rec_stage + kRecBytes + 8);
+        // every corner of every row this thread owns goes in flight before the first blend
+        uint4 c[kRowsPerThread][8];
 #pragma unroll
-        for (int i = 0; i < kRowsPerThread; ++i) produce_item(xb, p.cs, rec[i], ch0, stage + row_dst[i]);
-        if (sl == 1) {
-          ptx::fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(a_full(sa));
+        for (int i = 0; i < kRowsPerThread; ++i) {
+          const int r = r0 + kRowStride * i;
+          uint2 head = make_uint2(0u, 0u);
+          if (r < rows) head = *reinterpret_cast<const uint2*>(rec_stage + r * 48);
+          load_corners(xb, p.cs, head.x, head.y, c[i]);
         }
+        if (sl == 0 && !ptx::mbar_wait(a_empty(sa), ((t / kAStages) & 1) ^ 1, abort_flag)) break;
+        const uint32_t stage = a_base + sa * kAStageBytes + sl * kTileBytes;
 #pragma unroll
-        for (int i = 0; i < kRowsPerThread; ++i) rec[i] = rec_next[i];
+        for (int i = 0; i < kRowsPerThread; ++i) {
+          const int r = r0 + kRowStride * i;
+          uint4 w03 = make_uint4(0u, 0u, 0u, 0u), w47 = w03;   // rows past the clip end: stage bytes are stale
+          if (r < rows) {
+            w03 = *reinterpret_cast<const uint4*>(rec_stage + r * 48 + 16);
+            w47 = *reinterpret_cast<const uint4*>(rec_stage + r * 48 + 32);
+          }
+          blend_store(c[i], w03, w47, stage + row_dst[i]);
+        }
+        if (sl == 1) ptx::fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (sl == 1) ptx::mbar_arrive(a_full(sa));
+          ptx::mbar_arrive(r_empty(sr));
+        }
       }
     }
   }
@@ -287,7 +322,7 @@ bool make_dw_plan(const Geom& g, int sm_count, DwPlan* dp) {
   dp->n_pairs = (dp->S + 1) / 2;
   dp->NCH = (g.Cout + 255) / 256;
   dp->b_stage_bytes = dp->NCH * kChunkBytes;
-  dp->smem_bytes = kAStages * kAStageBytes + kBStages * dp->b_stage_bytes + 256 + 1024;
+  dp->smem_bytes = kAStages * kAStageBytes + kBStages * dp->b_stage_bytes + kRStages * kRStageBytes + 256 + 1024;
   if (dp->smem_bytes > kSmemLimit) return false;
   // enough (pair, voxel-range) work items for ~3 waves, but at least 8 tiles per item
   int nsplit = (3 * sm_count + dp->n_pairs - 1) / dp->n_pairs;
