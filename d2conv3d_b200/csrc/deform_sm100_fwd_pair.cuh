@@ -209,8 +209,12 @@ fwd_sm100_pair_kernel(const PairParams pp) {
         const int gt = s / p.nh, tap = gt % g.K, grp = gt / g.K;
         const int sr = k % kRStages;
         if (!ptx::mbar_wait(r_empty(sr), ((k / kRStages) & 1) ^ 1, abort_flag, 200)) break;
+        const int rows = tile_ok ? min(kBM, g.V - v0) : 0;
+        uint8_t* hdr = base_ptr + rec_off + sr * kRStageBytes + kRecBytes;
+        *reinterpret_cast<long long*>(hdr) = (long long)b * g.Vin * g.Cin + grp * g.cpg + (s % p.nh) * kBK;
+        *reinterpret_cast<int*>(hdr + 8) = rows;
         if (tile_ok) {
-          const uint32_t bytes = (uint32_t)min(kBM, g.V - v0) * 48u;
+          const uint32_t bytes = (uint32_t)rows * 48u;
           ptx::mbar_arrive_expect_tx(r_full(sr), bytes);
           ptx::bulk_g2s(rec_base + sr * kRStageBytes,
                         p.recs + 3 * ((((long long)b * g.G + grp) * g.K + tap) * g.V + v0), bytes, r_full(sr));
@@ -236,21 +240,21 @@ fwd_sm100_pair_kernel(const PairParams pp) {
       const int r = r0 + kRowStride * i;
       row_dst[i] = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((j ^ (r & 7)) << 4));
     }
-    uint32_t k = 0;
-    for (long long u = u_beg; u < u_end; ++u, ++k) {
-      int s, b, v0; bool tile_ok;
-      unit_tile(u, s, b, v0, tile_ok);
-      const int h = s % p.nh, grp = (s / p.nh) / g.K;
+    const uint32_t a_full_leader[kAStages] = {ptx::mapa_shared(a_full(0), 0), ptx::mapa_shared(a_full(1), 0),
+                                              ptx::mapa_shared(a_full(2), 0), ptx::mapa_shared(a_full(3), 0)};
+    const uint32_t n_my_units = (uint32_t)(u_end - u_beg);
+    for (uint32_t k = 0; k < n_my_units; ++k) {
       const int sr = k % kRStages, sa = k % kAStages;
       if (!ptx::mbar_wait(r_full(sr), (k / kRStages) & 1, abort_flag)) break;
       const uint8_t* rec_stage = base_ptr + rec_off + sr * kRStageBytes;
-      const __half* xb = p.x_cl + (long long)b * g.Vin * g.Cin + grp * g.cpg + h * kBK + j * 8;
+      const __half* xb = p.x_cl + *reinterpret_cast<const long long*>(rec_stage + kRecBytes) + j * 8;
+      const int rows = *reinterpret_cast<const int*>(rec_stage + kRecBytes + 8);
       uint4 c[kRowsPerThread][8];
 #pragma unroll
       for (int i = 0; i < kRowsPerThread; ++i) {
         const int r = r0 + kRowStride * i;
         uint2 head = make_uint2(0u, 0u);
-        if (tile_ok && v0 + r < g.V) head = *reinterpret_cast<const uint2*>(rec_stage + r * 48);
+        if (r < rows) head = *reinterpret_cast<const uint2*>(rec_stage + r * 48);
         load_corners(xb, p.cs, head.x, head.y, c[i]);
       }
       if (!ptx::mbar_wait_cluster(a_empty(sa), ((k / kAStages) & 1) ^ 1, abort_flag)) break;
@@ -259,7 +263,7 @@ fwd_sm100_pair_kernel(const PairParams pp) {
       for (int i = 0; i < kRowsPerThread; ++i) {
         const int r = r0 + kRowStride * i;
         uint4 w03 = make_uint4(0u, 0u, 0u, 0u), w47 = w03;
-        if (tile_ok && v0 + r < g.V) {
+        if (r < rows) {
           w03 = *reinterpret_cast<const uint4*>(rec_stage + r * 48 + 16);
           w47 = *reinterpret_cast<const uint4*>(rec_stage + r * 48 + 32);
         }
@@ -268,7 +272,7 @@ fwd_sm100_pair_kernel(const PairParams pp) {
       ptx::fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
-        ptx::mbar_arrive_cluster(ptx::mapa_shared(a_full(sa), 0));
+        ptx::mbar_arrive_cluster(a_full_leader[sa]);
         ptx::mbar_arrive(r_empty(sr));
       }
     }
