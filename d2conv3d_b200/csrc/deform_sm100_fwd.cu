@@ -55,7 +55,7 @@ __device__ int g_sm100_status = 0;   // sticky: set when a bounded wait gave up
 
 struct FwdParams {
   Geom g;
-  const __half* x_cl;          // [B][Vin][Cin] fp16 (channels-last staging of x)
+  const void* x_cl;            // [B][Vin][Cin] channels-last staging of x: fp16 (bf16 mode) or fp32 (bf16x3 mode)
   const uint8_t* w_sw;         // [S][N rows x 128 B], rows swizzled exactly as the smem B tile
   const uint4* recs;           // [B][G][K][V] gather records (3 x uint4 each, sm100_gather.cuh)
   const float* bias;           // [Cout] or nullptr
@@ -75,9 +75,14 @@ __device__ __forceinline__ void cta_unit_range(long long n_units, long long& beg
   end = n_units * (blockIdx.x + 1) / gridDim.x;
 }
 
-template <int kDummy>
+// kX3 = 0: math mode bf16 (a unit is 64 channels of one tap, one bf16 operand pair).
+// kX3 = 1: math mode bf16x3, the fp32-parity mode: a unit is 32 channels; the A row holds [hi(32) | lo(32)] of
+//          the fp32 blend, the weight row [hi(32) | lo(32)] of the fp32 weight, and the issuer forms
+//          a_hi*b_hi + a_lo*b_hi + a_hi*b_lo from the 16-channel K sub-blocks of the same two tiles.
+template <int kX3>
 __global__ void __launch_bounds__(kThreads, 1)
 fwd_sm100_kernel(const FwdParams p) {
+  constexpr int kUnitCh = kX3 ? 32 : 64;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = ptx::smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -176,13 +181,18 @@ fwd_sm100_kernel(const FwdParams p) {
           if (!ptx::mbar_wait(b_full(sb), (k / p.b_stages) & 1, abort_flag)) { ok = false; break; }
           ptx::tc_fence_after();
           const uint64_t adesc = ptx::umma_desc_kmajor_sw128(a_base + sa * kAStageBytes);
+          // K sub-blocks (16 channels = 32 bytes) of the A and B rows that meet in each MMA
+          constexpr int kSteps = kX3 ? 6 : 4;
+          constexpr int ka_[6] = {0, 1, kX3 ? 2 : 2, kX3 ? 3 : 3, 0, 1};   // bf16: (k,k); x3: hi*hi, lo*hi, hi*lo
+          constexpr int kb_[6] = {0, 1, kX3 ? 0 : 2, kX3 ? 1 : 3, 2, 3};
 #pragma unroll
-          for (int kk = 0; kk < kBK / 16; ++kk) {
+          for (int kk = 0; kk < kSteps; ++kk) {
             for (int n0 = 0; n0 < p.N; n0 += 256) {
               const int nc = min(256, p.N - n0);
               const uint64_t bdesc = ptx::umma_desc_kmajor_sw128(b_base + sb * p.b_stage_bytes + n0 * 128);
-              ptx::umma_bf16(tmem_base + (uint32_t)n0, adesc + (uint64_t)(2 * kk), bdesc + (uint64_t)(2 * kk),
-                             ptx::umma_idesc_bf16_f32(kBM, nc), (s > s_beg || kk > 0) ? 1u : 0u);
+              ptx::umma_bf16(tmem_base + (uint32_t)n0, adesc + (uint64_t)(2 * ka_[kk]),
+                             bdesc + (uint64_t)(2 * kb_[kk]), ptx::umma_idesc_bf16_f32(kBM, nc),
+                             (s > s_beg || kk > 0) ? 1u : 0u);
             }
           }
           ptx::umma_commit(a_empty(sa));
@@ -228,7 +238,7 @@ fwd_sm100_kernel(const FwdParams p) {
         // unit header for the gather warps (no index arithmetic there); ordered before their reads by the
         // release of the arrive below and the acquire of their wait
         uint8_t* hdr = base_ptr + rec_off + sr * kRStageBytes + kRecBytes;
-        *reinterpret_cast<long long*>(hdr) = (long long)b * g.Vin * g.Cin + grp * g.cpg + h * kBK;
+        *reinterpret_cast<long long*>(hdr) = (long long)b * g.Vin * g.Cin + grp * g.cpg + h * kUnitCh;
         *reinterpret_cast<int*>(hdr + 8) = rows;
         const uint32_t bytes = (uint32_t)rows * 48u;
         ptx::mbar_arrive_expect_tx(r_full(sr), bytes);
@@ -259,7 +269,7 @@ fwd_sm100_kernel(const FwdParams p) {
       const int sr = k % kRStages, sa = k % kAStages;
       if (!ptx::mbar_wait(r_full(sr), (k / kRStages) & 1, abort_flag)) break;
       const uint8_t* rec_stage = base_ptr + rec_off + sr * kRStageBytes;
-      const __half* xb = p.x_cl + *reinterpret_cast<const long long*>(rec_stage + kRecBytes) + j * 8;
+      const long long xoff = *reinterpret_cast<const long long*>(rec_stage + kRecBytes);
       const int rows = *reinterpret_cast<const int*>(rec_stage + kRecBytes + 8);
       // every corner of every row this thread owns goes in flight before the first blend
       uint4 c[kRowsPerThread][8];
@@ -268,19 +278,39 @@ fwd_sm100_kernel(const FwdParams p) {
         const int r = r0 + kRowStride * i;
         uint2 head = make_uint2(0u, 0u);
         if (r < rows) head = *reinterpret_cast<const uint2*>(rec_stage + r * 48);
-        load_corners(xb, p.cs, head.x, head.y, c[i]);
+        if constexpr (kX3)
+          load_corners_f32(reinterpret_cast<const float*>(p.x_cl) + xoff + j * 4, p.cs, head.x, head.y, c[i]);
+        else
+          load_corners(reinterpret_cast<const __half*>(p.x_cl) + xoff + j * 8, p.cs, head.x, head.y, c[i]);
       }
       if (!ptx::mbar_wait(a_empty(sa), ((k / kAStages) & 1) ^ 1, abort_flag)) break;
       const uint32_t stage = a_base + sa * kAStageBytes;
 #pragma unroll
       for (int i = 0; i < kRowsPerThread; ++i) {
         const int r = r0 + kRowStride * i;
-        uint4 w03 = make_uint4(0u, 0u, 0u, 0u), w47 = w03;   // rows past the clip end: stage bytes are stale
-        if (r < rows) {
-          w03 = *reinterpret_cast<const uint4*>(rec_stage + r * 48 + 16);
-          w47 = *reinterpret_cast<const uint4*>(rec_stage + r * 48 + 32);
+        if constexpr (kX3) {
+          float w[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};   // rows past the clip end: stage bytes are stale
+          if (r < rows) {
+            const uint2 w01 = *reinterpret_cast<const uint2*>(rec_stage + r * 48 + 8);
+            const uint4 w25 = *reinterpret_cast<const uint4*>(rec_stage + r * 48 + 16);
+            const uint2 w67 = *reinterpret_cast<const uint2*>(rec_stage + r * 48 + 32);
+            w[0] = __uint_as_float(w01.x); w[1] = __uint_as_float(w01.y);
+            w[2] = __uint_as_float(w25.x); w[3] = __uint_as_float(w25.y);
+            w[4] = __uint_as_float(w25.z); w[5] = __uint_as_float(w25.w);
+            w[6] = __uint_as_float(w67.x); w[7] = __uint_as_float(w67.y);
+          }
+          // item j = channels 4j..4j+3: hi in 16-byte chunk j/2 (half j&1), lo in chunk 4 + j/2
+          const uint32_t row_base = stage + (uint32_t)((r >> 3) * 1024 + (r & 7) * 128) + (uint32_t)((j & 1) * 8);
+          blend_split_store(c[i], w, row_base + ((((j >> 1)) ^ (r & 7)) << 4),
+                            row_base + (((4 + (j >> 1)) ^ (r & 7)) << 4));
+        } else {
+          uint4 w03 = make_uint4(0u, 0u, 0u, 0u), w47 = w03;   // rows past the clip end: stage bytes are stale
+          if (r < rows) {
+            w03 = *reinterpret_cast<const uint4*>(rec_stage + r * 48 + 16);
+            w47 = *reinterpret_cast<const uint4*>(rec_stage + r * 48 + 32);
+          }
+          blend_store(c[i], w03, w47, stage + row_dst[i]);
         }
-        blend_store(c[i], w03, w47, stage + row_dst[i]);
       }
       ptx::fence_proxy_async_smem();
       __syncwarp();
@@ -333,18 +363,50 @@ stage_weight_sw128_kernel(int Cout, int Cin, int K, int cpg, int nh, const float
   }
 }
 
+// bf16x3 mode: slice s = (grp*K + tap)*nh + h with nh = cpg/32 holds 32 channels; each row is
+// [hi(32 ch) | lo(32 ch)] where hi = bf16(w), lo = bf16(w - hi); same swizzle.
+__global__ void __launch_bounds__(64)
+stage_weight_sw128_x3_kernel(int Cout, int Cin, int K, int cpg, int nh, const float* __restrict__ w,
+                             uint8_t* __restrict__ w_sw) {
+  extern __shared__ float wrow[];   // [32 channels][K]
+  const int co = blockIdx.x, cblk = blockIdx.y;      // cblk: 32-channel block of Cin
+  const int c0 = cblk * 32;
+  const float* src = w + ((long long)co * Cin + c0) * K;
+  for (int i = threadIdx.x; i < 32 * K; i += 64) wrow[i] = __ldg(src + i);
+  __syncthreads();
+  const int grp = c0 / cpg, h = (c0 % cpg) / 32;
+  for (int item = threadIdx.x; item < K * 8; item += 64) {
+    const int tap = item >> 3, jj = item & 7;        // jj < 4: hi of channels 8jj.., jj >= 4: lo of channels 8(jj-4)..
+    const int cb = (jj & 3) * 8;
+    float v[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float f = wrow[(cb + e) * K + tap];
+      const float hi = ptx::bf16_lo(ptx::pack_bf16x2(f, 0.f));
+      v[e] = (jj < 4) ? f : f - hi;
+    }
+    uint4 out;
+    out.x = ptx::pack_bf16x2(v[0], v[1]); out.y = ptx::pack_bf16x2(v[2], v[3]);
+    out.z = ptx::pack_bf16x2(v[4], v[5]); out.w = ptx::pack_bf16x2(v[6], v[7]);
+    const long long s = ((long long)grp * K + tap) * nh + h;
+    uint8_t* dst = w_sw + s * (long long)Cout * 128 + (long long)(co >> 3) * 1024 + (co & 7) * 128 +
+                   ((jj ^ (co & 7)) << 4);
+    *reinterpret_cast<uint4*>(dst) = out;
+  }
+}
+
 struct Plan {
   int nh, S, tiles_per_clip, n_tiles, b_stages, b_stage_bytes, tmem_cols, smem_bytes;
   size_t x_cl_bytes, w_sw_bytes, rec_bytes;
 };
 
-bool make_plan(const Geom& g, Plan* pl) {
+bool make_plan(const Geom& g, bool x3, Plan* pl) {
   if (g.groups != 1) return false;
   if (g.cpg % kBK != 0) return false;
   if (g.Cout % 64 != 0 || g.Cout > kMaxN) return false;
   if (g.Vin * g.Cin > 0x7fffffffLL) return false;                 // 32-bit element offsets within a clip
   if (g.K * 64 * (int)sizeof(float) > 48 * 1024) return false;    // weight staging kernel's smem
-  pl->nh = g.cpg / kBK;
+  pl->nh = g.cpg / (x3 ? 32 : kBK);
   pl->S = g.G * g.K * pl->nh;
   pl->tiles_per_clip = (g.V + kBM - 1) / kBM;
   pl->n_tiles = pl->tiles_per_clip * g.B;
@@ -357,7 +419,7 @@ bool make_plan(const Geom& g, Plan* pl) {
   while (cols < g.Cout) cols <<= 1;
   pl->tmem_cols = cols;
   pl->smem_bytes = kAStages * kAStageBytes + pl->b_stages * pl->b_stage_bytes + kRStages * kRStageBytes + 256 + 1024;
-  pl->x_cl_bytes = align_up((size_t)g.B * g.Vin * g.Cin * 2, 256);
+  pl->x_cl_bytes = align_up((size_t)g.B * g.Vin * g.Cin * (x3 ? 4 : 2), 256);
   pl->w_sw_bytes = align_up((size_t)pl->S * pl->b_stage_bytes, 256);
   pl->rec_bytes = gather_records_bytes(g);
   return true;
@@ -374,13 +436,16 @@ int sm_count_cached(int* out) {
   return D2C_OK;
 }
 
+inline bool mode_is_x3(int math_mode) { return math_mode != D2C_MATH_BF16; }
+
 template <typename Coords>
-int run_fwd(const Geom& g, const Coords& coords, const float* x, const float* mask, const float* w,
+int run_fwd(const Geom& g, int math_mode, const Coords& coords, const float* x, const float* mask, const float* w,
             const float* bias, float* y, void* ws, cudaStream_t st) {
+  const bool x3 = mode_is_x3(math_mode);
   Plan pl;
-  if (!make_plan(g, &pl)) return D2C_ERR_MODE;
+  if (!make_plan(g, x3, &pl)) return D2C_ERR_MODE;
   uint8_t* wsp = reinterpret_cast<uint8_t*>(ws);
-  __half* x_cl = reinterpret_cast<__half*>(wsp); wsp += pl.x_cl_bytes;
+  void* x_cl = wsp; wsp += pl.x_cl_bytes;
   uint8_t* w_sw = wsp; wsp += pl.w_sw_bytes;
   uint4* recs = reinterpret_cast<uint4*>(wsp);
   int sm_count = 0, rc;
@@ -407,7 +472,7 @@ int run_fwd(const Geom& g, const Coords& coords, const float* x, const float* ma
       const char* e = getenv("D2C_SM100_PAIR");
       pair_enabled = (e && e[0] == '1') ? 1 : 0;
     }
-    if (pair_enabled && pl.n_tiles >= 2 && pair_b_stages >= 2) {
+    if (pair_enabled && !x3 && pl.n_tiles >= 2 && pair_b_stages >= 2) {
       D2C_CUDA_TRY(cudaFuncSetAttribute(pair::fwd_sm100_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pair_smem));
       cudaLaunchConfig_t cfg = {};
       cfg.gridDim = dim3(2 * (unsigned)sm_count, 1, 1);
@@ -432,12 +497,20 @@ int run_fwd(const Geom& g, const Coords& coords, const float* x, const float* ma
   prof_mark(st, "fwd_stage_operands");
   {
     dim3 sgrid((unsigned)((g.Vin + 31) / 32), (unsigned)((g.Cin + 63) / 64), (unsigned)g.B);
-    stage_input_cl_f16_kernel<<<sgrid, 256, 0, st>>>(g.Cin, g.Vin, x, x_cl);
-    D2C_LAUNCH_CHECK();
-    dim3 wgrid((unsigned)g.Cout, (unsigned)(g.Cin / 64));
-    stage_weight_sw128_kernel<<<wgrid, 64, 64 * g.K * sizeof(float), st>>>(g.Cout, g.Cin, g.K, g.cpg, pl.nh, w, w_sw);
-    D2C_LAUNCH_CHECK();
-    if ((rc = launch_sample_records(g, coords, mask, nullptr, recs, st))) return rc;
+    if (x3) {
+      stage_input_cl_f32_kernel<<<sgrid, 256, 0, st>>>(g.Cin, g.Vin, x, reinterpret_cast<float*>(x_cl));
+      D2C_LAUNCH_CHECK();
+      dim3 wgrid((unsigned)g.Cout, (unsigned)(g.Cin / 32));
+      stage_weight_sw128_x3_kernel<<<wgrid, 64, 32 * g.K * sizeof(float), st>>>(g.Cout, g.Cin, g.K, g.cpg, pl.nh, w, w_sw);
+      D2C_LAUNCH_CHECK();
+    } else {
+      stage_input_cl_f16_kernel<<<sgrid, 256, 0, st>>>(g.Cin, g.Vin, x, reinterpret_cast<__half*>(x_cl));
+      D2C_LAUNCH_CHECK();
+      dim3 wgrid((unsigned)g.Cout, (unsigned)(g.Cin / 64));
+      stage_weight_sw128_kernel<<<wgrid, 64, 64 * g.K * sizeof(float), st>>>(g.Cout, g.Cin, g.K, g.cpg, pl.nh, w, w_sw);
+      D2C_LAUNCH_CHECK();
+    }
+    if ((rc = launch_sample_records(g, coords, mask, nullptr, recs, st, x3))) return rc;
     if (!whole_tiles_only) D2C_CUDA_TRY(cudaMemsetAsync(y, 0, sizeof(float) * (size_t)g.B * g.Cout * g.V, st));
   }
 
@@ -459,9 +532,14 @@ int run_fwd(const Geom& g, const Coords& coords, const float* x, const float* ma
     prof_mark(st, nullptr);
     return D2C_OK;
   }
-  D2C_CUDA_TRY(cudaFuncSetAttribute(fwd_sm100_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes));
   prof_mark(st, "fwd_sm100_fused");
-  fwd_sm100_kernel<0><<<(unsigned)grid, kThreads, pl.smem_bytes, st>>>(p);
+  if (x3) {
+    D2C_CUDA_TRY(cudaFuncSetAttribute(fwd_sm100_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes));
+    fwd_sm100_kernel<1><<<(unsigned)grid, kThreads, pl.smem_bytes, st>>>(p);
+  } else {
+    D2C_CUDA_TRY(cudaFuncSetAttribute(fwd_sm100_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes));
+    fwd_sm100_kernel<0><<<(unsigned)grid, kThreads, pl.smem_bytes, st>>>(p);
+  }
   D2C_LAUNCH_CHECK();
   prof_mark(st, nullptr);
   return D2C_OK;
@@ -471,27 +549,27 @@ int run_fwd(const Geom& g, const Coords& coords, const float* x, const float* ma
 
 bool sm100_fwd_supported(const Geom& g, int dtype, int math_mode) {
   if (dtype != D2C_F32) return false;
-  if (math_mode != D2C_MATH_BF16) return false;
+  if (math_mode == D2C_MATH_FP32) return false;
   Plan pl;
-  return make_plan(g, &pl);
+  return make_plan(g, mode_is_x3(math_mode), &pl);
 }
 
 size_t sm100_fwd_workspace(const Geom& g, int dtype, int math_mode) {
   if (!sm100_fwd_supported(g, dtype, math_mode)) return 0;
   Plan pl;
-  make_plan(g, &pl);
+  make_plan(g, mode_is_x3(math_mode), &pl);
   return pl.x_cl_bytes + pl.w_sw_bytes + pl.rec_bytes;
 }
 
-int sm100_fwd_offsets(const Geom& g, int /*math_mode*/, const float* x, const float* offset, const float* mask,
+int sm100_fwd_offsets(const Geom& g, int math_mode, const float* x, const float* offset, const float* mask,
                       const float* w, const float* bias, float* y, void* ws, cudaStream_t st) {
   OffsetCoords<float> oc{offset};
-  return run_fwd(g, oc, x, mask, w, bias, y, ws, st);
+  return run_fwd(g, math_mode, oc, x, mask, w, bias, y, ws, st);
 }
 
-int sm100_fwd_field(const Geom& g, int /*math_mode*/, const FieldCoords<float>& fc, const float* x,
+int sm100_fwd_field(const Geom& g, int math_mode, const FieldCoords<float>& fc, const float* x,
                     const float* mask, const float* w, const float* bias, float* y, void* ws, cudaStream_t st) {
-  return run_fwd(g, fc, x, mask, w, bias, y, ws, st);
+  return run_fwd(g, math_mode, fc, x, mask, w, bias, y, ws, st);
 }
 
 int sm100_device_status() {

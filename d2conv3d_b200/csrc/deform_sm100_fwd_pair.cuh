@@ -247,7 +247,7 @@ fwd_sm100_pair_kernel(const PairParams pp) {
       const int sr = k % kRStages, sa = k % kAStages;
       if (!ptx::mbar_wait(r_full(sr), (k / kRStages) & 1, abort_flag)) break;
       const uint8_t* rec_stage = base_ptr + rec_off + sr * kRStageBytes;
-      const __half* xb = p.x_cl + *reinterpret_cast<const long long*>(rec_stage + kRecBytes) + j * 8;
+      const __half* xb = reinterpret_cast<const __half*>(p.x_cl) + *reinterpret_cast<const long long*>(rec_stage + kRecBytes) + j * 8;
       const int rows = *reinterpret_cast<const int*>(rec_stage + kRecBytes + 8);
       uint4 c[kRowsPerThread][8];
 #pragma unroll

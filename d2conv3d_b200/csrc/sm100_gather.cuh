@@ -42,7 +42,7 @@ __device__ __forceinline__ __half2 bits_h2(uint32_t u) { return *reinterpret_cas
 template <typename Coords>
 static __global__ void __launch_bounds__(256)
 sample_records_kernel(Geom g, Coords coords, const float* __restrict__ mask, float4* __restrict__ pos,
-                      uint4* __restrict__ gat) {
+                      uint4* __restrict__ gat, int f32_weights) {
   const int v = blockIdx.x * 256 + threadIdx.x;
   if (v >= g.V) return;
   const int tap = blockIdx.y % g.K, grp = blockIdx.y / g.K, b = blockIdx.z;
@@ -77,18 +77,28 @@ sample_records_kernel(Geom g, Coords coords, const float* __restrict__ mask, flo
     }
     const int voff = ((cz * g.H + cy) * g.W + cx) * g.Cin;
     uint4* o = gat + 3 * i;
-    o[0] = make_uint4((uint32_t)voff, steps, 0u, 0u);
-    o[1] = make_uint4(w[0], w[1], w[2], w[3]);
-    o[2] = make_uint4(w[4], w[5], w[6], w[7]);
+    if (f32_weights) {
+      // fp32-parity mode: the same 48 bytes hold the eight products a_j*mask in fp32
+      uint32_t f[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = ((valid >> j) & 1u) ? __float_as_uint(a[j] * m) : 0u;
+      o[0] = make_uint4((uint32_t)voff, steps, f[0], f[1]);
+      o[1] = make_uint4(f[2], f[3], f[4], f[5]);
+      o[2] = make_uint4(f[6], f[7], 0u, 0u);
+    } else {
+      o[0] = make_uint4((uint32_t)voff, steps, 0u, 0u);
+      o[1] = make_uint4(w[0], w[1], w[2], w[3]);
+      o[2] = make_uint4(w[4], w[5], w[6], w[7]);
+    }
   }
 }
 
 template <typename Coords>
 static int launch_sample_records(const Geom& g, const Coords& coords, const float* mask, float4* pos, uint4* gat,
-                                 cudaStream_t st) {
+                                 cudaStream_t st, bool f32_weights = false) {
   dim3 grid((unsigned)((g.V + 255) / 256), (unsigned)(g.G * g.K), (unsigned)g.B);
   if (grid.y > 65535 || grid.z > 65535) return D2C_ERR_TOO_LARGE;
-  sample_records_kernel<Coords><<<grid, 256, 0, st>>>(g, coords, mask, pos, gat);
+  sample_records_kernel<Coords><<<grid, 256, 0, st>>>(g, coords, mask, pos, gat, f32_weights ? 1 : 0);
   D2C_LAUNCH_CHECK();
   return D2C_OK;
 }
@@ -152,6 +162,44 @@ __device__ __forceinline__ void produce_item(const __half* __restrict__ xb, ClSt
   uint4 c[8];
   load_corners(xb + ch0, cs, r.head.x, r.head.y, c);
   blend_store(c, r.w03, r.w47, dst);
+}
+
+// ---- fp32-parity mode ("bf16x3"): fp32 staging, fp32 blend, bf16 hi/lo split -------------------------------
+// One item = 4 channels (16 bytes of fp32) of one sample.  The blended value v is written twice into the
+// 128-byte A row of a 32-channel unit: hi = bf16(v) at channel column c, lo = bf16(v - hi) at column 32 + c,
+// so that the MMA issuer can form a_hi*b_hi + a_lo*b_hi + a_hi*b_lo from K sub-blocks of ONE tile pair.
+__device__ __forceinline__ void load_corners_f32(const float* __restrict__ xb_ch, ClStrides cs, uint32_t voff,
+                                                 uint32_t steps, uint4 (&c)[8]) {
+  const int dx = (steps & 1u) ? cs.dx : 0, dy = (steps & 2u) ? cs.dy : 0, dz = (steps & 4u) ? cs.dz : 0;
+  const float* p0 = xb_ch + voff;
+  const float* p1 = p0 + dz;
+  c[0] = ptx::ldg_nc_v4(p0);
+  c[1] = ptx::ldg_nc_v4(p0 + dx);
+  c[2] = ptx::ldg_nc_v4(p0 + dy);
+  c[3] = ptx::ldg_nc_v4(p0 + dy + dx);
+  c[4] = ptx::ldg_nc_v4(p1);
+  c[5] = ptx::ldg_nc_v4(p1 + dx);
+  c[6] = ptx::ldg_nc_v4(p1 + dy);
+  c[7] = ptx::ldg_nc_v4(p1 + dy + dx);
+}
+
+// w: the eight fp32 products a_j*mask (corner order 000..111, the reference's interpolation chain).
+// dst_hi / dst_lo: shared-memory addresses of the 8-byte hi and lo slots of this item.
+__device__ __forceinline__ void blend_split_store(const uint4 (&c)[8], const float (&w)[8], uint32_t dst_hi,
+                                                  uint32_t dst_lo) {
+  float v[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    v[0] = __fmaf_rn(__uint_as_float(c[j].x), w[j], v[0]);
+    v[1] = __fmaf_rn(__uint_as_float(c[j].y), w[j], v[1]);
+    v[2] = __fmaf_rn(__uint_as_float(c[j].z), w[j], v[2]);
+    v[3] = __fmaf_rn(__uint_as_float(c[j].w), w[j], v[3]);
+  }
+  const uint32_t h01 = ptx::pack_bf16x2(v[0], v[1]), h23 = ptx::pack_bf16x2(v[2], v[3]);
+  const uint32_t l01 = ptx::pack_bf16x2(v[0] - ptx::bf16_lo(h01), v[1] - ptx::bf16_hi(h01));
+  const uint32_t l23 = ptx::pack_bf16x2(v[2] - ptx::bf16_lo(h23), v[3] - ptx::bf16_hi(h23));
+  ptx::sts_v2(dst_hi, make_uint2(h01, h23));
+  ptx::sts_v2(dst_lo, make_uint2(l01, l23));
 }
 
 // Gather records of the kRows rows (r0, r0+kStride, ...) a gather thread owns in the tile starting at voxel

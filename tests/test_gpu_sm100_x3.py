@@ -1,0 +1,85 @@
+"""GPU parity tests of the tensor-core tier in its fp32-parity mode ('bf16x3', also what 'auto' selects
+where the tensor-core kernels apply): every fp32 operand is split into bf16 hi + lo, the contraction is
+a_hi*b_hi + a_lo*b_hi + a_hi*b_lo with fp32 accumulation, the trilinear blend is done in fp32 on fp32
+channels-last data.  Bound: the same 1e-4 of the result's scale as the exact fp32 tier (the reference's
+cuBLAS fp32 GEMM and this split differ by ~1e-5)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as orc
+from tests._util import make_problem
+
+pytestmark = pytest.mark.gpu
+
+REL = 1e-4
+
+
+@pytest.fixture(params=["bf16x3", "auto"])
+def dn(request):
+    import d2conv3d_b200
+    from d2conv3d_b200 import _lib, dconv_native
+    _lib.lib()
+    d2conv3d_b200.set_math_mode(request.param)
+    yield dconv_native
+    d2conv3d_b200.set_math_mode("auto")
+    _lib.device_status()     # raises if any bounded device-side wait gave up
+
+
+def cu(a):
+    return None if a is None else torch.from_numpy(a).cuda()
+
+
+CASES = [
+    dict(B=1, Cin=64, Cout=64, dims=(4, 8, 8), G=1),                 # 2 full tiles
+    dict(B=2, Cin=128, Cout=128, dims=(3, 7, 9), G=2),               # ragged last tile, 2 groups
+    dict(B=1, Cin=128, Cout=64, dims=(3, 6, 8), G=1),                # 128 channels per group: 4 units per tap
+    dict(B=1, Cin=64, Cout=512, dims=(2, 8, 9), G=1),                # N = 512: two 256-column MMAs, all of TMEM
+    dict(B=1, Cin=64, Cout=320, dims=(2, 8, 9), G=1),                # N = 256 + 64
+    dict(B=2, Cin=64, Cout=64, dims=(8, 30, 40), G=1),               # 150 tiles: persistent loop wraps
+    dict(B=1, Cin=128, Cout=64, dims=(4, 9, 9), G=2, k=(1, 3, 3), padding=(0, 1, 1)),
+    dict(B=1, Cin=64, Cout=64, dims=(5, 9, 9), G=1, stride=(1, 2, 2), dilation=(2, 1, 1), padding=(2, 1, 1)),
+]
+
+
+@pytest.mark.parametrize("ci", range(len(CASES)))
+def test_forward_fp32_parity_mode_vs_oracle(dn, ci):
+    from d2conv3d_b200 import _lib
+    cfg = dict(CASES[ci])
+    cfg.setdefault("k", 3)
+    cfg.setdefault("padding", 1)
+    p = make_problem(700 + ci, dtype=np.float32, offset_std=2.0, **cfg)
+    kw = dict(stride=p["stride"], padding=p["padding"], dilation=p["dilation"], groups=1, offset_groups=p["offset_groups"])
+    _lib.profile_read(); _lib.profile_enable(True)
+    y = dn.deform_conv3d(cu(p["x"]), cu(p["geo"]), cu(p["mask"]), cu(p["weight"]), cu(p["bias"]), p["stride"],
+                         p["padding"], p["dilation"], 1, p["offset_groups"]).cpu().numpy()
+    _lib.profile_enable(False)
+    phases = [n for n, _ in _lib.profile_read()]
+    assert "fwd_sm100_fused" in phases, f"tensor-core tier was not used: {phases}"
+    want = orc.deform_conv3d_fwd(p["x"].astype(np.float64), p["geo"].astype(np.float64), p["mask"].astype(np.float64),
+                                 p["weight"].astype(np.float64), p["bias"].astype(np.float64), **kw)
+    err = np.abs(y - want).max() / np.abs(want).max()
+    print(f"case {ci}: rel err vs float64 oracle {err:.3e}")
+    assert err <= REL
+
+
+def test_integer_and_border_coordinates(dn):
+    """Offsets that put samples exactly on voxels, on the -1 / size borders and far outside: the clamped
+    stand-in corners must contribute exactly nothing."""
+    p = make_problem(720, 1, 64, 64, (3, 6, 7), padding=1, dtype=np.float32, offset_std=0.0)
+    rng = np.random.default_rng(5)
+    p["geo"][:] = rng.integers(-4, 5, size=p["geo"].shape).astype(np.float32)
+    y = dn.deform_conv3d(cu(p["x"]), cu(p["geo"]), cu(p["mask"]), cu(p["weight"]), cu(p["bias"]), 1, 1, 1).cpu().numpy()
+    want = orc.deform_conv3d_fwd(p["x"], p["geo"], p["mask"], p["weight"], p["bias"], padding=1)
+    assert np.abs(y - want).max() <= REL * np.abs(want).max()
+
+
+@pytest.mark.parametrize("mode", ["x", "xyz"])
+def test_dyn_dilated_fp32_parity_mode(dn, mode):
+    G = 2
+    p = make_problem(730, 2, 128, 64, (4, 9, 10), padding=1, G=G, dtype=np.float32, field_mode=mode)
+    y = dn.dyn_dilated_conv3d(cu(p["x"]), cu(p["geo"]), cu(p["mask"]), cu(p["weight"]), cu(p["bias"]), mode,
+                              1, 1, 1, 1, G).cpu().numpy()
+    want = orc.dyn_dilated_conv3d_fwd(p["x"], p["geo"], p["mask"], p["weight"], p["bias"], mode, padding=1,
+                                      offset_groups=G)
+    assert np.abs(y - want).max() <= REL * np.abs(want).max()
