@@ -269,7 +269,7 @@ int d2c_deform_conv3d_bwd(const d2c_conv_desc* desc, const void* grad_y, const v
   if (sm100_bwd_supported(g, desc->dtype, g_math_mode.load(), cap)) {
     if (!ws_ok(workspace, workspace_bytes, sm100_bwd_workspace(g, desc->dtype, g_math_mode.load(), cap)))
       return D2C_ERR_WORKSPACE;
-    return sm100_bwd_offsets(g, cap, (const float*)grad_y, (const float*)x, (const float*)offset,
+    return sm100_bwd_offsets(g, g_math_mode.load(), cap, (const float*)grad_y, (const float*)x, (const float*)offset,
                              (const float*)mask, (const float*)w, (float*)grad_x, (float*)grad_offset,
                              (float*)grad_mask, (float*)grad_w, (float*)grad_bias, workspace, st);
   }
@@ -367,7 +367,7 @@ int d2c_dyn_dilated_conv3d_bwd(const d2c_conv_desc* desc, int field_mode, const 
     if (sm100_bwd_supported(g, desc->dtype, g_math_mode.load(), cap)) {
       if (!ws_ok(workspace, workspace_bytes, sm100_bwd_workspace(g, desc->dtype, g_math_mode.load(), cap)))
         return D2C_ERR_WORKSPACE;
-      return sm100_bwd_field(g, cap, fc, (const float*)grad_y, (const float*)x, (const float*)mask,
+      return sm100_bwd_field(g, g_math_mode.load(), cap, fc, (const float*)grad_y, (const float*)x, (const float*)mask,
                              (const float*)w, (float*)grad_x, (float*)grad_size_map, gs_elems,
                              (float*)grad_mask, (float*)grad_w, (float*)grad_bias, workspace, st);
     }

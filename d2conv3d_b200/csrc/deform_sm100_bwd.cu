@@ -14,6 +14,8 @@
 // The weight gradient is in deform_sm100_dw.cu; sampling positions come from the records of
 // sm100_gather.cuh, computed once per backward call.
 #include "deform_generic.cuh"   // grad_bias_kernel, bwd_slice_clips
+#include <type_traits>
+
 #include "deform_sm100.h"
 #include "sm100_gather.cuh"
 #include "sm100_ptx.cuh"
@@ -40,26 +42,35 @@ __device__ int g_sm100_bwd_status = 0;
 // grad_out [B][Cout][V] fp32 -> per (tile, 64-wide co block) images of 128 rows (voxels) x 128 B (64 co,
 // bf16), 16-byte chunks XOR-swizzled by (row & 7): the byte image of a K-major SW128 A tile.
 // Rows past the end of the clip are zero.
+// x3 = 1 (fp32-parity mode): a K block is 32 co and a row is [hi(32 co) | lo(32 co)], hi = bf16(g),
+// lo = bf16(g - hi).
+__device__ __forceinline__ float split_part(float f, bool lo) {
+  return lo ? f - ptx::bf16_lo(ptx::pack_bf16x2(f, 0.f)) : f;
+}
+
 __global__ void __launch_bounds__(256)
-stage_gy_img_kernel(int Cout, int V, int tiles_per_clip, int b0, const float* __restrict__ gy,
+stage_gy_img_kernel(int Cout, int V, int tiles_per_clip, int b0, int x3, const float* __restrict__ gy,
                     uint8_t* __restrict__ img) {
   __shared__ float tile[64][129];
   const int tile_id = blockIdx.x, kb = blockIdx.y, KB = gridDim.y;
   const int bl = tile_id / tiles_per_clip, v0 = (tile_id % tiles_per_clip) * kBM;
   const int b = b0 + bl;
-  for (int e = threadIdx.x; e < 64 * 128; e += 256) {
+  const int nco = x3 ? 32 : 64;
+  for (int e = threadIdx.x; e < nco * 128; e += 256) {
     const int co = e >> 7, r = e & 127, v = v0 + r;
-    tile[co][r] = (v < V) ? __ldg(gy + ((long long)b * Cout + kb * 64 + co) * V + v) : 0.f;
+    tile[co][r] = (v < V) ? __ldg(gy + ((long long)b * Cout + kb * nco + co) * V + v) : 0.f;
   }
   __syncthreads();
   uint8_t* dst = img + ((long long)tile_id * KB + kb) * kABlockBytes;
   for (int e = threadIdx.x; e < 128 * 8; e += 256) {
     const int r = e >> 3, j = e & 7;
+    const bool lo = x3 && j >= 4;
+    const int cb = x3 ? (j & 3) * 8 : j * 8;
     uint4 o;
-    o.x = ptx::pack_bf16x2(tile[j * 8 + 0][r], tile[j * 8 + 1][r]);
-    o.y = ptx::pack_bf16x2(tile[j * 8 + 2][r], tile[j * 8 + 3][r]);
-    o.z = ptx::pack_bf16x2(tile[j * 8 + 4][r], tile[j * 8 + 5][r]);
-    o.w = ptx::pack_bf16x2(tile[j * 8 + 6][r], tile[j * 8 + 7][r]);
+    o.x = ptx::pack_bf16x2(split_part(tile[cb + 0][r], lo), split_part(tile[cb + 1][r], lo));
+    o.y = ptx::pack_bf16x2(split_part(tile[cb + 2][r], lo), split_part(tile[cb + 3][r], lo));
+    o.z = ptx::pack_bf16x2(split_part(tile[cb + 4][r], lo), split_part(tile[cb + 5][r], lo));
+    o.w = ptx::pack_bf16x2(split_part(tile[cb + 6][r], lo), split_part(tile[cb + 7][r], lo));
     *reinterpret_cast<uint4*>(dst + (r >> 3) * 1024 + (r & 7) * 128 + ((j ^ (r & 7)) << 4)) = o;
   }
 }
@@ -70,21 +81,24 @@ stage_gy_img_kernel(int Cout, int V, int tiles_per_clip, int b0, const float* __
 // as 64 contiguous runs of K floats into shared memory, then each tap's 64 co values are written as one
 // 128-byte row (8 swizzled 16-byte chunks).
 __global__ void __launch_bounds__(64)
-stage_wt_img_kernel(int Cout, int Cin, int K, int cpg, int nh, const float* __restrict__ w,
+stage_wt_img_kernel(int Cout, int Cin, int K, int cpg, int nh, int x3, const float* __restrict__ w,
                     uint8_t* __restrict__ img) {
-  extern __shared__ float wsm[];                    // [64 co][K]
+  extern __shared__ float wsm[];                    // [64 (x3: 32) co][K]
   const int kb = blockIdx.x, cin = blockIdx.y, KB = gridDim.x;
-  for (int i = threadIdx.x; i < 64 * K; i += 64) {
+  const int nco = x3 ? 32 : 64;
+  for (int i = threadIdx.x; i < nco * K; i += 64) {
     const int q = i / K, t = i - q * K;
-    wsm[i] = __ldg(w + ((long long)(kb * 64 + q) * Cin + cin) * K + t);
+    wsm[i] = __ldg(w + ((long long)(kb * nco + q) * Cin + cin) * K + t);
   }
   __syncthreads();
   const int grp = cin / cpg, h = (cin % cpg) / 64, c = cin & 63;
   for (int item = threadIdx.x; item < K * 8; item += 64) {
     const int tap = item >> 3, j = item & 7;
+    const bool lo = x3 && j >= 4;
+    const int cb = x3 ? (j & 3) * 8 : j * 8;
     float v[8];
 #pragma unroll
-    for (int q = 0; q < 8; ++q) v[q] = wsm[(j * 8 + q) * K + tap];
+    for (int q = 0; q < 8; ++q) v[q] = split_part(wsm[(cb + q) * K + tap], lo);
     uint4 o;
     o.x = ptx::pack_bf16x2(v[0], v[1]); o.y = ptx::pack_bf16x2(v[2], v[3]);
     o.z = ptx::pack_bf16x2(v[4], v[5]); o.w = ptx::pack_bf16x2(v[6], v[7]);
@@ -106,12 +120,18 @@ struct DcolParams {
   const uint8_t* gy_img;   // [n_tiles][KB][16 KB]
   const uint8_t* wt_img;   // [NB][KB][32 KB]
   float* dcol;             // [clips_in_chunk * V][NT]
-  int V, NT, KB, NB;
+  int V, NT, KB, NB;       // KB: K blocks (128-byte rows) contracted by this launch
+  int KBT, kb0;            // K blocks per image (image stride) and first block of this launch
+  int accumulate;          // add to dcol instead of overwriting it (second launch of a split contraction)
   int tiles_per_clip, n_tiles;
   long long n_units;       // n_tiles * NB
   int tmem_cols;
 };
 
+// kX3 = 1 (fp32-parity mode): a K block is 32 co with rows [hi | lo] in both operands and the issuer forms
+// g_hi*w_hi + g_lo*w_hi + g_hi*w_lo from the 16-wide K sub-blocks; the grad_out tile of Cout = 512 is then
+// 256 KB, so the contraction runs as two launches over half of the K blocks each, the second accumulating.
+template <int kX3>
 __global__ void __launch_bounds__(kDcolThreads, 1)
 dcol_sm100_kernel(const DcolParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -197,6 +217,10 @@ dcol_sm100_kernel(const DcolParams p) {
                                    __uint_as_float(recv[3]));
             }
             float4* dst = reinterpret_cast<float4*>(row_even + (2 * i + (odd ? 1 : 0)) * 4);
+            if (p.accumulate) {              // each element belongs to exactly one thread: plain read-add-write
+              if (ok_even) { const float4 o = dst[0]; first.x += o.x; first.y += o.y; first.z += o.z; first.w += o.w; }
+              if (ok_odd) { const float4 o = dst[16]; second.x += o.x; second.y += o.y; second.z += o.z; second.w += o.w; }
+            }
             if (ok_even) dst[0] = first;
             if (ok_odd) dst[16] = second;    // next row: + 64 floats
           }
@@ -229,10 +253,13 @@ dcol_sm100_kernel(const DcolParams p) {
             ptx::tc_fence_after();
             const uint64_t adesc = ptx::umma_desc_kmajor_sw128(a_base + kb * kABlockBytes);
             const uint64_t bdesc = ptx::umma_desc_kmajor_sw128(b_base + sb * kBStageBytes);
+            constexpr int kSteps = kX3 ? 6 : 4;     // K sub-blocks that meet: bf16 (k,k); x3 hi*hi, lo*hi, hi*lo
+            constexpr int ka_[6] = {0, 1, 2, 3, 0, 1};
+            constexpr int kb_[6] = {0, 1, kX3 ? 0 : 2, kX3 ? 1 : 3, 2, 3};
 #pragma unroll
-            for (int k = 0; k < 4; ++k)
-              ptx::umma_bf16(tmem_base + (uint32_t)(acc * kNBlock), adesc + (uint64_t)(2 * k),
-                             bdesc + (uint64_t)(2 * k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < kSteps; ++k)
+              ptx::umma_bf16(tmem_base + (uint32_t)(acc * kNBlock), adesc + (uint64_t)(2 * ka_[k]),
+                             bdesc + (uint64_t)(2 * kb_[k]), idesc, (kb > 0 || k > 0) ? 1u : 0u);
             ptx::umma_commit(b_empty(sb));
           }
           if (ok) ptx::umma_commit(acc_full(acc));
@@ -251,7 +278,7 @@ dcol_sm100_kernel(const DcolParams p) {
         u += nb_end - nb_beg;
         if (!ptx::mbar_wait(a_empty, (seg & 1) ^ 1, abort_flag)) break;
         ptx::mbar_arrive_expect_tx(a_full, (uint32_t)a_bytes);
-        const uint8_t* asrc = p.gy_img + (long long)tile * a_bytes;
+        const uint8_t* asrc = p.gy_img + ((long long)tile * p.KBT + p.kb0) * kABlockBytes;
         for (int off = 0; off < a_bytes; off += 32768)
           ptx::bulk_g2s(a_base + off, asrc + off, (uint32_t)min(32768, a_bytes - off), a_full);
         for (int nb = nb_beg; ok && nb < nb_end; ++nb) {
@@ -260,7 +287,7 @@ dcol_sm100_kernel(const DcolParams p) {
             const int sb = kbc % kBStages;
             if (!ptx::mbar_wait(b_empty(sb), ((kbc / kBStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
             ptx::mbar_arrive_expect_tx(b_full(sb), (uint32_t)(ncols * 128));
-            ptx::bulk_g2s(b_base + sb * kBStageBytes, p.wt_img + ((long long)nb * p.KB + kb) * kBStageBytes,
+            ptx::bulk_g2s(b_base + sb * kBStageBytes, p.wt_img + ((long long)nb * p.KBT + p.kb0 + kb) * kBStageBytes,
                           (uint32_t)(ncols * 128), b_full(sb));
           }
         }
@@ -299,10 +326,11 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
 // channels [8j, 8j+8) of each 64-channel slice.  The block walks the K taps; the record and the gradient
 // columns of tap t+1 are requested before tap t is processed, so the HBM stream of dcol (slice-major:
 // 8 KB contiguous per block and slice) stays in flight behind the L2 gathers and reductions.
-template <bool FieldOut>
-__global__ void __launch_bounds__(256, 3)
+// kF32X: the channels-last staging of x is fp32 (fp32-parity mode) instead of fp16.
+template <bool FieldOut, bool kF32X>
+__global__ void __launch_bounds__(256, kF32X ? 2 : 3)
 sample_grad_taps_kernel(Geom g, ClStrides cs, int b0, int nh, const float4* __restrict__ recs,
-                        const float* __restrict__ dcol, const __half* __restrict__ x_cl, bool has_mask,
+                        const float* __restrict__ dcol, const void* __restrict__ x_cl_v, bool has_mask,
                         float* __restrict__ grad_coord, float* __restrict__ grad_mask, float* __restrict__ gx_cl,
                         int field_nch, int3 field_ch, const float* __restrict__ field_axes) {
   const int j = threadIdx.x & 7;
@@ -317,7 +345,8 @@ sample_grad_taps_kernel(Geom g, ClStrides cs, int b0, int nh, const float4* __re
   // covers whole 32-byte sectors (two lanes each), which halves the sector operations of the reductions
   const float* dp = dcol + (((long long)bl * S + (long long)grp * g.K * nh) * g.V + vc) * 64 + j * 4;
   const long long slice_stride = (long long)g.V * 64;
-  const __half* xb = x_cl + (long long)b * g.Vin * g.Cin;
+  using XT = typename std::conditional<kF32X, float, __half>::type;
+  const XT* xb = reinterpret_cast<const XT*>(x_cl_v) + (long long)b * g.Vin * g.Cin;
   float* gxb = gx_cl + (long long)b * g.Vin * g.Cin;
   const int chbase = grp * g.cpg + j * 4;
 
@@ -349,24 +378,41 @@ sample_grad_taps_kernel(Geom g, ClStrides cs, int b0, int nh, const float4* __re
         const float4* cur = reinterpret_cast<const float4*>(dp + ((long long)tap * nh + h) * slice_stride);
         d0 = __ldg(cur); d1 = __ldg(cur + 8);
       }
-      uint4 c[8];
+      // corner values of this thread's 8 channels ([4j, 4j+4) and [32+4j, 32+4j+4)), as loaded
+      uint4 c[8], chi[kF32X ? 8 : 1];
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
         const int off = off0 + h * 64 + (q >> 2) * cs.dz + ((q >> 1) & 1) * cs.dy + (q & 1) * cs.dx;
-        if ((valid >> q) & 1u) {
-          const uint2 lo = ptx::ldg_nc_v2(xb + off), hi = ptx::ldg_nc_v2(xb + off + 32);
-          c[q] = make_uint4(lo.x, lo.y, hi.x, hi.y);
+        if constexpr (kF32X) {
+          if ((valid >> q) & 1u) {
+            c[q] = ptx::ldg_nc_v4(xb + off);
+            chi[q] = ptx::ldg_nc_v4(xb + off + 32);
+          } else {
+            c[q] = chi[q] = make_uint4(0u, 0u, 0u, 0u);
+          }
         } else {
-          c[q] = make_uint4(0u, 0u, 0u, 0u);
+          if ((valid >> q) & 1u) {
+            const uint2 lo = ptx::ldg_nc_v2(xb + off), hi = ptx::ldg_nc_v2(xb + off + 32);
+            c[q] = make_uint4(lo.x, lo.y, hi.x, hi.y);
+          } else {
+            c[q] = make_uint4(0u, 0u, 0u, 0u);
+          }
         }
       }
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
         const int dz = q >> 2, dy = (q >> 1) & 1, dx = q & 1;
-        const float2 x0 = __half22float2(bits_h2(c[q].x)), x1 = __half22float2(bits_h2(c[q].y));
-        const float2 x2 = __half22float2(bits_h2(c[q].z)), x3 = __half22float2(bits_h2(c[q].w));
-        G[q] += d0.x * x0.x + d0.y * x0.y + d0.z * x1.x + d0.w * x1.y + d1.x * x2.x + d1.y * x2.y + d1.z * x3.x +
-                d1.w * x3.y;
+        if constexpr (kF32X) {
+          G[q] += d0.x * __uint_as_float(c[q].x) + d0.y * __uint_as_float(c[q].y) + d0.z * __uint_as_float(c[q].z) +
+                  d0.w * __uint_as_float(c[q].w) + d1.x * __uint_as_float(chi[q].x) +
+                  d1.y * __uint_as_float(chi[q].y) + d1.z * __uint_as_float(chi[q].z) +
+                  d1.w * __uint_as_float(chi[q].w);
+        } else {
+          const float2 x0 = __half22float2(bits_h2(c[q].x)), x1 = __half22float2(bits_h2(c[q].y));
+          const float2 x2 = __half22float2(bits_h2(c[q].z)), x3 = __half22float2(bits_h2(c[q].w));
+          G[q] += d0.x * x0.x + d0.y * x0.y + d0.z * x1.x + d0.w * x1.y + d1.x * x2.x + d1.y * x2.y +
+                  d1.z * x3.x + d1.w * x3.y;
+        }
         if (((valid >> q) & 1u) && okz[dz] && oky[dy] && okx[dx]) {
           const float sw = mul_rn(mul_rn(wz[dz], wy[dy]), wx[dx]) * m;
           float* dst = gxb + (off0 + h * 64 + dz * cs.dz + dy * cs.dy + dx * cs.dx);
@@ -426,11 +472,11 @@ unstage_grad_input_kernel(int C, long long Vin, const float* __restrict__ gx_cl,
 }
 
 struct BwdPlan {
-  int nh, S, NT, KB, NB, tiles_per_clip, tmem_cols, smem_bytes, clips_per_chunk;
+  int nh, S, NT, KB, KBT, NB, tiles_per_clip, tmem_cols, smem_bytes, clips_per_chunk;
   size_t x_cl_bytes, rec_bytes, gat_bytes, gy_img_bytes, wt_img_bytes, dcol_bytes, gx_cl_bytes, axes_bytes;
 };
 
-bool make_bwd_plan(const Geom& g, unsigned long long cap, BwdPlan* pl) {
+bool make_bwd_plan(const Geom& g, unsigned long long cap, bool x3, BwdPlan* pl) {
   if (g.groups != 1 || g.cpg % 64 != 0 || g.Cout % 64 != 0 || g.Cout > 512) return false;
   if (g.Vin * g.Cin > 0x7fffffffLL) return false;
   if ((long long)g.G * g.K * g.B > 65535) return false;
@@ -438,18 +484,19 @@ bool make_bwd_plan(const Geom& g, unsigned long long cap, BwdPlan* pl) {
   pl->nh = g.cpg / 64;
   pl->S = g.G * g.K * pl->nh;
   pl->NT = pl->S * 64;
-  pl->KB = g.Cout / 64;
+  pl->KBT = g.Cout / (x3 ? 32 : 64);                     // K blocks per image
+  pl->KB = pl->KBT > 8 ? 8 : pl->KBT;                    // resident per launch (x3, Cout > 256: two launches)
   pl->NB = (pl->NT + kNBlock - 1) / kNBlock;
   pl->tiles_per_clip = (g.V + kBM - 1) / kBM;
   pl->tmem_cols = 512;
   pl->smem_bytes = pl->KB * kABlockBytes + kBStages * kBStageBytes + 256 + 1024;
   if (pl->smem_bytes > kSmemLimit) return false;
   pl->clips_per_chunk = bwd_slice_clips(g, cap);
-  pl->x_cl_bytes = align_up((size_t)g.B * g.Vin * g.Cin * 2, 256);
+  pl->x_cl_bytes = align_up((size_t)g.B * g.Vin * g.Cin * (x3 ? 4 : 2), 256);
   pl->rec_bytes = pos_records_bytes(g);
   pl->gat_bytes = gather_records_bytes(g);
-  pl->gy_img_bytes = align_up((size_t)pl->clips_per_chunk * pl->tiles_per_clip * pl->KB * kABlockBytes, 256);
-  pl->wt_img_bytes = align_up((size_t)pl->NB * pl->KB * kBStageBytes, 256);
+  pl->gy_img_bytes = align_up((size_t)pl->clips_per_chunk * pl->tiles_per_clip * pl->KBT * kABlockBytes, 256);
+  pl->wt_img_bytes = align_up((size_t)pl->NB * pl->KBT * kBStageBytes, 256);
   pl->dcol_bytes = align_up((size_t)pl->clips_per_chunk * g.V * pl->NT * 4, 256);
   pl->gx_cl_bytes = align_up((size_t)g.B * g.Vin * g.Cin * 4, 256);
   pl->axes_bytes = 256;
@@ -457,13 +504,13 @@ bool make_bwd_plan(const Geom& g, unsigned long long cap, BwdPlan* pl) {
 }
 
 template <typename Coords, bool FieldOut>
-int run_bwd(const Geom& g, const Coords& coords, unsigned long long cap, const float* gy, const float* x,
+int run_bwd(const Geom& g, bool x3, const Coords& coords, unsigned long long cap, const float* gy, const float* x,
             const float* mask, const float* w, float* grad_x, float* grad_coord, size_t grad_coord_elems,
             float* grad_mask, float* grad_w, float* grad_bias, void* ws, cudaStream_t st) {
   BwdPlan pl;
-  if (!make_bwd_plan(g, cap, &pl)) return D2C_ERR_MODE;
+  if (!make_bwd_plan(g, cap, x3, &pl)) return D2C_ERR_MODE;
   uint8_t* wsp = reinterpret_cast<uint8_t*>(ws);
-  __half* x_cl = reinterpret_cast<__half*>(wsp); wsp += pl.x_cl_bytes;
+  void* x_cl = wsp; wsp += pl.x_cl_bytes;
   float4* recs = reinterpret_cast<float4*>(wsp); wsp += pl.rec_bytes;
   uint4* gat = reinterpret_cast<uint4*>(wsp); wsp += pl.gat_bytes;
   uint8_t* gy_img = wsp; wsp += pl.gy_img_bytes;
@@ -498,21 +545,25 @@ int run_bwd(const Geom& g, const Coords& coords, unsigned long long cap, const f
   if (FieldOut) D2C_CUDA_TRY(cudaMemsetAsync(grad_coord, 0, sizeof(float) * grad_coord_elems, st));
   {
     dim3 grid((unsigned)((g.Vin + 31) / 32), (unsigned)((g.Cin + 63) / 64), (unsigned)g.B);
-    stage_input_cl_f16_kernel<<<grid, 256, 0, st>>>(g.Cin, g.Vin, x, x_cl);
+    if (x3)
+      stage_input_cl_f32_kernel<<<grid, 256, 0, st>>>(g.Cin, g.Vin, x, reinterpret_cast<float*>(x_cl));
+    else
+      stage_input_cl_f16_kernel<<<grid, 256, 0, st>>>(g.Cin, g.Vin, x, reinterpret_cast<__half*>(x_cl));
     D2C_LAUNCH_CHECK();
-    stage_wt_img_kernel<<<dim3((unsigned)pl.KB, (unsigned)g.Cin), 64, 64 * g.K * sizeof(float), st>>>(
-        g.Cout, g.Cin, g.K, g.cpg, pl.nh, w, wt_img);
+    stage_wt_img_kernel<<<dim3((unsigned)pl.KBT, (unsigned)g.Cin), 64, 64 * g.K * sizeof(float), st>>>(
+        g.Cout, g.Cin, g.K, g.cpg, pl.nh, x3 ? 1 : 0, w, wt_img);
     D2C_LAUNCH_CHECK();
-    if ((rc = launch_sample_records(g, coords, mask, recs, gat, st))) return rc;
+    if ((rc = launch_sample_records(g, coords, mask, recs, gat, st, x3))) return rc;
   }
-  D2C_CUDA_TRY(cudaFuncSetAttribute(dcol_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes));
+  D2C_CUDA_TRY(cudaFuncSetAttribute(dcol_sm100_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes));
+  D2C_CUDA_TRY(cudaFuncSetAttribute(dcol_sm100_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes));
 
   for (int b0 = 0; b0 < g.B; b0 += pl.clips_per_chunk) {
     const int nbc = (g.B - b0 < pl.clips_per_chunk) ? g.B - b0 : pl.clips_per_chunk;
     const int n_tiles = nbc * pl.tiles_per_clip;
     prof_mark(st, "bwd_stage_grad_out");
-    stage_gy_img_kernel<<<dim3((unsigned)n_tiles, (unsigned)pl.KB), 256, 0, st>>>(g.Cout, g.V, pl.tiles_per_clip, b0, gy,
-                                                                                 gy_img);
+    stage_gy_img_kernel<<<dim3((unsigned)n_tiles, (unsigned)pl.KBT), 256, 0, st>>>(g.Cout, g.V, pl.tiles_per_clip, b0,
+                                                                                  x3 ? 1 : 0, gy, gy_img);
     D2C_LAUNCH_CHECK();
     DcolParams p;
     p.gy_img = gy_img; p.wt_img = wt_img; p.dcol = dcol;
@@ -523,13 +574,25 @@ int run_bwd(const Geom& g, const Coords& coords, unsigned long long cap, const f
     if (grid > sm_count) grid = sm_count;
     if (grid < 1) grid = 1;
     prof_mark(st, "bwd_dcol_sm100");
-    dcol_sm100_kernel<<<(unsigned)grid, kDcolThreads, pl.smem_bytes, st>>>(p);
-    D2C_LAUNCH_CHECK();
+    p.KBT = pl.KBT;
+    for (int kb0 = 0; kb0 < pl.KBT; kb0 += pl.KB) {      // bf16 mode and Cout <= 256: a single launch
+      p.kb0 = kb0; p.KB = (pl.KBT - kb0 < pl.KB) ? pl.KBT - kb0 : pl.KB; p.accumulate = kb0 > 0;
+      if (x3)
+        dcol_sm100_kernel<1><<<(unsigned)grid, kDcolThreads, pl.smem_bytes, st>>>(p);
+      else
+        dcol_sm100_kernel<0><<<(unsigned)grid, kDcolThreads, pl.smem_bytes, st>>>(p);
+      D2C_LAUNCH_CHECK();
+    }
     prof_mark(st, "bwd_sample_grad");
     dim3 sgrid((unsigned)((g.V + 31) / 32), (unsigned)(nbc * g.G));
-    sample_grad_taps_kernel<FieldOut><<<sgrid, 256, 0, st>>>(g, cs, b0, pl.nh, recs, dcol, x_cl, mask != nullptr,
-                                                             grad_coord, grad_mask, gx_cl, field_nch, field_ch,
-                                                             axes_dev);
+    if (x3)
+      sample_grad_taps_kernel<FieldOut, true><<<sgrid, 256, 0, st>>>(g, cs, b0, pl.nh, recs, dcol, x_cl,
+                                                                     mask != nullptr, grad_coord, grad_mask, gx_cl,
+                                                                     field_nch, field_ch, axes_dev);
+    else
+      sample_grad_taps_kernel<FieldOut, false><<<sgrid, 256, 0, st>>>(g, cs, b0, pl.nh, recs, dcol, x_cl,
+                                                                      mask != nullptr, grad_coord, grad_mask, gx_cl,
+                                                                      field_nch, field_ch, axes_dev);
     D2C_LAUNCH_CHECK();
   }
   prof_mark(st, "bwd_unstage_grad_input");
@@ -539,7 +602,7 @@ int run_bwd(const Geom& g, const Coords& coords, unsigned long long cap, const f
     D2C_LAUNCH_CHECK();
   }
   // weight gradient: tensor-core implicit GEMM over the re-sampled tile
-  if ((rc = sm100_dw(g, gy, x_cl, gat, grad_w, dw_ws, st))) return rc;
+  if ((rc = sm100_dw(g, x3, gy, x_cl, gat, grad_w, dw_ws, st))) return rc;
   if (grad_bias) {
     prof_mark(st, "bwd_grad_bias");
     grad_bias_kernel<float><<<g.Cout, 256, 0, st>>>(g.B, g.Cout, g.V, gy, grad_bias);
@@ -552,32 +615,34 @@ int run_bwd(const Geom& g, const Coords& coords, unsigned long long cap, const f
 }  // namespace
 
 bool sm100_bwd_supported(const Geom& g, int dtype, int math_mode, unsigned long long cap) {
-  if (dtype != D2C_F32 || math_mode != D2C_MATH_BF16) return false;
+  if (dtype != D2C_F32 || math_mode == D2C_MATH_FP32) return false;
+  const bool x3 = math_mode != D2C_MATH_BF16;
   BwdPlan pl;
-  return make_bwd_plan(g, cap, &pl) && sm100_dw_workspace(g) > 0;
+  return make_bwd_plan(g, cap, x3, &pl) && sm100_dw_workspace(g, x3) > 0;
 }
 
 size_t sm100_bwd_workspace(const Geom& g, int dtype, int math_mode, unsigned long long cap) {
   if (!sm100_bwd_supported(g, dtype, math_mode, cap)) return 0;
+  const bool x3 = math_mode != D2C_MATH_BF16;
   BwdPlan pl;
-  make_bwd_plan(g, cap, &pl);
+  make_bwd_plan(g, cap, x3, &pl);
   return pl.x_cl_bytes + pl.rec_bytes + pl.gat_bytes + pl.gy_img_bytes + pl.wt_img_bytes + pl.dcol_bytes + pl.gx_cl_bytes +
-         pl.axes_bytes + sm100_dw_workspace(g);
+         pl.axes_bytes + sm100_dw_workspace(g, x3);
 }
 
-int sm100_bwd_offsets(const Geom& g, unsigned long long cap, const float* gy, const float* x, const float* offset,
+int sm100_bwd_offsets(const Geom& g, int math_mode, unsigned long long cap, const float* gy, const float* x, const float* offset,
                       const float* mask, const float* w, float* grad_x, float* grad_offset, float* grad_mask,
                       float* grad_w, float* grad_bias, void* ws, cudaStream_t st) {
   OffsetCoords<float> oc{offset};
-  return run_bwd<OffsetCoords<float>, false>(g, oc, cap, gy, x, mask, w, grad_x, grad_offset, 0, grad_mask, grad_w,
+  return run_bwd<OffsetCoords<float>, false>(g, math_mode != D2C_MATH_BF16, oc, cap, gy, x, mask, w, grad_x, grad_offset, 0, grad_mask, grad_w,
                                              grad_bias, ws, st);
 }
 
-int sm100_bwd_field(const Geom& g, unsigned long long cap, const FieldCoords<float>& fc, const float* gy,
+int sm100_bwd_field(const Geom& g, int math_mode, unsigned long long cap, const FieldCoords<float>& fc, const float* gy,
                     const float* x, const float* mask, const float* w, float* grad_x, float* grad_size_map,
                     size_t grad_size_elems, float* grad_mask, float* grad_w, float* grad_bias, void* ws,
                     cudaStream_t st) {
-  return run_bwd<FieldCoords<float>, true>(g, fc, cap, gy, x, mask, w, grad_x, grad_size_map, grad_size_elems,
+  return run_bwd<FieldCoords<float>, true>(g, math_mode != D2C_MATH_BF16, fc, cap, gy, x, mask, w, grad_x, grad_size_map, grad_size_elems,
                                            grad_mask, grad_w, grad_bias, ws, st);
 }
 

@@ -38,7 +38,7 @@ __device__ int g_sm100_dw_status = 0;
 
 struct DwParams {
   Geom g;
-  const __half* x_cl;        // channels-last fp16 staging of x
+  const void* x_cl;          // channels-last staging of x: fp16 (bf16 mode) or fp32 (bf16x3 mode)
   const uint4* recs;         // gather records (sm100_gather.cuh)
   const uint8_t* gyk_img;    // [n_tiles][2 voxel blocks][NCH][32 KB]
   float* dws;                // [S*64][Cout] fp32, zero-initialised
@@ -49,8 +49,10 @@ struct DwParams {
 
 // grad_out [B][Cout][V] fp32 -> per (tile, 64-voxel block, 256-co chunk) images: 256 rows (co) x 128 B
 // (64 voxels, bf16), chunks XOR-swizzled by (row & 7).  Voxels past the clip are zero.
+// x3 = 1 (fp32-parity mode): every (tile, voxel block) holds two image groups, hi = bf16(gy) then
+// lo = bf16(gy - hi), NCH chunks each.
 __global__ void __launch_bounds__(256)
-stage_gy_kmajor_kernel(int Cout, int V, int tiles_per_clip, int NCH, const float* __restrict__ gy,
+stage_gy_kmajor_kernel(int Cout, int V, int tiles_per_clip, int NCH, int x3, const float* __restrict__ gy,
                        uint8_t* __restrict__ img) {
   const int tile = blockIdx.x, coblk = blockIdx.y;        // coblk: 64 rows of co
   const int b = tile / tiles_per_clip, v0 = (tile % tiles_per_clip) * kBM;
@@ -67,14 +69,31 @@ stage_gy_kmajor_kernel(int Cout, int V, int tiles_per_clip, int NCH, const float
     o.x = ptx::pack_bf16x2(f[0], f[1]); o.y = ptx::pack_bf16x2(f[2], f[3]);
     o.z = ptx::pack_bf16x2(f[4], f[5]); o.w = ptx::pack_bf16x2(f[6], f[7]);
     const int kblk = q >> 3, j = q & 7, chunk = co >> 8, row = co & 255;
-    uint8_t* dst = img + (((long long)tile * 2 + kblk) * NCH + chunk) * kChunkBytes + (row >> 3) * 1024 +
-                   (row & 7) * 128 + ((j ^ (row & 7)) << 4);
-    *reinterpret_cast<uint4*>(dst) = o;
+    const long long in_img = (long long)(row >> 3) * 1024 + (row & 7) * 128 + ((j ^ (row & 7)) << 4);
+    if (!x3) {
+      *reinterpret_cast<uint4*>(img + (((long long)tile * 2 + kblk) * NCH + chunk) * kChunkBytes + in_img) = o;
+    } else {
+      uint4 l;
+      l.x = ptx::pack_bf16x2(f[0] - ptx::bf16_lo(o.x), f[1] - ptx::bf16_hi(o.x));
+      l.y = ptx::pack_bf16x2(f[2] - ptx::bf16_lo(o.y), f[3] - ptx::bf16_hi(o.y));
+      l.z = ptx::pack_bf16x2(f[4] - ptx::bf16_lo(o.z), f[5] - ptx::bf16_hi(o.z));
+      l.w = ptx::pack_bf16x2(f[6] - ptx::bf16_lo(o.w), f[7] - ptx::bf16_hi(o.w));
+      const long long grp0 = ((long long)tile * 2 + kblk) * 2;
+      *reinterpret_cast<uint4*>(img + ((grp0 + 0) * NCH + chunk) * kChunkBytes + in_img) = o;
+      *reinterpret_cast<uint4*>(img + ((grp0 + 1) * NCH + chunk) * kChunkBytes + in_img) = l;
+    }
   }
 }
 
+// kX3 = 0 (bf16 mode): a CTA owns a PAIR of 64-channel slices, the accumulator rows are (slice of the pair, c).
+// kX3 = 1 (bf16x3, fp32-parity mode): a CTA owns ONE slice; the two A tiles of a stage are the bf16 hi and lo
+//   parts of the fp32 sampled tile (rows 0-63 / 64-127 of the accumulator), every voxel block of grad_out comes
+//   as a hi image and a lo image and both are accumulated: (a_hi + a_lo)(g_hi + g_lo), all four products; the
+//   two accumulator halves meet in the same dws rows through the epilogue's reductions.
+template <int kX3>
 __global__ void __launch_bounds__(kThreads, 1)
 dw_sm100_kernel(const DwParams p) {
+  constexpr int kBSteps = kX3 ? 4 : 2;      // grad_out images per tile: voxel block x (hi, lo)
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = ptx::smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -124,7 +143,7 @@ dw_sm100_kernel(const DwParams p) {
       if (ptx::mbar_wait(acc_full, 0, abort_flag)) {
         ptx::tc_fence_after();
         const int m = warp * 32 + lane;
-        const int s = 2 * pair + (m >> 6);
+        const int s = kX3 ? pair : 2 * pair + (m >> 6);
         float* row = p.dws + ((long long)s * 64 + (m & 63)) * p.N;
         for (int c0 = 0; c0 < p.N; c0 += 32) {
           uint32_t r[32];
@@ -148,7 +167,8 @@ dw_sm100_kernel(const DwParams p) {
         for (int t = 0; ok && t < n_my_tiles; ++t) {
           const int sa = t % kAStages;
           if (!ptx::mbar_wait(a_full(sa), (t / kAStages) & 1, abort_flag)) break;
-          for (int kblk = 0; kblk < 2; ++kblk, ++kb) {
+          for (int step = 0; step < kBSteps; ++step, ++kb) {
+            const int kblk = kX3 ? (step >> 1) : step;
             const int sb = kb % kBStages;
             if (!ptx::mbar_wait(b_full(sb), (kb / kBStages) & 1, abort_flag)) { ok = false; break; }
             ptx::tc_fence_after();
@@ -165,7 +185,7 @@ dw_sm100_kernel(const DwParams p) {
                     (uint64_t)(2 * k4);
                 ptx::umma_bf16(tmem_base + (uint32_t)n0, adesc, bdesc,
                                ptx::umma_idesc_bf16_f32(kBM, nc) | (1u << 15) /* A is MN-major */,
-                               (t > 0 || kblk > 0 || k4 > 0) ? 1u : 0u);
+                               (t > 0 || step > 0 || k4 > 0) ? 1u : 0u);
               }
             }
             ptx::umma_commit(b_empty(sb));
@@ -179,11 +199,11 @@ dw_sm100_kernel(const DwParams p) {
         uint32_t kb = 0;
         bool ok = true;
         for (int t = 0; ok && t < n_my_tiles; ++t) {
-          for (int kblk = 0; kblk < 2; ++kblk, ++kb) {
+          for (int step = 0; step < kBSteps; ++step, ++kb) {
             const int sb = kb % kBStages;
             if (!ptx::mbar_wait(b_empty(sb), ((kb / kBStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
             ptx::mbar_arrive_expect_tx(b_full(sb), (uint32_t)p.b_stage_bytes);
-            const uint8_t* src = p.gyk_img + ((long long)(tile_beg + t) * 2 + kblk) * p.b_stage_bytes;
+            const uint8_t* src = p.gyk_img + ((long long)(tile_beg + t) * kBSteps + step) * p.b_stage_bytes;
             for (int off = 0; off < p.b_stage_bytes; off += 32768)
               ptx::bulk_g2s(b_base + sb * p.b_stage_bytes + off, src + off, 32768u, b_full(sb));
           }
@@ -205,13 +225,15 @@ dw_sm100_kernel(const DwParams p) {
         for (; q < nq; ++q) {
           const int tile = tile_beg + (q >> 1), sl = q & 1;
           const int b = tile / p.tiles_per_clip, v0 = (tile % p.tiles_per_clip) * kBM;
-          const int s = min(2 * pair + sl, p.S - 1);    // an odd last slice is produced twice, second copy unused
+          // bf16: slice sl of the pair (an odd last slice is produced twice, second copy unused);
+          // x3: channels [32 sl, 32 sl + 32) of the CTA's slice
+          const int s = kX3 ? pair : min(2 * pair + sl, p.S - 1);
           const int h = s % p.nh, gt = s / p.nh, tap = gt % g.K, grp = gt / g.K;
           const int sr = q % kRStages;
           if (!ptx::mbar_wait(r_empty(sr), ((q / kRStages) & 1) ^ 1, abort_flag, 200)) break;
           const int rows = min(kBM, g.V - v0);
           uint8_t* hdr = base_ptr + rec_off + sr * kRStageBytes + kRecBytes;
-          *reinterpret_cast<long long*>(hdr) = (long long)b * g.Vin * g.Cin + grp * g.cpg + h * kBK;
+          *reinterpret_cast<long long*>(hdr) = (long long)b * g.Vin * g.Cin + grp * g.cpg + h * kBK + (kX3 ? sl * 32 : 0);
           *reinterpret_cast<int*>(hdr + 8) = rows;
           ptx::mbar_arrive_expect_tx(r_full(sr), (uint32_t)rows * 48u);
           ptx::bulk_g2s(rec_base + sr * kRStageBytes,
@@ -240,7 +262,7 @@ dw_sm100_kernel(const DwParams p) {
         const int t = q >> 1, sl = q & 1, sa = t % kAStages, sr = q % kRStages;
         if (!ptx::mbar_wait(r_full(sr), (q / kRStages) & 1, abort_flag)) break;
         const uint8_t* rec_stage = base_ptr + rec_off + sr * kRStageBytes;
-        const __half* xb = p.x_cl + *reinterpret_cast<const long long*>(rec_stage + kRecBytes) + j * 8;
+        const long long xoff = *reinterpret_cast<const long long*>(rec_stage + kRecBytes);
         const int rows = *reinterpret_cast<const int*>(rec_stage + kRecBytes + 8);
         // every corner of every row this thread owns goes in flight before the first blend
         uint4 c[kRowsPerThread][8];
@@ -249,19 +271,39 @@ dw_sm100_kernel(const DwParams p) {
           const int r = r0 + kRowStride * i;
           uint2 head = make_uint2(0u, 0u);
           if (r < rows) head = *reinterpret_cast<const uint2*>(rec_stage + r * 48);
-          load_corners(xb, p.cs, head.x, head.y, c[i]);
+          if constexpr (kX3)
+            load_corners_f32(reinterpret_cast<const float*>(p.x_cl) + xoff + j * 4, p.cs, head.x, head.y, c[i]);
+          else
+            load_corners(reinterpret_cast<const __half*>(p.x_cl) + xoff + j * 8, p.cs, head.x, head.y, c[i]);
         }
         if (sl == 0 && !ptx::mbar_wait(a_empty(sa), ((t / kAStages) & 1) ^ 1, abort_flag)) break;
-        const uint32_t stage = a_base + sa * kAStageBytes + sl * kTileBytes;
+        const uint32_t stage = a_base + sa * kAStageBytes + (kX3 ? 0 : sl * kTileBytes);
 #pragma unroll
         for (int i = 0; i < kRowsPerThread; ++i) {
           const int r = r0 + kRowStride * i;
-          uint4 w03 = make_uint4(0u, 0u, 0u, 0u), w47 = w03;   // rows past the clip end: stage bytes are stale
-          if (r < rows) {
-            w03 = *reinterpret_cast<const uint4*>(rec_stage + r * 48 + 16);
-            w47 = *reinterpret_cast<const uint4*>(rec_stage + r * 48 + 32);
+          if constexpr (kX3) {
+            float w[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};   // rows past the clip end: stage bytes are stale
+            if (r < rows) {
+              const uint2 w01 = *reinterpret_cast<const uint2*>(rec_stage + r * 48 + 8);
+              const uint4 w25 = *reinterpret_cast<const uint4*>(rec_stage + r * 48 + 16);
+              const uint2 w67 = *reinterpret_cast<const uint2*>(rec_stage + r * 48 + 32);
+              w[0] = __uint_as_float(w01.x); w[1] = __uint_as_float(w01.y);
+              w[2] = __uint_as_float(w25.x); w[3] = __uint_as_float(w25.y);
+              w[4] = __uint_as_float(w25.z); w[5] = __uint_as_float(w25.w);
+              w[6] = __uint_as_float(w67.x); w[7] = __uint_as_float(w67.y);
+            }
+            // channels 32 sl + 4j .. + 3 of the slice: 16-byte chunk 4 sl + j/2, half j&1; hi tile, lo tile
+            const uint32_t in_tile = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128) +
+                                     (uint32_t)((((4 * sl + (j >> 1)) ^ (r & 7)) << 4) + (j & 1) * 8);
+            blend_split_store(c[i], w, stage + in_tile, stage + kTileBytes + in_tile);
+          } else {
+            uint4 w03 = make_uint4(0u, 0u, 0u, 0u), w47 = w03;   // rows past the clip end: stage bytes are stale
+            if (r < rows) {
+              w03 = *reinterpret_cast<const uint4*>(rec_stage + r * 48 + 16);
+              w47 = *reinterpret_cast<const uint4*>(rec_stage + r * 48 + 32);
+            }
+            blend_store(c[i], w03, w47, stage + row_dst[i]);
           }
-          blend_store(c[i], w03, w47, stage + row_dst[i]);
         }
         if (sl == 1) ptx::fence_proxy_async_smem();
         __syncwarp();
@@ -309,7 +351,7 @@ struct DwPlan {
   size_t gyk_bytes, dws_bytes;
 };
 
-bool make_dw_plan(const Geom& g, int sm_count, DwPlan* dp) {
+bool make_dw_plan(const Geom& g, int sm_count, bool x3, DwPlan* dp) {
   if (g.groups != 1 || g.cpg % kBK != 0 || g.Cout % 64 != 0 || g.Cout > 512) return false;
   if (g.Vin * g.Cin > 0x7fffffffLL) return false;
   dp->nh = g.cpg / kBK;
@@ -319,7 +361,7 @@ bool make_dw_plan(const Geom& g, int sm_count, DwPlan* dp) {
   int cols = 32;
   while (cols < g.Cout) cols <<= 1;
   dp->tmem_cols = cols;
-  dp->n_pairs = (dp->S + 1) / 2;
+  dp->n_pairs = x3 ? dp->S : (dp->S + 1) / 2;
   dp->NCH = (g.Cout + 255) / 256;
   dp->b_stage_bytes = dp->NCH * kChunkBytes;
   dp->smem_bytes = kAStages * kAStageBytes + kBStages * dp->b_stage_bytes + kRStages * kRStageBytes + 256 + 1024;
@@ -331,20 +373,20 @@ bool make_dw_plan(const Geom& g, int sm_count, DwPlan* dp) {
   if (nsplit < 1) nsplit = 1;
   dp->tiles_per_split = (dp->n_tiles + nsplit - 1) / nsplit;
   dp->nsplit = (dp->n_tiles + dp->tiles_per_split - 1) / dp->tiles_per_split;
-  dp->gyk_bytes = align_up((size_t)dp->n_tiles * 2 * dp->b_stage_bytes, 256);
+  dp->gyk_bytes = align_up((size_t)dp->n_tiles * (x3 ? 4 : 2) * dp->b_stage_bytes, 256);
   dp->dws_bytes = align_up((size_t)dp->S * 64 * g.Cout * 4, 256);
   return true;
 }
 
 }  // namespace
 
-size_t sm100_dw_workspace(const Geom& g) {
+size_t sm100_dw_workspace(const Geom& g, bool x3) {
   DwPlan dp;
-  if (!make_dw_plan(g, 148, &dp)) return 0;
+  if (!make_dw_plan(g, 148, x3, &dp)) return 0;
   return dp.gyk_bytes + dp.dws_bytes;
 }
 
-int sm100_dw(const Geom& g, const float* gy, const void* x_cl, const void* recs, float* grad_w, void* ws,
+int sm100_dw(const Geom& g, bool x3, const float* gy, const void* x_cl, const void* recs, float* grad_w, void* ws,
              cudaStream_t st) {
   static int sm_count = 0;
   if (sm_count == 0) {
@@ -353,26 +395,31 @@ int sm100_dw(const Geom& g, const float* gy, const void* x_cl, const void* recs,
     D2C_CUDA_TRY(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
   }
   DwPlan dp;
-  if (!make_dw_plan(g, sm_count, &dp)) return D2C_ERR_MODE;
+  if (!make_dw_plan(g, sm_count, x3, &dp)) return D2C_ERR_MODE;
   uint8_t* gyk = reinterpret_cast<uint8_t*>(ws);
   float* dws = reinterpret_cast<float*>(gyk + dp.gyk_bytes);
 
   prof_mark(st, "bwd_dw_stage");
   D2C_CUDA_TRY(cudaMemsetAsync(dws, 0, (size_t)dp.S * 64 * g.Cout * 4, st));
   stage_gy_kmajor_kernel<<<dim3((unsigned)dp.n_tiles, (unsigned)((g.Cout + 63) / 64)), 256, 0, st>>>(
-      g.Cout, g.V, dp.tiles_per_clip, dp.NCH, gy, gyk);
+      g.Cout, g.V, dp.tiles_per_clip, dp.NCH, x3 ? 1 : 0, gy, gyk);
   D2C_LAUNCH_CHECK();
 
   DwParams p;
-  p.g = g; p.x_cl = reinterpret_cast<const __half*>(x_cl); p.recs = reinterpret_cast<const uint4*>(recs);
+  p.g = g; p.x_cl = x_cl; p.recs = reinterpret_cast<const uint4*>(recs);
   p.gyk_img = gyk; p.dws = dws;
   p.cs.dz = g.H * g.W * g.Cin; p.cs.dy = g.W * g.Cin; p.cs.dx = g.Cin;
   p.N = g.Cout; p.nh = dp.nh; p.S = dp.S; p.tiles_per_clip = dp.tiles_per_clip; p.n_tiles = dp.n_tiles;
   p.tmem_cols = dp.tmem_cols;
   p.n_pairs = dp.n_pairs; p.tiles_per_split = dp.tiles_per_split; p.NCH = dp.NCH; p.b_stage_bytes = dp.b_stage_bytes;
-  D2C_CUDA_TRY(cudaFuncSetAttribute(dw_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dp.smem_bytes));
   prof_mark(st, "bwd_dw_sm100");
-  dw_sm100_kernel<<<dp.n_pairs * dp.nsplit, kThreads, dp.smem_bytes, st>>>(p);
+  if (x3) {
+    D2C_CUDA_TRY(cudaFuncSetAttribute(dw_sm100_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, dp.smem_bytes));
+    dw_sm100_kernel<1><<<dp.n_pairs * dp.nsplit, kThreads, dp.smem_bytes, st>>>(p);
+  } else {
+    D2C_CUDA_TRY(cudaFuncSetAttribute(dw_sm100_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, dp.smem_bytes));
+    dw_sm100_kernel<0><<<dp.n_pairs * dp.nsplit, kThreads, dp.smem_bytes, st>>>(p);
+  }
   D2C_LAUNCH_CHECK();
   prof_mark(st, "bwd_dw_unstage");
   unstage_dw_kernel<<<dim3((unsigned)((dp.S * 64 + 31) / 32), (unsigned)((g.Cout + 31) / 32)), 256, 0, st>>>(

@@ -83,3 +83,59 @@ def test_dyn_dilated_fp32_parity_mode(dn, mode):
     want = orc.dyn_dilated_conv3d_fwd(p["x"], p["geo"], p["mask"], p["weight"], p["bias"], mode, padding=1,
                                       offset_groups=G)
     assert np.abs(y - want).max() <= REL * np.abs(want).max()
+
+
+@pytest.mark.parametrize("ci", [0, 1, 2, 3, 4, 6, 7])
+def test_backward_fp32_parity_mode_vs_oracle(dn, ci):
+    """All five gradients on the tensor-core tier in the fp32-parity mode against the float64 oracle; 1e-4 of
+    each gradient's scale (case 3: Cout = 512, the gradient-column contraction runs as two accumulating
+    launches; case 4: Cout = 320, a partial second launch)."""
+    from d2conv3d_b200 import _lib
+    cfg = dict(CASES[ci])
+    cfg.setdefault("k", 3)
+    cfg.setdefault("padding", 1)
+    p = make_problem(800 + ci, dtype=np.float32, offset_std=2.0, **cfg)
+    kw = dict(stride=p["stride"], padding=p["padding"], dilation=p["dilation"], groups=1, offset_groups=p["offset_groups"])
+    d = lambda k: p[k].astype(np.float64)
+    want = orc.deform_conv3d_bwd(d("gy"), d("x"), d("geo"), d("mask"), d("weight"), True, **kw)
+    ts = [cu(p[k]).requires_grad_() for k in ("x", "geo", "mask", "weight", "bias")]
+    y = dn.deform_conv3d(*ts, p["stride"], p["padding"], p["dilation"], 1, p["offset_groups"])
+    _lib.profile_read(); _lib.profile_enable(True)
+    y.backward(cu(p["gy"]))
+    _lib.profile_enable(False)
+    phases = [n for n, _ in _lib.profile_read()]
+    assert "bwd_dcol_sm100" in phases and "bwd_sample_grad" in phases and "bwd_dw_sm100" in phases, phases
+    for t, w_, nm in zip(ts, want, ("grad_x", "grad_offset", "grad_mask", "grad_w", "grad_bias")):
+        err = np.abs(t.grad.cpu().numpy() - w_).max() / np.abs(w_).max()
+        print(f"case {ci} {nm}: rel err {err:.3e}")
+        assert err <= REL, nm
+
+
+@pytest.mark.parametrize("mode", ["x", "xyz"])
+def test_dyn_dilated_backward_fp32_parity_mode(dn, mode):
+    G = 2
+    p = make_problem(830, 2, 128, 64, (4, 9, 10), padding=1, G=G, dtype=np.float32, field_mode=mode)
+    want = orc.dyn_dilated_conv3d_bwd(p["gy"], p["x"], p["geo"], p["mask"], p["weight"], True, mode, padding=1,
+                                      offset_groups=G)
+    ts = [cu(p[k]).requires_grad_() for k in ("x", "geo", "mask", "weight", "bias")]
+    dn.dyn_dilated_conv3d(*ts, mode, 1, 1, 1, 1, G).backward(cu(p["gy"]))
+    for t, w_, nm in zip(ts, want, ("grad_x", "grad_size_map", "grad_mask", "grad_w", "grad_bias")):
+        err = np.abs(t.grad.cpu().numpy() - w_).max() / np.abs(w_).max()
+        assert err <= REL, (nm, err)
+
+
+def test_backward_chunked_by_intermediate_cap_fp32_parity_mode(dn):
+    p = make_problem(840, 3, 64, 64, (2, 8, 9), padding=1, dtype=np.float32)
+    def run():
+        ts = [cu(p[k]).requires_grad_() for k in ("x", "geo", "mask", "weight", "bias")]
+        dn.deform_conv3d(*ts, 1, 1, 1, 1, 1).backward(cu(p["gy"]))
+        return [t.grad.clone() for t in ts]
+    full = run()
+    old = dn._ops.config.get_max_intermediate_elements()
+    try:
+        dn._ops.config.set_max_intermediate_elements(64 * 27 * 144)    # one clip per chunk
+        chunked = run()
+    finally:
+        dn._ops.config.set_max_intermediate_elements(old)
+    for a, b in zip(full, chunked):
+        assert torch.allclose(a, b, rtol=1e-4, atol=1e-5 * float(a.abs().max()))
