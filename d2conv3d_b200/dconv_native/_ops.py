@@ -160,10 +160,26 @@ def dyn_dilated_conv3d(input, size_map, alpha, weight, bias, mode, stride, paddi
                                            tuple(padding), tuple(dilation), int(groups), int(offset_groups))
 
 
-def deform_conv1d(*args, **kwargs):
-    """dconv_native._ops.deform_conv1d (csrc/ops/dconv1d.h).  The 1-D op is outside
-    the accelerated path."""
-    raise NotImplementedError("deform_conv1d is not provided by d2conv3d_b200")
+def deform_conv1d(input, offset, alpha, weight, bias, stride, padding, dilation, groups, offset_groups):
+    """dconv_native._ops.deform_conv1d (csrc/ops/dconv1d.h, dconv1d_gpu.cu:24-55): modulated deformable
+    conv1d with one offset per (offset group, tap, output position) and linear interpolation.
+
+    Evaluated by the 3-D kernels on a [B, C, 1, 1, L] view: with depth = height = 1 and zero z / y offsets the
+    z and y coordinates are exactly 0, so the only contributing corners are (0, 0, x0) and (0, 0, x0 + 1) with
+    weights (1 - t) and t -- the reference's `lerp(v0, v1, x - x0)` with out-of-range neighbours read as 0
+    (its lines 47-53).  The x offsets become channel 3*(g*K + k) + 2 of a 3-D offset tensor whose other
+    channels are zero; autograd carries grad_offset back through that embedding."""
+    if input.dim() != 3 or offset.dim() != 3 or weight.dim() != 3:
+        raise RuntimeError("deform_conv1d expects input [B, C, L], offset [B, G*K, L_out], weight [Cout, Cin/groups, K]")
+    one = lambda v: int(v[0]) if isinstance(v, (tuple, list)) else int(v)
+    stride, padding, dilation = one(stride), one(padding), one(dilation)
+    B, GK, Lo = offset.shape
+    zeros = torch.zeros_like(offset)
+    off3 = torch.stack((zeros, zeros, offset), dim=2).reshape(B, 3 * GK, 1, 1, Lo)
+    alpha3 = None if alpha is None else alpha.reshape(B, GK, 1, 1, Lo)
+    y = deform_conv3d(input[:, :, None, None, :], off3, alpha3, weight[:, :, None, None, :], bias,
+                      1, 1, int(stride), 0, 0, int(padding), 1, 1, int(dilation), int(groups), int(offset_groups))
+    return y[:, :, 0, 0, :]
 
 
 def corners(input_shape, weight_shape, offset, stride, padding, dilation, offset_groups):

@@ -40,6 +40,9 @@ def dyn_dilated_conv3d(input, size_map, alpha, weight, bias=None, mode="xyz", st
 
 def deform_conv1d(input, offset, alpha, weight, bias=None, stride=1, padding=0, dilation=1,
                   n_weight_groups=1, n_offset_groups=1):
+    """ops/dconv-native/src/dconv_native/deform_conv.py:19-40: half inputs are up-cast; a missing bias or
+    alpha stands for zeros / ones."""
+    input, offset, alpha, weight, bias = _upcast_if_any_half((input, offset, alpha, weight, bias))
     return _ops.deform_conv1d(input, offset, alpha, weight, bias, stride, padding, dilation,
                               n_weight_groups, n_offset_groups)
 

@@ -209,3 +209,41 @@ def depthwise_conv3d_bwd(gy, x, w, has_bias=True, stride=1, padding=0, dilation=
     if rc:
         raise RuntimeError(f"oracle depthwise bwd failed: {rc}")
     return gx, gw, gb
+
+
+def deform_conv1d_fwd(x, offset, alpha, weight, bias=None, stride=1, padding=0, dilation=1, groups=1,
+                      offset_groups=1):
+    """Modulated deformable conv1d, restating ops/dconv-native/csrc/ops/dconv1d_gpu.cu:24-55 (im2col with
+    `a * lerp(v0, v1, x - x0)`, neighbours outside [0, L) read as 0) followed by the grouped GEMM + bias of
+    :95-160.  numpy, small cases only.  x [B, C, L], offset / alpha [B, G*K, Lo], weight [Cout, C/groups, K]."""
+    x = np.asarray(x); offset = np.asarray(offset); weight = np.asarray(weight)
+    B, C, L = x.shape
+    Cout, Cg, K = weight.shape
+    Lo = (L + 2 * padding - dilation * (K - 1) - 1) // stride + 1
+    assert offset.shape == (B, offset_groups * K, Lo)
+    if alpha is None:
+        alpha = np.ones_like(offset)
+    cpg = C // offset_groups
+    cols = np.zeros((B, C, K, Lo), dtype=x.dtype)
+    ox = np.arange(Lo)
+    for g in range(offset_groups):
+        for i in range(K):
+            pos = (ox * stride - padding + i * dilation).astype(x.dtype)[None, :] + offset[:, g * K + i, :]   # [B, Lo]
+            x0 = np.floor(pos).astype(np.int64)
+            x1 = x0 + 1
+            t = pos - x0.astype(x.dtype)
+            a = alpha[:, g * K + i, :]
+            for c in range(g * cpg, (g + 1) * cpg):
+                xc = x[:, c, :]                                           # [B, L]
+                v0 = np.where((x0 >= 0) & (x0 < L), np.take_along_axis(xc, np.clip(x0, 0, L - 1), axis=1), 0)
+                v1 = np.where((x1 >= 0) & (x1 < L), np.take_along_axis(xc, np.clip(x1, 0, L - 1), axis=1), 0)
+                cols[:, c, i, :] = a * (v0 + t * (v1 - v0))
+    y = np.zeros((B, Cout, Lo), dtype=x.dtype)
+    cog = Cout // groups
+    for gw in range(groups):
+        wg = weight[gw * cog:(gw + 1) * cog].reshape(cog, Cg * K)
+        cg = cols[:, gw * Cg:(gw + 1) * Cg].reshape(B, Cg * K, Lo)
+        y[:, gw * cog:(gw + 1) * cog] = np.einsum("ok,bkl->bol", wg, cg)
+    if bias is not None:
+        y += np.asarray(bias)[None, :, None]
+    return y

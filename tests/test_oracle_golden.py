@@ -173,3 +173,25 @@ def test_depthwise_matches_torch_cpu(stride, dilation, mult, bias, dtype, atol):
     assert np.allclose(gw, wt.grad.numpy(), atol=atol * 10)
     if bias:
         assert np.allclose(gb, bt.grad.numpy(), atol=atol * 10)
+
+
+def test_oracle_deform_conv1d_identities():
+    """The 1-D oracle reduces to a plain (grouped, strided, dilated) convolution for zero offsets and unit
+    modulation, and to a shifted one for integer offsets (ops/dconv-native/test/test_deform_conv.py:232-262)."""
+    import torch
+    rng = np.random.default_rng(21)
+    B, C, Cout, L, K, groups = 2, 6, 4, 19, 3, 2
+    x = rng.standard_normal((B, C, L)); w = rng.standard_normal((Cout, C // groups, K)); b = rng.standard_normal(Cout)
+    for stride, pad, dil in ((1, 0, 1), (2, 2, 2)):
+        Lo = (L + 2 * pad - dil * (K - 1) - 1) // stride + 1
+        off = np.zeros((B, K, Lo))
+        y = orc.deform_conv1d_fwd(x, off, None, w, b, stride, pad, dil, groups, 1)
+        ref = torch.nn.functional.conv1d(torch.from_numpy(x), torch.from_numpy(w), torch.from_numpy(b), stride, pad,
+                                         dil, groups).numpy()
+        assert np.allclose(y, ref, atol=1e-12)
+    # integer offset +1 on every tap == convolution of the input shifted left by one (zero fill)
+    off = np.ones((B, K, L - K + 1))
+    xs = np.concatenate([x[:, :, 1:], np.zeros((B, C, 1))], axis=2)
+    y = orc.deform_conv1d_fwd(x, off, None, w, b, 1, 0, 1, groups, 1)
+    ref = torch.nn.functional.conv1d(torch.from_numpy(xs), torch.from_numpy(w), torch.from_numpy(b), 1, 0, 1, groups).numpy()
+    assert np.allclose(y, ref, atol=1e-12)
