@@ -195,7 +195,13 @@ def run_reference_arm(args):
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised in profiles/
 # (same workload); None where no capture has been taken.
-TRAFFIC_PER_LAUNCH = {}      # (phase, math mode) -> bytes
+TRAFFIC_PER_LAUNCH = {       # (phase, math mode) -> DRAM read + write bytes of one launch (profiles/c2_fwd_bwd_step_kernels.md)
+    ("bwd_sample_grad", "bf16"): 1.603e9 + 0.137e9, ("bwd_sample_grad", "auto"): 1.630e9 + 0.139e9,
+    ("bwd_sample_grad", "bf16x3"): 1.630e9 + 0.139e9,
+    ("fwd_sm100_fused", "bf16"): 0.420e9 + 0.056e9, ("fwd_sm100_fused", "auto"): 1.096e9 + 0.072e9,
+    ("bwd_dcol_sm100", "bf16"): 0.076e9 + 1.382e9, ("bwd_dw_sm100", "bf16"): 0.430e9 + 0.073e9,
+    ("bwd_dw_sm100", "auto"): 0.556e9 + 0.070e9,
+}
 
 PHASE_WORK = {
     # phase name -> (bound, key of the algorithmic work of one launch)
