@@ -184,46 +184,66 @@ dcol_sm100_kernel(const DcolParams p) {
       const long long slice_stride = (long long)p.V * 64;
       const int acc = q & 1;
       const int ncols = min(kNBlock, p.NT - nb * kNBlock);
+      // Lanes 2i / 2i+1 hold rows v, v+1 (256 bytes apart).  They swap every other 16-byte chunk so that
+      // each store instruction has the pair write one full 32-byte sector of ONE row (first the even
+      // lane's row, then the odd lane's) instead of two half sectors of two rows.
+      const bool odd = lane & 1;
+      const bool ok_even = (v - (odd ? 1 : 0)) < p.V, ok_odd = (v + (odd ? 0 : 1)) < p.V;
+      auto chunk_ptr = [&](int c0) {   // this lane's first 16-byte slot of the even row in the 32-column chunk c0
+        return reinterpret_cast<float4*>(row - (odd ? 64 : 0) + (c0 >> 6) * slice_stride + (c0 & 63) + (odd ? 4 : 0));
+      };
+      // accumulating launch: the previous launch's values of a chunk are requested one chunk ahead (the first
+      // chunk's before the wait for the accumulator), so their latency hides behind the MMAs / the previous chunk
+      const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+      float4 old_e[4], old_o[4];
+      auto prefetch_old = [&](int c0, float4 (&oe)[4], float4 (&oo)[4]) {
+        const float4* src = chunk_ptr(c0);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          oe[i] = ok_even ? src[2 * i] : zero4;
+          oo[i] = ok_odd ? src[2 * i + 16] : zero4;
+        }
+      };
+      const int c_beg = half * 128, c_end = min(ncols, half * 128 + 128);
+      if (p.accumulate && c_beg < c_end) prefetch_old(c_beg, old_e, old_o);
       if (!ptx::mbar_wait(acc_full(acc), (q >> 1) & 1, abort_flag)) break;
       ptx::tc_fence_after();
-      for (int c0 = half * 128; c0 < min(ncols, half * 128 + 128); c0 += 32) {
+      for (int c0 = c_beg; c0 < c_end; c0 += 32) {
+        float4 nxt_e[4], nxt_o[4];
+        if (p.accumulate && c0 + 32 < c_end) prefetch_old(c0 + 32, nxt_e, nxt_o);
         uint32_t r[32];
         ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * kNBlock + c0), r);
         ptx::tmem_ld_wait();
-        // Lanes 2i / 2i+1 hold rows v, v+1 (256 bytes apart).  They swap every other 16-byte chunk so that
-        // each store instruction has the pair write one full 32-byte sector of ONE row (first the even
-        // lane's row, then the odd lane's) instead of two half sectors of two rows.
-        {
-          const bool odd = lane & 1;
-          float* row_even = row - (odd ? 64 : 0) + (c0 >> 6) * slice_stride + (c0 & 63);
-          const bool ok_even = (v - (odd ? 1 : 0)) < p.V, ok_odd = (v + (odd ? 0 : 1)) < p.V;
+        float4* dst = chunk_ptr(c0);
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint32_t send[4], recv[4];
+        for (int i = 0; i < 4; ++i) {
+          uint32_t send[4], recv[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) send[e] = odd ? r[8 * i + e] : r[8 * i + 4 + e];
+          for (int e = 0; e < 4; ++e) send[e] = odd ? r[8 * i + e] : r[8 * i + 4 + e];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) recv[e] = __shfl_xor_sync(0xffffffffu, send[e], 1);
-            float4 first, second;   // first: even row's chunk (2i + odd); second: odd row's chunk (2i + odd)
-            if (odd) {
-              first = make_float4(__uint_as_float(recv[0]), __uint_as_float(recv[1]), __uint_as_float(recv[2]),
-                                  __uint_as_float(recv[3]));
-              second = make_float4(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]),
-                                   __uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
-            } else {
-              first = make_float4(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1]),
-                                  __uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
-              second = make_float4(__uint_as_float(recv[0]), __uint_as_float(recv[1]), __uint_as_float(recv[2]),
-                                   __uint_as_float(recv[3]));
-            }
-            float4* dst = reinterpret_cast<float4*>(row_even + (2 * i + (odd ? 1 : 0)) * 4);
-            if (p.accumulate) {              // each element belongs to exactly one thread: plain read-add-write
-              if (ok_even) { const float4 o = dst[0]; first.x += o.x; first.y += o.y; first.z += o.z; first.w += o.w; }
-              if (ok_odd) { const float4 o = dst[16]; second.x += o.x; second.y += o.y; second.z += o.z; second.w += o.w; }
-            }
-            if (ok_even) dst[0] = first;
-            if (ok_odd) dst[16] = second;    // next row: + 64 floats
+          for (int e = 0; e < 4; ++e) recv[e] = __shfl_xor_sync(0xffffffffu, send[e], 1);
+          float4 first, second;   // first: even row's chunk (2i + odd); second: odd row's chunk (2i + odd)
+          if (odd) {
+            first = make_float4(__uint_as_float(recv[0]), __uint_as_float(recv[1]), __uint_as_float(recv[2]),
+                                __uint_as_float(recv[3]));
+            second = make_float4(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]),
+                                 __uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+          } else {
+            first = make_float4(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1]),
+                                __uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
+            second = make_float4(__uint_as_float(recv[0]), __uint_as_float(recv[1]), __uint_as_float(recv[2]),
+                                 __uint_as_float(recv[3]));
           }
+          if (p.accumulate) {              // each element belongs to exactly one thread: plain read-add-write
+            first.x += old_e[i].x; first.y += old_e[i].y; first.z += old_e[i].z; first.w += old_e[i].w;
+            second.x += old_o[i].x; second.y += old_o[i].y; second.z += old_o[i].z; second.w += old_o[i].w;
+          }
+          if (ok_even) dst[2 * i] = first;
+          if (ok_odd) dst[2 * i + 16] = second;    // next row: + 64 floats
+        }
+        if (p.accumulate) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) { old_e[i] = nxt_e[i]; old_o[i] = nxt_o[i]; }
         }
       }
       ptx::tc_fence_before();
