@@ -50,7 +50,7 @@ __device__ __forceinline__ float split_part(float f, bool lo) {
 
 __global__ void __launch_bounds__(256)
 stage_gy_img_kernel(int Cout, int V, int tiles_per_clip, int b0, int x3, const float* __restrict__ gy,
-                    uint8_t* __restrict__ img) {
+                    uint8_t* __restrict__ img, float* __restrict__ grad_bias) {
   __shared__ float tile[64][129];
   const int tile_id = blockIdx.x, kb = blockIdx.y, KB = gridDim.y;
   const int bl = tile_id / tiles_per_clip, v0 = (tile_id % tiles_per_clip) * kBM;
@@ -61,6 +61,13 @@ stage_gy_img_kernel(int Cout, int V, int tiles_per_clip, int b0, int x3, const f
     tile[co][r] = (v < V) ? __ldg(gy + ((long long)b * Cout + kb * nco + co) * V + v) : 0.f;
   }
   __syncthreads();
+  // grad_bias = grad_out summed over clips and voxels (reference dconv3d_gpu.cu:1329): this kernel reads every
+  // element of grad_out exactly once, so each block adds its 128-voxel partial sums (grad_bias zeroed before)
+  if (grad_bias && (int)threadIdx.x < nco) {
+    float sum = 0.f;
+    for (int r = 0; r < 128; ++r) sum += tile[threadIdx.x][(r + threadIdx.x) & 127];   // skewed: no bank conflicts
+    atomicAdd(grad_bias + kb * nco + threadIdx.x, sum);
+  }
   uint8_t* dst = img + ((long long)tile_id * KB + kb) * kABlockBytes;
   for (int e = threadIdx.x; e < 128 * 8; e += 256) {
     const int r = e >> 3, j = e & 7;
@@ -563,6 +570,7 @@ int run_bwd(const Geom& g, bool x3, const Coords& coords, unsigned long long cap
   prof_mark(st, "bwd_stage_operands");
   D2C_CUDA_TRY(cudaMemsetAsync(gx_cl, 0, (size_t)g.B * g.Vin * g.Cin * 4, st));
   if (FieldOut) D2C_CUDA_TRY(cudaMemsetAsync(grad_coord, 0, sizeof(float) * grad_coord_elems, st));
+  if (grad_bias) D2C_CUDA_TRY(cudaMemsetAsync(grad_bias, 0, sizeof(float) * g.Cout, st));
   {
     dim3 grid((unsigned)((g.Vin + 31) / 32), (unsigned)((g.Cin + 63) / 64), (unsigned)g.B);
     if (x3)
@@ -583,7 +591,7 @@ int run_bwd(const Geom& g, bool x3, const Coords& coords, unsigned long long cap
     const int n_tiles = nbc * pl.tiles_per_clip;
     prof_mark(st, "bwd_stage_grad_out");
     stage_gy_img_kernel<<<dim3((unsigned)n_tiles, (unsigned)pl.KBT), 256, 0, st>>>(g.Cout, g.V, pl.tiles_per_clip, b0,
-                                                                                  x3 ? 1 : 0, gy, gy_img);
+                                                                                  x3 ? 1 : 0, gy, gy_img, grad_bias);
     D2C_LAUNCH_CHECK();
     DcolParams p;
     p.gy_img = gy_img; p.wt_img = wt_img; p.dcol = dcol;
@@ -623,11 +631,6 @@ int run_bwd(const Geom& g, bool x3, const Coords& coords, unsigned long long cap
   }
   // weight gradient: tensor-core implicit GEMM over the re-sampled tile
   if ((rc = sm100_dw(g, x3, gy, x_cl, gat, grad_w, dw_ws, st))) return rc;
-  if (grad_bias) {
-    prof_mark(st, "bwd_grad_bias");
-    grad_bias_kernel<float><<<g.Cout, 256, 0, st>>>(g.B, g.Cout, g.V, gy, grad_bias);
-    D2C_LAUNCH_CHECK();
-  }
   prof_mark(st, nullptr);
   return D2C_OK;
 }
