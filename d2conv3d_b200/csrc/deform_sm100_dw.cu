@@ -10,6 +10,10 @@
 //   B operand: grad_out as bf16 [co rows x 64 voxels], K-major, staged per 64-voxel block.
 // The partial results of different voxel ranges are combined with vector reductions into a [S*64, Cout]
 // fp32 buffer that a last kernel permutes into the [Cout, Cin, kd, kh, kw] layout of grad_weight.
+// In the fp32-parity mode (template parameter) a CTA owns ONE slice whose bf16 hi and lo parts are the two
+// A tiles, and grad_out arrives as a hi and a lo image per voxel block: all four products are accumulated.
+// Gather records reach the 16 producer warps through a bulk-copied shared-memory ring with a unit header,
+// exactly as in the forward.
 #include "deform_sm100.h"
 #include "sm100_gather.cuh"
 #include "sm100_ptx.cuh"

@@ -8,22 +8,27 @@
 // GEMM view: M = output voxels (tiles of 128 consecutive voxels of one clip), N = Cout
 // (whole, <= 512, in tensor memory), K = Cin*27 walked as slices of 64 input channels of
 // one (offset group, tap).  All channels of a slice share their 8 trilinear corners, so
-// with the input staged channels-last in fp16 each corner of a slice is ONE contiguous
-// 128-byte line.
+// with the input staged channels-last each corner of a slice is ONE contiguous 128-byte
+// (fp16 staging) or 256-byte (fp32 staging) line.
 //
 // Work decomposition: the (tile, slice) units are cut into one contiguous range per CTA
 // (stream-K), so 203 tiles do not run as two ragged waves on 148 SMs.  A CTA whose range
 // covers a whole tile stores it; partial tiles are combined with fp32 reductions into the
 // zero-initialised output.
 //
-// Per CTA, 22 warps:
+// Per CTA, 23 warps:
 //   warps 0-3   epilogue: tcgen05.ld the 128 x N accumulator, add bias, store / reduce NCDHW
 //   warp  4     one thread issues tcgen05.mma and the commits that free the stages
 //   warp  5     one thread streams pre-swizzled weight slices with cp.async.bulk
-//   warps 6-21  gather producers: gather records (prefetched one unit ahead), predicated
-//               corner loads (16 B per thread), packed-fp16 blend with pre-modulated weights,
-//               bf16 pack, swizzled st.shared of the A tile
+//   warps 6-21  gather producers: unit header + gather record from the shared-memory record ring, 8
+//               unconditional corner loads (16 B) for each of the thread's two rows in flight at once, blend
+//               with pre-modulated weights, bf16 pack, swizzled st.shared of the A tile
+//   warp  22    one thread bulk-copies each unit's gather records into the record ring and writes the unit
+//               header (staging offset of the slice, valid rows), so the producers do no index arithmetic
 // Stage hand-off is by mbarriers; every wait is bounded (sm100_ptx.cuh).
+//
+// Two math modes share the kernel (template parameter): single-pass bf16 (64-channel units, fp16 staging) and
+// the fp32-parity split "bf16x3" (32-channel units, fp32 staging, rows [hi | lo], three K-sub-block products).
 #include "deform_sm100.h"
 #include "sm100_gather.cuh"
 #include "sm100_ptx.cuh"

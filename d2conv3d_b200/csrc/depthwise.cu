@@ -112,7 +112,6 @@ dw_bwd_input_kernel(Geom g, const T* __restrict__ gy, const T* __restrict__ w, T
 // from L1), then the block reduces K values.  Slices accumulate with fp32/fp64
 // atomics into `partial` ([Cout, K] in the accumulator type, zeroed beforehand);
 // a tiny second kernel converts to T.
-constexpr int kDwMaxTaps = 27;
 
 template <typename T, int KD, int KH, int KW>
 __global__ void __launch_bounds__(256)

@@ -18,9 +18,10 @@
 //                corner 1 of that axis is a different, readable voxel; otherwise both corners of the axis read
 //                the same (readable) voxel
 //        wj    = half2 {a_j*mask, a_j*mask}: trilinear weight x modulation, rounded to fp16, duplicated; ZERO
-//                for every corner that does not contribute to the forward sample
+//                for every corner that does not contribute to the forward sample.  In the fp32-parity mode
+//                the same 48 bytes hold {voff, steps, w0, w1}, w2..w5, {w6, w7, -, -} with fp32 weights.
 //   so a producer issues 8 unconditional loads of readable addresses and lets the zero weights discard the
-//   stand-ins (the staging is saturated fp16, hence finite, so 0 x stand-in = 0): no predicate, no zero-fill.
+//   stand-ins (the staging is kept finite, so 0 x stand-in = 0): no predicate, no zero-fill.
 #pragma once
 
 #include <cuda_fp16.h>
@@ -30,11 +31,6 @@
 
 namespace d2c {
 namespace {
-
-struct GatherRec {
-  uint4 head;   // x: voff, y: valid bits, z/w: unused
-  uint4 w03, w47;
-};
 
 __device__ __forceinline__ uint32_t h2_bits(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
 __device__ __forceinline__ __half2 bits_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
@@ -157,13 +153,6 @@ __device__ __forceinline__ void blend_store(const uint4 (&c)[8], uint4 w03, uint
   ptx::sts_v4(dst, out);
 }
 
-__device__ __forceinline__ void produce_item(const __half* __restrict__ xb, ClStrides cs, const GatherRec& r,
-                                             int ch0, uint32_t dst) {
-  uint4 c[8];
-  load_corners(xb + ch0, cs, r.head.x, r.head.y, c);
-  blend_store(c, r.w03, r.w47, dst);
-}
-
 // ---- fp32-parity mode ("bf16x3"): fp32 staging, fp32 blend, bf16 hi/lo split -------------------------------
 // One item = 4 channels (16 bytes of fp32) of one sample.  The blended value v is written twice into the
 // 128-byte A row of a 32-channel unit: hi = bf16(v) at channel column c, lo = bf16(v - hi) at column 32 + c,
@@ -200,25 +189,6 @@ __device__ __forceinline__ void blend_split_store(const uint4 (&c)[8], const flo
   const uint32_t l23 = ptx::pack_bf16x2(v[2] - ptx::bf16_lo(h23), v[3] - ptx::bf16_hi(h23));
   ptx::sts_v2(dst_hi, make_uint2(h01, h23));
   ptx::sts_v2(dst_lo, make_uint2(l01, l23));
-}
-
-// Gather records of the kRows rows (r0, r0+kStride, ...) a gather thread owns in the tile starting at voxel
-// v0.  Rows past the end of the clip get an all-zero record (zero weights -> a zero row).
-template <int kRows, int kStride>
-__device__ __forceinline__ void load_row_records(const uint4* __restrict__ gat, const Geom& g, int b, int grp,
-                                                 int tap, int v0, int r0, GatherRec (&out)[kRows]) {
-  const uint4* p = gat + 3 * ((((long long)b * g.G + grp) * g.K + tap) * g.V);
-#pragma unroll
-  for (int i = 0; i < kRows; ++i) {
-    const int v = v0 + r0 + kStride * i;
-    if (v < g.V) {
-      out[i].head = __ldg(p + 3 * (long long)v);
-      out[i].w03 = __ldg(p + 3 * (long long)v + 1);
-      out[i].w47 = __ldg(p + 3 * (long long)v + 2);
-    } else {
-      out[i].head = out[i].w03 = out[i].w47 = make_uint4(0u, 0u, 0u, 0u);
-    }
-  }
 }
 
 }  // namespace
