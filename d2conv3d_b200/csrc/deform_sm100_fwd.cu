@@ -407,7 +407,7 @@ struct Plan {
 
 bool make_plan(const Geom& g, bool x3, Plan* pl) {
   if (g.groups != 1) return false;
-  if (g.cpg % kBK != 0) return false;
+  if (g.cpg % (x3 ? 32 : kBK) != 0) return false;   // a unit must lie inside one offset group
   if (g.Cout % 64 != 0 || g.Cout > kMaxN) return false;
   if (g.Vin * g.Cin > 0x7fffffffLL) return false;                 // 32-bit element offsets within a clip
   if (g.K * 64 * (int)sizeof(float) > 48 * 1024) return false;    // weight staging kernel's smem

@@ -63,6 +63,29 @@ def test_forward_fp32_parity_mode_vs_oracle(dn, ci):
     assert err <= REL
 
 
+@pytest.mark.parametrize("cfg", [dict(B=1, Cin=64, Cout=64, dims=(3, 7, 8), G=2),
+                                 dict(B=2, Cin=256, Cout=256, dims=(2, 6, 9), G=8)])
+def test_forward_32_channels_per_offset_group(dn, cfg):
+    """32 channels per offset group (e.g. 256 channels in 8 groups): a 32-channel unit of the fp32-parity mode
+    still lies inside one group, so the forward stays on the tensor cores."""
+    from d2conv3d_b200 import _lib
+    p = make_problem(760, dtype=np.float32, offset_std=2.0, k=3, padding=1, **cfg)
+    _lib.profile_read(); _lib.profile_enable(True)
+    y = dn.deform_conv3d(cu(p["x"]), cu(p["geo"]), cu(p["mask"]), cu(p["weight"]), cu(p["bias"]), 1, 1, 1, 1,
+                         cfg["G"]).cpu().numpy()
+    _lib.profile_enable(False)
+    assert "fwd_sm100_fused" in [n for n, _ in _lib.profile_read()]
+    want = orc.deform_conv3d_fwd(p["x"], p["geo"], p["mask"], p["weight"], p["bias"], padding=1, offset_groups=cfg["G"])
+    assert np.abs(y - want).max() <= REL * np.abs(want).max()
+    # the backward of such a shape runs on the generic tier and must still be right
+    ts = [cu(p[k]).requires_grad_() for k in ("x", "geo", "mask", "weight", "bias")]
+    dn.deform_conv3d(*ts, 1, 1, 1, 1, cfg["G"]).backward(cu(p["gy"]))
+    wantg = orc.deform_conv3d_bwd(p["gy"], p["x"], p["geo"], p["mask"], p["weight"], True, padding=1,
+                                  offset_groups=cfg["G"])
+    for t, w_ in zip(ts, wantg):
+        assert np.abs(t.grad.cpu().numpy() - w_).max() <= REL * np.abs(w_).max()
+
+
 def test_integer_and_border_coordinates(dn):
     """Offsets that put samples exactly on voxels, on the -1 / size borders and far outside: the clamped
     stand-in corners must contribute exactly nothing."""
