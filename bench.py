@@ -511,6 +511,9 @@ EXTRA_WORKLOADS = {
     # BASELINE config 4: depthwise 3x3x3 of an ir-CSN bottleneck, then the modulated deformable 1024->256 stage
     "c4-depthwise": dict(kind="depthwise", B=8, C=1024, dims=(8, 30, 54)),
     "c4-md": dict(kind="deform", B=8, Cin=1024, Cout=256, dims=(8, 30, 54), G=8),
+    # BASELINE config 5 (decoder inference): the xyz dynamic-dilated 256->256 conv of a refine block at the
+    # stride-4 pyramid level, one clip, 8 offset groups (32 channels per group), forward only
+    "c5-e1": dict(kind="dyndil", mode="xyz", B=1, Cin=256, Cout=256, dims=(8, 120, 214), G=8, fwd_only=True),
 }
 
 
@@ -561,9 +564,12 @@ def run_extra_workload(args):
             t.grad = None
         flush.zero_()
         e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-        e[0].record(); y = fwd(); e[1].record(); y.backward(gy); e[2].record()
+        e[0].record(); y = fwd(); e[1].record()
+        if not wl.get("fwd_only"):
+            y.backward(gy)
+        e[2].record()
         torch.cuda.synchronize()
-        return e[0].elapsed_time(e[1]), e[1].elapsed_time(e[2])
+        return e[0].elapsed_time(e[1]), max(e[1].elapsed_time(e[2]), 1e-9)
 
     for _ in range(max(3, args.warmup)):
         one()

@@ -441,14 +441,22 @@ int sm_count_cached(int* out) {
   return D2C_OK;
 }
 
-inline bool mode_is_x3(int math_mode) { return math_mode != D2C_MATH_BF16; }
+// Which variant serves this shape in this math mode: bf16 mode takes the single-pass kernel where it applies
+// and otherwise the (more exact) split kernel, e.g. for 32 channels per offset group; auto / bf16x3 take the
+// split kernel only.  Returns false when the tensor-core tier does not apply.
+bool pick_variant(const Geom& g, int math_mode, bool* x3, Plan* pl) {
+  if (math_mode == D2C_MATH_FP32) return false;
+  if (math_mode == D2C_MATH_BF16 && make_plan(g, false, pl)) { *x3 = false; return true; }
+  if (make_plan(g, true, pl)) { *x3 = true; return true; }
+  return false;
+}
 
 template <typename Coords>
 int run_fwd(const Geom& g, int math_mode, const Coords& coords, const float* x, const float* mask, const float* w,
             const float* bias, float* y, void* ws, cudaStream_t st) {
-  const bool x3 = mode_is_x3(math_mode);
+  bool x3 = false;
   Plan pl;
-  if (!make_plan(g, x3, &pl)) return D2C_ERR_MODE;
+  if (!pick_variant(g, math_mode, &x3, &pl)) return D2C_ERR_MODE;
   uint8_t* wsp = reinterpret_cast<uint8_t*>(ws);
   void* x_cl = wsp; wsp += pl.x_cl_bytes;
   uint8_t* w_sw = wsp; wsp += pl.w_sw_bytes;
@@ -554,15 +562,16 @@ int run_fwd(const Geom& g, int math_mode, const Coords& coords, const float* x, 
 
 bool sm100_fwd_supported(const Geom& g, int dtype, int math_mode) {
   if (dtype != D2C_F32) return false;
-  if (math_mode == D2C_MATH_FP32) return false;
+  bool x3;
   Plan pl;
-  return make_plan(g, mode_is_x3(math_mode), &pl);
+  return pick_variant(g, math_mode, &x3, &pl);
 }
 
 size_t sm100_fwd_workspace(const Geom& g, int dtype, int math_mode) {
   if (!sm100_fwd_supported(g, dtype, math_mode)) return 0;
+  bool x3;
   Plan pl;
-  make_plan(g, mode_is_x3(math_mode), &pl);
+  pick_variant(g, math_mode, &x3, &pl);
   return pl.x_cl_bytes + pl.w_sw_bytes + pl.rec_bytes;
 }
 

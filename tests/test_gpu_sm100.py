@@ -101,6 +101,19 @@ def test_unsupported_shapes_fall_back_to_generic_tier(dn):
     assert np.abs(y.cpu().numpy() - want).max() <= 1e-4 * np.abs(want).max()
 
 
+def test_bf16_mode_uses_split_kernel_for_32_channels_per_group(dn):
+    """32 channels per offset group do not fill a 64-channel single-pass unit; bf16 mode then runs the forward
+    on the split (fp32-parity) tensor-core kernel instead of leaving the tensor cores."""
+    from d2conv3d_b200 import _lib
+    p = make_problem(350, 2, 256, 128, (2, 6, 9), padding=1, G=8, dtype=np.float32, offset_std=2.0)
+    _lib.profile_read(); _lib.profile_enable(True)
+    y = dn.deform_conv3d(cu(p["x"]), cu(p["geo"]), cu(p["mask"]), cu(p["weight"]), cu(p["bias"]), 1, 1, 1, 1, 8)
+    _lib.profile_enable(False)
+    assert "fwd_sm100_fused" in [n for n, _ in _lib.profile_read()]
+    want = orc.deform_conv3d_fwd(p["x"], p["geo"], p["mask"], p["weight"], p["bias"], padding=1, offset_groups=8)
+    assert np.abs(y.cpu().numpy() - want).max() <= 1e-4 * np.abs(want).max()
+
+
 REL_BF16_GRAD = 2e-2
 
 
