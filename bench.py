@@ -504,6 +504,8 @@ def run_gpu_arm(args):
 
 
 EXTRA_WORKLOADS = {
+    # BASELINE config 1: the plumbing / correctness layer (launch-latency bound at this size)
+    "c1": dict(kind="deform", B=1, Cin=64, Cout=64, dims=(4, 16, 16), G=1, offset_std=1.0),
     # BASELINE config 3: dynamic-dilation conv3d, one field shared by all taps, optional 27-channel mask
     "c3-xyz": dict(kind="dyndil", mode="xyz", B=4, Cin=256, Cout=256, dims=(8, 60, 108), G=1),
     "c3-xy": dict(kind="dyndil", mode="xy", B=4, Cin=256, Cout=256, dims=(8, 60, 108), G=1),
@@ -547,7 +549,7 @@ def run_extra_workload(args):
         unit, peak = "GB/s", peaks["hbm_gbs"]
     else:
         p = make_problem(1003, wl["B"], wl["Cin"], wl["Cout"], wl["dims"], k=3, padding=1, G=wl["G"],
-                         dtype=np.float32, offset_std=2.0, field_mode=wl.get("mode"))
+                         dtype=np.float32, offset_std=wl.get("offset_std", 2.0), field_mode=wl.get("mode"))
         ts = [torch.from_numpy(p[k]).to(dev).requires_grad_() for k in ("x", "geo", "mask", "weight", "bias")]
         gy = torch.from_numpy(p["gy"]).to(dev)
         if wl["kind"] == "dyndil":
