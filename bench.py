@@ -519,6 +519,74 @@ EXTRA_WORKLOADS = {
 }
 
 
+def run_decoder_workload(args):
+    """BASELINE config 5: decoder inference on synthetic ir-CSN features, clips sharded over the ranks with no
+    collective (one process per GPU under torchrun; one rank otherwise).  Every rank pushes its share of the 32
+    clips through the decoder one clip at a time (forward only, no_grad); rank 0 prints clips/s of the whole job
+    from the slowest rank's CUDA-event time."""
+    import torch
+    import torch.distributed as dist
+
+    import d2conv3d_b200
+    from d2conv3d_b200 import _lib, decoder
+
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.lib()
+    d2conv3d_b200.set_math_mode(args.mode)
+    torch.manual_seed(1005)
+    net = decoder.Decoder().to(dev).eval()
+    for m in net.modules():                          # non-trivial deformation: random predictor weights
+        if hasattr(m, "deform_params"):
+            torch.nn.init.normal_(m.deform_params.weight, std=0.02)
+    total_clips = args.clips
+    mine = decoder_share(total_clips, rank, world)
+    g = torch.Generator().manual_seed(1005 + rank)
+    feats = [torch.relu(torch.randn(s, generator=g)).to(dev) for s in decoder.pyramid_shapes(1)]
+
+    def one_clip():
+        with torch.no_grad():
+            return net(*feats)
+
+    for _ in range(2):
+        one_clip()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    launches0 = _lib.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(mine):
+        out = one_clip()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    _lib.device_status()
+    if rank == 0:
+        print(json.dumps({
+            "workload": "c5-decoder", "metric": "decoder_inference_clips_per_s", "value": total_clips / (float(ms.item()) * 1e-3),
+            "unit": "clips/s", "n_gpus": world, "clips": total_clips, "clips_per_rank": mine,
+            "ms_per_clip": float(ms.item()) / mine, "math_mode": _lib.get_math_mode(), "scaling": "strong",
+            "deformable_layers": net.converted, "gpu_launches_per_clip": (_lib.launch_count() - launches0) // max(1, mine),
+            "output_shape": list(out.shape), "data": "synthetic ReLU(N(0,1)) features, random-init decoder",
+            "config": {"features": [list(s) for s in decoder.pyramid_shapes(total_clips)],
+                       "decoder": "GC bridge + 3 refine blocks, xyz dilation-field + mask conv3d 3x3x3, Cout 256, 8 offset groups",
+                       "collective": "none"}}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def decoder_share(total, rank, world):
+    """Clips of rank `rank`: contiguous shares, the first `total % world` ranks take one more."""
+    return total // world + (1 if rank < total % world else 0)
+
+
 def run_extra_workload(args):
     """Secondary configurations (not the headline line): prints one JSON line with forward / backward
     milliseconds from CUDA events, contraction TFLOP/s or GB/s against the measured peaks."""
@@ -601,12 +669,15 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-reference-gpu", action="store_true")
-    ap.add_argument("--workload", default="c2", choices=["c2"] + sorted(EXTRA_WORKLOADS),
+    ap.add_argument("--clips", type=int, default=32, help="c5-decoder: clips of the whole job")
+    ap.add_argument("--workload", default="c2", choices=["c2", "c5-decoder"] + sorted(EXTRA_WORKLOADS),
                     help="c2 = the headline line (default); the others print a secondary line for one GPU")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.workload == "c5-decoder":
+        run_decoder_workload(args)
     elif args.workload != "c2":
         run_extra_workload(args)
     else:

@@ -71,6 +71,10 @@ def lib():
         L.d2c_dyn_dilated_conv3d_fwd.argtypes = [dp, i32] + [vp] * 7 + [sz, vp]
         L.d2c_dyn_dilated_conv3d_bwd.argtypes = [dp, i32] + [vp] * 11 + [sz, vp]
         L.d2c_dyn_dilated_conv3d_corners.argtypes = [dp, i32, vp, vp, vp]
+        L.d2c_act_group_norm_workspace_bytes.argtypes = [i32, i32]
+        L.d2c_act_group_norm_workspace_bytes.restype = sz
+        L.d2c_act_group_norm_fwd.argtypes = [vp, vp, vp, vp, i32, i32, ctypes.c_longlong, i32, ctypes.c_float, i32,
+                                             vp, sz, vp]
         L.d2c_depthwise_conv3d_fwd.argtypes = [dp] + [vp] * 4 + [vp]
         L.d2c_depthwise_conv3d_bwd.argtypes = [dp] + [vp] * 7 + [sz, vp]
         L.d2c_depthwise_conv3d_bwd_noalloc.argtypes = [dp] + [vp] * 6 + [vp]
@@ -154,3 +158,19 @@ def profile_read(max_records=65536):
     n = ctypes.c_int(0)
     check(lib().d2c_profile_read(recs, max_records, ctypes.byref(n)), "profile_read")
     return [(recs[i].name.decode(), float(recs[i].ms)) for i in range(n.value)]
+
+
+def act_group_norm(x, weight, bias, groups, eps=1e-5, relu=True):
+    """y = GroupNorm(relu(x)) (forward only) for a contiguous fp32 CUDA tensor [B, C, *spatial]."""
+    if not (x.is_cuda and x.dtype == torch.float32 and x.is_contiguous()):
+        raise RuntimeError("act_group_norm expects a contiguous fp32 CUDA tensor")
+    B, C = x.shape[0], x.shape[1]
+    spatial = x.numel() // (B * C)
+    L = lib()
+    with torch.cuda.device(x.device):
+        y = torch.empty_like(x)
+        n = L.d2c_act_group_norm_workspace_bytes(B, groups)
+        ws = torch.empty(n, dtype=torch.uint8, device=x.device)
+        check(L.d2c_act_group_norm_fwd(ptr(x), ptr(weight), ptr(bias), ptr(y), B, C, spatial, groups, float(eps),
+                                       1 if relu else 0, ptr(ws), n, stream_of(x)), "act_group_norm")
+    return y

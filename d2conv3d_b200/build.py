@@ -15,7 +15,8 @@ INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 LIB = os.path.join(HERE, "libd2conv3d.so")
 OBJ_DIR = os.path.join(HERE, "build")
 
-SOURCES = ["d2c_api.cu", "depthwise.cu", "deform_sm100_fwd.cu", "deform_sm100_bwd.cu", "deform_sm100_dw.cu"]
+SOURCES = ["d2c_api.cu", "depthwise.cu", "deform_sm100_fwd.cu", "deform_sm100_bwd.cu", "deform_sm100_dw.cu",
+           "act_norm.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-I", INCLUDE,
