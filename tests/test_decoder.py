@@ -89,3 +89,11 @@ def test_fused_relu_group_norm_matches_torch(shape, groups):
     y2 = _lib.act_group_norm(x, None, None, groups, 1e-5, relu=False)
     ref2 = torch.nn.functional.group_norm(x, groups, None, None, 1e-5)
     assert float((y2 - ref2).abs().max()) <= 1e-5 * max(1.0, float(ref2.abs().max()))
+
+
+def test_clip_shares_cover_the_job():
+    import bench
+    for total in (32, 7, 1):
+        for world in (1, 2, 4, 8):
+            shares = [bench.decoder_share(total, r, world) for r in range(world)]
+            assert sum(shares) == total and max(shares) - min(shares) <= 1
