@@ -75,6 +75,9 @@ def lib():
         L.d2c_act_group_norm_workspace_bytes.restype = sz
         L.d2c_act_group_norm_fwd.argtypes = [vp, vp, vp, vp, i32, i32, ctypes.c_longlong, i32, ctypes.c_float, i32,
                                              vp, sz, vp]
+        L.d2c_act_group_norm_bwd_workspace_bytes.argtypes = [i32, i32, i32]
+        L.d2c_act_group_norm_bwd_workspace_bytes.restype = sz
+        L.d2c_act_group_norm_bwd.argtypes = [vp] * 7 + [i32, i32, ctypes.c_longlong, i32, ctypes.c_float, i32, vp, sz, vp]
         L.d2c_depthwise_conv3d_fwd.argtypes = [dp] + [vp] * 4 + [vp]
         L.d2c_depthwise_conv3d_bwd.argtypes = [dp] + [vp] * 7 + [sz, vp]
         L.d2c_depthwise_conv3d_bwd_noalloc.argtypes = [dp] + [vp] * 6 + [vp]
@@ -160,17 +163,43 @@ def profile_read(max_records=65536):
     return [(recs[i].name.decode(), float(recs[i].ms)) for i in range(n.value)]
 
 
+class _ActGroupNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, groups, eps, relu):
+        if not (x.is_cuda and x.dtype == torch.float32):
+            raise RuntimeError("act_group_norm expects an fp32 CUDA tensor")
+        x = x.contiguous()
+        B, C = x.shape[0], x.shape[1]
+        spatial = x.numel() // (B * C)
+        L = lib()
+        with torch.cuda.device(x.device):
+            y = torch.empty_like(x)
+            n = L.d2c_act_group_norm_workspace_bytes(B, groups)
+            stats = torch.empty(n, dtype=torch.uint8, device=x.device)
+            check(L.d2c_act_group_norm_fwd(ptr(x), ptr(weight), ptr(bias), ptr(y), B, C, spatial, groups, float(eps),
+                                           1 if relu else 0, ptr(stats), n, stream_of(x)), "act_group_norm")
+        ctx.save_for_backward(x, weight, stats)
+        ctx.cfg = (B, C, spatial, groups, float(eps), 1 if relu else 0, bias is not None)
+        return y
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, gy):
+        x, weight, stats = ctx.saved_tensors
+        B, C, spatial, groups, eps, relu, has_bias = ctx.cfg
+        gy = gy.contiguous()
+        L = lib()
+        with torch.cuda.device(x.device):
+            gx = torch.empty_like(x)
+            gw = torch.empty(C, dtype=torch.float32, device=x.device) if weight is not None else None
+            gb = torch.empty(C, dtype=torch.float32, device=x.device) if has_bias else None
+            n = L.d2c_act_group_norm_bwd_workspace_bytes(B, C, groups)
+            ws = torch.empty(n, dtype=torch.uint8, device=x.device)
+            check(L.d2c_act_group_norm_bwd(ptr(x), ptr(weight), ptr(gy), ptr(stats), ptr(gx), ptr(gw), ptr(gb), B, C,
+                                           spatial, groups, eps, relu, ptr(ws), n, stream_of(x)), "act_group_norm backward")
+        return gx, gw, gb, None, None, None
+
+
 def act_group_norm(x, weight, bias, groups, eps=1e-5, relu=True):
-    """y = GroupNorm(relu(x)) (forward only) for a contiguous fp32 CUDA tensor [B, C, *spatial]."""
-    if not (x.is_cuda and x.dtype == torch.float32 and x.is_contiguous()):
-        raise RuntimeError("act_group_norm expects a contiguous fp32 CUDA tensor")
-    B, C = x.shape[0], x.shape[1]
-    spatial = x.numel() // (B * C)
-    L = lib()
-    with torch.cuda.device(x.device):
-        y = torch.empty_like(x)
-        n = L.d2c_act_group_norm_workspace_bytes(B, groups)
-        ws = torch.empty(n, dtype=torch.uint8, device=x.device)
-        check(L.d2c_act_group_norm_fwd(ptr(x), ptr(weight), ptr(bias), ptr(y), B, C, spatial, groups, float(eps),
-                                       1 if relu else 0, ptr(ws), n, stream_of(x)), "act_group_norm")
-    return y
+    """y = GroupNorm(relu(x)) for an fp32 CUDA tensor [B, C, *spatial]; differentiable in x, weight, bias."""
+    return _ActGroupNorm.apply(x, weight, bias, int(groups), float(eps), bool(relu))

@@ -1,4 +1,4 @@
-// Fused activation + group normalisation, forward (inference): y = GroupNorm(relu(x)) for NCDHW fp32 tensors.
+// Fused activation + group normalisation, forward and backward: y = GroupNorm(relu(x)) for NCDHW fp32 tensors.
 //
 // The unit right after every convolution of the reference's refine blocks is `ActivationType(), NormType(planes)`
 // with NormType = GroupNorm (network/modules/refinement.py:38-43; network/segmentation/encoder_decoder.py:116-119).
@@ -119,6 +119,154 @@ extern "C" int d2c_act_group_norm_fwd(const float* x, const float* gamma, const 
   if (perc < 1) perc = 1;
   act_normalize_kernel<<<dim3((unsigned)perc, (unsigned)bc), 256, 0, st>>>(x, gamma, beta, y, channels, cpg_norm, spatial,
                                                                        group_elems, eps, apply_relu, vec_n, ws);
+  D2C_LAUNCH_CHECK();
+  prof_mark(st, nullptr);
+  return D2C_OK;
+}
+
+// ---- backward ------------------------------------------------------------------------------------------
+// With a = act(x), ah = (a - mean) * rstd, y = ah * gamma + beta and N = elements of a group:
+//   grad_beta[c]  = sum_{b,v} gy           grad_gamma[c] = sum_{b,v} gy * ah
+//   grad_a = rstd * (gamma*gy - S1/N - ah * S2/N),  S1 = sum_group gamma*gy,  S2 = sum_group gamma*gy*ah
+//   grad_x = grad_a * (x > 0)   (relu)
+// Three passes: per-(clip, channel) sums t1 = sum_v gy, t2 = sum_v gy*ah (grid-wide, fp64 atomics); a tiny
+// kernel that folds them into S1, S2 per (clip, group) and grad_gamma / grad_beta; the streaming grad_x pass.
+namespace d2c {
+namespace {
+
+__device__ __forceinline__ void group_stats(const double* __restrict__ stats, long long bg, long long n, float eps,
+                                            float& mean, float& rstd) {
+  const double m = stats[2 * bg] / (double)n;
+  const double var = fmax(stats[2 * bg + 1] / (double)n - m * m, 0.0);
+  mean = (float)m;
+  rstd = (float)(1.0 / sqrt(var + (double)eps));
+}
+
+// t: [batch*channels][2] doubles, zeroed before.
+__global__ void __launch_bounds__(256)
+act_norm_bwd_sums_kernel(const float* __restrict__ x, const float* __restrict__ gy, int channels, int cpg_norm,
+                         long long spatial, long long group_elems, float eps, int apply_relu,
+                         const double* __restrict__ stats, double* __restrict__ t) {
+  const long long bc = blockIdx.y;
+  const int c = (int)(bc % channels);
+  const long long bg = (bc / channels) * (channels / cpg_norm) + c / cpg_norm;
+  float mean, rstd;
+  group_stats(stats, bg, group_elems, eps, mean, rstd);
+  const float* px = x + bc * spatial;
+  const float* pg = gy + bc * spatial;
+  float s1 = 0.f, s2 = 0.f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < spatial; i += (long long)gridDim.x * blockDim.x) {
+    float a = __ldg(px + i);
+    if (apply_relu) a = fmaxf(a, 0.f);
+    const float g = __ldg(pg + i);
+    s1 += g;
+    s2 += g * ((a - mean) * rstd);
+  }
+  double d1 = s1, d2 = s2;
+#pragma unroll
+  for (int o = 16; o >= 1; o >>= 1) {
+    d1 += __shfl_xor_sync(0xffffffffu, d1, o);
+    d2 += __shfl_xor_sync(0xffffffffu, d2, o);
+  }
+  __shared__ double red[2][8];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { red[0][warp] = d1; red[1][warp] = d2; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double a = 0, b = 0;
+    for (int w = 0; w < 8; ++w) { a += red[0][w]; b += red[1][w]; }
+    atomicAdd(t + 2 * bc, a);
+    atomicAdd(t + 2 * bc + 1, b);
+  }
+}
+
+// One thread per channel: grad_gamma / grad_beta over the clips; one thread per (clip, group): S1, S2.
+__global__ void __launch_bounds__(256)
+act_norm_bwd_fold_kernel(int batch, int channels, int groups, const float* __restrict__ gamma,
+                         const double* __restrict__ t, double* __restrict__ s, float* __restrict__ grad_gamma,
+                         float* __restrict__ grad_beta) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < channels) {
+    double a = 0, b = 0;
+    for (int bb = 0; bb < batch; ++bb) { a += t[2 * ((long long)bb * channels + i)]; b += t[2 * ((long long)bb * channels + i) + 1]; }
+    if (grad_beta) grad_beta[i] = (float)a;
+    if (grad_gamma) grad_gamma[i] = (float)b;
+  }
+  if (i < batch * groups) {
+    const int bb = i / groups, gidx = i % groups, cpg_norm = channels / groups;
+    double a = 0, b = 0;
+    for (int c = gidx * cpg_norm; c < (gidx + 1) * cpg_norm; ++c) {
+      const double ga = gamma ? (double)gamma[c] : 1.0;
+      a += ga * t[2 * ((long long)bb * channels + c)];
+      b += ga * t[2 * ((long long)bb * channels + c) + 1];
+    }
+    s[2 * i] = a;
+    s[2 * i + 1] = b;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+act_norm_bwd_dx_kernel(const float* __restrict__ x, const float* __restrict__ gy, const float* __restrict__ gamma,
+                       float* __restrict__ gx, int channels, int cpg_norm, long long spatial, long long group_elems,
+                       float eps, int apply_relu, const double* __restrict__ stats, const double* __restrict__ s) {
+  const long long bc = blockIdx.y;
+  const int c = (int)(bc % channels);
+  const long long bg = (bc / channels) * (channels / cpg_norm) + c / cpg_norm;
+  float mean, rstd;
+  group_stats(stats, bg, group_elems, eps, mean, rstd);
+  const float ga = gamma ? __ldg(gamma + c) : 1.f;
+  const float m1 = (float)(s[2 * bg] / (double)group_elems), m2 = (float)(s[2 * bg + 1] / (double)group_elems);
+  const float* px = x + bc * spatial;
+  const float* pg = gy + bc * spatial;
+  float* po = gx + bc * spatial;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < spatial; i += (long long)gridDim.x * blockDim.x) {
+    const float xv = __ldg(px + i);
+    const float a = apply_relu ? fmaxf(xv, 0.f) : xv;
+    const float ah = (a - mean) * rstd;
+    const float da = rstd * (ga * __ldg(pg + i) - m1 - ah * m2);
+    po[i] = (apply_relu && !(xv > 0.f)) ? 0.f : da;
+  }
+}
+
+}  // namespace
+}  // namespace d2c
+
+extern "C" size_t d2c_act_group_norm_bwd_workspace_bytes(int batch, int channels, int groups) {
+  const size_t b = batch > 0 ? batch : 0;
+  return d2c::align_up(sizeof(double) * 2 * b * (size_t)(channels > 0 ? channels : 0), 256) +
+         d2c::align_up(sizeof(double) * 2 * b * (size_t)(groups > 0 ? groups : 0), 256);
+}
+
+extern "C" int d2c_act_group_norm_bwd(const float* x, const float* gamma, const float* grad_y, const void* fwd_stats,
+                                      float* grad_x, float* grad_gamma, float* grad_beta, int batch, int channels,
+                                      long long spatial, int groups, float eps, int apply_relu, void* workspace,
+                                      size_t workspace_bytes, d2c_stream_t stream) {
+  using namespace d2c;
+  if (!x || !grad_y || !fwd_stats || !grad_x || !workspace) return D2C_ERR_NULL;
+  if (batch < 1 || channels < 1 || spatial < 1 || groups < 1 || channels % groups != 0) return D2C_ERR_SHAPE;
+  if (workspace_bytes < d2c_act_group_norm_bwd_workspace_bytes(batch, channels, groups)) return D2C_ERR_WORKSPACE;
+  const long long bc = (long long)batch * channels;
+  if (bc > 65535) return D2C_ERR_TOO_LARGE;
+  const int cpg_norm = channels / groups;
+  const long long group_elems = (long long)cpg_norm * spatial;
+  cudaStream_t st = (cudaStream_t)stream;
+  double* t = reinterpret_cast<double*>(workspace);
+  double* s = reinterpret_cast<double*>(reinterpret_cast<uint8_t*>(workspace) + align_up(sizeof(double) * 2 * (size_t)bc, 256));
+  const double* stats = reinterpret_cast<const double*>(fwd_stats);
+  D2C_CUDA_TRY(cudaMemsetAsync(t, 0, sizeof(double) * 2 * (size_t)bc, st));
+  prof_mark(st, "act_group_norm_bwd");
+  long long per = (148LL * 8 + bc - 1) / bc;
+  const long long maxb = (spatial + 255) / 256;
+  if (per > maxb) per = maxb;
+  if (per < 1) per = 1;
+  act_norm_bwd_sums_kernel<<<dim3((unsigned)per, (unsigned)bc), 256, 0, st>>>(x, grad_y, channels, cpg_norm, spatial,
+                                                                           group_elems, eps, apply_relu, stats, t);
+  D2C_LAUNCH_CHECK();
+  const int n = channels > batch * groups ? channels : batch * groups;
+  act_norm_bwd_fold_kernel<<<(n + 255) / 256, 256, 0, st>>>(batch, channels, groups, gamma, t, s, grad_gamma, grad_beta);
+  D2C_LAUNCH_CHECK();
+  act_norm_bwd_dx_kernel<<<dim3((unsigned)per, (unsigned)bc), 256, 0, st>>>(x, grad_y, gamma, grad_x, channels, cpg_norm,
+                                                                         spatial, group_elems, eps, apply_relu, stats, s);
   D2C_LAUNCH_CHECK();
   prof_mark(st, nullptr);
   return D2C_OK;

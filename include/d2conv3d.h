@@ -220,13 +220,20 @@ int d2c_depthwise_conv3d_bwd(const d2c_conv_desc* desc, const void* grad_y, cons
                              const void* w, void* grad_x, void* grad_w, void* grad_bias,
                              void* workspace, size_t workspace_bytes, d2c_stream_t stream);
 
-/* y = GroupNorm(act(x)) for a contiguous fp32 NCDHW tensor, forward only (inference), act = relu when
+/* y = GroupNorm(act(x)) for a contiguous fp32 NCDHW tensor, act = relu when
  * apply_relu != 0 else identity.  Replaces the `ActivationType(), NormType(planes)` tail of every conv unit of
  * the reference's refine blocks (network/modules/refinement.py:38-43 with NormType = GroupNorm,
  * network/segmentation/encoder_decoder.py:116-119) as two grid-wide streaming passes; statistics follow
  * torch.nn.GroupNorm (biased variance over the group's channels x voxels, eps inside the square root);
  * gamma / beta [channels] may be NULL (1 / 0).  x and y must not overlap.  workspace: see the size function. */
 size_t d2c_act_group_norm_workspace_bytes(int batch, int groups);
+/* Backward of the same unit: grad_x (and, when not NULL, grad_gamma / grad_beta [channels]) from grad_y.
+ * fwd_stats = the forward call's workspace, kept unchanged since (it holds the per-(clip, group) sums). */
+size_t d2c_act_group_norm_bwd_workspace_bytes(int batch, int channels, int groups);
+int d2c_act_group_norm_bwd(const float* x, const float* gamma, const float* grad_y, const void* fwd_stats,
+                           float* grad_x, float* grad_gamma, float* grad_beta, int batch, int channels,
+                           long long spatial, int groups, float eps, int apply_relu, void* workspace,
+                           size_t workspace_bytes, d2c_stream_t stream);
 int d2c_act_group_norm_fwd(const float* x, const float* gamma, const float* beta, float* y, int batch, int channels,
                            long long spatial, int groups, float eps, int apply_relu, void* workspace,
                            size_t workspace_bytes, d2c_stream_t stream);
