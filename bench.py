@@ -582,6 +582,50 @@ def run_decoder_workload(args):
         dist.destroy_process_group()
 
 
+def run_block_workload(args):
+    """ir-CSN stage-4 bottleneck block (1024 -> 256 -> depthwise 3x3x3 -> 1024) at 8x30x54, B = 8, forward +
+    backward in training mode: the depthwise kernels measured where the reference uses them; the 1x1x1
+    convolutions and batch norms are cuDNN / PyTorch."""
+    import torch
+
+    from d2conv3d_b200 import _lib
+    from d2conv3d_b200.backbone import IrBottleneck3d
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    _lib.lib()
+    torch.manual_seed(1004)
+    blk = IrBottleneck3d(1024, 256).to(dev).train()
+    x = torch.randn(8, 1024, 8, 30, 54, device=dev, requires_grad=True)
+    gy = torch.randn(8, 1024, 8, 30, 54, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def one():
+        x.grad = None
+        blk.zero_grad(set_to_none=True)
+        flush.zero_()
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        e[0].record(); y = blk(x); e[1].record(); y.backward(gy); e[2].record()
+        torch.cuda.synchronize()
+        return e[0].elapsed_time(e[1]), e[1].elapsed_time(e[2])
+
+    for _ in range(max(3, args.warmup)):
+        one()
+    _lib.profile_read(); _lib.profile_enable(True)
+    runs = [one() for _ in range(args.steps)]
+    _lib.profile_enable(False)
+    ph = {}
+    for k, v in _lib.profile_read():
+        ph[k] = ph.get(k, 0.0) + v / args.steps
+    f_ms = statistics.median(r[0] for r in runs)
+    b_ms = statistics.median(r[1] for r in runs)
+    print(json.dumps({
+        "workload": "c4-block", "config": "ir-CSN bottleneck 1024->256->1024, depthwise 3x3x3 on 256 channels, B=8, 8x30x54, train mode",
+        "steps": args.steps, "fwd_ms": f_ms, "bwd_ms": b_ms, "clips_per_s_fwd_bwd": 8 / ((f_ms + b_ms) * 1e-3),
+        "depthwise_ms_per_step": {k: round(v, 4) for k, v in ph.items()},
+        "depthwise_share": sum(ph.values()) / (f_ms + b_ms)}), flush=True)
+
+
 def decoder_share(total, rank, world):
     """Clips of rank `rank`: contiguous shares, the first `total % world` ranks take one more."""
     return total // world + (1 if rank < total % world else 0)
@@ -670,7 +714,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-reference-gpu", action="store_true")
     ap.add_argument("--clips", type=int, default=32, help="c5-decoder: clips of the whole job")
-    ap.add_argument("--workload", default="c2", choices=["c2", "c5-decoder"] + sorted(EXTRA_WORKLOADS),
+    ap.add_argument("--workload", default="c2", choices=["c2", "c4-block", "c5-decoder"] + sorted(EXTRA_WORKLOADS),
                     help="c2 = the headline line (default); the others print a secondary line for one GPU")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -678,6 +722,8 @@ def main():
         run_reference_arm(args)
     elif args.workload == "c5-decoder":
         run_decoder_workload(args)
+    elif args.workload == "c4-block":
+        run_block_workload(args)
     elif args.workload != "c2":
         run_extra_workload(args)
     else:
