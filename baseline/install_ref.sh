@@ -4,7 +4,7 @@
 # only as a GPU-side parity oracle and as the "kernel to beat" timing -- never on the product path.
 # The reference checkout is read-only, so the build runs from a copy under /tmp.
 set -euo pipefail
-REF=${1:-/root/reference}
+REF=${1:?usage: install_ref.sh <path of the reference checkout>}
 HERE=$(cd "$(dirname "$0")" && pwd)
 WORK=$(mktemp -d /tmp/refbuild.XXXXXX)
 export TORCH_CUDA_ARCH_LIST=10.0 MAX_JOBS=8 CC=/usr/bin/gcc CXX=/usr/bin/g++

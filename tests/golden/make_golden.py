@@ -29,7 +29,9 @@ import torch
 from torch.nn.modules.utils import _triple
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    raise SystemExit("usage: make_golden.py <path of the reference checkout>")
+REF = sys.argv[1]
 
 
 def _load(path, name):
