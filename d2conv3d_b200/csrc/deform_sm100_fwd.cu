@@ -84,16 +84,19 @@ __device__ __forceinline__ void cta_unit_range(long long n_units, long long& beg
 // kX3 = 1: math mode bf16x3, the fp32-parity mode: a unit is 32 channels; the A row holds [hi(32) | lo(32)] of
 //          the fp32 blend, the weight row [hi(32) | lo(32)] of the fp32 weight, and the issuer forms
 //          a_hi*b_hi + a_lo*b_hi + a_hi*b_lo from the 16-channel K sub-blocks of the same two tiles.
-template <int kX3>
+// kDual = 1 (single-pass mode only): 32 channels per offset group, a 64-channel unit spans two groups.
+template <int kX3, int kDual>
 __global__ void __launch_bounds__(kThreads, 1)
 fwd_sm100_kernel(const FwdParams p) {
   constexpr int kUnitCh = kX3 ? 32 : 64;
+  constexpr int kRStage = (1 + kDual) * kRecBytes + 16;      // record set(s) + unit header
+  constexpr int hdr_off = (1 + kDual) * kRecBytes;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = ptx::smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - raw);
   const int rec_off = kAStages * kAStageBytes + p.b_stages * p.b_stage_bytes;
-  const int bar_off = rec_off + kRStages * kRStageBytes;
+  const int bar_off = rec_off + kRStages * kRStage;
   const uint32_t a_base = base, b_base = base + kAStages * kAStageBytes, rec_base = base + rec_off,
                  bar_base = base + bar_off;
   auto a_full = [&](int s) { return bar_base + 8u * s; };
@@ -236,19 +239,24 @@ fwd_sm100_kernel(const FwdParams p) {
       for (long long u = u_beg; u < u_end; ++u, ++k) {
         const int tile = (int)(u / p.S), s = (int)(u % p.S);
         const int b = tile / p.tiles_per_clip, v0 = (tile % p.tiles_per_clip) * kBM;
-        const int gt = s / p.nh, tap = gt % g.K, grp = gt / g.K;
+        const int gt = s / p.nh, tap = gt % g.K, grp = gt / g.K;      // dual: grp is the index of a group PAIR
         const int sr = k % kRStages;
         if (!ptx::mbar_wait(r_empty(sr), ((k / kRStages) & 1) ^ 1, abort_flag, 200)) break;
         const int rows = min(kBM, g.V - v0), h = s % p.nh;
         // unit header for the gather warps (no index arithmetic there); ordered before their reads by the
         // release of the arrive below and the acquire of their wait
-        uint8_t* hdr = base_ptr + rec_off + sr * kRStageBytes + kRecBytes;
-        *reinterpret_cast<long long*>(hdr) = (long long)b * g.Vin * g.Cin + grp * g.cpg + h * kUnitCh;
+        uint8_t* hdr = base_ptr + rec_off + sr * kRStage + hdr_off;
+        *reinterpret_cast<long long*>(hdr) =
+            (long long)b * g.Vin * g.Cin + grp * (kDual ? 2 * g.cpg : g.cpg) + h * kUnitCh;
         *reinterpret_cast<int*>(hdr + 8) = rows;
         const uint32_t bytes = (uint32_t)rows * 48u;
-        ptx::mbar_arrive_expect_tx(r_full(sr), bytes);
-        ptx::bulk_g2s(rec_base + sr * kRStageBytes, p.recs + 3 * ((((long long)b * g.G + grp) * g.K + tap) * g.V + v0),
-                      bytes, r_full(sr));
+        ptx::mbar_arrive_expect_tx(r_full(sr), bytes * (uint32_t)(1 + kDual));
+#pragma unroll
+        for (int set = 0; set <= kDual; ++set) {
+          const int og = kDual ? 2 * grp + set : grp;      // offset group whose records fill this set
+          ptx::bulk_g2s(rec_base + sr * kRStage + set * kRecBytes,
+                        p.recs + 3 * ((((long long)b * g.G + og) * g.K + tap) * g.V + v0), bytes, r_full(sr));
+        }
       }
       const uint32_t issued = k;
       for (uint32_t q = (issued > (uint32_t)kRStages ? issued - kRStages : 0); q < issued; ++q) {
@@ -273,9 +281,11 @@ fwd_sm100_kernel(const FwdParams p) {
     for (; k < n_my_units; ++k) {
       const int sr = k % kRStages, sa = k % kAStages;
       if (!ptx::mbar_wait(r_full(sr), (k / kRStages) & 1, abort_flag)) break;
-      const uint8_t* rec_stage = base_ptr + rec_off + sr * kRStageBytes;
-      const long long xoff = *reinterpret_cast<const long long*>(rec_stage + kRecBytes);
-      const int rows = *reinterpret_cast<const int*>(rec_stage + kRecBytes + 8);
+      const uint8_t* rec_base_ptr = base_ptr + rec_off + sr * kRStage;
+      const long long xoff = *reinterpret_cast<const long long*>(rec_base_ptr + hdr_off);
+      const int rows = *reinterpret_cast<const int*>(rec_base_ptr + hdr_off + 8);
+      // dual: 16-byte chunks 4-7 of a row (channels 32-63 of the unit) belong to the second offset group
+      const uint8_t* rec_stage = rec_base_ptr + ((kDual && j >= 4) ? kRecBytes : 0);
       // every corner of every row this thread owns goes in flight before the first blend
       uint4 c[kRowsPerThread][8];
 #pragma unroll
@@ -401,29 +411,33 @@ stage_weight_sw128_x3_kernel(int Cout, int Cin, int K, int cpg, int nh, const fl
 }
 
 struct Plan {
-  int nh, S, tiles_per_clip, n_tiles, b_stages, b_stage_bytes, tmem_cols, smem_bytes;
+  int nh, S, tiles_per_clip, n_tiles, b_stages, b_stage_bytes, tmem_cols, smem_bytes, dual, r_stage_bytes;
   size_t x_cl_bytes, w_sw_bytes, rec_bytes;
 };
 
 bool make_plan(const Geom& g, bool x3, Plan* pl) {
   if (g.groups != 1) return false;
-  if (g.cpg % (x3 ? 32 : kBK) != 0) return false;   // a unit must lie inside one offset group
+  // a unit must lie inside one offset group -- or, single-pass mode with 32 channels per group, span exactly two
+  const bool dual = !x3 && g.cpg == 32 && g.G % 2 == 0;
+  if (!dual && g.cpg % (x3 ? 32 : kBK) != 0) return false;
+  pl->dual = dual ? 1 : 0;
+  pl->r_stage_bytes = (1 + pl->dual) * kRecBytes + 16;
   if (g.Cout % 64 != 0 || g.Cout > kMaxN) return false;
   if (g.Vin * g.Cin > 0x7fffffffLL) return false;                 // 32-bit element offsets within a clip
   if (g.K * 64 * (int)sizeof(float) > 48 * 1024) return false;    // weight staging kernel's smem
-  pl->nh = g.cpg / (x3 ? 32 : kBK);
-  pl->S = g.G * g.K * pl->nh;
+  pl->nh = dual ? 1 : g.cpg / (x3 ? 32 : kBK);
+  pl->S = (dual ? g.G / 2 : g.G) * g.K * pl->nh;
   pl->tiles_per_clip = (g.V + kBM - 1) / kBM;
   pl->n_tiles = pl->tiles_per_clip * g.B;
   pl->b_stage_bytes = g.Cout * 128;
-  int nb = (kSmemLimit - 1024 - 256 - kAStages * kAStageBytes - kRStages * kRStageBytes) / pl->b_stage_bytes;
+  int nb = (kSmemLimit - 1024 - 256 - kAStages * kAStageBytes - kRStages * pl->r_stage_bytes) / pl->b_stage_bytes;
   if (nb > 4) nb = 4;
   if (nb < 2) return false;
   pl->b_stages = nb;
   int cols = 32;
   while (cols < g.Cout) cols <<= 1;
   pl->tmem_cols = cols;
-  pl->smem_bytes = kAStages * kAStageBytes + pl->b_stages * pl->b_stage_bytes + kRStages * kRStageBytes + 256 + 1024;
+  pl->smem_bytes = kAStages * kAStageBytes + pl->b_stages * pl->b_stage_bytes + kRStages * pl->r_stage_bytes + 256 + 1024;
   pl->x_cl_bytes = align_up((size_t)g.B * g.Vin * g.Cin * (x3 ? 4 : 2), 256);
   pl->w_sw_bytes = align_up((size_t)pl->S * pl->b_stage_bytes, 256);
   pl->rec_bytes = gather_records_bytes(g);
@@ -485,7 +499,7 @@ int run_fwd(const Geom& g, int math_mode, const Coords& coords, const float* x, 
       const char* e = getenv("D2C_SM100_PAIR");
       pair_enabled = (e && e[0] == '1') ? 1 : 0;
     }
-    if (pair_enabled && !x3 && pl.n_tiles >= 2 && pair_b_stages >= 2) {
+    if (pair_enabled && !x3 && !pl.dual && pl.n_tiles >= 2 && pair_b_stages >= 2) {
       D2C_CUDA_TRY(cudaFuncSetAttribute(pair::fwd_sm100_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pair_smem));
       cudaLaunchConfig_t cfg = {};
       cfg.gridDim = dim3(2 * (unsigned)sm_count, 1, 1);
@@ -520,7 +534,8 @@ int run_fwd(const Geom& g, int math_mode, const Coords& coords, const float* x, 
       stage_input_cl_f16_kernel<<<sgrid, 256, 0, st>>>(g.Cin, g.Vin, x, reinterpret_cast<__half*>(x_cl));
       D2C_LAUNCH_CHECK();
       dim3 wgrid((unsigned)g.Cout, (unsigned)(g.Cin / 64));
-      stage_weight_sw128_kernel<<<wgrid, 64, 64 * g.K * sizeof(float), st>>>(g.Cout, g.Cin, g.K, g.cpg, pl.nh, w, w_sw);
+      stage_weight_sw128_kernel<<<wgrid, 64, 64 * g.K * sizeof(float), st>>>(g.Cout, g.Cin, g.K,
+                                                                              pl.dual ? 64 : g.cpg, pl.nh, w, w_sw);
       D2C_LAUNCH_CHECK();
     }
     if ((rc = launch_sample_records(g, coords, mask, nullptr, recs, st, x3))) return rc;
@@ -547,11 +562,14 @@ int run_fwd(const Geom& g, int math_mode, const Coords& coords, const float* x, 
   }
   prof_mark(st, "fwd_sm100_fused");
   if (x3) {
-    D2C_CUDA_TRY(cudaFuncSetAttribute(fwd_sm100_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes));
-    fwd_sm100_kernel<1><<<(unsigned)grid, kThreads, pl.smem_bytes, st>>>(p);
+    D2C_CUDA_TRY(cudaFuncSetAttribute(fwd_sm100_kernel<1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes));
+    fwd_sm100_kernel<1, 0><<<(unsigned)grid, kThreads, pl.smem_bytes, st>>>(p);
+  } else if (pl.dual) {
+    D2C_CUDA_TRY(cudaFuncSetAttribute(fwd_sm100_kernel<0, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes));
+    fwd_sm100_kernel<0, 1><<<(unsigned)grid, kThreads, pl.smem_bytes, st>>>(p);
   } else {
-    D2C_CUDA_TRY(cudaFuncSetAttribute(fwd_sm100_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes));
-    fwd_sm100_kernel<0><<<(unsigned)grid, kThreads, pl.smem_bytes, st>>>(p);
+    D2C_CUDA_TRY(cudaFuncSetAttribute(fwd_sm100_kernel<0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes));
+    fwd_sm100_kernel<0, 0><<<(unsigned)grid, kThreads, pl.smem_bytes, st>>>(p);
   }
   D2C_LAUNCH_CHECK();
   prof_mark(st, nullptr);

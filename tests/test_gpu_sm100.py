@@ -101,17 +101,28 @@ def test_unsupported_shapes_fall_back_to_generic_tier(dn):
     assert np.abs(y.cpu().numpy() - want).max() <= 1e-4 * np.abs(want).max()
 
 
-def test_bf16_mode_uses_split_kernel_for_32_channels_per_group(dn):
-    """32 channels per offset group do not fill a 64-channel single-pass unit; bf16 mode then runs the forward
-    on the split (fp32-parity) tensor-core kernel instead of leaving the tensor cores."""
+@pytest.mark.parametrize("cfg,bound", [
+    (dict(B=2, Cin=256, Cout=128, dims=(2, 6, 9), G=8), REL_BF16),     # units span two offset groups (two record sets)
+    (dict(B=1, Cin=64, Cout=64, dims=(3, 7, 8), G=2), REL_BF16),
+    (dict(B=1, Cin=96, Cout=192, dims=(3, 6, 8), G=3), 1e-4),          # odd group count: split kernel instead
+    (dict(B=1, Cin=64, Cout=512, dims=(2, 6, 8), G=2), 1e-4),          # no room for two record sets: split kernel
+])
+def test_bf16_mode_with_32_channels_per_group(dn, cfg, bound):
+    """32 channels per offset group: a 64-channel single-pass unit then spans two groups and takes chunks 0-3 /
+    4-7 of every row from two different record sets; where that does not apply (odd group count, weight slice
+    too large to leave room for the second set) bf16 mode runs the split (fp32-parity) kernel."""
     from d2conv3d_b200 import _lib
-    p = make_problem(350, 2, 256, 128, (2, 6, 9), padding=1, G=8, dtype=np.float32, offset_std=2.0)
+    p = make_problem(350, padding=1, dtype=np.float32, offset_std=2.0, **cfg)
     _lib.profile_read(); _lib.profile_enable(True)
-    y = dn.deform_conv3d(cu(p["x"]), cu(p["geo"]), cu(p["mask"]), cu(p["weight"]), cu(p["bias"]), 1, 1, 1, 1, 8)
+    y = dn.deform_conv3d(cu(p["x"]), cu(p["geo"]), cu(p["mask"]), cu(p["weight"]), cu(p["bias"]), 1, 1, 1, 1, cfg["G"])
     _lib.profile_enable(False)
     assert "fwd_sm100_fused" in [n for n, _ in _lib.profile_read()]
-    want = orc.deform_conv3d_fwd(p["x"], p["geo"], p["mask"], p["weight"], p["bias"], padding=1, offset_groups=8)
-    assert np.abs(y.cpu().numpy() - want).max() <= 1e-4 * np.abs(want).max()
+    want = orc.deform_conv3d_fwd(p["x"], p["geo"], p["mask"], p["weight"], p["bias"], padding=1, offset_groups=cfg["G"])
+    err = np.abs(y.cpu().numpy() - want).max() / np.abs(want).max()
+    print(cfg, err)
+    assert err <= bound
+    if bound == REL_BF16:
+        assert err > 1e-5, "expected the single-pass kernel (bf16-sized error), got fp32-parity accuracy"
 
 
 REL_BF16_GRAD = 2e-2
