@@ -10,7 +10,7 @@
 #include <mutex>
 
 #include "d2c_common.cuh"
-#include "depthwise_bulk.cuh"
+#include "depthwise_quad.cuh"
 #include "depthwise_tile.cuh"
 
 namespace d2c {
@@ -234,6 +234,30 @@ static unsigned blocks_for(long long total) {
   return (unsigned)(n < 1 ? 1 : (n > cap ? cap : n));
 }
 
+// fp32, even W: the packed-FMA kernels.  Returns false when they do not apply (then *rc is untouched).
+template <typename T>
+static bool quad_conv(const Geom& g, const void* in, const void* w, const void* bias, void* out, int flip,
+                      cudaStream_t st, int* rc) {
+  if constexpr (std::is_same<T, float>::value) {
+    DwQuadPlan qp;
+    if (!aligned16(in) || !aligned16(out) || !dw_quad_plan(g, 1, &qp)) return false;
+    *rc = dw_quad_conv(g, qp, (const float*)in, (const float*)w, (const float*)bias, (float*)out, flip, st);
+    return true;
+  }
+  return false;
+}
+
+template <typename T>
+static bool quad_wgrad(const Geom& g, const void* gy, const void* x, void* partial, cudaStream_t st, int* rc) {
+  if constexpr (std::is_same<T, float>::value) {
+    DwQuadPlan qp;
+    if (!aligned16(gy) || !aligned16(x) || !dw_quad_plan(g, 2, &qp)) return false;
+    *rc = dw_quad_wgrad(g, qp, (const float*)gy, (const float*)x, (float*)partial, st);
+    return true;
+  }
+  return false;
+}
+
 template <typename T>
 static int dw_fwd_t(const Geom& g, const void* x, const void* w, const void* bias, void* y, cudaStream_t st) {
   const long long total = (long long)g.B * g.Cout * g.V;
@@ -242,9 +266,13 @@ static int dw_fwd_t(const Geom& g, const void* x, const void* w, const void* bia
   if (dw_tile_plan(g, sizeof(typename AccOf<T>::type), &plan)) {
     using A = typename AccOf<T>::type;
     DwBulkPlan bulk;
-    const int rc = (aligned16(x) && dw_bulk_plan(g, sizeof(T), 1, plan, &bulk))
-                       ? dw_bulk_conv<T, A>(g, plan, bulk, (const T*)x, (const T*)w, (const T*)bias, (T*)y, 0, st)
-                       : dw_tile_conv<T, A>(g, plan, (const T*)x, (const T*)w, (const T*)bias, (T*)y, 0, st);
+    int rc;
+    if (quad_conv<T>(g, x, w, bias, y, 0, st, &rc)) {
+    } else if (aligned16(x) && dw_bulk_plan(g, sizeof(T), 1, plan, &bulk)) {
+      rc = dw_bulk_conv<T, A>(g, plan, bulk, (const T*)x, (const T*)w, (const T*)bias, (T*)y, 0, st);
+    } else {
+      rc = dw_tile_conv<T, A>(g, plan, (const T*)x, (const T*)w, (const T*)bias, (T*)y, 0, st);
+    }
     prof_mark(st, nullptr);
     return rc;
   }
@@ -270,9 +298,13 @@ static int dw_bwd_t(const Geom& g, const void* gy, const void* x, const void* w,
     if (tiled) {
       // grad_x = correlation of grad_out with the point-reflected kernel
       DwBulkPlan bulk;
-      const int rc = (aligned16(gy) && dw_bulk_plan(g, sizeof(T), 1, plan, &bulk))
-                         ? dw_bulk_conv<T, A>(g, plan, bulk, (const T*)gy, (const T*)w, (const T*)nullptr, (T*)gx, 1, st)
-                         : dw_tile_conv<T, A>(g, plan, (const T*)gy, (const T*)w, (const T*)nullptr, (T*)gx, 1, st);
+      int rc;
+      if (quad_conv<T>(g, gy, w, nullptr, gx, 1, st, &rc)) {
+      } else if (aligned16(gy) && dw_bulk_plan(g, sizeof(T), 1, plan, &bulk)) {
+        rc = dw_bulk_conv<T, A>(g, plan, bulk, (const T*)gy, (const T*)w, (const T*)nullptr, (T*)gx, 1, st);
+      } else {
+        rc = dw_tile_conv<T, A>(g, plan, (const T*)gy, (const T*)w, (const T*)nullptr, (T*)gx, 1, st);
+      }
       if (rc) return rc;
     } else if (k333)
       dw_bwd_input_kernel<T, 3, 3, 3><<<blocks_for(total), 256, 0, st>>>(g, (const T*)gy, (const T*)w, (T*)gx);
@@ -287,9 +319,13 @@ static int dw_bwd_t(const Geom& g, const void* gy, const void* x, const void* w,
     if (tiled) {
       D2C_CUDA_TRY(cudaMemsetAsync(partial, 0, sizeof(A) * (size_t)n, st));
       DwBulkPlan bulk;
-      const int rc = (aligned16(gy) && aligned16(x) && dw_bulk_plan(g, sizeof(T), 2, plan, &bulk))
-                         ? dw_bulk_wgrad<T, A>(g, plan, bulk, (const T*)gy, (const T*)x, partial, st)
-                         : dw_tile_wgrad<T, A>(g, plan, (const T*)gy, (const T*)x, partial, st);
+      int rc;
+      if (quad_wgrad<T>(g, gy, x, partial, st, &rc)) {
+      } else if (aligned16(gy) && aligned16(x) && dw_bulk_plan(g, sizeof(T), 2, plan, &bulk)) {
+        rc = dw_bulk_wgrad<T, A>(g, plan, bulk, (const T*)gy, (const T*)x, partial, st);
+      } else {
+        rc = dw_tile_wgrad<T, A>(g, plan, (const T*)gy, (const T*)x, partial, st);
+      }
       if (rc) return rc;
     } else if (k333) {
       D2C_CUDA_TRY(cudaMemsetAsync(partial, 0, sizeof(A) * (size_t)n, st));

@@ -70,6 +70,12 @@ def test_depthwise_other_kernel_shapes_and_larger_tile(dw):
     ((1, 2, 8, 56, 56), torch.float32, False),    # forward fits shared memory with one block per SM, weight gradient does not
     ((2, 8, 4, 6, 8), torch.float32, True),       # tensors at a 4-byte offset: no bulk copy possible
     ((1, 4, 1, 9, 32), torch.float64, False),     # single plane, double, odd height
+    # fp32 with even W: packed-FMA kernels (4-row x 2-column patches forward, 2 x 2 for the weight gradient)
+    ((1, 4, 1, 10, 8), torch.float32, False),     # one plane; H = 10 leaves a 2-row patch at the bottom
+    ((2, 3, 2, 7, 6), torch.float32, False),      # two planes, odd H (7 = 4 + 3 rows), W % 4 == 2
+    ((1, 5, 3, 30, 54), torch.float32, False),    # the benchmark's plane size, depth 3 (one full rotation)
+    ((3, 2, 7, 5, 12), torch.float32, False),     # depth 7, H = 5 (patch of one valid row), W % 4 == 0
+    ((2, 300, 4, 2, 4), torch.float32, False),    # tiny volumes, several per chunk, H smaller than a patch
 ])
 def test_depthwise_3x3x3_fast_paths(dw, shape, dtype, misalign):
     """The 3x3x3 / stride 1 / padding 1 case has three implementations chosen by size and alignment
@@ -99,6 +105,22 @@ def test_depthwise_3x3x3_fast_paths(dw, shape, dtype, misalign):
     scale = max(1.0, float(np.abs(wgw).max()))
     assert np.abs(np64(w.grad) - wgw).max() <= (1e-2 if dtype == torch.float16 else 1e-4) * scale
     _lib.device_status()
+
+
+def test_non_finite_input_next_to_a_border_stays_local(dw):
+    """The packed-FMA kernels read a neighbouring row's element where a patch touches the left / right border
+    and must discard it (not multiply it by zero): an Inf in the last column of a row may only reach the outputs
+    cuDNN lets it reach."""
+    torch.manual_seed(5)
+    x = torch.randn(1, 2, 3, 6, 8, device="cuda")
+    x[0, 0, 1, 2, 7] = float("inf")       # last column of row 2: precedes column 0 of row 3 in memory
+    x[0, 1, 1, 3, 0] = float("inf")       # first column of row 3: follows the last column of row 2
+    w = torch.randn(2, 1, 3, 3, 3, device="cuda").abs() + 0.1      # positive weights: Inf, never Inf - Inf
+    y = dw._ops.depthwise_separable_conv3d(x, w, None, 1, 1, 1)
+    ref = torch.nn.functional.conv3d(x, w, None, padding=1, groups=2)
+    assert torch.equal(torch.isfinite(y), torch.isfinite(ref))
+    fin = torch.isfinite(ref)
+    assert torch.allclose(y[fin], ref[fin], atol=1e-5)
 
 
 def test_autocast_keeps_half(dw):
