@@ -36,7 +36,7 @@ struct DwQuadPlan {
 };
 
 constexpr int kDwQuadMaxThreads = 224;
-constexpr int kDwQuadWgradMaxThreads = 448;
+constexpr int kDwQuadWgradMaxThreads = 448;   // compute threads + the loader warp
 constexpr int kDwQuadTab = 28;         // weight-pair table entries per volume: 27 taps + bias
 constexpr int kDwQuadConvRows = 4;     // patch rows, forward / input gradient
 constexpr int kDwQuadWgradRows = 2;    // patch rows, weight gradient
@@ -70,7 +70,7 @@ inline bool dw_quad_plan(const Geom& g, int tensors, DwQuadPlan* p) {
   p->stage_bytes = (uint32_t)stage;
   p->smem = need;
   const int per_sm = (tensors == 1 && need <= 112 * 1024) ? 2 : 1;
-  const int cap = tensors == 2 ? kDwQuadWgradMaxThreads : kDwQuadMaxThreads;
+  const int cap = tensors == 2 ? kDwQuadWgradMaxThreads - 32 : kDwQuadMaxThreads;
   const long long work = (long long)n * p->items;
   const long long passes = (work + cap - 1) / cap;
   int threads = (int)(((work + passes - 1) / passes + 31) / 32 * 32);
@@ -159,12 +159,13 @@ __device__ __forceinline__ void dwq_conv_step(const float* plane, const DwqRows<
     if (j + 1 < R + 2) raw[(j + 1) & 1] = dwq_row_load<R + 2>(plane, rows, j + 1);
     u64 P[3];
     dwq_row_pairs<R + 2>(raw[j & 1], rows, P);
+    // kx outermost: successive updates of one accumulator are 3 x (rows) packed FMAs apart
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-      const int ky = j - r;
-      if (ky < 0 || ky > 2) continue;
+    for (int kx = 0; kx < 3; ++kx)
 #pragma unroll
-      for (int kx = 0; kx < 3; ++kx) {
+      for (int r = 0; r < R; ++r) {
+        const int ky = j - r;
+        if (ky < 0 || ky > 2) continue;
         fma2(am1[r], wk[(2 * 3 + ky) * 3 + kx], P[kx]);
         fma2(a0[r], wk[(1 * 3 + ky) * 3 + kx], P[kx]);
         if (ky == 0 && kx == 0)
@@ -172,7 +173,6 @@ __device__ __forceinline__ void dwq_conv_step(const float* plane, const DwqRows<
         else
           fma2(ap1[r], wk[(0 * 3 + ky) * 3 + kx], P[kx]);
       }
-    }
   }
 }
 
@@ -183,97 +183,116 @@ __device__ __forceinline__ void dwq_store(float* dst, int W, int rows_ok, const 
     if (r < rows_ok) *reinterpret_cast<float2*>(dst + r * W) = unpk2(a[r]);
 }
 
-// Shared memory: [stage 0][stage 1][2 mbarriers][abort flag][weight-pair tables of both stages].
-__global__ void __launch_bounds__(kDwQuadMaxThreads, 2)
+// Forward / input gradient.  The last warp of the block is the loader: it fills a stage's weight-pair table and
+// issues the stage's bulk copies as soon as every compute warp has released that stage ("empty" mbarrier, one
+// arrival per compute warp); compute warps wait on the stage's "full" mbarrier, never on each other.
+// Shared memory: [stage 0][stage 1][full 0, full 1, empty 0, empty 1][abort flag at +64][weight-pair tables of
+// both stages at +128].
+__global__ void __launch_bounds__(kDwQuadMaxThreads + 32, 2)
 dw_quad_conv_kernel(Geom g, int nyp, int nxp, int nvol, long long nchunks, uint32_t plane_bytes, uint32_t gap_bytes,
                     uint32_t stage_bytes, const float* __restrict__ in, const float* __restrict__ w,
                     const float* __restrict__ bias, float* __restrict__ out, int flip) {
   constexpr int R = kDwQuadConvRows;
   extern __shared__ __align__(128) unsigned char dwb_smem[];
   const uint32_t bar0 = ptx::smem_u32(dwb_smem + 2 * (size_t)stage_bytes);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(dwb_smem + 2 * (size_t)stage_bytes + 16);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(dwb_smem + 2 * (size_t)stage_bytes + 64);
   float2* wtab = reinterpret_cast<float2*>(dwb_smem + 2 * (size_t)stage_bytes + 128);
   const long long lo = nchunks * blockIdx.x / gridDim.x, hi = nchunks * (blockIdx.x + 1) / gridDim.x;
   const int planes = nvol * g.D, HW = g.H * g.W;
   const uint32_t pstride = plane_bytes + gap_bytes;
+  const int compute_threads = (int)blockDim.x - 32;
+  auto full_bar = [&](int s) { return bar0 + 8 * s; };
+  auto empty_bar = [&](int s) { return bar0 + 16 + 8 * s; };
   if (threadIdx.x == 0) {
-    ptx::mbar_init(bar0, 1);
-    ptx::mbar_init(bar0 + 8, 1);
+    ptx::mbar_init(full_bar(0), 1);
+    ptx::mbar_init(full_bar(1), 1);
+    ptx::mbar_init(empty_bar(0), (uint32_t)(compute_threads / 32));
+    ptx::mbar_init(empty_bar(1), (uint32_t)(compute_threads / 32));
     *abort_flag = 0;
     ptx::fence_mbar_init();
   }
-  // table entry e = (vol, t) of chunk ch: (w, w) of that volume's channel, t = 27: the bias
-  const int tab_n = nvol * kDwQuadTab;
-  auto tab_value = [&](long long ch, int e) {
-    const int vol = e / kDwQuadTab, t = e - vol * kDwQuadTab;
-    const int c = (int)((ch * nvol + vol) % g.Cin);
-    return t < 27 ? __ldg(w + (long long)c * 27 + (flip ? 26 - t : t)) : (bias ? __ldg(bias + c) : 0.f);
-  };
-  if (lo < hi)
-    for (int e = threadIdx.x; e < tab_n; e += blockDim.x) {
-      const float v = tab_value(lo, e);
-      wtab[e] = make_float2(v, v);
-    }
   dwb_zero_gaps(dwb_smem, stage_bytes, plane_bytes, gap_bytes, planes);   // ends with a block barrier
-  const unsigned char* src_bytes = reinterpret_cast<const unsigned char*>(in);
-  auto issue = [&](long long ch, int s) {
-    const uint32_t bar = bar0 + 8 * s;
-    ptx::mbar_arrive_expect_tx(bar, (uint32_t)planes * plane_bytes);
-    const unsigned char* src = src_bytes + ch * (long long)planes * plane_bytes;
-    const uint32_t dst = ptx::smem_u32(dwb_smem + (size_t)s * stage_bytes + gap_bytes);
-    for (int k = 0; k < planes; ++k) ptx::bulk_g2s(dst + k * pstride, src + (size_t)k * plane_bytes, plane_bytes, bar);
-  };
-  if (threadIdx.x == 0 && lo < hi) issue(lo, 0);
-  const int items = nyp * nxp, work = nvol * items;
-  const int pstride_e = (int)(pstride / 4);
-  int it = 0;
-  for (long long ch = lo; ch < hi; ++ch, ++it) {
-    const int s = it & 1;
-    // stage s^1 and table half s^1 were released by the barrier that ended iteration it-1
-    if (threadIdx.x == 0 && ch + 1 < hi) issue(ch + 1, s ^ 1);
-    // next chunk's table entries: requested now, written to shared memory after this chunk's arithmetic
-    float tab_next = 0.f;
-    const bool tab_mine = ch + 1 < hi && (int)threadIdx.x < tab_n;
-    if (tab_mine) tab_next = tab_value(ch + 1, threadIdx.x);
-    if (!ptx::mbar_wait(bar0 + 8 * s, (it >> 1) & 1, abort_flag)) break;
-    const float* stage = reinterpret_cast<const float*>(dwb_smem + (size_t)s * stage_bytes + gap_bytes);
-    for (int wi = threadIdx.x; wi < work; wi += blockDim.x) {
-      const int vol = wi / items, rem = wi - vol * items;
-      const int yp = rem / nxp, xp = rem - yp * nxp, y0 = yp * R, x0 = xp * 2;
-      const long long bc = ch * nvol + vol;
-      const u64* wt = reinterpret_cast<const u64*>(wtab) + (s * nvol + vol) * kDwQuadTab;
-      u64 wk[27];
-#pragma unroll
-      for (int t = 0; t < 27; ++t) wk[t] = wt[t];
-      const u64 bb = wt[27];
-      const DwqRows<R + 2> rows = dwq_rows<R + 2>(y0, x0, g.H, g.W);
-      const float* sm = stage + (long long)vol * g.D * pstride_e;
-      float* dst = out + bc * g.Vin + (long long)y0 * g.W + x0;
-      const int rows_ok = min(R, g.H - y0);
-      u64 aa[R], ab[R], ac[R];
-#pragma unroll
-      for (int r = 0; r < R; ++r) aa[r] = ab[r] = ac[r] = bb;
-      // plane p completes output plane p-1; the accumulator roles rotate with period 3
-      for (int p = 0; p < g.D; p += 3) {
-        dwq_conv_step<R>(sm + p * pstride_e, rows, wk, bb, aa, ab, ac);
-        if (p >= 1) dwq_store<R>(dst + (long long)(p - 1) * HW, g.W, rows_ok, aa);
-        if (p + 1 >= g.D) { dwq_store<R>(dst + (long long)p * HW, g.W, rows_ok, ab); break; }
-        dwq_conv_step<R>(sm + (p + 1) * pstride_e, rows, wk, bb, ab, ac, aa);
-        dwq_store<R>(dst + (long long)p * HW, g.W, rows_ok, ab);
-        if (p + 2 >= g.D) { dwq_store<R>(dst + (long long)(p + 1) * HW, g.W, rows_ok, ac); break; }
-        dwq_conv_step<R>(sm + (p + 2) * pstride_e, rows, wk, bb, ac, aa, ab);
-        dwq_store<R>(dst + (long long)(p + 1) * HW, g.W, rows_ok, ac);
-        if (p + 3 >= g.D) dwq_store<R>(dst + (long long)(p + 2) * HW, g.W, rows_ok, aa);
+  const int tab_n = nvol * kDwQuadTab;
+
+  if ((int)threadIdx.x >= compute_threads) {
+    // ---- loader warp ----
+    const int lane = threadIdx.x & 31;
+    const unsigned char* src_bytes = reinterpret_cast<const unsigned char*>(in);
+    int it = 0;
+    bool ok = true;
+    for (long long ch = lo; ch < hi; ++ch, ++it) {
+      const int s = it & 1;
+      if (it >= 2 && !ptx::mbar_wait(empty_bar(s), ((it >> 1) - 1) & 1, abort_flag)) { ok = false; break; }
+      // table entry e = (vol, t): (w, w) of that volume's channel, t = 27: the bias
+      for (int e = lane; e < tab_n; e += 32) {
+        const int vol = e / kDwQuadTab, t = e - vol * kDwQuadTab;
+        const int c = (int)((ch * nvol + vol) % g.Cin);
+        const float v = t < 27 ? __ldg(w + (long long)c * 27 + (flip ? 26 - t : t)) : (bias ? __ldg(bias + c) : 0.f);
+        wtab[s * tab_n + e] = make_float2(v, v);
       }
+      __syncwarp();
+      if (lane == 0) {
+        // the arrive (release) below orders the table writes of the whole warp before the stage becomes full
+        ptx::mbar_arrive_expect_tx(full_bar(s), (uint32_t)planes * plane_bytes);
+        const unsigned char* src = src_bytes + ch * (long long)planes * plane_bytes;
+        const uint32_t dst = ptx::smem_u32(dwb_smem + (size_t)s * stage_bytes + gap_bytes);
+        for (int k = 0; k < planes; ++k)
+          ptx::bulk_g2s(dst + k * pstride, src + (size_t)k * plane_bytes, plane_bytes, full_bar(s));
+      }
+      __syncwarp();
     }
-    if (tab_mine) wtab[(s ^ 1) * tab_n + threadIdx.x] = make_float2(tab_next, tab_next);
-    if (ch + 1 < hi)
-      for (int e = threadIdx.x + blockDim.x; e < tab_n; e += blockDim.x) {
-        const float v = tab_value(ch + 1, e);
-        wtab[(s ^ 1) * tab_n + e] = make_float2(v, v);
+    // never leave with a bulk copy in flight: the last two stages issued must have landed
+    if (lane == 0)
+      for (int back = 1; back <= 2 && back <= it; ++back) {
+        const int j = it - back;
+        const long long t0 = clock64();
+        while (!ptx::mbar_try_wait(full_bar(j & 1), (j >> 1) & 1))
+          if (clock64() - t0 > ptx::kWaitBudgetCycles) break;
       }
-    __syncthreads();   // every thread is done reading stage s before it is refilled
+    if (!ok && lane == 0) *abort_flag = 1;
+  } else {
+    // ---- compute warps ----
+    const int items = nyp * nxp, work = nvol * items;
+    const int pstride_e = (int)(pstride / 4);
+    int it = 0;
+    for (long long ch = lo; ch < hi; ++ch, ++it) {
+      const int s = it & 1;
+      if (!ptx::mbar_wait(full_bar(s), (it >> 1) & 1, abort_flag)) break;
+      const float* stage = reinterpret_cast<const float*>(dwb_smem + (size_t)s * stage_bytes + gap_bytes);
+      for (int wi = threadIdx.x; wi < work; wi += compute_threads) {
+        const int vol = wi / items, rem = wi - vol * items;
+        const int yp = rem / nxp, xp = rem - yp * nxp, y0 = yp * R, x0 = xp * 2;
+        const long long bc = ch * nvol + vol;
+        const u64* wt = reinterpret_cast<const u64*>(wtab) + (s * nvol + vol) * kDwQuadTab;
+        u64 wk[27];
+#pragma unroll
+        for (int t = 0; t < 27; ++t) wk[t] = wt[t];
+        const u64 bb = wt[27];
+        const DwqRows<R + 2> rows = dwq_rows<R + 2>(y0, x0, g.H, g.W);
+        const float* sm = stage + (long long)vol * g.D * pstride_e;
+        float* dst = out + bc * g.Vin + (long long)y0 * g.W + x0;
+        const int rows_ok = min(R, g.H - y0);
+        u64 aa[R], ab[R], ac[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) aa[r] = ab[r] = ac[r] = bb;
+        // plane p completes output plane p-1; the accumulator roles rotate with period 3
+        for (int p = 0; p < g.D; p += 3) {
+          dwq_conv_step<R>(sm + p * pstride_e, rows, wk, bb, aa, ab, ac);
+          if (p >= 1) dwq_store<R>(dst + (long long)(p - 1) * HW, g.W, rows_ok, aa);
+          if (p + 1 >= g.D) { dwq_store<R>(dst + (long long)p * HW, g.W, rows_ok, ab); break; }
+          dwq_conv_step<R>(sm + (p + 1) * pstride_e, rows, wk, bb, ab, ac, aa);
+          dwq_store<R>(dst + (long long)p * HW, g.W, rows_ok, ab);
+          if (p + 2 >= g.D) { dwq_store<R>(dst + (long long)(p + 1) * HW, g.W, rows_ok, ac); break; }
+          dwq_conv_step<R>(sm + (p + 2) * pstride_e, rows, wk, bb, ac, aa, ab);
+          dwq_store<R>(dst + (long long)(p + 1) * HW, g.W, rows_ok, ac);
+          if (p + 3 >= g.D) dwq_store<R>(dst + (long long)(p + 2) * HW, g.W, rows_ok, aa);
+        }
+      }
+      __syncwarp();
+      if ((threadIdx.x & 31) == 0) ptx::mbar_arrive(empty_bar(s));   // this warp is done with stage s
+    }
   }
+  __syncthreads();
   if (threadIdx.x == 0 && *abort_flag) atomicExch(&g_dw_status, 1);
 }
 
@@ -314,9 +333,26 @@ __device__ __forceinline__ void dwq_wgrad_step(const float* xplane, const DwqRow
   }
 }
 
-// Work items are (channel, clip) pairs, channel-major; a block flushes its 27 sums (shuffle + one atomic per
-// tap) when its channel changes.  Shared memory: [stage0: gapped x volume, grad_out volume][stage1: ...]
-// [2 mbarriers][abort flag][reduction scratch warps x 27].
+// Sum of the 27 pair accumulators over the warp, one atomic per tap into partial[c][27]; clears acc.
+__device__ __forceinline__ void dwq_flush_warp(u64 (&acc)[27], float* __restrict__ partial, int c) {
+  const int lane = threadIdx.x & 31;
+  float mine = 0.f;
+#pragma unroll
+  for (int t = 0; t < 27; ++t) {
+    const float2 v = unpk2(acc[t]);
+    float sv = v.x + v.y;
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) sv += __shfl_xor_sync(0xffffffffu, sv, o);
+    if (lane == t) mine = sv;
+    acc[t] = 0ull;
+  }
+  if (lane < 27) atomicAdd(partial + (long long)c * 27 + lane, mine);
+}
+
+// Work items are (channel, clip) pairs, channel-major; a warp flushes its 27 sums (shuffles + one atomic per
+// tap) when the channel changes.  The block's last warp is the loader, as in the conv kernel; compute warps
+// never meet at a block barrier.  Shared memory: [stage0: gapped x volume, grad_out volume][stage1: ...]
+// [full 0, full 1, empty 0, empty 1][abort flag at +64].
 __global__ void __launch_bounds__(kDwQuadWgradMaxThreads, 1)
 dw_quad_wgrad_kernel(Geom g, int nyp, int nxp, uint32_t plane_bytes, uint32_t gap_bytes, uint32_t stage_x_bytes,
                      uint32_t stage_bytes, const float* __restrict__ gy, const float* __restrict__ x,
@@ -324,86 +360,103 @@ dw_quad_wgrad_kernel(Geom g, int nyp, int nxp, uint32_t plane_bytes, uint32_t ga
   constexpr int R = kDwQuadWgradRows;
   extern __shared__ __align__(128) unsigned char dwb_smem[];
   const uint32_t bar0 = ptx::smem_u32(dwb_smem + 2 * (size_t)stage_bytes);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(dwb_smem + 2 * (size_t)stage_bytes + 16);
-  float* red = reinterpret_cast<float*>(dwb_smem + 2 * (size_t)stage_bytes + 32);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(dwb_smem + 2 * (size_t)stage_bytes + 64);
   const long long n_items = (long long)g.Cin * g.B;
   const long long lo = n_items * blockIdx.x / gridDim.x, hi = n_items * (blockIdx.x + 1) / gridDim.x;
   const int HW = g.H * g.W;
   const uint32_t pstride = plane_bytes + gap_bytes, vol_bytes = (uint32_t)g.D * plane_bytes;
+  const int compute_threads = (int)blockDim.x - 32;
+  auto full_bar = [&](int s) { return bar0 + 8 * s; };
+  auto empty_bar = [&](int s) { return bar0 + 16 + 8 * s; };
   if (threadIdx.x == 0) {
-    ptx::mbar_init(bar0, 1);
-    ptx::mbar_init(bar0 + 8, 1);
+    ptx::mbar_init(full_bar(0), 1);
+    ptx::mbar_init(full_bar(1), 1);
+    ptx::mbar_init(empty_bar(0), (uint32_t)(compute_threads / 32));
+    ptx::mbar_init(empty_bar(1), (uint32_t)(compute_threads / 32));
     *abort_flag = 0;
     ptx::fence_mbar_init();
   }
-  dwb_zero_gaps(dwb_smem, stage_bytes, plane_bytes, gap_bytes, g.D);
-  const unsigned char* xb = reinterpret_cast<const unsigned char*>(x);
-  const unsigned char* gb = reinterpret_cast<const unsigned char*>(gy);
-  auto issue = [&](long long item, int s) {
-    const long long c = item / g.B, b = item - c * g.B;
-    const long long voff = (b * g.Cin + c) * (long long)vol_bytes;
-    const uint32_t bar = bar0 + 8 * s;
-    ptx::mbar_arrive_expect_tx(bar, 2 * vol_bytes);
-    const uint32_t dst = ptx::smem_u32(dwb_smem + (size_t)s * stage_bytes);
-    for (int k = 0; k < g.D; ++k)
-      ptx::bulk_g2s(dst + gap_bytes + k * pstride, xb + voff + (size_t)k * plane_bytes, plane_bytes, bar);
-    ptx::bulk_g2s(dst + stage_x_bytes, gb + voff, vol_bytes, bar);
-  };
-  if (threadIdx.x == 0 && lo < hi) issue(lo, 0);
-  const int patches = nyp * nxp, pstride_e = (int)(pstride / 4);
-  u64 acc[27];
+  dwb_zero_gaps(dwb_smem, stage_bytes, plane_bytes, gap_bytes, g.D);   // ends with a block barrier
+
+  if ((int)threadIdx.x >= compute_threads) {
+    // ---- loader warp (one lane) ----
+    if ((threadIdx.x & 31) == 0) {
+      const unsigned char* xb = reinterpret_cast<const unsigned char*>(x);
+      const unsigned char* gb = reinterpret_cast<const unsigned char*>(gy);
+      int it = 0;
+      bool ok = true;
+      for (long long item = lo; item < hi; ++item, ++it) {
+        const int s = it & 1;
+        if (it >= 2 && !ptx::mbar_wait(empty_bar(s), ((it >> 1) - 1) & 1, abort_flag)) { ok = false; break; }
+        const long long c = item / g.B, b = item - c * g.B;
+        const long long voff = (b * g.Cin + c) * (long long)vol_bytes;
+        ptx::mbar_arrive_expect_tx(full_bar(s), 2 * vol_bytes);
+        const uint32_t dst = ptx::smem_u32(dwb_smem + (size_t)s * stage_bytes);
+        for (int k = 0; k < g.D; ++k)
+          ptx::bulk_g2s(dst + gap_bytes + k * pstride, xb + voff + (size_t)k * plane_bytes, plane_bytes, full_bar(s));
+        ptx::bulk_g2s(dst + stage_x_bytes, gb + voff, vol_bytes, full_bar(s));
+      }
+      // never leave with a bulk copy in flight
+      for (int back = 1; back <= 2 && back <= it; ++back) {
+        const int j = it - back;
+        const long long t0 = clock64();
+        while (!ptx::mbar_try_wait(full_bar(j & 1), (j >> 1) & 1))
+          if (clock64() - t0 > ptx::kWaitBudgetCycles) break;
+      }
+      if (!ok) *abort_flag = 1;
+    }
+  } else {
+    // ---- compute warps ----
+    const int patches = nyp * nxp, pstride_e = (int)(pstride / 4);
+    u64 acc[27];
 #pragma unroll
-  for (int t = 0; t < 27; ++t) acc[t] = 0ull;
-  int it = 0;
-  bool ok = true;
-  for (long long item = lo; item < hi; ++item, ++it) {
-    const int s = it & 1;
-    if (threadIdx.x == 0 && item + 1 < hi) issue(item + 1, s ^ 1);
-    if (!ptx::mbar_wait(bar0 + 8 * s, (it >> 1) & 1, abort_flag)) { ok = false; break; }
-    const float* xs = reinterpret_cast<const float*>(dwb_smem + (size_t)s * stage_bytes + gap_bytes);
-    const float* gs0 = reinterpret_cast<const float*>(dwb_smem + (size_t)s * stage_bytes + stage_x_bytes);
-    for (int wi = threadIdx.x; wi < patches; wi += blockDim.x) {
-      const int yp = wi / nxp, xp = wi - yp * nxp, y0 = yp * R, x0 = xp * 2;
-      const DwqRows<R + 2> rows = dwq_rows<R + 2>(y0, x0, g.H, g.W);
-      const int rows_ok = min(R, g.H - y0);
-      const float* gs = gs0 + y0 * g.W + x0;
-      u64 ga[R], gbv[R], gc[R];
-      auto grads = [&](int q, u64 (&G)[R]) {
-        dwq_load_grads<R>(gs + (long long)q * HW, g.W, rows_ok, q >= 0 && q < g.D, G);
-      };
-      grads(-1, ga); grads(0, gbv); grads(1, gc);
-      for (int p = 0; p < g.D; p += 3) {
-        dwq_wgrad_step<R>(xs + p * pstride_e, rows, acc, ga, gbv, gc);
-        if (p + 1 >= g.D) break;
-        grads(p + 2, ga);
-        dwq_wgrad_step<R>(xs + (p + 1) * pstride_e, rows, acc, gbv, gc, ga);
-        if (p + 2 >= g.D) break;
-        grads(p + 3, gbv);
-        dwq_wgrad_step<R>(xs + (p + 2) * pstride_e, rows, acc, gc, ga, gbv);
-        grads(p + 4, gc);
+    for (int t = 0; t < 27; ++t) acc[t] = 0ull;
+    int it = 0;
+    long long c_open = -1;                    // channel whose sums are in acc
+    for (long long item = lo; item < hi; ++item, ++it) {
+      const int s = it & 1;
+      if (!ptx::mbar_wait(full_bar(s), (it >> 1) & 1, abort_flag)) break;
+      const float* xs = reinterpret_cast<const float*>(dwb_smem + (size_t)s * stage_bytes + gap_bytes);
+      const float* gs0 = reinterpret_cast<const float*>(dwb_smem + (size_t)s * stage_bytes + stage_x_bytes);
+      c_open = item / g.B;
+      for (int wi = threadIdx.x; wi < patches; wi += compute_threads) {
+        const int yp = wi / nxp, xp = wi - yp * nxp, y0 = yp * R, x0 = xp * 2;
+        const DwqRows<R + 2> rows = dwq_rows<R + 2>(y0, x0, g.H, g.W);
+        const int rows_ok = min(R, g.H - y0);
+        const float* gs = gs0 + y0 * g.W + x0;
+        u64 ga[R], gbv[R], gc[R];
+        auto grads = [&](int q, u64 (&G)[R]) {
+          dwq_load_grads<R>(gs + (long long)q * HW, g.W, rows_ok, q >= 0 && q < g.D, G);
+        };
+        grads(-1, ga); grads(0, gbv); grads(1, gc);
+        for (int p = 0; p < g.D; p += 3) {
+          dwq_wgrad_step<R>(xs + p * pstride_e, rows, acc, ga, gbv, gc);
+          if (p + 1 >= g.D) break;
+          grads(p + 2, ga);
+          dwq_wgrad_step<R>(xs + (p + 1) * pstride_e, rows, acc, gbv, gc, ga);
+          if (p + 2 >= g.D) break;
+          grads(p + 3, gbv);
+          dwq_wgrad_step<R>(xs + (p + 2) * pstride_e, rows, acc, gc, ga, gbv);
+          grads(p + 4, gc);
+        }
+      }
+      __syncwarp();
+      if ((threadIdx.x & 31) == 0) ptx::mbar_arrive(empty_bar(s));   // this warp is done with stage s
+      if (item + 1 == hi || (item + 1) / g.B != c_open) {
+        dwq_flush_warp(acc, partial, (int)c_open);
+        c_open = -1;
       }
     }
-    const long long c = item / g.B;
-    if (item + 1 == hi || (item + 1) / g.B != c) {
-      float sums[27];
-#pragma unroll
-      for (int t = 0; t < 27; ++t) {
-        const float2 v = unpk2(acc[t]);
-        sums[t] = v.x + v.y;
-        acc[t] = 0ull;
-      }
-      dwb_flush<float>(sums, red, partial, (int)c);   // ends with a block barrier
-    } else {
-      __syncthreads();   // every thread is done reading stage s before it is refilled
-    }
+    if (c_open >= 0) dwq_flush_warp(acc, partial, (int)c_open);      // left the loop early: keep what was summed
   }
-  if (threadIdx.x == 0 && (!ok || *abort_flag)) atomicExch(&g_dw_status, 1);
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(&g_dw_status, 1);
 }
 
 inline int dw_quad_conv(const Geom& g, const DwQuadPlan& p, const float* in, const float* w, const float* bias,
                         float* out, int flip, cudaStream_t st) {
   D2C_CUDA_TRY(cudaFuncSetAttribute(dw_quad_conv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem));
-  dw_quad_conv_kernel<<<p.blocks, p.threads, p.smem, st>>>(g, p.nyp, p.nxp, p.nvol, p.nchunks, p.plane_bytes,
+  dw_quad_conv_kernel<<<p.blocks, p.threads + 32, p.smem, st>>>(g, p.nyp, p.nxp, p.nvol, p.nchunks, p.plane_bytes,
                                                            p.gap_bytes, p.stage_bytes, in, w, bias, out, flip);
   D2C_LAUNCH_CHECK();
   return D2C_OK;
@@ -411,9 +464,9 @@ inline int dw_quad_conv(const Geom& g, const DwQuadPlan& p, const float* in, con
 
 inline int dw_quad_wgrad(const Geom& g, const DwQuadPlan& p, const float* gy, const float* x, float* partial,
                          cudaStream_t st) {
-  const size_t smem = p.smem + (size_t)(p.threads / 32) * 27 * sizeof(float);
+  const size_t smem = p.smem;
   D2C_CUDA_TRY(cudaFuncSetAttribute(dw_quad_wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  dw_quad_wgrad_kernel<<<p.blocks, p.threads, smem, st>>>(g, p.nyp, p.nxp, p.plane_bytes, p.gap_bytes,
+  dw_quad_wgrad_kernel<<<p.blocks, p.threads + 32, smem, st>>>(g, p.nyp, p.nxp, p.plane_bytes, p.gap_bytes,
                                                           p.stage_x_bytes, p.stage_bytes, gy, x, partial);
   D2C_LAUNCH_CHECK();
   return D2C_OK;
