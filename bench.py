@@ -516,6 +516,8 @@ EXTRA_WORKLOADS = {
     # BASELINE config 5 (decoder inference): the xyz dynamic-dilated 256->256 conv of a refine block at the
     # stride-4 pyramid level, one clip, 8 offset groups (32 channels per group), forward only
     "c5-e1": dict(kind="dyndil", mode="xyz", B=1, Cin=256, Cout=256, dims=(8, 120, 214), G=8, fwd_only=True),
+    # the same layer with its backward (decoder training)
+    "c5-e1-train": dict(kind="dyndil", mode="xyz", B=1, Cin=256, Cout=256, dims=(8, 120, 214), G=8),
 }
 
 

@@ -354,7 +354,10 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
 // columns of tap t+1 are requested before tap t is processed, so the HBM stream of dcol (slice-major:
 // 8 KB contiguous per block and slice) stays in flight behind the L2 gathers and reductions.
 // kF32X: the channels-last staging of x is fp32 (fp32-parity mode) instead of fp16.
-template <bool FieldOut, bool kF32X>
+// kNarrow (fp32 staging only): 32 channels per offset group.  The gradient columns keep their 64-channel
+// slices, each now holding two neighbouring groups; a block still serves one (clip, group) and its threads
+// own channels [4j, 4j+4) of the group's half of the slice.
+template <bool FieldOut, bool kF32X, bool kNarrow = false>
 __global__ void __launch_bounds__(256, kF32X ? 2 : 3)
 sample_grad_taps_kernel(Geom g, ClStrides cs, int b0, int nh, const float4* __restrict__ recs,
                         const float* __restrict__ dcol, const void* __restrict__ x_cl_v, bool has_mask,
@@ -366,26 +369,32 @@ sample_grad_taps_kernel(Geom g, ClStrides cs, int b0, int nh, const float4* __re
   const int b = b0 + bl;
   const bool active = v < g.V;
   const int vc = active ? v : g.V - 1;                       // clamped: inactive threads load valid memory
-  const long long S = (long long)g.G * g.K * nh;
+  static_assert(!kNarrow || kF32X, "the narrow variant reads the fp32 staging");
+  const long long S = kNarrow ? (long long)(g.G / 2) * g.K : (long long)g.G * g.K * nh;
   const float4* recp = recs + (((long long)b * g.G + grp) * g.K) * g.V + vc;
   // thread j owns channels [4j, 4j+4) and [32+4j, 32+4j+4) of a slice: one warp-wide 16-byte access then
   // covers whole 32-byte sectors (two lanes each), which halves the sector operations of the reductions
-  const float* dp = dcol + (((long long)bl * S + (long long)grp * g.K * nh) * g.V + vc) * 64 + j * 4;
+  const float* dp = kNarrow
+      ? dcol + (((long long)bl * S + (long long)(grp >> 1) * g.K) * g.V + vc) * 64 + (grp & 1) * 32 + j * 4
+      : dcol + (((long long)bl * S + (long long)grp * g.K * nh) * g.V + vc) * 64 + j * 4;
   const long long slice_stride = (long long)g.V * 64;
   using XT = typename std::conditional<kF32X, float, __half>::type;
   const XT* xb = reinterpret_cast<const XT*>(x_cl_v) + (long long)b * g.Vin * g.Cin;
   float* gxb = gx_cl + (long long)b * g.Vin * g.Cin;
   const int chbase = grp * g.cpg + j * 4;
 
+  const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
   float4 rec_n = __ldg(recp);
-  float4 d0_n = __ldg(reinterpret_cast<const float4*>(dp)), d1_n = __ldg(reinterpret_cast<const float4*>(dp + 32));
+  float4 d0_n = __ldg(reinterpret_cast<const float4*>(dp));
+  float4 d1_n = kNarrow ? zero4 : __ldg(reinterpret_cast<const float4*>(dp + 32));
   for (int tap = 0; tap < g.K; ++tap) {
     const float4 rec = rec_n;
     float4 d0 = d0_n, d1 = d1_n;
     if (tap + 1 < g.K) {
       rec_n = __ldg(recp + (long long)(tap + 1) * g.V);
       const float4* nx = reinterpret_cast<const float4*>(dp + (long long)(tap + 1) * nh * slice_stride);
-      d0_n = __ldg(nx); d1_n = __ldg(nx + 8);
+      d0_n = __ldg(nx);
+      if (!kNarrow) d1_n = __ldg(nx + 8);
     }
     const float m = rec.w;
     const Sample<float> s = make_sample(g, rec.x, rec.y, rec.z);
@@ -403,7 +412,8 @@ sample_grad_taps_kernel(Geom g, ClStrides cs, int b0, int nh, const float4* __re
     for (int h = 0; h < nh; ++h) {
       if (h > 0) {
         const float4* cur = reinterpret_cast<const float4*>(dp + ((long long)tap * nh + h) * slice_stride);
-        d0 = __ldg(cur); d1 = __ldg(cur + 8);
+        d0 = __ldg(cur);
+        if (!kNarrow) d1 = __ldg(cur + 8);
       }
       // corner values of this thread's 8 channels ([4j, 4j+4) and [32+4j, 32+4j+4)), as loaded
       uint4 c[8], chi[kF32X ? 8 : 1];
@@ -413,7 +423,7 @@ sample_grad_taps_kernel(Geom g, ClStrides cs, int b0, int nh, const float4* __re
         if constexpr (kF32X) {
           if ((valid >> q) & 1u) {
             c[q] = ptx::ldg_nc_v4(xb + off);
-            chi[q] = ptx::ldg_nc_v4(xb + off + 32);
+            chi[q] = kNarrow ? make_uint4(0u, 0u, 0u, 0u) : ptx::ldg_nc_v4(xb + off + 32);
           } else {
             c[q] = chi[q] = make_uint4(0u, 0u, 0u, 0u);
           }
@@ -431,9 +441,10 @@ sample_grad_taps_kernel(Geom g, ClStrides cs, int b0, int nh, const float4* __re
         const int dz = q >> 2, dy = (q >> 1) & 1, dx = q & 1;
         if constexpr (kF32X) {
           G[q] += d0.x * __uint_as_float(c[q].x) + d0.y * __uint_as_float(c[q].y) + d0.z * __uint_as_float(c[q].z) +
-                  d0.w * __uint_as_float(c[q].w) + d1.x * __uint_as_float(chi[q].x) +
-                  d1.y * __uint_as_float(chi[q].y) + d1.z * __uint_as_float(chi[q].z) +
-                  d1.w * __uint_as_float(chi[q].w);
+                  d0.w * __uint_as_float(c[q].w);
+          if (!kNarrow)
+            G[q] += d1.x * __uint_as_float(chi[q].x) + d1.y * __uint_as_float(chi[q].y) +
+                    d1.z * __uint_as_float(chi[q].z) + d1.w * __uint_as_float(chi[q].w);
         } else {
           const float2 x0 = __half22float2(bits_h2(c[q].x)), x1 = __half22float2(bits_h2(c[q].y));
           const float2 x2 = __half22float2(bits_h2(c[q].z)), x3 = __half22float2(bits_h2(c[q].w));
@@ -444,7 +455,7 @@ sample_grad_taps_kernel(Geom g, ClStrides cs, int b0, int nh, const float4* __re
           const float sw = mul_rn(mul_rn(wz[dz], wy[dy]), wx[dx]) * m;
           float* dst = gxb + (off0 + h * 64 + dz * cs.dz + dy * cs.dy + dx * cs.dx);
           red_add_v4(dst, sw * d0.x, sw * d0.y, sw * d0.z, sw * d0.w);
-          red_add_v4(dst + 32, sw * d1.x, sw * d1.y, sw * d1.z, sw * d1.w);
+          if (!kNarrow) red_add_v4(dst + 32, sw * d1.x, sw * d1.y, sw * d1.z, sw * d1.w);
         }
       }
     }
@@ -500,16 +511,20 @@ unstage_grad_input_kernel(int C, long long Vin, const float* __restrict__ gx_cl,
 
 struct BwdPlan {
   int nh, S, NT, KB, KBT, NB, tiles_per_clip, tmem_cols, smem_bytes, clips_per_chunk;
+  bool pairg;       // 32 channels per offset group: a 64-channel slice holds two neighbouring groups
   size_t x_cl_bytes, rec_bytes, gat_bytes, gy_img_bytes, wt_img_bytes, dcol_bytes, gx_cl_bytes, axes_bytes;
 };
 
 bool make_bwd_plan(const Geom& g, unsigned long long cap, bool x3, BwdPlan* pl) {
-  if (g.groups != 1 || g.cpg % 64 != 0 || g.Cout % 64 != 0 || g.Cout > 512) return false;
+  // the fp32-parity kernels also take 32 channels per group (an even number of groups): groups are
+  // contiguous channel ranges, so slices of 64 channels simply span two of them
+  pl->pairg = x3 && g.cpg == 32 && g.G % 2 == 0;
+  if (g.groups != 1 || (g.cpg % 64 != 0 && !pl->pairg) || g.Cout % 64 != 0 || g.Cout > 512) return false;
   if (g.Vin * g.Cin > 0x7fffffffLL) return false;
   if ((long long)g.G * g.K * g.B > 65535) return false;
   if (g.K * 64 * (int)sizeof(float) > 48 * 1024 || g.Cin > 65535) return false;   // weight staging kernel
-  pl->nh = g.cpg / 64;
-  pl->S = g.G * g.K * pl->nh;
+  pl->nh = pl->pairg ? 1 : g.cpg / 64;
+  pl->S = pl->pairg ? (g.G / 2) * g.K : g.G * g.K * pl->nh;
   pl->NT = pl->S * 64;
   pl->KBT = g.Cout / (x3 ? 32 : 64);                     // K blocks per image
   pl->KB = pl->KBT > 8 ? 8 : pl->KBT;                    // resident per launch (x3, Cout > 256: two launches)
@@ -579,7 +594,7 @@ int run_bwd(const Geom& g, bool x3, const Coords& coords, unsigned long long cap
       stage_input_cl_f16_kernel<<<grid, 256, 0, st>>>(g.Cin, g.Vin, x, reinterpret_cast<__half*>(x_cl));
     D2C_LAUNCH_CHECK();
     stage_wt_img_kernel<<<dim3((unsigned)pl.KBT, (unsigned)g.Cin), 64, 64 * g.K * sizeof(float), st>>>(
-        g.Cout, g.Cin, g.K, g.cpg, pl.nh, x3 ? 1 : 0, w, wt_img);
+        g.Cout, g.Cin, g.K, pl.pairg ? 64 : g.cpg, pl.nh, x3 ? 1 : 0, w, wt_img);
     D2C_LAUNCH_CHECK();
     if ((rc = launch_sample_records(g, coords, mask, recs, gat, st, x3))) return rc;
   }
@@ -613,7 +628,11 @@ int run_bwd(const Geom& g, bool x3, const Coords& coords, unsigned long long cap
     }
     prof_mark(st, "bwd_sample_grad");
     dim3 sgrid((unsigned)((g.V + 31) / 32), (unsigned)(nbc * g.G));
-    if (x3)
+    if (pl.pairg)
+      sample_grad_taps_kernel<FieldOut, true, true><<<sgrid, 256, 0, st>>>(g, cs, b0, pl.nh, recs, dcol, x_cl,
+                                                                           mask != nullptr, grad_coord, grad_mask,
+                                                                           gx_cl, field_nch, field_ch, axes_dev);
+    else if (x3)
       sample_grad_taps_kernel<FieldOut, true><<<sgrid, 256, 0, st>>>(g, cs, b0, pl.nh, recs, dcol, x_cl,
                                                                      mask != nullptr, grad_coord, grad_mask, gx_cl,
                                                                      field_nch, field_ch, axes_dev);
@@ -637,16 +656,20 @@ int run_bwd(const Geom& g, bool x3, const Coords& coords, unsigned long long cap
 
 }  // namespace
 
+// The single-pass bf16 kernels need 64 channels per offset group; with 32 the backward runs the fp32-parity
+// kernels in every tensor-core mode.
+static bool bwd_use_x3(const Geom& g, int math_mode) { return math_mode != D2C_MATH_BF16 || g.cpg % 64 != 0; }
+
 bool sm100_bwd_supported(const Geom& g, int dtype, int math_mode, unsigned long long cap) {
   if (dtype != D2C_F32 || math_mode == D2C_MATH_FP32) return false;
-  const bool x3 = math_mode != D2C_MATH_BF16;
+  const bool x3 = bwd_use_x3(g, math_mode);
   BwdPlan pl;
   return make_bwd_plan(g, cap, x3, &pl) && sm100_dw_workspace(g, x3) > 0;
 }
 
 size_t sm100_bwd_workspace(const Geom& g, int dtype, int math_mode, unsigned long long cap) {
   if (!sm100_bwd_supported(g, dtype, math_mode, cap)) return 0;
-  const bool x3 = math_mode != D2C_MATH_BF16;
+  const bool x3 = bwd_use_x3(g, math_mode);
   BwdPlan pl;
   make_bwd_plan(g, cap, x3, &pl);
   return pl.x_cl_bytes + pl.rec_bytes + pl.gat_bytes + pl.gy_img_bytes + pl.wt_img_bytes + pl.dcol_bytes + pl.gx_cl_bytes +
@@ -657,7 +680,7 @@ int sm100_bwd_offsets(const Geom& g, int math_mode, unsigned long long cap, cons
                       const float* mask, const float* w, float* grad_x, float* grad_offset, float* grad_mask,
                       float* grad_w, float* grad_bias, void* ws, cudaStream_t st) {
   OffsetCoords<float> oc{offset};
-  return run_bwd<OffsetCoords<float>, false>(g, math_mode != D2C_MATH_BF16, oc, cap, gy, x, mask, w, grad_x, grad_offset, 0, grad_mask, grad_w,
+  return run_bwd<OffsetCoords<float>, false>(g, bwd_use_x3(g, math_mode), oc, cap, gy, x, mask, w, grad_x, grad_offset, 0, grad_mask, grad_w,
                                              grad_bias, ws, st);
 }
 
@@ -665,7 +688,7 @@ int sm100_bwd_field(const Geom& g, int math_mode, unsigned long long cap, const 
                     const float* x, const float* mask, const float* w, float* grad_x, float* grad_size_map,
                     size_t grad_size_elems, float* grad_mask, float* grad_w, float* grad_bias, void* ws,
                     cudaStream_t st) {
-  return run_bwd<FieldCoords<float>, true>(g, math_mode != D2C_MATH_BF16, fc, cap, gy, x, mask, w, grad_x, grad_size_map, grad_size_elems,
+  return run_bwd<FieldCoords<float>, true>(g, bwd_use_x3(g, math_mode), fc, cap, gy, x, mask, w, grad_x, grad_size_map, grad_size_elems,
                                            grad_mask, grad_w, grad_bias, ws, st);
 }
 

@@ -49,6 +49,7 @@ struct DwParams {
   ClStrides cs;
   int N, nh, S, tiles_per_clip, n_tiles, tmem_cols;
   int n_pairs, tiles_per_split, NCH, b_stage_bytes;
+  int pairg;                 // bf16x3 only: 32 channels per offset group, a slice = two neighbouring groups
 };
 
 // grad_out [B][Cout][V] fp32 -> per (tile, 64-voxel block, 256-co chunk) images: 256 rows (co) x 128 B
@@ -233,15 +234,17 @@ dw_sm100_kernel(const DwParams p) {
           // x3: channels [32 sl, 32 sl + 32) of the CTA's slice
           const int s = kX3 ? pair : min(2 * pair + sl, p.S - 1);
           const int h = s % p.nh, gt = s / p.nh, tap = gt % g.K, grp = gt / g.K;
+          // slices of two 32-channel groups: the half-unit's channels belong to group 2 grp + sl
+          const int cpg = p.pairg ? kBK : g.cpg, grp_rec = p.pairg ? 2 * grp + sl : grp;
           const int sr = q % kRStages;
           if (!ptx::mbar_wait(r_empty(sr), ((q / kRStages) & 1) ^ 1, abort_flag, 200)) break;
           const int rows = min(kBM, g.V - v0);
           uint8_t* hdr = base_ptr + rec_off + sr * kRStageBytes + kRecBytes;
-          *reinterpret_cast<long long*>(hdr) = (long long)b * g.Vin * g.Cin + grp * g.cpg + h * kBK + (kX3 ? sl * 32 : 0);
+          *reinterpret_cast<long long*>(hdr) = (long long)b * g.Vin * g.Cin + grp * cpg + h * kBK + (kX3 ? sl * 32 : 0);
           *reinterpret_cast<int*>(hdr + 8) = rows;
           ptx::mbar_arrive_expect_tx(r_full(sr), (uint32_t)rows * 48u);
           ptx::bulk_g2s(rec_base + sr * kRStageBytes,
-                        p.recs + 3 * ((((long long)b * g.G + grp) * g.K + tap) * g.V + v0), (uint32_t)rows * 48u,
+                        p.recs + 3 * ((((long long)b * g.G + grp_rec) * g.K + tap) * g.V + v0), (uint32_t)rows * 48u,
                         r_full(sr));
         }
         const int issued = q;
@@ -350,16 +353,18 @@ unstage_dw_kernel(int Cout, int Cin, int K, int cpg, int nh, int S, const float*
 }
 
 struct DwPlan {
+  bool pairg;
   int nh, S, tiles_per_clip, n_tiles, tmem_cols;
   int n_pairs, nsplit, tiles_per_split, NCH, b_stage_bytes, smem_bytes;
   size_t gyk_bytes, dws_bytes;
 };
 
 bool make_dw_plan(const Geom& g, int sm_count, bool x3, DwPlan* dp) {
-  if (g.groups != 1 || g.cpg % kBK != 0 || g.Cout % 64 != 0 || g.Cout > 512) return false;
+  dp->pairg = x3 && g.cpg == 32 && g.G % 2 == 0;
+  if (g.groups != 1 || (g.cpg % kBK != 0 && !dp->pairg) || g.Cout % 64 != 0 || g.Cout > 512) return false;
   if (g.Vin * g.Cin > 0x7fffffffLL) return false;
-  dp->nh = g.cpg / kBK;
-  dp->S = g.G * g.K * dp->nh;
+  dp->nh = dp->pairg ? 1 : g.cpg / kBK;
+  dp->S = dp->pairg ? (g.G / 2) * g.K : g.G * g.K * dp->nh;
   dp->tiles_per_clip = (g.V + kBM - 1) / kBM;
   dp->n_tiles = dp->tiles_per_clip * g.B;
   int cols = 32;
@@ -416,6 +421,7 @@ int sm100_dw(const Geom& g, bool x3, const float* gy, const void* x_cl, const vo
   p.N = g.Cout; p.nh = dp.nh; p.S = dp.S; p.tiles_per_clip = dp.tiles_per_clip; p.n_tiles = dp.n_tiles;
   p.tmem_cols = dp.tmem_cols;
   p.n_pairs = dp.n_pairs; p.tiles_per_split = dp.tiles_per_split; p.NCH = dp.NCH; p.b_stage_bytes = dp.b_stage_bytes;
+  p.pairg = dp.pairg ? 1 : 0;
   prof_mark(st, "bwd_dw_sm100");
   if (x3) {
     D2C_CUDA_TRY(cudaFuncSetAttribute(dw_sm100_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, dp.smem_bytes));
@@ -427,7 +433,7 @@ int sm100_dw(const Geom& g, bool x3, const float* gy, const void* x_cl, const vo
   D2C_LAUNCH_CHECK();
   prof_mark(st, "bwd_dw_unstage");
   unstage_dw_kernel<<<dim3((unsigned)((dp.S * 64 + 31) / 32), (unsigned)((g.Cout + 31) / 32)), 256, 0, st>>>(
-      g.Cout, g.Cin, g.K, g.cpg, dp.nh, dp.S, dws, grad_w);
+      g.Cout, g.Cin, g.K, dp.pairg ? kBK : g.cpg, dp.nh, dp.S, dws, grad_w);
   D2C_LAUNCH_CHECK();
   return D2C_OK;
 }

@@ -162,3 +162,57 @@ def test_backward_chunked_by_intermediate_cap_fp32_parity_mode(dn):
         dn._ops.config.set_max_intermediate_elements(old)
     for a, b in zip(full, chunked):
         assert torch.allclose(a, b, rtol=1e-4, atol=1e-5 * float(a.abs().max()))
+
+
+@pytest.mark.parametrize("cfg", [
+    dict(B=2, Cin=256, Cout=128, dims=(2, 6, 9), G=8),      # the decoder's refine-block convs: 8 groups of 32
+    dict(B=1, Cin=64, Cout=64, dims=(3, 7, 8), G=2),
+    dict(B=2, Cin=128, Cout=512, dims=(2, 5, 6), G=4, stride=(1, 2, 1), dilation=(1, 1, 2)),   # two dcol launches
+])
+@pytest.mark.parametrize("tc_mode", ["auto", "bf16"])
+def test_backward_32_channels_per_offset_group(tc_mode, cfg):
+    """32 channels per offset group (even group count): the backward keeps 64-channel slices, each spanning two
+    neighbouring groups -- the sampling-gradient kernel serves one group per block on its half of the slice, the
+    weight-gradient kernel takes the two halves of a slice from the two groups' records.  The single-pass bf16
+    backward needs 64 channels per group, so `bf16` mode runs these fp32-parity kernels too: 1e-4 in both."""
+    import d2conv3d_b200
+    from d2conv3d_b200 import _lib, dconv_native
+    cfg = dict(cfg)
+    cfg.setdefault("padding", 1)
+    p = make_problem(860, dtype=np.float32, offset_std=2.0, **cfg)
+    kw = dict(stride=p["stride"], padding=p["padding"], dilation=p["dilation"], groups=1, offset_groups=cfg["G"])
+    d = lambda k: p[k].astype(np.float64)
+    want = orc.deform_conv3d_bwd(d("gy"), d("x"), d("geo"), d("mask"), d("weight"), True, **kw)
+    d2conv3d_b200.set_math_mode(tc_mode)
+    try:
+        ts = [cu(p[k]).requires_grad_() for k in ("x", "geo", "mask", "weight", "bias")]
+        y = dconv_native.deform_conv3d(*ts, p["stride"], p["padding"], p["dilation"], 1, cfg["G"])
+        _lib.profile_read(); _lib.profile_enable(True)
+        y.backward(cu(p["gy"]))
+        _lib.profile_enable(False)
+        _lib.device_status()
+    finally:
+        d2conv3d_b200.set_math_mode("auto")
+    phases = [n for n, _ in _lib.profile_read()]
+    assert "bwd_dcol_sm100" in phases and "bwd_sample_grad" in phases and "bwd_dw_sm100" in phases, phases
+    for t, w_, nm in zip(ts, want, ("grad_x", "grad_offset", "grad_mask", "grad_w", "grad_bias")):
+        err = np.abs(t.grad.cpu().numpy() - w_).max() / np.abs(w_).max()
+        print(f"{cfg} {nm}: rel err {err:.3e}")
+        assert err <= REL, nm
+
+
+def test_dyn_dilated_backward_32_channels_per_offset_group(dn):
+    G = 8
+    p = make_problem(870, 1, 256, 64, (3, 6, 8), padding=1, G=G, dtype=np.float32, field_mode="xyz")
+    want = orc.dyn_dilated_conv3d_bwd(p["gy"], p["x"], p["geo"], p["mask"], p["weight"], True, "xyz", padding=1,
+                                      offset_groups=G)
+    from d2conv3d_b200 import _lib
+    ts = [cu(p[k]).requires_grad_() for k in ("x", "geo", "mask", "weight", "bias")]
+    y = dn.dyn_dilated_conv3d(*ts, "xyz", 1, 1, 1, 1, G)
+    _lib.profile_read(); _lib.profile_enable(True)
+    y.backward(cu(p["gy"]))
+    _lib.profile_enable(False)
+    assert "bwd_dcol_sm100" in [n for n, _ in _lib.profile_read()]
+    for t, w_, nm in zip(ts, want, ("grad_x", "grad_size_map", "grad_mask", "grad_w", "grad_bias")):
+        err = np.abs(t.grad.cpu().numpy() - w_).max() / np.abs(w_).max()
+        assert err <= REL, (nm, err)
