@@ -384,6 +384,7 @@ sample_grad_taps_kernel(Geom g, ClStrides cs, int b0, int nh, const float4* __re
   const int chbase = grp * g.cpg + j * 4;
 
   const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  float fsum[3] = {0.f, 0.f, 0.f};
   float4 rec_n = __ldg(recp);
   float4 d0_n = __ldg(reinterpret_cast<const float4*>(dp));
   float4 d1_n = kNarrow ? zero4 : __ldg(reinterpret_cast<const float4*>(dp + 32));
@@ -481,12 +482,20 @@ sample_grad_taps_kernel(Geom g, ClStrides cs, int b0, int nh, const float4* __re
         go[g.V] = m * wts[1];
         go[2 * (long long)g.V] = m * wts[2];
       } else {
+        // the field's gradient sums over taps (and groups): taps are summed here, one atomic per group after
         const int k = tap % g.kw, jj = (tap / g.kw) % g.kh, i = tap / (g.kw * g.kh);
-        float* gs = grad_coord + (long long)b * field_nch * g.V + v;
-        if (field_ch.x >= 0) atomicAdd(gs + (long long)field_ch.x * g.V, field_axes[i] * (m * wts[0]));
-        if (field_ch.y >= 0) atomicAdd(gs + (long long)field_ch.y * g.V, field_axes[kMaxFieldKernelDim + jj] * (m * wts[1]));
-        if (field_ch.z >= 0) atomicAdd(gs + (long long)field_ch.z * g.V, field_axes[2 * kMaxFieldKernelDim + k] * (m * wts[2]));
+        fsum[0] += field_axes[i] * (m * wts[0]);
+        fsum[1] += field_axes[kMaxFieldKernelDim + jj] * (m * wts[1]);
+        fsum[2] += field_axes[2 * kMaxFieldKernelDim + k] * (m * wts[2]);
       }
+    }
+  }
+  if constexpr (FieldOut) {
+    if (active && j == 0) {
+      float* gs = grad_coord + (long long)b * field_nch * g.V + v;
+      if (field_ch.x >= 0) atomicAdd(gs + (long long)field_ch.x * g.V, fsum[0]);
+      if (field_ch.y >= 0) atomicAdd(gs + (long long)field_ch.y * g.V, fsum[1]);
+      if (field_ch.z >= 0) atomicAdd(gs + (long long)field_ch.z * g.V, fsum[2]);
     }
   }
 }
