@@ -354,7 +354,7 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
 // columns of tap t+1 are requested before tap t is processed, so the HBM stream of dcol (slice-major:
 // 8 KB contiguous per block and slice) stays in flight behind the L2 gathers and reductions.
 // kF32X: the channels-last staging of x is fp32 (fp32-parity mode) instead of fp16.
-// kNarrow (fp32 staging only): 32 channels per offset group.  The gradient columns keep their 64-channel
+// kNarrow: 32 channels per offset group.  The gradient columns keep their 64-channel
 // slices, each now holding two neighbouring groups; a block still serves one (clip, group) and its threads
 // own channels [4j, 4j+4) of the group's half of the slice.
 template <bool FieldOut, bool kF32X, bool kNarrow = false>
@@ -369,7 +369,6 @@ sample_grad_taps_kernel(Geom g, ClStrides cs, int b0, int nh, const float4* __re
   const int b = b0 + bl;
   const bool active = v < g.V;
   const int vc = active ? v : g.V - 1;                       // clamped: inactive threads load valid memory
-  static_assert(!kNarrow || kF32X, "the narrow variant reads the fp32 staging");
   const long long S = kNarrow ? (long long)(g.G / 2) * g.K : (long long)g.G * g.K * nh;
   const float4* recp = recs + (((long long)b * g.G + grp) * g.K) * g.V + vc;
   // thread j owns channels [4j, 4j+4) and [32+4j, 32+4j+4) of a slice: one warp-wide 16-byte access then
@@ -430,7 +429,8 @@ sample_grad_taps_kernel(Geom g, ClStrides cs, int b0, int nh, const float4* __re
           }
         } else {
           if ((valid >> q) & 1u) {
-            const uint2 lo = ptx::ldg_nc_v2(xb + off), hi = ptx::ldg_nc_v2(xb + off + 32);
+            const uint2 lo = ptx::ldg_nc_v2(xb + off);
+            const uint2 hi = kNarrow ? make_uint2(0u, 0u) : ptx::ldg_nc_v2(xb + off + 32);
             c[q] = make_uint4(lo.x, lo.y, hi.x, hi.y);
           } else {
             c[q] = make_uint4(0u, 0u, 0u, 0u);
@@ -449,8 +449,8 @@ sample_grad_taps_kernel(Geom g, ClStrides cs, int b0, int nh, const float4* __re
         } else {
           const float2 x0 = __half22float2(bits_h2(c[q].x)), x1 = __half22float2(bits_h2(c[q].y));
           const float2 x2 = __half22float2(bits_h2(c[q].z)), x3 = __half22float2(bits_h2(c[q].w));
-          G[q] += d0.x * x0.x + d0.y * x0.y + d0.z * x1.x + d0.w * x1.y + d1.x * x2.x + d1.y * x2.y +
-                  d1.z * x3.x + d1.w * x3.y;
+          G[q] += d0.x * x0.x + d0.y * x0.y + d0.z * x1.x + d0.w * x1.y;
+          if (!kNarrow) G[q] += d1.x * x2.x + d1.y * x2.y + d1.z * x3.x + d1.w * x3.y;
         }
         if (((valid >> q) & 1u) && okz[dz] && oky[dy] && okx[dx]) {
           const float sw = mul_rn(mul_rn(wz[dz], wy[dy]), wx[dx]) * m;
@@ -525,9 +525,9 @@ struct BwdPlan {
 };
 
 bool make_bwd_plan(const Geom& g, unsigned long long cap, bool x3, BwdPlan* pl) {
-  // the fp32-parity kernels also take 32 channels per group (an even number of groups): groups are
-  // contiguous channel ranges, so slices of 64 channels simply span two of them
-  pl->pairg = x3 && g.cpg == 32 && g.G % 2 == 0;
+  // 32 channels per group (an even number of groups): groups are contiguous channel ranges, so slices of 64
+  // channels simply span two of them
+  pl->pairg = g.cpg == 32 && g.G % 2 == 0;
   if (g.groups != 1 || (g.cpg % 64 != 0 && !pl->pairg) || g.Cout % 64 != 0 || g.Cout > 512) return false;
   if (g.Vin * g.Cin > 0x7fffffffLL) return false;
   if ((long long)g.G * g.K * g.B > 65535) return false;
@@ -637,10 +637,14 @@ int run_bwd(const Geom& g, bool x3, const Coords& coords, unsigned long long cap
     }
     prof_mark(st, "bwd_sample_grad");
     dim3 sgrid((unsigned)((g.V + 31) / 32), (unsigned)(nbc * g.G));
-    if (pl.pairg)
+    if (pl.pairg && x3)
       sample_grad_taps_kernel<FieldOut, true, true><<<sgrid, 256, 0, st>>>(g, cs, b0, pl.nh, recs, dcol, x_cl,
                                                                            mask != nullptr, grad_coord, grad_mask,
                                                                            gx_cl, field_nch, field_ch, axes_dev);
+    else if (pl.pairg)
+      sample_grad_taps_kernel<FieldOut, false, true><<<sgrid, 256, 0, st>>>(g, cs, b0, pl.nh, recs, dcol, x_cl,
+                                                                            mask != nullptr, grad_coord, grad_mask,
+                                                                            gx_cl, field_nch, field_ch, axes_dev);
     else if (x3)
       sample_grad_taps_kernel<FieldOut, true><<<sgrid, 256, 0, st>>>(g, cs, b0, pl.nh, recs, dcol, x_cl,
                                                                      mask != nullptr, grad_coord, grad_mask, gx_cl,
@@ -665,20 +669,24 @@ int run_bwd(const Geom& g, bool x3, const Coords& coords, unsigned long long cap
 
 }  // namespace
 
-// The single-pass bf16 kernels need 64 channels per offset group; with 32 the backward runs the fp32-parity
-// kernels in every tensor-core mode.
-static bool bwd_use_x3(const Geom& g, int math_mode) { return math_mode != D2C_MATH_BF16 || g.cpg % 64 != 0; }
+// bf16 mode runs the single-pass kernels where their plans fit (32 channels per group: the weight gradient needs
+// room for a second record set, i.e. Cout <= 256) and the fp32-parity kernels otherwise.
+static bool bwd_use_x3(const Geom& g, int math_mode, unsigned long long cap) {
+  if (math_mode != D2C_MATH_BF16) return true;
+  BwdPlan pl;
+  return !(make_bwd_plan(g, cap, false, &pl) && sm100_dw_workspace(g, false) > 0);
+}
 
 bool sm100_bwd_supported(const Geom& g, int dtype, int math_mode, unsigned long long cap) {
   if (dtype != D2C_F32 || math_mode == D2C_MATH_FP32) return false;
-  const bool x3 = bwd_use_x3(g, math_mode);
+  const bool x3 = bwd_use_x3(g, math_mode, cap);
   BwdPlan pl;
   return make_bwd_plan(g, cap, x3, &pl) && sm100_dw_workspace(g, x3) > 0;
 }
 
 size_t sm100_bwd_workspace(const Geom& g, int dtype, int math_mode, unsigned long long cap) {
   if (!sm100_bwd_supported(g, dtype, math_mode, cap)) return 0;
-  const bool x3 = bwd_use_x3(g, math_mode);
+  const bool x3 = bwd_use_x3(g, math_mode, cap);
   BwdPlan pl;
   make_bwd_plan(g, cap, x3, &pl);
   return pl.x_cl_bytes + pl.rec_bytes + pl.gat_bytes + pl.gy_img_bytes + pl.wt_img_bytes + pl.dcol_bytes + pl.gx_cl_bytes +
@@ -689,7 +697,7 @@ int sm100_bwd_offsets(const Geom& g, int math_mode, unsigned long long cap, cons
                       const float* mask, const float* w, float* grad_x, float* grad_offset, float* grad_mask,
                       float* grad_w, float* grad_bias, void* ws, cudaStream_t st) {
   OffsetCoords<float> oc{offset};
-  return run_bwd<OffsetCoords<float>, false>(g, bwd_use_x3(g, math_mode), oc, cap, gy, x, mask, w, grad_x, grad_offset, 0, grad_mask, grad_w,
+  return run_bwd<OffsetCoords<float>, false>(g, bwd_use_x3(g, math_mode, cap), oc, cap, gy, x, mask, w, grad_x, grad_offset, 0, grad_mask, grad_w,
                                              grad_bias, ws, st);
 }
 
@@ -697,7 +705,7 @@ int sm100_bwd_field(const Geom& g, int math_mode, unsigned long long cap, const 
                     const float* x, const float* mask, const float* w, float* grad_x, float* grad_size_map,
                     size_t grad_size_elems, float* grad_mask, float* grad_w, float* grad_bias, void* ws,
                     cudaStream_t st) {
-  return run_bwd<FieldCoords<float>, true>(g, bwd_use_x3(g, math_mode), fc, cap, gy, x, mask, w, grad_x, grad_size_map, grad_size_elems,
+  return run_bwd<FieldCoords<float>, true>(g, bwd_use_x3(g, math_mode, cap), fc, cap, gy, x, mask, w, grad_x, grad_size_map, grad_size_elems,
                                            grad_mask, grad_w, grad_bias, ws, st);
 }
 

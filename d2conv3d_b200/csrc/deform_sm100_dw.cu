@@ -32,8 +32,8 @@ constexpr int kChunkBytes = 256 * 128;               // one 256-row (co) x 64-vo
 constexpr int kThreads = (6 + 16 + 1) * 32;   // 4 epilogue + MMA + grad_out loader + 16 gather + record loader warps
 constexpr int kEpiWarps = 4, kMmaWarp = 4, kLoadWarp = 5, kGatherWarp0 = 6, kGatherWarps = 16, kRecWarp = 22;
 constexpr int kRStages = 4;                       // gather-record ring, one stage per (tile, slice) half-unit
-constexpr int kRecBytes = kBM * 48;               // 6 KB of records ...
-constexpr int kRStageBytes = kRecBytes + 16;      // ... + header {int64 x_cl element offset of the slice, int rows}
+constexpr int kRecBytes = kBM * 48;               // 6 KB of records per set; a stage adds a 16-byte header
+                                                  // {int64 x_cl element offset of the slice, int rows}
 constexpr int kRowStride = kGatherWarps * 4;          // 8 threads per row -> rows handled per pass
 constexpr int kRowsPerThread = kBM / kRowStride;
 constexpr int kSmemLimit = 227 * 1024;
@@ -95,17 +95,22 @@ stage_gy_kmajor_kernel(int Cout, int V, int tiles_per_clip, int NCH, int x3, con
 //   parts of the fp32 sampled tile (rows 0-63 / 64-127 of the accumulator), every voxel block of grad_out comes
 //   as a hi image and a lo image and both are accumulated: (a_hi + a_lo)(g_hi + g_lo), all four products; the
 //   two accumulator halves meet in the same dws rows through the epilogue's reductions.
-template <int kX3>
+// kDual = 1 (bf16 mode only): 32 channels per offset group; a 64-channel slice spans two neighbouring groups, a
+//   record stage holds both groups' records and the 16-byte chunks 0-3 / 4-7 of a row use the first / second set.
+template <int kX3, int kDual>
 __global__ void __launch_bounds__(kThreads, 1)
 dw_sm100_kernel(const DwParams p) {
+  static_assert(!(kX3 && kDual), "the fp32-parity kernel's 32-channel half-units need no second record set");
   constexpr int kBSteps = kX3 ? 4 : 2;      // grad_out images per tile: voxel block x (hi, lo)
+  constexpr int kRStage = (1 + kDual) * kRecBytes + 16;     // record set(s) + header
+  constexpr int hdr_off = (1 + kDual) * kRecBytes;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = ptx::smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - raw);
   const uint32_t a_base = base, b_base = base + kAStages * kAStageBytes;
   const int rec_off = kAStages * kAStageBytes + kBStages * p.b_stage_bytes;
-  const int bar_off = rec_off + kRStages * kRStageBytes;
+  const int bar_off = rec_off + kRStages * kRStage;
   const uint32_t rec_base = base + rec_off, bar_base = base + bar_off;
   auto a_full = [&](int s) { return bar_base + 8u * s; };
   auto a_empty = [&](int s) { return bar_base + 8u * (2 + s); };
@@ -239,13 +244,17 @@ dw_sm100_kernel(const DwParams p) {
           const int sr = q % kRStages;
           if (!ptx::mbar_wait(r_empty(sr), ((q / kRStages) & 1) ^ 1, abort_flag, 200)) break;
           const int rows = min(kBM, g.V - v0);
-          uint8_t* hdr = base_ptr + rec_off + sr * kRStageBytes + kRecBytes;
+          uint8_t* hdr = base_ptr + rec_off + sr * kRStage + hdr_off;
           *reinterpret_cast<long long*>(hdr) = (long long)b * g.Vin * g.Cin + grp * cpg + h * kBK + (kX3 ? sl * 32 : 0);
           *reinterpret_cast<int*>(hdr + 8) = rows;
-          ptx::mbar_arrive_expect_tx(r_full(sr), (uint32_t)rows * 48u);
-          ptx::bulk_g2s(rec_base + sr * kRStageBytes,
-                        p.recs + 3 * ((((long long)b * g.G + grp_rec) * g.K + tap) * g.V + v0), (uint32_t)rows * 48u,
-                        r_full(sr));
+          ptx::mbar_arrive_expect_tx(r_full(sr), (uint32_t)rows * 48u * (uint32_t)(1 + kDual));
+#pragma unroll
+          for (int set = 0; set <= kDual; ++set) {
+            const int og = kDual ? 2 * grp + set : grp_rec;     // offset group whose records fill this set
+            ptx::bulk_g2s(rec_base + sr * kRStage + set * kRecBytes,
+                          p.recs + 3 * ((((long long)b * g.G + og) * g.K + tap) * g.V + v0), (uint32_t)rows * 48u,
+                          r_full(sr));
+          }
         }
         const int issued = q;
         for (int w = (issued > kRStages ? issued - kRStages : 0); w < issued; ++w) {
@@ -268,9 +277,11 @@ dw_sm100_kernel(const DwParams p) {
       for (int q = 0; q < nq; ++q) {
         const int t = q >> 1, sl = q & 1, sa = t % kAStages, sr = q % kRStages;
         if (!ptx::mbar_wait(r_full(sr), (q / kRStages) & 1, abort_flag)) break;
-        const uint8_t* rec_stage = base_ptr + rec_off + sr * kRStageBytes;
-        const long long xoff = *reinterpret_cast<const long long*>(rec_stage + kRecBytes);
-        const int rows = *reinterpret_cast<const int*>(rec_stage + kRecBytes + 8);
+        const uint8_t* rec_stage0 = base_ptr + rec_off + sr * kRStage;
+        const long long xoff = *reinterpret_cast<const long long*>(rec_stage0 + hdr_off);
+        const int rows = *reinterpret_cast<const int*>(rec_stage0 + hdr_off + 8);
+        // dual: channels 32-63 of the slice (16-byte chunks 4-7) belong to the second offset group
+        const uint8_t* rec_stage = rec_stage0 + ((kDual && j >= 4) ? kRecBytes : 0);
         // every corner of every row this thread owns goes in flight before the first blend
         uint4 c[kRowsPerThread][8];
 #pragma unroll
@@ -360,7 +371,7 @@ struct DwPlan {
 };
 
 bool make_dw_plan(const Geom& g, int sm_count, bool x3, DwPlan* dp) {
-  dp->pairg = x3 && g.cpg == 32 && g.G % 2 == 0;
+  dp->pairg = g.cpg == 32 && g.G % 2 == 0;      // bf16 mode: two record sets per stage (kDual)
   if (g.groups != 1 || (g.cpg % kBK != 0 && !dp->pairg) || g.Cout % 64 != 0 || g.Cout > 512) return false;
   if (g.Vin * g.Cin > 0x7fffffffLL) return false;
   dp->nh = dp->pairg ? 1 : g.cpg / kBK;
@@ -373,7 +384,8 @@ bool make_dw_plan(const Geom& g, int sm_count, bool x3, DwPlan* dp) {
   dp->n_pairs = x3 ? dp->S : (dp->S + 1) / 2;
   dp->NCH = (g.Cout + 255) / 256;
   dp->b_stage_bytes = dp->NCH * kChunkBytes;
-  dp->smem_bytes = kAStages * kAStageBytes + kBStages * dp->b_stage_bytes + kRStages * kRStageBytes + 256 + 1024;
+  const int r_stage = ((dp->pairg && !x3) ? 2 : 1) * kRecBytes + 16;
+  dp->smem_bytes = kAStages * kAStageBytes + kBStages * dp->b_stage_bytes + kRStages * r_stage + 256 + 1024;
   if (dp->smem_bytes > kSmemLimit) return false;
   // enough (pair, voxel-range) work items for ~3 waves, but at least 8 tiles per item
   int nsplit = (3 * sm_count + dp->n_pairs - 1) / dp->n_pairs;
@@ -423,13 +435,9 @@ int sm100_dw(const Geom& g, bool x3, const float* gy, const void* x_cl, const vo
   p.n_pairs = dp.n_pairs; p.tiles_per_split = dp.tiles_per_split; p.NCH = dp.NCH; p.b_stage_bytes = dp.b_stage_bytes;
   p.pairg = dp.pairg ? 1 : 0;
   prof_mark(st, "bwd_dw_sm100");
-  if (x3) {
-    D2C_CUDA_TRY(cudaFuncSetAttribute(dw_sm100_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, dp.smem_bytes));
-    dw_sm100_kernel<1><<<dp.n_pairs * dp.nsplit, kThreads, dp.smem_bytes, st>>>(p);
-  } else {
-    D2C_CUDA_TRY(cudaFuncSetAttribute(dw_sm100_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, dp.smem_bytes));
-    dw_sm100_kernel<0><<<dp.n_pairs * dp.nsplit, kThreads, dp.smem_bytes, st>>>(p);
-  }
+  auto kern = x3 ? dw_sm100_kernel<1, 0> : (dp.pairg ? dw_sm100_kernel<0, 1> : dw_sm100_kernel<0, 0>);
+  D2C_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, dp.smem_bytes));
+  kern<<<dp.n_pairs * dp.nsplit, kThreads, dp.smem_bytes, st>>>(p);
   D2C_LAUNCH_CHECK();
   prof_mark(st, "bwd_dw_unstage");
   unstage_dw_kernel<<<dim3((unsigned)((dp.S * 64 + 31) / 32), (unsigned)((g.Cout + 31) / 32)), 256, 0, st>>>(

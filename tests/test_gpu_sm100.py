@@ -152,10 +152,9 @@ def test_backward_bf16_mode_vs_oracle(dn, ci):
         assert err <= REL_BF16_GRAD, nm
 
 
-@pytest.mark.parametrize("mode", ["x", "xyz"])
-def test_dyn_dilated_backward_bf16_mode(dn, mode):
-    G = 2
-    p = make_problem(430, 2, 128, 64, (4, 9, 10), padding=1, G=G, dtype=np.float32, field_mode=mode)
+@pytest.mark.parametrize("mode,G,Cin", [("x", 2, 128), ("xyz", 2, 128), ("xyz", 8, 256)])   # last: 32 channels per group
+def test_dyn_dilated_backward_bf16_mode(dn, mode, G, Cin):
+    p = make_problem(430, 2, Cin, 64, (4, 9, 10), padding=1, G=G, dtype=np.float32, field_mode=mode)
     want = orc.dyn_dilated_conv3d_bwd(p["gy"], p["x"], p["geo"], p["mask"], p["weight"], True, mode, padding=1,
                                       offset_groups=G)
     ts = [cu(p[k]).requires_grad_() for k in ("x", "geo", "mask", "weight", "bias")]

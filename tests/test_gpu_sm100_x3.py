@@ -173,8 +173,9 @@ def test_backward_chunked_by_intermediate_cap_fp32_parity_mode(dn):
 def test_backward_32_channels_per_offset_group(tc_mode, cfg):
     """32 channels per offset group (even group count): the backward keeps 64-channel slices, each spanning two
     neighbouring groups -- the sampling-gradient kernel serves one group per block on its half of the slice, the
-    weight-gradient kernel takes the two halves of a slice from the two groups' records.  The single-pass bf16
-    backward needs 64 channels per group, so `bf16` mode runs these fp32-parity kernels too: 1e-4 in both."""
+    weight-gradient kernel takes the two halves of a slice from the two groups' records.  fp32-parity mode: 1e-4;
+    `bf16` mode: its 2e-2 (single-pass kernels with two record sets per stage up to Cout = 256, the fp32-parity
+    kernels above that)."""
     import d2conv3d_b200
     from d2conv3d_b200 import _lib, dconv_native
     cfg = dict(cfg)
@@ -197,8 +198,8 @@ def test_backward_32_channels_per_offset_group(tc_mode, cfg):
     assert "bwd_dcol_sm100" in phases and "bwd_sample_grad" in phases and "bwd_dw_sm100" in phases, phases
     for t, w_, nm in zip(ts, want, ("grad_x", "grad_offset", "grad_mask", "grad_w", "grad_bias")):
         err = np.abs(t.grad.cpu().numpy() - w_).max() / np.abs(w_).max()
-        print(f"{cfg} {nm}: rel err {err:.3e}")
-        assert err <= REL, nm
+        print(f"{cfg} {tc_mode} {nm}: rel err {err:.3e}")
+        assert err <= (REL if tc_mode == "auto" else 2e-2), nm
 
 
 def test_dyn_dilated_backward_32_channels_per_offset_group(dn):
