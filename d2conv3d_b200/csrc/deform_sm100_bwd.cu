@@ -129,7 +129,6 @@ struct DcolParams {
   float* dcol;             // [clips_in_chunk * V][NT]
   int V, NT, KB, NB;       // KB: K blocks (128-byte rows) contracted by this launch
   int KBT, kb0;            // K blocks per image (image stride) and first block of this launch
-  int accumulate;          // add to dcol instead of overwriting it (second launch of a split contraction)
   int tiles_per_clip, n_tiles;
   long long n_units;       // n_tiles * NB
   int tmem_cols;
@@ -137,7 +136,9 @@ struct DcolParams {
 
 // kX3 = 1 (fp32-parity mode): a K block is 32 co with rows [hi | lo] in both operands and the issuer forms
 // g_hi*w_hi + g_lo*w_hi + g_hi*w_lo from the 16-wide K sub-blocks; the grad_out tile of Cout = 512 is then
-// 256 KB, so the contraction runs as two launches over half of the K blocks each, the second accumulating.
+// 256 KB, so the contraction runs as two launches over half of the K blocks each, into two partial buffers
+// that the sampling-gradient kernel adds as it reads them (a second launch that read-modify-wrote the first
+// one's result cost 0.87 ms against 0.50 ms).
 template <int kX3>
 __global__ void __launch_bounds__(kDcolThreads, 1)
 dcol_sm100_kernel(const DcolParams p) {
@@ -199,25 +200,10 @@ dcol_sm100_kernel(const DcolParams p) {
       auto chunk_ptr = [&](int c0) {   // this lane's first 16-byte slot of the even row in the 32-column chunk c0
         return reinterpret_cast<float4*>(row - (odd ? 64 : 0) + (c0 >> 6) * slice_stride + (c0 & 63) + (odd ? 4 : 0));
       };
-      // accumulating launch: the previous launch's values of a chunk are requested one chunk ahead (the first
-      // chunk's before the wait for the accumulator), so their latency hides behind the MMAs / the previous chunk
-      const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
-      float4 old_e[4], old_o[4];
-      auto prefetch_old = [&](int c0, float4 (&oe)[4], float4 (&oo)[4]) {
-        const float4* src = chunk_ptr(c0);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          oe[i] = ok_even ? src[2 * i] : zero4;
-          oo[i] = ok_odd ? src[2 * i + 16] : zero4;
-        }
-      };
       const int c_beg = half * 128, c_end = min(ncols, half * 128 + 128);
-      if (p.accumulate && c_beg < c_end) prefetch_old(c_beg, old_e, old_o);
       if (!ptx::mbar_wait(acc_full(acc), (q >> 1) & 1, abort_flag)) break;
       ptx::tc_fence_after();
       for (int c0 = c_beg; c0 < c_end; c0 += 32) {
-        float4 nxt_e[4], nxt_o[4];
-        if (p.accumulate && c0 + 32 < c_end) prefetch_old(c0 + 32, nxt_e, nxt_o);
         uint32_t r[32];
         ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * kNBlock + c0), r);
         ptx::tmem_ld_wait();
@@ -241,16 +227,8 @@ dcol_sm100_kernel(const DcolParams p) {
             second = make_float4(__uint_as_float(recv[0]), __uint_as_float(recv[1]), __uint_as_float(recv[2]),
                                  __uint_as_float(recv[3]));
           }
-          if (p.accumulate) {              // each element belongs to exactly one thread: plain read-add-write
-            first.x += old_e[i].x; first.y += old_e[i].y; first.z += old_e[i].z; first.w += old_e[i].w;
-            second.x += old_o[i].x; second.y += old_o[i].y; second.z += old_o[i].z; second.w += old_o[i].w;
-          }
           if (ok_even) dst[2 * i] = first;
           if (ok_odd) dst[2 * i + 16] = second;    // next row: + 64 floats
-        }
-        if (p.accumulate) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) { old_e[i] = nxt_e[i]; old_o[i] = nxt_o[i]; }
         }
       }
       ptx::tc_fence_before();
@@ -360,7 +338,7 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
 template <bool FieldOut, bool kF32X, bool kNarrow = false>
 __global__ void __launch_bounds__(256, kF32X ? 2 : 3)
 sample_grad_taps_kernel(Geom g, ClStrides cs, int b0, int nh, const float4* __restrict__ recs,
-                        const float* __restrict__ dcol, const void* __restrict__ x_cl_v, bool has_mask,
+                        const float* __restrict__ dcol, long long dcol2_off, const void* __restrict__ x_cl_v, bool has_mask,
                         float* __restrict__ grad_coord, float* __restrict__ grad_mask, float* __restrict__ gx_cl,
                         int field_nch, int3 field_ch, const float* __restrict__ field_axes) {
   const int j = threadIdx.x & 7;
@@ -384,17 +362,28 @@ sample_grad_taps_kernel(Geom g, ClStrides cs, int b0, int nh, const float4* __re
 
   const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
   float fsum[3] = {0.f, 0.f, 0.f};
+  // gradient columns of a contraction split over two launches arrive as two partial buffers, dcol2_off apart
+  auto ld_cols = [&](const float* q, float4& a, float4& b) {
+    a = __ldg(reinterpret_cast<const float4*>(q));
+    b = kNarrow ? zero4 : __ldg(reinterpret_cast<const float4*>(q + 32));
+    if (kF32X && dcol2_off) {        // only the fp32-parity contraction is ever split
+      const float4 a2 = __ldg(reinterpret_cast<const float4*>(q + dcol2_off));
+      a.x += a2.x; a.y += a2.y; a.z += a2.z; a.w += a2.w;
+      if (!kNarrow) {
+        const float4 b2 = __ldg(reinterpret_cast<const float4*>(q + dcol2_off + 32));
+        b.x += b2.x; b.y += b2.y; b.z += b2.z; b.w += b2.w;
+      }
+    }
+  };
   float4 rec_n = __ldg(recp);
-  float4 d0_n = __ldg(reinterpret_cast<const float4*>(dp));
-  float4 d1_n = kNarrow ? zero4 : __ldg(reinterpret_cast<const float4*>(dp + 32));
+  float4 d0_n, d1_n;
+  ld_cols(dp, d0_n, d1_n);
   for (int tap = 0; tap < g.K; ++tap) {
     const float4 rec = rec_n;
     float4 d0 = d0_n, d1 = d1_n;
     if (tap + 1 < g.K) {
       rec_n = __ldg(recp + (long long)(tap + 1) * g.V);
-      const float4* nx = reinterpret_cast<const float4*>(dp + (long long)(tap + 1) * nh * slice_stride);
-      d0_n = __ldg(nx);
-      if (!kNarrow) d1_n = __ldg(nx + 8);
+      ld_cols(dp + (long long)(tap + 1) * nh * slice_stride, d0_n, d1_n);
     }
     const float m = rec.w;
     const Sample<float> s = make_sample(g, rec.x, rec.y, rec.z);
@@ -411,9 +400,7 @@ sample_grad_taps_kernel(Geom g, ClStrides cs, int b0, int nh, const float4* __re
     for (int q = 0; q < 8; ++q) G[q] = 0.f;
     for (int h = 0; h < nh; ++h) {
       if (h > 0) {
-        const float4* cur = reinterpret_cast<const float4*>(dp + ((long long)tap * nh + h) * slice_stride);
-        d0 = __ldg(cur);
-        if (!kNarrow) d1 = __ldg(cur + 8);
+        ld_cols(dp + ((long long)tap * nh + h) * slice_stride, d0, d1);
       }
       // corner values of this thread's 8 channels ([4j, 4j+4) and [32+4j, 32+4j+4)), as loaded
       uint4 c[8], chi[kF32X ? 8 : 1];
@@ -441,16 +428,22 @@ sample_grad_taps_kernel(Geom g, ClStrides cs, int b0, int nh, const float4* __re
       for (int q = 0; q < 8; ++q) {
         const int dz = q >> 2, dy = (q >> 1) & 1, dx = q & 1;
         if constexpr (kF32X) {
-          G[q] += d0.x * __uint_as_float(c[q].x) + d0.y * __uint_as_float(c[q].y) + d0.z * __uint_as_float(c[q].z) +
-                  d0.w * __uint_as_float(c[q].w);
-          if (!kNarrow)
-            G[q] += d1.x * __uint_as_float(chi[q].x) + d1.y * __uint_as_float(chi[q].y) +
+          if constexpr (kNarrow)
+            G[q] += d0.x * __uint_as_float(c[q].x) + d0.y * __uint_as_float(c[q].y) +
+                    d0.z * __uint_as_float(c[q].z) + d0.w * __uint_as_float(c[q].w);
+          else
+            G[q] += d0.x * __uint_as_float(c[q].x) + d0.y * __uint_as_float(c[q].y) +
+                    d0.z * __uint_as_float(c[q].z) + d0.w * __uint_as_float(c[q].w) +
+                    d1.x * __uint_as_float(chi[q].x) + d1.y * __uint_as_float(chi[q].y) +
                     d1.z * __uint_as_float(chi[q].z) + d1.w * __uint_as_float(chi[q].w);
         } else {
           const float2 x0 = __half22float2(bits_h2(c[q].x)), x1 = __half22float2(bits_h2(c[q].y));
           const float2 x2 = __half22float2(bits_h2(c[q].z)), x3 = __half22float2(bits_h2(c[q].w));
-          G[q] += d0.x * x0.x + d0.y * x0.y + d0.z * x1.x + d0.w * x1.y;
-          if (!kNarrow) G[q] += d1.x * x2.x + d1.y * x2.y + d1.z * x3.x + d1.w * x3.y;
+          if constexpr (kNarrow)
+            G[q] += d0.x * x0.x + d0.y * x0.y + d0.z * x1.x + d0.w * x1.y;
+          else
+            G[q] += d0.x * x0.x + d0.y * x0.y + d0.z * x1.x + d0.w * x1.y + d1.x * x2.x + d1.y * x2.y +
+                    d1.z * x3.x + d1.w * x3.y;
         }
         if (((valid >> q) & 1u) && okz[dz] && oky[dy] && okx[dx]) {
           const float sw = mul_rn(mul_rn(wz[dz], wy[dy]), wx[dx]) * m;
@@ -548,7 +541,7 @@ bool make_bwd_plan(const Geom& g, unsigned long long cap, bool x3, BwdPlan* pl) 
   pl->gat_bytes = gather_records_bytes(g);
   pl->gy_img_bytes = align_up((size_t)pl->clips_per_chunk * pl->tiles_per_clip * pl->KBT * kABlockBytes, 256);
   pl->wt_img_bytes = align_up((size_t)pl->NB * pl->KBT * kBStageBytes, 256);
-  pl->dcol_bytes = align_up((size_t)pl->clips_per_chunk * g.V * pl->NT * 4, 256);
+  pl->dcol_bytes = align_up((size_t)pl->clips_per_chunk * g.V * pl->NT * 4 * (pl->KBT > pl->KB ? 2 : 1), 256);
   pl->gx_cl_bytes = align_up((size_t)g.B * g.Vin * g.Cin * 4, 256);
   pl->axes_bytes = 256;
   return true;
@@ -627,8 +620,13 @@ int run_bwd(const Geom& g, bool x3, const Coords& coords, unsigned long long cap
     if (grid < 1) grid = 1;
     prof_mark(st, "bwd_dcol_sm100");
     p.KBT = pl.KBT;
+    // a contraction longer than the resident grad_out tile (fp32-parity mode, Cout > 256) runs as two launches
+    // into two partial buffers that the sampling-gradient kernel adds while it reads them
+    const long long dcol_part = (long long)pl.clips_per_chunk * g.V * pl.NT;
+    const long long dcol2_off = pl.KBT > pl.KB ? dcol_part : 0;
     for (int kb0 = 0; kb0 < pl.KBT; kb0 += pl.KB) {      // bf16 mode and Cout <= 256: a single launch
-      p.kb0 = kb0; p.KB = (pl.KBT - kb0 < pl.KB) ? pl.KBT - kb0 : pl.KB; p.accumulate = kb0 > 0;
+      p.kb0 = kb0; p.KB = (pl.KBT - kb0 < pl.KB) ? pl.KBT - kb0 : pl.KB;
+      p.dcol = dcol + (kb0 > 0 ? dcol_part : 0);
       if (x3)
         dcol_sm100_kernel<1><<<(unsigned)grid, kDcolThreads, pl.smem_bytes, st>>>(p);
       else
@@ -638,19 +636,19 @@ int run_bwd(const Geom& g, bool x3, const Coords& coords, unsigned long long cap
     prof_mark(st, "bwd_sample_grad");
     dim3 sgrid((unsigned)((g.V + 31) / 32), (unsigned)(nbc * g.G));
     if (pl.pairg && x3)
-      sample_grad_taps_kernel<FieldOut, true, true><<<sgrid, 256, 0, st>>>(g, cs, b0, pl.nh, recs, dcol, x_cl,
+      sample_grad_taps_kernel<FieldOut, true, true><<<sgrid, 256, 0, st>>>(g, cs, b0, pl.nh, recs, dcol, dcol2_off, x_cl,
                                                                            mask != nullptr, grad_coord, grad_mask,
                                                                            gx_cl, field_nch, field_ch, axes_dev);
     else if (pl.pairg)
-      sample_grad_taps_kernel<FieldOut, false, true><<<sgrid, 256, 0, st>>>(g, cs, b0, pl.nh, recs, dcol, x_cl,
+      sample_grad_taps_kernel<FieldOut, false, true><<<sgrid, 256, 0, st>>>(g, cs, b0, pl.nh, recs, dcol, dcol2_off, x_cl,
                                                                             mask != nullptr, grad_coord, grad_mask,
                                                                             gx_cl, field_nch, field_ch, axes_dev);
     else if (x3)
-      sample_grad_taps_kernel<FieldOut, true><<<sgrid, 256, 0, st>>>(g, cs, b0, pl.nh, recs, dcol, x_cl,
+      sample_grad_taps_kernel<FieldOut, true><<<sgrid, 256, 0, st>>>(g, cs, b0, pl.nh, recs, dcol, dcol2_off, x_cl,
                                                                      mask != nullptr, grad_coord, grad_mask, gx_cl,
                                                                      field_nch, field_ch, axes_dev);
     else
-      sample_grad_taps_kernel<FieldOut, false><<<sgrid, 256, 0, st>>>(g, cs, b0, pl.nh, recs, dcol, x_cl,
+      sample_grad_taps_kernel<FieldOut, false><<<sgrid, 256, 0, st>>>(g, cs, b0, pl.nh, recs, dcol, dcol2_off, x_cl,
                                                                       mask != nullptr, grad_coord, grad_mask, gx_cl,
                                                                       field_nch, field_ch, axes_dev);
     D2C_LAUNCH_CHECK();

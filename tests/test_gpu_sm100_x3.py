@@ -111,8 +111,8 @@ def test_dyn_dilated_fp32_parity_mode(dn, mode):
 @pytest.mark.parametrize("ci", [0, 1, 2, 3, 4, 6, 7])
 def test_backward_fp32_parity_mode_vs_oracle(dn, ci):
     """All five gradients on the tensor-core tier in the fp32-parity mode against the float64 oracle; 1e-4 of
-    each gradient's scale (case 3: Cout = 512, the gradient-column contraction runs as two accumulating
-    launches; case 4: Cout = 320, a partial second launch)."""
+    each gradient's scale (case 3: Cout = 512, the gradient-column contraction runs as two launches
+    into two partial buffers; case 4: Cout = 320, a partial second launch)."""
     from d2conv3d_b200 import _lib
     cfg = dict(CASES[ci])
     cfg.setdefault("k", 3)
