@@ -196,11 +196,13 @@ def run_reference_arm(args):
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised in profiles/
 # (same workload); None where no capture has been taken.
 TRAFFIC_PER_LAUNCH = {       # (phase, math mode) -> DRAM read + write bytes of one launch (profiles/c2_fwd_bwd_step_kernels.md)
-    ("bwd_sample_grad", "bf16"): 1.603e9 + 0.137e9, ("bwd_sample_grad", "auto"): 1.630e9 + 0.139e9,
-    ("bwd_sample_grad", "bf16x3"): 1.630e9 + 0.139e9,
-    ("fwd_sm100_fused", "bf16"): 0.420e9 + 0.056e9, ("fwd_sm100_fused", "auto"): 1.096e9 + 0.072e9,
+    # fp32-parity mode, Cout = 512: the gradient columns arrive as two partial buffers (2 x 1.43 GB read)
+    ("bwd_sample_grad", "bf16"): 1.603e9 + 0.137e9, ("bwd_sample_grad", "auto"): 3.065e9 + 0.142e9,
+    ("bwd_sample_grad", "bf16x3"): 3.065e9 + 0.142e9,
+    ("fwd_sm100_fused", "bf16"): 0.420e9 + 0.056e9, ("fwd_sm100_fused", "auto"): 1.141e9 + 0.070e9,
     ("bwd_dcol_sm100", "bf16"): 0.076e9 + 1.382e9, ("bwd_dw_sm100", "bf16"): 0.430e9 + 0.073e9,
-    ("bwd_dw_sm100", "auto"): 0.556e9 + 0.070e9,
+    ("bwd_dw_sm100", "auto"): 0.554e9 + 0.066e9,
+    ("bwd_dcol_sm100", "auto"): 2 * (0.088e9 + 1.384e9), ("bwd_dcol_sm100", "bf16x3"): 2 * (0.088e9 + 1.384e9),
 }
 
 PHASE_WORK = {
