@@ -506,16 +506,16 @@ def run_gpu_arm(args):
 
 
 EXTRA_WORKLOADS = {
-    # BASELINE config 1: the plumbing / correctness layer (launch-latency bound at this size)
+    # benchmark configuration 1: the plumbing / correctness layer (launch-latency bound at this size)
     "c1": dict(kind="deform", B=1, Cin=64, Cout=64, dims=(4, 16, 16), G=1, offset_std=1.0),
-    # BASELINE config 3: dynamic-dilation conv3d, one field shared by all taps, optional 27-channel mask
+    # benchmark configuration 3: dynamic-dilation conv3d, one field shared by all taps, optional 27-channel mask
     "c3-xyz": dict(kind="dyndil", mode="xyz", B=4, Cin=256, Cout=256, dims=(8, 60, 108), G=1),
     "c3-xy": dict(kind="dyndil", mode="xy", B=4, Cin=256, Cout=256, dims=(8, 60, 108), G=1),
     "c3-x": dict(kind="dyndil", mode="x", B=4, Cin=256, Cout=256, dims=(8, 60, 108), G=1),
-    # BASELINE config 4: depthwise 3x3x3 of an ir-CSN bottleneck, then the modulated deformable 1024->256 stage
+    # benchmark configuration 4: depthwise 3x3x3 of an ir-CSN bottleneck, then the modulated deformable 1024->256 stage
     "c4-depthwise": dict(kind="depthwise", B=8, C=1024, dims=(8, 30, 54)),
     "c4-md": dict(kind="deform", B=8, Cin=1024, Cout=256, dims=(8, 30, 54), G=8),
-    # BASELINE config 5 (decoder inference): the xyz dynamic-dilated 256->256 conv of a refine block at the
+    # benchmark configuration 5 (decoder inference): the xyz dynamic-dilated 256->256 conv of a refine block at the
     # stride-4 pyramid level, one clip, 8 offset groups (32 channels per group), forward only
     "c5-e1": dict(kind="dyndil", mode="xyz", B=1, Cin=256, Cout=256, dims=(8, 120, 214), G=8, fwd_only=True),
     # the same layer with its backward (decoder training)
@@ -524,7 +524,7 @@ EXTRA_WORKLOADS = {
 
 
 def run_decoder_workload(args):
-    """BASELINE config 5: decoder inference on synthetic ir-CSN features, clips sharded over the ranks with no
+    """Benchmark configuration 5: decoder inference on synthetic ir-CSN features, clips sharded over the ranks with no
     collective (one process per GPU under torchrun; one rank otherwise).  Every rank pushes its share of the 32
     clips through the decoder one clip at a time (forward only, no_grad); rank 0 prints clips/s of the whole job
     from the slowest rank's CUDA-event time."""

@@ -48,7 +48,7 @@ def t3(v):
 
 def make_problem(seed, B, Cin, Cout, dims, k=3, stride=1, padding=0, dilation=1, groups=1, G=1, dtype=np.float32,
                  offset_std=1.0, bias=True, mask=True, field_mode=None):
-    """Seeded synthetic problem in the BASELINE style: x ~ N(0,1), offsets ~ N(0, offset_std),
+    """Seeded synthetic problem in the style of the benchmark configurations: x ~ N(0,1), offsets ~ N(0, offset_std),
     mask = sigmoid(N(0,1)), weight ~ Kaiming-normal, bias ~ N(0,1)."""
     rng = np.random.default_rng(seed)
     k, s, p, d = t3(k), t3(stride), t3(padding), t3(dilation)

@@ -1,4 +1,4 @@
-"""GPU checks at the full sizes of the BASELINE configurations, where the CPU oracle is too slow: properties
+"""GPU checks at the full sizes of the benchmark configurations, where the CPU oracle is too slow: properties
 that do not depend on size (the identities the reference's own test-suite uses,
 ops/dconv-native/test/test_deform_conv.py:262-330 and test_modules.py:48-67) checked against cuDNN / PyTorch,
 and -- when baseline/_ref holds the reference's compiled op -- the reference's own CUDA kernels on the same

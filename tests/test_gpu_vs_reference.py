@@ -42,7 +42,7 @@ GEOMS = [
     dict(B=2, Cin=8, Cout=8, dims=(4, 9, 11), k=3, padding=1, G=2),
     dict(B=1, Cin=16, Cout=24, dims=(3, 8, 8), k=(1, 3, 3), padding=(0, 1, 1), stride=(1, 2, 2), G=4, groups=2),
     dict(B=3, Cin=6, Cout=6, dims=(5, 6, 7), k=(3, 1, 3), padding=(2, 0, 2), dilation=(2, 1, 2), G=3, groups=6),
-    dict(B=1, Cin=64, Cout=64, dims=(4, 16, 16), k=3, padding=1, G=1),        # BASELINE config 1
+    dict(B=1, Cin=64, Cout=64, dims=(4, 16, 16), k=3, padding=1, G=1),        # benchmark configuration 1
 ]
 NAMES = ("y", "grad_x", "grad_offset", "grad_mask", "grad_w", "grad_bias")
 
