@@ -402,26 +402,27 @@ sample_grad_taps_kernel(Geom g, ClStrides cs, int b0, int nh, const float4* __re
       if (h > 0) {
         ld_cols(dp + ((long long)tap * nh + h) * slice_stride, d0, d1);
       }
-      // corner values of this thread's 8 channels ([4j, 4j+4) and [32+4j, 32+4j+4)), as loaded
+      // corner values of this thread's 8 channels ([4j, 4j+4) and [32+4j, 32+4j+4)), as loaded.  fp16 staging:
+      // the loads are unconditional -- a corner outside the volume reads the clip's first voxel instead and its
+      // dot product is discarded by a select after the slice loop (a select, so a non-finite stand-in cannot
+      // leak); measured 0.13 ms per step faster than predicated loads.  fp32 staging: predicated loads (twice
+      // the bytes per corner; fetching the stand-ins measured 0.08 ms slower).
       uint4 c[8], chi[kF32X ? 8 : 1];
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
-        const int off = off0 + h * 64 + (q >> 2) * cs.dz + ((q >> 1) & 1) * cs.dy + (q & 1) * cs.dx;
+        const int off_in = off0 + h * 64 + (q >> 2) * cs.dz + ((q >> 1) & 1) * cs.dy + (q & 1) * cs.dx;
         if constexpr (kF32X) {
           if ((valid >> q) & 1u) {
-            c[q] = ptx::ldg_nc_v4(xb + off);
-            chi[q] = kNarrow ? make_uint4(0u, 0u, 0u, 0u) : ptx::ldg_nc_v4(xb + off + 32);
+            c[q] = ptx::ldg_nc_v4(xb + off_in);
+            chi[q] = kNarrow ? make_uint4(0u, 0u, 0u, 0u) : ptx::ldg_nc_v4(xb + off_in + 32);
           } else {
             c[q] = chi[q] = make_uint4(0u, 0u, 0u, 0u);
           }
         } else {
-          if ((valid >> q) & 1u) {
-            const uint2 lo = ptx::ldg_nc_v2(xb + off);
-            const uint2 hi = kNarrow ? make_uint2(0u, 0u) : ptx::ldg_nc_v2(xb + off + 32);
-            c[q] = make_uint4(lo.x, lo.y, hi.x, hi.y);
-          } else {
-            c[q] = make_uint4(0u, 0u, 0u, 0u);
-          }
+          const int off = ((valid >> q) & 1u) ? off_in : chbase + h * 64;
+          const uint2 lo = ptx::ldg_nc_v2(xb + off);
+          const uint2 hi = kNarrow ? make_uint2(0u, 0u) : ptx::ldg_nc_v2(xb + off + 32);
+          c[q] = make_uint4(lo.x, lo.y, hi.x, hi.y);
         }
       }
 #pragma unroll
@@ -453,9 +454,10 @@ sample_grad_taps_kernel(Geom g, ClStrides cs, int b0, int nh, const float4* __re
         }
       }
     }
-    // channel reduction of the 8 corner dot-products across the voxel's 8 threads
+    // channel reduction of the 8 corner dot-products across the voxel's 8 threads (corners outside: zero)
 #pragma unroll
     for (int q = 0; q < 8; ++q) {
+      if (!kF32X) G[q] = ((valid >> q) & 1u) ? G[q] : 0.f;
       G[q] += __shfl_xor_sync(0xffffffffu, G[q], 1);
       G[q] += __shfl_xor_sync(0xffffffffu, G[q], 2);
       G[q] += __shfl_xor_sync(0xffffffffu, G[q], 4);
