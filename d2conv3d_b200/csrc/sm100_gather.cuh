@@ -35,66 +35,74 @@ namespace {
 __device__ __forceinline__ uint32_t h2_bits(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
 __device__ __forceinline__ __half2 bits_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
 
-template <typename Coords>
+// kShared: the coordinates do not depend on the offset group (dilation field): a thread serves one (voxel, tap)
+// and all groups, computing the position, corners and weights once and applying each group's modulation.
+template <typename Coords, bool kShared>
 static __global__ void __launch_bounds__(256)
 sample_records_kernel(Geom g, Coords coords, const float* __restrict__ mask, float4* __restrict__ pos,
                       uint4* __restrict__ gat, int f32_weights) {
   const int v = blockIdx.x * 256 + threadIdx.x;
   if (v >= g.V) return;
-  const int tap = blockIdx.y % g.K, grp = blockIdx.y / g.K, b = blockIdx.z;
+  const int tap = kShared ? blockIdx.y : blockIdx.y % g.K, b = blockIdx.z;
+  const int grp_beg = kShared ? 0 : blockIdx.y / g.K, grp_end = kShared ? g.G : grp_beg + 1;
   int bz, by, bx;
   voxel_tap_base(g, v, tap, bz, by, bx);
   float z, y, x;
-  coords.get(g, b, grp, tap, v, bz, by, bx, z, y, x);
-  const long long i = (((long long)b * g.G + grp) * g.K + tap) * g.V + v;
-  const float m = mask ? __ldg(mask + i) : 1.f;
-  if (pos) pos[i] = make_float4(z, y, x, m);
-  if (gat) {
-    const Sample<float> s = make_sample(g, z, y, x);
-    float a[8];
-    sample_weights(s, a);
-    uint32_t w[8];
+  coords.get(g, b, grp_beg, tap, v, bz, by, bx, z, y, x);
+  const Sample<float> s = make_sample(g, z, y, x);
+  float a[8];
+  sample_weights(s, a);
+  const unsigned valid = s.inside ? s.valid : 0u;
+  int cz, cy, cx;
+  unsigned steps = 0;
+  {
+    const bool z0ok = s.z0 >= 0 && s.z0 < g.D, z1ok = s.z0 + 1 >= 0 && s.z0 + 1 < g.D;
+    const bool y0ok = s.y0 >= 0 && s.y0 < g.H, y1ok = s.y0 + 1 >= 0 && s.y0 + 1 < g.H;
+    const bool x0ok = s.x0 >= 0 && s.x0 < g.W, x1ok = s.x0 + 1 >= 0 && s.x0 + 1 < g.W;
+    cz = z0ok ? s.z0 : (z1ok ? s.z0 + 1 : 0);
+    cy = y0ok ? s.y0 : (y1ok ? s.y0 + 1 : 0);
+    cx = x0ok ? s.x0 : (x1ok ? s.x0 + 1 : 0);
+    steps = (x0ok && x1ok ? 1u : 0u) | (y0ok && y1ok ? 2u : 0u) | (z0ok && z1ok ? 4u : 0u);
+  }
+  const int voff = ((cz * g.H + cy) * g.W + cx) * g.Cin;
+  for (int grp = grp_beg; grp < grp_end; ++grp) {
+    const long long i = (((long long)b * g.G + grp) * g.K + tap) * g.V + v;
+    const float m = mask ? __ldg(mask + i) : 1.f;
+    if (pos) pos[i] = make_float4(z, y, x, m);
+    if (gat) {
+      uint4* o = gat + 3 * i;
+      if (f32_weights) {
+        // fp32-parity mode: the 48 bytes hold the eight products a_j*mask in fp32
+        uint32_t f[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) w[j] = h2_bits(__float2half2_rn(a[j] * m));
-    const unsigned valid = s.inside ? s.valid : 0u;
+        for (int j = 0; j < 8; ++j) f[j] = ((valid >> j) & 1u) ? __float_as_uint(a[j] * m) : 0u;
+        o[0] = make_uint4((uint32_t)voff, steps, f[0], f[1]);
+        o[1] = make_uint4(f[2], f[3], f[4], f[5]);
+        o[2] = make_uint4(f[6], f[7], 0u, 0u);
+      } else {
+        uint32_t w[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
-      if (!((valid >> j) & 1u)) w[j] = 0u;
-    int cz, cy, cx;
-    unsigned steps = 0;
-    {
-      const bool z0ok = s.z0 >= 0 && s.z0 < g.D, z1ok = s.z0 + 1 >= 0 && s.z0 + 1 < g.D;
-      const bool y0ok = s.y0 >= 0 && s.y0 < g.H, y1ok = s.y0 + 1 >= 0 && s.y0 + 1 < g.H;
-      const bool x0ok = s.x0 >= 0 && s.x0 < g.W, x1ok = s.x0 + 1 >= 0 && s.x0 + 1 < g.W;
-      cz = z0ok ? s.z0 : (z1ok ? s.z0 + 1 : 0);
-      cy = y0ok ? s.y0 : (y1ok ? s.y0 + 1 : 0);
-      cx = x0ok ? s.x0 : (x1ok ? s.x0 + 1 : 0);
-      steps = (x0ok && x1ok ? 1u : 0u) | (y0ok && y1ok ? 2u : 0u) | (z0ok && z1ok ? 4u : 0u);
-    }
-    const int voff = ((cz * g.H + cy) * g.W + cx) * g.Cin;
-    uint4* o = gat + 3 * i;
-    if (f32_weights) {
-      // fp32-parity mode: the same 48 bytes hold the eight products a_j*mask in fp32
-      uint32_t f[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) f[j] = ((valid >> j) & 1u) ? __float_as_uint(a[j] * m) : 0u;
-      o[0] = make_uint4((uint32_t)voff, steps, f[0], f[1]);
-      o[1] = make_uint4(f[2], f[3], f[4], f[5]);
-      o[2] = make_uint4(f[6], f[7], 0u, 0u);
-    } else {
-      o[0] = make_uint4((uint32_t)voff, steps, 0u, 0u);
-      o[1] = make_uint4(w[0], w[1], w[2], w[3]);
-      o[2] = make_uint4(w[4], w[5], w[6], w[7]);
+        for (int j = 0; j < 8; ++j) w[j] = ((valid >> j) & 1u) ? h2_bits(__float2half2_rn(a[j] * m)) : 0u;
+        o[0] = make_uint4((uint32_t)voff, steps, 0u, 0u);
+        o[1] = make_uint4(w[0], w[1], w[2], w[3]);
+        o[2] = make_uint4(w[4], w[5], w[6], w[7]);
+      }
     }
   }
 }
 
 template <typename Coords>
+struct CoordsSharedAcrossGroups { static constexpr bool value = false; };
+template <typename T>
+struct CoordsSharedAcrossGroups<FieldCoords<T>> { static constexpr bool value = true; };
+
+template <typename Coords>
 static int launch_sample_records(const Geom& g, const Coords& coords, const float* mask, float4* pos, uint4* gat,
                                  cudaStream_t st, bool f32_weights = false) {
-  dim3 grid((unsigned)((g.V + 255) / 256), (unsigned)(g.G * g.K), (unsigned)g.B);
+  constexpr bool kShared = CoordsSharedAcrossGroups<Coords>::value;
+  dim3 grid((unsigned)((g.V + 255) / 256), (unsigned)(kShared ? g.K : g.G * g.K), (unsigned)g.B);
   if (grid.y > 65535 || grid.z > 65535) return D2C_ERR_TOO_LARGE;
-  sample_records_kernel<Coords><<<grid, 256, 0, st>>>(g, coords, mask, pos, gat, f32_weights ? 1 : 0);
+  sample_records_kernel<Coords, kShared><<<grid, 256, 0, st>>>(g, coords, mask, pos, gat, f32_weights ? 1 : 0);
   D2C_LAUNCH_CHECK();
   return D2C_OK;
 }
