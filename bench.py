@@ -149,7 +149,9 @@ def cpu_arm(steps, warmup, budget_s):
     ladder so that warmup+steps fit the time budget.  Returns (TFLOP/s, ms per step, sample text)."""
     from oracle import oracle as orc
     wl = WORKLOAD
-    cores = os.cpu_count() or 1
+    # all host cores, whatever OMP_NUM_THREADS the launcher exported (torchrun sets 1 for its ranks)
+    avail = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    cores = orc.set_threads(avail)
     probe = make_inputs(5, wl, B=1, dims=(2, 4, wl["dims"][2]))
     cpu_step(orc, probe)
     t0 = time.perf_counter(); cpu_step(orc, probe); tp = time.perf_counter() - t0

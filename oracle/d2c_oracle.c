@@ -67,6 +67,18 @@ static int orc_make_geom_dw(const d2c_conv_desc* d, orc_geom* g) {
   return 0;
 }
 
+/* OpenMP team size of the loops below.  A launcher may have exported OMP_NUM_THREADS=1 before this library was
+ * loaded (torchrun does for every rank); the timing legs set the team size explicitly instead. */
+#ifdef _OPENMP
+#include <omp.h>
+int orc_set_threads(int n) {
+  if (n > 0) omp_set_num_threads(n);
+  return omp_get_max_threads();
+}
+#else
+int orc_set_threads(int n) { (void)n; return 1; }
+#endif
+
 int orc_output_dims(const d2c_conv_desc* d, int32_t out[3]) {
   orc_geom g;
   if (orc_fill(d, &g)) return -1;

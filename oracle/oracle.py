@@ -49,6 +49,13 @@ def lib():
     return _lib
 
 
+def set_threads(n=0):
+    """Sets the OpenMP team size of the oracle's loops (n <= 0: leave it) and returns the size in effect."""
+    f = lib().orc_set_threads
+    f.argtypes, f.restype = [ctypes.c_int], ctypes.c_int
+    return int(f(int(n)))
+
+
 def _triple(v):
     return tuple(v) if isinstance(v, (tuple, list)) else (v, v, v)
 
