@@ -195,3 +195,19 @@ def test_oracle_deform_conv1d_identities():
     y = orc.deform_conv1d_fwd(x, off, None, w, b, 1, 0, 1, groups, 1)
     ref = torch.nn.functional.conv1d(torch.from_numpy(xs), torch.from_numpy(w), torch.from_numpy(b), 1, 0, 1, groups).numpy()
     assert np.allclose(y, ref, atol=1e-12)
+
+
+def test_oracle_thread_count_can_be_set_explicitly():
+    """The timing legs of the bench set the OpenMP team size themselves (a launcher may export OMP_NUM_THREADS=1);
+    results do not depend on it."""
+    from tests._util import make_problem
+    p = make_problem(77, 1, 4, 4, (2, 4, 4), padding=1, dtype=np.float64)
+    before = orc.set_threads(0)
+    try:
+        assert orc.set_threads(2) == 2
+        y2 = orc.deform_conv3d_fwd(p["x"], p["geo"], p["mask"], p["weight"], p["bias"], padding=1)
+        assert orc.set_threads(1) == 1
+        y1 = orc.deform_conv3d_fwd(p["x"], p["geo"], p["mask"], p["weight"], p["bias"], padding=1)
+        assert np.array_equal(y1, y2)
+    finally:
+        orc.set_threads(before)
