@@ -59,6 +59,8 @@ def lib():
         L.d2c_status_string.restype = ctypes.c_char_p
         L.d2c_last_cuda_error.restype = ctypes.c_char_p
         L.d2c_launch_count.restype = ctypes.c_uint64
+        L.d2c_device_status_clear.restype = None
+        L.d2c_selftest_wait_expiry.argtypes = [ctypes.c_uint32, vp]
         L.d2c_profile_enable.argtypes = [i32]
         L.d2c_profile_read.argtypes = [ctypes.POINTER(ProfileRecord), i32, ctypes.POINTER(i32)]
         L.d2c_set_math_mode.argtypes = [i32]
@@ -68,6 +70,8 @@ def lib():
         L.d2c_deform_conv3d_fwd.argtypes = [dp] + [vp] * 7 + [sz, vp]
         L.d2c_deform_conv3d_bwd.argtypes = [dp] + [vp] * 11 + [sz, vp]
         L.d2c_deform_conv3d_corners.argtypes = [dp, vp, vp, vp]
+        L.d2c_deform_conv1d_fwd.argtypes = [dp] + [vp] * 6 + [vp]
+        L.d2c_deform_conv1d_bwd.argtypes = [dp] + [vp] * 11 + [sz, vp]
         L.d2c_dyn_dilated_conv3d_fwd.argtypes = [dp, i32] + [vp] * 7 + [sz, vp]
         L.d2c_dyn_dilated_conv3d_bwd.argtypes = [dp, i32] + [vp] * 11 + [sz, vp]
         L.d2c_dyn_dilated_conv3d_corners.argtypes = [dp, i32, vp, vp, vp]
@@ -142,8 +146,13 @@ def get_math_mode():
 
 
 def device_status():
-    """Synchronises and raises if a device-side bounded wait gave up."""
+    """Synchronises, then raises (once: the report clears the flag) if a kernel's bounded wait gave up
+    since the last report on this device."""
     check(lib().d2c_device_status(), "device status")
+
+
+def device_status_clear():
+    lib().d2c_device_status_clear()
 
 
 def launch_count():

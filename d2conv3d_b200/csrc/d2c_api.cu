@@ -38,12 +38,72 @@ static std::atomic<int> g_math_mode{D2C_MATH_AUTO};
 // Default of the reference's MAX_INTERMEDIATE_ELEMENTS (csrc/ops/dconv3d_gpu.cu:12).
 static std::atomic<unsigned long long> g_max_intermediate{1ull << 32};
 
+// ---- per-device state ---------------------------------------------------------------------------
+constexpr int kMaxDevices = 64;
+
+// Status words: one int per device (64 bytes apart) in a page of the library's own image that is page-locked
+// and mapped into the devices' address space on first use -- nothing is allocated.  A kernel whose bounded wait
+// gave up stores 1 there (sm100_ptx.cuh: report_device_timeout); the host reads it at the start of the next
+// library call on that device, reports D2C_ERR_DEVICE_TIMEOUT once and clears it.
+struct alignas(4096) StatusPage { volatile int word[kMaxDevices][16]; };
+static StatusPage g_status_page;
+static std::mutex g_status_mu;
+static bool g_status_registered = false;
+static int* g_status_dev_ptr[kMaxDevices];
+
+int status_word_device_ptr(int** dev_ptr) {
+  int dev = -1;
+  D2C_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return D2C_ERR_TOO_LARGE;
+  std::lock_guard<std::mutex> lk(g_status_mu);
+  if (!g_status_registered) {
+    D2C_CUDA_TRY(cudaHostRegister((void*)&g_status_page, sizeof(g_status_page),
+                                  cudaHostRegisterMapped | cudaHostRegisterPortable));
+    g_status_registered = true;
+  }
+  if (!g_status_dev_ptr[dev]) {
+    void* d = nullptr;
+    D2C_CUDA_TRY(cudaHostGetDevicePointer(&d, (void*)&g_status_page.word[dev][0], 0));
+    g_status_dev_ptr[dev] = reinterpret_cast<int*>(d);
+  }
+  *dev_ptr = g_status_dev_ptr[dev];
+  return D2C_OK;
+}
+
+// Reads and clears the current device's status word.  No synchronisation: sees what finished kernels reported.
+static int status_take() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return D2C_OK;
+  volatile int* w = &g_status_page.word[dev][0];
+  if (*w == 0) return D2C_OK;
+  *w = 0;
+  return D2C_ERR_DEVICE_TIMEOUT;
+}
+#define D2C_TAKE_STATUS()                      \
+  do {                                         \
+    const int _st = ::d2c::status_take();      \
+    if (_st) return _st;                       \
+  } while (0)
+
+int device_sm_count(int* out) {
+  static std::atomic<int> cache[kMaxDevices];
+  int dev = -1;
+  D2C_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return D2C_ERR_TOO_LARGE;
+  int n = cache[dev].load(std::memory_order_relaxed);
+  if (n == 0) {
+    D2C_CUDA_TRY(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
+    cache[dev].store(n, std::memory_order_relaxed);
+  }
+  *out = n;
+  return D2C_OK;
+}
+
 int depthwise_fwd(const Geom& g, int dtype, const void* x, const void* w, const void* bias, void* y,
                   cudaStream_t st);
 int depthwise_bwd(const Geom& g, int dtype, const void* gy, const void* x, const void* w, void* gx,
                   void* gw, void* gbias, void* ws, cudaStream_t st);
 size_t depthwise_bwd_workspace(const Geom& g);
-int depthwise_device_status();
 
 static size_t dtype_size(int dtype) { return dtype == D2C_F64 ? 8 : (dtype == D2C_F16 ? 2 : 4); }
 
@@ -99,8 +159,8 @@ static bool ws_ok(const void* ws, size_t have, size_t need) {
   return ws != nullptr && (reinterpret_cast<uintptr_t>(ws) % 256) == 0 && have >= need;
 }
 
-static size_t generic_bwd_workspace(const Geom& g, int dtype) {
-  const int nb = bwd_slice_clips(g, g_max_intermediate.load());
+static size_t generic_bwd_workspace(const Geom& g, int dtype, unsigned long long cap) {
+  const int nb = bwd_slice_clips(g, cap);
   return align_up(dtype_size(dtype) * (size_t)nb * g.Cin * g.K * g.V, 256);
 }
 
@@ -142,14 +202,17 @@ size_t d2c_workspace_bytes(int op, const d2c_conv_desc* desc) {
   Geom g;
   const bool dw = (op == D2C_OP_DEPTHWISE_FWD || op == D2C_OP_DEPTHWISE_BWD);
   if (make_geom(desc, &g, dw)) return 0;
+  // the mode and the cap are read once per call: a concurrent setter cannot make one call see two plans
+  const int mode = g_math_mode.load();
+  const unsigned long long cap = g_max_intermediate.load();
   switch (op) {
     case D2C_OP_DEFORM_FWD:
     case D2C_OP_DYNDIL_FWD:
-      return sm100_fwd_workspace(g, desc->dtype, g_math_mode.load());
+      return sm100_fwd_workspace(g, desc->dtype, mode);
     case D2C_OP_DEFORM_BWD:
     case D2C_OP_DYNDIL_BWD: {
-      const size_t fast = sm100_bwd_workspace(g, desc->dtype, g_math_mode.load(), g_max_intermediate.load());
-      const size_t gen = generic_bwd_workspace(g, desc->dtype);
+      const size_t fast = sm100_bwd_workspace(g, desc->dtype, mode, cap);
+      const size_t gen = generic_bwd_workspace(g, desc->dtype, cap);
       return fast > gen ? fast : gen;
     }
     case D2C_OP_DEPTHWISE_BWD:
@@ -186,10 +249,23 @@ const char* d2c_last_cuda_error(void) { return g_last_cuda_error; }
 int d2c_device_status(void) {
   int rc = check_cuda(cudaDeviceSynchronize());
   if (rc) return rc;
-  const int v1 = sm100_device_status() | depthwise_device_status(), v2 = sm100_bwd_device_status() | sm100_dw_device_status();
-  if (v1 < 0 || v2 < 0) return D2C_ERR_CUDA;
-  const int v = v1 | v2;
-  return v ? D2C_ERR_DEVICE_TIMEOUT : D2C_OK;
+  return status_take();
+}
+
+int d2c_device_status_peek(void) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return D2C_ERR_CUDA;
+  return g_status_page.word[dev][0] ? D2C_ERR_DEVICE_TIMEOUT : D2C_OK;
+}
+
+void d2c_device_status_clear(void) { (void)status_take(); }
+
+int d2c_selftest_wait_expiry(uint32_t budget_us, d2c_stream_t stream) {
+  if (budget_us == 0 || budget_us > 100000u) return D2C_ERR_SHAPE;     // at most 0.1 s
+  int dev = 0, khz = 0;
+  D2C_CUDA_TRY(cudaGetDevice(&dev));
+  D2C_CUDA_TRY(cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, dev));
+  return sm100_selftest_wait_expiry((long long)budget_us * (long long)(khz / 1000), (cudaStream_t)stream);
 }
 
 uint64_t d2c_launch_count(void) { return g_launches.load(); }
@@ -236,6 +312,7 @@ int d2c_deform_conv3d_fwd(const d2c_conv_desc* desc, const void* x, const void* 
   int rc = make_geom(desc, &g, false);
   if (rc) return rc;
   cudaStream_t st = (cudaStream_t)stream;
+  D2C_TAKE_STATUS();
   if (desc->dtype == D2C_F32) {
     OffsetCoords<float> oc{(const float*)offset};
     const int mode = g_math_mode.load();
@@ -265,15 +342,17 @@ int d2c_deform_conv3d_bwd(const d2c_conv_desc* desc, const void* grad_y, const v
   if (rc) return rc;
   if (desc->dtype != D2C_F32 && desc->dtype != D2C_F64) return D2C_ERR_DTYPE;
   cudaStream_t st = (cudaStream_t)stream;
+  D2C_TAKE_STATUS();
   const unsigned long long cap = g_max_intermediate.load();
-  if (sm100_bwd_supported(g, desc->dtype, g_math_mode.load(), cap)) {
-    if (!ws_ok(workspace, workspace_bytes, sm100_bwd_workspace(g, desc->dtype, g_math_mode.load(), cap)))
+  const int mode = g_math_mode.load();
+  if (sm100_bwd_supported(g, desc->dtype, mode, cap)) {
+    if (!ws_ok(workspace, workspace_bytes, sm100_bwd_workspace(g, desc->dtype, mode, cap)))
       return D2C_ERR_WORKSPACE;
-    return sm100_bwd_offsets(g, g_math_mode.load(), cap, (const float*)grad_y, (const float*)x, (const float*)offset,
+    return sm100_bwd_offsets(g, mode, cap, (const float*)grad_y, (const float*)x, (const float*)offset,
                              (const float*)mask, (const float*)w, (float*)grad_x, (float*)grad_offset,
                              (float*)grad_mask, (float*)grad_w, (float*)grad_bias, workspace, st);
   }
-  const size_t need = generic_bwd_workspace(g, desc->dtype);
+  const size_t need = generic_bwd_workspace(g, desc->dtype, cap);
   if (!ws_ok(workspace, workspace_bytes, need)) return D2C_ERR_WORKSPACE;
   const int nb = bwd_slice_clips(g, cap);
   if (desc->dtype == D2C_F32) {
@@ -311,6 +390,63 @@ int d2c_deform_conv3d_corners(const d2c_conv_desc* desc, const void* offset, int
   return D2C_OK;
 }
 
+// ---- deform_conv1d --------------------------------------------------------------------------------
+
+static int make_geom_1d(const d2c_conv_desc* desc, Geom* g) {
+  int rc = make_geom(desc, g, false);
+  if (rc) return rc;
+  if (g->D != 1 || g->H != 1 || g->kd != 1 || g->kh != 1 || g->sd != 1 || g->sh != 1 || g->pd != 0 || g->ph != 0)
+    return D2C_ERR_SHAPE;
+  return D2C_OK;
+}
+
+int d2c_deform_conv1d_fwd(const d2c_conv_desc* desc, const void* x, const void* offset, const void* mask,
+                          const void* w, const void* bias, void* y, d2c_stream_t stream) {
+  if (!desc || !x || !offset || !w || !y) return D2C_ERR_NULL;
+  Geom g;
+  int rc = make_geom_1d(desc, &g);
+  if (rc) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  D2C_TAKE_STATUS();
+  if (desc->dtype == D2C_F32) {
+    Offset1dCoords<float> oc{(const float*)offset};
+    return launch_fwd_generic<float>(g, oc, (const float*)x, (const float*)mask, (const float*)w, (const float*)bias,
+                                     (float*)y, st);
+  } else if (desc->dtype == D2C_F64) {
+    Offset1dCoords<double> oc{(const double*)offset};
+    return launch_fwd_generic<double>(g, oc, (const double*)x, (const double*)mask, (const double*)w,
+                                      (const double*)bias, (double*)y, st);
+  }
+  return D2C_ERR_DTYPE;
+}
+
+int d2c_deform_conv1d_bwd(const d2c_conv_desc* desc, const void* grad_y, const void* x, const void* offset,
+                          const void* mask, const void* w, void* grad_x, void* grad_offset, void* grad_mask,
+                          void* grad_w, void* grad_bias, void* workspace, size_t workspace_bytes,
+                          d2c_stream_t stream) {
+  if (!desc || !grad_y || !x || !offset || !w || !grad_x || !grad_offset || !grad_w) return D2C_ERR_NULL;
+  if (mask && !grad_mask) return D2C_ERR_NULL;
+  Geom g;
+  int rc = make_geom_1d(desc, &g);
+  if (rc) return rc;
+  if (desc->dtype != D2C_F32 && desc->dtype != D2C_F64) return D2C_ERR_DTYPE;
+  cudaStream_t st = (cudaStream_t)stream;
+  D2C_TAKE_STATUS();
+  const unsigned long long cap = g_max_intermediate.load();
+  if (!ws_ok(workspace, workspace_bytes, generic_bwd_workspace(g, desc->dtype, cap))) return D2C_ERR_WORKSPACE;
+  const int nb = bwd_slice_clips(g, cap);
+  if (desc->dtype == D2C_F32) {
+    Offset1dCoords<float> oc{(const float*)offset};
+    return launch_bwd_generic<float, Offset1dCoords<float>, false>(
+        g, oc, (const float*)grad_y, (const float*)x, (const float*)mask, (const float*)w, (float*)grad_x,
+        (float*)grad_offset, 0, (float*)grad_mask, (float*)grad_w, (float*)grad_bias, (float*)workspace, nb, st);
+  }
+  Offset1dCoords<double> oc{(const double*)offset};
+  return launch_bwd_generic<double, Offset1dCoords<double>, false>(
+      g, oc, (const double*)grad_y, (const double*)x, (const double*)mask, (const double*)w, (double*)grad_x,
+      (double*)grad_offset, 0, (double*)grad_mask, (double*)grad_w, (double*)grad_bias, (double*)workspace, nb, st);
+}
+
 // ---- dynamic-dilated conv ------------------------------------------------------------------------
 
 int d2c_dyn_dilated_conv3d_fwd(const d2c_conv_desc* desc, int field_mode, const void* x,
@@ -322,6 +458,7 @@ int d2c_dyn_dilated_conv3d_fwd(const d2c_conv_desc* desc, int field_mode, const 
   int rc = make_geom(desc, &g, false);
   if (rc) return rc;
   cudaStream_t st = (cudaStream_t)stream;
+  D2C_TAKE_STATUS();
   if (desc->dtype == D2C_F32) {
     FieldCoords<float> fc;
     if ((rc = make_field_coords<float>(g, field_mode, size_map, &fc))) return rc;
@@ -354,20 +491,22 @@ int d2c_dyn_dilated_conv3d_bwd(const d2c_conv_desc* desc, int field_mode, const 
   if (rc) return rc;
   if (desc->dtype != D2C_F32 && desc->dtype != D2C_F64) return D2C_ERR_DTYPE;
   cudaStream_t st = (cudaStream_t)stream;
-  const size_t need = generic_bwd_workspace(g, desc->dtype);
+  D2C_TAKE_STATUS();
+  const unsigned long long cap = g_max_intermediate.load();
+  const int mode = g_math_mode.load();
+  const size_t need = generic_bwd_workspace(g, desc->dtype, cap);
   if (!ws_ok(workspace, workspace_bytes, need)) return D2C_ERR_WORKSPACE;
-  const int nb = bwd_slice_clips(g, g_max_intermediate.load());
+  const int nb = bwd_slice_clips(g, cap);
   const int nch = field_channels(field_mode);
   if (nch < 0) return D2C_ERR_MODE;
   const size_t gs_elems = (size_t)g.B * nch * g.V;
   if (desc->dtype == D2C_F32) {
     FieldCoords<float> fc;
     if ((rc = make_field_coords<float>(g, field_mode, size_map, &fc))) return rc;
-    const unsigned long long cap = g_max_intermediate.load();
-    if (sm100_bwd_supported(g, desc->dtype, g_math_mode.load(), cap)) {
-      if (!ws_ok(workspace, workspace_bytes, sm100_bwd_workspace(g, desc->dtype, g_math_mode.load(), cap)))
+    if (sm100_bwd_supported(g, desc->dtype, mode, cap)) {
+      if (!ws_ok(workspace, workspace_bytes, sm100_bwd_workspace(g, desc->dtype, mode, cap)))
         return D2C_ERR_WORKSPACE;
-      return sm100_bwd_field(g, g_math_mode.load(), cap, fc, (const float*)grad_y, (const float*)x, (const float*)mask,
+      return sm100_bwd_field(g, mode, cap, fc, (const float*)grad_y, (const float*)x, (const float*)mask,
                              (const float*)w, (float*)grad_x, (float*)grad_size_map, gs_elems,
                              (float*)grad_mask, (float*)grad_w, (float*)grad_bias, workspace, st);
     }
@@ -418,6 +557,7 @@ int d2c_depthwise_conv3d_fwd(const d2c_conv_desc* desc, const void* x, const voi
   // int32 range rule of the reference (csrc/grouped_conv3d.cu:431-440)
   if ((long long)g.B * g.Cin * g.Vin > 0x7fffffffLL || (long long)g.B * g.Cout * g.V > 0x7fffffffLL)
     return D2C_ERR_TOO_LARGE;
+  D2C_TAKE_STATUS();
   return depthwise_fwd(g, desc->dtype, x, w, bias, y, (cudaStream_t)stream);
 }
 
@@ -431,6 +571,7 @@ int d2c_depthwise_conv3d_bwd(const d2c_conv_desc* desc, const void* grad_y, cons
   if ((long long)g.B * g.Cin * g.Vin > 0x7fffffffLL || (long long)g.B * g.Cout * g.V > 0x7fffffffLL)
     return D2C_ERR_TOO_LARGE;
   if (grad_w && !ws_ok(workspace, workspace_bytes, depthwise_bwd_workspace(g))) return D2C_ERR_WORKSPACE;
+  D2C_TAKE_STATUS();
   return depthwise_bwd(g, desc->dtype, grad_y, x, w, grad_x, grad_w, grad_bias, workspace,
                        (cudaStream_t)stream);
 }

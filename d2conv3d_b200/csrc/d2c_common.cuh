@@ -87,6 +87,24 @@ struct OffsetCoords {
   }
 };
 
+// deform_conv1d evaluated on a [B, C, 1, 1, L] view: one offset per (group, tap, position),
+// offset [B, G*K, Lo]; depth and height coordinates are exactly 0 (reference csrc/ops/dconv1d_gpu.cu:44-46).
+template <typename T>
+struct Offset1dCoords {
+  const T* offset;
+  __device__ __forceinline__ void get(const Geom& g, int b, int grp, int tap, int v, int bz, int by,
+                                      int bx, T& z, T& y, T& x) const {
+    z = (T)bz;
+    y = (T)by;
+    x = add_rn((T)bx, __ldg(offset + (((long long)b * g.G + grp) * g.K + tap) * g.V + v));
+  }
+};
+
+template <typename Coords>
+struct CoordsIs1d { static constexpr bool value = false; };
+template <typename T>
+struct CoordsIs1d<Offset1dCoords<T>> { static constexpr bool value = true; };
+
 // Offsets synthesised from a dilation field shared by all offset groups:
 // offset_d = base_d[tap] * (s_d - 1) with the two roundings of the reference's
 // PyTorch expression `base_offset * (size_map - 1)` (utils/grid.py:97), then the
@@ -225,5 +243,8 @@ void count_launch();
 void prof_mark(cudaStream_t st, const char* name);
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// Multiprocessor count of the current device (cached per device).
+int device_sm_count(int* out);
 
 }  // namespace d2c

@@ -215,6 +215,56 @@ coord_grad_generic_kernel(Geom g, Coords coords, int b0, int nb, const T* __rest
   }
 }
 
+// ---- deform_conv1d: offset / modulation gradients (reference csrc/ops/dconv1d_gpu.cu:300-349) -----------
+// The 1-D op has its own convention where linear interpolation is not differentiable: when the sampling
+// position is (within 1e-8 of) an integer, the LEFT neighbour moves one further left (`x0 -= 1`, line 336) while
+// the right neighbour stays x0 + 1, so grad_offset becomes the two-cell difference input[x+1] - input[x-1] and
+// grad_alpha is interpolated between those two cells with parameter x - x0 (= 1 at an integer, i.e. the value
+// of the RIGHT cell).  Followed literally, with the reference's lerp (line 13-15).
+// One thread per (clip, offset group, tap, output position); x is [B, Cin, L], dcol [nb, Cin*K, Lo].
+template <typename T>
+__device__ __forceinline__ T lerp_1d(T v0, T v1, T t) { return fma_rn(t, v1, fma_rn(-t, v0, v0)); }
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+coord_grad_1d_kernel(Geom g, Offset1dCoords<T> coords, int b0, int nb, const T* __restrict__ dcol,
+                     const T* __restrict__ x, const T* __restrict__ mask, T* __restrict__ grad_offset,
+                     T* __restrict__ grad_mask) {
+  const long long total = (long long)nb * g.G * g.K * g.V;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int v = (int)(idx % g.V);
+    const int tap = (int)((idx / g.V) % g.K);
+    const int grp = (int)((idx / ((long long)g.V * g.K)) % g.G);
+    const int bl = (int)(idx / ((long long)g.V * g.K * g.G));
+    const int b = b0 + bl;
+    int bz, by, bx;
+    voxel_tap_base(g, v, tap, bz, by, bx);
+    T z, y, pos;
+    coords.get(g, b, grp, tap, v, bz, by, bx, z, y, pos);
+    int x0 = floor_int(pos);
+    const int x1 = x0 + 1;
+    if (sub_rn(pos, (T)x0) < (T)1e-8) x0 -= 1;
+    const T t = sub_rn(pos, (T)x0);
+    const long long mi = (((long long)b * g.G + grp) * g.K + tap) * g.V + v;
+    const T a = mask ? __ldg(mask + mi) : (T)1;
+    T val = 0, alpha_val = 0;
+    const T* dc = dcol + (((long long)bl * g.Cin + (long long)grp * g.cpg) * g.K + tap) * g.V + v;
+    const T* row = x + ((long long)b * g.Cin + (long long)grp * g.cpg) * g.Vin;
+    for (int c = 0; c < g.cpg; ++c) {
+      const T v0 = (x0 >= 0 && x0 < g.W) ? __ldg(row + x0) : (T)0;
+      const T v1 = (x1 >= 0 && x1 < g.W) ? __ldg(row + x1) : (T)0;
+      const T col = __ldg(dc);
+      alpha_val += col * lerp_1d(v0, v1, t);
+      val += (v1 - v0) * col * a;
+      dc += (long long)g.K * g.V;
+      row += g.Vin;
+    }
+    grad_offset[mi] = val;
+    if (mask && grad_mask) grad_mask[mi] = alpha_val;
+  }
+}
+
 // ---- backward step 3: col2im scatter (reference dconv3d_gpu.cu:562-643) ----------------------
 template <typename T, typename Coords>
 __global__ void __launch_bounds__(256)
@@ -405,9 +455,13 @@ int launch_bwd_generic(const Geom& g, const Coords& coords, const T* gy, const T
     dcol_generic_kernel<T><<<grid, kGemmThreads, 0, st>>>(g, b0, gy, w, dcol);
     D2C_LAUNCH_CHECK();
     prof_mark(st, "bwd_coord_grad_generic");
-    coord_grad_generic_kernel<T, Coords, FieldOut>
-        <<<grid_1d((long long)nb * g.G * g.K * g.V, 256), 256, 0, st>>>(g, coords, b0, nb, dcol, x, mask,
-                                                                       grad_coord, grad_mask);
+    if constexpr (CoordsIs1d<Coords>::value)
+      coord_grad_1d_kernel<T><<<grid_1d((long long)nb * g.G * g.K * g.V, 256), 256, 0, st>>>(
+          g, coords, b0, nb, dcol, x, mask, grad_coord, grad_mask);
+    else
+      coord_grad_generic_kernel<T, Coords, FieldOut>
+          <<<grid_1d((long long)nb * g.G * g.K * g.V, 256), 256, 0, st>>>(g, coords, b0, nb, dcol, x, mask,
+                                                                         grad_coord, grad_mask);
     D2C_LAUNCH_CHECK();
     prof_mark(st, "bwd_col2im_generic");
     col2im_generic_kernel<T, Coords>

@@ -33,9 +33,8 @@ int sm100_bwd_field(const Geom& g, int math_mode, unsigned long long cap, const 
                     size_t grad_size_elems, float* grad_mask, float* grad_w, float* grad_bias, void* ws,
                     cudaStream_t st);
 
-// 0 = healthy; 1 = some kernel's bounded wait gave up (sticky); -1 = could not be read.
-int sm100_device_status();
-int sm100_bwd_device_status();
-int sm100_dw_device_status();
+// Test-only kernel: one warp waits `budget_cycles` on an mbarrier that nobody arrives on, gives up and reports
+// through the status word like every product kernel does.
+int sm100_selftest_wait_expiry(long long budget_cycles, cudaStream_t st);
 
 }  // namespace d2c

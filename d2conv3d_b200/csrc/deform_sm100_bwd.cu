@@ -35,8 +35,6 @@ constexpr int kDcolMmaWarp = 8, kDcolLoadWarp = 9;
 constexpr int kDcolThreads = 320;
 constexpr int kSmemLimit = 227 * 1024;
 
-__device__ int g_sm100_bwd_status = 0;
-
 // ---- staging ------------------------------------------------------------------------------------
 
 // grad_out [B][Cout][V] fp32 -> per (tile, 64-wide co block) images of 128 rows (voxels) x 128 B (64 co,
@@ -313,7 +311,7 @@ dcol_sm100_kernel(const DcolParams p) {
   }
   ptx::tc_fence_before();
   __syncthreads();
-  if (threadIdx.x == 0 && *abort_flag) atomicExch(&g_sm100_bwd_status, 1);
+  if (threadIdx.x == 0 && *abort_flag) ptx::report_device_timeout();
   if (warp == 0) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
@@ -566,13 +564,9 @@ int run_bwd(const Geom& g, bool x3, const Coords& coords, unsigned long long cap
   float* axes_dev = reinterpret_cast<float*>(wsp); wsp += pl.axes_bytes;
   void* dw_ws = wsp;
 
-  static int sm_count = 0;
-  if (sm_count == 0) {
-    int dev = 0;
-    D2C_CUDA_TRY(cudaGetDevice(&dev));
-    D2C_CUDA_TRY(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
-  }
-  int rc;
+  int sm_count = 0, rc;
+  if ((rc = device_sm_count(&sm_count))) return rc;
+  ptx::bind_status_sink();
   ClStrides cs;
   cs.dz = g.H * g.W * g.Cin; cs.dy = g.W * g.Cin; cs.dx = g.Cin;
 
@@ -707,12 +701,6 @@ int sm100_bwd_field(const Geom& g, int math_mode, unsigned long long cap, const 
                     cudaStream_t st) {
   return run_bwd<FieldCoords<float>, true>(g, bwd_use_x3(g, math_mode, cap), fc, cap, gy, x, mask, w, grad_x, grad_size_map, grad_size_elems,
                                            grad_mask, grad_w, grad_bias, ws, st);
-}
-
-int sm100_bwd_device_status() {
-  int v = 0;
-  if (cudaMemcpyFromSymbol(&v, g_sm100_bwd_status, sizeof(int)) != cudaSuccess) return -1;
-  return v;
 }
 
 }  // namespace d2c

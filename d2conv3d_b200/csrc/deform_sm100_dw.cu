@@ -38,8 +38,6 @@ constexpr int kRowStride = kGatherWarps * 4;          // 8 threads per row -> ro
 constexpr int kRowsPerThread = kBM / kRowStride;
 constexpr int kSmemLimit = 227 * 1024;
 
-__device__ int g_sm100_dw_status = 0;
-
 struct DwParams {
   Geom g;
   const void* x_cl;          // channels-last staging of x: fp16 (bf16 mode) or fp32 (bf16x3 mode)
@@ -334,7 +332,7 @@ dw_sm100_kernel(const DwParams p) {
   }
   ptx::tc_fence_before();
   __syncthreads();
-  if (threadIdx.x == 0 && *abort_flag) atomicExch(&g_sm100_dw_status, 1);
+  if (threadIdx.x == 0 && *abort_flag) ptx::report_device_timeout();
   if (warp == 0) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
@@ -409,12 +407,12 @@ size_t sm100_dw_workspace(const Geom& g, bool x3) {
 
 int sm100_dw(const Geom& g, bool x3, const float* gy, const void* x_cl, const void* recs, float* grad_w, void* ws,
              cudaStream_t st) {
-  static int sm_count = 0;
-  if (sm_count == 0) {
-    int dev = 0;
-    D2C_CUDA_TRY(cudaGetDevice(&dev));
-    D2C_CUDA_TRY(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
+  int sm_count = 0;
+  {
+    const int rc = device_sm_count(&sm_count);
+    if (rc) return rc;
   }
+  ptx::bind_status_sink();
   DwPlan dp;
   if (!make_dw_plan(g, sm_count, x3, &dp)) return D2C_ERR_MODE;
   uint8_t* gyk = reinterpret_cast<uint8_t*>(ws);
@@ -444,12 +442,6 @@ int sm100_dw(const Geom& g, bool x3, const float* gy, const void* x_cl, const vo
       g.Cout, g.Cin, g.K, dp.pairg ? kBK : g.cpg, dp.nh, dp.S, dws, grad_w);
   D2C_LAUNCH_CHECK();
   return D2C_OK;
-}
-
-int sm100_dw_device_status() {
-  int v = 0;
-  if (cudaMemcpyFromSymbol(&v, g_sm100_dw_status, sizeof(int)) != cudaSuccess) return -1;
-  return v;
 }
 
 }  // namespace d2c

@@ -56,8 +56,6 @@ constexpr int kRowsPerThread = kBM / kRowStride;
 constexpr int kSmemLimit = 227 * 1024;
 constexpr int kMinUnitsPerCta = 16;
 
-__device__ int g_sm100_status = 0;   // sticky: set when a bounded wait gave up
-
 struct FwdParams {
   Geom g;
   const void* x_cl;            // [B][Vin][Cin] channels-last staging of x: fp16 (bf16 mode) or fp32 (bf16x3 mode)
@@ -339,7 +337,7 @@ fwd_sm100_kernel(const FwdParams p) {
   // ---- teardown ----
   ptx::tc_fence_before();
   __syncthreads();
-  if (threadIdx.x == 0 && *abort_flag) atomicExch(&g_sm100_status, 1);
+  if (threadIdx.x == 0 && *abort_flag) ptx::report_device_timeout();
   if (warp == 0) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
@@ -444,17 +442,6 @@ bool make_plan(const Geom& g, bool x3, Plan* pl) {
   return true;
 }
 
-int sm_count_cached(int* out) {
-  static int sm_count = 0;
-  if (sm_count == 0) {
-    int dev = 0;
-    D2C_CUDA_TRY(cudaGetDevice(&dev));
-    D2C_CUDA_TRY(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
-  }
-  *out = sm_count;
-  return D2C_OK;
-}
-
 // Which variant serves this shape in this math mode: bf16 mode takes the single-pass kernel where it applies
 // and otherwise the (more exact) split kernel, e.g. for 32 channels per offset group; auto / bf16x3 take the
 // split kernel only.  Returns false when the tensor-core tier does not apply.
@@ -476,7 +463,8 @@ int run_fwd(const Geom& g, int math_mode, const Coords& coords, const float* x, 
   uint8_t* w_sw = wsp; wsp += pl.w_sw_bytes;
   uint4* recs = reinterpret_cast<uint4*>(wsp);
   int sm_count = 0, rc;
-  if ((rc = sm_count_cached(&sm_count))) return rc;
+  if ((rc = device_sm_count(&sm_count))) return rc;
+  ptx::bind_status_sink();
 
   const long long n_units = (long long)pl.n_tiles * pl.S;
   long long grid = n_units / kMinUnitsPerCta;
@@ -554,7 +542,7 @@ int run_fwd(const Geom& g, int math_mode, const Coords& coords, const float* x, 
     pp.f = p;
     pp.n_tile_pairs = n_tile_pairs; pp.n_pair_units = n_pair_units;
     pp.b_stages = pair_b_stages; pp.b_half_bytes = pl.b_stage_bytes / 2;
-    prof_mark(st, "fwd_sm100_fused");
+    prof_mark(st, "fwd_sm100_pair");
     pair::fwd_sm100_pair_kernel<<<(unsigned)(2 * pair_clusters), kThreads, pair_smem, st>>>(pp);
     D2C_LAUNCH_CHECK();
     prof_mark(st, nullptr);
@@ -604,10 +592,32 @@ int sm100_fwd_field(const Geom& g, int math_mode, const FieldCoords<float>& fc, 
   return run_fwd(g, math_mode, fc, x, mask, w, bias, y, ws, st);
 }
 
-int sm100_device_status() {
-  int v = 0;
-  if (cudaMemcpyFromSymbol(&v, g_sm100_status, sizeof(int)) != cudaSuccess) return -1;
-  return v;
+// ---- wait-expiry self-test ------------------------------------------------------------------------
+// One warp initialises an mbarrier that nobody will ever arrive on, waits on it with the product kernels' own
+// bounded wait (a short budget instead of the default) and, when the wait gives up, reports exactly as they
+// do.  No tensor memory, no bulk copy: nothing is left in flight.  The kernel returns normally.
+namespace {
+__global__ void __launch_bounds__(32) selftest_wait_expiry_kernel(long long budget_cycles) {
+  __shared__ __align__(8) unsigned long long bar;
+  __shared__ int abort_flag;
+  const uint32_t bar_addr = ptx::smem_u32(&bar);
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(bar_addr, 1);
+    abort_flag = 0;
+    ptx::fence_mbar_init();
+  }
+  __syncwarp();
+  const bool done = ptx::mbar_wait(bar_addr, 0, &abort_flag, 100, budget_cycles);
+  __syncwarp();
+  if (threadIdx.x == 0 && (!done || abort_flag)) ptx::report_device_timeout();
+}
+}  // namespace
+
+int sm100_selftest_wait_expiry(long long budget_cycles, cudaStream_t st) {
+  ptx::bind_status_sink();
+  selftest_wait_expiry_kernel<<<1, 32, 0, st>>>(budget_cycles);
+  D2C_LAUNCH_CHECK();
+  return D2C_OK;
 }
 
 }  // namespace d2c

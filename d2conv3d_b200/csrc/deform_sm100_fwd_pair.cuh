@@ -282,7 +282,7 @@ fwd_sm100_pair_kernel(const PairParams pp) {
   ptx::tc_fence_before();
   __syncthreads();
   ptx::cluster_sync();
-  if (threadIdx.x == 0 && *abort_flag) atomicExch(&g_sm100_status, 1);
+  if (threadIdx.x == 0 && *abort_flag) ptx::report_device_timeout();
   if (warp == 0) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc_pair(tmem_base, (uint32_t)p.tmem_cols);

@@ -261,6 +261,7 @@ static bool quad_wgrad(const Geom& g, const void* gy, const void* x, void* parti
 template <typename T>
 static int dw_fwd_t(const Geom& g, const void* x, const void* w, const void* bias, void* y, cudaStream_t st) {
   const long long total = (long long)g.B * g.Cout * g.V;
+  ptx::bind_status_sink();
   prof_mark(st, "depthwise_fwd");
   DwTilePlan plan;
   if (dw_tile_plan(g, sizeof(typename AccOf<T>::type), &plan)) {
@@ -292,6 +293,7 @@ static int dw_bwd_t(const Geom& g, const void* gy, const void* x, const void* w,
   const bool k333 = g.kd == 3 && g.kh == 3 && g.kw == 3;
   DwTilePlan plan;
   const bool tiled = dw_tile_plan(g, sizeof(A), &plan);
+  ptx::bind_status_sink();
   if (gx) {
     const long long total = (long long)g.B * g.Cin * g.Vin;
     prof_mark(st, "depthwise_bwd_input");
@@ -350,12 +352,6 @@ static int dw_bwd_t(const Geom& g, const void* gy, const void* x, const void* w,
   }
   prof_mark(st, nullptr);
   return D2C_OK;
-}
-
-int depthwise_device_status() {
-  int v = 0;
-  if (cudaMemcpyFromSymbol(&v, g_dw_status, sizeof(int)) != cudaSuccess) return -1;
-  return v;
 }
 
 size_t depthwise_bwd_workspace(const Geom& g) { return align_up(sizeof(double) * (size_t)g.Cout * g.K, 256); }

@@ -25,7 +25,6 @@
 namespace d2c {
 namespace {
 
-__device__ int g_dw_status = 0;   // sticky: 1 after a bulk copy did not complete within the wait budget
 
 struct DwBulkPlan {
   int nvol;               // volumes per chunk (forward / input gradient); 1 for the weight gradient
@@ -211,7 +210,7 @@ dw_bulk_conv_kernel(Geom g, int nyp, int nvol, long long nchunks, uint32_t plane
     }
     __syncthreads();   // every thread is done reading stage s before it is refilled
   }
-  if (threadIdx.x == 0 && *abort_flag) atomicExch(&g_dw_status, 1);
+  if (threadIdx.x == 0 && *abort_flag) ptx::report_device_timeout();
 }
 
 // One z step of the weight-gradient march over staged volumes: x plane p meets grad_out planes p+1 (kz=0),
@@ -342,7 +341,7 @@ dw_bulk_wgrad_kernel(Geom g, int nyp, uint32_t plane_bytes, uint32_t gap_bytes, 
     else
       __syncthreads();   // every thread is done reading stage s before it is refilled
   }
-  if (threadIdx.x == 0 && (!ok || *abort_flag)) atomicExch(&g_dw_status, 1);
+  if (threadIdx.x == 0 && (!ok || *abort_flag)) ptx::report_device_timeout();
 }
 
 template <typename T, typename A>

@@ -293,7 +293,7 @@ dw_quad_conv_kernel(Geom g, int nyp, int nxp, int nvol, long long nchunks, uint3
     }
   }
   __syncthreads();
-  if (threadIdx.x == 0 && *abort_flag) atomicExch(&g_dw_status, 1);
+  if (threadIdx.x == 0 && *abort_flag) ptx::report_device_timeout();
 }
 
 // Weight gradient.  grad_out pairs of the patch's R rows at plane q of the contiguous staged volume; rows and
@@ -450,7 +450,7 @@ dw_quad_wgrad_kernel(Geom g, int nyp, int nxp, uint32_t plane_bytes, uint32_t ga
     if (c_open >= 0) dwq_flush_warp(acc, partial, (int)c_open);      // left the loop early: keep what was summed
   }
   __syncthreads();
-  if (threadIdx.x == 0 && *abort_flag) atomicExch(&g_dw_status, 1);
+  if (threadIdx.x == 0 && *abort_flag) ptx::report_device_timeout();
 }
 
 inline int dw_quad_conv(const Geom& g, const DwQuadPlan& p, const float* in, const float* w, const float* bias,

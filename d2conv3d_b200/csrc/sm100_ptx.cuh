@@ -10,8 +10,43 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 namespace d2c {
+
+// Device-visible address of the calling device's status word (d2c_api.cu): one int per device in page-locked
+// host memory that the device can write, so that the host learns of a bounded wait that gave up by reading
+// its own memory -- no synchronisation, no copy.
+int status_word_device_ptr(int** dev_ptr);
+
 namespace ptx {
+
+// Where the kernels of THIS translation unit report (every .cu file that includes this header has its own
+// copy; bind_status_sink() points it at the device's status word once per device).
+static __device__ int* g_status_sink = nullptr;
+
+// Called by one thread of a CTA whose bounded wait gave up, after the CTA has drained its copies.
+__device__ __forceinline__ void report_device_timeout() {
+  int* p = g_status_sink;
+  if (p) {
+    *reinterpret_cast<volatile int*>(p) = 1;
+    __threadfence_system();
+  }
+}
+
+// Host: makes the kernels of this translation unit report to the current device's status word.  The first call
+// per device copies 8 bytes to the device (synchronously); later calls only test a bit.
+static inline int bind_status_sink() {
+  static std::atomic<unsigned long long> bound{0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;   // reporting stays off; not an error
+  if ((bound.load(std::memory_order_acquire) >> dev) & 1ull) return 0;
+  int* p = nullptr;
+  if (status_word_device_ptr(&p) != 0 || !p) return 0;
+  if (cudaMemcpyToSymbol(g_status_sink, &p, sizeof(p)) != cudaSuccess) { (void)cudaGetLastError(); return 0; }
+  bound.fetch_or(1ull << dev, std::memory_order_release);
+  return 0;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -50,8 +85,10 @@ constexpr long long kWaitBudgetCycles = 4000000000LL;
 // another role already aborted.
 // backoff_ns > 0: sleep between polls (for roles whose waits are long and not latency-critical, so that
 // their polling does not take issue slots from the producers).
+// budget: clock cycles this wait may take (the default suits every product kernel; the wait-expiry self-test
+// passes a short one).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          unsigned backoff_ns = 0) {
+                                          unsigned backoff_ns = 0, long long budget = kWaitBudgetCycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
@@ -61,7 +98,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       if (backoff_ns) __nanosleep(backoff_ns);
     }
     if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitBudgetCycles) {
+    if (clock64() - t0 > budget) {
       *abort_flag = 1;
       return false;
     }

@@ -160,26 +160,74 @@ def dyn_dilated_conv3d(input, size_map, alpha, weight, bias, mode, stride, paddi
                                            tuple(padding), tuple(dilation), int(groups), int(offset_groups))
 
 
-def deform_conv1d(input, offset, alpha, weight, bias, stride, padding, dilation, groups, offset_groups):
-    """dconv_native._ops.deform_conv1d (csrc/ops/dconv1d.h, dconv1d_gpu.cu:24-55): modulated deformable
-    conv1d with one offset per (offset group, tap, output position) and linear interpolation.
+class _DeformConv1dFunction(torch.autograd.Function):
+    """DeformConv1dFunction of the reference (csrc/ops/dconv1d.h:69-156)."""
 
-    Evaluated by the 3-D kernels on a [B, C, 1, 1, L] view: with depth = height = 1 and zero z / y offsets the
-    z and y coordinates are exactly 0, so the only contributing corners are (0, 0, x0) and (0, 0, x0 + 1) with
-    weights (1 - t) and t -- the reference's `lerp(v0, v1, x - x0)` with out-of-range neighbours read as 0
-    (its lines 47-53).  The x offsets become channel 3*(g*K + k) + 2 of a 3-D offset tensor whose other
-    channels are zero; autograd carries grad_offset back through that embedding."""
-    if input.dim() != 3 or offset.dim() != 3 or weight.dim() != 3:
-        raise RuntimeError("deform_conv1d expects input [B, C, L], offset [B, G*K, L_out], weight [Cout, Cin/groups, K]")
+    @staticmethod
+    def forward(ctx, input, offset, alpha, weight, bias, stride, padding, dilation, groups, offset_groups):
+        input, offset, weight = input.contiguous(), offset.contiguous(), weight.contiguous()
+        alpha = None if alpha is None else alpha.contiguous()
+        bias = None if bias is None else bias.contiguous()
+        for t, nd, name in ((input, 3, "input"), (offset, 3, "offset"), (alpha, 3, "alpha"), (weight, 3, "weight"),
+                            (bias, 1, "bias")):
+            if t is not None:
+                _require(t.dim() == nd, f"{name}.ndimension() == {nd}")
+                _require(t.is_cuda, f"{name}.device().is_cuda()")
+                if t.dtype != input.dtype:
+                    raise RuntimeError(f"expected scalar type {input.dtype} but found {t.dtype}")
+        if input.dtype not in (torch.float32, torch.float64):
+            raise RuntimeError(f'"deform_conv1d" not implemented for \'{input.dtype}\'')
+        _check_groups(input, weight, bias, groups)
+        K = weight.shape[2]
+        # the [B, C, 1, 1, L] view of the problem
+        desc = _lib.ConvDesc(_lib.dtype_code(input), input.shape[0], input.shape[1], weight.shape[0], 1, 1,
+                             input.shape[2], 1, 1, K, 1, 1, stride, 0, 0, padding, 1, 1, dilation, groups,
+                             offset_groups)
+        Lo = _lib.output_dims(desc, "deform_conv1d")[2]
+        if offset.shape[0] != input.shape[0] or offset.shape[1] != offset_groups * K or offset.shape[2] != Lo:
+            raise RuntimeError(f"offset output dims do not match computed dims. Got: {tuple(offset.shape)} but expected: "
+                               f"{(input.shape[0], offset_groups * K, Lo)}")
+        if alpha is not None and tuple(alpha.shape) != tuple(offset.shape):
+            raise RuntimeError(f"mask output dims do not match computed dims. Got: {tuple(alpha.shape)} but expected: "
+                               f"{tuple(offset.shape)}")
+        L = _lib.lib()
+        with torch.cuda.device(input.device):
+            y = torch.empty((input.shape[0], weight.shape[0], Lo), dtype=input.dtype, device=input.device)
+            _lib.check(L.d2c_deform_conv1d_fwd(ctypes.byref(desc), _lib.ptr(input), _lib.ptr(offset), _lib.ptr(alpha),
+                                               _lib.ptr(weight), _lib.ptr(bias), _lib.ptr(y), _lib.stream_of(input)),
+                       "deform_conv1d forward")
+        ctx.save_for_backward(input, offset, alpha, weight, bias)
+        ctx.desc = desc
+        return y
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, grad_out):
+        input, offset, alpha, weight, bias = ctx.saved_tensors
+        desc = ctx.desc
+        grad_out = grad_out.contiguous()
+        L = _lib.lib()
+        with torch.cuda.device(input.device):
+            gx, goff, gw = torch.empty_like(input), torch.empty_like(offset), torch.empty_like(weight)
+            galpha = None if alpha is None else torch.empty_like(alpha)
+            gbias = None if bias is None else torch.empty_like(bias)
+            ws, ws_bytes = _lib.workspace(_lib.OP_DEFORM_BWD, desc, input.device)
+            _lib.check(L.d2c_deform_conv1d_bwd(
+                ctypes.byref(desc), _lib.ptr(grad_out), _lib.ptr(input), _lib.ptr(offset), _lib.ptr(alpha),
+                _lib.ptr(weight), _lib.ptr(gx), _lib.ptr(goff), _lib.ptr(galpha), _lib.ptr(gw), _lib.ptr(gbias),
+                _lib.ptr(ws), ws_bytes, _lib.stream_of(input)), "deform_conv1d backward")
+        return (gx, goff, galpha, gw, gbias) + (None,) * 5
+
+
+def deform_conv1d(input, offset, alpha, weight, bias, stride, padding, dilation, groups, offset_groups):
+    """dconv_native._ops.deform_conv1d (csrc/ops/dconv1d.h:158-186, dconv1d_gpu.cu): modulated deformable conv1d
+    with one offset per (offset group, tap, output position) and linear interpolation, out-of-range neighbours
+    read as 0.  Forward, grad_input, grad_weight and grad_bias run on the library's generic kernels over the
+    [B, C, 1, 1, L] view of the problem; grad_offset / grad_alpha come from a kernel of their own that follows the
+    1-D reference's rule at integer sampling positions (`x0 -= 1`, dconv1d_gpu.cu:334-337)."""
     one = lambda v: int(v[0]) if isinstance(v, (tuple, list)) else int(v)
-    stride, padding, dilation = one(stride), one(padding), one(dilation)
-    B, GK, Lo = offset.shape
-    zeros = torch.zeros_like(offset)
-    off3 = torch.stack((zeros, zeros, offset), dim=2).reshape(B, 3 * GK, 1, 1, Lo)
-    alpha3 = None if alpha is None else alpha.reshape(B, GK, 1, 1, Lo)
-    y = deform_conv3d(input[:, :, None, None, :], off3, alpha3, weight[:, :, None, None, :], bias,
-                      1, 1, int(stride), 0, 0, int(padding), 1, 1, int(dilation), int(groups), int(offset_groups))
-    return y[:, :, 0, 0, :]
+    return _DeformConv1dFunction.apply(input, offset, alpha, weight, bias, one(stride), one(padding), one(dilation),
+                                       int(groups), int(offset_groups))
 
 
 def corners(input_shape, weight_shape, offset, stride, padding, dilation, offset_groups):

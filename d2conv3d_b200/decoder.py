@@ -41,8 +41,8 @@ class GlobalConv3d(nn.Module):
 
 class ConvActNorm(nn.Sequential):
     """conv -> activation -> norm, in this order (refinement.py:38-43); GroupNorm with one group.  Same three
-    sub-modules (and state-dict keys) as the reference's nn.Sequential.  On a CUDA fp32 tensor the ReLU +
-    GroupNorm tail (forward and backward) runs as the library's fused streaming kernels: PyTorch's GroupNorm reduces
+    sub-modules (and state-dict keys) as the reference's nn.Sequential.  The ReLU + GroupNorm tail (forward and
+    backward) runs as the library's fused streaming kernels (fp32 CUDA tensors only): PyTorch's GroupNorm reduces
     each (clip, group) row in ONE thread block, which for one group of 50 M elements takes 19 ms per layer and
     was 85 % of the decoder's inference time."""
 
@@ -50,12 +50,11 @@ class ConvActNorm(nn.Sequential):
         super().__init__(nn.Conv3d(cin, cout, 3, padding=1), nn.ReLU(), nn.GroupNorm(1, cout))
 
     def forward(self, x):
+        from . import _lib
         y = self[0](x)
         norm = self[2]
-        if y.is_cuda and y.dtype == torch.float32 and isinstance(norm, nn.GroupNorm):
-            from . import _lib
-            return _lib.act_group_norm(y, norm.weight, norm.bias, norm.num_groups, norm.eps, relu=True)
-        return norm(self[1](y))
+        # no eager stand-in: act_group_norm raises for anything but an fp32 CUDA tensor
+        return _lib.act_group_norm(y, norm.weight, norm.bias, norm.num_groups, norm.eps, relu=True)
 
 
 def _unit(cin, cout):

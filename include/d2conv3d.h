@@ -121,10 +121,28 @@ const char* d2c_last_cuda_error(void);
 int d2c_set_math_mode(int mode);
 int d2c_get_math_mode(void);
 
-/* Synchronises with the device and reports whether any tensor-core kernel of this
- * process gave up a bounded device-side wait (D2C_ERR_DEVICE_TIMEOUT) since the
- * library was loaded.  Results of calls made after such an event are undefined. */
+/* Device-side failure reporting.  Every wait inside the kernels is bounded; a kernel
+ * whose wait gave up returns early (its outputs are then incomplete) and raises the
+ * current device's status word, which lives in page-locked host memory.
+ *   - Every compute entry point first looks at that word (a host memory read, no
+ *     synchronisation): if it is raised, the call launches nothing, returns
+ *     D2C_ERR_DEVICE_TIMEOUT once and clears the word.  So a failure surfaces at the
+ *     next library call on that device at the latest.
+ *   - d2c_device_status() synchronises with the device first and then reports and
+ *     clears in the same way: call it after a step whose results must be trusted.
+ *   - d2c_device_status_peek() reports without synchronising or clearing;
+ *     d2c_device_status_clear() clears without reporting.
+ * The reference has no counterpart: its kernels have no waits (launch failures are
+ * only printed, csrc/ops/dconv3d_gpu.cu:259-262). */
 int d2c_device_status(void);
+int d2c_device_status_peek(void);
+void d2c_device_status_clear(void);
+
+/* Self-test of the reporting path: launches a one-warp kernel that waits `budget_us`
+ * microseconds (1 .. 100000) on a barrier nobody arrives on, gives up and raises the
+ * status word; the kernel returns normally and the context stays usable.  Expect
+ * d2c_device_status() == D2C_ERR_DEVICE_TIMEOUT afterwards, once. */
+int d2c_selftest_wait_expiry(uint32_t budget_us, d2c_stream_t stream);
 
 /* Number of kernels this library has launched in this process so far. */
 uint64_t d2c_launch_count(void);
@@ -175,6 +193,24 @@ int d2c_deform_conv3d_bwd(const d2c_conv_desc* desc, const void* grad_y, const v
  * floor of :63-65.  corners is int32 [B, G*K, 3, Do*Ho*Wo] (z0, y0, x0). */
 int d2c_deform_conv3d_corners(const d2c_conv_desc* desc, const void* offset, int32_t* corners,
                               d2c_stream_t stream);
+
+/* ---- modulated deformable conv1d ------------------------------------------ */
+
+/* deform_conv1d_forward_cuda / deform_conv1d_backward_cuda, csrc/ops/dconv1d_gpu.cu:101-198, :351-538
+ * (dconv_native._ops.deform_conv1d).  The descriptor describes the [B, C, 1, 1, L] view of the problem:
+ * in_d = in_h = 1, kd = kh = 1, stride_d = stride_h = 1, pad_d = pad_h = 0 (anything else: D2C_ERR_SHAPE);
+ * in_w = L, kw = K, stride_w / pad_w / dil_w the 1-D geometry.
+ *   x [B, Cin, L]   offset [B, G*K, Lo]   mask [B, G*K, Lo] nullable   w [Cout, Cin/groups, K]   bias nullable
+ * Linear interpolation with out-of-range neighbours read as zero.  The backward follows the 1-D reference's own
+ * rule at sampling positions within 1e-8 of an integer (:334-337): there the left neighbour is taken one cell
+ * further left, so grad_offset is mask * (x[p+1] - x[p-1]) * dcol and grad_mask uses the right cell's value.
+ * fp32 / fp64, CUDA-core kernels.  Workspace of the backward: d2c_workspace_bytes(D2C_OP_DEFORM_BWD, desc). */
+int d2c_deform_conv1d_fwd(const d2c_conv_desc* desc, const void* x, const void* offset, const void* mask,
+                          const void* w, const void* bias, void* y, d2c_stream_t stream);
+int d2c_deform_conv1d_bwd(const d2c_conv_desc* desc, const void* grad_y, const void* x, const void* offset,
+                          const void* mask, const void* w, void* grad_x, void* grad_offset, void* grad_mask,
+                          void* grad_w, void* grad_bias, void* workspace, size_t workspace_bytes,
+                          d2c_stream_t stream);
 
 /* ---- dynamic-dilated conv3d (dilation field instead of offsets) ---------- */
 

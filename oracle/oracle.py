@@ -254,3 +254,82 @@ def deform_conv1d_fwd(x, offset, alpha, weight, bias=None, stride=1, padding=0, 
     if bias is not None:
         y += np.asarray(bias)[None, :, None]
     return y
+
+
+def _cols_1d(x, offset, alpha, K, stride, padding, dilation, offset_groups):
+    """im2col of the 1-D op (dconv1d_gpu.cu:36-54): cols[b, c, i, ox] = a * lerp(v0, v1, x - x0)."""
+    B, C, L = x.shape
+    Lo = offset.shape[2]
+    cpg = C // offset_groups
+    cols = np.zeros((B, C, K, Lo), dtype=x.dtype)
+    ox = np.arange(Lo)
+    for g in range(offset_groups):
+        for i in range(K):
+            pos = (ox * stride - padding + i * dilation).astype(x.dtype)[None, :] + offset[:, g * K + i, :]   # [B, Lo]
+            x0 = np.floor(pos).astype(np.int64)
+            x1 = x0 + 1
+            t = pos - x0.astype(x.dtype)
+            a = alpha[:, g * K + i, :]
+            for c in range(g * cpg, (g + 1) * cpg):
+                xc = x[:, c, :]                                           # [B, L]
+                v0 = np.where((x0 >= 0) & (x0 < L), np.take_along_axis(xc, np.clip(x0, 0, L - 1), axis=1), 0)
+                v1 = np.where((x1 >= 0) & (x1 < L), np.take_along_axis(xc, np.clip(x1, 0, L - 1), axis=1), 0)
+                cols[:, c, i, :] = a * (v0 + t * (v1 - v0))
+    return cols
+
+
+def deform_conv1d_bwd(gy, x, offset, alpha, weight, has_bias=True, stride=1, padding=0, dilation=1, groups=1,
+                      offset_groups=1):
+    """All five gradients of the modulated deformable conv1d, restating
+    ops/dconv-native/csrc/ops/dconv1d_gpu.cu: gradient columns (:459-480), grad_input scatter with the
+    `x1 - x < 1` test (:200-240), grad_offset / grad_alpha with the integer-position rule `x0 -= 1` when
+    x - x0 < 1e-8 (:300-349), grad_weight from the re-computed columns (:499-536), grad_bias (:537).
+    numpy, small cases only.  Returns (grad_x, grad_offset, grad_alpha, grad_weight, grad_bias or None)."""
+    gy = np.asarray(gy); x = np.asarray(x); offset = np.asarray(offset); weight = np.asarray(weight)
+    B, C, L = x.shape
+    Cout, Cg, K = weight.shape
+    Lo = gy.shape[2]
+    had_alpha = alpha is not None
+    alpha = np.ones_like(offset) if alpha is None else np.asarray(alpha)
+    cog = Cout // groups
+    cpg = C // offset_groups
+    dcol = np.zeros((B, C, K, Lo), dtype=x.dtype)
+    for gw in range(groups):
+        wg = weight[gw * cog:(gw + 1) * cog]                                        # [cog, Cg, K]
+        dcol[:, gw * Cg:(gw + 1) * Cg] = np.einsum("bol,ock->bckl", gy[:, gw * cog:(gw + 1) * cog], wg)
+    gx = np.zeros_like(x)
+    goff = np.zeros_like(offset)
+    galpha = np.zeros_like(offset)
+    ox = np.arange(Lo)
+    bi = np.arange(B)[:, None]
+    for g in range(offset_groups):
+        for i in range(K):
+            pos = (ox * stride - padding + i * dilation).astype(x.dtype)[None, :] + offset[:, g * K + i, :]
+            a = alpha[:, g * K + i, :]
+            x0 = np.floor(pos).astype(np.int64)
+            x1 = x0 + 1
+            # scatter (:221-236)
+            w0 = 1 - (pos - x0)
+            w1 = pos - x0
+            ok0 = (x0 >= 0) & (x0 < L)
+            ok1 = (x1 >= 0) & (x1 < L) & ((x1 - pos) < 1)
+            # coordinate gradient (:329-346)
+            x0g = np.where((pos - x0) < 1e-8, x0 - 1, x0)
+            tg = pos - x0g
+            for c in range(g * cpg, (g + 1) * cpg):
+                col = dcol[:, c, i, :]
+                grad = a * col
+                np.add.at(gx[:, c, :], (np.broadcast_to(bi, x0.shape)[ok0], x0[ok0]), (w0 * grad)[ok0])
+                np.add.at(gx[:, c, :], (np.broadcast_to(bi, x1.shape)[ok1], x1[ok1]), (w1 * grad)[ok1])
+                xc = x[:, c, :]
+                v0 = np.where((x0g >= 0) & (x0g < L), np.take_along_axis(xc, np.clip(x0g, 0, L - 1), axis=1), 0)
+                v1 = np.where((x1 >= 0) & (x1 < L), np.take_along_axis(xc, np.clip(x1, 0, L - 1), axis=1), 0)
+                galpha[:, g * K + i, :] += col * (tg * v1 + (-tg * v0 + v0))
+                goff[:, g * K + i, :] += (v1 - v0) * col * a
+    cols = _cols_1d(x, offset, alpha, K, stride, padding, dilation, offset_groups)
+    gwt = np.zeros_like(weight)
+    for gw in range(groups):
+        gwt[gw * cog:(gw + 1) * cog] = np.einsum("bol,bckl->ock", gy[:, gw * cog:(gw + 1) * cog],
+                                                 cols[:, gw * Cg:(gw + 1) * Cg])
+    gb = gy.sum(axis=(0, 2)) if has_bias else None
+    return gx, goff, (galpha if had_alpha else None), gwt, gb

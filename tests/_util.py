@@ -68,3 +68,27 @@ def make_problem(seed, B, Cin, Cout, dims, k=3, stride=1, padding=0, dilation=1,
     cast = lambda a: None if a is None else np.ascontiguousarray(a, dtype=dtype)
     return dict(x=cast(x), geo=cast(geo), mask=cast(m), weight=cast(w), bias=cast(b), gy=cast(gy),
                 stride=s, padding=p, dilation=d, groups=groups, offset_groups=G, out_dims=od)
+
+
+_deform1d = None
+
+
+def deform1d_cases():
+    global _deform1d
+    if _deform1d is None:
+        _deform1d = np.load(os.path.join(GOLDEN, "deform1d_fwd_cases.npz"))
+    return _deform1d
+
+
+def deform1d_case_names():
+    return [str(n) for n in deform1d_cases()["names"]]
+
+
+def load_deform1d_case(name, dtype=np.float64):
+    d = deform1d_cases()
+    g = [int(v) for v in d[f"{name}/geom"]]
+    bias = d[f"{name}/bias"].astype(dtype) if f"{name}/bias" in d else None
+    return dict(x=d[f"{name}/x"].astype(dtype), offset=d[f"{name}/offset"].astype(dtype),
+                mask=d[f"{name}/mask"].astype(dtype), weight=d[f"{name}/weight"].astype(dtype), bias=bias,
+                expected=d[f"{name}/expected"], stride=g[0], padding=g[1], dilation=g[2], groups=g[3],
+                offset_groups=g[4])

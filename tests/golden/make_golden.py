@@ -2,7 +2,9 @@
 
 Run once, in a container where the reference checkout is mounted:
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference [size_map] [deform3d] [deform1d]
+
+(no set names: all three sets).
 
 What it executes from the reference (imported as modules, nothing is copied):
   * ops/dconv-native/test/test_deform_conv.py : `expected_fn` -- the reference's
@@ -17,7 +19,10 @@ The test module imports the compiled `dconv_native` extension at import time and
 `utils/grid.py` imports `utils.util` (which needs imageio); both are satisfied by
 stub modules because only the pure-Python functions are wanted.
 
-Outputs: deform_fwd_cases.npz, size_map_cases.npz (a few hundred KB in total).
+  * the same `expected_fn` with N = 1 (linear interpolation) for the geometries of DeformConv1dTester
+    (:232-340) plus integer offsets.
+
+Outputs: deform_fwd_cases.npz, size_map_cases.npz, deform1d_fwd_cases.npz (a few hundred KB in total).
 """
 import importlib.util
 import os
@@ -155,6 +160,53 @@ def make_size_map_cases():
     print(f"size-map cases: {len(names)}")
 
 
+# geometries of DeformConv1dTester (ops/dconv-native/test/test_deform_conv.py:232-340) + integer offsets
+CASES_1D = {
+    "default": dict(),
+    "stride3": dict(stride=3),
+    "offset_groups": dict(channels_in=12, channels_out=4, n_offset_groups=2, bias=False),
+    "weight_groups": dict(channels_in=12, channels_out=6, n_weight_groups=3, bias=False),
+    "groups": dict(channels_in=24, channels_out=12, n_weight_groups=6, n_offset_groups=2, bias=False),
+    "forward_mixed": dict(batch_size=3, channels_in=3, channels_out=5, dimensions=34, kernel_size=5, stride=2,
+                          padding=3, dilation=2),
+    "no_bias": dict(bias=False),
+    "integer_offsets": dict(channels_in=4, channels_out=3, dimensions=12, padding=1, _integer_offsets=True),
+}
+
+
+def make_deform1d_cases():
+    ref = load_reference_test_module()
+    out = {}
+    names = []
+    for idx, (name, kw) in enumerate(CASES_1D.items()):
+        kw = dict(kw)
+        torch.manual_seed(9876 + idx)
+        integer = kw.pop("_integer_offsets", False)
+        x, offset, alpha, weight, bias = ref.generate_data(1, device="cpu", dtype=torch.float64, **kw)
+        if integer:
+            offset = torch.randint(-2, 3, offset.shape).to(torch.float64)
+        stride, padding, dilation = kw.get("stride", 1), kw.get("padding", 0), kw.get("dilation", 1)
+        expected = ref.expected_fn(1, x, offset, alpha, weight, bias, stride, padding, dilation)
+        names.append(name)
+        out[f"{name}/x"] = x.numpy()
+        out[f"{name}/offset"] = offset.numpy()
+        out[f"{name}/mask"] = alpha.numpy()
+        out[f"{name}/weight"] = weight.numpy()
+        if bias is not None:
+            out[f"{name}/bias"] = bias.numpy()
+        out[f"{name}/expected"] = expected.numpy()
+        out[f"{name}/geom"] = np.array([stride, padding, dilation, kw.get("n_weight_groups", 1),
+                                        kw.get("n_offset_groups", 1)], dtype=np.int64)
+        print(f"1d {name}: out {tuple(expected.shape)}", flush=True)
+    out["names"] = np.array(names)
+    np.savez_compressed(os.path.join(HERE, "deform1d_fwd_cases.npz"), **out)
+
+
 if __name__ == "__main__":
-    make_size_map_cases()
-    make_deform_cases()
+    sets = sys.argv[2:] or ["size_map", "deform3d", "deform1d"]
+    if "size_map" in sets:
+        make_size_map_cases()
+    if "deform3d" in sets:
+        make_deform_cases()
+    if "deform1d" in sets:
+        make_deform1d_cases()

@@ -1,11 +1,14 @@
-"""GPU tests of deform_conv1d (evaluated by the 3-D kernels on a [B, C, 1, 1, L] view), following
-ops/dconv-native/test/test_deform_conv.py:232-262: identity with conv1d for zero offsets, stride, groups,
-float64 gradcheck; plus the numpy restatement of the reference's 1-D kernel as the oracle."""
+"""GPU tests of deform_conv1d, following ops/dconv-native/test/test_deform_conv.py:232-340: the golden outputs of
+the reference's expected_fn(1, ...), identity with conv1d for zero offsets, stride, groups, float64 gradcheck;
+forward and all five gradients against the numpy restatement of the reference's 1-D kernels -- at fractional
+AND at exactly-integer sampling positions, where the 1-D reference has a rule of its own (dconv1d_gpu.cu:334-337)
+-- and against the reference's own compiled CUDA op when baseline/_ref is present."""
 import numpy as np
 import pytest
 import torch
 
 from oracle import oracle as orc
+from tests import _reference, _util
 
 pytestmark = pytest.mark.gpu
 
@@ -67,3 +70,81 @@ def test_module_and_defaults(dn):
     y = m(x, off, None)
     ref = torch.nn.functional.conv1d(x, m.weight, m.bias, padding=1)
     assert torch.allclose(y, ref, atol=1e-5)
+
+
+@pytest.mark.parametrize("name", _util.deform1d_case_names())
+def test_forward_matches_reference_expected_fn(dn, name):
+    c = _util.load_deform1d_case(name)
+    cu = lambda a: None if a is None else torch.from_numpy(a).cuda()
+    y = dn.deform_conv1d(cu(c["x"]), cu(c["offset"]), cu(c["mask"]), cu(c["weight"]), cu(c["bias"]), c["stride"],
+                         c["padding"], c["dilation"], c["groups"], c["offset_groups"]).cpu().numpy()
+    assert np.allclose(y, c["expected"], rtol=1e-5, atol=1e-8)      # float64, the suite's allclose defaults
+
+
+def _integerise(off, frac):
+    """Every `frac`-th offset becomes an exact integer (the zero-initialised predictor's case)."""
+    off = off.clone()
+    flat = off.view(-1)
+    flat[::frac] = torch.round(flat[::frac])
+    return off
+
+
+GRAD_CASES = [
+    dict(B=2, C=8, Cout=6, L=33, K=3),
+    dict(B=1, C=12, Cout=6, L=40, K=5, stride=2, pad=2, dil=2, groups=3, G=2),
+    dict(B=2, C=64, Cout=64, L=150, K=3, pad=1),
+]
+
+
+@pytest.mark.parametrize("ci", range(len(GRAD_CASES)))
+@pytest.mark.parametrize("integer_every", [0, 1, 3])
+@pytest.mark.parametrize("dtype", [torch.float64, torch.float32])
+def test_all_gradients_vs_oracle_including_integer_positions(dn, ci, integer_every, dtype):
+    cfg = GRAD_CASES[ci]
+    x, off, alpha, w, b = make(40 + ci, dtype=torch.float64, **cfg)
+    if integer_every:
+        off = _integerise(off, integer_every)
+    Lo = off.shape[2]
+    gy = torch.randn(x.shape[0], w.shape[0], Lo, generator=torch.Generator().manual_seed(50 + ci), dtype=torch.float64)
+    kw = dict(stride=cfg.get("stride", 1), padding=cfg.get("pad", 0), dilation=cfg.get("dil", 1))
+    g, G = cfg.get("groups", 1), cfg.get("G", 1)
+    want_y = orc.deform_conv1d_fwd(x.numpy(), off.numpy(), alpha.numpy(), w.numpy(), b.numpy(), groups=g,
+                                   offset_groups=G, **kw)
+    want = orc.deform_conv1d_bwd(gy.numpy(), x.numpy(), off.numpy(), alpha.numpy(), w.numpy(), True, groups=g,
+                                 offset_groups=G, **kw)
+    ts = [t.to(dtype).cuda().requires_grad_() for t in (x, off, alpha, w, b)]
+    y = dn.deform_conv1d(*ts, n_weight_groups=g, n_offset_groups=G, **kw)
+    y.backward(gy.to(dtype).cuda())
+    tol = 1e-10 if dtype == torch.float64 else 1e-4
+    rel = lambda got, ref: float(np.abs(got.detach().cpu().double().numpy() - ref).max() / max(np.abs(ref).max(), 1e-30))
+    assert rel(y, want_y) <= tol
+    for name, t, ref in zip(("x", "offset", "alpha", "weight", "bias"), ts, want):
+        assert rel(t.grad, ref) <= tol, (name, rel(t.grad, ref))
+
+
+@pytest.mark.skipif(not _reference.available(), reason="baseline/_ref (the reference's compiled extension) is absent")
+@pytest.mark.parametrize("ci", range(len(GRAD_CASES)))
+@pytest.mark.parametrize("integer_every", [0, 1, 3])
+def test_forward_and_all_gradients_vs_reference_cuda_op(dn, ci, integer_every):
+    """Same seeded inputs through the reference's own deform_conv1d (unmodified sources) and through this library."""
+    ref = _reference.load("dconv_native")
+    if ref is None:
+        pytest.skip("the reference extension did not import")
+    cfg = GRAD_CASES[ci]
+    x, off, alpha, w, b = make(60 + ci, dtype=torch.float64, **cfg)
+    if integer_every:
+        off = _integerise(off, integer_every)
+    gy = torch.randn(x.shape[0], w.shape[0], off.shape[2], generator=torch.Generator().manual_seed(70 + ci),
+                     dtype=torch.float64).cuda()
+    kw = dict(stride=cfg.get("stride", 1), padding=cfg.get("pad", 0), dilation=cfg.get("dil", 1),
+              n_weight_groups=cfg.get("groups", 1), n_offset_groups=cfg.get("G", 1))
+    outs = []
+    for fn in (ref.deform_conv1d, dn.deform_conv1d):
+        ts = [t.cuda().requires_grad_() for t in (x, off, alpha, w, b)]
+        y = fn(*ts, **kw)
+        y.backward(gy)
+        torch.cuda.synchronize()
+        outs.append([y.detach()] + [t.grad for t in ts])
+    for name, a, c in zip(("y", "grad_x", "grad_offset", "grad_alpha", "grad_weight", "grad_bias"), *outs):
+        scale = max(float(a.abs().max()), 1e-30)
+        assert float((a - c).abs().max()) <= 1e-10 * scale, name

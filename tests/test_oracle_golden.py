@@ -14,6 +14,7 @@ import torch
 import torch.nn.functional as F
 
 from oracle import oracle as orc
+from tests import _util
 from tests._util import deform_case_names, load_deform_case, make_problem, size_map_cases
 
 
@@ -195,6 +196,64 @@ def test_oracle_deform_conv1d_identities():
     y = orc.deform_conv1d_fwd(x, off, None, w, b, 1, 0, 1, groups, 1)
     ref = torch.nn.functional.conv1d(torch.from_numpy(xs), torch.from_numpy(w), torch.from_numpy(b), 1, 0, 1, groups).numpy()
     assert np.allclose(y, ref, atol=1e-12)
+
+
+@pytest.mark.parametrize("name", _util.deform1d_case_names())
+def test_deform_conv1d_matches_reference_expected_fn(name):
+    """The 1-D oracle against outputs of the reference's own executable specification, expected_fn(1, ...)
+    (ops/dconv-native/test/test_deform_conv.py:127-191), stored by tests/golden/make_golden.py."""
+    c = _util.load_deform1d_case(name)
+    y = orc.deform_conv1d_fwd(c["x"], c["offset"], c["mask"], c["weight"], c["bias"], c["stride"], c["padding"],
+                              c["dilation"], c["groups"], c["offset_groups"])
+    assert y.shape == c["expected"].shape
+    assert np.allclose(y, c["expected"], rtol=1e-5, atol=1e-8)
+
+
+def test_deform_conv1d_backward_matches_finite_differences():
+    """Away from integer positions the 1-D op is differentiable: central differences of the pinned forward."""
+    rng = np.random.default_rng(31)
+    B, C, Cout, L, K, G, groups = 2, 4, 4, 11, 3, 2, 2
+    stride, pad, dil = 2, 2, 1
+    Lo = (L + 2 * pad - dil * (K - 1) - 1) // stride + 1
+    x = rng.standard_normal((B, C, L)); w = rng.standard_normal((Cout, C // groups, K)); b = rng.standard_normal(Cout)
+    off = rng.standard_normal((B, G * K, Lo)) * 1.5
+    off = np.floor(off) + 0.2 + 0.6 * rng.random(off.shape)              # fractions in [0.2, 0.8]
+    alpha = rng.random((B, G * K, Lo)) + 0.5
+    gy = rng.standard_normal((B, Cout, Lo))
+    kw = dict(stride=stride, padding=pad, dilation=dil, groups=groups, offset_groups=G)
+    gx, goff, galpha, gw, gb = orc.deform_conv1d_bwd(gy, x, off, alpha, w, True, **kw)
+    f = lambda x_, o_, a_, w_, b_: float((orc.deform_conv1d_fwd(x_, o_, a_, w_, b_, **kw) * gy).sum())
+    eps = 1e-6
+    for name, arr, grad, idx in (("x", x, gx, (1, 2, 5)), ("offset", off, goff, (0, 4, 3)), ("alpha", alpha, galpha, (1, 1, 2)),
+                                 ("w", w, gw, (2, 1, 1)), ("b", b, gb, (3,))):
+        args = dict(x=x, offset=off, alpha=alpha, w=w, b=b)
+        hi, lo = arr.copy(), arr.copy()
+        hi[idx] += eps; lo[idx] -= eps
+        vals = []
+        for v in (hi, lo):
+            a2 = dict(args); a2[name] = v
+            vals.append(f(a2["x"], a2["offset"], a2["alpha"], a2["w"], a2["b"]))
+        fd = (vals[0] - vals[1]) / (2 * eps)
+        assert abs(fd - grad[idx]) <= 1e-6 * max(1.0, abs(fd)), (name, fd, grad[idx])
+
+
+def test_deform_conv1d_backward_integer_position_rule():
+    """At an integer sampling position the reference's 1-D kernel moves the left neighbour one cell further left
+    (dconv1d_gpu.cu:334-337): grad_offset = alpha * (x[p+1] - x[p-1]) * dcol and grad_alpha = x[p+1] * dcol."""
+    x = np.array([[[1.0, 4.0, 9.0, 16.0, 25.0]]])          # B = C = 1, L = 5
+    w = np.array([[[2.0]]])                                 # Cout = 1, K = 1
+    off = np.zeros((1, 1, 5)); off[0, 0, 2] = 1.0           # position 2 samples cell 3 exactly
+    alpha = np.full((1, 1, 5), 0.5)
+    gy = np.ones((1, 1, 5))
+    gx, goff, galpha, gw, gb = orc.deform_conv1d_bwd(gy, x, off, alpha, w, True)
+    dcol = 2.0
+    assert goff[0, 0, 2] == 0.5 * (25.0 - 9.0) * dcol       # cells 4 and 2 around the sampled cell 3
+    assert galpha[0, 0, 2] == 25.0 * dcol                   # lerp(x[2], x[4], 1) = x[4]
+    assert goff[0, 0, 0] == 0.5 * (4.0 - 0.0) * dcol        # position 0: left neighbour -1 is outside -> 0
+    assert goff[0, 0, 4] == 0.5 * (0.0 - 16.0) * dcol       # position 4: right neighbour 5 is outside -> 0
+    # the scatter keeps the ordinary corners: all of the gradient goes to the sampled cell
+    assert gx[0, 0, 3] == 0.5 * dcol + 0.5 * dcol           # from positions 2 (offset +1) and 3
+    assert gx[0, 0, 2] == 0.0
 
 
 def test_oracle_thread_count_can_be_set_explicitly():
