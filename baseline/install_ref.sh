@@ -13,5 +13,10 @@ for pkg in dconv-native fast-depthwise-conv3d; do
   python -m pip install --no-index --no-build-isolation --no-deps --find-links /opt/wheelhouse \
       --target "$HERE/_ref" --upgrade "$WORK/$pkg"
 done
+# the reference's own unit tests travel with the install (same git-ignored folder), so that they can be run
+# unmodified against this repository's drop-in on a GPU box where the reference checkout is not mounted
+mkdir -p "$HERE/_ref/_reference_tests/dconv_native" "$HERE/_ref/_reference_tests/fast_depthwise_conv3d"
+cp "$REF"/ops/dconv-native/test/*.py "$HERE/_ref/_reference_tests/dconv_native/"
+cp "$REF"/ops/fast-depthwise-conv3d/test/*.py "$HERE/_ref/_reference_tests/fast_depthwise_conv3d/"
 rm -rf "$WORK"
 echo "installed into $HERE/_ref"

@@ -61,7 +61,7 @@ def build(force=False, verbose=False):
         failed |= p.returncode != 0
     if failed:
         raise RuntimeError("nvcc failed building libd2conv3d.so")
-    cmd = [_nvcc(), "-shared", "-o", LIB] + objs + ["-cudart", "static"]
+    cmd = [_nvcc(), "-shared", "-o", LIB] + objs + ["-cudart", "static", "-Xlinker", "-soname=libd2conv3d.so"]
     subprocess.run(cmd, check=True)
     return LIB
 

@@ -31,6 +31,7 @@ _MASK_ACTIVATIONS = {
     "relu": torch.relu,
     "tanh": torch.tanh,
     "linear": lambda t: t,
+    "none": lambda t: t,
 }
 
 
@@ -47,35 +48,96 @@ def apply_size_activation(mode, size_map):
     raise ValueError(f"Unexpected size activation mode '{mode}'")
 
 
+# Positional arguments after `activation`: the package's modules.py continues with (deform_param_op), the
+# training code's network/layers.py with (init, norm_type, norm_groups, size_activation, deform_param_op).
+_LAYERS_PY_ORDER = ("init", "norm_type", "norm_groups", "size_activation", "deform_param_op")
+
+
 class _DConvBase(nn.Module):
+    """Constructor: the ten leading arguments of both reference classes, then either reference's remaining ones
+    (positionally: a string in 11th place means network/layers.py's order, anything else the package's
+    `deform_param_op`), all of them also accepted as keywords:
+
+      init             "zero" (default) | "random" (modulated layers only: network/layers.py:122-132)
+      norm_type        "none" | "GroupNorm" | "BatchNorm": a norm on the predictor's input (layers.py:37-44)
+      norm_groups      groups of that GroupNorm
+      size_activation  "elu" | "relu" | "relu_plus_one" | "linear" (layers.py:171-181)
+      deform_param_op  class of the predictor, or a ready nn.Module instance (then used as is, not initialised)
+
+    and three that only this package has: `norm` (a ready norm module instead of norm_type), `use_checkpoint`
+    (recompute the predictor in the backward, what layers.py:99 always does) and `fused_field`."""
+
     # variant description (overridden by subclasses)
     modulated = False      # predict a modulation mask (DCNv2)
     field_mode = None      # None: predict 3*G*K offsets; else dilation-field mode "x"/"xy"/"xxz"/"xyz"
     frozen_dims = ()       # offset components (0:z 1:y 2:x) forced to zero (Spatial*/Temporal*)
 
     def __init__(self, in_channels, out_channels, kernel_size, stride=1, padding=0, dilation=1, groups=1,
-                 offset_groups=1, bias=True, activation="sigmoid", deform_param_op=nn.Conv3d,
-                 size_activation="elu", norm=None, use_checkpoint=False, fused_field=True):
+                 offset_groups=1, bias=True, activation="sigmoid", *extra, **kw):
         super().__init__()
+        if extra:
+            names = _LAYERS_PY_ORDER if isinstance(extra[0], str) else ("deform_param_op",)
+            if len(extra) > len(names):
+                raise TypeError(f"too many positional arguments ({10 + len(extra)})")
+            for n, v in zip(names, extra):
+                if n in kw:
+                    raise TypeError(f"got multiple values for argument '{n}'")
+                kw[n] = v
+        init = kw.pop("init", "zero")
+        norm_type = kw.pop("norm_type", "none")
+        norm_groups = kw.pop("norm_groups", 1)
+        size_activation = kw.pop("size_activation", "elu")
+        deform_param_op = kw.pop("deform_param_op", nn.Conv3d)
+        norm = kw.pop("norm", None)
+        use_checkpoint = kw.pop("use_checkpoint", False)
+        fused_field = kw.pop("fused_field", True)
+        if kw:
+            raise TypeError(f"unexpected keyword argument(s): {sorted(kw)}")
+
         kernel_size = _triple(kernel_size)
         self.num_kernel_points = kernel_size[0] * kernel_size[1] * kernel_size[2]
         self.offset_groups, self.groups = offset_groups, groups
         self.size_activation = size_activation
         self.use_checkpoint = use_checkpoint
         self.fused_field = fused_field
+        if norm_type not in ("BatchNorm", "GroupNorm", "none"):
+            raise ValueError(f"Unexpected norm_type: '{norm_type}'")
+        if norm is None and norm_type == "GroupNorm":
+            norm = nn.GroupNorm(norm_groups, in_channels)
+        elif norm is None and norm_type == "BatchNorm":
+            norm = nn.BatchNorm3d(in_channels)
         self.norm = norm
         self.alpha_channels = offset_groups * self.num_kernel_points if self.modulated else 0
         if self.field_mode is None:
             self.offset_channels = 3 * offset_groups * self.num_kernel_points
         else:
             self.offset_channels = {"x": 1, "xy": 2, "xxz": 2, "xyz": 3}[self.field_mode]
-        self.deform_params = deform_param_op(in_channels, self._deform_channels(), kernel_size, stride, padding,
-                                             dilation, 1, bias)
+        if isinstance(deform_param_op, nn.Module):
+            self.deform_params = deform_param_op
+        else:
+            self.deform_params = deform_param_op(in_channels, self._deform_channels(), kernel_size, stride, padding,
+                                                 dilation, 1, bias)
         self.deform_conv = DeformConv3d(in_channels, out_channels, kernel_size, stride, padding, dilation,
                                         groups, offset_groups, bias)
         self.activation = _MASK_ACTIVATIONS[activation] if isinstance(activation, str) else activation
-        # zero-initialised predictor: the layer starts as an ordinary convolution
-        nn.init.zeros_(self.deform_params.weight)
+        if not isinstance(deform_param_op, nn.Module):
+            self._init_deform_params(activation, init)
+
+    def _init_deform_params(self, activation, init):
+        """network/layers.py:78-86 (offset-only layers) and :122-132 (modulated layers)."""
+        w = self.deform_params.weight
+        if init == "zero":
+            # the layer starts as an ordinary convolution (times the activation of 0 when modulated)
+            nn.init.zeros_(w)
+        elif init == "random" and self.modulated:
+            # the reference re-draws the modulation rows only; the geometry rows keep the predictor's own init
+            with torch.no_grad():
+                if activation in ("sigmoid", "tanh"):
+                    nn.init.xavier_normal_(w[self.offset_channels:])
+                else:
+                    nn.init.kaiming_normal_(w[self.offset_channels:])
+        else:
+            raise ValueError(f"init scheme {init} not supported")
         if getattr(self.deform_params, "bias", None) is not None:
             nn.init.zeros_(self.deform_params.bias)
 

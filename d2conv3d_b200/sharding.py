@@ -35,28 +35,38 @@ def shard_clips(tensors, rank=None, world_size=None):
 
 
 def all_reduce_param_grads(grads, group=None, async_op=False):
-    """Sums parameter gradients (grad_weight, grad_bias; None entries skipped) over all ranks in place.
-    One flat bucket, so small gradients cost a single collective.  Returns the work handle when
-    async_op (call .wait() and then `unflatten()` on the returned tuple's second element)."""
+    """Sums parameter gradients (grad_weight, grad_bias; None entries skipped) over all ranks, as ONE flat
+    bucket so that small gradients cost a single collective.
+
+    Always returns `(work, finish)`: `work` is the collective's handle (None when nothing had to be launched or
+    the call was synchronous) and `finish()` waits for it (if needed) and copies the reduced values back into
+    the gradient tensors.  With async_op=False `finish` has already run and is a no-op to call again."""
     live = [g for g in grads if g is not None]
     if not live or not dist.is_initialized() or dist.get_world_size(group) == 1:
-        return None
-    if len(live) == 1:
-        return dist.all_reduce(live[0], op=dist.ReduceOp.SUM, group=group, async_op=async_op)
-    flat = torch.cat([g.reshape(-1) for g in live])
+        return None, (lambda: None)
+    flat = live[0].reshape(-1) if (len(live) == 1 and live[0].is_contiguous()) else \
+        torch.cat([g.reshape(-1) for g in live])
+    in_place = len(live) == 1 and flat.data_ptr() == live[0].data_ptr()
     work = dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group, async_op=async_op)
+    state = {"done": False}
 
-    def unflatten():
-        off = 0
-        for g in live:
-            n = g.numel()
-            g.copy_(flat[off:off + n].view_as(g))
-            off += n
+    def finish():
+        if state["done"]:
+            return
+        if work is not None:
+            work.wait()
+        if not in_place:
+            off = 0
+            for g in live:
+                n = g.numel()
+                g.copy_(flat[off:off + n].view_as(g))
+                off += n
+        state["done"] = True
 
-    if async_op:
-        return work, unflatten
-    unflatten()
-    return None
+    if not async_op:
+        finish()
+        return None, finish
+    return work, finish
 
 
 def broadcast_params(params, src=0, group=None):

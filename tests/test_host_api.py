@@ -79,6 +79,54 @@ def test_get_deformation_on_cpu_matches_reference_semantics():
     assert offsets[:, 1::3].abs().max() == 0 and offsets[:, 2::3].abs().max() == 0 and offsets[:, 0::3].abs().max() > 0
 
 
+def test_layer_constructor_accepts_both_reference_signatures():
+    """The package's modules.py (ops/dconv-native/src/dconv_native/modules.py:17-19) continues after `activation`
+    with deform_param_op; the training code's network/layers.py:27-30 with init, norm_type, norm_groups,
+    size_activation, deform_param_op.  Both call styles, positional and keyword, must work."""
+    # network/layers.py keywords
+    layer = modules.MDConv3d(8, 8, 3, padding=1, init="zero", norm_type="GroupNorm", norm_groups=2,
+                             size_activation="relu", deform_param_op=nn.Conv3d, activation="none")
+    assert isinstance(layer.norm, nn.GroupNorm) and layer.norm.num_groups == 2 and layer.size_activation == "relu"
+    assert layer.activation(torch.tensor(-3.0)) == -3.0                     # "none" = identity
+    assert isinstance(modules.DConv3d(8, 8, 3, norm_type="BatchNorm").norm, nn.BatchNorm3d)
+    with pytest.raises(ValueError):
+        modules.DConv3d(8, 8, 3, norm_type="LayerNorm")
+    # layers.py positional order: (..., activation, init, norm_type, norm_groups, size_activation, deform_param_op)
+    layer = modules.XYZSizeConditionedMDConv3d(8, 8, 3, 1, 1, 1, 1, 2, True, "sigmoid", "zero", "GroupNorm", 4,
+                                                "relu_plus_one", nn.Conv3d)
+    assert layer.norm.num_groups == 4 and layer.size_activation == "relu_plus_one"
+    # package order: (..., activation, deform_param_op)
+    made = []
+
+    def factory(*a):
+        made.append(a)
+        return nn.Conv3d(*a)
+    layer = modules.DConv3d(8, 8, 3, 1, 1, 1, 1, 1, True, "sigmoid", factory)
+    assert made and made[0][1] == 81
+    # a ready module instance is used as is and not re-initialised
+    pred = nn.Conv3d(8, 4 * 27, 3, padding=1)
+    nn.init.constant_(pred.weight, 0.25)
+    layer = modules.MDConv3d(8, 8, 3, padding=1, deform_param_op=pred)
+    assert layer.deform_params is pred and torch.all(pred.weight == 0.25)
+    with pytest.raises(TypeError):
+        modules.DConv3d(8, 8, 3, bogus=1)
+
+
+def test_layer_init_schemes_follow_the_training_code():
+    """network/layers.py:78-86,122-132: 'zero' for every layer; 'random' only for modulated layers, where it re-draws
+    the modulation rows of the predictor and zeroes its bias."""
+    torch.manual_seed(0)
+    layer = modules.MDConv3d(8, 8, 3, padding=1, init="random")
+    w = layer.deform_params.weight
+    assert w[layer.offset_channels:].abs().sum() > 0 and layer.deform_params.bias.abs().sum() == 0
+    layer = modules.XYZSizeConditionedMDConv3d(8, 8, 3, padding=1, init="random", activation="relu")
+    assert layer.deform_params.weight[3:].abs().sum() > 0
+    with pytest.raises(ValueError):
+        modules.DConv3d(8, 8, 3, init="random")
+    with pytest.raises(ValueError):
+        modules.MDConv3d(8, 8, 3, init="orthogonal")
+
+
 def test_add_deformable_conv_replaces_conv3d():
     net = nn.Sequential(nn.Conv3d(4, 8, 3, padding=1), nn.ReLU(), nn.Sequential(nn.Conv3d(8, 8, 1), nn.Conv3d(8, 4, 3, bias=False)))
     w0 = net[0].weight.data.clone()

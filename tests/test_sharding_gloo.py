@@ -50,7 +50,19 @@ def _worker(rank, world, port, out_dir):
     y = orc.deform_conv3d_fwd(x.numpy(), off.numpy(), m.numpy(), w.numpy(), bias.numpy(), **kw)
     gx, goff, gm, gw, gb = orc.deform_conv3d_bwd(gy.numpy(), x.numpy(), off.numpy(), m.numpy(), w.numpy(), True, **kw)
     gw_t, gb_t = torch.from_numpy(gw), torch.from_numpy(gb)
-    sharding.all_reduce_param_grads([gw_t, None, gb_t])       # the only collective
+    work, finish = sharding.all_reduce_param_grads([gw_t, None, gb_t])       # the only collective
+    assert work is None
+    finish()                                                  # synchronous call: already done, a no-op
+    # the asynchronous form returns the same (work, finish) shape; values land when finish() returns
+    probe = [torch.full((3,), float(rank + 1)), torch.full((2, 2), 10.0 * (rank + 1))]
+    work, finish = sharding.all_reduce_param_grads(probe, async_op=True)
+    assert work is not None
+    finish()
+    assert torch.all(probe[0] == 3.0) and torch.all(probe[1] == 30.0)
+    single = [torch.full((4,), float(rank + 1))]
+    work, finish = sharding.all_reduce_param_grads(single, async_op=True)
+    finish()
+    assert torch.all(single[0] == 3.0)
     np.savez(os.path.join(out_dir, f"rank{rank}.npz"), y=y, gx=gx, goff=goff, gm=gm, gw=gw_t.numpy(), gb=gb_t.numpy())
     dist.barrier()
     dist.destroy_process_group()
