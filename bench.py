@@ -16,8 +16,11 @@ inside the timed region); `roofline` describes the dominant kernel phase as time
 library's own CUDA events during the timed steps; `cpu_baseline` is the CPU restatement of the
 reference algorithm (oracle/) on a bounded sample of the same workload.
 
-`--impl reference` times that CPU restatement alone on the host cores (the reference op has no
-CPU implementation and cannot be built without its GPU toolchain here), rank 0 only.
+`--impl reference` times the UNMODIFIED reference op on the same inputs with the same protocol: its compiled
+CUDA extension from baseline/_ref (the reference has no CPU implementation of this op) -- every rank on its own
+clips, grad_weight all-reduced, device-timed value and host-buffer `e2e` like the line above; the CPU
+restatement (oracle/) is timed beside it on rank 0 and reported as `cpu_baseline`.  Only when that extension
+cannot be loaded or there is no GPU does the arm fall back to the CPU restatement alone (rank 0), saying why.
 """
 import argparse
 import json
@@ -177,7 +180,22 @@ def cpu_arm(steps, warmup, budget_s):
 
 
 def run_reference_arm(args):
+    """The reference's own implementation of the path.  Its op is CUDA-only (every tensor is checked with
+    is_cuda, ops/dconv-native/csrc/ops/dconv_gpu_common.h:32-36), so the like-for-like arm is its compiled
+    extension on the same GPU(s); the CPU restatement is the fallback and the `cpu_baseline` figure."""
     rank = int(os.environ.get("RANK", "0"))
+    why = None
+    try:
+        import torch
+        from tests import _reference
+        if not torch.cuda.is_available():
+            why = "no CUDA device"
+        elif _reference.load("dconv_native") is None:
+            why = "baseline/_ref (the reference's compiled extension) is absent or does not import"
+    except Exception as exc:                                  # pragma: no cover
+        why = f"{type(exc).__name__}: {exc}"
+    if why is None:
+        return run_gpu_arm(args, impl="reference")
     if rank != 0:
         return
     val, ms, sample, cores = cpu_arm(args.steps, args.warmup, budget_s=150.0)
@@ -188,16 +206,18 @@ def run_reference_arm(args):
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
-        "note": "the reference op is CUDA-only; this arm times the CPU restatement of its algorithm (oracle/)",
+        "note": f"reference CUDA op not usable here ({why}); this line times the CPU restatement of its algorithm (oracle/)",
     }
     print(json.dumps(line), flush=True)
 
 
 # ---- GPU arm ---------------------------------------------------------------------------------------
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised in profiles/
-# (same workload); None where no capture has been taken.
-TRAFFIC_PER_LAUNCH = {       # (phase, math mode) -> DRAM read + write bytes of one launch (profiles/c2_fwd_bwd_step_kernels.md)
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch, from ncu captures of this workload at full size
+# (None where no capture has been taken).  TRAFFIC_SOURCE names the capture; kernels changed after it keep their
+# entry only if the change cannot alter DRAM traffic.
+TRAFFIC_SOURCE = "ncu --set full capture of this bench's C2 step, one launch per kernel, both math modes"
+TRAFFIC_PER_LAUNCH = {       # (phase, math mode) -> DRAM read + write bytes of one launch
     # fp32-parity mode, Cout = 512: the gradient columns arrive as two partial buffers (2 x 1.43 GB read)
     ("bwd_sample_grad", "bf16"): 1.603e9 + 0.137e9, ("bwd_sample_grad", "auto"): 3.065e9 + 0.142e9,
     ("bwd_sample_grad", "bf16x3"): 3.065e9 + 0.142e9,
@@ -206,6 +226,12 @@ TRAFFIC_PER_LAUNCH = {       # (phase, math mode) -> DRAM read + write bytes of 
     ("bwd_dw_sm100", "auto"): 0.554e9 + 0.066e9,
     ("bwd_dcol_sm100", "auto"): 2 * (0.088e9 + 1.384e9), ("bwd_dcol_sm100", "bf16x3"): 2 * (0.088e9 + 1.384e9),
 }
+# The sampling-gradient kernel's real limiter: every live corner of every sample adds 64 fp32 channels into the
+# L2-resident grad_input accumulator.  payload_bytes = corners inside the volume for the benchmark's offsets
+# (5.69 of 8 per sample on average at sigma = 2 voxels, D = 8) x 5.6 M samples x 256 B; rate = what
+# red.global.add.v4.f32 sustains on this part for exactly this access pattern (microbenchmark, 11.5 GB in 1.70 ms).
+SCATTER = {"payload_bytes": 5.687 * 2 * 8 * 27 * 12960 * 256, "rate_gbs": 6747.0,
+           "source": "d2conv3d_b200/csrc/microbench/l2_rates.cu on a B200 of this pool"}
 
 PHASE_WORK = {
     # phase name -> (bound, key of the algorithmic work of one launch)
@@ -258,12 +284,36 @@ def time_reference_cuda_op(host, w, bias, wl, F):
         return {"error": f"{type(exc).__name__}: {exc}"}
 
 
-def run_gpu_arm(args):
+def bind_to_gpu_numa_node(local_rank):
+    """Pins this process to the CPUs that NVML reports as nearest to its GPU (read-only query), BEFORE any pinned
+    host buffer is allocated, so that the buffers land on that NUMA node and N ranks do not all stream through
+    one socket's memory.  Returns a short description for the JSON line."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(local_rank)
+        n_words = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(h, n_words)
+        cpus = {64 * i + b for i, w in enumerate(mask) for b in range(64) if (w >> b) & 1}
+        allowed = os.sched_getaffinity(0)
+        cpus &= allowed
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            return f"{len(cpus)} CPUs near GPU {local_rank} (NVML affinity)"
+        return "NVML affinity empty: unchanged"
+    except Exception as exc:
+        return f"unchanged ({type(exc).__name__})"
+
+
+def run_gpu_arm(args, impl="ours"):
+    """One step = forward + full backward of the C2 layer on every rank's own clips; with N > 1 the parameter
+    gradients are all-reduced (NCCL) inside the step.  impl = "ours": this library; impl = "reference": the
+    reference's compiled CUDA op from baseline/_ref, same inputs, same timing protocol."""
     import torch
     import torch.distributed as dist
 
     import d2conv3d_b200
-    from d2conv3d_b200 import _lib, dconv_native
+    from d2conv3d_b200 import _lib, dconv_native, sharding
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -271,18 +321,39 @@ def run_gpu_arm(args):
     if args.gpus != world:
         if world == 1 and args.gpus > 1:
             raise SystemExit("launch N>1 with torchrun (one rank per GPU)")
+    affinity = bind_to_gpu_numa_node(local_rank)
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    ours = impl == "ours"
     _lib.lib()
-    d2conv3d_b200.set_math_mode(args.mode)
     wl = WORKLOAD
     peaks = measured_peaks()
+    if ours:
+        d2conv3d_b200.set_math_mode(args.mode)
+        op = lambda *t: dconv_native.deform_conv3d(*t, 1, wl["pad"], 1, 1, wl["G"])
+    else:
+        from tests import _reference
+        ref = _reference.load("dconv_native")
+        torch.backends.cuda.matmul.allow_tf32 = False          # the reference's cuBLAS path in plain fp32
+        op = lambda *t: ref.deform_conv3d(*t, 1, wl["pad"], 1, 1, wl["G"])
 
     p = make_inputs(1002 + rank, wl)
-    host = {k: torch.from_numpy(p[k]).pin_memory() for k in ("x", "geo", "mask", "gy")}
-    x, off, mask, gy = (host[k].to(dev) for k in ("x", "geo", "mask", "gy"))
+    # ONE pinned buffer per direction: the four inputs of a step are slices of `host_in` (and of one device
+    # buffer), so a step's upload is a single copy
+    keys = ("x", "geo", "mask", "gy")
+    sizes = [p[k].size for k in keys]
+    offs = np.concatenate([[0], np.cumsum([(n + 63) // 64 * 64 for n in sizes])])      # 256-byte aligned slices
+    host_in = torch.empty(int(offs[-1]), dtype=torch.float32).pin_memory()
+    for k, o, n in zip(keys, offs, sizes):
+        host_in[int(o):int(o) + n].copy_(torch.from_numpy(p[k]).reshape(-1))
+
+    def views(flat):
+        return {k: flat[int(o):int(o) + n].view(p[k].shape) for k, o, n in zip(keys, offs, sizes)}
+
+    dev_in = views(host_in.to(dev))
+    x, off, mask, gy = (dev_in[k] for k in keys)
     w = torch.from_numpy(make_inputs(1002, wl)["weight"]).to(dev)      # weights replicated across ranks
     bias = torch.zeros(wl["Cout"], device=dev)
     for t in (x, off, mask, w, bias):
@@ -297,21 +368,59 @@ def run_gpu_arm(args):
     work = {"F": F, "coord_bytes": coord_bytes, "col2im_bytes": col2im_bytes, "sample_grad_bytes": sample_grad_bytes}
 
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)      # 256 MB > 126 MB L2
+    s_main = torch.cuda.current_stream()
+    s_coll = torch.cuda.Stream() if world > 1 else None
+
+    def reduce_param_grads(wt, bt):
+        """All-reduce of grad_weight + grad_bias as one bucket.  This library: issued from a side stream that
+        waits only for the event the backward records when the parameter gradients are final (they are computed
+        first), so the collective runs under the data-side backward; the compute stream joins at the end of the
+        step.  Reference op: no such event, the collective follows the backward (what DDP does for a
+        single-bucket model)."""
+        if world == 1:
+            return
+        ev = dconv_native._ops.params_ready_event() if ours else None
+        finish = sharding.all_reduce_param_grads_overlapped([wt.grad, bt.grad], ev, s_coll)
+        finish()
 
     def step():
         for t in (x, off, mask, w, bias):
             t.grad = None
-        y = dconv_native.deform_conv3d(x, off, mask, w, bias, 1, wl["pad"], 1, 1, wl["G"])
+        y = op(x, off, mask, w, bias)
         y.backward(gy)
-        if world > 1:
-            dist.all_reduce(w.grad)
-            dist.all_reduce(bias.grad)
+        reduce_param_grads(w, bias)
         return y
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    # ---- N > 1: the all-reduced parameter gradients against the single-GPU full-batch gradient -------------
+    allreduce_check = None
+    if world > 1:
+        step()
+        torch.cuda.synchronize()
+        got_w, got_b = w.grad.clone(), bias.grad.clone()
+        if rank == 0:
+            want_w, want_b = torch.zeros_like(w), torch.zeros_like(bias)
+            for r in range(world):                       # every rank's clips, one rank after the other, on this GPU
+                q = p if r == 0 else make_inputs(1002 + r, wl)
+                ts = [torch.from_numpy(q[k]).to(dev).requires_grad_(k != "gy") for k in keys]
+                wr, br = w.detach().clone().requires_grad_(), bias.detach().clone().requires_grad_()
+                op(ts[0], ts[1], ts[2], wr, br).backward(ts[3])
+                want_w += wr.grad; want_b += br.grad
+                del ts, q
+            torch.cuda.synchronize()
+            ew = float((got_w - want_w).abs().max() / want_w.abs().max())
+            eb = float((got_b - want_b).abs().max() / want_b.abs().max())
+            bound = 1e-4 if (not ours or args.mode != "bf16") else 2e-2
+            allreduce_check = {"status": "ok" if max(ew, eb) <= bound else "MISMATCH", "grad_weight_rel_err": ew,
+                               "grad_bias_rel_err": eb, "bound": bound,
+                               "what": f"all-reduced gradients of {world} ranks vs the sum over the same {world * wl['B']} "
+                                       "clips evaluated on one GPU"}
+            del want_w, want_b
+        dist.barrier()
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -322,59 +431,71 @@ def run_gpu_arm(args):
     barrier()
     if rank == 0:
         sampler.wait_for_samples()
-    _lib.profile_read()
-    _lib.profile_enable(True)
+
+    def timed_steps(n, with_phases):
+        if with_phases:
+            _lib.profile_read()
+            _lib.profile_enable(True)
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n)]
+        barrier()
+        t0 = time.time()
+        for i in range(n):
+            flush.zero_()                      # L2 flush between timed iterations, outside the event pair
+            ev[i][0].record()
+            step()
+            ev[i][1].record()
+        barrier()
+        t1 = time.time()
+        phases = None
+        if with_phases:
+            _lib.profile_enable(False)
+            phases = _lib.profile_read()
+        tt = torch.tensor([sum(a.elapsed_time(b) for a, b in ev)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        return float(tt.item()) / n, phases, t0, t1
+
     launches0 = _lib.launch_count()
-    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    barrier()
-    t_start = time.time()
-    for i in range(args.steps):
-        flush.zero_()                      # L2 flush between timed iterations, outside the event pair
-        ev[i][0].record()
-        step()
-        ev[i][1].record()
-    barrier()
-    t_end = time.time()
+    ms_per_step, phases, t_start, t_end = timed_steps(args.steps, ours)
     launches = _lib.launch_count() - launches0
-    _lib.profile_enable(False)
-    phases = _lib.profile_read()
     clocks = None
     if rank == 0:
         sampler.stop()
         clocks = sampler.summary(t_start, t_end)
-    _lib.device_status()               # raises if a bounded device-side wait gave up
-    total_ms = sum(a.elapsed_time(b) for a, b in ev)
-    tt = torch.tensor([total_ms], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-    total_ms = float(tt.item())
-    ms_per_step = total_ms / args.steps
+    if ours:
+        _lib.device_status()               # raises if a bounded device-side wait gave up
     value = 3 * F * world / (ms_per_step * 1e-3) / 1e12
 
     # ---- end-to-end with host buffers: pinned H2D of the step's inputs, D2H of its results ----
-    # Every step copies its own inputs up and its own results down; the copies of neighbouring steps run on two
-    # copy streams (PCIe is full duplex) behind the compute stream, with double-buffered device inputs and pinned
-    # host outputs, as a training / serving loop with a prefetching loader would.
-    outs = [{k: torch.empty_like(v, device="cpu").pin_memory() for k, v in
-             (("y", gy), ("gx", x), ("goff", off), ("gmask", mask), ("gw", w))} for _ in range(2)]
-    ins = [{k: torch.empty_like(host[k], device=dev) for k in host} for _ in range(2)]
-    h2d = sum(host[k].numel() * 4 for k in host)
-    d2h = sum(outs[0][k].numel() * 4 for k in outs[0])
-    s_main = torch.cuda.current_stream()
+    # Every step copies its own inputs up (ONE copy: the packed input buffer) and its own results down (into ONE
+    # packed pinned buffer; the five results are separate device tensors, so five slice copies).  The copies of
+    # neighbouring steps run on two copy streams (the link is full duplex) behind the compute stream, with
+    # double-buffered device inputs and pinned host outputs, as a training loop with a prefetching loader would.
+    # grad_weight is identical on every rank after the all-reduce: only rank 0 reads it back.
+    out_keys = ("y", "gx", "goff", "gmask") + (("gw",) if rank == 0 else ())
+    out_like = {"y": gy, "gx": x, "goff": off, "gmask": mask, "gw": w}
+    out_sizes = [out_like[k].numel() for k in out_keys]
+    out_offs = np.concatenate([[0], np.cumsum([(n + 63) // 64 * 64 for n in out_sizes])])
+    host_out = [torch.empty(int(out_offs[-1]), dtype=torch.float32).pin_memory() for _ in range(2)]
+    ins = [torch.empty_like(host_in, device=dev) for _ in range(2)]
+    h2d = host_in.numel() * 4
+    d2h = sum(out_sizes) * 4
     s_up, s_down = torch.cuda.Stream(), torch.cuda.Stream()
 
-    def e2e_run(n):
+    def e2e_run(n, compute=True):
         up_done = [torch.cuda.Event() for _ in range(2)]
         comp_done = [torch.cuda.Event() for _ in range(2)]
         down_done = [torch.cuda.Event() for _ in range(2)]
+        stand_in = None
+        if not compute:      # copy-only run: the same bytes move, no kernel of the layer runs
+            stand_in = {"y": gy, "gx": x.detach(), "goff": off.detach(), "gmask": mask.detach(), "gw": w.detach()}
 
         def upload(i):
             cur = i & 1
             with torch.cuda.stream(s_up):
                 if i >= 2:
                     s_up.wait_event(comp_done[cur])          # step i-2 no longer reads this input buffer
-                for k in host:
-                    ins[cur][k].copy_(host[k], non_blocking=True)
+                ins[cur].copy_(host_in, non_blocking=True)
                 up_done[cur].record(s_up)
 
         upload(0)
@@ -383,75 +504,105 @@ def run_gpu_arm(args):
             if i + 1 < n:
                 upload(i + 1)
             s_main.wait_event(up_done[cur])
-            xs, os_, ms_ = (ins[cur][k].detach().requires_grad_(True) for k in ("x", "geo", "mask"))
-            w.grad = None
-            y = dconv_native.deform_conv3d(xs, os_, ms_, w, bias, 1, wl["pad"], 1, 1, wl["G"])
-            y.backward(ins[cur]["gy"])
-            if world > 1:
-                dist.all_reduce(w.grad)
+            if compute:
+                v = views(ins[cur])
+                xs, os_, ms_ = (v[k].detach().requires_grad_(True) for k in ("x", "geo", "mask"))
+                w.grad = None
+                bias.grad = None
+                y = op(xs, os_, ms_, w, bias)
+                y.backward(v["gy"])
+                reduce_param_grads(w, bias)
+                res = {"y": y.detach(), "gx": xs.grad, "goff": os_.grad, "gmask": ms_.grad, "gw": w.grad}
+            else:
+                res = stand_in
             comp_done[cur].record(s_main)
-            res = {"y": y.detach(), "gx": xs.grad, "goff": os_.grad, "gmask": ms_.grad, "gw": w.grad}
             with torch.cuda.stream(s_down):
                 s_down.wait_event(comp_done[cur])
                 if i >= 2:
-                    s_down.wait_event(down_done[cur])        # host buffers of step i-2 are free again
-                for k, t in res.items():
-                    outs[cur][k].copy_(t, non_blocking=True)
-                    t.record_stream(s_down)
+                    s_down.wait_event(down_done[cur])        # host buffer of step i-2 is free again
+                for k, o, nn_ in zip(out_keys, out_offs, out_sizes):
+                    host_out[cur][int(o):int(o) + nn_].copy_(res[k].reshape(-1), non_blocking=True)
+                    res[k].record_stream(s_down)
                 down_done[cur].record(s_down)
         s_main.wait_stream(s_down)
         s_main.wait_stream(s_up)
 
-    e2e = None
-    if not args.no_e2e:
-        e2e_steps = max(2, min(args.steps, 10))
-        e2e_run(2)
+    def e2e_time(n, compute):
+        e2e_run(2, compute)
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        e2e_run(e2e_steps)
+        e2e_run(n, compute)
         e1.record()
         barrier()
         te = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
         if world > 1:
             dist.all_reduce(te, op=dist.ReduceOp.MAX)
-        e2e_ms = float(te.item()) / e2e_steps
+        return float(te.item()) / n
+
+    e2e = None
+    if not args.no_e2e:
+        e2e_steps = max(2, min(args.steps, 10))
+        e2e_ms = e2e_time(e2e_steps, True)
+        copy_ms = e2e_time(e2e_steps, False)
         e2e = {"value": 3 * F * world / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps,
+               "copy_only_ms": copy_ms,
+               "copy_only_note": "the same uploads and downloads per step with no kernel of the layer in between: "
+                                 "what the host link sustains with all ranks copying at once",
+               "host_buffers": f"one packed pinned buffer per direction, allocated after binding to {affinity}",
                "overlap": "copies of neighbouring steps on two copy streams behind the compute stream"}
 
     # ---- the single-pass bf16 mode (looser stated parity bound) on the same inputs, as a second figure ----
     bf16_mode = None
     main_mode = _lib.get_math_mode()
-    if main_mode != "bf16" and not args.no_bf16_mode:
+    if ours and main_mode != "bf16" and not args.no_bf16_mode:
         d2conv3d_b200.set_math_mode("bf16")
         n2 = max(1, min(args.steps, 20))
         for _ in range(3):
             flush.zero_()
             step()
-        barrier()
-        ev2 = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n2)]
-        for i in range(n2):
-            flush.zero_()
-            ev2[i][0].record()
-            step()
-            ev2[i][1].record()
-        barrier()
-        t2 = torch.tensor([sum(a.elapsed_time(b) for a, b in ev2)], device=dev, dtype=torch.float64)
-        if world > 1:
-            dist.all_reduce(t2, op=dist.ReduceOp.MAX)
-        ms2 = float(t2.item()) / n2
+        ms2, ph2, _, _ = timed_steps(n2, True)
+        agg2 = {}
+        for name, ms in ph2:
+            agg2[name] = agg2.get(name, 0.0) + ms / n2
         bf16_mode = {"ms_per_step": ms2, "value": 3 * F * world / (ms2 * 1e-3) / 1e12, "unit": UNIT, "steps": n2,
-                     "parity": "output <= 1e-2, gradients <= 2e-2 of scale (stated bound of this mode)"}
+                     "parity": "output <= 1e-2, gradients <= 2e-2 of scale (stated bound of this mode)",
+                     "phases": {k: {"ms_avg": round(v, 4),
+                                    **({"frac_of_peak": round(F / (v * 1e-3) / 1e12 / peaks["tensor_sustained"], 4)}
+                                       if PHASE_WORK.get(k, ("", ""))[0] == "tensor" else
+                                       {"frac_of_peak": round(work[PHASE_WORK[k][1]] / (v * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)}
+                                       if k in PHASE_WORK else {})}
+                                for k, v in agg2.items()}}
         d2conv3d_b200.set_math_mode(main_mode)
         _lib.device_status()
 
-    if rank == 0:
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "data": "synthetic", "tensor_dtype": "f32",
+        "config": {"workload": wl["name"], "l2": "256 MB buffer written between timed iterations",
+                   "collective": ("all-reduce of grad_weight+grad_bias as one bucket (NCCL)" +
+                                  (", issued when the weight gradient is done, under the data-side backward" if ours else
+                                   ", after the backward")) if world > 1 else "none"},
+        "clips_per_s": wl["B"] * world / (ms_per_step * 1e-3),
+        "e2e": e2e, "clocks": clocks,
+    }
+    if allreduce_check is not None:
+        line["allreduce_check"] = allreduce_check["status"]
+        line["allreduce_check_detail"] = allreduce_check
+    if ours:
         # ---- roofline of the dominant kernel phase (library events over the timed steps) ----
         agg = {}
         for name, ms in phases:
             a = agg.setdefault(name, [0, 0.0])
             a[0] += 1; a[1] += ms
+
         def phase_roofline(name, avg_ms, launches_per_step=1.0):
             # avg_ms: the phase's time per STEP (a phase may be more than one launch: the fp32-parity mode runs
             # the gradient-column contraction as two accumulating launches); work[key] is per step as well
@@ -462,10 +613,20 @@ def run_gpu_arm(args):
                 achieved, peak, unit = work[key] / (avg_ms * 1e-3) / 1e12, peaks["tensor_sustained"], "TFLOP/s"
             else:
                 achieved, peak, unit = work[key] / (avg_ms * 1e-3) / 1e9, peaks["hbm_gbs"], "GB/s"
-            return {"kernel": name, "bound": bound, "achieved": achieved, "peak": peak, "unit": unit,
-                    "frac": achieved / peak, "traffic": TRAFFIC_PER_LAUNCH.get((name, _lib.get_math_mode())),
-                    "ms_per_launch": avg_ms / launches_per_step, "launches_per_step": launches_per_step,
-                    "peak_source": peaks["source"] + (" (bf16 dense, sustained)" if bound == "tensor" else " (copy)")}
+            r = {"kernel": name, "bound": bound, "achieved": achieved, "peak": peak, "unit": unit,
+                 "frac": achieved / peak, "traffic": TRAFFIC_PER_LAUNCH.get((name, _lib.get_math_mode())),
+                 "traffic_source": TRAFFIC_SOURCE,
+                 "ms_per_launch": avg_ms / launches_per_step, "launches_per_step": launches_per_step,
+                 "peak_source": peaks["source"] + (" (bf16 dense, sustained)" if bound == "tensor" else " (copy)")}
+            if name == "bwd_sample_grad":
+                # what actually bounds this kernel: fp32 vector reductions into the L2-resident grad_input
+                # accumulator; the payload and the sustained rate of such reductions are measured, see SCATTER
+                r["second_bound"] = {"what": "fp32 red.global.add.v4 payload into L2", "payload_bytes": SCATTER["payload_bytes"],
+                                     "measured_rate_gbs": SCATTER["rate_gbs"],
+                                     "floor_ms": SCATTER["payload_bytes"] / SCATTER["rate_gbs"] / 1e6,
+                                     "frac": SCATTER["payload_bytes"] / SCATTER["rate_gbs"] / 1e6 / (avg_ms / launches_per_step),
+                                     "source": SCATTER["source"]}
+            return r
 
         phase_summary = {}
         for n, (c, t) in agg.items():
@@ -478,33 +639,63 @@ def run_gpu_arm(args):
         if candidates:
             dom = max(candidates, key=lambda n: agg[n][1])
             roofline = phase_roofline(dom, agg[dom][1] / args.steps, agg[dom][0] / args.steps)
-        cpu = None
+        mode = _lib.get_math_mode()
+        line.update({
+            "dtype": {"bf16": "bf16", "fp32": "f32"}.get(mode, "bf16x3"), "math_mode": mode,
+            "parity": ("1e-4 of scale vs the fp32 reference (bf16 hi/lo split of both operands, fp32 accumulate)"
+                       if mode in ("auto", "bf16x3") else
+                       "1e-4 of scale (FMA pipe)" if mode == "fp32" else
+                       "output <= 1e-2, gradients <= 2e-2 of scale (stated bound of this mode)"),
+            "gpu_launches": int(launches), "roofline": roofline, "phases": phase_summary, "bf16_mode": bf16_mode,
+        })
         if world == 1 and not args.no_cpu_baseline:
             val, ms, sample, cores = cpu_arm(1, 1, budget_s=40.0)
-            cpu = {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample, "ms_per_sample_step": ms}
-        ref_gpu = None
+            line["cpu_baseline"] = {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample,
+                                    "ms_per_sample_step": ms}
+        else:
+            line["cpu_baseline"] = None
         if world == 1 and not args.no_reference_gpu:
-            ref_gpu = time_reference_cuda_op(host, w, bias, wl, F)
-        line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": {"bf16": "bf16", "fp32": "f32"}.get(_lib.get_math_mode(), "bf16x3"),
-            "math_mode": _lib.get_math_mode(),
-            "parity": ("1e-4 of scale vs the fp32 reference (bf16 hi/lo split of both operands, fp32 accumulate)"
-                       if _lib.get_math_mode() in ("auto", "bf16x3") else
-                       "1e-4 of scale (FMA pipe)" if _lib.get_math_mode() == "fp32" else
-                       "output <= 1e-2, gradients <= 2e-2 of scale (stated bound of this mode)"),
-            "tensor_dtype": "f32", "data": "synthetic",
-            "config": {"workload": wl["name"], "l2": "256 MB buffer written between timed iterations",
-                       "collective": "all-reduce of grad_weight+grad_bias (NCCL)" if world > 1 else "none"},
-            "clips_per_s": wl["B"] * world / (ms_per_step * 1e-3),
-            "e2e": e2e,
-            "gpu_launches": int(launches), "roofline": roofline, "phases": phase_summary, "cpu_baseline": cpu,
-            "clocks": clocks, "reference_cuda_op": ref_gpu, "bf16_mode": bf16_mode,
-        }
-        print(json.dumps(line), flush=True)
+            host = {k: torch.from_numpy(p[k]) for k in keys}
+            line["reference_cuda_op"] = time_reference_cuda_op(host, w, bias, wl, F)
+        if world == 1 and args.secondary:
+            del x, off, mask, gy, dev_in, ins, host_out
+            torch.cuda.empty_cache()
+            line["secondary"] = secondary_summary(args)
+    else:
+        # the reference arm: its kernels are not this library's, so no launch count of ours
+        val, ms, sample, cores = cpu_arm(1, 1, budget_s=40.0) if not args.no_cpu_baseline else (None, None, None, None)
+        line.update({
+            "impl": "reference", "dtype": "f32", "gpu_launches": 0,
+            "what": "unmodified reference dconv_native (im2col + cuBLAS fp32, allow_tf32=False) from baseline/_ref, "
+                    f"{world} rank(s) x {wl['B']} clips, same inputs / flush / events as the other arm",
+            "peak_mem_gb": torch.cuda.max_memory_allocated() / 1e9,
+            "cpu_baseline": None if val is None else {"value": val, "unit": UNIT, "cores": cores, "kind": "port",
+                                                      "sample": sample, "ms_per_sample_step": ms,
+                                                      "note": "the reference has no CPU implementation of this op; this is "
+                                                              "the CPU restatement of its algorithm (oracle/), for context"},
+        })
+    print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def secondary_summary(args):
+    """Forward / backward milliseconds and fraction of the measured peak of the secondary configurations, in the
+    headline line's math mode and in bf16 mode, so that one record carries them (each as `--workload NAME` would
+    print it, fewer steps)."""
+    import d2conv3d_b200
+    out = {}
+    for name in ("c3-xyz", "c4-depthwise", "c4-md", "c5-e1-train"):
+        modes = [args.mode] if name == "c4-depthwise" or args.mode == "bf16" else [args.mode, "bf16"]
+        try:
+            for mode, r in measure_extra_workload(name, modes, steps=5, warmup=3).items():
+                out[f"{name}/{mode}"] = {"fwd_ms": round(r["fwd_ms"], 4), "bwd_ms": round(r["bwd_ms"], 4),
+                                         "fwd_frac": round(r["fwd"]["frac_of_measured_peak"], 4),
+                                         "bwd_frac": round(r["bwd"]["frac_of_measured_peak"], 4), "unit": r["fwd"]["unit"]}
+        except Exception as exc:
+            out[name] = {"error": f"{type(exc).__name__}: {exc}"}
+    d2conv3d_b200.set_math_mode(args.mode)
+    return out
 
 
 EXTRA_WORKLOADS = {
@@ -637,20 +828,20 @@ def decoder_share(total, rank, world):
     return total // world + (1 if rank < total % world else 0)
 
 
-def run_extra_workload(args):
-    """Secondary configurations (not the headline line): prints one JSON line with forward / backward
-    milliseconds from CUDA events, contraction TFLOP/s or GB/s against the measured peaks."""
+def measure_extra_workload(name, modes, steps, warmup):
+    """Secondary configurations: forward / backward milliseconds from CUDA events (median over `steps`), contraction
+    TFLOP/s or GB/s against the measured peaks, for each math mode of `modes` on the same tensors.  Returns
+    {mode: the dict that `--workload NAME --mode MODE` prints}."""
     import torch
 
     import d2conv3d_b200
     from d2conv3d_b200 import _lib, dconv_native, fast_depthwise_conv3d
     from tests._util import make_problem
 
-    wl = EXTRA_WORKLOADS[args.workload]
+    wl = EXTRA_WORKLOADS[name]
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
     _lib.lib()
-    d2conv3d_b200.set_math_mode(args.mode)
     peaks = measured_peaks()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     V = wl["dims"][0] * wl["dims"][1] * wl["dims"][2]
@@ -670,6 +861,7 @@ def run_extra_workload(args):
                          dtype=np.float32, offset_std=wl.get("offset_std", 2.0), field_mode=wl.get("mode"))
         ts = [torch.from_numpy(p[k]).to(dev).requires_grad_() for k in ("x", "geo", "mask", "weight", "bias")]
         gy = torch.from_numpy(p["gy"]).to(dev)
+        del p
         if wl["kind"] == "dyndil":
             fwd = lambda: dconv_native.dyn_dilated_conv3d(*ts, wl["mode"], 1, 1, 1, 1, wl["G"])
         else:
@@ -691,20 +883,28 @@ def run_extra_workload(args):
         torch.cuda.synchronize()
         return e[0].elapsed_time(e[1]), max(e[1].elapsed_time(e[2]), 1e-9)
 
-    for _ in range(max(3, args.warmup)):
-        one()
-    runs = [one() for _ in range(args.steps)]
-    f_ms = statistics.median(r[0] for r in runs)
-    b_ms = statistics.median(r[1] for r in runs)
+    out = {}
     scale = 1e9 if unit == "GB/s" else 1e12
-    _lib.device_status()
-    print(json.dumps({
-        "workload": args.workload, "config": wl, "math_mode": _lib.get_math_mode(), "steps": args.steps,
-        "fwd_ms": f_ms, "bwd_ms": b_ms, "clips_per_s_fwd_bwd": wl["B"] / ((f_ms + b_ms) * 1e-3),
-        "fwd": {"achieved": work_f / (f_ms * 1e-3) / scale, "unit": unit, "frac_of_measured_peak": work_f / (f_ms * 1e-3) / scale / peak},
-        "bwd": {"achieved": work_b / (b_ms * 1e-3) / scale, "unit": unit, "frac_of_measured_peak": work_b / (b_ms * 1e-3) / scale / peak},
-        "note": "times include operand staging and (backward) all gradients; L2 flushed between iterations",
-    }), flush=True)
+    for mode in modes:
+        d2conv3d_b200.set_math_mode(mode)
+        for _ in range(max(3, warmup)):
+            one()
+        runs = [one() for _ in range(steps)]
+        f_ms = statistics.median(r[0] for r in runs)
+        b_ms = statistics.median(r[1] for r in runs)
+        _lib.device_status()
+        out[mode] = {
+            "workload": name, "config": wl, "math_mode": _lib.get_math_mode(), "steps": steps,
+            "fwd_ms": f_ms, "bwd_ms": b_ms, "clips_per_s_fwd_bwd": wl["B"] / ((f_ms + b_ms) * 1e-3),
+            "fwd": {"achieved": work_f / (f_ms * 1e-3) / scale, "unit": unit, "frac_of_measured_peak": work_f / (f_ms * 1e-3) / scale / peak},
+            "bwd": {"achieved": work_b / (b_ms * 1e-3) / scale, "unit": unit, "frac_of_measured_peak": work_b / (b_ms * 1e-3) / scale / peak},
+            "note": "times include operand staging and (backward) all gradients; L2 flushed between iterations",
+        }
+    return out
+
+
+def run_extra_workload(args):
+    print(json.dumps(measure_extra_workload(args.workload, [args.mode], args.steps, args.warmup)[args.mode]), flush=True)
 
 
 def main():
@@ -719,11 +919,13 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-reference-gpu", action="store_true")
+    ap.add_argument("--no-secondary", dest="secondary", action="store_false",
+                    help="skip the `secondary` key (c3-xyz, c4-depthwise, c4-md, c5-e1-train, a few steps each)")
     ap.add_argument("--clips", type=int, default=32, help="c5-decoder: clips of the whole job")
     ap.add_argument("--workload", default="c2", choices=["c2", "c4-block", "c5-decoder"] + sorted(EXTRA_WORKLOADS),
                     help="c2 = the headline line (default); the others print a secondary line for one GPU")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference_arm(args)
     elif args.workload == "c5-decoder":

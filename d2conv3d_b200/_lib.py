@@ -69,6 +69,8 @@ def lib():
         L.d2c_set_max_intermediate_elements.restype = None
         L.d2c_deform_conv3d_fwd.argtypes = [dp] + [vp] * 7 + [sz, vp]
         L.d2c_deform_conv3d_bwd.argtypes = [dp] + [vp] * 11 + [sz, vp]
+        L.d2c_deform_conv3d_bwd_ev.argtypes = [dp] + [vp] * 11 + [sz, vp, vp]
+        L.d2c_dyn_dilated_conv3d_bwd_ev.argtypes = [dp, i32] + [vp] * 11 + [sz, vp, vp]
         L.d2c_deform_conv3d_corners.argtypes = [dp, vp, vp, vp]
         L.d2c_deform_conv1d_fwd.argtypes = [dp] + [vp] * 6 + [vp]
         L.d2c_deform_conv1d_bwd.argtypes = [dp] + [vp] * 11 + [sz, vp]

@@ -1,6 +1,9 @@
 """Builds libd2conv3d.so (the C-ABI CUDA library) in-tree with nvcc for sm_100a.
 
-    python -m d2conv3d_b200.build [--force] [--verbose]
+    python -m d2conv3d_b200.build [--force] [--verbose] [--microbench]
+
+--microbench also builds csrc/microbench/l2_rates.cu into build/l2_rates, a stand-alone program that measures the
+L2 scatter-add and gather rates which bound the sampling kernels (run it on the GPU; it is not part of the library).
 
 The library links only the CUDA runtime (statically); it has no dependency on
 torch or Python.  A GPU is not needed to build.
@@ -30,7 +33,8 @@ def _nvcc():
 def _deps():
     out = [os.path.join(INCLUDE, "d2conv3d.h")]
     for f in os.listdir(CSRC):
-        out.append(os.path.join(CSRC, f))
+        if os.path.isfile(os.path.join(CSRC, f)):
+            out.append(os.path.join(CSRC, f))
     return out
 
 
@@ -66,5 +70,16 @@ def build(force=False, verbose=False):
     return LIB
 
 
+def build_microbench():
+    os.makedirs(OBJ_DIR, exist_ok=True)
+    out = os.path.join(OBJ_DIR, "l2_rates")
+    cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-o", out,
+           os.path.join(CSRC, "microbench", "l2_rates.cu")]
+    subprocess.run(cmd, check=True)
+    return out
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    if "--microbench" in sys.argv:
+        print(build_microbench())

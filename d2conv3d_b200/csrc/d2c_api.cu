@@ -335,6 +335,15 @@ int d2c_deform_conv3d_bwd(const d2c_conv_desc* desc, const void* grad_y, const v
                           const void* offset, const void* mask, const void* w, void* grad_x,
                           void* grad_offset, void* grad_mask, void* grad_w, void* grad_bias,
                           void* workspace, size_t workspace_bytes, d2c_stream_t stream) {
+  return d2c_deform_conv3d_bwd_ev(desc, grad_y, x, offset, mask, w, grad_x, grad_offset, grad_mask, grad_w, grad_bias,
+                                  workspace, workspace_bytes, stream, nullptr);
+}
+
+int d2c_deform_conv3d_bwd_ev(const d2c_conv_desc* desc, const void* grad_y, const void* x,
+                             const void* offset, const void* mask, const void* w, void* grad_x,
+                             void* grad_offset, void* grad_mask, void* grad_w, void* grad_bias,
+                             void* workspace, size_t workspace_bytes, d2c_stream_t stream,
+                             d2c_event_t params_ready) {
   if (!desc || !grad_y || !x || !offset || !w || !grad_x || !grad_offset || !grad_w) return D2C_ERR_NULL;
   if (mask && !grad_mask) return D2C_ERR_NULL;
   Geom g;
@@ -350,23 +359,28 @@ int d2c_deform_conv3d_bwd(const d2c_conv_desc* desc, const void* grad_y, const v
       return D2C_ERR_WORKSPACE;
     return sm100_bwd_offsets(g, mode, cap, (const float*)grad_y, (const float*)x, (const float*)offset,
                              (const float*)mask, (const float*)w, (float*)grad_x, (float*)grad_offset,
-                             (float*)grad_mask, (float*)grad_w, (float*)grad_bias, workspace, st);
+                             (float*)grad_mask, (float*)grad_w, (float*)grad_bias, workspace, st,
+                             (cudaEvent_t)params_ready);
   }
   const size_t need = generic_bwd_workspace(g, desc->dtype, cap);
   if (!ws_ok(workspace, workspace_bytes, need)) return D2C_ERR_WORKSPACE;
   const int nb = bwd_slice_clips(g, cap);
   if (desc->dtype == D2C_F32) {
     OffsetCoords<float> oc{(const float*)offset};
-    return launch_bwd_generic<float, OffsetCoords<float>, false>(
+    rc = launch_bwd_generic<float, OffsetCoords<float>, false>(
         g, oc, (const float*)grad_y, (const float*)x, (const float*)mask, (const float*)w,
         (float*)grad_x, (float*)grad_offset, 0, (float*)grad_mask, (float*)grad_w, (float*)grad_bias,
         (float*)workspace, nb, st);
+  } else {
+    OffsetCoords<double> oc{(const double*)offset};
+    rc = launch_bwd_generic<double, OffsetCoords<double>, false>(
+        g, oc, (const double*)grad_y, (const double*)x, (const double*)mask, (const double*)w,
+        (double*)grad_x, (double*)grad_offset, 0, (double*)grad_mask, (double*)grad_w,
+        (double*)grad_bias, (double*)workspace, nb, st);
   }
-  OffsetCoords<double> oc{(const double*)offset};
-  return launch_bwd_generic<double, OffsetCoords<double>, false>(
-      g, oc, (const double*)grad_y, (const double*)x, (const double*)mask, (const double*)w,
-      (double*)grad_x, (double*)grad_offset, 0, (double*)grad_mask, (double*)grad_w,
-      (double*)grad_bias, (double*)workspace, nb, st);
+  // the CUDA-core kernels produce the parameter gradients last
+  if (rc == D2C_OK && params_ready) D2C_CUDA_TRY(cudaEventRecord((cudaEvent_t)params_ready, st));
+  return rc;
 }
 
 int d2c_deform_conv3d_corners(const d2c_conv_desc* desc, const void* offset, int32_t* corners,
@@ -484,6 +498,15 @@ int d2c_dyn_dilated_conv3d_bwd(const d2c_conv_desc* desc, int field_mode, const 
                                const void* w, void* grad_x, void* grad_size_map, void* grad_mask,
                                void* grad_w, void* grad_bias, void* workspace,
                                size_t workspace_bytes, d2c_stream_t stream) {
+  return d2c_dyn_dilated_conv3d_bwd_ev(desc, field_mode, grad_y, x, size_map, mask, w, grad_x, grad_size_map, grad_mask,
+                                       grad_w, grad_bias, workspace, workspace_bytes, stream, nullptr);
+}
+
+int d2c_dyn_dilated_conv3d_bwd_ev(const d2c_conv_desc* desc, int field_mode, const void* grad_y,
+                                  const void* x, const void* size_map, const void* mask,
+                                  const void* w, void* grad_x, void* grad_size_map, void* grad_mask,
+                                  void* grad_w, void* grad_bias, void* workspace,
+                                  size_t workspace_bytes, d2c_stream_t stream, d2c_event_t params_ready) {
   if (!desc || !grad_y || !x || !size_map || !w || !grad_x || !grad_size_map || !grad_w) return D2C_ERR_NULL;
   if (mask && !grad_mask) return D2C_ERR_NULL;
   Geom g;
@@ -508,19 +531,23 @@ int d2c_dyn_dilated_conv3d_bwd(const d2c_conv_desc* desc, int field_mode, const 
         return D2C_ERR_WORKSPACE;
       return sm100_bwd_field(g, mode, cap, fc, (const float*)grad_y, (const float*)x, (const float*)mask,
                              (const float*)w, (float*)grad_x, (float*)grad_size_map, gs_elems,
-                             (float*)grad_mask, (float*)grad_w, (float*)grad_bias, workspace, st);
+                             (float*)grad_mask, (float*)grad_w, (float*)grad_bias, workspace, st,
+                             (cudaEvent_t)params_ready);
     }
-    return launch_bwd_generic<float, FieldCoords<float>, true>(
+    rc = launch_bwd_generic<float, FieldCoords<float>, true>(
         g, fc, (const float*)grad_y, (const float*)x, (const float*)mask, (const float*)w,
         (float*)grad_x, (float*)grad_size_map, gs_elems, (float*)grad_mask, (float*)grad_w,
         (float*)grad_bias, (float*)workspace, nb, st);
+  } else {
+    FieldCoords<double> fc;
+    if ((rc = make_field_coords<double>(g, field_mode, size_map, &fc))) return rc;
+    rc = launch_bwd_generic<double, FieldCoords<double>, true>(
+        g, fc, (const double*)grad_y, (const double*)x, (const double*)mask, (const double*)w,
+        (double*)grad_x, (double*)grad_size_map, gs_elems, (double*)grad_mask, (double*)grad_w,
+        (double*)grad_bias, (double*)workspace, nb, st);
   }
-  FieldCoords<double> fc;
-  if ((rc = make_field_coords<double>(g, field_mode, size_map, &fc))) return rc;
-  return launch_bwd_generic<double, FieldCoords<double>, true>(
-      g, fc, (const double*)grad_y, (const double*)x, (const double*)mask, (const double*)w,
-      (double*)grad_x, (double*)grad_size_map, gs_elems, (double*)grad_mask, (double*)grad_w,
-      (double*)grad_bias, (double*)workspace, nb, st);
+  if (rc == D2C_OK && params_ready) D2C_CUDA_TRY(cudaEventRecord((cudaEvent_t)params_ready, st));
+  return rc;
 }
 
 int d2c_dyn_dilated_conv3d_corners(const d2c_conv_desc* desc, int field_mode, const void* size_map,

@@ -48,7 +48,7 @@ __device__ __forceinline__ float split_part(float f, bool lo) {
 
 __global__ void __launch_bounds__(256)
 stage_gy_img_kernel(int Cout, int V, int tiles_per_clip, int b0, int x3, const float* __restrict__ gy,
-                    uint8_t* __restrict__ img, float* __restrict__ grad_bias) {
+                    uint8_t* __restrict__ img) {
   __shared__ float tile[64][129];
   const int tile_id = blockIdx.x, kb = blockIdx.y, KB = gridDim.y;
   const int bl = tile_id / tiles_per_clip, v0 = (tile_id % tiles_per_clip) * kBM;
@@ -59,13 +59,6 @@ stage_gy_img_kernel(int Cout, int V, int tiles_per_clip, int b0, int x3, const f
     tile[co][r] = (v < V) ? __ldg(gy + ((long long)b * Cout + kb * nco + co) * V + v) : 0.f;
   }
   __syncthreads();
-  // grad_bias = grad_out summed over clips and voxels (reference dconv3d_gpu.cu:1329): this kernel reads every
-  // element of grad_out exactly once, so each block adds its 128-voxel partial sums (grad_bias zeroed before)
-  if (grad_bias && (int)threadIdx.x < nco) {
-    float sum = 0.f;
-    for (int r = 0; r < 128; ++r) sum += tile[threadIdx.x][(r + threadIdx.x) & 127];   // skewed: no bank conflicts
-    atomicAdd(grad_bias + kb * nco + threadIdx.x, sum);
-  }
   uint8_t* dst = img + ((long long)tile_id * KB + kb) * kABlockBytes;
   for (int e = threadIdx.x; e < 128 * 8; e += 256) {
     const int r = e >> 3, j = e & 7;
@@ -550,7 +543,7 @@ bool make_bwd_plan(const Geom& g, unsigned long long cap, bool x3, BwdPlan* pl) 
 template <typename Coords, bool FieldOut>
 int run_bwd(const Geom& g, bool x3, const Coords& coords, unsigned long long cap, const float* gy, const float* x,
             const float* mask, const float* w, float* grad_x, float* grad_coord, size_t grad_coord_elems,
-            float* grad_mask, float* grad_w, float* grad_bias, void* ws, cudaStream_t st) {
+            float* grad_mask, float* grad_w, float* grad_bias, void* ws, cudaStream_t st, cudaEvent_t params_ready) {
   BwdPlan pl;
   if (!make_bwd_plan(g, cap, x3, &pl)) return D2C_ERR_MODE;
   uint8_t* wsp = reinterpret_cast<uint8_t*>(ws);
@@ -591,11 +584,17 @@ int run_bwd(const Geom& g, bool x3, const Coords& coords, unsigned long long cap
     else
       stage_input_cl_f16_kernel<<<grid, 256, 0, st>>>(g.Cin, g.Vin, x, reinterpret_cast<__half*>(x_cl));
     D2C_LAUNCH_CHECK();
-    stage_wt_img_kernel<<<dim3((unsigned)pl.KBT, (unsigned)g.Cin), 64, 64 * g.K * sizeof(float), st>>>(
-        g.Cout, g.Cin, g.K, pl.pairg ? 64 : g.cpg, pl.nh, x3 ? 1 : 0, w, wt_img);
-    D2C_LAUNCH_CHECK();
     if ((rc = launch_sample_records(g, coords, mask, recs, gat, st, x3))) return rc;
   }
+  // The parameter gradients come first: the weight gradient (tensor-core implicit GEMM over the re-sampled tile)
+  // needs only the records and the staged input, and its grad_out staging pass also sums grad_bias.  A caller that
+  // reduces them across GPUs can start as soon as `params_ready` fires, under the data-side kernels below.
+  if ((rc = sm100_dw(g, x3, gy, x_cl, gat, grad_w, grad_bias, dw_ws, st))) return rc;
+  if (params_ready) D2C_CUDA_TRY(cudaEventRecord(params_ready, st));
+  prof_mark(st, "bwd_stage_weights");
+  stage_wt_img_kernel<<<dim3((unsigned)pl.KBT, (unsigned)g.Cin), 64, 64 * g.K * sizeof(float), st>>>(
+      g.Cout, g.Cin, g.K, pl.pairg ? 64 : g.cpg, pl.nh, x3 ? 1 : 0, w, wt_img);
+  D2C_LAUNCH_CHECK();
   D2C_CUDA_TRY(cudaFuncSetAttribute(dcol_sm100_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes));
   D2C_CUDA_TRY(cudaFuncSetAttribute(dcol_sm100_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes));
 
@@ -604,7 +603,7 @@ int run_bwd(const Geom& g, bool x3, const Coords& coords, unsigned long long cap
     const int n_tiles = nbc * pl.tiles_per_clip;
     prof_mark(st, "bwd_stage_grad_out");
     stage_gy_img_kernel<<<dim3((unsigned)n_tiles, (unsigned)pl.KBT), 256, 0, st>>>(g.Cout, g.V, pl.tiles_per_clip, b0,
-                                                                                  x3 ? 1 : 0, gy, gy_img, grad_bias);
+                                                                                  x3 ? 1 : 0, gy, gy_img);
     D2C_LAUNCH_CHECK();
     DcolParams p;
     p.gy_img = gy_img; p.wt_img = wt_img; p.dcol = dcol;
@@ -655,8 +654,6 @@ int run_bwd(const Geom& g, bool x3, const Coords& coords, unsigned long long cap
     unstage_grad_input_kernel<<<grid, 256, 0, st>>>(g.Cin, g.Vin, gx_cl, grad_x);
     D2C_LAUNCH_CHECK();
   }
-  // weight gradient: tensor-core implicit GEMM over the re-sampled tile
-  if ((rc = sm100_dw(g, x3, gy, x_cl, gat, grad_w, dw_ws, st))) return rc;
   prof_mark(st, nullptr);
   return D2C_OK;
 }
@@ -689,18 +686,18 @@ size_t sm100_bwd_workspace(const Geom& g, int dtype, int math_mode, unsigned lon
 
 int sm100_bwd_offsets(const Geom& g, int math_mode, unsigned long long cap, const float* gy, const float* x, const float* offset,
                       const float* mask, const float* w, float* grad_x, float* grad_offset, float* grad_mask,
-                      float* grad_w, float* grad_bias, void* ws, cudaStream_t st) {
+                      float* grad_w, float* grad_bias, void* ws, cudaStream_t st, cudaEvent_t params_ready) {
   OffsetCoords<float> oc{offset};
   return run_bwd<OffsetCoords<float>, false>(g, bwd_use_x3(g, math_mode, cap), oc, cap, gy, x, mask, w, grad_x, grad_offset, 0, grad_mask, grad_w,
-                                             grad_bias, ws, st);
+                                             grad_bias, ws, st, params_ready);
 }
 
 int sm100_bwd_field(const Geom& g, int math_mode, unsigned long long cap, const FieldCoords<float>& fc, const float* gy,
                     const float* x, const float* mask, const float* w, float* grad_x, float* grad_size_map,
                     size_t grad_size_elems, float* grad_mask, float* grad_w, float* grad_bias, void* ws,
-                    cudaStream_t st) {
+                    cudaStream_t st, cudaEvent_t params_ready) {
   return run_bwd<FieldCoords<float>, true>(g, bwd_use_x3(g, math_mode, cap), fc, cap, gy, x, mask, w, grad_x, grad_size_map, grad_size_elems,
-                                           grad_mask, grad_w, grad_bias, ws, st);
+                                           grad_mask, grad_w, grad_bias, ws, st, params_ready);
 }
 
 }  // namespace d2c

@@ -54,20 +54,30 @@ struct DwParams {
 // (64 voxels, bf16), chunks XOR-swizzled by (row & 7).  Voxels past the clip are zero.
 // x3 = 1 (fp32-parity mode): every (tile, voxel block) holds two image groups, hi = bf16(gy) then
 // lo = bf16(gy - hi), NCH chunks each.
+// grad_bias (nullable) = grad_out summed over clips and voxels (reference dconv3d_gpu.cu:1329): this kernel reads
+// every element of grad_out exactly once, so the 16 threads that share a row add their 128-voxel partial sum with
+// one atomic (grad_bias zeroed before).
 __global__ void __launch_bounds__(256)
 stage_gy_kmajor_kernel(int Cout, int V, int tiles_per_clip, int NCH, int x3, const float* __restrict__ gy,
-                       uint8_t* __restrict__ img) {
+                       uint8_t* __restrict__ img, float* __restrict__ grad_bias) {
   const int tile = blockIdx.x, coblk = blockIdx.y;        // coblk: 64 rows of co
   const int b = tile / tiles_per_clip, v0 = (tile % tiles_per_clip) * kBM;
-  for (int e = threadIdx.x; e < 64 * 16; e += 256) {
+  for (int e = threadIdx.x; e < 64 * 16; e += 256) {      // Cout is a multiple of 64: no thread leaves the loop early
     const int rl = e >> 4, q = e & 15;                    // row within block, 8-voxel chunk (0..15)
     const int co = coblk * 64 + rl;
-    if (co >= Cout) continue;
     const int v = v0 + q * 8;
     float f[8];
     const float* src = gy + ((long long)b * Cout + co) * V;
 #pragma unroll
     for (int i = 0; i < 8; ++i) f[i] = (v + i < V) ? __ldg(src + v + i) : 0.f;
+    if (grad_bias) {
+      float sum = ((f[0] + f[1]) + (f[2] + f[3])) + ((f[4] + f[5]) + (f[6] + f[7]));
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 8);
+      if (q == 0) atomicAdd(grad_bias + co, sum);
+    }
     uint4 o;
     o.x = ptx::pack_bf16x2(f[0], f[1]); o.y = ptx::pack_bf16x2(f[2], f[3]);
     o.z = ptx::pack_bf16x2(f[4], f[5]); o.w = ptx::pack_bf16x2(f[6], f[7]);
@@ -405,8 +415,8 @@ size_t sm100_dw_workspace(const Geom& g, bool x3) {
   return dp.gyk_bytes + dp.dws_bytes;
 }
 
-int sm100_dw(const Geom& g, bool x3, const float* gy, const void* x_cl, const void* recs, float* grad_w, void* ws,
-             cudaStream_t st) {
+int sm100_dw(const Geom& g, bool x3, const float* gy, const void* x_cl, const void* recs, float* grad_w,
+             float* grad_bias, void* ws, cudaStream_t st) {
   int sm_count = 0;
   {
     const int rc = device_sm_count(&sm_count);
@@ -421,7 +431,7 @@ int sm100_dw(const Geom& g, bool x3, const float* gy, const void* x_cl, const vo
   prof_mark(st, "bwd_dw_stage");
   D2C_CUDA_TRY(cudaMemsetAsync(dws, 0, (size_t)dp.S * 64 * g.Cout * 4, st));
   stage_gy_kmajor_kernel<<<dim3((unsigned)dp.n_tiles, (unsigned)((g.Cout + 63) / 64)), 256, 0, st>>>(
-      g.Cout, g.V, dp.tiles_per_clip, dp.NCH, x3 ? 1 : 0, gy, gyk);
+      g.Cout, g.V, dp.tiles_per_clip, dp.NCH, x3 ? 1 : 0, gy, gyk, grad_bias);
   D2C_LAUNCH_CHECK();
 
   DwParams p;

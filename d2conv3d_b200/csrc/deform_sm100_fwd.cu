@@ -344,6 +344,7 @@ fwd_sm100_kernel(const FwdParams p) {
   }
 }
 
+#include "deform_sm100_fwd_v2.cuh"
 #include "deform_sm100_fwd_pair.cuh"
 
 // ---- staging kernels -------------------------------------------------------------------------
@@ -549,7 +550,16 @@ int run_fwd(const Geom& g, int math_mode, const Coords& coords, const float* x, 
     return D2C_OK;
   }
   prof_mark(st, "fwd_sm100_fused");
-  if (x3) {
+  static int fwd_v = -1;
+  if (fwd_v < 0) {
+    const char* e = getenv("D2C_FWD_V");
+    fwd_v = (e && e[0] == '1') ? 1 : 2;
+  }
+  if (fwd_v == 2) {
+    auto kern = x3 ? fwd_sm100_v2_kernel<1, 0> : (pl.dual ? fwd_sm100_v2_kernel<0, 1> : fwd_sm100_v2_kernel<0, 0>);
+    D2C_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes));
+    kern<<<(unsigned)grid, kThreads2, pl.smem_bytes, st>>>(p);
+  } else if (x3) {
     D2C_CUDA_TRY(cudaFuncSetAttribute(fwd_sm100_kernel<1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes));
     fwd_sm100_kernel<1, 0><<<(unsigned)grid, kThreads, pl.smem_bytes, st>>>(p);
   } else if (pl.dual) {

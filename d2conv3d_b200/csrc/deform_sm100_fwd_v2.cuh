@@ -1,0 +1,294 @@
+// Second generation of the single-CTA forward kernel.  Same tiles, rings, barriers and MMA issue as
+// fwd_sm100_kernel above; what differs is the producer side:
+//   * warp roles are aligned to warpgroups (4 epilogue warps | MMA, weight loader, record loader, one idle warp |
+//     16 gather warps) so that `setmaxnreg` can move registers from the light roles to the gather warps;
+//   * the gather loop is software-pipelined at row granularity (see the producer branch).
+constexpr int kThreads2 = 24 * 32;
+constexpr int kMmaWarp2 = 4, kLoadWarp2 = 5, kRecWarp2 = 6, kGatherWarp02 = 8;
+
+// kX3 = 0: math mode bf16 (a unit is 64 channels of one tap, one bf16 operand pair).
+// kX3 = 1: math mode bf16x3, the fp32-parity mode: a unit is 32 channels; the A row holds [hi(32) | lo(32)] of
+//          the fp32 blend, the weight row [hi(32) | lo(32)] of the fp32 weight, and the issuer forms
+//          a_hi*b_hi + a_lo*b_hi + a_hi*b_lo from the 16-channel K sub-blocks of the same two tiles.
+// kDual = 1 (single-pass mode only): 32 channels per offset group, a 64-channel unit spans two groups.
+template <int kX3, int kDual>
+__global__ void __launch_bounds__(kThreads2, 1)
+fwd_sm100_v2_kernel(const FwdParams p) {
+  constexpr int kUnitCh = kX3 ? 32 : 64;
+  constexpr int kRStage = (1 + kDual) * kRecBytes + 16;      // record set(s) + unit header
+  constexpr int hdr_off = (1 + kDual) * kRecBytes;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = ptx::smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - raw);
+  const int rec_off = kAStages * kAStageBytes + p.b_stages * p.b_stage_bytes;
+  const int bar_off = rec_off + kRStages * kRStage;
+  const uint32_t a_base = base, b_base = base + kAStages * kAStageBytes, rec_base = base + rec_off,
+                 bar_base = base + bar_off;
+  auto a_full = [&](int s) { return bar_base + 8u * s; };
+  auto a_empty = [&](int s) { return bar_base + 8u * (kAStages + s); };
+  auto b_full = [&](int s) { return bar_base + 8u * (2 * kAStages + s); };
+  auto b_empty = [&](int s) { return bar_base + 8u * (2 * kAStages + 4 + s); };
+  const uint32_t acc_full = bar_base + 8u * (2 * kAStages + 8);
+  const uint32_t acc_empty = bar_base + 8u * (2 * kAStages + 9);
+  auto r_full = [&](int s) { return bar_base + 8u * (2 * kAStages + 11 + s); };
+  auto r_empty = [&](int s) { return bar_base + 8u * (2 * kAStages + 11 + kRStages + s); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + bar_off + 8 * (2 * kAStages + 10));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + bar_off + 8 * (2 * kAStages + 10) + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const Geom& g = p.g;
+  long long u_beg, u_end;
+  cta_unit_range(p.n_units, u_beg, u_end);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kAStages; ++s) { ptx::mbar_init(a_full(s), kGatherWarps); ptx::mbar_init(a_empty(s), 1); }
+    for (int s = 0; s < p.b_stages; ++s) { ptx::mbar_init(b_full(s), 1); ptx::mbar_init(b_empty(s), 1); }
+    for (int s = 0; s < kRStages; ++s) { ptx::mbar_init(r_full(s), 1); ptx::mbar_init(r_empty(s), kGatherWarps); }
+    ptx::mbar_init(acc_full, 1);
+    ptx::mbar_init(acc_empty, kEpiWarps);
+    *abort_flag = 0;
+    ptx::fence_mbar_init();
+  }
+  if (warp == 0) {
+    __syncwarp();
+    ptx::tmem_alloc(ptx::smem_u32((const void*)tmem_slot), (uint32_t)p.tmem_cols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // Register re-balancing between the roles (warpgroup-wide): the epilogue and service warps give registers back,
+  // the gather warps take them, so that a gather thread can hold the corner loads of TWO rows in flight while it
+  // blends -- the loads of the next row (or of the next unit's first row) are issued before the current row is
+  // consumed.  7168 + 5120 + 53248 = 65536 registers.
+  if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+  } else if (warp < 8) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
+  }
+
+  if (warp < kEpiWarps) {
+    // ===================== epilogue: one pass per tile segment =====================
+    int seg = 0;
+    for (long long u = u_beg; u < u_end; ++seg) {
+      const int tile = (int)(u / p.S), s_beg = (int)(u % p.S);
+      const int s_end = (int)min((long long)p.S, s_beg + (u_end - u));
+      u += s_end - s_beg;
+      const bool whole = (s_beg == 0 && s_end == p.S);
+      const int b = tile / p.tiles_per_clip, v0 = (tile % p.tiles_per_clip) * kBM;
+      if (!ptx::mbar_wait(acc_full, seg & 1, abort_flag, 2000)) break;
+      ptx::tc_fence_after();
+      const int v = v0 + warp * 32 + lane;
+      float* yb = p.y + (long long)b * g.Cout * g.V + v;
+      for (int c0 = 0; c0 < p.N; c0 += 32) {
+        uint32_t r[32];
+        ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);
+        ptx::tmem_ld_wait();
+        if (v < g.V) {
+          if (whole) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float bb = p.bias ? __ldg(p.bias + c0 + j) : 0.f;
+              yb[(long long)(c0 + j) * g.V] = __uint_as_float(r[j]) + bb;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float bb = (p.bias && s_beg == 0) ? __ldg(p.bias + c0 + j) : 0.f;
+              atomicAdd(yb + (long long)(c0 + j) * g.V, __uint_as_float(r[j]) + bb);
+            }
+          }
+        }
+      }
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(acc_empty);
+    }
+  } else if (warp == kMmaWarp2) {
+    // ===================== MMA issuer =====================
+    if (lane == 0) {
+      int seg = 0;
+      uint32_t k = 0;           // units consumed so far (A and B rings advance together)
+      bool ok = true;
+      for (long long u = u_beg; ok && u < u_end; ++seg) {
+        const int s_beg = (int)(u % p.S);
+        const int s_end = (int)min((long long)p.S, s_beg + (u_end - u));
+        u += s_end - s_beg;
+        if (!ptx::mbar_wait(acc_empty, (seg & 1) ^ 1, abort_flag)) break;
+        ptx::tc_fence_after();
+        for (int s = s_beg; s < s_end; ++s, ++k) {
+          const int sa = k % kAStages, sb = k % p.b_stages;
+          if (!ptx::mbar_wait(a_full(sa), (k / kAStages) & 1, abort_flag)) { ok = false; break; }
+          if (!ptx::mbar_wait(b_full(sb), (k / p.b_stages) & 1, abort_flag)) { ok = false; break; }
+          ptx::tc_fence_after();
+          const uint64_t adesc = ptx::umma_desc_kmajor_sw128(a_base + sa * kAStageBytes);
+          // K sub-blocks (16 channels = 32 bytes) of the A and B rows that meet in each MMA
+          constexpr int kSteps = kX3 ? 6 : 4;
+          constexpr int ka_[6] = {0, 1, kX3 ? 2 : 2, kX3 ? 3 : 3, 0, 1};   // bf16: (k,k); x3: hi*hi, lo*hi, hi*lo
+          constexpr int kb_[6] = {0, 1, kX3 ? 0 : 2, kX3 ? 1 : 3, 2, 3};
+#pragma unroll
+          for (int kk = 0; kk < kSteps; ++kk) {
+            for (int n0 = 0; n0 < p.N; n0 += 256) {
+              const int nc = min(256, p.N - n0);
+              const uint64_t bdesc = ptx::umma_desc_kmajor_sw128(b_base + sb * p.b_stage_bytes + n0 * 128);
+              ptx::umma_bf16(tmem_base + (uint32_t)n0, adesc + (uint64_t)(2 * ka_[kk]),
+                             bdesc + (uint64_t)(2 * kb_[kk]), ptx::umma_idesc_bf16_f32(kBM, nc),
+                             (s > s_beg || kk > 0) ? 1u : 0u);
+            }
+          }
+          ptx::umma_commit(a_empty(sa));
+          ptx::umma_commit(b_empty(sb));
+        }
+        if (ok) ptx::umma_commit(acc_full);
+      }
+    }
+  } else if (warp == kLoadWarp2) {
+    // ===================== weight-slice loader =====================
+    if (lane == 0) {
+      uint32_t k = 0;
+      for (long long u = u_beg; u < u_end; ++u, ++k) {
+        const int s = (int)(u % p.S), sb = k % p.b_stages;
+        if (!ptx::mbar_wait(b_empty(sb), ((k / p.b_stages) & 1) ^ 1, abort_flag, 200)) break;
+        ptx::mbar_arrive_expect_tx(b_full(sb), (uint32_t)p.b_stage_bytes);
+        const uint8_t* src = p.w_sw + (long long)s * p.b_stage_bytes;
+        const uint32_t dst = b_base + sb * p.b_stage_bytes;
+        for (int off = 0; off < p.b_stage_bytes; off += 32768)
+          ptx::bulk_g2s(dst + off, src + off, (uint32_t)min(32768, p.b_stage_bytes - off), b_full(sb));
+      }
+      // never leave with a bulk copy in flight: wait (bounded) for the last copies issued
+      const uint32_t issued = k;
+      for (uint32_t q = (issued > (uint32_t)p.b_stages ? issued - p.b_stages : 0); q < issued; ++q) {
+        const long long t0 = clock64();
+        while (!ptx::mbar_try_wait(b_full(q % p.b_stages), (q / p.b_stages) & 1))
+          if (clock64() - t0 > ptx::kWaitBudgetCycles) break;
+      }
+    }
+  } else if (warp == kRecWarp2) {
+    // ===================== gather-record loader =====================
+    // The records of a unit's rows are one contiguous run of the [B][G][K][V] stream: one bulk copy per unit,
+    // kRStages units ahead of the gather warps, so the producers read them from shared memory.
+    if (lane == 0) {
+      uint32_t k = 0;
+      for (long long u = u_beg; u < u_end; ++u, ++k) {
+        const int tile = (int)(u / p.S), s = (int)(u % p.S);
+        const int b = tile / p.tiles_per_clip, v0 = (tile % p.tiles_per_clip) * kBM;
+        const int gt = s / p.nh, tap = gt % g.K, grp = gt / g.K;      // dual: grp is the index of a group PAIR
+        const int sr = k % kRStages;
+        if (!ptx::mbar_wait(r_empty(sr), ((k / kRStages) & 1) ^ 1, abort_flag, 200)) break;
+        const int rows = min(kBM, g.V - v0), h = s % p.nh;
+        // unit header for the gather warps (no index arithmetic there); ordered before their reads by the
+        // release of the arrive below and the acquire of their wait
+        uint8_t* hdr = base_ptr + rec_off + sr * kRStage + hdr_off;
+        *reinterpret_cast<long long*>(hdr) =
+            (long long)b * g.Vin * g.Cin + grp * (kDual ? 2 * g.cpg : g.cpg) + h * kUnitCh;
+        *reinterpret_cast<int*>(hdr + 8) = rows;
+        const uint32_t bytes = (uint32_t)rows * 48u;
+        ptx::mbar_arrive_expect_tx(r_full(sr), bytes * (uint32_t)(1 + kDual));
+#pragma unroll
+        for (int set = 0; set <= kDual; ++set) {
+          const int og = kDual ? 2 * grp + set : grp;      // offset group whose records fill this set
+          ptx::bulk_g2s(rec_base + sr * kRStage + set * kRecBytes,
+                        p.recs + 3 * ((((long long)b * g.G + og) * g.K + tap) * g.V + v0), bytes, r_full(sr));
+        }
+      }
+      const uint32_t issued = k;
+      for (uint32_t q = (issued > (uint32_t)kRStages ? issued - kRStages : 0); q < issued; ++q) {
+        const long long t0 = clock64();
+        while (!ptx::mbar_try_wait(r_full(q % kRStages), (q / kRStages) & 1))
+          if (clock64() - t0 > ptx::kWaitBudgetCycles) break;
+      }
+    }
+  } else if (warp >= kGatherWarp02) {
+    // ===================== gather producers (software-pipelined) =====================
+    // A thread owns rows r0 and r0 + 64 of every unit, chunk j (16 B of the 128-byte A row).  Items are taken in
+    // the order (unit k, row 0), (unit k, row 1), (unit k+1, row 0) ...; the 8 corner loads of item t+1 are
+    // issued before item t is blended, so 8 loads are always in flight under the blend and 16 while it waits.
+    const int t = threadIdx.x - kGatherWarp02 * 32;
+    const int j = t & 7;             // 16-byte chunk (8 channels) of the 128-byte row
+    const int r0 = t >> 3;           // rows r0, r0 + kRowStride
+    const uint32_t n_my_units = (uint32_t)(u_end - u_beg);
+    bool ok = true;
+
+    auto issue = [&](uint32_t k, int i, uint4 (&c)[8]) {
+      const uint8_t* rec_base_ptr = base_ptr + rec_off + (k % kRStages) * kRStage;
+      const long long xoff = *reinterpret_cast<const long long*>(rec_base_ptr + hdr_off);
+      const int rows = *reinterpret_cast<const int*>(rec_base_ptr + hdr_off + 8);
+      // dual: 16-byte chunks 4-7 of a row (channels 32-63 of the unit) belong to the second offset group
+      const uint8_t* rec_stage = rec_base_ptr + ((kDual && j >= 4) ? kRecBytes : 0);
+      const int r = r0 + kRowStride * i;
+      uint2 head = make_uint2(0u, 0u);
+      if (r < rows) head = *reinterpret_cast<const uint2*>(rec_stage + r * 48);
+      if constexpr (kX3)
+        load_corners_f32(reinterpret_cast<const float*>(p.x_cl) + xoff + j * 4, p.cs, head.x, head.y, c);
+      else
+        load_corners(reinterpret_cast<const __half*>(p.x_cl) + xoff + j * 8, p.cs, head.x, head.y, c);
+    };
+    auto consume = [&](uint32_t k, int i, const uint4 (&c)[8]) {
+      const uint8_t* rec_base_ptr = base_ptr + rec_off + (k % kRStages) * kRStage;
+      const int rows = *reinterpret_cast<const int*>(rec_base_ptr + hdr_off + 8);
+      const uint8_t* rec_stage = rec_base_ptr + ((kDual && j >= 4) ? kRecBytes : 0);
+      const uint32_t stage = a_base + (k % kAStages) * kAStageBytes;
+      const int r = r0 + kRowStride * i;
+      if constexpr (kX3) {
+        float w[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};   // rows past the clip end: stage bytes are stale
+        if (r < rows) {
+          const uint2 w01 = *reinterpret_cast<const uint2*>(rec_stage + r * 48 + 8);
+          const uint4 w25 = *reinterpret_cast<const uint4*>(rec_stage + r * 48 + 16);
+          const uint2 w67 = *reinterpret_cast<const uint2*>(rec_stage + r * 48 + 32);
+          w[0] = __uint_as_float(w01.x); w[1] = __uint_as_float(w01.y);
+          w[2] = __uint_as_float(w25.x); w[3] = __uint_as_float(w25.y);
+          w[4] = __uint_as_float(w25.z); w[5] = __uint_as_float(w25.w);
+          w[6] = __uint_as_float(w67.x); w[7] = __uint_as_float(w67.y);
+        }
+        // item j = channels 4j..4j+3: hi in 16-byte chunk j/2 (half j&1), lo in chunk 4 + j/2
+        const uint32_t row_base = stage + (uint32_t)((r >> 3) * 1024 + (r & 7) * 128) + (uint32_t)((j & 1) * 8);
+        blend_split_store(c, w, row_base + ((((j >> 1)) ^ (r & 7)) << 4), row_base + (((4 + (j >> 1)) ^ (r & 7)) << 4));
+      } else {
+        uint4 w03 = make_uint4(0u, 0u, 0u, 0u), w47 = w03;       // rows past the clip end: stage bytes are stale
+        if (r < rows) {
+          w03 = *reinterpret_cast<const uint4*>(rec_stage + r * 48 + 16);
+          w47 = *reinterpret_cast<const uint4*>(rec_stage + r * 48 + 32);
+        }
+        blend_store(c, w03, w47, stage + (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((j ^ (r & 7)) << 4)));
+      }
+    };
+
+    uint4 c0[8], c1[8];
+    if (n_my_units > 0) {
+      ok = ptx::mbar_wait(r_full(0), 0, abort_flag);
+      if (ok) issue(0, 0, c0);
+    }
+    for (uint32_t k = 0; ok && k < n_my_units; ++k) {
+      const int sr = k % kRStages, sa = k % kAStages;
+      issue(k, 1, c1);
+      if (!ptx::mbar_wait(a_empty(sa), ((k / kAStages) & 1) ^ 1, abort_flag)) break;
+      consume(k, 0, c0);
+      if (k + 1 < n_my_units) {
+        if (!ptx::mbar_wait(r_full((k + 1) % kRStages), ((k + 1) / kRStages) & 1, abort_flag)) break;
+        issue(k + 1, 0, c0);
+      }
+      consume(k, 1, c1);
+      ptx::fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        ptx::mbar_arrive(a_full(sa));
+        ptx::mbar_arrive(r_empty(sr));
+      }
+    }
+  }
+
+  // ---- teardown ----
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag) ptx::report_device_timeout();
+  if (warp == 0) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+  }
+}
+

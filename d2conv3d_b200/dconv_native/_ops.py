@@ -13,6 +13,26 @@ from torch.autograd.function import once_differentiable
 from .. import _lib
 
 
+class _BackwardState:
+    """Event recorded by the most recent deformable backward once grad_weight and grad_bias were final."""
+    params_ready = None
+
+
+def params_ready_event():
+    """The torch.cuda.Event that the most recent `deform_conv3d` / `dyn_dilated_conv3d` backward of this process
+    recorded as soon as its parameter gradients (grad_weight, grad_bias) were final -- on the tensor-core tier
+    before the data-side gradients are computed.  A data-parallel trainer makes a side stream wait for it and
+    all-reduces the parameter gradients there (d2conv3d_b200.sharding.all_reduce_param_grads_overlapped), which
+    hides the collective under the rest of the backward.  None before the first backward."""
+    return _BackwardState.params_ready
+
+
+def _new_event(stream):
+    ev = torch.cuda.Event()
+    ev.record(stream)                  # creates the underlying CUDA event; the library records it again later
+    return ev
+
+
 def _require(cond, expr):
     # TORCH_CHECK(expr) of the reference raises RuntimeError("Expected <expr> to be true ...")
     if not cond:
@@ -88,10 +108,12 @@ class _DeformConv3dFunction(torch.autograd.Function):
             gmask = None if alpha is None else torch.empty_like(alpha)
             gbias = None if bias is None else torch.empty_like(bias)
             ws, ws_bytes = _lib.workspace(_lib.OP_DEFORM_BWD, desc, input.device)
-            _lib.check(L.d2c_deform_conv3d_bwd(
+            ev = _new_event(torch.cuda.current_stream(input.device))
+            _lib.check(L.d2c_deform_conv3d_bwd_ev(
                 ctypes.byref(desc), _lib.ptr(grad_out), _lib.ptr(input), _lib.ptr(offset), _lib.ptr(alpha),
                 _lib.ptr(weight), _lib.ptr(gx), _lib.ptr(goff), _lib.ptr(gmask), _lib.ptr(gw), _lib.ptr(gbias),
-                _lib.ptr(ws), ws_bytes, _lib.stream_of(input)), "deform_conv3d backward")
+                _lib.ptr(ws), ws_bytes, _lib.stream_of(input), ctypes.c_void_p(ev.cuda_event)), "deform_conv3d backward")
+            _BackwardState.params_ready = ev
         return (gx, goff, gmask, gw, gbias) + (None,) * 11
 
 
@@ -143,11 +165,13 @@ class _DynDilatedConv3dFunction(torch.autograd.Function):
             gmask = None if alpha is None else torch.empty_like(alpha)
             gbias = None if bias is None else torch.empty_like(bias)
             ws, ws_bytes = _lib.workspace(_lib.OP_DYNDIL_BWD, desc, input.device)
-            _lib.check(L.d2c_dyn_dilated_conv3d_bwd(
+            ev = _new_event(torch.cuda.current_stream(input.device))
+            _lib.check(L.d2c_dyn_dilated_conv3d_bwd_ev(
                 ctypes.byref(desc), _lib.FIELD_MODES[ctx.mode], _lib.ptr(grad_out), _lib.ptr(input),
                 _lib.ptr(size_map), _lib.ptr(alpha), _lib.ptr(weight), _lib.ptr(gx), _lib.ptr(gs), _lib.ptr(gmask),
-                _lib.ptr(gw), _lib.ptr(gbias), _lib.ptr(ws), ws_bytes, _lib.stream_of(input)),
-                "dyn_dilated_conv3d backward")
+                _lib.ptr(gw), _lib.ptr(gbias), _lib.ptr(ws), ws_bytes, _lib.stream_of(input),
+                ctypes.c_void_p(ev.cuda_event)), "dyn_dilated_conv3d backward")
+            _BackwardState.params_ready = ev
         return (gx, gs, gmask, gw, gbias) + (None,) * 6
 
 

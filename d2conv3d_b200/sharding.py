@@ -69,6 +69,33 @@ def all_reduce_param_grads(grads, group=None, async_op=False):
     return work, finish
 
 
+def all_reduce_param_grads_overlapped(grads, ready_event, side_stream, group=None):
+    """The DDP-style overlap for this layer: `side_stream` waits for `ready_event` (the event the library records
+    when grad_weight / grad_bias are final, `dconv_native._ops.params_ready_event()`), the flat-bucket all-reduce
+    of all_reduce_param_grads is issued from there, and the stream that was current at the call -- on which the
+    rest of the backward is still running -- is NOT made to wait.  Returns `finish`: call it on the compute stream
+    before the gradients are used (it makes the current stream wait for the collective and unpacks the bucket).
+    Single rank or no process group: returns a no-op."""
+    live = [g for g in grads if g is not None]
+    if not live or not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return lambda: None
+    if ready_event is not None:
+        side_stream.wait_event(ready_event)
+    else:
+        side_stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side_stream):
+        work, finish_side = all_reduce_param_grads(live, group=group, async_op=True)
+        for g in live:
+            g.record_stream(side_stream)
+
+    def finish():
+        with torch.cuda.stream(side_stream):
+            finish_side()
+        torch.cuda.current_stream().wait_stream(side_stream)
+
+    return finish
+
+
 def broadcast_params(params, src=0, group=None):
     """Replicates weights / bias from `src` at start-up."""
     if not dist.is_initialized() or dist.get_world_size(group) == 1:

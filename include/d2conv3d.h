@@ -30,6 +30,7 @@ extern "C" {
 
 /* Opaque to this header so that C callers need no CUDA headers. */
 typedef void* d2c_stream_t; /* a cudaStream_t */
+typedef void* d2c_event_t;  /* a cudaEvent_t */
 
 enum d2c_dtype { D2C_F32 = 0, D2C_F64 = 1, D2C_F16 = 2 /* depthwise only */ };
 
@@ -188,6 +189,17 @@ int d2c_deform_conv3d_bwd(const d2c_conv_desc* desc, const void* grad_y, const v
                           void* grad_offset, void* grad_mask, void* grad_w, void* grad_bias,
                           void* workspace, size_t workspace_bytes, d2c_stream_t stream);
 
+/* Same as d2c_deform_conv3d_bwd, plus an event (nullable) that is recorded on `stream` as soon as grad_w and
+ * grad_bias hold their final values.  On the tensor-core tier the weight gradient runs first, so a data-parallel
+ * caller can wait for the event on a second stream and all-reduce the parameter gradients while the data-side
+ * backward (grad_x, grad_offset, grad_mask) is still running -- what the reference gets from DistributedDataParallel's
+ * bucketed overlap (trainer.py:111).  On the CUDA-core tier the event fires at the end of the call. */
+int d2c_deform_conv3d_bwd_ev(const d2c_conv_desc* desc, const void* grad_y, const void* x,
+                             const void* offset, const void* mask, const void* w, void* grad_x,
+                             void* grad_offset, void* grad_mask, void* grad_w, void* grad_bias,
+                             void* workspace, size_t workspace_bytes, d2c_stream_t stream,
+                             d2c_event_t params_ready);
+
 /* Parity probe: the integer corner (floor) coordinates the kernels use.
  * Same coordinate formation as csrc/ops/dconv3d_gpu.cu:192-194 followed by the
  * floor of :63-65.  corners is int32 [B, G*K, 3, Do*Ho*Wo] (z0, y0, x0). */
@@ -234,6 +246,13 @@ int d2c_dyn_dilated_conv3d_bwd(const d2c_conv_desc* desc, int field_mode, const 
                                const void* w, void* grad_x, void* grad_size_map,
                                void* grad_mask, void* grad_w, void* grad_bias, void* workspace,
                                size_t workspace_bytes, d2c_stream_t stream);
+
+/* d2c_dyn_dilated_conv3d_bwd with the parameter-gradient event of d2c_deform_conv3d_bwd_ev. */
+int d2c_dyn_dilated_conv3d_bwd_ev(const d2c_conv_desc* desc, int field_mode, const void* grad_y,
+                                  const void* x, const void* size_map, const void* mask,
+                                  const void* w, void* grad_x, void* grad_size_map, void* grad_mask,
+                                  void* grad_w, void* grad_bias, void* workspace,
+                                  size_t workspace_bytes, d2c_stream_t stream, d2c_event_t params_ready);
 
 /* Corner probe for the field path (see d2c_deform_conv3d_corners). */
 int d2c_dyn_dilated_conv3d_corners(const d2c_conv_desc* desc, int field_mode,

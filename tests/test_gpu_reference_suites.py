@@ -8,8 +8,10 @@ The files are not part of this repository: baseline/install_ref.sh puts them bes
 extension in baseline/_ref/_reference_tests (git-ignored), from where they are loaded by path.  Each file runs in
 an interpreter of its own in which d2conv3d_b200.install_as_dropin() has registered this package's mirrors under
 the names `dconv_native` and `fast_depthwise_conv3d`, so `from dconv_native import deform_conv3d` in the test
-file resolves to the C-ABI-backed implementation here.  The only stand-in is a stub for the `expecttest` module,
-a test helper that torch.testing's TestCase imports and this image does not ship.
+file resolves to the C-ABI-backed implementation here.  Two things are set up around the unmodified files: a stub
+for the `expecttest` module (a test helper that torch.testing's TestCase imports and this image does not ship), and
+TF32 switched off for cuDNN / cuBLAS, because the suites compare against PyTorch's own convolutions at 1e-5 .. 1e-7
+and were written when those ran in plain fp32.
 """
 import os
 import subprocess
@@ -32,6 +34,9 @@ except ImportError:
     stub.TestCase = unittest.TestCase
     sys.modules["expecttest"] = stub
 import torch
+# the suites compare with cuDNN / cuBLAS results at 1e-5 .. 1e-7: those must be evaluated in plain fp32, not TF32
+torch.backends.cudnn.allow_tf32 = False
+torch.backends.cuda.matmul.allow_tf32 = False
 import d2conv3d_b200
 d2conv3d_b200.install_as_dropin()
 import dconv_native, fast_depthwise_conv3d
