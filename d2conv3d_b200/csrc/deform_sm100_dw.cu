@@ -400,6 +400,13 @@ bool make_dw_plan(const Geom& g, int sm_count, bool x3, DwPlan* dp) {
   const int max_split = (dp->n_tiles + 7) / 8;
   if (nsplit > max_split) nsplit = max_split;
   if (nsplit < 1) nsplit = 1;
+  // The tensor cores add into their fp32 accumulator with truncation (a chain of n accumulating MMAs loses about
+  // n * 2^-26 of the result), so the fp32-parity mode ends an accumulation chain after 40 tiles (640 MMAs, ~1e-5);
+  // partial sums of different voxel ranges meet in `dws` through fp32 reductions anyway.
+  if (x3) {
+    const int min_split = (dp->n_tiles + 39) / 40;
+    if (nsplit < min_split) nsplit = min_split;
+  }
   dp->tiles_per_split = (dp->n_tiles + nsplit - 1) / nsplit;
   dp->nsplit = (dp->n_tiles + dp->tiles_per_split - 1) / dp->tiles_per_split;
   dp->gyk_bytes = align_up((size_t)dp->n_tiles * (x3 ? 4 : 2) * dp->b_stage_bytes, 256);

@@ -16,16 +16,18 @@
 // covers a whole tile stores it; partial tiles are combined with fp32 reductions into the
 // zero-initialised output.
 //
-// Per CTA, 23 warps:
+// Per CTA, 24 warps in warpgroup-aligned roles (deform_sm100_fwd_kernel.cuh):
 //   warps 0-3   epilogue: tcgen05.ld the 128 x N accumulator, add bias, store / reduce NCDHW
 //   warp  4     one thread issues tcgen05.mma and the commits that free the stages
 //   warp  5     one thread streams pre-swizzled weight slices with cp.async.bulk
-//   warps 6-21  gather producers: unit header + gather record from the shared-memory record ring, 8
-//               unconditional corner loads (16 B) for each of the thread's two rows in flight at once, blend
-//               with pre-modulated weights, bf16 pack, swizzled st.shared of the A tile
-//   warp  22    one thread bulk-copies each unit's gather records into the record ring and writes the unit
+//   warp  6     one thread bulk-copies each unit's gather records into the record ring and writes the unit
 //               header (staging offset of the slice, valid rows), so the producers do no index arithmetic
-// Stage hand-off is by mbarriers; every wait is bounded (sm100_ptx.cuh).
+//   warp  7     idle (completes the warpgroup)
+//   warps 8-23  gather producers: unit header + gather record from the shared-memory record ring, 8
+//               unconditional corner loads (16 B) per row, the next row's loads issued before the current row is
+//               blended (setmaxnreg moves registers from warps 0-7 to these), blend with pre-modulated weights,
+//               bf16 pack, swizzled st.shared of the A tile
+// Stage hand-off is by mbarriers; every wait in the kernel's own code is bounded (sm100_ptx.cuh).
 //
 // Two math modes share the kernel (template parameter): single-pass bf16 (64-channel units, fp16 staging) and
 // the fp32-parity split "bf16x3" (32-channel units, fp32 staging, rows [hi | lo], three K-sub-block products).
@@ -69,6 +71,8 @@ struct FwdParams {
   int S;                       // slices per tile = G * K * nh
   int tiles_per_clip, n_tiles;
   long long n_units;           // n_tiles * S
+  int seg_cap;                 // at most this many units accumulate in tensor memory before the partial result is
+                               // added to y (see run_fwd); S = no limit
   int b_stages, b_stage_bytes;
   int tmem_cols;
 };
@@ -78,273 +82,7 @@ __device__ __forceinline__ void cta_unit_range(long long n_units, long long& beg
   end = n_units * (blockIdx.x + 1) / gridDim.x;
 }
 
-// kX3 = 0: math mode bf16 (a unit is 64 channels of one tap, one bf16 operand pair).
-// kX3 = 1: math mode bf16x3, the fp32-parity mode: a unit is 32 channels; the A row holds [hi(32) | lo(32)] of
-//          the fp32 blend, the weight row [hi(32) | lo(32)] of the fp32 weight, and the issuer forms
-//          a_hi*b_hi + a_lo*b_hi + a_hi*b_lo from the 16-channel K sub-blocks of the same two tiles.
-// kDual = 1 (single-pass mode only): 32 channels per offset group, a 64-channel unit spans two groups.
-template <int kX3, int kDual>
-__global__ void __launch_bounds__(kThreads, 1)
-fwd_sm100_kernel(const FwdParams p) {
-  constexpr int kUnitCh = kX3 ? 32 : 64;
-  constexpr int kRStage = (1 + kDual) * kRecBytes + 16;      // record set(s) + unit header
-  constexpr int hdr_off = (1 + kDual) * kRecBytes;
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t raw = ptx::smem_u32(smem_raw);
-  const uint32_t base = (raw + 1023u) & ~1023u;
-  uint8_t* base_ptr = smem_raw + (base - raw);
-  const int rec_off = kAStages * kAStageBytes + p.b_stages * p.b_stage_bytes;
-  const int bar_off = rec_off + kRStages * kRStage;
-  const uint32_t a_base = base, b_base = base + kAStages * kAStageBytes, rec_base = base + rec_off,
-                 bar_base = base + bar_off;
-  auto a_full = [&](int s) { return bar_base + 8u * s; };
-  auto a_empty = [&](int s) { return bar_base + 8u * (kAStages + s); };
-  auto b_full = [&](int s) { return bar_base + 8u * (2 * kAStages + s); };
-  auto b_empty = [&](int s) { return bar_base + 8u * (2 * kAStages + 4 + s); };
-  const uint32_t acc_full = bar_base + 8u * (2 * kAStages + 8);
-  const uint32_t acc_empty = bar_base + 8u * (2 * kAStages + 9);
-  auto r_full = [&](int s) { return bar_base + 8u * (2 * kAStages + 11 + s); };
-  auto r_empty = [&](int s) { return bar_base + 8u * (2 * kAStages + 11 + kRStages + s); };
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + bar_off + 8 * (2 * kAStages + 10));
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + bar_off + 8 * (2 * kAStages + 10) + 4);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const Geom& g = p.g;
-  long long u_beg, u_end;
-  cta_unit_range(p.n_units, u_beg, u_end);
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < kAStages; ++s) { ptx::mbar_init(a_full(s), kGatherWarps); ptx::mbar_init(a_empty(s), 1); }
-    for (int s = 0; s < p.b_stages; ++s) { ptx::mbar_init(b_full(s), 1); ptx::mbar_init(b_empty(s), 1); }
-    for (int s = 0; s < kRStages; ++s) { ptx::mbar_init(r_full(s), 1); ptx::mbar_init(r_empty(s), kGatherWarps); }
-    ptx::mbar_init(acc_full, 1);
-    ptx::mbar_init(acc_empty, kEpiWarps);
-    *abort_flag = 0;
-    ptx::fence_mbar_init();
-  }
-  if (warp == 0) {
-    __syncwarp();
-    ptx::tmem_alloc(ptx::smem_u32((const void*)tmem_slot), (uint32_t)p.tmem_cols);
-    ptx::tmem_relinquish();
-  }
-  ptx::tc_fence_before();
-  __syncthreads();
-  ptx::tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-
-  if (warp < kEpiWarps) {
-    // ===================== epilogue: one pass per tile segment =====================
-    int seg = 0;
-    for (long long u = u_beg; u < u_end; ++seg) {
-      const int tile = (int)(u / p.S), s_beg = (int)(u % p.S);
-      const int s_end = (int)min((long long)p.S, s_beg + (u_end - u));
-      u += s_end - s_beg;
-      const bool whole = (s_beg == 0 && s_end == p.S);
-      const int b = tile / p.tiles_per_clip, v0 = (tile % p.tiles_per_clip) * kBM;
-      if (!ptx::mbar_wait(acc_full, seg & 1, abort_flag, 2000)) break;
-      ptx::tc_fence_after();
-      const int v = v0 + warp * 32 + lane;
-      float* yb = p.y + (long long)b * g.Cout * g.V + v;
-      for (int c0 = 0; c0 < p.N; c0 += 32) {
-        uint32_t r[32];
-        ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);
-        ptx::tmem_ld_wait();
-        if (v < g.V) {
-          if (whole) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const float bb = p.bias ? __ldg(p.bias + c0 + j) : 0.f;
-              yb[(long long)(c0 + j) * g.V] = __uint_as_float(r[j]) + bb;
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const float bb = (p.bias && s_beg == 0) ? __ldg(p.bias + c0 + j) : 0.f;
-              atomicAdd(yb + (long long)(c0 + j) * g.V, __uint_as_float(r[j]) + bb);
-            }
-          }
-        }
-      }
-      ptx::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(acc_empty);
-    }
-  } else if (warp == kMmaWarp) {
-    // ===================== MMA issuer =====================
-    if (lane == 0) {
-      int seg = 0;
-      uint32_t k = 0;           // units consumed so far (A and B rings advance together)
-      bool ok = true;
-      for (long long u = u_beg; ok && u < u_end; ++seg) {
-        const int s_beg = (int)(u % p.S);
-        const int s_end = (int)min((long long)p.S, s_beg + (u_end - u));
-        u += s_end - s_beg;
-        if (!ptx::mbar_wait(acc_empty, (seg & 1) ^ 1, abort_flag)) break;
-        ptx::tc_fence_after();
-        for (int s = s_beg; s < s_end; ++s, ++k) {
-          const int sa = k % kAStages, sb = k % p.b_stages;
-          if (!ptx::mbar_wait(a_full(sa), (k / kAStages) & 1, abort_flag)) { ok = false; break; }
-          if (!ptx::mbar_wait(b_full(sb), (k / p.b_stages) & 1, abort_flag)) { ok = false; break; }
-          ptx::tc_fence_after();
-          const uint64_t adesc = ptx::umma_desc_kmajor_sw128(a_base + sa * kAStageBytes);
-          // K sub-blocks (16 channels = 32 bytes) of the A and B rows that meet in each MMA
-          constexpr int kSteps = kX3 ? 6 : 4;
-          constexpr int ka_[6] = {0, 1, kX3 ? 2 : 2, kX3 ? 3 : 3, 0, 1};   // bf16: (k,k); x3: hi*hi, lo*hi, hi*lo
-          constexpr int kb_[6] = {0, 1, kX3 ? 0 : 2, kX3 ? 1 : 3, 2, 3};
-#pragma unroll
-          for (int kk = 0; kk < kSteps; ++kk) {
-            for (int n0 = 0; n0 < p.N; n0 += 256) {
-              const int nc = min(256, p.N - n0);
-              const uint64_t bdesc = ptx::umma_desc_kmajor_sw128(b_base + sb * p.b_stage_bytes + n0 * 128);
-              ptx::umma_bf16(tmem_base + (uint32_t)n0, adesc + (uint64_t)(2 * ka_[kk]),
-                             bdesc + (uint64_t)(2 * kb_[kk]), ptx::umma_idesc_bf16_f32(kBM, nc),
-                             (s > s_beg || kk > 0) ? 1u : 0u);
-            }
-          }
-          ptx::umma_commit(a_empty(sa));
-          ptx::umma_commit(b_empty(sb));
-        }
-        if (ok) ptx::umma_commit(acc_full);
-      }
-    }
-  } else if (warp == kLoadWarp) {
-    // ===================== weight-slice loader =====================
-    if (lane == 0) {
-      uint32_t k = 0;
-      for (long long u = u_beg; u < u_end; ++u, ++k) {
-        const int s = (int)(u % p.S), sb = k % p.b_stages;
-        if (!ptx::mbar_wait(b_empty(sb), ((k / p.b_stages) & 1) ^ 1, abort_flag, 200)) break;
-        ptx::mbar_arrive_expect_tx(b_full(sb), (uint32_t)p.b_stage_bytes);
-        const uint8_t* src = p.w_sw + (long long)s * p.b_stage_bytes;
-        const uint32_t dst = b_base + sb * p.b_stage_bytes;
-        for (int off = 0; off < p.b_stage_bytes; off += 32768)
-          ptx::bulk_g2s(dst + off, src + off, (uint32_t)min(32768, p.b_stage_bytes - off), b_full(sb));
-      }
-      // never leave with a bulk copy in flight: wait (bounded) for the last copies issued
-      const uint32_t issued = k;
-      for (uint32_t q = (issued > (uint32_t)p.b_stages ? issued - p.b_stages : 0); q < issued; ++q) {
-        const long long t0 = clock64();
-        while (!ptx::mbar_try_wait(b_full(q % p.b_stages), (q / p.b_stages) & 1))
-          if (clock64() - t0 > ptx::kWaitBudgetCycles) break;
-      }
-    }
-  } else if (warp == kRecWarp) {
-    // ===================== gather-record loader =====================
-    // The records of a unit's rows are one contiguous run of the [B][G][K][V] stream: one bulk copy per unit,
-    // kRStages units ahead of the gather warps, so the producers read them from shared memory.
-    if (lane == 0) {
-      uint32_t k = 0;
-      for (long long u = u_beg; u < u_end; ++u, ++k) {
-        const int tile = (int)(u / p.S), s = (int)(u % p.S);
-        const int b = tile / p.tiles_per_clip, v0 = (tile % p.tiles_per_clip) * kBM;
-        const int gt = s / p.nh, tap = gt % g.K, grp = gt / g.K;      // dual: grp is the index of a group PAIR
-        const int sr = k % kRStages;
-        if (!ptx::mbar_wait(r_empty(sr), ((k / kRStages) & 1) ^ 1, abort_flag, 200)) break;
-        const int rows = min(kBM, g.V - v0), h = s % p.nh;
-        // unit header for the gather warps (no index arithmetic there); ordered before their reads by the
-        // release of the arrive below and the acquire of their wait
-        uint8_t* hdr = base_ptr + rec_off + sr * kRStage + hdr_off;
-        *reinterpret_cast<long long*>(hdr) =
-            (long long)b * g.Vin * g.Cin + grp * (kDual ? 2 * g.cpg : g.cpg) + h * kUnitCh;
-        *reinterpret_cast<int*>(hdr + 8) = rows;
-        const uint32_t bytes = (uint32_t)rows * 48u;
-        ptx::mbar_arrive_expect_tx(r_full(sr), bytes * (uint32_t)(1 + kDual));
-#pragma unroll
-        for (int set = 0; set <= kDual; ++set) {
-          const int og = kDual ? 2 * grp + set : grp;      // offset group whose records fill this set
-          ptx::bulk_g2s(rec_base + sr * kRStage + set * kRecBytes,
-                        p.recs + 3 * ((((long long)b * g.G + og) * g.K + tap) * g.V + v0), bytes, r_full(sr));
-        }
-      }
-      const uint32_t issued = k;
-      for (uint32_t q = (issued > (uint32_t)kRStages ? issued - kRStages : 0); q < issued; ++q) {
-        const long long t0 = clock64();
-        while (!ptx::mbar_try_wait(r_full(q % kRStages), (q / kRStages) & 1))
-          if (clock64() - t0 > ptx::kWaitBudgetCycles) break;
-      }
-    }
-  } else {
-    // ===================== gather producers =====================
-    const int t = threadIdx.x - kGatherWarp0 * 32;
-    const int j = t & 7;             // 16-byte chunk (8 channels) of the 128-byte row
-    const int r0 = t >> 3;           // rows r0, r0+kRowStride, ...
-    uint32_t row_dst[kRowsPerThread];
-#pragma unroll
-    for (int i = 0; i < kRowsPerThread; ++i) {
-      const int r = r0 + kRowStride * i;
-      row_dst[i] = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((j ^ (r & 7)) << 4));
-    }
-    uint32_t k = 0;
-    const uint32_t n_my_units = (uint32_t)(u_end - u_beg);
-    for (; k < n_my_units; ++k) {
-      const int sr = k % kRStages, sa = k % kAStages;
-      if (!ptx::mbar_wait(r_full(sr), (k / kRStages) & 1, abort_flag)) break;
-      const uint8_t* rec_base_ptr = base_ptr + rec_off + sr * kRStage;
-      const long long xoff = *reinterpret_cast<const long long*>(rec_base_ptr + hdr_off);
-      const int rows = *reinterpret_cast<const int*>(rec_base_ptr + hdr_off + 8);
-      // dual: 16-byte chunks 4-7 of a row (channels 32-63 of the unit) belong to the second offset group
-      const uint8_t* rec_stage = rec_base_ptr + ((kDual && j >= 4) ? kRecBytes : 0);
-      // every corner of every row this thread owns goes in flight before the first blend
-      uint4 c[kRowsPerThread][8];
-#pragma unroll
-      for (int i = 0; i < kRowsPerThread; ++i) {
-        const int r = r0 + kRowStride * i;
-        uint2 head = make_uint2(0u, 0u);
-        if (r < rows) head = *reinterpret_cast<const uint2*>(rec_stage + r * 48);
-        if constexpr (kX3)
-          load_corners_f32(reinterpret_cast<const float*>(p.x_cl) + xoff + j * 4, p.cs, head.x, head.y, c[i]);
-        else
-          load_corners(reinterpret_cast<const __half*>(p.x_cl) + xoff + j * 8, p.cs, head.x, head.y, c[i]);
-      }
-      if (!ptx::mbar_wait(a_empty(sa), ((k / kAStages) & 1) ^ 1, abort_flag)) break;
-      const uint32_t stage = a_base + sa * kAStageBytes;
-#pragma unroll
-      for (int i = 0; i < kRowsPerThread; ++i) {
-        const int r = r0 + kRowStride * i;
-        if constexpr (kX3) {
-          float w[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};   // rows past the clip end: stage bytes are stale
-          if (r < rows) {
-            const uint2 w01 = *reinterpret_cast<const uint2*>(rec_stage + r * 48 + 8);
-            const uint4 w25 = *reinterpret_cast<const uint4*>(rec_stage + r * 48 + 16);
-            const uint2 w67 = *reinterpret_cast<const uint2*>(rec_stage + r * 48 + 32);
-            w[0] = __uint_as_float(w01.x); w[1] = __uint_as_float(w01.y);
-            w[2] = __uint_as_float(w25.x); w[3] = __uint_as_float(w25.y);
-            w[4] = __uint_as_float(w25.z); w[5] = __uint_as_float(w25.w);
-            w[6] = __uint_as_float(w67.x); w[7] = __uint_as_float(w67.y);
-          }
-          // item j = channels 4j..4j+3: hi in 16-byte chunk j/2 (half j&1), lo in chunk 4 + j/2
-          const uint32_t row_base = stage + (uint32_t)((r >> 3) * 1024 + (r & 7) * 128) + (uint32_t)((j & 1) * 8);
-          blend_split_store(c[i], w, row_base + ((((j >> 1)) ^ (r & 7)) << 4),
-                            row_base + (((4 + (j >> 1)) ^ (r & 7)) << 4));
-        } else {
-          uint4 w03 = make_uint4(0u, 0u, 0u, 0u), w47 = w03;   // rows past the clip end: stage bytes are stale
-          if (r < rows) {
-            w03 = *reinterpret_cast<const uint4*>(rec_stage + r * 48 + 16);
-            w47 = *reinterpret_cast<const uint4*>(rec_stage + r * 48 + 32);
-          }
-          blend_store(c[i], w03, w47, stage + row_dst[i]);
-        }
-      }
-      ptx::fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) {
-        ptx::mbar_arrive(a_full(sa));
-        ptx::mbar_arrive(r_empty(sr));
-      }
-    }
-  }
-
-  // ---- teardown ----
-  ptx::tc_fence_before();
-  __syncthreads();
-  if (threadIdx.x == 0 && *abort_flag) ptx::report_device_timeout();
-  if (warp == 0) {
-    ptx::tc_fence_after();
-    ptx::tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
-  }
-}
-
-#include "deform_sm100_fwd_v2.cuh"
+#include "deform_sm100_fwd_kernel.cuh"
 #include "deform_sm100_fwd_pair.cuh"
 
 // ---- staging kernels -------------------------------------------------------------------------
@@ -471,7 +209,12 @@ int run_fwd(const Geom& g, int math_mode, const Coords& coords, const float* x, 
   long long grid = n_units / kMinUnitsPerCta;
   if (grid > sm_count) grid = sm_count;
   if (grid < 1) grid = 1;
-  bool whole_tiles_only = (pl.n_tiles % grid == 0);
+  // The tensor cores add into their fp32 accumulator with truncation: a chain of n accumulating MMAs loses about
+  // n * 2^-26 of the result (measured: 2e-5 of scale after 2 600 steps, 8e-5 after 5 200).  The fp32-parity mode
+  // therefore ends a chain after 108 units (648 MMAs, ~1e-5) and adds the partial tile to y with fp32 atomics,
+  // exactly as it does where a tile is shared between two CTAs.
+  const int seg_cap = x3 ? 108 : pl.S;
+  bool whole_tiles_only = (pl.n_tiles % grid == 0) && seg_cap >= pl.S;
 
   // CTA pairs (deform_sm100_fwd_pair.cuh) whenever there are at least two tiles and the device can co-schedule
   // clusters of 2 with this kernel's shared memory.  Opt-in (D2C_SM100_PAIR=1): measured slower than the
@@ -536,6 +279,7 @@ int run_fwd(const Geom& g, int math_mode, const Coords& coords, const float* x, 
   p.cs.dz = g.H * g.W * g.Cin; p.cs.dy = g.W * g.Cin; p.cs.dx = g.Cin;
   p.N = g.Cout; p.nh = pl.nh; p.S = pl.S; p.tiles_per_clip = pl.tiles_per_clip; p.n_tiles = pl.n_tiles;
   p.n_units = n_units;
+  p.seg_cap = seg_cap;
   p.b_stages = pl.b_stages; p.b_stage_bytes = pl.b_stage_bytes; p.tmem_cols = pl.tmem_cols;
 
   if (pair_clusters > 0) {
@@ -550,25 +294,9 @@ int run_fwd(const Geom& g, int math_mode, const Coords& coords, const float* x, 
     return D2C_OK;
   }
   prof_mark(st, "fwd_sm100_fused");
-  static int fwd_v = -1;
-  if (fwd_v < 0) {
-    const char* e = getenv("D2C_FWD_V");
-    fwd_v = (e && e[0] == '1') ? 1 : 2;
-  }
-  if (fwd_v == 2) {
-    auto kern = x3 ? fwd_sm100_v2_kernel<1, 0> : (pl.dual ? fwd_sm100_v2_kernel<0, 1> : fwd_sm100_v2_kernel<0, 0>);
-    D2C_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes));
-    kern<<<(unsigned)grid, kThreads2, pl.smem_bytes, st>>>(p);
-  } else if (x3) {
-    D2C_CUDA_TRY(cudaFuncSetAttribute(fwd_sm100_kernel<1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes));
-    fwd_sm100_kernel<1, 0><<<(unsigned)grid, kThreads, pl.smem_bytes, st>>>(p);
-  } else if (pl.dual) {
-    D2C_CUDA_TRY(cudaFuncSetAttribute(fwd_sm100_kernel<0, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes));
-    fwd_sm100_kernel<0, 1><<<(unsigned)grid, kThreads, pl.smem_bytes, st>>>(p);
-  } else {
-    D2C_CUDA_TRY(cudaFuncSetAttribute(fwd_sm100_kernel<0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes));
-    fwd_sm100_kernel<0, 0><<<(unsigned)grid, kThreads, pl.smem_bytes, st>>>(p);
-  }
+  auto kern = x3 ? fwd_sm100_kernel<1, 0> : (pl.dual ? fwd_sm100_kernel<0, 1> : fwd_sm100_kernel<0, 0>);
+  D2C_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes));
+  kern<<<(unsigned)grid, kThreadsFwd, pl.smem_bytes, st>>>(p);
   D2C_LAUNCH_CHECK();
   prof_mark(st, nullptr);
   return D2C_OK;

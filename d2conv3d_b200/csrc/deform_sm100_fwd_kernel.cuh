@@ -1,10 +1,10 @@
-// Second generation of the single-CTA forward kernel.  Same tiles, rings, barriers and MMA issue as
-// fwd_sm100_kernel above; what differs is the producer side:
-//   * warp roles are aligned to warpgroups (4 epilogue warps | MMA, weight loader, record loader, one idle warp |
-//     16 gather warps) so that `setmaxnreg` can move registers from the light roles to the gather warps;
-//   * the gather loop is software-pipelined at row granularity (see the producer branch).
-constexpr int kThreads2 = 24 * 32;
-constexpr int kMmaWarp2 = 4, kLoadWarp2 = 5, kRecWarp2 = 6, kGatherWarp02 = 8;
+// The single-CTA forward kernel (included by deform_sm100_fwd.cu, whose constants, FwdParams and gather helpers it
+// uses).  Warp roles are aligned to warpgroups (4 epilogue warps | MMA, weight loader, record loader, one idle warp
+// | 16 gather warps) so that `setmaxnreg` can move registers from the light roles to the gather warps, whose loop
+// is software-pipelined at row granularity (see the producer branch).
+constexpr int kThreadsFwd = 24 * 32;
+static_assert(128 * 56 + 128 * 40 + 512 * 96 <= kThreadsFwd * 80, "setmaxnreg budget exceeds the CTA's register allocation");
+constexpr int kMmaWarpFwd = 4, kLoadWarpFwd = 5, kRecWarpFwd = 6, kGatherWarp0Fwd = 8;
 
 // kX3 = 0: math mode bf16 (a unit is 64 channels of one tap, one bf16 operand pair).
 // kX3 = 1: math mode bf16x3, the fp32-parity mode: a unit is 32 channels; the A row holds [hi(32) | lo(32)] of
@@ -12,8 +12,8 @@ constexpr int kMmaWarp2 = 4, kLoadWarp2 = 5, kRecWarp2 = 6, kGatherWarp02 = 8;
 //          a_hi*b_hi + a_lo*b_hi + a_hi*b_lo from the 16-channel K sub-blocks of the same two tiles.
 // kDual = 1 (single-pass mode only): 32 channels per offset group, a 64-channel unit spans two groups.
 template <int kX3, int kDual>
-__global__ void __launch_bounds__(kThreads2, 1)
-fwd_sm100_v2_kernel(const FwdParams p) {
+__global__ void __launch_bounds__(kThreadsFwd, 1)
+fwd_sm100_kernel(const FwdParams p) {
   constexpr int kUnitCh = kX3 ? 32 : 64;
   constexpr int kRStage = (1 + kDual) * kRecBytes + 16;      // record set(s) + unit header
   constexpr int hdr_off = (1 + kDual) * kRecBytes;
@@ -60,24 +60,18 @@ fwd_sm100_v2_kernel(const FwdParams p) {
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  // Register re-balancing between the roles (warpgroup-wide): the epilogue and service warps give registers back,
-  // the gather warps take them, so that a gather thread can hold the corner loads of TWO rows in flight while it
-  // blends -- the loads of the next row (or of the next unit's first row) are issued before the current row is
-  // consumed.  7168 + 5120 + 53248 = 65536 registers.
-  if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
-  } else if (warp < 8) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
-  } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
-  }
-
+  // Register re-balancing between the roles (warpgroup-wide, first statement of each role's branch): the epilogue
+  // and service warps give registers back, the gather warps take them, so that a gather thread can hold the corner
+  // loads of TWO rows in flight while it blends.  The increase is served from what the CTA itself gave back: the CTA
+  // is launched with 768 x 80 = 61440 registers and 128*56 + 128*40 + 512*96 = 61440 (asking for more would make
+  // the increase wait for registers that never come).
   if (warp < kEpiWarps) {
     // ===================== epilogue: one pass per tile segment =====================
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     int seg = 0;
     for (long long u = u_beg; u < u_end; ++seg) {
       const int tile = (int)(u / p.S), s_beg = (int)(u % p.S);
-      const int s_end = (int)min((long long)p.S, s_beg + (u_end - u));
+      const int s_end = min((int)min((long long)p.S, s_beg + (u_end - u)), s_beg + p.seg_cap);
       u += s_end - s_beg;
       const bool whole = (s_beg == 0 && s_end == p.S);
       const int b = tile / p.tiles_per_clip, v0 = (tile % p.tiles_per_clip) * kBM;
@@ -109,7 +103,9 @@ fwd_sm100_v2_kernel(const FwdParams p) {
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(acc_empty);
     }
-  } else if (warp == kMmaWarp2) {
+  } else if (warp < kGatherWarp0Fwd) {
+   asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+   if (warp == kMmaWarpFwd) {
     // ===================== MMA issuer =====================
     if (lane == 0) {
       int seg = 0;
@@ -117,7 +113,7 @@ fwd_sm100_v2_kernel(const FwdParams p) {
       bool ok = true;
       for (long long u = u_beg; ok && u < u_end; ++seg) {
         const int s_beg = (int)(u % p.S);
-        const int s_end = (int)min((long long)p.S, s_beg + (u_end - u));
+        const int s_end = min((int)min((long long)p.S, s_beg + (u_end - u)), s_beg + p.seg_cap);
         u += s_end - s_beg;
         if (!ptx::mbar_wait(acc_empty, (seg & 1) ^ 1, abort_flag)) break;
         ptx::tc_fence_after();
@@ -147,7 +143,7 @@ fwd_sm100_v2_kernel(const FwdParams p) {
         if (ok) ptx::umma_commit(acc_full);
       }
     }
-  } else if (warp == kLoadWarp2) {
+  } else if (warp == kLoadWarpFwd) {
     // ===================== weight-slice loader =====================
     if (lane == 0) {
       uint32_t k = 0;
@@ -168,7 +164,7 @@ fwd_sm100_v2_kernel(const FwdParams p) {
           if (clock64() - t0 > ptx::kWaitBudgetCycles) break;
       }
     }
-  } else if (warp == kRecWarp2) {
+  } else if (warp == kRecWarpFwd) {
     // ===================== gather-record loader =====================
     // The records of a unit's rows are one contiguous run of the [B][G][K][V] stream: one bulk copy per unit,
     // kRStages units ahead of the gather warps, so the producers read them from shared memory.
@@ -203,12 +199,14 @@ fwd_sm100_v2_kernel(const FwdParams p) {
           if (clock64() - t0 > ptx::kWaitBudgetCycles) break;
       }
     }
-  } else if (warp >= kGatherWarp02) {
+   }
+  } else {
     // ===================== gather producers (software-pipelined) =====================
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 96;");
     // A thread owns rows r0 and r0 + 64 of every unit, chunk j (16 B of the 128-byte A row).  Items are taken in
     // the order (unit k, row 0), (unit k, row 1), (unit k+1, row 0) ...; the 8 corner loads of item t+1 are
     // issued before item t is blended, so 8 loads are always in flight under the blend and 16 while it waits.
-    const int t = threadIdx.x - kGatherWarp02 * 32;
+    const int t = threadIdx.x - kGatherWarp0Fwd * 32;
     const int j = t & 7;             // 16-byte chunk (8 channels) of the 128-byte row
     const int r0 = t >> 3;           // rows r0, r0 + kRowStride
     const uint32_t n_my_units = (uint32_t)(u_end - u_beg);
