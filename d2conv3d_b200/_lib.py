@@ -31,6 +31,16 @@ class ConvDesc(ctypes.Structure):
         "dil_d", "dil_h", "dil_w", "groups", "offset_groups")]
 
 
+class HeadDesc(ctypes.Structure):
+    """d2c_head_desc"""
+
+    _fields_ = [(n, ctypes.c_int32) for n in ("raw_channels", "geo_channel0", "mask_channel0", "mask_act", "size_act")]
+
+
+MASK_ACTS = {"linear": 0, "none": 0, "sigmoid": 1, "relu": 2, "tanh": 3}
+SIZE_ACTS = {"linear": 0, "elu": 1, "relu": 2, "relu_plus_one": 3}
+
+
 class ProfileRecord(ctypes.Structure):
     """d2c_profile_record"""
 
@@ -77,6 +87,13 @@ def lib():
         L.d2c_dyn_dilated_conv3d_fwd.argtypes = [dp, i32] + [vp] * 7 + [sz, vp]
         L.d2c_dyn_dilated_conv3d_bwd.argtypes = [dp, i32] + [vp] * 11 + [sz, vp]
         L.d2c_dyn_dilated_conv3d_corners.argtypes = [dp, i32, vp, vp, vp]
+        hp = ctypes.POINTER(HeadDesc)
+        L.d2c_head_workspace_bytes.argtypes = [i32, dp, hp, i32]
+        L.d2c_head_workspace_bytes.restype = sz
+        L.d2c_deform_conv3d_head_fwd.argtypes = [dp, hp] + [vp] * 6 + [sz, vp]
+        L.d2c_deform_conv3d_head_bwd.argtypes = [dp, hp] + [vp] * 9 + [sz, vp, vp]
+        L.d2c_dyn_dilated_conv3d_head_fwd.argtypes = [dp, hp, i32] + [vp] * 6 + [sz, vp]
+        L.d2c_dyn_dilated_conv3d_head_bwd.argtypes = [dp, hp, i32] + [vp] * 9 + [sz, vp, vp]
         L.d2c_act_group_norm_workspace_bytes.argtypes = [i32, i32]
         L.d2c_act_group_norm_workspace_bytes.restype = sz
         L.d2c_act_group_norm_fwd.argtypes = [vp, vp, vp, vp, i32, i32, ctypes.c_longlong, i32, ctypes.c_float, i32,
@@ -135,6 +152,13 @@ def workspace(op, desc, device):
         return None, 0
     ws = torch.empty(n, dtype=torch.uint8, device=device)
     return ws, n
+
+
+def head_workspace(op, desc, head, field_mode, device):
+    n = lib().d2c_head_workspace_bytes(op, ctypes.byref(desc), ctypes.byref(head), field_mode)
+    if n == 0:
+        return None, 0
+    return torch.empty(n, dtype=torch.uint8, device=device), n
 
 
 def set_math_mode(mode):

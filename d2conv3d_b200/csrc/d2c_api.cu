@@ -573,6 +573,271 @@ int d2c_dyn_dilated_conv3d_corners(const d2c_conv_desc* desc, int field_mode, co
   return D2C_OK;
 }
 
+// ---- deformation head fused into the op ------------------------------------------------------------
+
+}  // extern "C"
+
+namespace d2c {
+namespace {
+
+struct HeadPlan {
+  int geo_n, mask_n;          // geometry / mask channels
+  long long rstride;          // raw_channels * V
+  size_t geo_bytes, mask_bytes;   // dense staging tensors of the CUDA-core route (element size applied)
+};
+
+int make_head_plan(const Geom& g, const d2c_head_desc* h, int field_nch, int dtype, HeadPlan* hp) {
+  if (!h) return D2C_ERR_NULL;
+  hp->geo_n = field_nch > 0 ? field_nch : g.G * 3 * g.K;
+  hp->mask_n = h->mask_channel0 >= 0 ? g.G * g.K : 0;
+  if (h->raw_channels <= 0 || h->geo_channel0 < 0 || h->geo_channel0 + hp->geo_n > h->raw_channels)
+    return D2C_ERR_OFFSET_SHAPE;
+  if (hp->mask_n) {
+    if (h->mask_channel0 + hp->mask_n > h->raw_channels) return D2C_ERR_MASK_SHAPE;
+    const bool disjoint = h->mask_channel0 >= h->geo_channel0 + hp->geo_n || h->geo_channel0 >= h->mask_channel0 + hp->mask_n;
+    if (!disjoint) return D2C_ERR_MASK_SHAPE;
+  }
+  if (h->mask_act < D2C_MASK_LINEAR || h->mask_act > D2C_MASK_TANH) return D2C_ERR_MODE;
+  if (h->size_act < D2C_SIZE_LINEAR || h->size_act > D2C_SIZE_RELU_PLUS_ONE) return D2C_ERR_MODE;
+  hp->rstride = (long long)h->raw_channels * g.V;
+  const size_t es = dtype == D2C_F64 ? 8 : 4;
+  hp->geo_bytes = align_up(es * (size_t)g.B * hp->geo_n * g.V, 256);
+  hp->mask_bytes = align_up(es * (size_t)g.B * hp->mask_n * g.V, 256);
+  return D2C_OK;
+}
+
+// CUDA-core route: activated dense copies of the geometry and mask channels
+template <typename T>
+__global__ void __launch_bounds__(256)
+head_apply_kernel(const T* __restrict__ raw, long long rstride, int V, int B, int geo_c0, int geo_n, int mask_c0, int mask_n,
+                  int size_act, int mask_act, T* __restrict__ geo, T* __restrict__ mask) {
+  const long long per = (long long)(geo_n + mask_n) * V;
+  for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < (long long)B * per; i += (long long)gridDim.x * 256) {
+    const long long b = i / per, r = i % per;
+    const int c = (int)(r / V), v = (int)(r % V);
+    if (c < geo_n)
+      geo[((long long)b * geo_n + c) * V + v] = size_act_value(size_act, raw[b * rstride + (long long)(geo_c0 + c) * V + v]);
+    else
+      mask[((long long)b * mask_n + (c - geo_n)) * V + v] =
+          mask_act_value(mask_act, raw[b * rstride + (long long)(mask_c0 + c - geo_n) * V + v]);
+  }
+}
+
+// CUDA-core route: dense gradients -> gradient of the raw tensor (every channel written)
+template <typename T>
+__global__ void __launch_bounds__(256)
+head_grad_kernel(const T* __restrict__ raw, long long rstride, int C, int V, int B, int geo_c0, int geo_n, int mask_c0, int mask_n,
+                 int size_act, int mask_act, const T* __restrict__ ggeo, const T* __restrict__ gmask,
+                 const T* __restrict__ mask_activated, T* __restrict__ graw) {
+  for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < (long long)B * C * V; i += (long long)gridDim.x * 256) {
+    const long long b = i / ((long long)C * V), r = i % ((long long)C * V);
+    const int c = (int)(r / V), v = (int)(r % V);
+    T out = (T)0;
+    if (c >= geo_c0 && c < geo_c0 + geo_n) {
+      out = ggeo[((long long)b * geo_n + (c - geo_c0)) * V + v] * size_act_slope(size_act, raw[b * rstride + r]);
+    } else if (mask_n && c >= mask_c0 && c < mask_c0 + mask_n) {
+      const long long mi = ((long long)b * mask_n + (c - mask_c0)) * V + v;
+      out = gmask[mi] * mask_act_slope(mask_act, mask_activated[mi]);
+    }
+    graw[b * rstride + r] = out;
+  }
+}
+
+bool head_fused_fwd(const Geom& g, int dtype, int mode) { return sm100_fwd_supported(g, dtype, mode); }
+bool head_fused_bwd(const Geom& g, int dtype, int mode, unsigned long long cap) { return sm100_bwd_supported(g, dtype, mode, cap); }
+
+template <typename T>
+int head_fwd_t(const Geom& g, const d2c_head_desc* h, const HeadPlan& hp, int field_mode, bool is_field, const T* x, const T* raw,
+               const T* w, const T* bias, T* y, void* workspace, size_t workspace_bytes, cudaStream_t st) {
+  // the CUDA-core route: stage activated dense tensors, then the ordinary kernels
+  uint8_t* wsp = reinterpret_cast<uint8_t*>(workspace);
+  if (!ws_ok(workspace, workspace_bytes, hp.geo_bytes + hp.mask_bytes)) return D2C_ERR_WORKSPACE;
+  T* geo = reinterpret_cast<T*>(wsp);
+  T* mask = hp.mask_n ? reinterpret_cast<T*>(wsp + hp.geo_bytes) : nullptr;
+  head_apply_kernel<T><<<grid_1d((long long)g.B * (hp.geo_n + hp.mask_n) * g.V, 256), 256, 0, st>>>(
+      raw, hp.rstride, g.V, g.B, h->geo_channel0, hp.geo_n, h->mask_channel0, hp.mask_n, is_field ? h->size_act : 0,
+      h->mask_act, geo, mask);
+  D2C_LAUNCH_CHECK();
+  if (is_field) {
+    FieldCoords<T> fc;
+    int rc = make_field_coords<T>(g, field_mode, geo, &fc);
+    if (rc) return rc;
+    return launch_fwd_generic<T>(g, fc, x, mask, w, bias, y, st);
+  }
+  OffsetCoords<T> oc{geo, 0};
+  return launch_fwd_generic<T>(g, oc, x, mask, w, bias, y, st);
+}
+
+template <typename T>
+int head_bwd_t(const Geom& g, const d2c_head_desc* h, const HeadPlan& hp, int field_mode, bool is_field, unsigned long long cap,
+               const T* gy, const T* x, const T* raw, const T* w, T* gx, T* graw, T* gw, T* gbias, void* workspace,
+               size_t workspace_bytes, cudaStream_t st) {
+  const size_t stage = 2 * (hp.geo_bytes + hp.mask_bytes);
+  const size_t need = stage + generic_bwd_workspace(g, sizeof(T) == 8 ? D2C_F64 : D2C_F32, cap);
+  if (!ws_ok(workspace, workspace_bytes, need)) return D2C_ERR_WORKSPACE;
+  uint8_t* wsp = reinterpret_cast<uint8_t*>(workspace);
+  T* geo = reinterpret_cast<T*>(wsp);
+  T* mask = hp.mask_n ? reinterpret_cast<T*>(wsp + hp.geo_bytes) : nullptr;
+  T* ggeo = reinterpret_cast<T*>(wsp + hp.geo_bytes + hp.mask_bytes);
+  T* gmask = hp.mask_n ? reinterpret_cast<T*>(wsp + 2 * hp.geo_bytes + hp.mask_bytes) : nullptr;
+  T* dcol = reinterpret_cast<T*>(wsp + stage);
+  head_apply_kernel<T><<<grid_1d((long long)g.B * (hp.geo_n + hp.mask_n) * g.V, 256), 256, 0, st>>>(
+      raw, hp.rstride, g.V, g.B, h->geo_channel0, hp.geo_n, h->mask_channel0, hp.mask_n, is_field ? h->size_act : 0,
+      h->mask_act, geo, mask);
+  D2C_LAUNCH_CHECK();
+  const int nb = bwd_slice_clips(g, cap);
+  int rc;
+  if (is_field) {
+    FieldCoords<T> fc;
+    if ((rc = make_field_coords<T>(g, field_mode, geo, &fc))) return rc;
+    rc = launch_bwd_generic<T, FieldCoords<T>, true>(g, fc, gy, x, mask, w, gx, ggeo, (size_t)g.B * hp.geo_n * g.V, gmask, gw,
+                                                     gbias, dcol, nb, st);
+  } else {
+    OffsetCoords<T> oc{geo, 0};
+    rc = launch_bwd_generic<T, OffsetCoords<T>, false>(g, oc, gy, x, mask, w, gx, ggeo, 0, gmask, gw, gbias, dcol, nb, st);
+  }
+  if (rc) return rc;
+  head_grad_kernel<T><<<grid_1d((long long)g.B * h->raw_channels * g.V, 256), 256, 0, st>>>(
+      raw, hp.rstride, h->raw_channels, g.V, g.B, h->geo_channel0, hp.geo_n, h->mask_channel0, hp.mask_n,
+      is_field ? h->size_act : 0, h->mask_act, ggeo, gmask, mask, graw);
+  D2C_LAUNCH_CHECK();
+  return D2C_OK;
+}
+
+int head_fwd(const d2c_conv_desc* desc, const d2c_head_desc* head, int field_mode, bool is_field, const void* x, const void* raw,
+             const void* w, const void* bias, void* y, void* workspace, size_t workspace_bytes, cudaStream_t st) {
+  if (!desc || !head || !x || !raw || !w || !y) return D2C_ERR_NULL;
+  Geom g;
+  int rc = make_geom(desc, &g, false);
+  if (rc) return rc;
+  if (desc->dtype != D2C_F32 && desc->dtype != D2C_F64) return D2C_ERR_DTYPE;
+  const int nch = is_field ? field_channels(field_mode) : 0;
+  if (is_field && nch < 0) return D2C_ERR_MODE;
+  HeadPlan hp;
+  if ((rc = make_head_plan(g, head, nch, desc->dtype, &hp))) return rc;
+  D2C_TAKE_STATUS();
+  const int mode = g_math_mode.load();
+  if (head_fused_fwd(g, desc->dtype, mode)) {
+    if (!ws_ok(workspace, workspace_bytes, sm100_fwd_workspace(g, desc->dtype, mode))) return D2C_ERR_WORKSPACE;
+    const float* r = (const float*)raw;
+    HeadCfg cfg{hp.rstride, hp.mask_n ? hp.rstride : 0, head->mask_act, head->size_act};
+    const float* mask = hp.mask_n ? r + (long long)head->mask_channel0 * g.V : nullptr;
+    if (is_field) {
+      FieldCoords<float> fc;
+      if ((rc = make_field_coords<float>(g, field_mode, r + (long long)head->geo_channel0 * g.V, &fc))) return rc;
+      fc.bstride = hp.rstride;
+      fc.act = head->size_act;
+      return sm100_fwd_field(g, mode, fc, (const float*)x, mask, (const float*)w, (const float*)bias, (float*)y, workspace, st, cfg);
+    }
+    return sm100_fwd_offsets(g, mode, (const float*)x, r + (long long)head->geo_channel0 * g.V, mask, (const float*)w,
+                             (const float*)bias, (float*)y, workspace, st, cfg);
+  }
+  if (desc->dtype == D2C_F32)
+    return head_fwd_t<float>(g, head, hp, field_mode, is_field, (const float*)x, (const float*)raw, (const float*)w,
+                             (const float*)bias, (float*)y, workspace, workspace_bytes, st);
+  return head_fwd_t<double>(g, head, hp, field_mode, is_field, (const double*)x, (const double*)raw, (const double*)w,
+                            (const double*)bias, (double*)y, workspace, workspace_bytes, st);
+}
+
+int head_bwd(const d2c_conv_desc* desc, const d2c_head_desc* head, int field_mode, bool is_field, const void* gy, const void* x,
+             const void* raw, const void* w, void* gx, void* graw, void* gw, void* gbias, void* workspace,
+             size_t workspace_bytes, cudaStream_t st, cudaEvent_t params_ready) {
+  if (!desc || !head || !gy || !x || !raw || !w || !gx || !graw || !gw) return D2C_ERR_NULL;
+  Geom g;
+  int rc = make_geom(desc, &g, false);
+  if (rc) return rc;
+  if (desc->dtype != D2C_F32 && desc->dtype != D2C_F64) return D2C_ERR_DTYPE;
+  const int nch = is_field ? field_channels(field_mode) : 0;
+  if (is_field && nch < 0) return D2C_ERR_MODE;
+  HeadPlan hp;
+  if ((rc = make_head_plan(g, head, nch, desc->dtype, &hp))) return rc;
+  D2C_TAKE_STATUS();
+  const int mode = g_math_mode.load();
+  const unsigned long long cap = g_max_intermediate.load();
+  if (head_fused_bwd(g, desc->dtype, mode, cap)) {
+    if (!ws_ok(workspace, workspace_bytes, sm100_bwd_workspace(g, desc->dtype, mode, cap))) return D2C_ERR_WORKSPACE;
+    const float* r = (const float*)raw;
+    float* gr = (float*)graw;
+    // channels of raw that feed neither part get a zero gradient
+    if (hp.geo_n + hp.mask_n < head->raw_channels)
+      D2C_CUDA_TRY(cudaMemsetAsync(gr, 0, sizeof(float) * (size_t)g.B * hp.rstride, st));
+    HeadCfg cfg{hp.rstride, hp.mask_n ? hp.rstride : 0, head->mask_act, head->size_act};
+    const float* mask = hp.mask_n ? r + (long long)head->mask_channel0 * g.V : nullptr;
+    float* gmask = hp.mask_n ? gr + (long long)head->mask_channel0 * g.V : nullptr;
+    float* ggeo = gr + (long long)head->geo_channel0 * g.V;
+    if (is_field) {
+      FieldCoords<float> fc;
+      if ((rc = make_field_coords<float>(g, field_mode, r + (long long)head->geo_channel0 * g.V, &fc))) return rc;
+      fc.bstride = hp.rstride;
+      fc.act = head->size_act;
+      return sm100_bwd_field(g, mode, cap, fc, (const float*)gy, (const float*)x, mask, (const float*)w, (float*)gx, ggeo,
+                             (size_t)g.B * nch * g.V, gmask, (float*)gw, (float*)gbias, workspace, st, params_ready, cfg);
+    }
+    return sm100_bwd_offsets(g, mode, cap, (const float*)gy, (const float*)x, r + (long long)head->geo_channel0 * g.V, mask,
+                             (const float*)w, (float*)gx, ggeo, gmask, (float*)gw, (float*)gbias, workspace, st, params_ready,
+                             cfg);
+  }
+  if (desc->dtype == D2C_F32)
+    rc = head_bwd_t<float>(g, head, hp, field_mode, is_field, cap, (const float*)gy, (const float*)x, (const float*)raw,
+                           (const float*)w, (float*)gx, (float*)graw, (float*)gw, (float*)gbias, workspace, workspace_bytes, st);
+  else
+    rc = head_bwd_t<double>(g, head, hp, field_mode, is_field, cap, (const double*)gy, (const double*)x, (const double*)raw,
+                            (const double*)w, (double*)gx, (double*)graw, (double*)gw, (double*)gbias, workspace,
+                            workspace_bytes, st);
+  if (rc == D2C_OK && params_ready) D2C_CUDA_TRY(cudaEventRecord(params_ready, st));
+  return rc;
+}
+
+}  // namespace
+}  // namespace d2c
+
+extern "C" {
+
+size_t d2c_head_workspace_bytes(int op, const d2c_conv_desc* desc, const d2c_head_desc* head, int field_mode) {
+  Geom g;
+  if (!desc || !head || make_geom(desc, &g, false)) return 0;
+  const bool is_field = op == D2C_OP_DYNDIL_FWD || op == D2C_OP_DYNDIL_BWD;
+  const bool bwd = op == D2C_OP_DEFORM_BWD || op == D2C_OP_DYNDIL_BWD;
+  const int nch = is_field ? field_channels(field_mode) : 0;
+  HeadPlan hp;
+  if ((is_field && nch < 0) || make_head_plan(g, head, nch, desc->dtype, &hp)) return 0;
+  const int mode = g_math_mode.load();
+  const unsigned long long cap = g_max_intermediate.load();
+  // whichever route the call takes under the current settings, and never less than the plain op's workspace
+  const size_t plain = d2c_workspace_bytes(op, desc);
+  const size_t staged = (bwd ? 2 : 1) * (hp.geo_bytes + hp.mask_bytes) + (bwd ? generic_bwd_workspace(g, desc->dtype, cap) : 0);
+  const bool fused = bwd ? head_fused_bwd(g, desc->dtype, mode, cap) : head_fused_fwd(g, desc->dtype, mode);
+  return fused ? plain : (staged > plain ? staged : plain);
+}
+
+int d2c_deform_conv3d_head_fwd(const d2c_conv_desc* desc, const d2c_head_desc* head, const void* x, const void* raw,
+                               const void* w, const void* bias, void* y, void* workspace, size_t workspace_bytes,
+                               d2c_stream_t stream) {
+  return head_fwd(desc, head, 0, false, x, raw, w, bias, y, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+int d2c_deform_conv3d_head_bwd(const d2c_conv_desc* desc, const d2c_head_desc* head, const void* grad_y, const void* x,
+                               const void* raw, const void* w, void* grad_x, void* grad_raw, void* grad_w,
+                               void* grad_bias, void* workspace, size_t workspace_bytes, d2c_stream_t stream,
+                               d2c_event_t params_ready) {
+  return head_bwd(desc, head, 0, false, grad_y, x, raw, w, grad_x, grad_raw, grad_w, grad_bias, workspace, workspace_bytes,
+                  (cudaStream_t)stream, (cudaEvent_t)params_ready);
+}
+
+int d2c_dyn_dilated_conv3d_head_fwd(const d2c_conv_desc* desc, const d2c_head_desc* head, int field_mode, const void* x,
+                                    const void* raw, const void* w, const void* bias, void* y, void* workspace,
+                                    size_t workspace_bytes, d2c_stream_t stream) {
+  return head_fwd(desc, head, field_mode, true, x, raw, w, bias, y, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+int d2c_dyn_dilated_conv3d_head_bwd(const d2c_conv_desc* desc, const d2c_head_desc* head, int field_mode,
+                                    const void* grad_y, const void* x, const void* raw, const void* w, void* grad_x,
+                                    void* grad_raw, void* grad_w, void* grad_bias, void* workspace,
+                                    size_t workspace_bytes, d2c_stream_t stream, d2c_event_t params_ready) {
+  return head_bwd(desc, head, field_mode, true, grad_y, x, raw, w, grad_x, grad_raw, grad_w, grad_bias, workspace,
+                  workspace_bytes, (cudaStream_t)stream, (cudaEvent_t)params_ready);
+}
+
 // ---- depthwise -----------------------------------------------------------------------------------
 
 int d2c_depthwise_conv3d_fwd(const d2c_conv_desc* desc, const void* x, const void* w,

@@ -71,6 +71,60 @@ __device__ __forceinline__ double fma_rn(double a, double b, double c) { return 
 __device__ __forceinline__ int floor_int(float a) { return __float2int_rd(a); }
 __device__ __forceinline__ int floor_int(double a) { return __double2int_rd(a); }
 
+// ---- deformation head fused into the op ---------------------------------------------------------
+// The layers around the op (network/layers.py:107-120, 171-181, 302-313) take ONE tensor from their predictor
+// convolution, split it into [geometry | mask logits] channels and apply an activation to each part.  With a head
+// configuration the kernels read that raw tensor in place (clip stride = all of its channels), apply the
+// activation where they read it, and write the gradient w.r.t. the raw tensor (chain rule included).
+// All-zero configuration = the plain op: dense tensors, no activation.
+struct HeadCfg {
+  long long geo_bstride;    // elements between clips of the offset / field tensor (0: dense)
+  long long mask_bstride;   // ... of the mask tensor (0: dense)
+  int mask_act;             // d2c_mask_act
+  int size_act;             // d2c_size_act (dilation-field variants)
+};
+
+// mask activations of the reference's layers (network/layers.py:19-25)
+template <typename T>
+__host__ __device__ __forceinline__ T mask_act_value(int act, T r) {
+  switch (act) {
+    case D2C_MASK_SIGMOID: return (T)1 / ((T)1 + exp(-r));
+    case D2C_MASK_RELU: return r > (T)0 ? r : (T)0;
+    case D2C_MASK_TANH: return tanh(r);
+    default: return r;
+  }
+}
+// derivative of the activation, from the ACTIVATED value m
+template <typename T>
+__host__ __device__ __forceinline__ T mask_act_slope(int act, T m) {
+  switch (act) {
+    case D2C_MASK_SIGMOID: return m * ((T)1 - m);
+    case D2C_MASK_RELU: return m > (T)0 ? (T)1 : (T)0;
+    case D2C_MASK_TANH: return (T)1 - m * m;
+    default: return (T)1;
+  }
+}
+// size activations (network/layers.py:171-181): elu(x)+1, relu(x+1), relu(x+1e-3)+1, identity
+template <typename T>
+__host__ __device__ __forceinline__ T size_act_value(int act, T r) {
+  switch (act) {
+    case D2C_SIZE_ELU: return (r > (T)0 ? r : (exp(r) - (T)1)) + (T)1;
+    case D2C_SIZE_RELU: { const T t = r + (T)1; return t > (T)0 ? t : (T)0; }
+    case D2C_SIZE_RELU_PLUS_ONE: { const T t = r + (T)1e-3; return (t > (T)0 ? t : (T)0) + (T)1; }
+    default: return r;
+  }
+}
+// derivative w.r.t. the RAW value r (torch's conventions at the kinks: elu' (0) = 1, relu'(0) = 0)
+template <typename T>
+__host__ __device__ __forceinline__ T size_act_slope(int act, T r) {
+  switch (act) {
+    case D2C_SIZE_ELU: return r > (T)0 ? (T)1 : exp(r);
+    case D2C_SIZE_RELU: return r + (T)1 > (T)0 ? (T)1 : (T)0;
+    case D2C_SIZE_RELU_PLUS_ONE: return r + (T)1e-3 > (T)0 ? (T)1 : (T)0;
+    default: return (T)1;
+  }
+}
+
 // ---- where the sampling coordinates come from ----------------------------------------------
 
 // Offsets given explicitly: [B, G*3K, V], channel 3*(grp*K+tap)+{0:z,1:y,2:x}
@@ -78,9 +132,11 @@ __device__ __forceinline__ int floor_int(double a) { return __double2int_rd(a); 
 template <typename T>
 struct OffsetCoords {
   const T* offset;
+  long long bstride;   // elements between clips; 0 = dense [B, G*3K, V]
   __device__ __forceinline__ void get(const Geom& g, int b, int grp, int tap, int v, int bz, int by,
                                       int bx, T& z, T& y, T& x) const {
-    const T* p = offset + (((long long)b * g.G + grp) * 3 * g.K + 3 * tap) * g.V + v;
+    const long long bs = bstride ? bstride : (long long)g.G * 3 * g.K * g.V;
+    const T* p = offset + (long long)b * bs + ((long long)grp * 3 * g.K + 3 * tap) * g.V + v;
     z = add_rn((T)bz, __ldg(p));
     y = add_rn((T)by, __ldg(p + g.V));
     x = add_rn((T)bx, __ldg(p + 2 * (long long)g.V));
@@ -115,13 +171,15 @@ struct FieldCoords {
   int nch;
   int ch[3];
   T axis[3][kMaxFieldKernelDim];  // linspace(-dil*(k/2), dil*(k/2), k) per dim
+  long long bstride;  // elements between clips; 0 = dense [B, nch, V]
+  int act;            // d2c_size_act applied to the values read (0: the map holds the scales themselves)
   __device__ __forceinline__ void get(const Geom& g, int b, int /*grp*/, int tap, int v, int bz,
                                       int by, int bx, T& z, T& y, T& x) const {
     const int k = tap % g.kw, j = (tap / g.kw) % g.kh, i = tap / (g.kw * g.kh);
-    const T* p = size_map + (long long)b * nch * g.V + v;
-    const T sz = ch[0] < 0 ? (T)1 : __ldg(p + (long long)ch[0] * g.V);
-    const T sy = ch[1] < 0 ? (T)1 : __ldg(p + (long long)ch[1] * g.V);
-    const T sx = ch[2] < 0 ? (T)1 : __ldg(p + (long long)ch[2] * g.V);
+    const T* p = size_map + (long long)b * (bstride ? bstride : (long long)nch * g.V) + v;
+    const T sz = ch[0] < 0 ? (T)1 : size_act_value(act, __ldg(p + (long long)ch[0] * g.V));
+    const T sy = ch[1] < 0 ? (T)1 : size_act_value(act, __ldg(p + (long long)ch[1] * g.V));
+    const T sx = ch[2] < 0 ? (T)1 : size_act_value(act, __ldg(p + (long long)ch[2] * g.V));
     z = add_rn((T)bz, mul_rn(axis[0][i], sub_rn(sz, (T)1)));
     y = add_rn((T)by, mul_rn(axis[1][j], sub_rn(sy, (T)1)));
     x = add_rn((T)bx, mul_rn(axis[2][k], sub_rn(sx, (T)1)));

@@ -9,12 +9,14 @@ namespace d2c {
 
 bool sm100_fwd_supported(const Geom& g, int dtype, int math_mode);
 size_t sm100_fwd_workspace(const Geom& g, int dtype, int math_mode);
+// head: where offsets / field (FieldCoords carries its own stride and activation) and mask are read from and how
+// they are activated; HeadCfg{} = the plain op.
 int sm100_fwd_offsets(const Geom& g, int math_mode, const float* x, const float* offset,
                       const float* mask, const float* w, const float* bias, float* y, void* ws,
-                      cudaStream_t st);
+                      cudaStream_t st, const HeadCfg& head = HeadCfg{});
 int sm100_fwd_field(const Geom& g, int math_mode, const FieldCoords<float>& fc, const float* x,
                     const float* mask, const float* w, const float* bias, float* y, void* ws,
-                    cudaStream_t st);
+                    cudaStream_t st, const HeadCfg& head = HeadCfg{});
 
 // Weight gradient (implicit GEMM over the sampled tile).  x_cl = channels-last bf16 staging of x,
 // recs = the call's sampling records (float4 {z, y, x, mask} per (clip, group, tap, voxel)).
@@ -30,11 +32,12 @@ size_t sm100_bwd_workspace(const Geom& g, int dtype, int math_mode, unsigned lon
 // runs first, so a caller can start reducing the parameter gradients while the data-side backward still runs.
 int sm100_bwd_offsets(const Geom& g, int math_mode, unsigned long long cap, const float* gy, const float* x, const float* offset,
                       const float* mask, const float* w, float* grad_x, float* grad_offset, float* grad_mask,
-                      float* grad_w, float* grad_bias, void* ws, cudaStream_t st, cudaEvent_t params_ready);
+                      float* grad_w, float* grad_bias, void* ws, cudaStream_t st, cudaEvent_t params_ready,
+                      const HeadCfg& head = HeadCfg{});
 int sm100_bwd_field(const Geom& g, int math_mode, unsigned long long cap, const FieldCoords<float>& fc, const float* gy,
                     const float* x, const float* mask, const float* w, float* grad_x, float* grad_size_map,
                     size_t grad_size_elems, float* grad_mask, float* grad_w, float* grad_bias, void* ws,
-                    cudaStream_t st, cudaEvent_t params_ready);
+                    cudaStream_t st, cudaEvent_t params_ready, const HeadCfg& head = HeadCfg{});
 
 // Test-only kernel: one warp waits `budget_cycles` on an mbarrier that nobody arrives on, gives up and reports
 // through the status word like every product kernel does.

@@ -331,7 +331,7 @@ __global__ void __launch_bounds__(256, kF32X ? 2 : 3)
 sample_grad_taps_kernel(Geom g, ClStrides cs, int b0, int nh, const float4* __restrict__ recs,
                         const float* __restrict__ dcol, long long dcol2_off, const void* __restrict__ x_cl_v, bool has_mask,
                         float* __restrict__ grad_coord, float* __restrict__ grad_mask, float* __restrict__ gx_cl,
-                        int field_nch, int3 field_ch, const float* __restrict__ field_axes) {
+                        int field_nch, int3 field_ch, const float* __restrict__ field_axes, HeadCfg head) {
   const int j = threadIdx.x & 7;
   const int v = blockIdx.x * 32 + (threadIdx.x >> 3);
   const int grp = blockIdx.y % g.G, bl = blockIdx.y / g.G;
@@ -456,14 +456,18 @@ sample_grad_taps_kernel(Geom g, ClStrides cs, int b0, int nh, const float4* __re
     if (active && j == 0) {
       float wts[3];
       coord_weights(G, s, wts);    // linear in the corner values: applies to the channel-summed corners
-      const long long ri = (((long long)b * g.G + grp) * g.K + tap) * g.V + v;
+      // head.*_bstride != 0: the gradients go into the gradient of the predictor's raw output (clip stride = all of
+      // its channels), the mask's through the derivative of its activation (taken from the activated value m)
       if (has_mask && grad_mask) {
         float a[8];
         sample_weights(s, a);
-        grad_mask[ri] = s.inside ? blend(G, a) : 0.f;
+        const long long ri = head.mask_bstride ? (long long)b * head.mask_bstride + ((long long)grp * g.K + tap) * g.V + v
+                                               : (((long long)b * g.G + grp) * g.K + tap) * g.V + v;
+        grad_mask[ri] = s.inside ? blend(G, a) * mask_act_slope(head.mask_act, m) : 0.f;
       }
       if constexpr (!FieldOut) {
-        float* go = grad_coord + (((long long)b * g.G + grp) * 3 * g.K + 3 * tap) * g.V + v;
+        float* go = grad_coord + (head.geo_bstride ? (long long)b * head.geo_bstride + ((long long)grp * 3 * g.K + 3 * tap) * g.V + v
+                                                   : (((long long)b * g.G + grp) * 3 * g.K + 3 * tap) * g.V + v);
         go[0] = m * wts[0];
         go[g.V] = m * wts[1];
         go[2 * (long long)g.V] = m * wts[2];
@@ -478,7 +482,7 @@ sample_grad_taps_kernel(Geom g, ClStrides cs, int b0, int nh, const float4* __re
   }
   if constexpr (FieldOut) {
     if (active && j == 0) {
-      float* gs = grad_coord + (long long)b * field_nch * g.V + v;
+      float* gs = grad_coord + (long long)b * (head.geo_bstride ? head.geo_bstride : (long long)field_nch * g.V) + v;
       if (field_ch.x >= 0) atomicAdd(gs + (long long)field_ch.x * g.V, fsum[0]);
       if (field_ch.y >= 0) atomicAdd(gs + (long long)field_ch.y * g.V, fsum[1]);
       if (field_ch.z >= 0) atomicAdd(gs + (long long)field_ch.z * g.V, fsum[2]);
@@ -503,6 +507,20 @@ unstage_grad_input_kernel(int C, long long Vin, const float* __restrict__ gx_cl,
     if (v < Vin && c0 + cc < C) gx[((long long)b * C + c0 + cc) * Vin + v] = tile[tx][cc];
   }
 }
+
+// grad[b, c, v] *= d size_act / d raw (raw[b, c, v]) for the field's channels (both tensors with clip stride bstride)
+__global__ void __launch_bounds__(256)
+field_act_grad_kernel(const float* __restrict__ raw, float* __restrict__ grad, long long bstride, int nch, int V, int B, int act) {
+  const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (i >= (long long)B * nch * V) return;
+  const long long b = i / ((long long)nch * V), r = i % ((long long)nch * V);
+  grad[b * bstride + r] *= size_act_slope(act, __ldg(raw + b * bstride + r));
+}
+
+template <typename Coords>
+int field_nch_of(const Coords&) { return 0; }
+template <>
+int field_nch_of<FieldCoords<float>>(const FieldCoords<float>& c) { return c.nch; }
 
 struct BwdPlan {
   int nh, S, NT, KB, KBT, NB, tiles_per_clip, tmem_cols, smem_bytes, clips_per_chunk;
@@ -543,7 +561,8 @@ bool make_bwd_plan(const Geom& g, unsigned long long cap, bool x3, BwdPlan* pl) 
 template <typename Coords, bool FieldOut>
 int run_bwd(const Geom& g, bool x3, const Coords& coords, unsigned long long cap, const float* gy, const float* x,
             const float* mask, const float* w, float* grad_x, float* grad_coord, size_t grad_coord_elems,
-            float* grad_mask, float* grad_w, float* grad_bias, void* ws, cudaStream_t st, cudaEvent_t params_ready) {
+            float* grad_mask, float* grad_w, float* grad_bias, void* ws, cudaStream_t st, cudaEvent_t params_ready,
+            const HeadCfg& head, const float* raw_field) {
   BwdPlan pl;
   if (!make_bwd_plan(g, cap, x3, &pl)) return D2C_ERR_MODE;
   uint8_t* wsp = reinterpret_cast<uint8_t*>(ws);
@@ -575,7 +594,13 @@ int run_bwd(const Geom& g, bool x3, const Coords& coords, unsigned long long cap
 
   prof_mark(st, "bwd_stage_operands");
   D2C_CUDA_TRY(cudaMemsetAsync(gx_cl, 0, (size_t)g.B * g.Vin * g.Cin * 4, st));
-  if (FieldOut) D2C_CUDA_TRY(cudaMemsetAsync(grad_coord, 0, sizeof(float) * grad_coord_elems, st));
+  if (FieldOut) {
+    if (head.geo_bstride)      // the field's gradient channels inside the raw gradient: nch planes per clip
+      D2C_CUDA_TRY(cudaMemset2DAsync(grad_coord, sizeof(float) * head.geo_bstride, 0, sizeof(float) * field_nch_of(coords) * g.V,
+                                     g.B, st));
+    else
+      D2C_CUDA_TRY(cudaMemsetAsync(grad_coord, 0, sizeof(float) * grad_coord_elems, st));
+  }
   if (grad_bias) D2C_CUDA_TRY(cudaMemsetAsync(grad_bias, 0, sizeof(float) * g.Cout, st));
   {
     dim3 grid((unsigned)((g.Vin + 31) / 32), (unsigned)((g.Cin + 63) / 64), (unsigned)g.B);
@@ -584,7 +609,7 @@ int run_bwd(const Geom& g, bool x3, const Coords& coords, unsigned long long cap
     else
       stage_input_cl_f16_kernel<<<grid, 256, 0, st>>>(g.Cin, g.Vin, x, reinterpret_cast<__half*>(x_cl));
     D2C_LAUNCH_CHECK();
-    if ((rc = launch_sample_records(g, coords, mask, recs, gat, st, x3))) return rc;
+    if ((rc = launch_sample_records(g, coords, mask, head, recs, gat, st, x3))) return rc;
   }
   // The parameter gradients come first: the weight gradient (tensor-core implicit GEMM over the re-sampled tile)
   // needs only the records and the staged input, and its grad_out staging pass also sums grad_bias.  A caller that
@@ -633,20 +658,29 @@ int run_bwd(const Geom& g, bool x3, const Coords& coords, unsigned long long cap
     if (pl.pairg && x3)
       sample_grad_taps_kernel<FieldOut, true, true><<<sgrid, 256, 0, st>>>(g, cs, b0, pl.nh, recs, dcol, dcol2_off, x_cl,
                                                                            mask != nullptr, grad_coord, grad_mask,
-                                                                           gx_cl, field_nch, field_ch, axes_dev);
+                                                                           gx_cl, field_nch, field_ch, axes_dev, head);
     else if (pl.pairg)
       sample_grad_taps_kernel<FieldOut, false, true><<<sgrid, 256, 0, st>>>(g, cs, b0, pl.nh, recs, dcol, dcol2_off, x_cl,
                                                                             mask != nullptr, grad_coord, grad_mask,
-                                                                            gx_cl, field_nch, field_ch, axes_dev);
+                                                                            gx_cl, field_nch, field_ch, axes_dev, head);
     else if (x3)
       sample_grad_taps_kernel<FieldOut, true><<<sgrid, 256, 0, st>>>(g, cs, b0, pl.nh, recs, dcol, dcol2_off, x_cl,
                                                                      mask != nullptr, grad_coord, grad_mask, gx_cl,
-                                                                     field_nch, field_ch, axes_dev);
+                                                                     field_nch, field_ch, axes_dev, head);
     else
       sample_grad_taps_kernel<FieldOut, false><<<sgrid, 256, 0, st>>>(g, cs, b0, pl.nh, recs, dcol, dcol2_off, x_cl,
                                                                       mask != nullptr, grad_coord, grad_mask, gx_cl,
-                                                                      field_nch, field_ch, axes_dev);
+                                                                      field_nch, field_ch, axes_dev, head);
     D2C_LAUNCH_CHECK();
+  }
+  if constexpr (FieldOut) {
+    if (head.size_act != 0 && raw_field) {      // chain rule through the size activation, on the summed gradient
+      const long long n = (long long)g.B * field_nch * g.V;
+      field_act_grad_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(
+          raw_field, grad_coord, head.geo_bstride ? head.geo_bstride : (long long)field_nch * g.V, field_nch, g.V, g.B,
+          head.size_act);
+      D2C_LAUNCH_CHECK();
+    }
   }
   prof_mark(st, "bwd_unstage_grad_input");
   {
@@ -686,18 +720,19 @@ size_t sm100_bwd_workspace(const Geom& g, int dtype, int math_mode, unsigned lon
 
 int sm100_bwd_offsets(const Geom& g, int math_mode, unsigned long long cap, const float* gy, const float* x, const float* offset,
                       const float* mask, const float* w, float* grad_x, float* grad_offset, float* grad_mask,
-                      float* grad_w, float* grad_bias, void* ws, cudaStream_t st, cudaEvent_t params_ready) {
-  OffsetCoords<float> oc{offset};
+                      float* grad_w, float* grad_bias, void* ws, cudaStream_t st, cudaEvent_t params_ready,
+                      const HeadCfg& head) {
+  OffsetCoords<float> oc{offset, head.geo_bstride};
   return run_bwd<OffsetCoords<float>, false>(g, bwd_use_x3(g, math_mode, cap), oc, cap, gy, x, mask, w, grad_x, grad_offset, 0, grad_mask, grad_w,
-                                             grad_bias, ws, st, params_ready);
+                                             grad_bias, ws, st, params_ready, head, nullptr);
 }
 
 int sm100_bwd_field(const Geom& g, int math_mode, unsigned long long cap, const FieldCoords<float>& fc, const float* gy,
                     const float* x, const float* mask, const float* w, float* grad_x, float* grad_size_map,
                     size_t grad_size_elems, float* grad_mask, float* grad_w, float* grad_bias, void* ws,
-                    cudaStream_t st, cudaEvent_t params_ready) {
+                    cudaStream_t st, cudaEvent_t params_ready, const HeadCfg& head) {
   return run_bwd<FieldCoords<float>, true>(g, bwd_use_x3(g, math_mode, cap), fc, cap, gy, x, mask, w, grad_x, grad_size_map, grad_size_elems,
-                                           grad_mask, grad_w, grad_bias, ws, st, params_ready);
+                                           grad_mask, grad_w, grad_bias, ws, st, params_ready, head, fc.size_map);
 }
 
 }  // namespace d2c

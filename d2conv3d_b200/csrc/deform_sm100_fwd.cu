@@ -192,8 +192,8 @@ bool pick_variant(const Geom& g, int math_mode, bool* x3, Plan* pl) {
 }
 
 template <typename Coords>
-int run_fwd(const Geom& g, int math_mode, const Coords& coords, const float* x, const float* mask, const float* w,
-            const float* bias, float* y, void* ws, cudaStream_t st) {
+int run_fwd(const Geom& g, int math_mode, const Coords& coords, const HeadCfg& head, const float* x, const float* mask,
+            const float* w, const float* bias, float* y, void* ws, cudaStream_t st) {
   bool x3 = false;
   Plan pl;
   if (!pick_variant(g, math_mode, &x3, &pl)) return D2C_ERR_MODE;
@@ -270,7 +270,7 @@ int run_fwd(const Geom& g, int math_mode, const Coords& coords, const float* x, 
                                                                               pl.dual ? 64 : g.cpg, pl.nh, w, w_sw);
       D2C_LAUNCH_CHECK();
     }
-    if ((rc = launch_sample_records(g, coords, mask, nullptr, recs, st, x3))) return rc;
+    if ((rc = launch_sample_records(g, coords, mask, head, nullptr, recs, st, x3))) return rc;
     if (!whole_tiles_only) D2C_CUDA_TRY(cudaMemsetAsync(y, 0, sizeof(float) * (size_t)g.B * g.Cout * g.V, st));
   }
 
@@ -320,14 +320,15 @@ size_t sm100_fwd_workspace(const Geom& g, int dtype, int math_mode) {
 }
 
 int sm100_fwd_offsets(const Geom& g, int math_mode, const float* x, const float* offset, const float* mask,
-                      const float* w, const float* bias, float* y, void* ws, cudaStream_t st) {
-  OffsetCoords<float> oc{offset};
-  return run_fwd(g, math_mode, oc, x, mask, w, bias, y, ws, st);
+                      const float* w, const float* bias, float* y, void* ws, cudaStream_t st, const HeadCfg& head) {
+  OffsetCoords<float> oc{offset, head.geo_bstride};
+  return run_fwd(g, math_mode, oc, head, x, mask, w, bias, y, ws, st);
 }
 
 int sm100_fwd_field(const Geom& g, int math_mode, const FieldCoords<float>& fc, const float* x,
-                    const float* mask, const float* w, const float* bias, float* y, void* ws, cudaStream_t st) {
-  return run_fwd(g, math_mode, fc, x, mask, w, bias, y, ws, st);
+                    const float* mask, const float* w, const float* bias, float* y, void* ws, cudaStream_t st,
+                    const HeadCfg& head) {
+  return run_fwd(g, math_mode, fc, head, x, mask, w, bias, y, ws, st);
 }
 
 // ---- wait-expiry self-test ------------------------------------------------------------------------

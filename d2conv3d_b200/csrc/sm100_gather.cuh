@@ -39,8 +39,8 @@ __device__ __forceinline__ __half2 bits_h2(uint32_t u) { return *reinterpret_cas
 // and all groups, computing the position, corners and weights once and applying each group's modulation.
 template <typename Coords, bool kShared>
 static __global__ void __launch_bounds__(256)
-sample_records_kernel(Geom g, Coords coords, const float* __restrict__ mask, float4* __restrict__ pos,
-                      uint4* __restrict__ gat, int f32_weights) {
+sample_records_kernel(Geom g, Coords coords, const float* __restrict__ mask, long long mask_bstride, int mask_act,
+                      float4* __restrict__ pos, uint4* __restrict__ gat, int f32_weights) {
   const int v = blockIdx.x * 256 + threadIdx.x;
   if (v >= g.V) return;
   const int tap = kShared ? blockIdx.y : blockIdx.y % g.K, b = blockIdx.z;
@@ -67,7 +67,10 @@ sample_records_kernel(Geom g, Coords coords, const float* __restrict__ mask, flo
   const int voff = ((cz * g.H + cy) * g.W + cx) * g.Cin;
   for (int grp = grp_beg; grp < grp_end; ++grp) {
     const long long i = (((long long)b * g.G + grp) * g.K + tap) * g.V + v;
-    const float m = mask ? __ldg(mask + i) : 1.f;
+    // the mask as the op receives it, or the predictor's logits read in place and activated here
+    const float m = mask ? mask_act_value(mask_act, __ldg(mask + (mask_bstride ? (long long)b * mask_bstride +
+                                                          ((long long)grp * g.K + tap) * g.V + v : i)))
+                         : 1.f;
     if (pos) pos[i] = make_float4(z, y, x, m);
     if (gat) {
       uint4* o = gat + 3 * i;
@@ -97,12 +100,13 @@ template <typename T>
 struct CoordsSharedAcrossGroups<FieldCoords<T>> { static constexpr bool value = true; };
 
 template <typename Coords>
-static int launch_sample_records(const Geom& g, const Coords& coords, const float* mask, float4* pos, uint4* gat,
-                                 cudaStream_t st, bool f32_weights = false) {
+static int launch_sample_records(const Geom& g, const Coords& coords, const float* mask, const HeadCfg& head, float4* pos,
+                                 uint4* gat, cudaStream_t st, bool f32_weights = false) {
   constexpr bool kShared = CoordsSharedAcrossGroups<Coords>::value;
   dim3 grid((unsigned)((g.V + 255) / 256), (unsigned)(kShared ? g.K : g.G * g.K), (unsigned)g.B);
   if (grid.y > 65535 || grid.z > 65535) return D2C_ERR_TOO_LARGE;
-  sample_records_kernel<Coords, kShared><<<grid, 256, 0, st>>>(g, coords, mask, pos, gat, f32_weights ? 1 : 0);
+  sample_records_kernel<Coords, kShared><<<grid, 256, 0, st>>>(g, coords, mask, head.mask_bstride, head.mask_act, pos, gat,
+                                                              f32_weights ? 1 : 0);
   D2C_LAUNCH_CHECK();
   return D2C_OK;
 }

@@ -243,6 +243,89 @@ class _DeformConv1dFunction(torch.autograd.Function):
         return (gx, goff, galpha, gw, gbias) + (None,) * 5
 
 
+class _HeadConv3dFunction(torch.autograd.Function):
+    """Deformable / dynamic-dilated conv3d that takes the predictor's RAW output: the split into geometry and mask
+    channels and their activations (network/layers.py:107-120, 171-181, 302-313) happen inside the kernels, and
+    the backward returns the gradient w.r.t. the raw tensor."""
+
+    @staticmethod
+    def forward(ctx, input, raw, weight, bias, field_mode, mask_channel0, mask_act, size_act, stride, padding,
+                dilation, groups, offset_groups):
+        input, raw, weight = input.contiguous(), raw.contiguous(), weight.contiguous()
+        bias = None if bias is None else bias.contiguous()
+        for t, nd, name in ((input, 5, "input"), (raw, 5, "deformation"), (weight, 5, "weight"), (bias, 1, "bias")):
+            if t is not None:
+                _require(t.dim() == nd, f"{name}.ndimension() == {nd}")
+                _require(t.is_cuda, f"{name}.device().is_cuda()")
+                if t.dtype != input.dtype:
+                    raise RuntimeError(f"expected scalar type {input.dtype} but found {t.dtype}")
+        if input.dtype not in (torch.float32, torch.float64):
+            raise RuntimeError(f'"deform_conv3d" not implemented for \'{input.dtype}\'')
+        _require(raw.size(0) == input.size(0), "offset.size(0) == input.size(0)")
+        _check_groups(input, weight, bias, groups)
+        desc = _lib.make_desc(input, weight, stride, padding, dilation, groups, offset_groups)
+        out_dims = _lib.output_dims(desc, "deform_conv3d")
+        if tuple(raw.shape[2:]) != out_dims:
+            raise RuntimeError(_lib.lib().d2c_status_string(-6).decode())
+        head = _lib.HeadDesc(raw.shape[1], 0, mask_channel0, _lib.MASK_ACTS[mask_act], _lib.SIZE_ACTS[size_act])
+        L = _lib.lib()
+        fm = -1 if field_mode is None else _lib.FIELD_MODES[field_mode]
+        op = _lib.OP_DEFORM_FWD if field_mode is None else _lib.OP_DYNDIL_FWD
+        with torch.cuda.device(input.device):
+            y = torch.empty((input.shape[0], weight.shape[0]) + out_dims, dtype=input.dtype, device=input.device)
+            ws, ws_bytes = _lib.head_workspace(op, desc, head, max(fm, 0), input.device)
+            args = (_lib.ptr(input), _lib.ptr(raw), _lib.ptr(weight), _lib.ptr(bias), _lib.ptr(y), _lib.ptr(ws), ws_bytes,
+                    _lib.stream_of(input))
+            if field_mode is None:
+                rc = L.d2c_deform_conv3d_head_fwd(ctypes.byref(desc), ctypes.byref(head), *args)
+            else:
+                rc = L.d2c_dyn_dilated_conv3d_head_fwd(ctypes.byref(desc), ctypes.byref(head), fm, *args)
+            _lib.check(rc, "deform_conv3d (fused head) forward")
+        ctx.save_for_backward(input, raw, weight, bias)
+        ctx.desc, ctx.head, ctx.fm = desc, head, fm
+        return y
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, grad_out):
+        input, raw, weight, bias = ctx.saved_tensors
+        desc, head, fm = ctx.desc, ctx.head, ctx.fm
+        grad_out = grad_out.contiguous()
+        L = _lib.lib()
+        op = _lib.OP_DEFORM_BWD if fm < 0 else _lib.OP_DYNDIL_BWD
+        with torch.cuda.device(input.device):
+            gx, graw, gw = torch.empty_like(input), torch.empty_like(raw), torch.empty_like(weight)
+            gbias = None if bias is None else torch.empty_like(bias)
+            ws, ws_bytes = _lib.head_workspace(op, desc, head, max(fm, 0), input.device)
+            ev = _new_event(torch.cuda.current_stream(input.device))
+            args = (_lib.ptr(grad_out), _lib.ptr(input), _lib.ptr(raw), _lib.ptr(weight), _lib.ptr(gx), _lib.ptr(graw),
+                    _lib.ptr(gw), _lib.ptr(gbias), _lib.ptr(ws), ws_bytes, _lib.stream_of(input),
+                    ctypes.c_void_p(ev.cuda_event))
+            if fm < 0:
+                rc = L.d2c_deform_conv3d_head_bwd(ctypes.byref(desc), ctypes.byref(head), *args)
+            else:
+                rc = L.d2c_dyn_dilated_conv3d_head_bwd(ctypes.byref(desc), ctypes.byref(head), fm, *args)
+            _lib.check(rc, "deform_conv3d (fused head) backward")
+            _BackwardState.params_ready = ev
+        return (gx, graw, gw, gbias) + (None,) * 9
+
+
+def deform_conv3d_head(input, raw, weight, bias, field_mode, modulated, mask_act, size_act, stride, padding, dilation,
+                       groups, offset_groups):
+    """The layer's op on the predictor's raw output `raw` = [geometry channels | G*K mask logits (if modulated)]:
+    geometry = 3*G*K offsets (field_mode None) or the 1..3 channels of a dilation field ("x", "xy", "xxz", "xyz").
+    mask_act: "sigmoid" | "relu" | "tanh" | "linear" | "none"; size_act: "elu" | "relu" | "relu_plus_one" | "linear".
+    No counterpart in the reference's compiled module, which is called after the split and the activations."""
+    K = weight.shape[2] * weight.shape[3] * weight.shape[4]
+    geo = 3 * offset_groups * K if field_mode is None else _lib.FIELD_CHANNELS[field_mode]
+    want = geo + (offset_groups * K if modulated else 0)
+    if raw.dim() != 5 or raw.shape[1] != want:
+        raise RuntimeError(f"the deformation tensor must have {want} channels, got {tuple(raw.shape)}")
+    return _HeadConv3dFunction.apply(input, raw, weight, bias, field_mode, geo if modulated else -1, mask_act,
+                                     size_act if field_mode is not None else "linear", tuple(stride), tuple(padding),
+                                     tuple(dilation), int(groups), int(offset_groups))
+
+
 def deform_conv1d(input, offset, alpha, weight, bias, stride, padding, dilation, groups, offset_groups):
     """dconv_native._ops.deform_conv1d (csrc/ops/dconv1d.h:158-186, dconv1d_gpu.cu): modulated deformable conv1d
     with one offset per (offset group, tap, output position) and linear interpolation, out-of-range neighbours

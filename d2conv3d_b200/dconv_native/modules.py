@@ -23,6 +23,7 @@ import torch.nn.functional as F
 from torch.nn.modules.utils import _triple
 from torch.utils.checkpoint import checkpoint
 
+from . import _ops
 from .deform_conv import DeformConv3d
 from .grid import offsets_from_size_map
 
@@ -64,8 +65,12 @@ class _DConvBase(nn.Module):
       size_activation  "elu" | "relu" | "relu_plus_one" | "linear" (layers.py:171-181)
       deform_param_op  class of the predictor, or a ready nn.Module instance (then used as is, not initialised)
 
-    and three that only this package has: `norm` (a ready norm module instead of norm_type), `use_checkpoint`
-    (recompute the predictor in the backward, what layers.py:99 always does) and `fused_field`."""
+    and four that only this package has: `norm` (a ready norm module instead of norm_type), `use_checkpoint`
+    (recompute the predictor in the backward, what layers.py:99 always does), `fused_field` (hand the dilation field
+    to the kernels instead of expanding it to 3*K offset channels) and `fused_head` (default True: the predictor's
+    raw output goes to the op as it is -- split, mask activation and size activation happen inside the kernels,
+    forward and backward; taken when the activation is one of the named ones, the tensors are CUDA fp32 / fp64 and
+    neither `use_checkpoint` nor frozen offset components are in play, otherwise the unfused path runs)."""
 
     # variant description (overridden by subclasses)
     modulated = False      # predict a modulation mask (DCNv2)
@@ -91,6 +96,7 @@ class _DConvBase(nn.Module):
         norm = kw.pop("norm", None)
         use_checkpoint = kw.pop("use_checkpoint", False)
         fused_field = kw.pop("fused_field", True)
+        fused_head = kw.pop("fused_head", True)
         if kw:
             raise TypeError(f"unexpected keyword argument(s): {sorted(kw)}")
 
@@ -100,6 +106,8 @@ class _DConvBase(nn.Module):
         self.size_activation = size_activation
         self.use_checkpoint = use_checkpoint
         self.fused_field = fused_field
+        self.fused_head = fused_head
+        self._mask_act_name = activation if isinstance(activation, str) else None
         if norm_type not in ("BatchNorm", "GroupNorm", "none"):
             raise ValueError(f"Unexpected norm_type: '{norm_type}'")
         if norm is None and norm_type == "GroupNorm":
@@ -170,7 +178,21 @@ class _DConvBase(nn.Module):
                                         self.deform_conv.dilation)
         return geo, alpha
 
+    def _can_fuse_head(self, input):
+        return (self.fused_head and input.is_cuda and input.dtype in (torch.float32, torch.float64)
+                and not self.frozen_dims and not (self.use_checkpoint and input.requires_grad)
+                and (not self.modulated or self._mask_act_name is not None)
+                and (self.field_mode is None or self.fused_field)
+                and self.deform_conv.weight.dtype == input.dtype)
+
     def forward(self, input):
+        if self._can_fuse_head(input):
+            raw = self.deform_params(input if self.norm is None else self.norm(input))
+            dc = self.deform_conv
+            # a half-precision predictor output (autocast) is up-cast, as the reference's front-end does
+            return _ops.deform_conv3d_head(input, raw.to(input.dtype), dc.weight, dc.bias, self.field_mode,
+                                           self.modulated, self._mask_act_name or "linear", self.size_activation,
+                                           dc.stride, dc.padding, dc.dilation, dc.groups, dc.offset_groups)
         if self.use_checkpoint and input.requires_grad:
             geo, alpha = checkpoint(self._predict, input, use_reentrant=False)
         else:

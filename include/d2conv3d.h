@@ -53,6 +53,15 @@ enum d2c_field_mode {
   D2C_FIELD_XYZ = 3  /* 3 channels (z,y,x)                                 */
 };
 
+/* Activations of the deformation head (see d2c_head_desc).  Names follow network/layers.py:19-25 and :171-181. */
+enum d2c_mask_act { D2C_MASK_LINEAR = 0, D2C_MASK_SIGMOID = 1, D2C_MASK_RELU = 2, D2C_MASK_TANH = 3 };
+enum d2c_size_act {
+  D2C_SIZE_LINEAR = 0,       /* s = r                  */
+  D2C_SIZE_ELU = 1,          /* s = elu(r) + 1         */
+  D2C_SIZE_RELU = 2,         /* s = relu(r + 1)        */
+  D2C_SIZE_RELU_PLUS_ONE = 3 /* s = relu(r + 1e-3) + 1 */
+};
+
 enum d2c_status {
   D2C_OK = 0,
   D2C_ERR_NULL = -1,          /* required pointer is NULL */
@@ -257,6 +266,43 @@ int d2c_dyn_dilated_conv3d_bwd_ev(const d2c_conv_desc* desc, int field_mode, con
 /* Corner probe for the field path (see d2c_deform_conv3d_corners). */
 int d2c_dyn_dilated_conv3d_corners(const d2c_conv_desc* desc, int field_mode,
                                    const void* size_map, int32_t* corners, d2c_stream_t stream);
+
+/* ---- deformation head fused into the op ------------------------------------ */
+
+/* The reference's layers (network/layers.py:107-120 MDConv3d, :171-181 size activations, :302-313
+ * XYZSizeConditionedMDConv3d and their siblings) run a predictor convolution, split its output `raw`
+ * [B, raw_channels, Do, Ho, Wo] into geometry channels (3*G*K offsets, or the 1..3 channels of a dilation field)
+ * and G*K mask logits, apply sigmoid / relu / tanh to the logits and elu+1 / ... to the field, and only then call
+ * the op -- four elementwise passes over tensors as large as the offsets.  The *_head entry points take `raw` as it
+ * leaves the predictor: the kernels read its channels in place, activate where they read, and the backward writes
+ * grad_raw (same shape as raw, every channel, chain rule through the activations included).  On the tensor-core
+ * tier nothing activated is ever written to memory; on the CUDA-core tier the library stages the activated
+ * tensors in the workspace itself. */
+typedef struct d2c_head_desc {
+  int32_t raw_channels;   /* channels of `raw` */
+  int32_t geo_channel0;   /* first geometry channel: 3*G*K offset channels, or the field's 1..3 channels */
+  int32_t mask_channel0;  /* first of the G*K mask-logit channels; -1 = no mask */
+  int32_t mask_act;       /* enum d2c_mask_act */
+  int32_t size_act;       /* enum d2c_size_act; dilation-field entry points only */
+} d2c_head_desc;
+
+/* Workspace of the four entry points below: `op` is D2C_OP_DEFORM_FWD / _BWD / D2C_OP_DYNDIL_FWD / _BWD. */
+size_t d2c_head_workspace_bytes(int op, const d2c_conv_desc* desc, const d2c_head_desc* head, int field_mode);
+
+int d2c_deform_conv3d_head_fwd(const d2c_conv_desc* desc, const d2c_head_desc* head, const void* x, const void* raw,
+                               const void* w, const void* bias, void* y, void* workspace, size_t workspace_bytes,
+                               d2c_stream_t stream);
+int d2c_deform_conv3d_head_bwd(const d2c_conv_desc* desc, const d2c_head_desc* head, const void* grad_y, const void* x,
+                               const void* raw, const void* w, void* grad_x, void* grad_raw, void* grad_w,
+                               void* grad_bias, void* workspace, size_t workspace_bytes, d2c_stream_t stream,
+                               d2c_event_t params_ready);
+int d2c_dyn_dilated_conv3d_head_fwd(const d2c_conv_desc* desc, const d2c_head_desc* head, int field_mode, const void* x,
+                                    const void* raw, const void* w, const void* bias, void* y, void* workspace,
+                                    size_t workspace_bytes, d2c_stream_t stream);
+int d2c_dyn_dilated_conv3d_head_bwd(const d2c_conv_desc* desc, const d2c_head_desc* head, int field_mode,
+                                    const void* grad_y, const void* x, const void* raw, const void* w, void* grad_x,
+                                    void* grad_raw, void* grad_w, void* grad_bias, void* workspace,
+                                    size_t workspace_bytes, d2c_stream_t stream, d2c_event_t params_ready);
 
 /* ---- depthwise conv3d ------------------------------------------------------ */
 
