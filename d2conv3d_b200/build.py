@@ -2,8 +2,9 @@
 
     python -m d2conv3d_b200.build [--force] [--verbose] [--microbench]
 
---microbench also builds csrc/microbench/l2_rates.cu into build/l2_rates, a stand-alone program that measures the
-L2 scatter-add and gather rates which bound the sampling kernels (run it on the GPU; it is not part of the library).
+--microbench also builds the stand-alone programs of csrc/microbench into build/: l2_rates (the L2 scatter-add and
+gather rates that bound the sampling kernels) and mma_rate (clocks per tcgen05.mma of the kernels' shape).  They run
+on the GPU and are not part of the library.
 
 The library links only the CUDA runtime (statically); it has no dependency on
 torch or Python.  A GPU is not needed to build.
@@ -72,11 +73,14 @@ def build(force=False, verbose=False):
 
 def build_microbench():
     os.makedirs(OBJ_DIR, exist_ok=True)
-    out = os.path.join(OBJ_DIR, "l2_rates")
-    cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-o", out,
-           os.path.join(CSRC, "microbench", "l2_rates.cu")]
-    subprocess.run(cmd, check=True)
-    return out
+    outs = []
+    for name in ("l2_rates", "mma_rate"):
+        out = os.path.join(OBJ_DIR, name)
+        cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-o", out,
+               os.path.join(CSRC, "microbench", name + ".cu")]
+        subprocess.run(cmd, check=True)
+        outs.append(out)
+    return outs
 
 
 if __name__ == "__main__":

@@ -239,29 +239,45 @@ dw_sm100_kernel(const DwParams p) {
       //      with a header that spares the gather warps all index arithmetic
       if (lane == 0) {
         const int nq = 2 * n_my_tiles;
-        int q = 0;
-        for (; q < nq; ++q) {
-          const int tile = tile_beg + (q >> 1), sl = q & 1;
-          const int b = tile / p.tiles_per_clip, v0 = (tile % p.tiles_per_clip) * kBM;
+        // The CTA's two half-units per tile always use the same slices: everything that depends only on the slice
+        // (offset group, tap, channel offset) is computed once; the tile's clip and first voxel advance by counters.
+        // This single thread's instruction latency sits between "stage free" and "copy issued" for every half-unit,
+        // so the loop holds no integer division.
+        long long ch_off[2];
+        int tap_[2], grp_rec_[2];
+#pragma unroll
+        for (int sl = 0; sl < 2; ++sl) {
           // bf16: slice sl of the pair (an odd last slice is produced twice, second copy unused);
           // x3: channels [32 sl, 32 sl + 32) of the CTA's slice
-          const int s = kX3 ? pair : min(2 * pair + sl, p.S - 1);
-          const int h = s % p.nh, gt = s / p.nh, tap = gt % g.K, grp = gt / g.K;
+          const int sidx = kX3 ? pair : min(2 * pair + sl, p.S - 1);
+          const int h = sidx % p.nh, gt = sidx / p.nh, tap = gt % g.K, grp = gt / g.K;
           // slices of two 32-channel groups: the half-unit's channels belong to group 2 grp + sl
-          const int cpg = p.pairg ? kBK : g.cpg, grp_rec = p.pairg ? 2 * grp + sl : grp;
-          const int sr = q % kRStages;
+          const int cpg = p.pairg ? kBK : g.cpg;
+          ch_off[sl] = (long long)grp * cpg + h * kBK + (kX3 ? sl * 32 : 0);
+          tap_[sl] = tap;
+          grp_rec_[sl] = kDual ? grp : (p.pairg ? 2 * grp + sl : grp);
+        }
+        int b = tile_beg / p.tiles_per_clip, v0 = (tile_beg % p.tiles_per_clip) * kBM;
+        int q = 0;
+        for (; q < nq; ++q) {
+          const int sl = q & 1;
+          const int sr = q & (kRStages - 1);
           if (!ptx::mbar_wait(r_empty(sr), ((q / kRStages) & 1) ^ 1, abort_flag, 200)) break;
           const int rows = min(kBM, g.V - v0);
           uint8_t* hdr = base_ptr + rec_off + sr * kRStage + hdr_off;
-          *reinterpret_cast<long long*>(hdr) = (long long)b * g.Vin * g.Cin + grp * cpg + h * kBK + (kX3 ? sl * 32 : 0);
+          *reinterpret_cast<long long*>(hdr) = (long long)b * g.Vin * g.Cin + ch_off[sl];
           *reinterpret_cast<int*>(hdr + 8) = rows;
           ptx::mbar_arrive_expect_tx(r_full(sr), (uint32_t)rows * 48u * (uint32_t)(1 + kDual));
 #pragma unroll
           for (int set = 0; set <= kDual; ++set) {
-            const int og = kDual ? 2 * grp + set : grp_rec;     // offset group whose records fill this set
+            const int og = kDual ? 2 * grp_rec_[sl] + set : grp_rec_[sl];     // offset group whose records fill this set
             ptx::bulk_g2s(rec_base + sr * kRStage + set * kRecBytes,
-                          p.recs + 3 * ((((long long)b * g.G + og) * g.K + tap) * g.V + v0), (uint32_t)rows * 48u,
+                          p.recs + 3 * ((((long long)b * g.G + og) * g.K + tap_[sl]) * g.V + v0), (uint32_t)rows * 48u,
                           r_full(sr));
+          }
+          if (sl == 1) {                      // next tile of the range
+            v0 += kBM;
+            if (v0 >= p.tiles_per_clip * kBM) { v0 = 0; ++b; }
           }
         }
         const int issued = q;

@@ -108,53 +108,69 @@ fwd_sm100_kernel(const FwdParams p) {
    if (warp == kMmaWarpFwd) {
     // ===================== MMA issuer =====================
     if (lane == 0) {
+      // One thread drives the tensor core, so its own instruction latency is on the critical path of every unit:
+      // no integer division or modulo by run-time values in the per-unit path (ring slots and phases are carried as
+      // counters), descriptors are built from constants hoisted out of the loops.
       int seg = 0;
       uint32_t k = 0;           // units consumed so far (A and B rings advance together)
+      int sb = 0;               // weight-ring slot of unit k and its phase
+      uint32_t phb = 0;
       bool ok = true;
+      constexpr int kSteps = kX3 ? 6 : 4;
+      // K sub-blocks (16 channels = 32 bytes) of the A and B rows that meet in each MMA
+      constexpr int ka_[6] = {0, 1, kX3 ? 2 : 2, kX3 ? 3 : 3, 0, 1};   // bf16: (k,k); x3: hi*hi, lo*hi, hi*lo
+      constexpr int kb_[6] = {0, 1, kX3 ? 0 : 2, kX3 ? 1 : 3, 2, 3};
+      const int n_halves = (p.N + 255) / 256;
+      const uint32_t idesc_full = ptx::umma_idesc_bf16_f32(kBM, 256);
+      const uint32_t idesc_last = ptx::umma_idesc_bf16_f32(kBM, p.N - (n_halves - 1) * 256);
+      const uint64_t adesc0 = ptx::umma_desc_kmajor_sw128(a_base), bdesc0 = ptx::umma_desc_kmajor_sw128(b_base);
+      const uint64_t a_step = (uint64_t)(kAStageBytes >> 4), b_step = (uint64_t)(p.b_stage_bytes >> 4);
+      int s_beg = (int)(u_beg % p.S);                                   // once per CTA
       for (long long u = u_beg; ok && u < u_end; ++seg) {
-        const int s_beg = (int)(u % p.S);
         const int s_end = min((int)min((long long)p.S, s_beg + (u_end - u)), s_beg + p.seg_cap);
         u += s_end - s_beg;
         if (!ptx::mbar_wait(acc_empty, (seg & 1) ^ 1, abort_flag)) break;
         ptx::tc_fence_after();
         for (int s = s_beg; s < s_end; ++s, ++k) {
-          const int sa = k % kAStages, sb = k % p.b_stages;
+          const int sa = k & (kAStages - 1);
           if (!ptx::mbar_wait(a_full(sa), (k / kAStages) & 1, abort_flag)) { ok = false; break; }
-          if (!ptx::mbar_wait(b_full(sb), (k / p.b_stages) & 1, abort_flag)) { ok = false; break; }
+          if (!ptx::mbar_wait(b_full(sb), phb, abort_flag)) { ok = false; break; }
           ptx::tc_fence_after();
-          const uint64_t adesc = ptx::umma_desc_kmajor_sw128(a_base + sa * kAStageBytes);
-          // K sub-blocks (16 channels = 32 bytes) of the A and B rows that meet in each MMA
-          constexpr int kSteps = kX3 ? 6 : 4;
-          constexpr int ka_[6] = {0, 1, kX3 ? 2 : 2, kX3 ? 3 : 3, 0, 1};   // bf16: (k,k); x3: hi*hi, lo*hi, hi*lo
-          constexpr int kb_[6] = {0, 1, kX3 ? 0 : 2, kX3 ? 1 : 3, 2, 3};
+          // descriptor address fields count 16-byte units: a stage further along adds stage_bytes / 16
+          const uint64_t adesc = adesc0 + a_step * (uint64_t)sa;
+          const uint64_t bdesc = bdesc0 + b_step * (uint64_t)sb;
 #pragma unroll
           for (int kk = 0; kk < kSteps; ++kk) {
-            for (int n0 = 0; n0 < p.N; n0 += 256) {
-              const int nc = min(256, p.N - n0);
-              const uint64_t bdesc = ptx::umma_desc_kmajor_sw128(b_base + sb * p.b_stage_bytes + n0 * 128);
-              ptx::umma_bf16(tmem_base + (uint32_t)n0, adesc + (uint64_t)(2 * ka_[kk]),
-                             bdesc + (uint64_t)(2 * kb_[kk]), ptx::umma_idesc_bf16_f32(kBM, nc),
-                             (s > s_beg || kk > 0) ? 1u : 0u);
-            }
+            for (int h = 0; h < n_halves; ++h)
+              ptx::umma_bf16(tmem_base + (uint32_t)(h * 256), adesc + (uint64_t)(2 * ka_[kk]),
+                             bdesc + (uint64_t)(h * (256 * 128 / 16)) + (uint64_t)(2 * kb_[kk]),
+                             h + 1 < n_halves ? idesc_full : idesc_last, (s > s_beg || kk > 0) ? 1u : 0u);
           }
           ptx::umma_commit(a_empty(sa));
           ptx::umma_commit(b_empty(sb));
+          if (++sb == p.b_stages) { sb = 0; phb ^= 1u; }
         }
         if (ok) ptx::umma_commit(acc_full);
+        s_beg = s_end == p.S ? 0 : s_end;
       }
     }
   } else if (warp == kLoadWarpFwd) {
     // ===================== weight-slice loader =====================
     if (lane == 0) {
       uint32_t k = 0;
+      int sb = 0;                       // ring slot and phase as counters: no division in the per-unit path
+      uint32_t phb = 1;                 // the wait for a FREE slot looks at the previous phase
+      int s = (int)(u_beg % p.S);       // once per CTA
+      const uint8_t* src = p.w_sw + (long long)s * p.b_stage_bytes;
       for (long long u = u_beg; u < u_end; ++u, ++k) {
-        const int s = (int)(u % p.S), sb = k % p.b_stages;
-        if (!ptx::mbar_wait(b_empty(sb), ((k / p.b_stages) & 1) ^ 1, abort_flag, 200)) break;
+        if (!ptx::mbar_wait(b_empty(sb), phb, abort_flag, 200)) break;
         ptx::mbar_arrive_expect_tx(b_full(sb), (uint32_t)p.b_stage_bytes);
-        const uint8_t* src = p.w_sw + (long long)s * p.b_stage_bytes;
         const uint32_t dst = b_base + sb * p.b_stage_bytes;
         for (int off = 0; off < p.b_stage_bytes; off += 32768)
           ptx::bulk_g2s(dst + off, src + off, (uint32_t)min(32768, p.b_stage_bytes - off), b_full(sb));
+        if (++sb == p.b_stages) { sb = 0; phb ^= 1u; }
+        src += p.b_stage_bytes;
+        if (++s == p.S) { s = 0; src = p.w_sw; }
       }
       // never leave with a bulk copy in flight: wait (bounded) for the last copies issued
       const uint32_t issued = k;
@@ -170,18 +186,21 @@ fwd_sm100_kernel(const FwdParams p) {
     // kRStages units ahead of the gather warps, so the producers read them from shared memory.
     if (lane == 0) {
       uint32_t k = 0;
+      // position of the first unit, once per CTA; then everything advances by counters (this single thread's
+      // instruction latency sits between "stage free" and "copy issued" for every unit: no division in the loop)
+      int s = (int)(u_beg % p.S);
+      const int tile0 = (int)(u_beg / p.S);
+      int b = tile0 / p.tiles_per_clip, v0 = (tile0 % p.tiles_per_clip) * kBM;
+      int h = s % p.nh, tap = (s / p.nh) % g.K, grp = (s / p.nh) / g.K;   // dual: grp is the index of a group PAIR
+      const long long grp_ch = kDual ? 2 * g.cpg : g.cpg;
       for (long long u = u_beg; u < u_end; ++u, ++k) {
-        const int tile = (int)(u / p.S), s = (int)(u % p.S);
-        const int b = tile / p.tiles_per_clip, v0 = (tile % p.tiles_per_clip) * kBM;
-        const int gt = s / p.nh, tap = gt % g.K, grp = gt / g.K;      // dual: grp is the index of a group PAIR
-        const int sr = k % kRStages;
+        const int sr = k & (kRStages - 1);
         if (!ptx::mbar_wait(r_empty(sr), ((k / kRStages) & 1) ^ 1, abort_flag, 200)) break;
-        const int rows = min(kBM, g.V - v0), h = s % p.nh;
+        const int rows = min(kBM, g.V - v0);
         // unit header for the gather warps (no index arithmetic there); ordered before their reads by the
         // release of the arrive below and the acquire of their wait
         uint8_t* hdr = base_ptr + rec_off + sr * kRStage + hdr_off;
-        *reinterpret_cast<long long*>(hdr) =
-            (long long)b * g.Vin * g.Cin + grp * (kDual ? 2 * g.cpg : g.cpg) + h * kUnitCh;
+        *reinterpret_cast<long long*>(hdr) = (long long)b * g.Vin * g.Cin + grp * grp_ch + h * kUnitCh;
         *reinterpret_cast<int*>(hdr + 8) = rows;
         const uint32_t bytes = (uint32_t)rows * 48u;
         ptx::mbar_arrive_expect_tx(r_full(sr), bytes * (uint32_t)(1 + kDual));
@@ -190,6 +209,16 @@ fwd_sm100_kernel(const FwdParams p) {
           const int og = kDual ? 2 * grp + set : grp;      // offset group whose records fill this set
           ptx::bulk_g2s(rec_base + sr * kRStage + set * kRecBytes,
                         p.recs + 3 * ((((long long)b * g.G + og) * g.K + tap) * g.V + v0), bytes, r_full(sr));
+        }
+        // next unit: (h, tap, grp) count through the tile's slices, then the next tile of the clip / next clip
+        if (++h == p.nh) {
+          h = 0;
+          if (++tap == g.K) { tap = 0; ++grp; }
+        }
+        if (++s == p.S) {
+          s = 0; h = 0; tap = 0; grp = 0;
+          v0 += kBM;
+          if (v0 >= p.tiles_per_clip * kBM) { v0 = 0; ++b; }
         }
       }
       const uint32_t issued = k;
