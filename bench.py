@@ -219,18 +219,19 @@ def run_reference_arm(args):
 TRAFFIC_SOURCE = "ncu --set full capture of this bench's C2 step, one launch per kernel, both math modes"
 TRAFFIC_PER_LAUNCH = {       # (phase, math mode) -> DRAM read + write bytes of one launch
     # fp32-parity mode, Cout = 512: the gradient columns arrive as two partial buffers (2 x 1.43 GB read)
-    ("bwd_sample_grad", "bf16"): 1.603e9 + 0.137e9, ("bwd_sample_grad", "auto"): 3.065e9 + 0.142e9,
-    ("bwd_sample_grad", "bf16x3"): 3.065e9 + 0.142e9,
-    ("fwd_sm100_fused", "bf16"): 0.420e9 + 0.056e9, ("fwd_sm100_fused", "auto"): 1.141e9 + 0.070e9,
-    ("bwd_dcol_sm100", "bf16"): 0.076e9 + 1.382e9, ("bwd_dw_sm100", "bf16"): 0.430e9 + 0.073e9,
-    ("bwd_dw_sm100", "auto"): 0.554e9 + 0.066e9,
-    ("bwd_dcol_sm100", "auto"): 2 * (0.088e9 + 1.384e9), ("bwd_dcol_sm100", "bf16x3"): 2 * (0.088e9 + 1.384e9),
+    ("bwd_sample_grad", "bf16"): 1.603e9 + 0.137e9, ("bwd_sample_grad", "auto"): 3.065e9 + 0.143e9,
+    ("bwd_sample_grad", "bf16x3"): 3.065e9 + 0.143e9,
+    ("fwd_sm100_fused", "bf16"): 0.419e9 + 0.053e9, ("fwd_sm100_fused", "auto"): 1.349e9 + 0.219e9,
+    ("fwd_sm100_fused", "bf16x3"): 1.349e9 + 0.219e9,
+    ("bwd_dcol_sm100", "bf16"): 0.088e9 + 1.382e9, ("bwd_dw_sm100", "bf16"): 0.430e9 + 0.073e9,
+    ("bwd_dw_sm100", "auto"): 0.592e9 + 0.127e9, ("bwd_dw_sm100", "bf16x3"): 0.592e9 + 0.127e9,
+    ("bwd_dcol_sm100", "auto"): 2 * (0.086e9 + 1.382e9), ("bwd_dcol_sm100", "bf16x3"): 2 * (0.086e9 + 1.382e9),
 }
 # The sampling-gradient kernel's real limiter: every live corner of every sample adds 64 fp32 channels into the
 # L2-resident grad_input accumulator.  payload_bytes = corners inside the volume for the benchmark's offsets
 # (5.69 of 8 per sample on average at sigma = 2 voxels, D = 8) x 5.6 M samples x 256 B; rate = what
-# red.global.add.v4.f32 sustains on this part for exactly this access pattern (microbenchmark, 11.5 GB in 1.70 ms).
-SCATTER = {"payload_bytes": 5.687 * 2 * 8 * 27 * 12960 * 256, "rate_gbs": 6747.0,
+# red.global.add.v4.f32 sustains on this part for exactly this access pattern (microbenchmark, 11.5 GB in 1.69 ms).
+SCATTER = {"payload_bytes": 5.687 * 2 * 8 * 27 * 12960 * 256, "rate_gbs": 6773.0,
            "source": "d2conv3d_b200/csrc/microbench/l2_rates.cu on a B200 of this pool"}
 
 PHASE_WORK = {
