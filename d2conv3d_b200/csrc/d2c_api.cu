@@ -85,6 +85,27 @@ static int status_take() {
     if (_st) return _st;                       \
   } while (0)
 
+// ---- sample cache binding ------------------------------------------------------------------------
+// d2c_bind_sample_cache() parks the caller's cache in a thread-local slot; the next deformable / dilation-field
+// forward or backward call of the same thread takes it for its own duration (a forward first marks it empty).
+static thread_local SampleCache* g_bound_cache = nullptr;
+static thread_local SampleCache* g_current_cache = nullptr;
+
+SampleCache* current_sample_cache() { return g_current_cache; }
+
+namespace {
+struct SampleCacheScope {
+  explicit SampleCacheScope(bool forward) {
+    g_current_cache = g_bound_cache;
+    g_bound_cache = nullptr;
+    if (forward && g_current_cache) g_current_cache->format = 0;
+  }
+  ~SampleCacheScope() { g_current_cache = nullptr; }
+  SampleCacheScope(const SampleCacheScope&) = delete;
+  SampleCacheScope& operator=(const SampleCacheScope&) = delete;
+};
+}  // namespace
+
 int device_sm_count(int* out) {
   static std::atomic<int> cache[kMaxDevices];
   int dev = -1;
@@ -302,11 +323,34 @@ int d2c_get_math_mode(void) { return g_math_mode.load(); }
 uint64_t d2c_get_max_intermediate_elements(void) { return g_max_intermediate.load(); }
 void d2c_set_max_intermediate_elements(uint64_t n) { g_max_intermediate.store(n ? n : 1); }
 
+// ---- sample cache ----------------------------------------------------------------------------------
+
+size_t d2c_sample_cache_bytes(const d2c_conv_desc* desc) {
+  Geom g;
+  if (!desc || make_geom(desc, &g, false) || desc->dtype != D2C_F32) return 0;
+  const int mode = g_math_mode.load();
+  const unsigned long long cap = g_max_intermediate.load();
+  // the image is a column matrix in 16 bits: the cap on intermediate elements applies to it
+  if ((unsigned long long)g.B * g.Cin * g.K * g.V > cap) return 0;
+  bool fx3 = false, bx3 = false;
+  if (!sm100_fwd_variant(g, mode, &fx3) || !sm100_bwd_variant(g, mode, cap, &bx3) || fx3 != bx3) return 0;
+  int np = 0;
+  size_t bytes = 0;
+  return sm100_sample_image_plan(g, fx3, &np, &bytes) ? bytes : 0;
+}
+
+int d2c_bind_sample_cache(d2c_sample_cache* cache) {
+  static_assert(sizeof(d2c_sample_cache) == sizeof(SampleCache), "public and internal cache structs differ");
+  g_bound_cache = reinterpret_cast<SampleCache*>(cache);
+  return D2C_OK;
+}
+
 // ---- deformable conv ---------------------------------------------------------------------------
 
 int d2c_deform_conv3d_fwd(const d2c_conv_desc* desc, const void* x, const void* offset,
                           const void* mask, const void* w, const void* bias, void* y,
                           void* workspace, size_t workspace_bytes, d2c_stream_t stream) {
+  SampleCacheScope cache_scope(true);
   if (!desc || !x || !offset || !w || !y) return D2C_ERR_NULL;
   Geom g;
   int rc = make_geom(desc, &g, false);
@@ -344,6 +388,7 @@ int d2c_deform_conv3d_bwd_ev(const d2c_conv_desc* desc, const void* grad_y, cons
                              void* grad_offset, void* grad_mask, void* grad_w, void* grad_bias,
                              void* workspace, size_t workspace_bytes, d2c_stream_t stream,
                              d2c_event_t params_ready) {
+  SampleCacheScope cache_scope(false);
   if (!desc || !grad_y || !x || !offset || !w || !grad_x || !grad_offset || !grad_w) return D2C_ERR_NULL;
   if (mask && !grad_mask) return D2C_ERR_NULL;
   Geom g;
@@ -467,6 +512,7 @@ int d2c_dyn_dilated_conv3d_fwd(const d2c_conv_desc* desc, int field_mode, const 
                                const void* size_map, const void* mask, const void* w,
                                const void* bias, void* y, void* workspace, size_t workspace_bytes,
                                d2c_stream_t stream) {
+  SampleCacheScope cache_scope(true);
   if (!desc || !x || !size_map || !w || !y) return D2C_ERR_NULL;
   Geom g;
   int rc = make_geom(desc, &g, false);
@@ -507,6 +553,7 @@ int d2c_dyn_dilated_conv3d_bwd_ev(const d2c_conv_desc* desc, int field_mode, con
                                   const void* w, void* grad_x, void* grad_size_map, void* grad_mask,
                                   void* grad_w, void* grad_bias, void* workspace,
                                   size_t workspace_bytes, d2c_stream_t stream, d2c_event_t params_ready) {
+  SampleCacheScope cache_scope(false);
   if (!desc || !grad_y || !x || !size_map || !w || !grad_x || !grad_size_map || !grad_w) return D2C_ERR_NULL;
   if (mask && !grad_mask) return D2C_ERR_NULL;
   Geom g;
@@ -706,6 +753,7 @@ int head_bwd_t(const Geom& g, const d2c_head_desc* h, const HeadPlan& hp, int fi
 
 int head_fwd(const d2c_conv_desc* desc, const d2c_head_desc* head, int field_mode, bool is_field, const void* x, const void* raw,
              const void* w, const void* bias, void* y, void* workspace, size_t workspace_bytes, cudaStream_t st) {
+  SampleCacheScope cache_scope(true);
   if (!desc || !head || !x || !raw || !w || !y) return D2C_ERR_NULL;
   Geom g;
   int rc = make_geom(desc, &g, false);
@@ -742,6 +790,7 @@ int head_fwd(const d2c_conv_desc* desc, const d2c_head_desc* head, int field_mod
 int head_bwd(const d2c_conv_desc* desc, const d2c_head_desc* head, int field_mode, bool is_field, const void* gy, const void* x,
              const void* raw, const void* w, void* gx, void* graw, void* gw, void* gbias, void* workspace,
              size_t workspace_bytes, cudaStream_t st, cudaEvent_t params_ready) {
+  SampleCacheScope cache_scope(false);
   if (!desc || !head || !gy || !x || !raw || !w || !gx || !graw || !gw) return D2C_ERR_NULL;
   Geom g;
   int rc = make_geom(desc, &g, false);

@@ -581,6 +581,7 @@ int run_bwd(const Geom& g, bool x3, const Coords& coords, unsigned long long cap
   ptx::bind_status_sink();
   ClStrides cs;
   cs.dz = g.H * g.W * g.Cin; cs.dy = g.W * g.Cin; cs.dx = g.Cin;
+  const void* sav = nullptr;
 
   // dilation-field variant: tap positions per dim, read by the kernel that accumulates grad_size_map
   int field_nch = 0;
@@ -609,12 +610,19 @@ int run_bwd(const Geom& g, bool x3, const Coords& coords, unsigned long long cap
     else
       stage_input_cl_f16_kernel<<<grid, 256, 0, st>>>(g.Cin, g.Vin, x, reinterpret_cast<__half*>(x_cl));
     D2C_LAUNCH_CHECK();
-    if ((rc = launch_sample_records(g, coords, mask, head, recs, gat, st, x3))) return rc;
+    // samples kept by the forward in this mode's format: the weight gradient reads them, no gather records needed
+    if (SampleCache* sc = current_sample_cache()) {
+      int np = 0;
+      size_t need = 0;
+      if (sc->data && sc->format == (x3 ? 2 : 1) && sm100_sample_image_plan(g, x3, &np, &need) && sc->bytes >= need)
+        sav = sc->data;
+    }
+    if ((rc = launch_sample_records(g, coords, mask, head, recs, sav ? nullptr : gat, st, x3))) return rc;
   }
   // The parameter gradients come first: the weight gradient (tensor-core implicit GEMM over the re-sampled tile)
   // needs only the records and the staged input, and its grad_out staging pass also sums grad_bias.  A caller that
   // reduces them across GPUs can start as soon as `params_ready` fires, under the data-side kernels below.
-  if ((rc = sm100_dw(g, x3, gy, x_cl, gat, grad_w, grad_bias, dw_ws, st))) return rc;
+  if ((rc = sm100_dw(g, x3, gy, x_cl, gat, grad_w, grad_bias, dw_ws, st, sav))) return rc;
   if (params_ready) D2C_CUDA_TRY(cudaEventRecord(params_ready, st));
   prof_mark(st, "bwd_stage_weights");
   stage_wt_img_kernel<<<dim3((unsigned)pl.KBT, (unsigned)g.Cin), 64, 64 * g.K * sizeof(float), st>>>(
@@ -700,6 +708,12 @@ static bool bwd_use_x3(const Geom& g, int math_mode, unsigned long long cap) {
   if (math_mode != D2C_MATH_BF16) return true;
   BwdPlan pl;
   return !(make_bwd_plan(g, cap, false, &pl) && sm100_dw_workspace(g, false) > 0);
+}
+
+bool sm100_bwd_variant(const Geom& g, int math_mode, unsigned long long cap, bool* x3) {
+  *x3 = bwd_use_x3(g, math_mode, cap);
+  BwdPlan pl;
+  return make_bwd_plan(g, cap, *x3, &pl) && sm100_dw_workspace(g, *x3) > 0;
 }
 
 bool sm100_bwd_supported(const Geom& g, int dtype, int math_mode, unsigned long long cap) {

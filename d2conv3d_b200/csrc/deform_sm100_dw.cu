@@ -18,6 +18,8 @@
 #include "sm100_gather.cuh"
 #include "sm100_ptx.cuh"
 
+#include <algorithm>
+
 namespace d2c {
 
 namespace {
@@ -365,6 +367,193 @@ dw_sm100_kernel(const DwParams p) {
   }
 }
 
+// ---- weight gradient from the samples the forward kept ------------------------------------------------------
+// When the forward of the same call pair wrote its blended A tiles to global memory (FwdParams::sav in
+// deform_sm100_fwd.cu), nothing is gathered or blended again: the sampled operand arrives by bulk copy like
+// grad_out does, and the kernel is a plain two-operand streaming GEMM.
+//   ring granularity = one 64-voxel block: A stage = the block's 8 KB images of the CTA's slice pair
+//     bf16 mode : [slice 0 | slice 1]                         16 KB, M = 128 rows (slice of the pair, channel)
+//     bf16x3    : [hi s0 | hi s1 | lo s0 | lo s1]             32 KB; hi and lo are two M = 128 operands that
+//                 accumulate into the SAME rows: a_hi*g_hi + a_lo*g_hi + a_hi*g_lo, three products, no lo*lo
+//   B ring = 32 KB chunks (256 co rows x 64 voxels) of the grad_out images, in the order
+//     (block, [hi, lo], chunk) -- the order stage_gy_kmajor_kernel writes them, so the q-th chunk of a CTA is
+//     one linear step further.
+constexpr int kSvThreads = 7 * 32;        // 4 epilogue warps, MMA issuer, grad_out loader, sample loader
+constexpr int kSvLoadWarp = 5, kSvSampleWarp = 6;
+constexpr int kSvBlkBytes = 8192;         // one 64-channel slice x 64 voxels
+constexpr int kSvBStages = 5;
+constexpr int kSvARingBytes = 64 * 1024;  // 4 stages of 16 KB (bf16) or 2 stages of 32 KB (bf16x3)
+
+struct DwSavedParams {
+  const uint8_t* sav;        // sample image, see FwdParams::sav
+  const uint8_t* gyk_img;    // grad_out images of stage_gy_kmajor_kernel
+  float* dws;                // [S*64][Cout] fp32, zero-initialised
+  int N, S, NCH, n_pairs, n_tiles, tiles_per_split, tmem_cols;
+};
+
+template <int kX3>
+__global__ void __launch_bounds__(kSvThreads, 1)
+dw_saved_sm100_kernel(const DwSavedParams p) {
+  constexpr int kAStage = (kX3 ? 4 : 2) * kSvBlkBytes;
+  constexpr int kASt = kSvARingBytes / kAStage;
+  constexpr int kParts = kX3 ? 2 : 1;                 // grad_out image groups per block: hi, lo
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = ptx::smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - raw);
+  const uint32_t a_base = base, b_base = base + kSvARingBytes;
+  const int bar_off = kSvARingBytes + kSvBStages * kChunkBytes;
+  const uint32_t bar_base = base + bar_off;
+  auto a_full = [&](int s) { return bar_base + 8u * s; };
+  auto a_empty = [&](int s) { return bar_base + 8u * (4 + s); };
+  auto b_full = [&](int s) { return bar_base + 8u * (8 + s); };
+  auto b_empty = [&](int s) { return bar_base + 8u * (8 + kSvBStages + s); };
+  const uint32_t acc_full = bar_base + 8u * (8 + 2 * kSvBStages);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + bar_off + 8 * (9 + 2 * kSvBStages));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + bar_off + 8 * (9 + 2 * kSvBStages) + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int pair = blockIdx.x % p.n_pairs, split = blockIdx.x / p.n_pairs;
+  const int tile_beg = split * p.tiles_per_split;
+  const int tile_end = min(p.n_tiles, tile_beg + p.tiles_per_split);
+  const int n_blocks = 2 * (tile_end - tile_beg);      // 64-voxel blocks; may be <= 0 for a trailing split
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kASt; ++s) { ptx::mbar_init(a_full(s), 1); ptx::mbar_init(a_empty(s), 1); }
+    for (int s = 0; s < kSvBStages; ++s) { ptx::mbar_init(b_full(s), 1); ptx::mbar_init(b_empty(s), 1); }
+    ptx::mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    ptx::fence_mbar_init();
+  }
+  if (warp == 0) {
+    __syncwarp();
+    ptx::tmem_alloc(ptx::smem_u32((const void*)tmem_slot), (uint32_t)p.tmem_cols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (n_blocks > 0) {
+    if (warp < kEpiWarps) {
+      // ---- epilogue (once): accumulator rows (slice of the pair, c) x columns co -> dws, vector reductions
+      if (ptx::mbar_wait(acc_full, 0, abort_flag, 1000)) {
+        ptx::tc_fence_after();
+        const int m = warp * 32 + lane;
+        const int s = 2 * pair + (m >> 6);
+        float* row = p.dws + ((long long)s * 64 + (m & 63)) * p.N;
+        for (int c0 = 0; c0 < p.N; c0 += 32) {
+          uint32_t r[32];
+          ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);
+          ptx::tmem_ld_wait();
+          if (s < p.S) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(row + c0 + 4 * i),
+                           "f"(__uint_as_float(r[4 * i])), "f"(__uint_as_float(r[4 * i + 1])),
+                           "f"(__uint_as_float(r[4 * i + 2])), "f"(__uint_as_float(r[4 * i + 3]))
+                           : "memory");
+          }
+        }
+        ptx::tc_fence_before();
+      }
+    } else if (warp == kMmaWarp) {
+      if (lane == 0) {
+        uint32_t q = 0;
+        int sb = 0;
+        uint32_t phb = 0;
+        bool ok = true;
+        for (int kb = 0; ok && kb < n_blocks; ++kb) {
+          const int sa = kb % kASt;
+          if (!ptx::mbar_wait(a_full(sa), (kb / kASt) & 1, abort_flag)) break;
+          const uint32_t a_stage = a_base + sa * kAStage;
+          for (int part = 0; ok && part < kParts; ++part) {
+            for (int c = 0; c < p.NCH; ++c, ++q) {
+              if (!ptx::mbar_wait(b_full(sb), phb, abort_flag)) { ok = false; break; }
+              ptx::tc_fence_after();
+              const uint32_t idesc = ptx::umma_idesc_bf16_f32(kBM, min(256, p.N - 256 * c)) | (1u << 15);  // A is MN-major
+              const uint64_t bdesc0 = ptx::umma_desc_kmajor_sw128(b_base + sb * kChunkBytes);
+              const uint32_t d = tmem_base + (uint32_t)(256 * c);
+#pragma unroll
+              for (int k4 = 0; k4 < 4; ++k4) {
+                // A: 16 voxels from voxel k4*16 of the block = two 8-row groups of 1024 bytes (SBO); the second
+                // slice of the pair (rows 64..127 of M) lies one 8 KB image further (LBO)
+                const uint64_t a_hi = ptx::umma_desc_mnmajor_sw128(a_stage + k4 * 2048, kSvBlkBytes, 1024);
+                const uint64_t bdesc = bdesc0 + (uint64_t)(2 * k4);
+                if (!kX3) {
+                  ptx::umma_bf16(d, a_hi, bdesc, idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
+                } else if (part == 0) {
+                  const uint64_t a_lo = ptx::umma_desc_mnmajor_sw128(a_stage + 2 * kSvBlkBytes + k4 * 2048, kSvBlkBytes, 1024);
+                  ptx::umma_bf16(d, a_hi, bdesc, idesc, (kb > 0 || k4 > 0) ? 1u : 0u);     // a_hi * g_hi
+                  ptx::umma_bf16(d, a_lo, bdesc, idesc, 1u);                                // a_lo * g_hi
+                } else {
+                  ptx::umma_bf16(d, a_hi, bdesc, idesc, 1u);                                // a_hi * g_lo
+                }
+              }
+              ptx::umma_commit(b_empty(sb));
+              if (++sb == kSvBStages) { sb = 0; phb ^= 1u; }
+            }
+          }
+          if (ok) ptx::umma_commit(a_empty(sa));
+        }
+        if (ok) ptx::umma_commit(acc_full);
+      }
+    } else if (warp == kSvLoadWarp) {
+      // ---- grad_out chunks: one linear stream per CTA
+      if (lane == 0) {
+        const int cpb = kParts * p.NCH;                       // chunks per block
+        const uint32_t nq = (uint32_t)n_blocks * (uint32_t)cpb;
+        const uint8_t* src = p.gyk_img + (long long)tile_beg * 2 * cpb * kChunkBytes;
+        uint32_t q = 0;
+        int sb = 0, c = 0;
+        uint32_t phb = 1;                                     // the wait for a FREE slot looks at the previous phase
+        for (; q < nq; ++q) {
+          if (!ptx::mbar_wait(b_empty(sb), phb, abort_flag, 100)) break;
+          const uint32_t bytes = (uint32_t)min(256, p.N - 256 * c) * 128u;
+          ptx::mbar_arrive_expect_tx(b_full(sb), bytes);
+          ptx::bulk_g2s(b_base + sb * kChunkBytes, src, bytes, b_full(sb));
+          src += kChunkBytes;
+          if (++c == p.NCH) c = 0;
+          if (++sb == kSvBStages) { sb = 0; phb ^= 1u; }
+        }
+        // never leave with a bulk copy in flight: wait (bounded) for the last copies issued
+        for (uint32_t w = (q > (uint32_t)kSvBStages ? q - kSvBStages : 0); w < q; ++w) {
+          const long long t0 = clock64();
+          while (!ptx::mbar_try_wait(b_full(w % kSvBStages), (w / kSvBStages) & 1))
+            if (clock64() - t0 > ptx::kWaitBudgetCycles) break;
+        }
+      }
+    } else if (warp == kSvSampleWarp) {
+      // ---- kept samples: the slice pair's images of every 64-voxel block of the range
+      if (lane == 0) {
+        const long long blk_stride = (long long)p.n_pairs * kAStage;   // bytes between consecutive blocks
+        const uint8_t* src = p.sav + (long long)tile_beg * 2 * blk_stride + (long long)pair * kAStage;
+        int kb = 0;
+        for (; kb < n_blocks; ++kb) {
+          const int sa = kb % kASt;
+          if (!ptx::mbar_wait(a_empty(sa), ((kb / kASt) & 1) ^ 1, abort_flag, 100)) break;
+          ptx::mbar_arrive_expect_tx(a_full(sa), (uint32_t)kAStage);
+          ptx::bulk_g2s(a_base + sa * kAStage, src, (uint32_t)kAStage, a_full(sa));
+          src += blk_stride;
+        }
+        for (int w = (kb > kASt ? kb - kASt : 0); w < kb; ++w) {
+          const long long t0 = clock64();
+          while (!ptx::mbar_try_wait(a_full(w % kASt), (w / kASt) & 1))
+            if (clock64() - t0 > ptx::kWaitBudgetCycles) break;
+        }
+      }
+    }
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag) ptx::report_device_timeout();
+  if (warp == 0) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+  }
+}
+
 // dws [(slice, c)][co] -> grad_w [co][cin][tap]   (cin = grp*cpg + h*64 + c)
 __global__ void __launch_bounds__(256)
 unstage_dw_kernel(int Cout, int Cin, int K, int cpg, int nh, int S, const float* __restrict__ dws,
@@ -430,7 +619,43 @@ bool make_dw_plan(const Geom& g, int sm_count, bool x3, DwPlan* dp) {
   return true;
 }
 
+// Work split of the saved-samples kernel: (slice pair, voxel range) items, about three waves of them, ranges of at
+// least 8 tiles, the count chosen so that the last wave is as full as possible; the fp32-parity mode ends an
+// accumulation chain after 27 tiles (24 accumulating MMAs per tile and column range -> 648, see make_dw_plan).
+void split_saved(const DwPlan& dp, int sm_count, bool x3, int* tiles_per_split, int* nsplit_out) {
+  const int n_pairs = (dp.S + 1) / 2;
+  const int chain_min = x3 ? (dp.n_tiles + 26) / 27 : 1;              // fewest ranges the chain cap allows
+  const int size_max = std::max(1, dp.n_tiles / 8);                   // most ranges of at least 8 tiles
+  const int lo = std::max(chain_min, std::min(size_max, (2 * sm_count + n_pairs - 1) / n_pairs));
+  const int hi = std::max(lo, std::min(size_max, lo + 8));
+  int best = lo;
+  double best_eff = -1.0;
+  for (int ns = lo; ns <= hi; ++ns) {
+    const int tps = (dp.n_tiles + ns - 1) / ns;
+    const long long ctas = (long long)((dp.n_tiles + tps - 1) / tps) * n_pairs;
+    const long long waves = (ctas + sm_count - 1) / sm_count;
+    const double eff = (double)ctas / (double)(waves * sm_count);
+    if (eff > best_eff + 1e-9) { best_eff = eff; best = ns; }
+  }
+  *tiles_per_split = (dp.n_tiles + best - 1) / best;
+  *nsplit_out = (dp.n_tiles + *tiles_per_split - 1) / *tiles_per_split;
+}
+
+constexpr int kSvSmemBytes = kSvARingBytes + kSvBStages * kChunkBytes + 256 + 1024;
+static_assert(kSvSmemBytes <= kSmemLimit, "saved-samples kernel: shared memory");
+
 }  // namespace
+
+bool sm100_sample_image_plan(const Geom& g, bool x3, int* n_pairs, size_t* bytes) {
+  DwPlan dp;
+  if (!make_dw_plan(g, 148, x3, &dp)) return false;
+  const int np = (dp.S + 1) / 2;
+  // block indices travel as 31-bit words through the forward's unit header
+  if ((long long)dp.n_tiles * np * 16 >= 0x7fffffffLL) return false;
+  *n_pairs = np;
+  *bytes = (size_t)dp.n_tiles * 2 * np * (x3 ? 4 : 2) * kSvBlkBytes;
+  return true;
+}
 
 size_t sm100_dw_workspace(const Geom& g, bool x3) {
   DwPlan dp;
@@ -439,7 +664,7 @@ size_t sm100_dw_workspace(const Geom& g, bool x3) {
 }
 
 int sm100_dw(const Geom& g, bool x3, const float* gy, const void* x_cl, const void* recs, float* grad_w,
-             float* grad_bias, void* ws, cudaStream_t st) {
+             float* grad_bias, void* ws, cudaStream_t st, const void* sav) {
   int sm_count = 0;
   {
     const int rc = device_sm_count(&sm_count);
@@ -465,11 +690,25 @@ int sm100_dw(const Geom& g, bool x3, const float* gy, const void* x_cl, const vo
   p.tmem_cols = dp.tmem_cols;
   p.n_pairs = dp.n_pairs; p.tiles_per_split = dp.tiles_per_split; p.NCH = dp.NCH; p.b_stage_bytes = dp.b_stage_bytes;
   p.pairg = dp.pairg ? 1 : 0;
-  prof_mark(st, "bwd_dw_sm100");
-  auto kern = x3 ? dw_sm100_kernel<1, 0> : (dp.pairg ? dw_sm100_kernel<0, 1> : dw_sm100_kernel<0, 0>);
-  D2C_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, dp.smem_bytes));
-  kern<<<dp.n_pairs * dp.nsplit, kThreads, dp.smem_bytes, st>>>(p);
-  D2C_LAUNCH_CHECK();
+  if (sav) {
+    DwSavedParams sp;
+    sp.sav = reinterpret_cast<const uint8_t*>(sav); sp.gyk_img = gyk; sp.dws = dws;
+    sp.N = g.Cout; sp.S = dp.S; sp.NCH = dp.NCH; sp.n_pairs = (dp.S + 1) / 2; sp.n_tiles = dp.n_tiles;
+    sp.tmem_cols = dp.tmem_cols;
+    int nsplit = 1;
+    split_saved(dp, sm_count, x3, &sp.tiles_per_split, &nsplit);
+    prof_mark(st, "bwd_dw_sm100_saved");
+    auto kern = x3 ? dw_saved_sm100_kernel<1> : dw_saved_sm100_kernel<0>;
+    D2C_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSvSmemBytes));
+    kern<<<sp.n_pairs * nsplit, kSvThreads, kSvSmemBytes, st>>>(sp);
+    D2C_LAUNCH_CHECK();
+  } else {
+    prof_mark(st, "bwd_dw_sm100");
+    auto kern = x3 ? dw_sm100_kernel<1, 0> : (dp.pairg ? dw_sm100_kernel<0, 1> : dw_sm100_kernel<0, 0>);
+    D2C_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, dp.smem_bytes));
+    kern<<<dp.n_pairs * dp.nsplit, kThreads, dp.smem_bytes, st>>>(p);
+    D2C_LAUNCH_CHECK();
+  }
   prof_mark(st, "bwd_dw_unstage");
   unstage_dw_kernel<<<dim3((unsigned)((dp.S * 64 + 31) / 32), (unsigned)((g.Cout + 31) / 32)), 256, 0, st>>>(
       g.Cout, g.Cin, g.K, dp.pairg ? kBK : g.cpg, dp.nh, dp.S, dws, grad_w);

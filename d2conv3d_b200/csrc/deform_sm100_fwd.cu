@@ -75,6 +75,14 @@ struct FwdParams {
                                // added to y (see run_fwd); S = no limit
   int b_stages, b_stage_bytes;
   int tmem_cols;
+  // Samples kept for the weight gradient (nullable): the blended A tiles, written to global as they are produced,
+  // in blocks of 8 KB = one 64-channel slice x 64 voxels (rows of 128 B, 16-byte chunks XOR-swizzled by row & 7):
+  //   bf16 mode:  [tile][64-voxel block][slice s, padded to 2*sav_np]
+  //   bf16x3:     [tile][64-voxel block][slice pair][hi | lo][slice of the pair]   (a unit fills half of each row)
+  // exactly the operand images deform_sm100_dw.cu bulk-copies.
+  uint8_t* sav;
+  int sav_np;                  // slice pairs of the weight gradient
+  int sav_pairg;               // bf16x3: 32 channels per offset group (a 64-channel slice spans two groups)
 };
 
 __device__ __forceinline__ void cta_unit_range(long long n_units, long long& beg, long long& end) {
@@ -281,6 +289,16 @@ int run_fwd(const Geom& g, int math_mode, const Coords& coords, const HeadCfg& h
   p.n_units = n_units;
   p.seg_cap = seg_cap;
   p.b_stages = pl.b_stages; p.b_stage_bytes = pl.b_stage_bytes; p.tmem_cols = pl.tmem_cols;
+  // keep the samples for the weight gradient when the caller bound a cache that is large enough
+  p.sav = nullptr; p.sav_np = 0; p.sav_pairg = (g.cpg == 32) ? 1 : 0;
+  if (SampleCache* sc = current_sample_cache()) {
+    sc->format = 0;
+    size_t need = 0;
+    if (sc->data && pair_clusters == 0 && sm100_sample_image_plan(g, x3, &p.sav_np, &need) && sc->bytes >= need) {
+      p.sav = reinterpret_cast<uint8_t*>(sc->data);
+      sc->format = x3 ? 2 : 1;
+    }
+  }
 
   if (pair_clusters > 0) {
     pair::PairParams pp;
@@ -303,6 +321,11 @@ int run_fwd(const Geom& g, int math_mode, const Coords& coords, const HeadCfg& h
 }
 
 }  // namespace
+
+bool sm100_fwd_variant(const Geom& g, int math_mode, bool* x3) {
+  Plan pl;
+  return pick_variant(g, math_mode, x3, &pl);
+}
 
 bool sm100_fwd_supported(const Geom& g, int dtype, int math_mode) {
   if (dtype != D2C_F32) return false;

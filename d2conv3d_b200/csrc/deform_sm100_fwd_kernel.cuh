@@ -191,6 +191,7 @@ fwd_sm100_kernel(const FwdParams p) {
       int s = (int)(u_beg % p.S);
       const int tile0 = (int)(u_beg / p.S);
       int b = tile0 / p.tiles_per_clip, v0 = (tile0 % p.tiles_per_clip) * kBM;
+      int tile = tile0;
       int h = s % p.nh, tap = (s / p.nh) % g.K, grp = (s / p.nh) / g.K;   // dual: grp is the index of a group PAIR
       const long long grp_ch = kDual ? 2 * g.cpg : g.cpg;
       for (long long u = u_beg; u < u_end; ++u, ++k) {
@@ -202,6 +203,19 @@ fwd_sm100_kernel(const FwdParams p) {
         uint8_t* hdr = base_ptr + rec_off + sr * kRStage + hdr_off;
         *reinterpret_cast<long long*>(hdr) = (long long)b * g.Vin * g.Cin + grp * grp_ch + h * kUnitCh;
         *reinterpret_cast<int*>(hdr + 8) = rows;
+        if (p.sav) {
+          // where this unit's samples go in the image kept for the weight gradient (8 KB blocks, see FwdParams)
+          int word;
+          if constexpr (kX3) {
+            // 64-channel slice of the weight gradient that holds this 32-channel unit, and which half of it
+            const int s64 = p.sav_pairg ? (grp >> 1) * g.K + tap : (grp * g.K + tap) * (p.nh >> 1) + (h >> 1);
+            const int half = p.sav_pairg ? (grp & 1) : (h & 1);
+            word = (((tile * 2 * p.sav_np + (s64 >> 1)) * 4 + (s64 & 1)) << 1) | half;
+          } else {
+            word = tile * 2 * (2 * p.sav_np) + s;
+          }
+          *reinterpret_cast<int*>(hdr + 12) = word;
+        }
         const uint32_t bytes = (uint32_t)rows * 48u;
         ptx::mbar_arrive_expect_tx(r_full(sr), bytes * (uint32_t)(1 + kDual));
 #pragma unroll
@@ -217,6 +231,7 @@ fwd_sm100_kernel(const FwdParams p) {
         }
         if (++s == p.S) {
           s = 0; h = 0; tap = 0; grp = 0;
+          ++tile;
           v0 += kBM;
           if (v0 >= p.tiles_per_clip * kBM) { v0 = 0; ++b; }
         }
@@ -240,6 +255,9 @@ fwd_sm100_kernel(const FwdParams p) {
     const int r0 = t >> 3;           // rows r0, r0 + kRowStride
     const uint32_t n_my_units = (uint32_t)(u_end - u_beg);
     bool ok = true;
+    // Samples kept for the weight gradient (p.sav != nullptr): the thread's two rows r0 and r0 + 64 are the same row
+    // of the two 64-voxel blocks of the tile, so its byte offset inside an 8 KB block is fixed.
+    const uint32_t sav_row = (uint32_t)((r0 >> 3) * 1024 + (r0 & 7) * 128);
 
     auto issue = [&](uint32_t k, int i, uint4 (&c)[8]) {
       const uint8_t* rec_base_ptr = base_ptr + rec_off + (k % kRStages) * kRStage;
@@ -274,14 +292,31 @@ fwd_sm100_kernel(const FwdParams p) {
         }
         // item j = channels 4j..4j+3: hi in 16-byte chunk j/2 (half j&1), lo in chunk 4 + j/2
         const uint32_t row_base = stage + (uint32_t)((r >> 3) * 1024 + (r & 7) * 128) + (uint32_t)((j & 1) * 8);
-        blend_split_store(c, w, row_base + ((((j >> 1)) ^ (r & 7)) << 4), row_base + (((4 + (j >> 1)) ^ (r & 7)) << 4));
+        const uint4 hl = blend_split_store(c, w, row_base + ((((j >> 1)) ^ (r & 7)) << 4),
+                                           row_base + (((4 + (j >> 1)) ^ (r & 7)) << 4));
+        if (p.sav) {
+          // image block = (tile, 64-voxel block i, slice pair, {hi, lo}, slice of the pair): a 64-channel row holds
+          // this unit's 32 channels in its half `half`; hi and lo parts lie two blocks apart
+          const int word = *reinterpret_cast<const int*>(rec_base_ptr + hdr_off + 12);
+          const int half = word & 1;
+          uint8_t* dst = p.sav + ((long long)((word >> 1) + i * p.sav_np * 4) << 13) + sav_row +
+                         (uint32_t)((((4 * half + (j >> 1)) ^ (r0 & 7)) << 4) + (j & 1) * 8);
+          __stcs(reinterpret_cast<uint2*>(dst), make_uint2(hl.x, hl.y));
+          __stcs(reinterpret_cast<uint2*>(dst + 2 * 8192), make_uint2(hl.z, hl.w));
+        }
       } else {
         uint4 w03 = make_uint4(0u, 0u, 0u, 0u), w47 = w03;       // rows past the clip end: stage bytes are stale
         if (r < rows) {
           w03 = *reinterpret_cast<const uint4*>(rec_stage + r * 48 + 16);
           w47 = *reinterpret_cast<const uint4*>(rec_stage + r * 48 + 32);
         }
-        blend_store(c, w03, w47, stage + (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((j ^ (r & 7)) << 4)));
+        const uint4 o = blend_store(c, w03, w47, stage + (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((j ^ (r & 7)) << 4)));
+        if (p.sav) {
+          // image block = (tile, 64-voxel block i, slice): the byte image of this half of the A tile
+          const int word = *reinterpret_cast<const int*>(rec_base_ptr + hdr_off + 12);
+          __stcs(reinterpret_cast<uint4*>(p.sav + ((long long)(word + i * 2 * p.sav_np) << 13) + sav_row +
+                                          (uint32_t)((j ^ (r0 & 7)) << 4)), o);
+        }
       }
     };
 

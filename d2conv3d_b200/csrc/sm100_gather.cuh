@@ -143,7 +143,8 @@ __device__ __forceinline__ void load_corners(const __half* __restrict__ xb_ch, C
   c[7] = ptx::ldg_nc_v4(p1 + dy + dx);
 }
 
-__device__ __forceinline__ void blend_store(const uint4 (&c)[8], uint4 w03, uint4 w47, uint32_t dst) {
+// Returns the 16 bytes it stored (a caller that also keeps the samples for the backward writes them to global).
+__device__ __forceinline__ uint4 blend_store(const uint4 (&c)[8], uint4 w03, uint4 w47, uint32_t dst) {
   const uint32_t w[8] = {w03.x, w03.y, w03.z, w03.w, w47.x, w47.y, w47.z, w47.w};
   __half2 acc[4];
 #pragma unroll
@@ -163,6 +164,7 @@ __device__ __forceinline__ void blend_store(const uint4 (&c)[8], uint4 w03, uint
   f = __half22float2(acc[2]); out.z = ptx::pack_bf16x2(f.x, f.y);
   f = __half22float2(acc[3]); out.w = ptx::pack_bf16x2(f.x, f.y);
   ptx::sts_v4(dst, out);
+  return out;
 }
 
 // ---- fp32-parity mode ("bf16x3"): fp32 staging, fp32 blend, bf16 hi/lo split -------------------------------
@@ -186,8 +188,9 @@ __device__ __forceinline__ void load_corners_f32(const float* __restrict__ xb_ch
 
 // w: the eight fp32 products a_j*mask (corner order 000..111, the reference's interpolation chain).
 // dst_hi / dst_lo: shared-memory addresses of the 8-byte hi and lo slots of this item.
-__device__ __forceinline__ void blend_split_store(const uint4 (&c)[8], const float (&w)[8], uint32_t dst_hi,
-                                                  uint32_t dst_lo) {
+// Returns {hi (8 bytes), lo (8 bytes)} as stored.
+__device__ __forceinline__ uint4 blend_split_store(const uint4 (&c)[8], const float (&w)[8], uint32_t dst_hi,
+                                                   uint32_t dst_lo) {
   float v[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
@@ -201,6 +204,7 @@ __device__ __forceinline__ void blend_split_store(const uint4 (&c)[8], const flo
   const uint32_t l23 = ptx::pack_bf16x2(v[2] - ptx::bf16_lo(h23), v[3] - ptx::bf16_hi(h23));
   ptx::sts_v2(dst_hi, make_uint2(h01, h23));
   ptx::sts_v2(dst_lo, make_uint2(l01, l23));
+  return make_uint4(h01, h23, l01, l23);
 }
 
 }  // namespace

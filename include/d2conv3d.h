@@ -177,6 +177,37 @@ int d2c_profile_read(d2c_profile_record* records, int max_records, int* n_record
 uint64_t d2c_get_max_intermediate_elements(void);
 void d2c_set_max_intermediate_elements(uint64_t n);
 
+/* ---- samples handed from the forward to the backward ---------------------- */
+
+/* The reference builds the column matrix of trilinear samples twice per training step: deformable_im2col in the
+ * forward (csrc/ops/dconv3d_gpu.cu:111-203) and again for the weight gradient in the backward (:1037-1060).  On the
+ * tensor-core tier the forward can instead KEEP its blended operand tiles (16-bit, the byte image its tensor-core
+ * operand has in shared memory) in a caller-owned buffer, and the weight gradient of the matching backward call
+ * streams them back with bulk copies: no second gather, no second blend.
+ *
+ *   d2c_sample_cache c = { buf, d2c_sample_cache_bytes(&desc), 0, 0 };
+ *   d2c_bind_sample_cache(&c);  d2c_deform_conv3d_fwd(...);       -- fills buf, sets c.format (0 = nothing kept)
+ *   ...
+ *   d2c_bind_sample_cache(&c);  d2c_deform_conv3d_bwd_ev(...);    -- reads buf when c.format fits the call
+ *
+ * d2c_bind_sample_cache applies to the NEXT deformable / dilation-field (plain or *_head) forward or backward call
+ * made by the calling thread and is consumed by it, whatever that call returns; `cache` must stay valid until that
+ * call has returned and `data` until the backward's work on the stream is done.  Binding NULL unbinds.  A call that
+ * cannot use the cache (CUDA-core tier, math mode changed between the two calls, buffer too small) ignores it, so
+ * results never depend on it being there; x, offsets / field / raw head output and mask passed to the backward
+ * must be the forward's, as for any backward call.
+ * d2c_sample_cache_bytes: bytes to allocate (256-byte aligned) for this shape under the current math mode and
+ * intermediate-element cap (the image holds batch*Cin*K*V elements; shapes above the cap keep nothing): 0 when the
+ * call pair would not use a cache. */
+typedef struct d2c_sample_cache {
+  void* data;
+  size_t bytes;
+  int32_t format;    /* written by the forward: 0 nothing kept, otherwise the image format */
+  int32_t reserved;
+} d2c_sample_cache;
+size_t d2c_sample_cache_bytes(const d2c_conv_desc* desc);
+int d2c_bind_sample_cache(d2c_sample_cache* cache);
+
 /* ---- modulated deformable conv3d ----------------------------------------- */
 
 /* deform_conv3d_forward_cuda, csrc/ops/dconv3d_gpu.cu:460-560.
