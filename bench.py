@@ -238,7 +238,7 @@ PHASE_WORK = {
     # phase name -> (bound, key of the algorithmic work of one launch)
     "fwd_sm100_fused": ("tensor", "F"), "fwd_generic": ("tensor", "F"),
     "bwd_dcol_sm100": ("tensor", "F"), "bwd_dcol_generic": ("tensor", "F"),
-    "bwd_dw_sm100": ("tensor", "F"), "bwd_dw_generic": ("tensor", "F"),
+    "bwd_dw_sm100": ("tensor", "F"), "bwd_dw_sm100_saved": ("tensor", "F"), "bwd_dw_generic": ("tensor", "F"),
     "bwd_sample_grad": ("hbm", "sample_grad_bytes"),
     "bwd_coord_grad_generic": ("hbm", "coord_bytes"), "bwd_col2im_generic": ("hbm", "col2im_bytes"),
 }

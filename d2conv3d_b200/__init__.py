@@ -10,13 +10,14 @@ CPU or PyTorch fallback.
 import sys
 
 from . import _lib
-from ._lib import get_math_mode, set_math_mode
+from ._lib import get_keep_samples, get_math_mode, set_keep_samples, set_math_mode
 from . import dconv_native, fast_depthwise_conv3d
 from .dconv_native import (DConv3d, DeformConv3d, MDConv3d, deform_conv3d, dyn_dilated_conv3d)
 from .fast_depthwise_conv3d import DepthwiseConv3d
 
 __all__ = ["dconv_native", "fast_depthwise_conv3d", "deform_conv3d", "dyn_dilated_conv3d", "DeformConv3d",
-           "DConv3d", "MDConv3d", "DepthwiseConv3d", "set_math_mode", "get_math_mode", "install_as_dropin"]
+           "DConv3d", "MDConv3d", "DepthwiseConv3d", "set_math_mode", "get_math_mode", "set_keep_samples", "get_keep_samples",
+           "install_as_dropin"]
 
 
 def install_as_dropin():

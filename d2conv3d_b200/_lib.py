@@ -41,6 +41,13 @@ MASK_ACTS = {"linear": 0, "none": 0, "sigmoid": 1, "relu": 2, "tanh": 3}
 SIZE_ACTS = {"linear": 0, "elu": 1, "relu": 2, "relu_plus_one": 3}
 
 
+class SampleCacheStruct(ctypes.Structure):
+    """d2c_sample_cache"""
+
+    _fields_ = [("data", ctypes.c_void_p), ("bytes", ctypes.c_size_t), ("format", ctypes.c_int32),
+                ("reserved", ctypes.c_int32)]
+
+
 class ProfileRecord(ctypes.Structure):
     """d2c_profile_record"""
 
@@ -77,6 +84,9 @@ def lib():
         L.d2c_get_max_intermediate_elements.restype = ctypes.c_uint64
         L.d2c_set_max_intermediate_elements.argtypes = [ctypes.c_uint64]
         L.d2c_set_max_intermediate_elements.restype = None
+        L.d2c_sample_cache_bytes.argtypes = [dp]
+        L.d2c_sample_cache_bytes.restype = sz
+        L.d2c_bind_sample_cache.argtypes = [ctypes.POINTER(SampleCacheStruct)]
         L.d2c_deform_conv3d_fwd.argtypes = [dp] + [vp] * 7 + [sz, vp]
         L.d2c_deform_conv3d_bwd.argtypes = [dp] + [vp] * 11 + [sz, vp]
         L.d2c_deform_conv3d_bwd_ev.argtypes = [dp] + [vp] * 11 + [sz, vp, vp]
@@ -159,6 +169,54 @@ def head_workspace(op, desc, head, field_mode, device):
     if n == 0:
         return None, 0
     return torch.empty(n, dtype=torch.uint8, device=device), n
+
+
+_keep_samples = True
+
+
+def set_keep_samples(on):
+    """Whether a forward that will be differentiated keeps its blended samples (16-bit, B*Cin*K*V elements) for the
+    weight gradient of its backward -- the reference computes them twice.  On by default; switch it off to trade the
+    backward's speed for that memory.  Shapes above the intermediate-element cap never keep them."""
+    global _keep_samples
+    _keep_samples = bool(on)
+
+
+def get_keep_samples():
+    return _keep_samples
+
+
+class SampleCache:
+    """Buffer + descriptor handed from a forward call to its backward (d2c_sample_cache)."""
+
+    def __init__(self, desc, device):
+        n = lib().d2c_sample_cache_bytes(ctypes.byref(desc))
+        self.buf = torch.empty(n, dtype=torch.uint8, device=device) if n else None
+        self.c = SampleCacheStruct(self.buf.data_ptr() if n else None, n, 0, 0)
+
+    @staticmethod
+    def for_forward(desc, device, differentiated):
+        """A bound cache for the forward call that follows, or None (nothing to keep / switched off)."""
+        if not (differentiated and _keep_samples):
+            return None
+        cache = SampleCache(desc, device)
+        if cache.buf is None:
+            return None
+        cache.bind()
+        return cache
+
+    def bind(self):
+        """Applies to the next deformable forward / backward call of this thread."""
+        check(lib().d2c_bind_sample_cache(ctypes.byref(self.c)), "bind_sample_cache")
+
+    @property
+    def kept(self):
+        return self.c.format != 0
+
+
+def finish_forward_cache(cache):
+    """After the forward call: the cache if the kernels filled it, else None (buffer released)."""
+    return cache if cache is not None and cache.kept else None
 
 
 def set_math_mode(mode):

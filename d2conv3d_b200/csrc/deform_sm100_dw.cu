@@ -293,6 +293,7 @@ dw_sm100_kernel(const DwParams p) {
       // ---- gather producers: the forward's producer, two slices per stage
       const int tt = threadIdx.x - kGatherWarp0 * 32;
       const int j = tt & 7, r0 = tt >> 3;
+      const uint64_t pol_keep = ptx::l2_evict_last();
       uint32_t row_dst[kRowsPerThread];
 #pragma unroll
       for (int i = 0; i < kRowsPerThread; ++i) {
@@ -316,9 +317,9 @@ dw_sm100_kernel(const DwParams p) {
           uint2 head = make_uint2(0u, 0u);
           if (r < rows) head = *reinterpret_cast<const uint2*>(rec_stage + r * 48);
           if constexpr (kX3)
-            load_corners_f32(reinterpret_cast<const float*>(p.x_cl) + xoff + j * 4, p.cs, head.x, head.y, c[i]);
+            load_corners_f32(reinterpret_cast<const float*>(p.x_cl) + xoff + j * 4, p.cs, head.x, head.y, c[i], pol_keep);
           else
-            load_corners(reinterpret_cast<const __half*>(p.x_cl) + xoff + j * 8, p.cs, head.x, head.y, c[i]);
+            load_corners(reinterpret_cast<const __half*>(p.x_cl) + xoff + j * 8, p.cs, head.x, head.y, c[i], pol_keep);
         }
         if (sl == 0 && !ptx::mbar_wait(a_empty(sa), ((t / kAStages) & 1) ^ 1, abort_flag)) break;
         const uint32_t stage = a_base + sa * kAStageBytes + (kX3 ? 0 : sl * kTileBytes);
@@ -460,7 +461,6 @@ dw_saved_sm100_kernel(const DwSavedParams p) {
       }
     } else if (warp == kMmaWarp) {
       if (lane == 0) {
-        uint32_t q = 0;
         int sb = 0;
         uint32_t phb = 0;
         bool ok = true;
@@ -469,31 +469,52 @@ dw_saved_sm100_kernel(const DwSavedParams p) {
           if (!ptx::mbar_wait(a_full(sa), (kb / kASt) & 1, abort_flag)) break;
           const uint32_t a_stage = a_base + sa * kAStage;
           for (int part = 0; ok && part < kParts; ++part) {
-            for (int c = 0; c < p.NCH; ++c, ++q) {
-              if (!ptx::mbar_wait(b_full(sb), phb, abort_flag)) { ok = false; break; }
-              ptx::tc_fence_after();
-              const uint32_t idesc = ptx::umma_idesc_bf16_f32(kBM, min(256, p.N - 256 * c)) | (1u << 15);  // A is MN-major
-              const uint64_t bdesc0 = ptx::umma_desc_kmajor_sw128(b_base + sb * kChunkBytes);
-              const uint32_t d = tmem_base + (uint32_t)(256 * c);
+            // the NCH chunks of this image group: wait for all of them, then walk the K steps with the column
+            // ranges innermost, so that consecutive MMAs alternate between accumulators (back-to-back MMAs into
+            // the same columns issue at 217 clocks, alternating ones at 139)
+            int sbc[2] = {0, 0};
+            uint64_t bdesc0[2] = {0, 0};
+            uint32_t idesc[2] = {0, 0};
 #pragma unroll
-              for (int k4 = 0; k4 < 4; ++k4) {
-                // A: 16 voxels from voxel k4*16 of the block = two 8-row groups of 1024 bytes (SBO); the second
-                // slice of the pair (rows 64..127 of M) lies one 8 KB image further (LBO)
-                const uint64_t a_hi = ptx::umma_desc_mnmajor_sw128(a_stage + k4 * 2048, kSvBlkBytes, 1024);
-                const uint64_t bdesc = bdesc0 + (uint64_t)(2 * k4);
-                if (!kX3) {
-                  ptx::umma_bf16(d, a_hi, bdesc, idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
-                } else if (part == 0) {
-                  const uint64_t a_lo = ptx::umma_desc_mnmajor_sw128(a_stage + 2 * kSvBlkBytes + k4 * 2048, kSvBlkBytes, 1024);
-                  ptx::umma_bf16(d, a_hi, bdesc, idesc, (kb > 0 || k4 > 0) ? 1u : 0u);     // a_hi * g_hi
-                  ptx::umma_bf16(d, a_lo, bdesc, idesc, 1u);                                // a_lo * g_hi
-                } else {
-                  ptx::umma_bf16(d, a_hi, bdesc, idesc, 1u);                                // a_hi * g_lo
-                }
+            for (int c = 0; c < 2; ++c) {             // NCH <= 2 (Cout <= 512); fixed bounds keep these in registers
+              if (c < p.NCH && ok) {
+                if (!ptx::mbar_wait(b_full(sb), phb, abort_flag)) { ok = false; }
+                sbc[c] = sb;
+                bdesc0[c] = ptx::umma_desc_kmajor_sw128(b_base + sb * kChunkBytes);
+                idesc[c] = ptx::umma_idesc_bf16_f32(kBM, min(256, p.N - 256 * c)) | (1u << 15);   // A is MN-major
+                if (++sb == kSvBStages) { sb = 0; phb ^= 1u; }
               }
-              ptx::umma_commit(b_empty(sb));
-              if (++sb == kSvBStages) { sb = 0; phb ^= 1u; }
             }
+            if (!ok) break;
+            ptx::tc_fence_after();
+#pragma unroll
+            for (int k4 = 0; k4 < 4; ++k4) {
+              // A: 16 voxels from voxel k4*16 of the block = two 8-row groups of 1024 bytes (SBO); the second
+              // slice of the pair (rows 64..127 of M) lies one 8 KB image further (LBO)
+              const uint64_t a_hi = ptx::umma_desc_mnmajor_sw128(a_stage + k4 * 2048, kSvBlkBytes, 1024);
+              const uint64_t a_lo = ptx::umma_desc_mnmajor_sw128(a_stage + 2 * kSvBlkBytes + k4 * 2048, kSvBlkBytes, 1024);
+              const uint32_t acc = (kb > 0 || k4 > 0) ? 1u : 0u;
+              if (!kX3 || part == 0) {
+#pragma unroll
+                for (int c = 0; c < 2; ++c)                                                  // a (a_hi) * g (g_hi)
+                  if (c < p.NCH)
+                    ptx::umma_bf16(tmem_base + (uint32_t)(256 * c), a_hi, bdesc0[c] + (uint64_t)(2 * k4), idesc[c], acc);
+                if (kX3) {
+#pragma unroll
+                  for (int c = 0; c < 2; ++c)                                                // a_lo * g_hi
+                    if (c < p.NCH)
+                      ptx::umma_bf16(tmem_base + (uint32_t)(256 * c), a_lo, bdesc0[c] + (uint64_t)(2 * k4), idesc[c], 1u);
+                }
+              } else {
+#pragma unroll
+                for (int c = 0; c < 2; ++c)                                                  // a_hi * g_lo
+                  if (c < p.NCH)
+                    ptx::umma_bf16(tmem_base + (uint32_t)(256 * c), a_hi, bdesc0[c] + (uint64_t)(2 * k4), idesc[c], 1u);
+              }
+            }
+#pragma unroll
+            for (int c = 0; c < 2; ++c)
+              if (c < p.NCH) ptx::umma_commit(b_empty(sbc[c]));
           }
           if (ok) ptx::umma_commit(a_empty(sa));
         }
@@ -508,11 +529,12 @@ dw_saved_sm100_kernel(const DwSavedParams p) {
         uint32_t q = 0;
         int sb = 0, c = 0;
         uint32_t phb = 1;                                     // the wait for a FREE slot looks at the previous phase
+        const uint64_t pol_keep = ptx::l2_evict_last();       // every slice pair streams the same grad_out images
         for (; q < nq; ++q) {
           if (!ptx::mbar_wait(b_empty(sb), phb, abort_flag, 100)) break;
           const uint32_t bytes = (uint32_t)min(256, p.N - 256 * c) * 128u;
           ptx::mbar_arrive_expect_tx(b_full(sb), bytes);
-          ptx::bulk_g2s(b_base + sb * kChunkBytes, src, bytes, b_full(sb));
+          ptx::bulk_g2s_hint(b_base + sb * kChunkBytes, src, bytes, b_full(sb), pol_keep);
           src += kChunkBytes;
           if (++c == p.NCH) c = 0;
           if (++sb == kSvBStages) { sb = 0; phb ^= 1u; }
@@ -530,11 +552,12 @@ dw_saved_sm100_kernel(const DwSavedParams p) {
         const long long blk_stride = (long long)p.n_pairs * kAStage;   // bytes between consecutive blocks
         const uint8_t* src = p.sav + (long long)tile_beg * 2 * blk_stride + (long long)pair * kAStage;
         int kb = 0;
+        const uint64_t pol_stream = ptx::l2_evict_first();    // every byte of the image is read exactly once
         for (; kb < n_blocks; ++kb) {
           const int sa = kb % kASt;
           if (!ptx::mbar_wait(a_empty(sa), ((kb / kASt) & 1) ^ 1, abort_flag, 100)) break;
           ptx::mbar_arrive_expect_tx(a_full(sa), (uint32_t)kAStage);
-          ptx::bulk_g2s(a_base + sa * kAStage, src, (uint32_t)kAStage, a_full(sa));
+          ptx::bulk_g2s_hint(a_base + sa * kAStage, src, (uint32_t)kAStage, a_full(sa), pol_stream);
           src += blk_stride;
         }
         for (int w = (kb > kASt ? kb - kASt : 0); w < kb; ++w) {
@@ -619,8 +642,8 @@ bool make_dw_plan(const Geom& g, int sm_count, bool x3, DwPlan* dp) {
   return true;
 }
 
-// Work split of the saved-samples kernel: (slice pair, voxel range) items, about three waves of them, ranges of at
-// least 8 tiles, the count chosen so that the last wave is as full as possible; the fp32-parity mode ends an
+// Work split of the saved-samples kernel: (slice pair, voxel range) items, at least two waves of them, ranges of at
+// least 8 tiles, the smallest count whose last wave is at least 95 % full (else the fullest); the fp32-parity mode ends an
 // accumulation chain after 27 tiles (24 accumulating MMAs per tile and column range -> 648, see make_dw_plan).
 void split_saved(const DwPlan& dp, int sm_count, bool x3, int* tiles_per_split, int* nsplit_out) {
   const int n_pairs = (dp.S + 1) / 2;
@@ -636,6 +659,7 @@ void split_saved(const DwPlan& dp, int sm_count, bool x3, int* tiles_per_split, 
     const long long waves = (ctas + sm_count - 1) / sm_count;
     const double eff = (double)ctas / (double)(waves * sm_count);
     if (eff > best_eff + 1e-9) { best_eff = eff; best = ns; }
+    if (eff >= 0.95) break;      // full enough: every further range costs one more epilogue and pipeline fill per pair
   }
   *tiles_per_split = (dp.n_tiles + best - 1) / best;
   *nsplit_out = (dp.n_tiles + *tiles_per_split - 1) / *tiles_per_split;

@@ -162,12 +162,13 @@ fwd_sm100_kernel(const FwdParams p) {
       uint32_t phb = 1;                 // the wait for a FREE slot looks at the previous phase
       int s = (int)(u_beg % p.S);       // once per CTA
       const uint8_t* src = p.w_sw + (long long)s * p.b_stage_bytes;
+      const uint64_t pol_keep = ptx::l2_evict_last();          // every CTA streams every slice once per tile
       for (long long u = u_beg; u < u_end; ++u, ++k) {
         if (!ptx::mbar_wait(b_empty(sb), phb, abort_flag, 200)) break;
         ptx::mbar_arrive_expect_tx(b_full(sb), (uint32_t)p.b_stage_bytes);
         const uint32_t dst = b_base + sb * p.b_stage_bytes;
         for (int off = 0; off < p.b_stage_bytes; off += 32768)
-          ptx::bulk_g2s(dst + off, src + off, (uint32_t)min(32768, p.b_stage_bytes - off), b_full(sb));
+          ptx::bulk_g2s_hint(dst + off, src + off, (uint32_t)min(32768, p.b_stage_bytes - off), b_full(sb), pol_keep);
         if (++sb == p.b_stages) { sb = 0; phb ^= 1u; }
         src += p.b_stage_bytes;
         if (++s == p.S) { s = 0; src = p.w_sw; }
@@ -194,6 +195,7 @@ fwd_sm100_kernel(const FwdParams p) {
       int tile = tile0;
       int h = s % p.nh, tap = (s / p.nh) % g.K, grp = (s / p.nh) / g.K;   // dual: grp is the index of a group PAIR
       const long long grp_ch = kDual ? 2 * g.cpg : g.cpg;
+      const uint64_t pol_stream = ptx::l2_evict_first();       // records are read once
       for (long long u = u_beg; u < u_end; ++u, ++k) {
         const int sr = k & (kRStages - 1);
         if (!ptx::mbar_wait(r_empty(sr), ((k / kRStages) & 1) ^ 1, abort_flag, 200)) break;
@@ -221,8 +223,8 @@ fwd_sm100_kernel(const FwdParams p) {
 #pragma unroll
         for (int set = 0; set <= kDual; ++set) {
           const int og = kDual ? 2 * grp + set : grp;      // offset group whose records fill this set
-          ptx::bulk_g2s(rec_base + sr * kRStage + set * kRecBytes,
-                        p.recs + 3 * ((((long long)b * g.G + og) * g.K + tap) * g.V + v0), bytes, r_full(sr));
+          ptx::bulk_g2s_hint(rec_base + sr * kRStage + set * kRecBytes,
+                             p.recs + 3 * ((((long long)b * g.G + og) * g.K + tap) * g.V + v0), bytes, r_full(sr), pol_stream);
         }
         // next unit: (h, tap, grp) count through the tile's slices, then the next tile of the clip / next clip
         if (++h == p.nh) {
@@ -258,6 +260,7 @@ fwd_sm100_kernel(const FwdParams p) {
     // Samples kept for the weight gradient (p.sav != nullptr): the thread's two rows r0 and r0 + 64 are the same row
     // of the two 64-voxel blocks of the tile, so its byte offset inside an 8 KB block is fixed.
     const uint32_t sav_row = (uint32_t)((r0 >> 3) * 1024 + (r0 & 7) * 128);
+    const uint64_t pol_keep = ptx::l2_evict_last(), pol_stream = ptx::l2_evict_first();
 
     auto issue = [&](uint32_t k, int i, uint4 (&c)[8]) {
       const uint8_t* rec_base_ptr = base_ptr + rec_off + (k % kRStages) * kRStage;
@@ -269,11 +272,12 @@ fwd_sm100_kernel(const FwdParams p) {
       uint2 head = make_uint2(0u, 0u);
       if (r < rows) head = *reinterpret_cast<const uint2*>(rec_stage + r * 48);
       if constexpr (kX3)
-        load_corners_f32(reinterpret_cast<const float*>(p.x_cl) + xoff + j * 4, p.cs, head.x, head.y, c);
+        load_corners_f32(reinterpret_cast<const float*>(p.x_cl) + xoff + j * 4, p.cs, head.x, head.y, c, pol_keep);
       else
-        load_corners(reinterpret_cast<const __half*>(p.x_cl) + xoff + j * 8, p.cs, head.x, head.y, c);
+        load_corners(reinterpret_cast<const __half*>(p.x_cl) + xoff + j * 8, p.cs, head.x, head.y, c, pol_keep);
     };
-    auto consume = [&](uint32_t k, int i, const uint4 (&c)[8]) {
+    // returns the bytes written to the A tile (bf16: the item's 16 bytes; bf16x3: {hi 8 bytes, lo 8 bytes})
+    auto consume = [&](uint32_t k, int i, const uint4 (&c)[8]) -> uint4 {
       const uint8_t* rec_base_ptr = base_ptr + rec_off + (k % kRStages) * kRStage;
       const int rows = *reinterpret_cast<const int*>(rec_base_ptr + hdr_off + 8);
       const uint8_t* rec_stage = rec_base_ptr + ((kDual && j >= 4) ? kRecBytes : 0);
@@ -292,31 +296,15 @@ fwd_sm100_kernel(const FwdParams p) {
         }
         // item j = channels 4j..4j+3: hi in 16-byte chunk j/2 (half j&1), lo in chunk 4 + j/2
         const uint32_t row_base = stage + (uint32_t)((r >> 3) * 1024 + (r & 7) * 128) + (uint32_t)((j & 1) * 8);
-        const uint4 hl = blend_split_store(c, w, row_base + ((((j >> 1)) ^ (r & 7)) << 4),
-                                           row_base + (((4 + (j >> 1)) ^ (r & 7)) << 4));
-        if (p.sav) {
-          // image block = (tile, 64-voxel block i, slice pair, {hi, lo}, slice of the pair): a 64-channel row holds
-          // this unit's 32 channels in its half `half`; hi and lo parts lie two blocks apart
-          const int word = *reinterpret_cast<const int*>(rec_base_ptr + hdr_off + 12);
-          const int half = word & 1;
-          uint8_t* dst = p.sav + ((long long)((word >> 1) + i * p.sav_np * 4) << 13) + sav_row +
-                         (uint32_t)((((4 * half + (j >> 1)) ^ (r0 & 7)) << 4) + (j & 1) * 8);
-          __stcs(reinterpret_cast<uint2*>(dst), make_uint2(hl.x, hl.y));
-          __stcs(reinterpret_cast<uint2*>(dst + 2 * 8192), make_uint2(hl.z, hl.w));
-        }
+        return blend_split_store(c, w, row_base + ((((j >> 1)) ^ (r & 7)) << 4),
+                                 row_base + (((4 + (j >> 1)) ^ (r & 7)) << 4));
       } else {
         uint4 w03 = make_uint4(0u, 0u, 0u, 0u), w47 = w03;       // rows past the clip end: stage bytes are stale
         if (r < rows) {
           w03 = *reinterpret_cast<const uint4*>(rec_stage + r * 48 + 16);
           w47 = *reinterpret_cast<const uint4*>(rec_stage + r * 48 + 32);
         }
-        const uint4 o = blend_store(c, w03, w47, stage + (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((j ^ (r & 7)) << 4)));
-        if (p.sav) {
-          // image block = (tile, 64-voxel block i, slice): the byte image of this half of the A tile
-          const int word = *reinterpret_cast<const int*>(rec_base_ptr + hdr_off + 12);
-          __stcs(reinterpret_cast<uint4*>(p.sav + ((long long)(word + i * 2 * p.sav_np) << 13) + sav_row +
-                                          (uint32_t)((j ^ (r0 & 7)) << 4)), o);
-        }
+        return blend_store(c, w03, w47, stage + (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((j ^ (r & 7)) << 4)));
       }
     };
 
@@ -327,19 +315,45 @@ fwd_sm100_kernel(const FwdParams p) {
     }
     for (uint32_t k = 0; ok && k < n_my_units; ++k) {
       const int sr = k % kRStages, sa = k % kAStages;
+      // where the unit's samples go in the kept image (read before the record stage is released below)
+      int word = 0;
+      if (p.sav) word = *reinterpret_cast<const int*>(base_ptr + rec_off + sr * kRStage + hdr_off + 12);
       issue(k, 1, c1);
       if (!ptx::mbar_wait(a_empty(sa), ((k / kAStages) & 1) ^ 1, abort_flag)) break;
-      consume(k, 0, c0);
+      const uint4 o0 = consume(k, 0, c0);
       if (k + 1 < n_my_units) {
         if (!ptx::mbar_wait(r_full((k + 1) % kRStages), ((k + 1) / kRStages) & 1, abort_flag)) break;
         issue(k + 1, 0, c0);
       }
-      consume(k, 1, c1);
+      const uint4 o1 = consume(k, 1, c1);
       ptx::fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
         ptx::mbar_arrive(a_full(sa));
         ptx::mbar_arrive(r_empty(sr));
+      }
+      // The kept copy goes to global memory AFTER the arrives: an arrive releases the thread's earlier writes, so
+      // global stores issued before it would put their round trip to L2 on every unit's critical path (measured:
+      // +25 % kernel time); issued here they have a whole unit to complete before the next arrive.
+      if (p.sav) {
+        if constexpr (kX3) {
+          // image block = (tile, 64-voxel block, slice pair, {hi, lo}, slice of the pair): a 64-channel row holds
+          // this unit's 32 channels in its half `half`; hi and lo blocks lie two blocks apart, the tile's second
+          // 64-voxel block sav_np * 4 blocks further
+          const int half = word & 1;
+          uint8_t* dst = p.sav + ((long long)(word >> 1) << 13) + sav_row +
+                         (uint32_t)((((4 * half + (j >> 1)) ^ (r0 & 7)) << 4) + (j & 1) * 8);
+          const long long blk1 = (long long)(p.sav_np * 4) << 13;
+          ptx::stg_v2_hint(dst, make_uint2(o0.x, o0.y), pol_stream);
+          ptx::stg_v2_hint(dst + 2 * 8192, make_uint2(o0.z, o0.w), pol_stream);
+          ptx::stg_v2_hint(dst + blk1, make_uint2(o1.x, o1.y), pol_stream);
+          ptx::stg_v2_hint(dst + blk1 + 2 * 8192, make_uint2(o1.z, o1.w), pol_stream);
+        } else {
+          // image block = (tile, 64-voxel block, slice): the byte image of that half of the A tile
+          uint8_t* dst = p.sav + ((long long)word << 13) + sav_row + (uint32_t)((j ^ (r0 & 7)) << 4);
+          ptx::stg_v4_hint(dst, o0, pol_stream);
+          ptx::stg_v4_hint(dst + ((long long)(2 * p.sav_np) << 13), o1, pol_stream);
+        }
       }
     }
   }

@@ -89,11 +89,13 @@ class _DeformConv3dFunction(torch.autograd.Function):
         with torch.cuda.device(input.device):
             y = torch.empty((input.shape[0], weight.shape[0]) + out_dims, dtype=input.dtype, device=input.device)
             ws, ws_bytes = _lib.workspace(_lib.OP_DEFORM_FWD, desc, input.device)
+            cache = _lib.SampleCache.for_forward(desc, input.device, any(ctx.needs_input_grad))
             _lib.check(L.d2c_deform_conv3d_fwd(
                 ctypes.byref(desc), _lib.ptr(input), _lib.ptr(offset), _lib.ptr(alpha), _lib.ptr(weight),
                 _lib.ptr(bias), _lib.ptr(y), _lib.ptr(ws), ws_bytes, _lib.stream_of(input)), "deform_conv3d forward")
         ctx.save_for_backward(input, offset, alpha, weight, bias)
         ctx.desc = desc
+        ctx.sample_cache = _lib.finish_forward_cache(cache)
         return y
 
     @staticmethod
@@ -109,6 +111,8 @@ class _DeformConv3dFunction(torch.autograd.Function):
             gbias = None if bias is None else torch.empty_like(bias)
             ws, ws_bytes = _lib.workspace(_lib.OP_DEFORM_BWD, desc, input.device)
             ev = _new_event(torch.cuda.current_stream(input.device))
+            if ctx.sample_cache is not None:
+                ctx.sample_cache.bind()
             _lib.check(L.d2c_deform_conv3d_bwd_ev(
                 ctypes.byref(desc), _lib.ptr(grad_out), _lib.ptr(input), _lib.ptr(offset), _lib.ptr(alpha),
                 _lib.ptr(weight), _lib.ptr(gx), _lib.ptr(goff), _lib.ptr(gmask), _lib.ptr(gw), _lib.ptr(gbias),
@@ -145,12 +149,14 @@ class _DynDilatedConv3dFunction(torch.autograd.Function):
         with torch.cuda.device(input.device):
             y = torch.empty((input.shape[0], weight.shape[0]) + out_dims, dtype=input.dtype, device=input.device)
             ws, ws_bytes = _lib.workspace(_lib.OP_DYNDIL_FWD, desc, input.device)
+            cache = _lib.SampleCache.for_forward(desc, input.device, any(ctx.needs_input_grad))
             _lib.check(L.d2c_dyn_dilated_conv3d_fwd(
                 ctypes.byref(desc), _lib.FIELD_MODES[mode], _lib.ptr(input), _lib.ptr(size_map), _lib.ptr(alpha),
                 _lib.ptr(weight), _lib.ptr(bias), _lib.ptr(y), _lib.ptr(ws), ws_bytes, _lib.stream_of(input)),
                 "dyn_dilated_conv3d forward")
         ctx.save_for_backward(input, size_map, alpha, weight, bias)
         ctx.desc, ctx.mode = desc, mode
+        ctx.sample_cache = _lib.finish_forward_cache(cache)
         return y
 
     @staticmethod
@@ -166,6 +172,8 @@ class _DynDilatedConv3dFunction(torch.autograd.Function):
             gbias = None if bias is None else torch.empty_like(bias)
             ws, ws_bytes = _lib.workspace(_lib.OP_DYNDIL_BWD, desc, input.device)
             ev = _new_event(torch.cuda.current_stream(input.device))
+            if ctx.sample_cache is not None:
+                ctx.sample_cache.bind()
             _lib.check(L.d2c_dyn_dilated_conv3d_bwd_ev(
                 ctypes.byref(desc), _lib.FIELD_MODES[ctx.mode], _lib.ptr(grad_out), _lib.ptr(input),
                 _lib.ptr(size_map), _lib.ptr(alpha), _lib.ptr(weight), _lib.ptr(gx), _lib.ptr(gs), _lib.ptr(gmask),
@@ -276,6 +284,7 @@ class _HeadConv3dFunction(torch.autograd.Function):
             ws, ws_bytes = _lib.head_workspace(op, desc, head, max(fm, 0), input.device)
             args = (_lib.ptr(input), _lib.ptr(raw), _lib.ptr(weight), _lib.ptr(bias), _lib.ptr(y), _lib.ptr(ws), ws_bytes,
                     _lib.stream_of(input))
+            cache = _lib.SampleCache.for_forward(desc, input.device, any(ctx.needs_input_grad))
             if field_mode is None:
                 rc = L.d2c_deform_conv3d_head_fwd(ctypes.byref(desc), ctypes.byref(head), *args)
             else:
@@ -283,6 +292,7 @@ class _HeadConv3dFunction(torch.autograd.Function):
             _lib.check(rc, "deform_conv3d (fused head) forward")
         ctx.save_for_backward(input, raw, weight, bias)
         ctx.desc, ctx.head, ctx.fm = desc, head, fm
+        ctx.sample_cache = _lib.finish_forward_cache(cache)
         return y
 
     @staticmethod
@@ -301,6 +311,8 @@ class _HeadConv3dFunction(torch.autograd.Function):
             args = (_lib.ptr(grad_out), _lib.ptr(input), _lib.ptr(raw), _lib.ptr(weight), _lib.ptr(gx), _lib.ptr(graw),
                     _lib.ptr(gw), _lib.ptr(gbias), _lib.ptr(ws), ws_bytes, _lib.stream_of(input),
                     ctypes.c_void_p(ev.cuda_event))
+            if ctx.sample_cache is not None:
+                ctx.sample_cache.bind()
             if fm < 0:
                 rc = L.d2c_deform_conv3d_head_bwd(ctypes.byref(desc), ctypes.byref(head), *args)
             else:

@@ -50,6 +50,7 @@ def lib_mode():
         d2conv3d_b200.set_math_mode(m)
     yield set_mode
     d2conv3d_b200.set_math_mode("auto")
+    d2conv3d_b200.set_keep_samples(True)
     _lib.device_status()
 
 
@@ -222,14 +223,18 @@ def _many_tile_case(kind):
     return _oracle_cache[kind]
 
 
+@pytest.mark.parametrize("keep", [False, True])
 @pytest.mark.parametrize("kind", ["offsets", "field"])
 @pytest.mark.parametrize("mode", ["auto", "bf16"])
-def test_300_tiles_with_32_channels_per_offset_group(lib_mode, mode, kind):
+def test_300_tiles_with_32_channels_per_offset_group(lib_mode, mode, kind, keep):
     """auto: split forward on 32-channel units, sampling gradient on half slices, weight gradient from two groups'
-    records per slice.  bf16: forward and weight gradient with two record sets per ring stage."""
+    records per slice.  bf16: forward and weight gradient with two record sets per ring stage.  keep: the weight
+    gradient streams the samples the forward kept instead of gathering them again (the default for training)."""
+    import d2conv3d_b200
     from d2conv3d_b200 import _lib, dconv_native
     p, want32, want64 = _many_tile_case(kind)
     lib_mode(mode)
+    d2conv3d_b200.set_keep_samples(keep)
     cu = lambda a: torch.from_numpy(a).cuda()
     ts = [cu(p[k]).requires_grad_() for k in ("x", "geo", "mask", "weight", "bias")]
     _lib.profile_read(); _lib.profile_enable(True)
@@ -240,7 +245,9 @@ def test_300_tiles_with_32_channels_per_offset_group(lib_mode, mode, kind):
     y.backward(cu(p["gy"]))
     _lib.profile_enable(False)
     phases = {n for n, _ in _lib.profile_read()}
-    assert {"fwd_sm100_fused", "bwd_dcol_sm100", "bwd_sample_grad", "bwd_dw_sm100"} <= phases, phases
+    d2conv3d_b200.set_keep_samples(True)
+    assert {"fwd_sm100_fused", "bwd_dcol_sm100", "bwd_sample_grad",
+            "bwd_dw_sm100_saved" if keep else "bwd_dw_sm100"} <= phases, phases
     got = [y.detach().cpu()] + [t.grad.cpu() for t in ts]
     check_all(f"300-tiles-{kind}", mode, ("y", "grad_x", "grad_geo", "grad_mask", "grad_w", "grad_bias"), got, want32, want64,
               {"grad_geo"})

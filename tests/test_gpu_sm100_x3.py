@@ -127,7 +127,8 @@ def test_backward_fp32_parity_mode_vs_oracle(dn, ci):
     y.backward(cu(p["gy"]))
     _lib.profile_enable(False)
     phases = [n for n, _ in _lib.profile_read()]
-    assert "bwd_dcol_sm100" in phases and "bwd_sample_grad" in phases and "bwd_dw_sm100" in phases, phases
+    assert "bwd_dcol_sm100" in phases and "bwd_sample_grad" in phases, phases
+    assert "bwd_dw_sm100" in phases or "bwd_dw_sm100_saved" in phases, phases
     for t, w_, nm in zip(ts, want, ("grad_x", "grad_offset", "grad_mask", "grad_w", "grad_bias")):
         err = np.abs(t.grad.cpu().numpy() - w_).max() / np.abs(w_).max()
         print(f"case {ci} {nm}: rel err {err:.3e}")
@@ -195,7 +196,8 @@ def test_backward_32_channels_per_offset_group(tc_mode, cfg):
     finally:
         d2conv3d_b200.set_math_mode("auto")
     phases = [n for n, _ in _lib.profile_read()]
-    assert "bwd_dcol_sm100" in phases and "bwd_sample_grad" in phases and "bwd_dw_sm100" in phases, phases
+    assert "bwd_dcol_sm100" in phases and "bwd_sample_grad" in phases, phases
+    assert "bwd_dw_sm100" in phases or "bwd_dw_sm100_saved" in phases, phases
     for t, w_, nm in zip(ts, want, ("grad_x", "grad_offset", "grad_mask", "grad_w", "grad_bias")):
         err = np.abs(t.grad.cpu().numpy() - w_).max() / np.abs(w_).max()
         print(f"{cfg} {tc_mode} {nm}: rel err {err:.3e}")
