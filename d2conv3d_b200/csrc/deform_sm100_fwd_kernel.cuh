@@ -79,6 +79,43 @@ fwd_sm100_kernel(const FwdParams p) {
       ptx::tc_fence_after();
       const int v = v0 + warp * 32 + lane;
       float* yb = p.y + (long long)b * g.Cout * g.V + v;
+      if ((g.V & 3) == 0) {
+        // Each lane holds 32 channels of ONE voxel; y is [clip][channel][voxel], so a lane's values lie V floats
+        // apart.  A 4 x 4 transpose inside every lane quad (two shuffle stages) gives lane q of the quad channel
+        // 4i + q of the quad's four consecutive voxels: 16-byte stores / vector reductions, a quarter of the memory
+        // instructions (the partial-tile epilogue was bound by their issue, not by bytes).
+        const int q = lane & 3;
+        const int vq = v0 + warp * 32 + (lane & ~3);
+        float* yq = p.y + (long long)b * g.Cout * g.V + vq;
+        const bool live = vq < g.V;                      // V is a multiple of 4: a quad is valid or invalid as a whole
+        for (int c0 = 0; c0 < p.N; c0 += 32) {
+          uint32_t r[32];
+          ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            uint32_t* a = r + 4 * i;
+            const uint32_t t0 = __shfl_xor_sync(0xffffffffu, (q & 1) ? a[0] : a[1], 1);
+            const uint32_t t1 = __shfl_xor_sync(0xffffffffu, (q & 1) ? a[2] : a[3], 1);
+            if (q & 1) { a[0] = t0; a[2] = t1; } else { a[1] = t0; a[3] = t1; }
+            const uint32_t u0 = __shfl_xor_sync(0xffffffffu, (q & 2) ? a[0] : a[2], 2);
+            const uint32_t u1 = __shfl_xor_sync(0xffffffffu, (q & 2) ? a[1] : a[3], 2);
+            if (q & 2) { a[0] = u0; a[1] = u1; } else { a[2] = u0; a[3] = u1; }
+            if (live) {
+              const int c = c0 + 4 * i + q;
+              const float bb = (p.bias && (whole || s_beg == 0)) ? __ldg(p.bias + c) : 0.f;
+              float* dst = yq + (long long)c * g.V;
+              const float f0 = __uint_as_float(a[0]) + bb, f1 = __uint_as_float(a[1]) + bb,
+                          f2 = __uint_as_float(a[2]) + bb, f3 = __uint_as_float(a[3]) + bb;
+              if (whole)
+                *reinterpret_cast<float4*>(dst) = make_float4(f0, f1, f2, f3);
+              else
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(f0), "f"(f1), "f"(f2), "f"(f3)
+                             : "memory");
+            }
+          }
+        }
+      } else {
       for (int c0 = 0; c0 < p.N; c0 += 32) {
         uint32_t r[32];
         ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);
@@ -98,6 +135,7 @@ fwd_sm100_kernel(const FwdParams p) {
             }
           }
         }
+      }
       }
       ptx::tc_fence_before();
       __syncwarp();
