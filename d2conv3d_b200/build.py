@@ -46,11 +46,14 @@ def needs_build():
     return any(os.path.getmtime(d) > t for d in _deps())
 
 
-def build(force=False, verbose=False):
-    if not force and not needs_build():
+def build(force=False, verbose=False, unit_trace=False):
+    """unit_trace: compile the forward kernel's per-unit timeline instrumentation in (-DD2C_UNIT_TRACE, see
+    csrc/deform_sm100_fwd_kernel.cuh and unit_trace.py); always rebuilds.  Build again without it afterwards: the
+    instrumented library is for measurements only."""
+    if not force and not unit_trace and not needs_build():
         return LIB
     os.makedirs(OBJ_DIR, exist_ok=True)
-    extra = ["-Xptxas", "-v"] if verbose else []
+    extra = (["-Xptxas", "-v"] if verbose else []) + (["-DD2C_UNIT_TRACE"] if unit_trace else [])
     procs = []
     objs = []
     for src in SOURCES:
@@ -84,6 +87,6 @@ def build_microbench():
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, unit_trace="--unit-trace" in sys.argv))
     if "--microbench" in sys.argv:
         print(build_microbench())

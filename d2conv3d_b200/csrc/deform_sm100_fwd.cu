@@ -80,6 +80,10 @@ struct FwdParams {
   //   bf16 mode:  [tile][64-voxel block][slice s, padded to 2*sav_np]
   //   bf16x3:     [tile][64-voxel block][slice pair][hi | lo][slice of the pair]   (a unit fills half of each row)
   // exactly the operand images deform_sm100_dw.cu bulk-copies.
+#ifdef D2C_UNIT_TRACE
+  long long* trace;            // instrumentation buffer (deform_sm100_fwd_kernel.cuh), nullptr = off
+  int trace_cta, trace_k0;
+#endif
   uint8_t* sav;
   int sav_np;                  // slice pairs of the weight gradient
   int sav_pairg;               // bf16x3: 32 channels per offset group (a 64-channel slice spans two groups)
@@ -311,11 +315,39 @@ int run_fwd(const Geom& g, int math_mode, const Coords& coords, const HeadCfg& h
     prof_mark(st, nullptr);
     return D2C_OK;
   }
+#ifdef D2C_UNIT_TRACE
+  // D2C_UNIT_TRACE=<cta> [D2C_UNIT_TRACE_K0=<first unit of the window>] [D2C_UNIT_TRACE_FILE=<path>]: the call
+  // synchronises and writes the buffer after the kernel (instrumented builds only)
+  constexpr size_t kTraceWords = 5 * 64 * 8 + 1024 * 4;
+  static long long* trace_dev = nullptr;
+  p.trace = nullptr; p.trace_cta = 0; p.trace_k0 = 0;
+  if (const char* tc = getenv("D2C_UNIT_TRACE")) {
+    if (!trace_dev) D2C_CUDA_TRY(cudaMalloc(&trace_dev, kTraceWords * sizeof(long long)));
+    D2C_CUDA_TRY(cudaMemsetAsync(trace_dev, 0, kTraceWords * sizeof(long long), st));
+    p.trace = trace_dev; p.trace_cta = atoi(tc);
+    p.trace_k0 = getenv("D2C_UNIT_TRACE_K0") ? atoi(getenv("D2C_UNIT_TRACE_K0")) : 200;
+  }
+#endif
   prof_mark(st, "fwd_sm100_fused");
   auto kern = x3 ? fwd_sm100_kernel<1, 0> : (pl.dual ? fwd_sm100_kernel<0, 1> : fwd_sm100_kernel<0, 0>);
   D2C_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes));
   kern<<<(unsigned)grid, kThreadsFwd, pl.smem_bytes, st>>>(p);
   D2C_LAUNCH_CHECK();
+#ifdef D2C_UNIT_TRACE
+  if (p.trace) {
+    static long long host[kTraceWords];
+    D2C_CUDA_TRY(cudaStreamSynchronize(st));
+    D2C_CUDA_TRY(cudaMemcpy(host, trace_dev, sizeof(host), cudaMemcpyDeviceToHost));
+    const char* path = getenv("D2C_UNIT_TRACE_FILE");
+    FILE* f = fopen(path ? path : (x3 ? "unit_trace_x3.bin" : "unit_trace_bf16.bin"), "wb");
+    if (f) {
+      const long long hdr[2] = {(long long)grid, (long long)p.trace_k0};
+      fwrite(hdr, sizeof(long long), 2, f);
+      fwrite(host, sizeof(long long), 5 * 64 * 8 + (size_t)grid * 4, f);
+      fclose(f);
+    }
+  }
+#endif
   prof_mark(st, nullptr);
   return D2C_OK;
 }

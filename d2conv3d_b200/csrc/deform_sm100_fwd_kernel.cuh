@@ -2,6 +2,21 @@
 // uses).  Warp roles are aligned to warpgroups (4 epilogue warps | MMA, weight loader, record loader, one idle warp
 // | 16 gather warps) so that `setmaxnreg` can move registers from the light roles to the gather warps, whose loop
 // is software-pipelined at row granularity (see the producer branch).
+// Optional instrumentation (compiled in with -DD2C_UNIT_TRACE, `python -m d2conv3d_b200.build --unit-trace`): every
+// role of ONE CTA stamps clock64() at fixed points of its per-unit loop for a window of 64 units, and every CTA
+// records its start / end (globaltimer), its SM and its unit count.  Read with `python -m d2conv3d_b200.unit_trace`.
+// Layout of the buffer (long long): [role 0..4][unit 0..63][event 0..7], then [CTA][t0, t1, smid, units].
+// Roles: 0 record loader, 1 weight loader, 2 MMA issuer, 3 / 4 first / last gather warp (lane 0).
+#ifdef D2C_UNIT_TRACE
+#define D2C_TR(role, k, e)                                                                                    \
+  do {                                                                                                        \
+    if (p.trace && (int)blockIdx.x == p.trace_cta && (int)(k) >= p.trace_k0 && (int)(k) < p.trace_k0 + 64)    \
+      p.trace[((role) * 64 + ((int)(k) - p.trace_k0)) * 8 + (e)] = clock64();                                 \
+  } while (0)
+#else
+#define D2C_TR(role, k, e) ((void)0)
+#endif
+
 constexpr int kThreadsFwd = 24 * 32;
 static_assert(128 * 56 + 128 * 40 + 512 * 96 <= kThreadsFwd * 80, "setmaxnreg budget exceeds the CTA's register allocation");
 constexpr int kMmaWarpFwd = 4, kLoadWarpFwd = 5, kRecWarpFwd = 6, kGatherWarp0Fwd = 8;
@@ -36,6 +51,10 @@ fwd_sm100_kernel(const FwdParams p) {
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + bar_off + 8 * (2 * kAStages + 10));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + bar_off + 8 * (2 * kAStages + 10) + 4);
 
+#ifdef D2C_UNIT_TRACE
+  unsigned long long cta_t0;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(cta_t0));
+#endif
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const Geom& g = p.g;
   long long u_beg, u_end;
@@ -171,8 +190,11 @@ fwd_sm100_kernel(const FwdParams p) {
         ptx::tc_fence_after();
         for (int s = s_beg; s < s_end; ++s, ++k) {
           const int sa = k & (kAStages - 1);
+          D2C_TR(2, k, 0);
           if (!ptx::mbar_wait(a_full(sa), (k / kAStages) & 1, abort_flag)) { ok = false; break; }
+          D2C_TR(2, k, 1);
           if (!ptx::mbar_wait(b_full(sb), phb, abort_flag)) { ok = false; break; }
+          D2C_TR(2, k, 2);
           ptx::tc_fence_after();
           // descriptor address fields count 16-byte units: a stage further along adds stage_bytes / 16
           const uint64_t adesc = adesc0 + a_step * (uint64_t)sa;
@@ -184,8 +206,10 @@ fwd_sm100_kernel(const FwdParams p) {
                              bdesc + (uint64_t)(h * (256 * 128 / 16)) + (uint64_t)(2 * kb_[kk]),
                              h + 1 < n_halves ? idesc_full : idesc_last, (s > s_beg || kk > 0) ? 1u : 0u);
           }
+          D2C_TR(2, k, 3);
           ptx::umma_commit(a_empty(sa));
           ptx::umma_commit(b_empty(sb));
+          D2C_TR(2, k, 4);
           if (++sb == p.b_stages) { sb = 0; phb ^= 1u; }
         }
         if (ok) ptx::umma_commit(acc_full);
@@ -202,7 +226,9 @@ fwd_sm100_kernel(const FwdParams p) {
       const uint8_t* src = p.w_sw + (long long)s * p.b_stage_bytes;
       const uint64_t pol_keep = ptx::l2_evict_last();          // every CTA streams every slice once per tile
       for (long long u = u_beg; u < u_end; ++u, ++k) {
+        D2C_TR(1, k, 0);
         if (!ptx::mbar_wait(b_empty(sb), phb, abort_flag, 200)) break;
+        D2C_TR(1, k, 1);
         ptx::mbar_arrive_expect_tx(b_full(sb), (uint32_t)p.b_stage_bytes);
         const uint32_t dst = b_base + sb * p.b_stage_bytes;
         for (int off = 0; off < p.b_stage_bytes; off += 32768)
@@ -236,7 +262,9 @@ fwd_sm100_kernel(const FwdParams p) {
       const uint64_t pol_stream = ptx::l2_evict_first();       // records are read once
       for (long long u = u_beg; u < u_end; ++u, ++k) {
         const int sr = k & (kRStages - 1);
+        D2C_TR(0, k, 0);
         if (!ptx::mbar_wait(r_empty(sr), ((k / kRStages) & 1) ^ 1, abort_flag, 200)) break;
+        D2C_TR(0, k, 1);
         const int rows = min(kBM, g.V - v0);
         // unit header for the gather warps (no index arithmetic there); ordered before their reads by the
         // release of the arrive below and the acquire of their wait
@@ -314,7 +342,7 @@ fwd_sm100_kernel(const FwdParams p) {
       else
         load_corners(reinterpret_cast<const __half*>(p.x_cl) + xoff + j * 8, p.cs, head.x, head.y, c, pol_keep);
     };
-    // returns the bytes written to the A tile (bf16: the item's 16 bytes; bf16x3: {hi 8 bytes, lo 8 bytes})
+    // returns the 16 bytes this lane wrote to the A tile (bf16x3: the lane pair's hi chunk or lo chunk)
     auto consume = [&](uint32_t k, int i, const uint4 (&c)[8]) -> uint4 {
       const uint8_t* rec_base_ptr = base_ptr + rec_off + (k % kRStages) * kRStage;
       const int rows = *reinterpret_cast<const int*>(rec_base_ptr + hdr_off + 8);
@@ -332,10 +360,10 @@ fwd_sm100_kernel(const FwdParams p) {
           w[4] = __uint_as_float(w25.z); w[5] = __uint_as_float(w25.w);
           w[6] = __uint_as_float(w67.x); w[7] = __uint_as_float(w67.y);
         }
-        // item j = channels 4j..4j+3: hi in 16-byte chunk j/2 (half j&1), lo in chunk 4 + j/2
-        const uint32_t row_base = stage + (uint32_t)((r >> 3) * 1024 + (r & 7) * 128) + (uint32_t)((j & 1) * 8);
-        return blend_split_store(c, w, row_base + ((((j >> 1)) ^ (r & 7)) << 4),
-                                 row_base + (((4 + (j >> 1)) ^ (r & 7)) << 4));
+        // item j = channels 4j..4j+3: hi in 16-byte chunk j/2 (half j&1), lo in chunk 4 + j/2; the lane pair (j, j^1)
+        // shares both chunks: the even lane writes the hi chunk, the odd lane the lo chunk
+        const uint32_t row_base = stage + (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
+        return blend_split_store16(c, w, row_base + ((((j & 1) * 4 + (j >> 1)) ^ (r & 7)) << 4), (j & 1) != 0);
       } else {
         uint4 w03 = make_uint4(0u, 0u, 0u, 0u), w47 = w03;       // rows past the clip end: stage bytes are stale
         if (r < rows) {
@@ -356,20 +384,34 @@ fwd_sm100_kernel(const FwdParams p) {
       // where the unit's samples go in the kept image (read before the record stage is released below)
       int word = 0;
       if (p.sav) word = *reinterpret_cast<const int*>(base_ptr + rec_off + sr * kRStage + hdr_off + 12);
+#ifdef D2C_UNIT_TRACE
+      const int trole = lane != 0 ? -1 : (warp == kGatherWarp0Fwd ? 3 : (warp == kGatherWarp0Fwd + 15 ? 4 : -1));
+#define D2C_TG(e) do { if (trole >= 0) D2C_TR(trole, k, e); } while (0)
+#else
+#define D2C_TG(e) ((void)0)
+#endif
+      D2C_TG(0);
       issue(k, 1, c1);
+      D2C_TG(1);
       if (!ptx::mbar_wait(a_empty(sa), ((k / kAStages) & 1) ^ 1, abort_flag)) break;
+      D2C_TG(2);
       const uint4 o0 = consume(k, 0, c0);
+      D2C_TG(3);
       if (k + 1 < n_my_units) {
         if (!ptx::mbar_wait(r_full((k + 1) % kRStages), ((k + 1) / kRStages) & 1, abort_flag)) break;
+        D2C_TG(4);
         issue(k + 1, 0, c0);
       }
+      D2C_TG(5);
       const uint4 o1 = consume(k, 1, c1);
+      D2C_TG(6);
       ptx::fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
         ptx::mbar_arrive(a_full(sa));
         ptx::mbar_arrive(r_empty(sr));
       }
+      D2C_TG(7);
       // The kept copy goes to global memory AFTER the arrives: an arrive releases the thread's earlier writes, so
       // global stores issued before it would put their round trip to L2 on every unit's critical path (measured:
       // +25 % kernel time); issued here they have a whole unit to complete before the next arrive.
@@ -378,14 +420,12 @@ fwd_sm100_kernel(const FwdParams p) {
           // image block = (tile, 64-voxel block, slice pair, {hi, lo}, slice of the pair): a 64-channel row holds
           // this unit's 32 channels in its half `half`; hi and lo blocks lie two blocks apart, the tile's second
           // 64-voxel block sav_np * 4 blocks further
+          // (an even lane holds the 16-byte hi chunk of the lane pair's 8 channels, an odd lane the lo chunk)
           const int half = word & 1;
-          uint8_t* dst = p.sav + ((long long)(word >> 1) << 13) + sav_row +
-                         (uint32_t)((((4 * half + (j >> 1)) ^ (r0 & 7)) << 4) + (j & 1) * 8);
-          const long long blk1 = (long long)(p.sav_np * 4) << 13;
-          ptx::stg_v2_hint(dst, make_uint2(o0.x, o0.y), pol_stream);
-          ptx::stg_v2_hint(dst + 2 * 8192, make_uint2(o0.z, o0.w), pol_stream);
-          ptx::stg_v2_hint(dst + blk1, make_uint2(o1.x, o1.y), pol_stream);
-          ptx::stg_v2_hint(dst + blk1 + 2 * 8192, make_uint2(o1.z, o1.w), pol_stream);
+          uint8_t* dst = p.sav + ((long long)((word >> 1) + (j & 1) * 2) << 13) + sav_row +
+                         (uint32_t)(((4 * half + (j >> 1)) ^ (r0 & 7)) << 4);
+          ptx::stg_v4_hint(dst, o0, pol_stream);
+          ptx::stg_v4_hint(dst + ((long long)(p.sav_np * 4) << 13), o1, pol_stream);
         } else {
           // image block = (tile, 64-voxel block, slice): the byte image of that half of the A tile
           uint8_t* dst = p.sav + ((long long)word << 13) + sav_row + (uint32_t)((j ^ (r0 & 7)) << 4);
@@ -399,6 +439,16 @@ fwd_sm100_kernel(const FwdParams p) {
   // ---- teardown ----
   ptx::tc_fence_before();
   __syncthreads();
+#ifdef D2C_UNIT_TRACE
+  if (p.trace && threadIdx.x == 0) {
+    unsigned long long t1;
+    unsigned smid;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
+    asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
+    long long* rec = p.trace + 5 * 64 * 8 + blockIdx.x * 4;
+    rec[0] = (long long)cta_t0; rec[1] = (long long)t1; rec[2] = (long long)smid; rec[3] = u_end - u_beg;
+  }
+#endif
   if (threadIdx.x == 0 && *abort_flag) ptx::report_device_timeout();
   if (warp == 0) {
     ptx::tc_fence_after();

@@ -208,5 +208,31 @@ __device__ __forceinline__ uint4 blend_split_store(const uint4 (&c)[8], const fl
   return make_uint4(h01, h23, l01, l23);
 }
 
+// The same item written with ONE 16-byte store per lane: lanes 2i and 2i+1 of a warp hold neighbouring 4-channel
+// items of the same row, so the even lane takes both hi halves (one 16-byte chunk of the row's hi part) and the odd
+// lane both lo halves.  dst_chunk: shared-memory address of the 16-byte chunk THIS lane writes (hi chunk for an even
+// lane, lo chunk for an odd one).  Returns the 16 bytes stored.  Two 8-byte stores per lane cost 2.6x the
+// shared-memory wavefronts of this form (bank conflicts between the half-chunks of different rows).
+__device__ __forceinline__ uint4 blend_split_store16(const uint4 (&c)[8], const float (&w)[8], uint32_t dst_chunk,
+                                                     bool odd_lane) {
+  float v[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    v[0] = __fmaf_rn(__uint_as_float(c[j].x), w[j], v[0]);
+    v[1] = __fmaf_rn(__uint_as_float(c[j].y), w[j], v[1]);
+    v[2] = __fmaf_rn(__uint_as_float(c[j].z), w[j], v[2]);
+    v[3] = __fmaf_rn(__uint_as_float(c[j].w), w[j], v[3]);
+  }
+  const uint32_t h01 = ptx::pack_bf16x2(v[0], v[1]), h23 = ptx::pack_bf16x2(v[2], v[3]);
+  const uint32_t l01 = ptx::pack_bf16x2(v[0] - ptx::bf16_lo(h01), v[1] - ptx::bf16_hi(h01));
+  const uint32_t l23 = ptx::pack_bf16x2(v[2] - ptx::bf16_lo(h23), v[3] - ptx::bf16_hi(h23));
+  // even lane gives its lo and receives the odd lane's hi; the odd lane the other way round
+  const uint32_t t0 = __shfl_xor_sync(0xffffffffu, odd_lane ? h01 : l01, 1);
+  const uint32_t t1 = __shfl_xor_sync(0xffffffffu, odd_lane ? h23 : l23, 1);
+  const uint4 out = odd_lane ? make_uint4(t0, t1, l01, l23) : make_uint4(h01, h23, t0, t1);
+  ptx::sts_v4(dst_chunk, out);
+  return out;
+}
+
 }  // namespace
 }  // namespace d2c
