@@ -42,18 +42,20 @@ constexpr int kSmemLimit = 227 * 1024;
 // Rows past the end of the clip are zero.
 // x3 = 1 (fp32-parity mode): a K block is 32 co and a row is [hi(32 co) | lo(32 co)], hi = bf16(g),
 // lo = bf16(g - hi).
+// x3 = 2 (fp32-parity mode, long contractions): K blocks of 64 co as in the single-pass mode, written twice: the hi
+// parts as one image and the lo parts as a second image `lo_off` bytes further.
 __device__ __forceinline__ float split_part(float f, bool lo) {
   return lo ? f - ptx::bf16_lo(ptx::pack_bf16x2(f, 0.f)) : f;
 }
 
 __global__ void __launch_bounds__(256)
 stage_gy_img_kernel(int Cout, int V, int tiles_per_clip, int b0, int x3, const float* __restrict__ gy,
-                    uint8_t* __restrict__ img) {
+                    uint8_t* __restrict__ img, long long lo_off) {
   __shared__ float tile[64][129];
   const int tile_id = blockIdx.x, kb = blockIdx.y, KB = gridDim.y;
   const int bl = tile_id / tiles_per_clip, v0 = (tile_id % tiles_per_clip) * kBM;
   const int b = b0 + bl;
-  const int nco = x3 ? 32 : 64;
+  const int nco = x3 == 1 ? 32 : 64;
   for (int e = threadIdx.x; e < nco * 128; e += 256) {
     const int co = e >> 7, r = e & 127, v = v0 + r;
     tile[co][r] = (v < V) ? __ldg(gy + ((long long)b * Cout + kb * nco + co) * V + v) : 0.f;
@@ -62,14 +64,22 @@ stage_gy_img_kernel(int Cout, int V, int tiles_per_clip, int b0, int x3, const f
   uint8_t* dst = img + ((long long)tile_id * KB + kb) * kABlockBytes;
   for (int e = threadIdx.x; e < 128 * 8; e += 256) {
     const int r = e >> 3, j = e & 7;
-    const bool lo = x3 && j >= 4;
-    const int cb = x3 ? (j & 3) * 8 : j * 8;
+    const bool lo = x3 == 1 && j >= 4;
+    const int cb = x3 == 1 ? (j & 3) * 8 : j * 8;
+    const long long at = (r >> 3) * 1024 + (r & 7) * 128 + ((j ^ (r & 7)) << 4);
     uint4 o;
     o.x = ptx::pack_bf16x2(split_part(tile[cb + 0][r], lo), split_part(tile[cb + 1][r], lo));
     o.y = ptx::pack_bf16x2(split_part(tile[cb + 2][r], lo), split_part(tile[cb + 3][r], lo));
     o.z = ptx::pack_bf16x2(split_part(tile[cb + 4][r], lo), split_part(tile[cb + 5][r], lo));
     o.w = ptx::pack_bf16x2(split_part(tile[cb + 6][r], lo), split_part(tile[cb + 7][r], lo));
-    *reinterpret_cast<uint4*>(dst + (r >> 3) * 1024 + (r & 7) * 128 + ((j ^ (r & 7)) << 4)) = o;
+    *reinterpret_cast<uint4*>(dst + at) = o;
+    if (x3 == 2) {
+      o.x = ptx::pack_bf16x2(split_part(tile[cb + 0][r], true), split_part(tile[cb + 1][r], true));
+      o.y = ptx::pack_bf16x2(split_part(tile[cb + 2][r], true), split_part(tile[cb + 3][r], true));
+      o.z = ptx::pack_bf16x2(split_part(tile[cb + 4][r], true), split_part(tile[cb + 5][r], true));
+      o.w = ptx::pack_bf16x2(split_part(tile[cb + 6][r], true), split_part(tile[cb + 7][r], true));
+      *reinterpret_cast<uint4*>(dst + lo_off + at) = o;
+    }
   }
 }
 
@@ -80,10 +90,10 @@ stage_gy_img_kernel(int Cout, int V, int tiles_per_clip, int b0, int x3, const f
 // 128-byte row (8 swizzled 16-byte chunks).
 __global__ void __launch_bounds__(64)
 stage_wt_img_kernel(int Cout, int Cin, int K, int cpg, int nh, int x3, const float* __restrict__ w,
-                    uint8_t* __restrict__ img) {
+                    uint8_t* __restrict__ img, long long lo_off) {
   extern __shared__ float wsm[];                    // [64 (x3: 32) co][K]
   const int kb = blockIdx.x, cin = blockIdx.y, KB = gridDim.x;
-  const int nco = x3 ? 32 : 64;
+  const int nco = x3 == 1 ? 32 : 64;
   for (int i = threadIdx.x; i < nco * K; i += 64) {
     const int q = i / K, t = i - q * K;
     wsm[i] = __ldg(w + ((long long)(kb * nco + q) * Cin + cin) * K + t);
@@ -92,8 +102,8 @@ stage_wt_img_kernel(int Cout, int Cin, int K, int cpg, int nh, int x3, const flo
   const int grp = cin / cpg, h = (cin % cpg) / 64, c = cin & 63;
   for (int item = threadIdx.x; item < K * 8; item += 64) {
     const int tap = item >> 3, j = item & 7;
-    const bool lo = x3 && j >= 4;
-    const int cb = x3 ? (j & 3) * 8 : j * 8;
+    const bool lo = x3 == 1 && j >= 4;
+    const int cb = x3 == 1 ? (j & 3) * 8 : j * 8;
     float v[8];
 #pragma unroll
     for (int q = 0; q < 8; ++q) v[q] = split_part(wsm[(cb + q) * K + tap], lo);
@@ -105,6 +115,13 @@ stage_wt_img_kernel(int Cout, int Cin, int K, int cpg, int nh, int x3, const flo
     uint8_t* dst = img + ((long long)nb * KB + kb) * kBStageBytes + (row >> 3) * 1024 + (row & 7) * 128 +
                    ((j ^ (row & 7)) << 4);
     *reinterpret_cast<uint4*>(dst) = o;
+    if (x3 == 2) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q) v[q] = split_part(wsm[(cb + q) * K + tap], true);
+      o.x = ptx::pack_bf16x2(v[0], v[1]); o.y = ptx::pack_bf16x2(v[2], v[3]);
+      o.z = ptx::pack_bf16x2(v[4], v[5]); o.w = ptx::pack_bf16x2(v[6], v[7]);
+      *reinterpret_cast<uint4*>(dst + lo_off) = o;
+    }
   }
 }
 
@@ -123,13 +140,75 @@ struct DcolParams {
   int tiles_per_clip, n_tiles;
   long long n_units;       // n_tiles * NB
   int tmem_cols;
+  long long gy_lo_off, wt_lo_off;   // dcol_sm100_split_kernel: byte offsets of the lo images
 };
 
+// Store epilogue shared by the gradient-column kernels: warp w serves TMEM lane quarter w % 4 and column half w / 4 of
+// the block's accumulator (two accumulators alternate; their full / empty barriers are 8 bytes apart).
+__device__ __forceinline__ void dcol_epilogue(const DcolParams& p, int warp, int lane, long long u_beg, long long u_end,
+                                              uint32_t tmem_base, uint32_t acc_full0, uint32_t acc_empty0,
+                                              volatile int* abort_flag) {
+    // ---- epilogue: TMEM -> dcol (a thread owns one voxel row and a 128-column half of the block)
+    const int quarter = warp & 3, half = warp >> 2;
+    uint32_t q = 0;
+    for (long long u = u_beg; u < u_end; ++u, ++q) {
+      const int tile = (int)(u / p.NB), nb = (int)(u % p.NB);
+      const int bl = tile / p.tiles_per_clip, v0 = (tile % p.tiles_per_clip) * kBM;
+      const int v = v0 + quarter * 32 + lane;
+      // dcol is slice-major: [clip][slice][voxel][64 channels]; a 256-column block is 4 slices
+      const long long S = p.NT / 64;
+      float* row = p.dcol + (((long long)bl * S + nb * 4) * p.V + v) * 64;
+      const long long slice_stride = (long long)p.V * 64;
+      const int acc = q & 1;
+      const int ncols = min(kNBlock, p.NT - nb * kNBlock);
+      // Lanes 2i / 2i+1 hold rows v, v+1 (256 bytes apart).  They swap every other 16-byte chunk so that
+      // each store instruction has the pair write one full 32-byte sector of ONE row (first the even
+      // lane's row, then the odd lane's) instead of two half sectors of two rows.
+      const bool odd = lane & 1;
+      const bool ok_even = (v - (odd ? 1 : 0)) < p.V, ok_odd = (v + (odd ? 0 : 1)) < p.V;
+      auto chunk_ptr = [&](int c0) {   // this lane's first 16-byte slot of the even row in the 32-column chunk c0
+        return reinterpret_cast<float4*>(row - (odd ? 64 : 0) + (c0 >> 6) * slice_stride + (c0 & 63) + (odd ? 4 : 0));
+      };
+      const int c_beg = half * 128, c_end = min(ncols, half * 128 + 128);
+      if (!ptx::mbar_wait(acc_full0 + 8u * acc, (q >> 1) & 1, abort_flag)) break;
+      ptx::tc_fence_after();
+      for (int c0 = c_beg; c0 < c_end; c0 += 32) {
+        uint32_t r[32];
+        ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * kNBlock + c0), r);
+        ptx::tmem_ld_wait();
+        float4* dst = chunk_ptr(c0);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          uint32_t send[4], recv[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) send[e] = odd ? r[8 * i + e] : r[8 * i + 4 + e];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) recv[e] = __shfl_xor_sync(0xffffffffu, send[e], 1);
+          float4 first, second;   // first: even row's chunk (2i + odd); second: odd row's chunk (2i + odd)
+          if (odd) {
+            first = make_float4(__uint_as_float(recv[0]), __uint_as_float(recv[1]), __uint_as_float(recv[2]),
+                                __uint_as_float(recv[3]));
+            second = make_float4(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]),
+                                 __uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+          } else {
+            first = make_float4(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1]),
+                                __uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
+            second = make_float4(__uint_as_float(recv[0]), __uint_as_float(recv[1]), __uint_as_float(recv[2]),
+                                 __uint_as_float(recv[3]));
+          }
+          if (ok_even) dst[2 * i] = first;
+          if (ok_odd) dst[2 * i + 16] = second;    // next row: + 64 floats
+        }
+      }
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(acc_empty0 + 8u * acc);
+    }
+}
+
 // kX3 = 1 (fp32-parity mode): a K block is 32 co with rows [hi | lo] in both operands and the issuer forms
-// g_hi*w_hi + g_lo*w_hi + g_hi*w_lo from the 16-wide K sub-blocks; the grad_out tile of Cout = 512 is then
-// 256 KB, so the contraction runs as two launches over half of the K blocks each, into two partial buffers
-// that the sampling-gradient kernel adds as it reads them (a second launch that read-modify-wrote the first
-// one's result cost 0.87 ms against 0.50 ms).
+// g_hi*w_hi + g_lo*w_hi + g_hi*w_lo from the 16-wide K sub-blocks.  The whole grad_out tile must be resident
+// (at most 8 blocks): Cout <= 256 in this mode; longer contractions run dcol_sm100_split_kernel below.
 template <int kX3>
 __global__ void __launch_bounds__(kDcolThreads, 1)
 dcol_sm100_kernel(const DcolParams p) {
@@ -170,62 +249,7 @@ dcol_sm100_kernel(const DcolParams p) {
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp < kDcolEpiWarps) {
-    // ---- epilogue: TMEM -> dcol (a thread owns one voxel row and a 128-column half of the block)
-    const int quarter = warp & 3, half = warp >> 2;
-    uint32_t q = 0;
-    for (long long u = u_beg; u < u_end; ++u, ++q) {
-      const int tile = (int)(u / p.NB), nb = (int)(u % p.NB);
-      const int bl = tile / p.tiles_per_clip, v0 = (tile % p.tiles_per_clip) * kBM;
-      const int v = v0 + quarter * 32 + lane;
-      // dcol is slice-major: [clip][slice][voxel][64 channels]; a 256-column block is 4 slices
-      const long long S = p.NT / 64;
-      float* row = p.dcol + (((long long)bl * S + nb * 4) * p.V + v) * 64;
-      const long long slice_stride = (long long)p.V * 64;
-      const int acc = q & 1;
-      const int ncols = min(kNBlock, p.NT - nb * kNBlock);
-      // Lanes 2i / 2i+1 hold rows v, v+1 (256 bytes apart).  They swap every other 16-byte chunk so that
-      // each store instruction has the pair write one full 32-byte sector of ONE row (first the even
-      // lane's row, then the odd lane's) instead of two half sectors of two rows.
-      const bool odd = lane & 1;
-      const bool ok_even = (v - (odd ? 1 : 0)) < p.V, ok_odd = (v + (odd ? 0 : 1)) < p.V;
-      auto chunk_ptr = [&](int c0) {   // this lane's first 16-byte slot of the even row in the 32-column chunk c0
-        return reinterpret_cast<float4*>(row - (odd ? 64 : 0) + (c0 >> 6) * slice_stride + (c0 & 63) + (odd ? 4 : 0));
-      };
-      const int c_beg = half * 128, c_end = min(ncols, half * 128 + 128);
-      if (!ptx::mbar_wait(acc_full(acc), (q >> 1) & 1, abort_flag)) break;
-      ptx::tc_fence_after();
-      for (int c0 = c_beg; c0 < c_end; c0 += 32) {
-        uint32_t r[32];
-        ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * kNBlock + c0), r);
-        ptx::tmem_ld_wait();
-        float4* dst = chunk_ptr(c0);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          uint32_t send[4], recv[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) send[e] = odd ? r[8 * i + e] : r[8 * i + 4 + e];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) recv[e] = __shfl_xor_sync(0xffffffffu, send[e], 1);
-          float4 first, second;   // first: even row's chunk (2i + odd); second: odd row's chunk (2i + odd)
-          if (odd) {
-            first = make_float4(__uint_as_float(recv[0]), __uint_as_float(recv[1]), __uint_as_float(recv[2]),
-                                __uint_as_float(recv[3]));
-            second = make_float4(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]),
-                                 __uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
-          } else {
-            first = make_float4(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1]),
-                                __uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
-            second = make_float4(__uint_as_float(recv[0]), __uint_as_float(recv[1]), __uint_as_float(recv[2]),
-                                 __uint_as_float(recv[3]));
-          }
-          if (ok_even) dst[2 * i] = first;
-          if (ok_odd) dst[2 * i + 16] = second;    // next row: + 64 floats
-        }
-      }
-      ptx::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(acc_empty(acc));
-    }
+    dcol_epilogue(p, warp, lane, u_beg, u_end, tmem_base, acc_full(0), acc_empty(0), abort_flag);
   } else if (warp == kDcolMmaWarp) {
     if (lane == 0) {
       uint32_t q = 0, kbc = 0;
@@ -311,6 +335,161 @@ dcol_sm100_kernel(const DcolParams p) {
   }
 }
 
+// Fp32-parity contraction longer than the resident tile (Cout > 256) in ONE launch.  Operands come as separate hi and
+// lo images of 64-wide K blocks.  The hi part of the grad_out tile stays resident (Cout/64 blocks of 16 KB); per
+// (256-column block, K block) three ring entries arrive in this order
+//     W_hi (up to 32 KB)   -> g_hi * w_hi
+//     g_lo (16 KB)         -> g_lo * w_hi      (W_hi still in its stage)
+//     W_lo (up to 32 KB)   -> g_hi * w_lo
+// so every product accumulates into the block's accumulator before the epilogue stores it: the gradient columns are
+// written once (two launches into two partial buffers wrote and re-read 1.4 GB more).  The lo part of the tile is
+// re-streamed from L2 for every column block (+25 % bytes into shared memory).
+__global__ void __launch_bounds__(kDcolThreads, 1)
+dcol_sm100_split_kernel(const DcolParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = ptx::smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - raw);
+  const int a_bytes = p.KB * kABlockBytes;
+  const uint32_t a_base = base, b_base = base + a_bytes, bar_base = b_base + kBStages * kBStageBytes;
+  auto b_full = [&](int s) { return bar_base + 8u * s; };
+  auto b_empty = [&](int s) { return bar_base + 8u * (kBStages + s); };
+  auto acc_full = [&](int a) { return bar_base + 8u * (2 * kBStages + a); };
+  auto acc_empty = [&](int a) { return bar_base + 8u * (2 * kBStages + 2 + a); };
+  const uint32_t a_full = bar_base + 8u * (2 * kBStages + 4), a_empty = bar_base + 8u * (2 * kBStages + 5);
+  const int slot_off = a_bytes + kBStages * kBStageBytes + 8 * (2 * kBStages + 6);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + slot_off);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + slot_off + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long u_beg = p.n_units * blockIdx.x / gridDim.x, u_end = p.n_units * (blockIdx.x + 1) / gridDim.x;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kBStages; ++s) { ptx::mbar_init(b_full(s), 1); ptx::mbar_init(b_empty(s), 1); }
+    for (int a = 0; a < 2; ++a) { ptx::mbar_init(acc_full(a), 1); ptx::mbar_init(acc_empty(a), kDcolEpiWarps); }
+    ptx::mbar_init(a_full, 1);
+    ptx::mbar_init(a_empty, 1);
+    *abort_flag = 0;
+    ptx::fence_mbar_init();
+  }
+  if (warp == 0) {
+    __syncwarp();
+    ptx::tmem_alloc(ptx::smem_u32((const void*)tmem_slot), (uint32_t)p.tmem_cols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp < kDcolEpiWarps) {
+    dcol_epilogue(p, warp, lane, u_beg, u_end, tmem_base, acc_full(0), acc_empty(0), abort_flag);
+  } else if (warp == kDcolMmaWarp) {
+    if (lane == 0) {
+      uint32_t q = 0, e = 0;            // column blocks and ring entries consumed so far
+      int seg = 0;
+      bool ok = true;
+      auto wait_entry = [&](uint32_t idx) {
+        return ptx::mbar_wait(b_full(idx % kBStages), (idx / kBStages) & 1, abort_flag);
+      };
+      for (long long u = u_beg; ok && u < u_end; ++seg) {
+        const int nb_beg = (int)(u % p.NB);
+        const int nb_end = (int)min((long long)p.NB, nb_beg + (u_end - u));
+        u += nb_end - nb_beg;
+        if (!ptx::mbar_wait(a_full, seg & 1, abort_flag)) break;
+        ptx::tc_fence_after();
+        for (int nb = nb_beg; ok && nb < nb_end; ++nb, ++q) {
+          const int acc = q & 1;
+          const int ncols = min(kNBlock, p.NT - nb * kNBlock);
+          if (!ptx::mbar_wait(acc_empty(acc), ((q >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+          ptx::tc_fence_after();
+          const uint32_t idesc = ptx::umma_idesc_bf16_f32(kBM, ncols);
+          const uint32_t d = tmem_base + (uint32_t)(acc * kNBlock);
+          for (int kb = 0; kb < p.KB; ++kb, e += 3) {
+            const uint64_t a_hi = ptx::umma_desc_kmajor_sw128(a_base + kb * kABlockBytes);
+            const uint32_t s_whi = e % kBStages, s_glo = (e + 1) % kBStages, s_wlo = (e + 2) % kBStages;
+            const uint64_t w_hi = ptx::umma_desc_kmajor_sw128(b_base + s_whi * kBStageBytes);
+            const uint64_t g_lo = ptx::umma_desc_kmajor_sw128(b_base + s_glo * kBStageBytes);
+            const uint64_t w_lo = ptx::umma_desc_kmajor_sw128(b_base + s_wlo * kBStageBytes);
+            if (!wait_entry(e)) { ok = false; break; }
+            ptx::tc_fence_after();
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              ptx::umma_bf16(d, a_hi + (uint64_t)(2 * k), w_hi + (uint64_t)(2 * k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            if (!wait_entry(e + 1)) { ok = false; break; }
+            ptx::tc_fence_after();
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              ptx::umma_bf16(d, g_lo + (uint64_t)(2 * k), w_hi + (uint64_t)(2 * k), idesc, 1u);
+            ptx::umma_commit(b_empty(s_whi));
+            ptx::umma_commit(b_empty(s_glo));
+            if (!wait_entry(e + 2)) { ok = false; break; }
+            ptx::tc_fence_after();
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              ptx::umma_bf16(d, a_hi + (uint64_t)(2 * k), w_lo + (uint64_t)(2 * k), idesc, 1u);
+            ptx::umma_commit(b_empty(s_wlo));
+          }
+          if (ok) ptx::umma_commit(acc_full(acc));
+        }
+        if (ok) ptx::umma_commit(a_empty);
+      }
+    }
+  } else if (warp == kDcolLoadWarp) {
+    if (lane == 0) {
+      uint32_t e = 0;
+      int seg = 0;
+      bool ok = true;
+      const uint64_t pol_keep = ptx::l2_evict_last();      // both images are re-read by every CTA
+      auto push = [&](const uint8_t* src, uint32_t bytes) {
+        const int sb = e % kBStages;
+        if (!ptx::mbar_wait(b_empty(sb), ((e / kBStages) & 1) ^ 1, abort_flag)) return false;
+        ptx::mbar_arrive_expect_tx(b_full(sb), bytes);
+        ptx::bulk_g2s_hint(b_base + sb * kBStageBytes, src, bytes, b_full(sb), pol_keep);
+        ++e;
+        return true;
+      };
+      for (long long u = u_beg; ok && u < u_end; ++seg) {
+        const int tile = (int)(u / p.NB), nb_beg = (int)(u % p.NB);
+        const int nb_end = (int)min((long long)p.NB, nb_beg + (u_end - u));
+        u += nb_end - nb_beg;
+        if (!ptx::mbar_wait(a_empty, (seg & 1) ^ 1, abort_flag)) break;
+        ptx::mbar_arrive_expect_tx(a_full, (uint32_t)a_bytes);
+        const uint8_t* asrc = p.gy_img + (long long)tile * p.KBT * kABlockBytes;
+        for (int off = 0; off < a_bytes; off += 32768)
+          ptx::bulk_g2s_hint(a_base + off, asrc + off, (uint32_t)min(32768, a_bytes - off), a_full, pol_keep);
+        for (int nb = nb_beg; ok && nb < nb_end; ++nb) {
+          const uint32_t wbytes = (uint32_t)(min(kNBlock, p.NT - nb * kNBlock) * 128);
+          for (int kb = 0; ok && kb < p.KB; ++kb) {
+            const uint8_t* w_hi = p.wt_img + ((long long)nb * p.KBT + kb) * kBStageBytes;
+            ok = push(w_hi, wbytes) && push(asrc + p.gy_lo_off + (long long)kb * kABlockBytes, (uint32_t)kABlockBytes) &&
+                 push(w_hi + p.wt_lo_off, wbytes);
+          }
+        }
+      }
+      // drain: never exit with a bulk copy in flight
+      const uint32_t issued = e;
+      for (uint32_t qq = (issued > (uint32_t)kBStages ? issued - kBStages : 0); qq < issued; ++qq) {
+        const long long t0 = clock64();
+        while (!ptx::mbar_try_wait(b_full(qq % kBStages), (qq / kBStages) & 1))
+          if (clock64() - t0 > ptx::kWaitBudgetCycles) break;
+      }
+      if (seg > 0) {
+        const long long t0 = clock64();
+        while (!ptx::mbar_try_wait(a_full, (seg - 1) & 1))
+          if (clock64() - t0 > ptx::kWaitBudgetCycles) break;
+      }
+    }
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag) ptx::report_device_timeout();
+  if (warp == 0) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+  }
+}
+
 // ---- (b) sampling gradient + scatter ---------------------------------------------------------------
 
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
@@ -329,7 +508,7 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
 template <bool FieldOut, bool kF32X, bool kNarrow = false>
 __global__ void __launch_bounds__(256, kF32X ? 2 : 3)
 sample_grad_taps_kernel(Geom g, ClStrides cs, int b0, int nh, const float4* __restrict__ recs,
-                        const float* __restrict__ dcol, long long dcol2_off, const void* __restrict__ x_cl_v, bool has_mask,
+                        const float* __restrict__ dcol, const void* __restrict__ x_cl_v, bool has_mask,
                         float* __restrict__ grad_coord, float* __restrict__ grad_mask, float* __restrict__ gx_cl,
                         int field_nch, int3 field_ch, const float* __restrict__ field_axes, HeadCfg head) {
   const int j = threadIdx.x & 7;
@@ -353,18 +532,9 @@ sample_grad_taps_kernel(Geom g, ClStrides cs, int b0, int nh, const float4* __re
 
   const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
   float fsum[3] = {0.f, 0.f, 0.f};
-  // gradient columns of a contraction split over two launches arrive as two partial buffers, dcol2_off apart
   auto ld_cols = [&](const float* q, float4& a, float4& b) {
     a = __ldg(reinterpret_cast<const float4*>(q));
     b = kNarrow ? zero4 : __ldg(reinterpret_cast<const float4*>(q + 32));
-    if (kF32X && dcol2_off) {        // only the fp32-parity contraction is ever split
-      const float4 a2 = __ldg(reinterpret_cast<const float4*>(q + dcol2_off));
-      a.x += a2.x; a.y += a2.y; a.z += a2.z; a.w += a2.w;
-      if (!kNarrow) {
-        const float4 b2 = __ldg(reinterpret_cast<const float4*>(q + dcol2_off + 32));
-        b.x += b2.x; b.y += b2.y; b.z += b2.z; b.w += b2.w;
-      }
-    }
   };
   float4 rec_n = __ldg(recp);
   float4 d0_n, d1_n;
@@ -525,6 +695,8 @@ int field_nch_of<FieldCoords<float>>(const FieldCoords<float>& c) { return c.nch
 struct BwdPlan {
   int nh, S, NT, KB, KBT, NB, tiles_per_clip, tmem_cols, smem_bytes, clips_per_chunk;
   bool pairg;       // 32 channels per offset group: a 64-channel slice holds two neighbouring groups
+  bool split;       // fp32-parity mode with Cout > 256: separate hi / lo operand images, dcol_sm100_split_kernel
+  long long gy_lo_off, wt_lo_off;
   size_t x_cl_bytes, rec_bytes, gat_bytes, gy_img_bytes, wt_img_bytes, dcol_bytes, gx_cl_bytes, axes_bytes;
 };
 
@@ -539,8 +711,9 @@ bool make_bwd_plan(const Geom& g, unsigned long long cap, bool x3, BwdPlan* pl) 
   pl->nh = pl->pairg ? 1 : g.cpg / 64;
   pl->S = pl->pairg ? (g.G / 2) * g.K : g.G * g.K * pl->nh;
   pl->NT = pl->S * 64;
-  pl->KBT = g.Cout / (x3 ? 32 : 64);                     // K blocks per image
-  pl->KB = pl->KBT > 8 ? 8 : pl->KBT;                    // resident per launch (x3, Cout > 256: two launches)
+  pl->split = x3 && g.Cout > 256;
+  pl->KBT = g.Cout / ((x3 && !pl->split) ? 32 : 64);     // K blocks per image
+  pl->KB = pl->KBT;                                      // all resident (<= 8 blocks of 16 KB)
   pl->NB = (pl->NT + kNBlock - 1) / kNBlock;
   pl->tiles_per_clip = (g.V + kBM - 1) / kBM;
   pl->tmem_cols = 512;
@@ -550,9 +723,11 @@ bool make_bwd_plan(const Geom& g, unsigned long long cap, bool x3, BwdPlan* pl) 
   pl->x_cl_bytes = align_up((size_t)g.B * g.Vin * g.Cin * (x3 ? 4 : 2), 256);
   pl->rec_bytes = pos_records_bytes(g);
   pl->gat_bytes = gather_records_bytes(g);
-  pl->gy_img_bytes = align_up((size_t)pl->clips_per_chunk * pl->tiles_per_clip * pl->KBT * kABlockBytes, 256);
-  pl->wt_img_bytes = align_up((size_t)pl->NB * pl->KBT * kBStageBytes, 256);
-  pl->dcol_bytes = align_up((size_t)pl->clips_per_chunk * g.V * pl->NT * 4 * (pl->KBT > pl->KB ? 2 : 1), 256);
+  pl->gy_lo_off = (long long)pl->clips_per_chunk * pl->tiles_per_clip * pl->KBT * kABlockBytes;
+  pl->wt_lo_off = (long long)pl->NB * pl->KBT * kBStageBytes;
+  pl->gy_img_bytes = align_up((size_t)pl->gy_lo_off * (pl->split ? 2 : 1), 256);
+  pl->wt_img_bytes = align_up((size_t)pl->wt_lo_off * (pl->split ? 2 : 1), 256);
+  pl->dcol_bytes = align_up((size_t)pl->clips_per_chunk * g.V * pl->NT * 4, 256);
   pl->gx_cl_bytes = align_up((size_t)g.B * g.Vin * g.Cin * 4, 256);
   pl->axes_bytes = 256;
   return true;
@@ -625,18 +800,20 @@ int run_bwd(const Geom& g, bool x3, const Coords& coords, unsigned long long cap
   if ((rc = sm100_dw(g, x3, gy, x_cl, gat, grad_w, grad_bias, dw_ws, st, sav))) return rc;
   if (params_ready) D2C_CUDA_TRY(cudaEventRecord(params_ready, st));
   prof_mark(st, "bwd_stage_weights");
+  const int img_mode = pl.split ? 2 : (x3 ? 1 : 0);
   stage_wt_img_kernel<<<dim3((unsigned)pl.KBT, (unsigned)g.Cin), 64, 64 * g.K * sizeof(float), st>>>(
-      g.Cout, g.Cin, g.K, pl.pairg ? 64 : g.cpg, pl.nh, x3 ? 1 : 0, w, wt_img);
+      g.Cout, g.Cin, g.K, pl.pairg ? 64 : g.cpg, pl.nh, img_mode, w, wt_img, pl.wt_lo_off);
   D2C_LAUNCH_CHECK();
   D2C_CUDA_TRY(cudaFuncSetAttribute(dcol_sm100_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes));
   D2C_CUDA_TRY(cudaFuncSetAttribute(dcol_sm100_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes));
+  D2C_CUDA_TRY(cudaFuncSetAttribute(dcol_sm100_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes));
 
   for (int b0 = 0; b0 < g.B; b0 += pl.clips_per_chunk) {
     const int nbc = (g.B - b0 < pl.clips_per_chunk) ? g.B - b0 : pl.clips_per_chunk;
     const int n_tiles = nbc * pl.tiles_per_clip;
     prof_mark(st, "bwd_stage_grad_out");
     stage_gy_img_kernel<<<dim3((unsigned)n_tiles, (unsigned)pl.KBT), 256, 0, st>>>(g.Cout, g.V, pl.tiles_per_clip, b0,
-                                                                                  x3 ? 1 : 0, gy, gy_img);
+                                                                                  img_mode, gy, gy_img, pl.gy_lo_off);
     D2C_LAUNCH_CHECK();
     DcolParams p;
     p.gy_img = gy_img; p.wt_img = wt_img; p.dcol = dcol;
@@ -647,36 +824,31 @@ int run_bwd(const Geom& g, bool x3, const Coords& coords, unsigned long long cap
     if (grid > sm_count) grid = sm_count;
     if (grid < 1) grid = 1;
     prof_mark(st, "bwd_dcol_sm100");
-    p.KBT = pl.KBT;
-    // a contraction longer than the resident grad_out tile (fp32-parity mode, Cout > 256) runs as two launches
-    // into two partial buffers that the sampling-gradient kernel adds while it reads them
-    const long long dcol_part = (long long)pl.clips_per_chunk * g.V * pl.NT;
-    const long long dcol2_off = pl.KBT > pl.KB ? dcol_part : 0;
-    for (int kb0 = 0; kb0 < pl.KBT; kb0 += pl.KB) {      // bf16 mode and Cout <= 256: a single launch
-      p.kb0 = kb0; p.KB = (pl.KBT - kb0 < pl.KB) ? pl.KBT - kb0 : pl.KB;
-      p.dcol = dcol + (kb0 > 0 ? dcol_part : 0);
-      if (x3)
-        dcol_sm100_kernel<1><<<(unsigned)grid, kDcolThreads, pl.smem_bytes, st>>>(p);
-      else
-        dcol_sm100_kernel<0><<<(unsigned)grid, kDcolThreads, pl.smem_bytes, st>>>(p);
-      D2C_LAUNCH_CHECK();
-    }
+    p.KBT = pl.KBT; p.kb0 = 0; p.KB = pl.KB;
+    p.gy_lo_off = pl.gy_lo_off; p.wt_lo_off = pl.wt_lo_off;
+    if (pl.split)
+      dcol_sm100_split_kernel<<<(unsigned)grid, kDcolThreads, pl.smem_bytes, st>>>(p);
+    else if (x3)
+      dcol_sm100_kernel<1><<<(unsigned)grid, kDcolThreads, pl.smem_bytes, st>>>(p);
+    else
+      dcol_sm100_kernel<0><<<(unsigned)grid, kDcolThreads, pl.smem_bytes, st>>>(p);
+    D2C_LAUNCH_CHECK();
     prof_mark(st, "bwd_sample_grad");
     dim3 sgrid((unsigned)((g.V + 31) / 32), (unsigned)(nbc * g.G));
     if (pl.pairg && x3)
-      sample_grad_taps_kernel<FieldOut, true, true><<<sgrid, 256, 0, st>>>(g, cs, b0, pl.nh, recs, dcol, dcol2_off, x_cl,
+      sample_grad_taps_kernel<FieldOut, true, true><<<sgrid, 256, 0, st>>>(g, cs, b0, pl.nh, recs, dcol, x_cl,
                                                                            mask != nullptr, grad_coord, grad_mask,
                                                                            gx_cl, field_nch, field_ch, axes_dev, head);
     else if (pl.pairg)
-      sample_grad_taps_kernel<FieldOut, false, true><<<sgrid, 256, 0, st>>>(g, cs, b0, pl.nh, recs, dcol, dcol2_off, x_cl,
+      sample_grad_taps_kernel<FieldOut, false, true><<<sgrid, 256, 0, st>>>(g, cs, b0, pl.nh, recs, dcol, x_cl,
                                                                             mask != nullptr, grad_coord, grad_mask,
                                                                             gx_cl, field_nch, field_ch, axes_dev, head);
     else if (x3)
-      sample_grad_taps_kernel<FieldOut, true><<<sgrid, 256, 0, st>>>(g, cs, b0, pl.nh, recs, dcol, dcol2_off, x_cl,
+      sample_grad_taps_kernel<FieldOut, true><<<sgrid, 256, 0, st>>>(g, cs, b0, pl.nh, recs, dcol, x_cl,
                                                                      mask != nullptr, grad_coord, grad_mask, gx_cl,
                                                                      field_nch, field_ch, axes_dev, head);
     else
-      sample_grad_taps_kernel<FieldOut, false><<<sgrid, 256, 0, st>>>(g, cs, b0, pl.nh, recs, dcol, dcol2_off, x_cl,
+      sample_grad_taps_kernel<FieldOut, false><<<sgrid, 256, 0, st>>>(g, cs, b0, pl.nh, recs, dcol, x_cl,
                                                                       mask != nullptr, grad_coord, grad_mask, gx_cl,
                                                                       field_nch, field_ch, axes_dev, head);
     D2C_LAUNCH_CHECK();
