@@ -335,8 +335,8 @@ size_t d2c_sample_cache_bytes(const d2c_conv_desc* desc) {
   bool fx3 = false, bx3 = false;
   if (!sm100_fwd_variant(g, mode, &fx3) || !sm100_bwd_variant(g, mode, cap, &bx3) || fx3 != bx3) return 0;
   int np = 0;
-  size_t bytes = 0;
-  return sm100_sample_image_plan(g, fx3, &np, &bytes) ? bytes : 0;
+  SampleCacheLayout lay{};
+  return sm100_sample_cache_layout(g, fx3, &np, &lay) ? lay.total() : 0;
 }
 
 int d2c_bind_sample_cache(d2c_sample_cache* cache) {

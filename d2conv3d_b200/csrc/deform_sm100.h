@@ -33,6 +33,13 @@ SampleCache* current_sample_cache();
 // Image geometry for this shape in this mode: slice pairs of the weight gradient and total bytes; false when the
 // weight-gradient kernel does not take the shape.
 bool sm100_sample_image_plan(const Geom& g, bool x3, int* n_pairs, size_t* bytes);
+// What else the cache carries behind the image, so that the backward stages nothing twice: the channels-last copy of
+// x (fp16 / fp32 as the mode wants it) and the sampling-position records {z, y, x, mask} of every sample.
+struct SampleCacheLayout {
+  size_t image_bytes, x_cl_bytes, pos_bytes;
+  size_t total() const { return image_bytes + x_cl_bytes + pos_bytes; }
+};
+bool sm100_sample_cache_layout(const Geom& g, bool x3, int* n_pairs, SampleCacheLayout* lay);
 // Which kernel family (single-pass / hi-lo split) the forward and the backward of this shape run in this mode.
 bool sm100_fwd_variant(const Geom& g, int math_mode, bool* x3);
 bool sm100_bwd_variant(const Geom& g, int math_mode, unsigned long long cap, bool* x3);

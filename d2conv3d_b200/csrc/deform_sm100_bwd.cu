@@ -778,21 +778,25 @@ int run_bwd(const Geom& g, bool x3, const Coords& coords, unsigned long long cap
       D2C_CUDA_TRY(cudaMemsetAsync(grad_coord, 0, sizeof(float) * grad_coord_elems, st));
   }
   if (grad_bias) D2C_CUDA_TRY(cudaMemsetAsync(grad_bias, 0, sizeof(float) * g.Cout, st));
-  {
+  // What the forward of this call kept in this mode's format: its operand tiles (the weight gradient streams them, no
+  // gather records needed), the staged input and the position records -- nothing is staged a second time.
+  if (SampleCache* sc = current_sample_cache()) {
+    int np = 0;
+    SampleCacheLayout lay{};
+    if (sc->data && sc->format == (x3 ? 2 : 1) && sm100_sample_cache_layout(g, x3, &np, &lay) && sc->bytes >= lay.total()) {
+      sav = sc->data;
+      x_cl = reinterpret_cast<uint8_t*>(sc->data) + lay.image_bytes;
+      recs = reinterpret_cast<float4*>(reinterpret_cast<uint8_t*>(sc->data) + lay.image_bytes + lay.x_cl_bytes);
+    }
+  }
+  if (!sav) {
     dim3 grid((unsigned)((g.Vin + 31) / 32), (unsigned)((g.Cin + 63) / 64), (unsigned)g.B);
     if (x3)
       stage_input_cl_f32_kernel<<<grid, 256, 0, st>>>(g.Cin, g.Vin, x, reinterpret_cast<float*>(x_cl));
     else
       stage_input_cl_f16_kernel<<<grid, 256, 0, st>>>(g.Cin, g.Vin, x, reinterpret_cast<__half*>(x_cl));
     D2C_LAUNCH_CHECK();
-    // samples kept by the forward in this mode's format: the weight gradient reads them, no gather records needed
-    if (SampleCache* sc = current_sample_cache()) {
-      int np = 0;
-      size_t need = 0;
-      if (sc->data && sc->format == (x3 ? 2 : 1) && sm100_sample_image_plan(g, x3, &np, &need) && sc->bytes >= need)
-        sav = sc->data;
-    }
-    if ((rc = launch_sample_records(g, coords, mask, head, recs, sav ? nullptr : gat, st, x3))) return rc;
+    if (!sav && (rc = launch_sample_records(g, coords, mask, head, recs, gat, st, x3))) return rc;
   }
   // The parameter gradients come first: the weight gradient (tensor-core implicit GEMM over the re-sampled tile)
   // needs only the records and the staged input, and its grad_out staging pass also sums grad_bias.  A caller that

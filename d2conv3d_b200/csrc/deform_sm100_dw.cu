@@ -681,6 +681,15 @@ bool sm100_sample_image_plan(const Geom& g, bool x3, int* n_pairs, size_t* bytes
   return true;
 }
 
+bool sm100_sample_cache_layout(const Geom& g, bool x3, int* n_pairs, SampleCacheLayout* lay) {
+  size_t img = 0;
+  if (!sm100_sample_image_plan(g, x3, n_pairs, &img)) return false;
+  lay->image_bytes = align_up(img, 256);
+  lay->x_cl_bytes = align_up((size_t)g.B * g.Vin * g.Cin * (x3 ? 4 : 2), 256);
+  lay->pos_bytes = pos_records_bytes(g);
+  return true;
+}
+
 size_t sm100_dw_workspace(const Geom& g, bool x3) {
   DwPlan dp;
   if (!make_dw_plan(g, 148, x3, &dp)) return 0;

@@ -213,6 +213,21 @@ int run_fwd(const Geom& g, int math_mode, const Coords& coords, const HeadCfg& h
   void* x_cl = wsp; wsp += pl.x_cl_bytes;
   uint8_t* w_sw = wsp; wsp += pl.w_sw_bytes;
   uint4* recs = reinterpret_cast<uint4*>(wsp);
+  // A bound sample cache that is large enough takes the operand tiles (written by the kernel), and the staged input
+  // and the position records move into it, so that the backward of this call stages nothing a second time.
+  SampleCache* sc = current_sample_cache();
+  SampleCacheLayout lay{};
+  int sav_np = 0;
+  uint8_t* sav = nullptr;
+  float4* pos = nullptr;
+  if (sc) {
+    sc->format = 0;
+    if (sc->data && sm100_sample_cache_layout(g, x3, &sav_np, &lay) && sc->bytes >= lay.total()) {
+      sav = reinterpret_cast<uint8_t*>(sc->data);
+      x_cl = sav + lay.image_bytes;
+      pos = reinterpret_cast<float4*>(sav + lay.image_bytes + lay.x_cl_bytes);
+    }
+  }
   int sm_count = 0, rc;
   if ((rc = device_sm_count(&sm_count))) return rc;
   ptx::bind_status_sink();
@@ -265,6 +280,7 @@ int run_fwd(const Geom& g, int math_mode, const Coords& coords, const HeadCfg& h
     }
   }
 
+  if (pair_clusters > 0) { sav = nullptr; pos = nullptr; x_cl = ws; }       // the CTA-pair kernel keeps nothing
   prof_mark(st, "fwd_stage_operands");
   {
     dim3 sgrid((unsigned)((g.Vin + 31) / 32), (unsigned)((g.Cin + 63) / 64), (unsigned)g.B);
@@ -282,7 +298,7 @@ int run_fwd(const Geom& g, int math_mode, const Coords& coords, const HeadCfg& h
                                                                               pl.dual ? 64 : g.cpg, pl.nh, w, w_sw);
       D2C_LAUNCH_CHECK();
     }
-    if ((rc = launch_sample_records(g, coords, mask, head, nullptr, recs, st, x3))) return rc;
+    if ((rc = launch_sample_records(g, coords, mask, head, pos, recs, st, x3))) return rc;
     if (!whole_tiles_only) D2C_CUDA_TRY(cudaMemsetAsync(y, 0, sizeof(float) * (size_t)g.B * g.Cout * g.V, st));
   }
 
@@ -294,15 +310,8 @@ int run_fwd(const Geom& g, int math_mode, const Coords& coords, const HeadCfg& h
   p.seg_cap = seg_cap;
   p.b_stages = pl.b_stages; p.b_stage_bytes = pl.b_stage_bytes; p.tmem_cols = pl.tmem_cols;
   // keep the samples for the weight gradient when the caller bound a cache that is large enough
-  p.sav = nullptr; p.sav_np = 0; p.sav_pairg = (g.cpg == 32) ? 1 : 0;
-  if (SampleCache* sc = current_sample_cache()) {
-    sc->format = 0;
-    size_t need = 0;
-    if (sc->data && pair_clusters == 0 && sm100_sample_image_plan(g, x3, &p.sav_np, &need) && sc->bytes >= need) {
-      p.sav = reinterpret_cast<uint8_t*>(sc->data);
-      sc->format = x3 ? 2 : 1;
-    }
-  }
+  p.sav = sav; p.sav_np = sav_np; p.sav_pairg = (g.cpg == 32) ? 1 : 0;
+  if (sav) sc->format = x3 ? 2 : 1;
 
   if (pair_clusters > 0) {
     pair::PairParams pp;

@@ -123,7 +123,8 @@ def test_no_cache_without_gradients_or_on_the_cuda_core_tier():
     x = torch.zeros(1, 64, 4, 8, 8, device="cuda")
     w = torch.zeros(64, 64, 3, 3, 3, device="cuda")
     desc = _lib.make_desc(x, w, (1, 1, 1), (1, 1, 1), (1, 1, 1), 1, 1)
-    assert L.d2c_sample_cache_bytes(ctypes.byref(desc)) == 2 * 2 * 14 * 4 * 8192      # 2 tiles, 2 blocks, 14 pairs, hi/lo x 2
+    # operand image (2 tiles x 2 blocks x 14 slice pairs x {hi, lo} x 2 slices x 8 KB) + staged fp32 input + positions
+    assert L.d2c_sample_cache_bytes(ctypes.byref(desc)) == 2 * 2 * 14 * 4 * 8192 + 256 * 64 * 4 + 27 * 256 * 16
     assert _lib.SampleCache.for_forward(desc, x.device, differentiated=False) is None
     d2conv3d_b200.set_math_mode("fp32")
     assert L.d2c_sample_cache_bytes(ctypes.byref(desc)) == 0
