@@ -71,6 +71,8 @@ struct FwdParams {
   int S;                       // slices per tile = G * K * nh
   int tiles_per_clip, n_tiles;
   long long n_units;           // n_tiles * S
+  int n_parts, part_shift;     // see cta_part_range
+  long long units_per_part;
   int seg_cap;                 // at most this many units accumulate in tensor memory before the partial result is
                                // added to y (see run_fwd); S = no limit
   int b_stages, b_stage_bytes;
@@ -92,6 +94,18 @@ struct FwdParams {
 __device__ __forceinline__ void cta_unit_range(long long n_units, long long& beg, long long& end) {
   beg = n_units * blockIdx.x / gridDim.x;
   end = n_units * (blockIdx.x + 1) / gridDim.x;
+}
+
+// Part r of a CTA's work: the units of part r (a clip, FwdParams::units_per_part each) are cut into one contiguous
+// range per CTA, and the CTA takes the range (blockIdx.x + r * part_shift) mod gridDim.x.  All CTAs therefore work
+// inside the SAME clip at the same time -- the staged input they gather from is one clip, not the whole batch, which
+// is what L2 can hold -- and a CTA's ranges lie at different depths of successive clips, which evens out the cost
+// of ranges in the middle of the volume (more in-volume corners, more distinct lines) against those at its faces.
+__device__ __forceinline__ void cta_part_range(const FwdParams& p, int part, long long& beg, long long& end) {
+  const long long q = ((long long)blockIdx.x + (long long)part * p.part_shift) % gridDim.x;
+  const long long base = (long long)part * p.units_per_part;
+  beg = base + p.units_per_part * q / gridDim.x;
+  end = base + p.units_per_part * (q + 1) / gridDim.x;
 }
 
 #include "deform_sm100_fwd_kernel.cuh"
@@ -178,15 +192,17 @@ bool make_plan(const Geom& g, bool x3, Plan* pl) {
   pl->S = (dual ? g.G / 2 : g.G) * g.K * pl->nh;
   pl->tiles_per_clip = (g.V + kBM - 1) / kBM;
   pl->n_tiles = pl->tiles_per_clip * g.B;
+  if ((long long)pl->n_tiles * pl->S > 0x7fffffffLL) return false;   // the kernel counts units in 31 bits
   pl->b_stage_bytes = g.Cout * 128;
-  int nb = (kSmemLimit - 1024 - 256 - kAStages * kAStageBytes - kRStages * pl->r_stage_bytes) / pl->b_stage_bytes;
+  // 256 bytes of barriers + 272 bytes of part ranges (rounded to 512) + 1 KB of alignment slack
+  int nb = (kSmemLimit - 1024 - 768 - kAStages * kAStageBytes - kRStages * pl->r_stage_bytes) / pl->b_stage_bytes;
   if (nb > 4) nb = 4;
   if (nb < 2) return false;
   pl->b_stages = nb;
   int cols = 32;
   while (cols < g.Cout) cols <<= 1;
   pl->tmem_cols = cols;
-  pl->smem_bytes = kAStages * kAStageBytes + pl->b_stages * pl->b_stage_bytes + kRStages * pl->r_stage_bytes + 256 + 1024;
+  pl->smem_bytes = kAStages * kAStageBytes + pl->b_stages * pl->b_stage_bytes + kRStages * pl->r_stage_bytes + 768 + 1024;
   pl->x_cl_bytes = align_up((size_t)g.B * g.Vin * g.Cin * (x3 ? 4 : 2), 256);
   pl->w_sw_bytes = align_up((size_t)pl->S * pl->b_stage_bytes, 256);
   pl->rec_bytes = gather_records_bytes(g);
@@ -241,7 +257,10 @@ int run_fwd(const Geom& g, int math_mode, const Coords& coords, const HeadCfg& h
   // therefore ends a chain after 108 units (648 MMAs, ~1e-5) and adds the partial tile to y with fp32 atomics,
   // exactly as it does where a tile is shared between two CTAs.
   const int seg_cap = x3 ? 108 : pl.S;
-  bool whole_tiles_only = (pl.n_tiles % grid == 0) && seg_cap >= pl.S;
+  // One part per clip (cta_part_range) while every CTA still gets a worthwhile range inside each clip.
+  const long long units_per_clip = (long long)pl.tiles_per_clip * pl.S;
+  const int n_parts = (g.B > 1 && g.B <= 16 && units_per_clip / grid >= 4 * kMinUnitsPerCta) ? g.B : 1;
+  bool whole_tiles_only = (pl.n_tiles % grid == 0) && seg_cap >= pl.S && n_parts == 1;
 
   // CTA pairs (deform_sm100_fwd_pair.cuh) whenever there are at least two tiles and the device can co-schedule
   // clusters of 2 with this kernel's shared memory.  Opt-in (D2C_SM100_PAIR=1): measured slower than the
@@ -307,6 +326,7 @@ int run_fwd(const Geom& g, int math_mode, const Coords& coords, const HeadCfg& h
   p.cs.dz = g.H * g.W * g.Cin; p.cs.dy = g.W * g.Cin; p.cs.dx = g.Cin;
   p.N = g.Cout; p.nh = pl.nh; p.S = pl.S; p.tiles_per_clip = pl.tiles_per_clip; p.n_tiles = pl.n_tiles;
   p.n_units = n_units;
+  p.n_parts = n_parts; p.units_per_part = n_units / n_parts; p.part_shift = (int)(grid / n_parts);
   p.seg_cap = seg_cap;
   p.b_stages = pl.b_stages; p.b_stage_bytes = pl.b_stage_bytes; p.tmem_cols = pl.tmem_cols;
   // keep the samples for the weight gradient when the caller bound a cache that is large enough

@@ -57,10 +57,22 @@ fwd_sm100_kernel(const FwdParams p) {
 #endif
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const Geom& g = p.g;
-  long long u_beg, u_end;
-  cta_unit_range(p.n_units, u_beg, u_end);
+  // A CTA's work is n_parts (<= 16) contiguous unit ranges, one inside every clip (cta_part_range in
+  // deform_sm100_fwd.cu); ring slots, phases and segment counters run on across the parts, positions restart at every
+  // part.  Thread 0 puts the ranges into shared memory once, so that the roles (some of them left with 40 registers)
+  // do no 64-bit division.
+  // (unit indices fit 31 bits: checked by the host)
+  int* part_tab = reinterpret_cast<int*>(base_ptr + bar_off + 256);      // [part][beg, end], then the total
 
   if (threadIdx.x == 0) {
+    int total = 0;
+    for (int part = 0; part < p.n_parts; ++part) {
+      long long pb, pe;
+      cta_part_range(p, part, pb, pe);
+      part_tab[2 * part] = (int)pb; part_tab[2 * part + 1] = (int)pe;
+      total += (int)(pe - pb);
+    }
+    part_tab[32] = total;
     for (int s = 0; s < kAStages; ++s) { ptx::mbar_init(a_full(s), kGatherWarps); ptx::mbar_init(a_empty(s), 1); }
     for (int s = 0; s < p.b_stages; ++s) { ptx::mbar_init(b_full(s), 1); ptx::mbar_init(b_empty(s), 1); }
     for (int s = 0; s < kRStages; ++s) { ptx::mbar_init(r_full(s), 1); ptx::mbar_init(r_empty(s), kGatherWarps); }
@@ -88,9 +100,12 @@ fwd_sm100_kernel(const FwdParams p) {
     // ===================== epilogue: one pass per tile segment =====================
     asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     int seg = 0;
-    for (long long u = u_beg; u < u_end; ++seg) {
-      const int tile = (int)(u / p.S), s_beg = (int)(u % p.S);
-      const int s_end = min((int)min((long long)p.S, s_beg + (u_end - u)), s_beg + p.seg_cap);
+    for (int part = 0; part < p.n_parts; ++part) {
+    if (*abort_flag) break;
+    const int u_beg = part_tab[2 * part], u_end = part_tab[2 * part + 1];
+    for (int u = u_beg; u < u_end; ++seg) {
+      const int tile = u / p.S, s_beg = u % p.S;
+      const int s_end = min(min(p.S, s_beg + (u_end - u)), s_beg + p.seg_cap);
       u += s_end - s_beg;
       const bool whole = (s_beg == 0 && s_end == p.S);
       const int b = tile / p.tiles_per_clip, v0 = (tile % p.tiles_per_clip) * kBM;
@@ -160,6 +175,7 @@ fwd_sm100_kernel(const FwdParams p) {
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(acc_empty);
     }
+    }
   } else if (warp < kGatherWarp0Fwd) {
    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
    if (warp == kMmaWarpFwd) {
@@ -182,9 +198,12 @@ fwd_sm100_kernel(const FwdParams p) {
       const uint32_t idesc_last = ptx::umma_idesc_bf16_f32(kBM, p.N - (n_halves - 1) * 256);
       const uint64_t adesc0 = ptx::umma_desc_kmajor_sw128(a_base), bdesc0 = ptx::umma_desc_kmajor_sw128(b_base);
       const uint64_t a_step = (uint64_t)(kAStageBytes >> 4), b_step = (uint64_t)(p.b_stage_bytes >> 4);
-      int s_beg = (int)(u_beg % p.S);                                   // once per CTA
-      for (long long u = u_beg; ok && u < u_end; ++seg) {
-        const int s_end = min((int)min((long long)p.S, s_beg + (u_end - u)), s_beg + p.seg_cap);
+      for (int part = 0; ok && part < p.n_parts; ++part) {
+      if (*abort_flag) break;
+      const int u_beg = part_tab[2 * part], u_end = part_tab[2 * part + 1];
+      int s_beg = u_beg % p.S;                                          // once per part
+      for (int u = u_beg; ok && u < u_end; ++seg) {
+        const int s_end = min(min(p.S, s_beg + (u_end - u)), s_beg + p.seg_cap);
         u += s_end - s_beg;
         if (!ptx::mbar_wait(acc_empty, (seg & 1) ^ 1, abort_flag)) break;
         ptx::tc_fence_after();
@@ -215,6 +234,7 @@ fwd_sm100_kernel(const FwdParams p) {
         if (ok) ptx::umma_commit(acc_full);
         s_beg = s_end == p.S ? 0 : s_end;
       }
+      }
     }
   } else if (warp == kLoadWarpFwd) {
     // ===================== weight-slice loader =====================
@@ -222,10 +242,14 @@ fwd_sm100_kernel(const FwdParams p) {
       uint32_t k = 0;
       int sb = 0;                       // ring slot and phase as counters: no division in the per-unit path
       uint32_t phb = 1;                 // the wait for a FREE slot looks at the previous phase
-      int s = (int)(u_beg % p.S);       // once per CTA
-      const uint8_t* src = p.w_sw + (long long)s * p.b_stage_bytes;
       const uint64_t pol_keep = ptx::l2_evict_last();          // every CTA streams every slice once per tile
-      for (long long u = u_beg; u < u_end; ++u, ++k) {
+      for (int part = 0; part < p.n_parts; ++part) {
+      if (*abort_flag) break;
+      const int u_beg = part_tab[2 * part], u_end = part_tab[2 * part + 1];
+      int s = u_beg % p.S;              // once per part
+      const uint8_t* src = p.w_sw + (long long)s * p.b_stage_bytes;
+      const int n_part_units = u_end - u_beg;
+      for (int i = 0; i < n_part_units; ++i, ++k) {
         D2C_TR(1, k, 0);
         if (!ptx::mbar_wait(b_empty(sb), phb, abort_flag, 200)) break;
         D2C_TR(1, k, 1);
@@ -236,6 +260,7 @@ fwd_sm100_kernel(const FwdParams p) {
         if (++sb == p.b_stages) { sb = 0; phb ^= 1u; }
         src += p.b_stage_bytes;
         if (++s == p.S) { s = 0; src = p.w_sw; }
+      }
       }
       // never leave with a bulk copy in flight: wait (bounded) for the last copies issued
       const uint32_t issued = k;
@@ -253,14 +278,18 @@ fwd_sm100_kernel(const FwdParams p) {
       uint32_t k = 0;
       // position of the first unit, once per CTA; then everything advances by counters (this single thread's
       // instruction latency sits between "stage free" and "copy issued" for every unit: no division in the loop)
-      int s = (int)(u_beg % p.S);
-      const int tile0 = (int)(u_beg / p.S);
+      const long long grp_ch = kDual ? 2 * g.cpg : g.cpg;
+      const uint64_t pol_stream = ptx::l2_evict_first();       // records are read once
+      for (int part = 0; part < p.n_parts; ++part) {
+      if (*abort_flag) break;
+      const int u_beg = part_tab[2 * part], u_end = part_tab[2 * part + 1];
+      int s = u_beg % p.S;
+      const int tile0 = u_beg / p.S;
       int b = tile0 / p.tiles_per_clip, v0 = (tile0 % p.tiles_per_clip) * kBM;
       int tile = tile0;
       int h = s % p.nh, tap = (s / p.nh) % g.K, grp = (s / p.nh) / g.K;   // dual: grp is the index of a group PAIR
-      const long long grp_ch = kDual ? 2 * g.cpg : g.cpg;
-      const uint64_t pol_stream = ptx::l2_evict_first();       // records are read once
-      for (long long u = u_beg; u < u_end; ++u, ++k) {
+      const int n_part_units = u_end - u_beg;
+      for (int i = 0; i < n_part_units; ++i, ++k) {
         const int sr = k & (kRStages - 1);
         D2C_TR(0, k, 0);
         if (!ptx::mbar_wait(r_empty(sr), ((k / kRStages) & 1) ^ 1, abort_flag, 200)) break;
@@ -304,6 +333,7 @@ fwd_sm100_kernel(const FwdParams p) {
           if (v0 >= p.tiles_per_clip * kBM) { v0 = 0; ++b; }
         }
       }
+      }
       const uint32_t issued = k;
       for (uint32_t q = (issued > (uint32_t)kRStages ? issued - kRStages : 0); q < issued; ++q) {
         const long long t0 = clock64();
@@ -321,7 +351,7 @@ fwd_sm100_kernel(const FwdParams p) {
     const int t = threadIdx.x - kGatherWarp0Fwd * 32;
     const int j = t & 7;             // 16-byte chunk (8 channels) of the 128-byte row
     const int r0 = t >> 3;           // rows r0, r0 + kRowStride
-    const uint32_t n_my_units = (uint32_t)(u_end - u_beg);
+    const uint32_t n_my_units = (uint32_t)part_tab[32];
     bool ok = true;
     // Samples kept for the weight gradient (p.sav != nullptr): the thread's two rows r0 and r0 + 64 are the same row
     // of the two 64-voxel blocks of the tile, so its byte offset inside an 8 KB block is fixed.
@@ -446,7 +476,7 @@ fwd_sm100_kernel(const FwdParams p) {
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
     asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
     long long* rec = p.trace + 5 * 64 * 8 + blockIdx.x * 4;
-    rec[0] = (long long)cta_t0; rec[1] = (long long)t1; rec[2] = (long long)smid; rec[3] = u_end - u_beg;
+    rec[0] = (long long)cta_t0; rec[1] = (long long)t1; rec[2] = (long long)smid; rec[3] = (long long)part_tab[32];
   }
 #endif
   if (threadIdx.x == 0 && *abort_flag) ptx::report_device_timeout();
