@@ -883,7 +883,13 @@ def measure_extra_workload(name, modes, steps, warmup):
             t.grad = None
         flush.zero_()
         e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-        e[0].record(); y = fwd(); e[1].record()
+        e[0].record()
+        if wl.get("fwd_only"):
+            with torch.no_grad():      # an inference layer: nothing is kept for a backward
+                y = fwd()
+        else:
+            y = fwd()
+        e[1].record()
         if not wl.get("fwd_only"):
             y.backward(gy)
         e[2].record()
@@ -926,6 +932,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-reference-gpu", action="store_true")
+    ap.add_argument("--no-keep-samples", action="store_true",
+                    help="the forward keeps nothing for the backward (d2conv3d_b200.set_keep_samples(False)): the weight "
+                         "gradient gathers and blends its samples again, as the reference does")
     ap.add_argument("--no-secondary", dest="secondary", action="store_false",
                     help="skip the `secondary` key (c3-xyz, c4-depthwise, c4-md, c5-e1-train, a few steps each)")
     ap.add_argument("--clips", type=int, default=32, help="c5-decoder: clips of the whole job")
@@ -933,6 +942,9 @@ def main():
                     help="c2 = the headline line (default); the others print a secondary line for one GPU")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.no_keep_samples:
+        import d2conv3d_b200
+        d2conv3d_b200.set_keep_samples(False)
     if args.impl == "reference":
         run_reference_arm(args)
     elif args.workload == "c5-decoder":

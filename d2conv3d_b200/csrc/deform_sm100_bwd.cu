@@ -440,12 +440,11 @@ dcol_sm100_split_kernel(const DcolParams p) {
       uint32_t e = 0;
       int seg = 0;
       bool ok = true;
-      const uint64_t pol_keep = ptx::l2_evict_last();      // both images are re-read by every CTA
       auto push = [&](const uint8_t* src, uint32_t bytes) {
         const int sb = e % kBStages;
         if (!ptx::mbar_wait(b_empty(sb), ((e / kBStages) & 1) ^ 1, abort_flag)) return false;
         ptx::mbar_arrive_expect_tx(b_full(sb), bytes);
-        ptx::bulk_g2s_hint(b_base + sb * kBStageBytes, src, bytes, b_full(sb), pol_keep);
+        ptx::bulk_g2s(b_base + sb * kBStageBytes, src, bytes, b_full(sb));
         ++e;
         return true;
       };
@@ -457,7 +456,7 @@ dcol_sm100_split_kernel(const DcolParams p) {
         ptx::mbar_arrive_expect_tx(a_full, (uint32_t)a_bytes);
         const uint8_t* asrc = p.gy_img + (long long)tile * p.KBT * kABlockBytes;
         for (int off = 0; off < a_bytes; off += 32768)
-          ptx::bulk_g2s_hint(a_base + off, asrc + off, (uint32_t)min(32768, a_bytes - off), a_full, pol_keep);
+          ptx::bulk_g2s(a_base + off, asrc + off, (uint32_t)min(32768, a_bytes - off), a_full);
         for (int nb = nb_beg; ok && nb < nb_end; ++nb) {
           const uint32_t wbytes = (uint32_t)(min(kNBlock, p.NT - nb * kNBlock) * 128);
           for (int kb = 0; ok && kb < p.KB; ++kb) {

@@ -293,7 +293,6 @@ dw_sm100_kernel(const DwParams p) {
       // ---- gather producers: the forward's producer, two slices per stage
       const int tt = threadIdx.x - kGatherWarp0 * 32;
       const int j = tt & 7, r0 = tt >> 3;
-      const uint64_t pol_keep = ptx::l2_evict_last();
       uint32_t row_dst[kRowsPerThread];
 #pragma unroll
       for (int i = 0; i < kRowsPerThread; ++i) {
@@ -317,9 +316,9 @@ dw_sm100_kernel(const DwParams p) {
           uint2 head = make_uint2(0u, 0u);
           if (r < rows) head = *reinterpret_cast<const uint2*>(rec_stage + r * 48);
           if constexpr (kX3)
-            load_corners_f32(reinterpret_cast<const float*>(p.x_cl) + xoff + j * 4, p.cs, head.x, head.y, c[i], pol_keep);
+            load_corners_f32(reinterpret_cast<const float*>(p.x_cl) + xoff + j * 4, p.cs, head.x, head.y, c[i]);
           else
-            load_corners(reinterpret_cast<const __half*>(p.x_cl) + xoff + j * 8, p.cs, head.x, head.y, c[i], pol_keep);
+            load_corners(reinterpret_cast<const __half*>(p.x_cl) + xoff + j * 8, p.cs, head.x, head.y, c[i]);
         }
         if (sl == 0 && !ptx::mbar_wait(a_empty(sa), ((t / kAStages) & 1) ^ 1, abort_flag)) break;
         const uint32_t stage = a_base + sa * kAStageBytes + (kX3 ? 0 : sl * kTileBytes);
@@ -529,12 +528,11 @@ dw_saved_sm100_kernel(const DwSavedParams p) {
         uint32_t q = 0;
         int sb = 0, c = 0;
         uint32_t phb = 1;                                     // the wait for a FREE slot looks at the previous phase
-        const uint64_t pol_keep = ptx::l2_evict_last();       // every slice pair streams the same grad_out images
         for (; q < nq; ++q) {
           if (!ptx::mbar_wait(b_empty(sb), phb, abort_flag, 100)) break;
           const uint32_t bytes = (uint32_t)min(256, p.N - 256 * c) * 128u;
           ptx::mbar_arrive_expect_tx(b_full(sb), bytes);
-          ptx::bulk_g2s_hint(b_base + sb * kChunkBytes, src, bytes, b_full(sb), pol_keep);
+          ptx::bulk_g2s(b_base + sb * kChunkBytes, src, bytes, b_full(sb));
           src += kChunkBytes;
           if (++c == p.NCH) c = 0;
           if (++sb == kSvBStages) { sb = 0; phb ^= 1u; }

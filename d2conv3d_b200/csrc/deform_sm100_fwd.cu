@@ -358,7 +358,8 @@ int run_fwd(const Geom& g, int math_mode, const Coords& coords, const HeadCfg& h
   }
 #endif
   prof_mark(st, "fwd_sm100_fused");
-  auto kern = x3 ? fwd_sm100_kernel<1, 0> : (pl.dual ? fwd_sm100_kernel<0, 1> : fwd_sm100_kernel<0, 0>);
+  auto kern = sav ? (x3 ? fwd_sm100_kernel<1, 0, 1> : (pl.dual ? fwd_sm100_kernel<0, 1, 1> : fwd_sm100_kernel<0, 0, 1>))
+                  : (x3 ? fwd_sm100_kernel<1, 0, 0> : (pl.dual ? fwd_sm100_kernel<0, 1, 0> : fwd_sm100_kernel<0, 0, 0>));
   D2C_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes));
   kern<<<(unsigned)grid, kThreadsFwd, pl.smem_bytes, st>>>(p);
   D2C_LAUNCH_CHECK();

@@ -26,7 +26,10 @@ constexpr int kMmaWarpFwd = 4, kLoadWarpFwd = 5, kRecWarpFwd = 6, kGatherWarp0Fw
 //          the fp32 blend, the weight row [hi(32) | lo(32)] of the fp32 weight, and the issuer forms
 //          a_hi*b_hi + a_lo*b_hi + a_hi*b_lo from the 16-channel K sub-blocks of the same two tiles.
 // kDual = 1 (single-pass mode only): 32 channels per offset group, a 64-channel unit spans two groups.
-template <int kX3, int kDual>
+// kSave = 1: the blended tiles are also written to FwdParams::sav (a forward whose backward will follow).  A template
+//          parameter, not a run-time test: values kept live for the extra stores cost the inference kernel 20-30 % on
+//          the large decoder layers when the two shared one body.
+template <int kX3, int kDual, int kSave>
 __global__ void __launch_bounds__(kThreadsFwd, 1)
 fwd_sm100_kernel(const FwdParams p) {
   constexpr int kUnitCh = kX3 ? 32 : 64;
@@ -242,7 +245,6 @@ fwd_sm100_kernel(const FwdParams p) {
       uint32_t k = 0;
       int sb = 0;                       // ring slot and phase as counters: no division in the per-unit path
       uint32_t phb = 1;                 // the wait for a FREE slot looks at the previous phase
-      const uint64_t pol_keep = ptx::l2_evict_last();          // every CTA streams every slice once per tile
       for (int part = 0; part < p.n_parts; ++part) {
       if (*abort_flag) break;
       const int u_beg = part_tab[2 * part], u_end = part_tab[2 * part + 1];
@@ -256,7 +258,7 @@ fwd_sm100_kernel(const FwdParams p) {
         ptx::mbar_arrive_expect_tx(b_full(sb), (uint32_t)p.b_stage_bytes);
         const uint32_t dst = b_base + sb * p.b_stage_bytes;
         for (int off = 0; off < p.b_stage_bytes; off += 32768)
-          ptx::bulk_g2s_hint(dst + off, src + off, (uint32_t)min(32768, p.b_stage_bytes - off), b_full(sb), pol_keep);
+          ptx::bulk_g2s(dst + off, src + off, (uint32_t)min(32768, p.b_stage_bytes - off), b_full(sb));
         if (++sb == p.b_stages) { sb = 0; phb ^= 1u; }
         src += p.b_stage_bytes;
         if (++s == p.S) { s = 0; src = p.w_sw; }
@@ -300,7 +302,7 @@ fwd_sm100_kernel(const FwdParams p) {
         uint8_t* hdr = base_ptr + rec_off + sr * kRStage + hdr_off;
         *reinterpret_cast<long long*>(hdr) = (long long)b * g.Vin * g.Cin + grp * grp_ch + h * kUnitCh;
         *reinterpret_cast<int*>(hdr + 8) = rows;
-        if (p.sav) {
+        if constexpr (kSave) {
           // where this unit's samples go in the image kept for the weight gradient (8 KB blocks, see FwdParams)
           int word;
           if constexpr (kX3) {
@@ -356,7 +358,7 @@ fwd_sm100_kernel(const FwdParams p) {
     // Samples kept for the weight gradient (p.sav != nullptr): the thread's two rows r0 and r0 + 64 are the same row
     // of the two 64-voxel blocks of the tile, so its byte offset inside an 8 KB block is fixed.
     const uint32_t sav_row = (uint32_t)((r0 >> 3) * 1024 + (r0 & 7) * 128);
-    const uint64_t pol_keep = ptx::l2_evict_last(), pol_stream = ptx::l2_evict_first();
+    const uint64_t pol_stream = ptx::l2_evict_first();
 
     auto issue = [&](uint32_t k, int i, uint4 (&c)[8]) {
       const uint8_t* rec_base_ptr = base_ptr + rec_off + (k % kRStages) * kRStage;
@@ -368,12 +370,13 @@ fwd_sm100_kernel(const FwdParams p) {
       uint2 head = make_uint2(0u, 0u);
       if (r < rows) head = *reinterpret_cast<const uint2*>(rec_stage + r * 48);
       if constexpr (kX3)
-        load_corners_f32(reinterpret_cast<const float*>(p.x_cl) + xoff + j * 4, p.cs, head.x, head.y, c, pol_keep);
+        load_corners_f32(reinterpret_cast<const float*>(p.x_cl) + xoff + j * 4, p.cs, head.x, head.y, c);
       else
-        load_corners(reinterpret_cast<const __half*>(p.x_cl) + xoff + j * 8, p.cs, head.x, head.y, c, pol_keep);
+        load_corners(reinterpret_cast<const __half*>(p.x_cl) + xoff + j * 8, p.cs, head.x, head.y, c);
     };
-    // returns the 16 bytes this lane wrote to the A tile (bf16x3: the lane pair's hi chunk or lo chunk)
-    auto consume = [&](uint32_t k, int i, const uint4 (&c)[8]) -> uint4 {
+    // sd (kSave): where the 16 bytes this lane writes to the A tile (bf16x3: the lane pair's hi chunk or lo chunk) go
+    // in the kept image
+    auto consume = [&](uint32_t k, int i, const uint4 (&c)[8], uint8_t* sd) {
       const uint8_t* rec_base_ptr = base_ptr + rec_off + (k % kRStages) * kRStage;
       const int rows = *reinterpret_cast<const int*>(rec_base_ptr + hdr_off + 8);
       const uint8_t* rec_stage = rec_base_ptr + ((kDual && j >= 4) ? kRecBytes : 0);
@@ -393,14 +396,16 @@ fwd_sm100_kernel(const FwdParams p) {
         // item j = channels 4j..4j+3: hi in 16-byte chunk j/2 (half j&1), lo in chunk 4 + j/2; the lane pair (j, j^1)
         // shares both chunks: the even lane writes the hi chunk, the odd lane the lo chunk
         const uint32_t row_base = stage + (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
-        return blend_split_store16(c, w, row_base + ((((j & 1) * 4 + (j >> 1)) ^ (r & 7)) << 4), (j & 1) != 0);
+        const uint4 o = blend_split_store16(c, w, row_base + ((((j & 1) * 4 + (j >> 1)) ^ (r & 7)) << 4), (j & 1) != 0);
+        if constexpr (kSave) ptx::stg_v4_hint(sd, o, pol_stream);
       } else {
         uint4 w03 = make_uint4(0u, 0u, 0u, 0u), w47 = w03;       // rows past the clip end: stage bytes are stale
         if (r < rows) {
           w03 = *reinterpret_cast<const uint4*>(rec_stage + r * 48 + 16);
           w47 = *reinterpret_cast<const uint4*>(rec_stage + r * 48 + 32);
         }
-        return blend_store(c, w03, w47, stage + (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((j ^ (r & 7)) << 4)));
+        const uint4 o = blend_store(c, w03, w47, stage + (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((j ^ (r & 7)) << 4)));
+        if constexpr (kSave) ptx::stg_v4_hint(sd, o, pol_stream);
       }
     };
 
@@ -411,9 +416,24 @@ fwd_sm100_kernel(const FwdParams p) {
     }
     for (uint32_t k = 0; ok && k < n_my_units; ++k) {
       const int sr = k % kRStages, sa = k % kAStages;
-      // where the unit's samples go in the kept image (read before the record stage is released below)
-      int word = 0;
-      if (p.sav) word = *reinterpret_cast<const int*>(base_ptr + rec_off + sr * kRStage + hdr_off + 12);
+      // where this lane's bytes of the unit go in the kept image: block = (tile, 64-voxel block, slice) in the
+      // single-pass mode; (tile, 64-voxel block, slice pair, {hi, lo}, slice of the pair) in the hi/lo mode, where a
+      // 64-channel row holds this unit's 32 channels in its half `half`, an even lane holds the hi chunk of the lane
+      // pair's 8 channels and an odd lane the lo chunk two blocks further.  The tile's second 64-voxel block (row 1 of
+      // this thread) lies sav_blk1 bytes further.
+      uint8_t* sav_dst = nullptr;
+      long long sav_blk1 = 0;
+      if constexpr (kSave) {
+        const int word = *reinterpret_cast<const int*>(base_ptr + rec_off + sr * kRStage + hdr_off + 12);
+        if constexpr (kX3) {
+          sav_dst = p.sav + ((long long)((word >> 1) + (j & 1) * 2) << 13) + sav_row +
+                    (uint32_t)(((4 * (word & 1) + (j >> 1)) ^ (r0 & 7)) << 4);
+          sav_blk1 = (long long)(p.sav_np * 4) << 13;
+        } else {
+          sav_dst = p.sav + ((long long)word << 13) + sav_row + (uint32_t)((j ^ (r0 & 7)) << 4);
+          sav_blk1 = (long long)(2 * p.sav_np) << 13;
+        }
+      }
 #ifdef D2C_UNIT_TRACE
       const int trole = lane != 0 ? -1 : (warp == kGatherWarp0Fwd ? 3 : (warp == kGatherWarp0Fwd + 15 ? 4 : -1));
 #define D2C_TG(e) do { if (trole >= 0) D2C_TR(trole, k, e); } while (0)
@@ -425,7 +445,7 @@ fwd_sm100_kernel(const FwdParams p) {
       D2C_TG(1);
       if (!ptx::mbar_wait(a_empty(sa), ((k / kAStages) & 1) ^ 1, abort_flag)) break;
       D2C_TG(2);
-      const uint4 o0 = consume(k, 0, c0);
+      consume(k, 0, c0, sav_dst);
       D2C_TG(3);
       if (k + 1 < n_my_units) {
         if (!ptx::mbar_wait(r_full((k + 1) % kRStages), ((k + 1) / kRStages) & 1, abort_flag)) break;
@@ -433,7 +453,7 @@ fwd_sm100_kernel(const FwdParams p) {
         issue(k + 1, 0, c0);
       }
       D2C_TG(5);
-      const uint4 o1 = consume(k, 1, c1);
+      consume(k, 1, c1, sav_dst + sav_blk1);
       D2C_TG(6);
       ptx::fence_proxy_async_smem();
       __syncwarp();
@@ -442,27 +462,6 @@ fwd_sm100_kernel(const FwdParams p) {
         ptx::mbar_arrive(r_empty(sr));
       }
       D2C_TG(7);
-      // The kept copy goes to global memory AFTER the arrives: an arrive releases the thread's earlier writes, so
-      // global stores issued before it would put their round trip to L2 on every unit's critical path (measured:
-      // +25 % kernel time); issued here they have a whole unit to complete before the next arrive.
-      if (p.sav) {
-        if constexpr (kX3) {
-          // image block = (tile, 64-voxel block, slice pair, {hi, lo}, slice of the pair): a 64-channel row holds
-          // this unit's 32 channels in its half `half`; hi and lo blocks lie two blocks apart, the tile's second
-          // 64-voxel block sav_np * 4 blocks further
-          // (an even lane holds the 16-byte hi chunk of the lane pair's 8 channels, an odd lane the lo chunk)
-          const int half = word & 1;
-          uint8_t* dst = p.sav + ((long long)((word >> 1) + (j & 1) * 2) << 13) + sav_row +
-                         (uint32_t)(((4 * half + (j >> 1)) ^ (r0 & 7)) << 4);
-          ptx::stg_v4_hint(dst, o0, pol_stream);
-          ptx::stg_v4_hint(dst + ((long long)(p.sav_np * 4) << 13), o1, pol_stream);
-        } else {
-          // image block = (tile, 64-voxel block, slice): the byte image of that half of the A tile
-          uint8_t* dst = p.sav + ((long long)word << 13) + sav_row + (uint32_t)((j ^ (r0 & 7)) << 4);
-          ptx::stg_v4_hint(dst, o0, pol_stream);
-          ptx::stg_v4_hint(dst + ((long long)(2 * p.sav_np) << 13), o1, pol_stream);
-        }
-      }
     }
   }
 

@@ -243,7 +243,6 @@ fwd_sm100_pair_kernel(const PairParams pp) {
     const uint32_t a_full_leader[kAStages] = {ptx::mapa_shared(a_full(0), 0), ptx::mapa_shared(a_full(1), 0),
                                               ptx::mapa_shared(a_full(2), 0), ptx::mapa_shared(a_full(3), 0)};
     const uint32_t n_my_units = (uint32_t)(u_end - u_beg);
-    const uint64_t pol_keep = ptx::l2_evict_last();
     for (uint32_t k = 0; k < n_my_units; ++k) {
       const int sr = k % kRStages, sa = k % kAStages;
       if (!ptx::mbar_wait(r_full(sr), (k / kRStages) & 1, abort_flag)) break;
@@ -256,7 +255,7 @@ fwd_sm100_pair_kernel(const PairParams pp) {
         const int r = r0 + kRowStride * i;
         uint2 head = make_uint2(0u, 0u);
         if (r < rows) head = *reinterpret_cast<const uint2*>(rec_stage + r * 48);
-        load_corners(xb, p.cs, head.x, head.y, c[i], pol_keep);
+        load_corners(xb, p.cs, head.x, head.y, c[i]);
       }
       if (!ptx::mbar_wait_cluster(a_empty(sa), ((k / kAStages) & 1) ^ 1, abort_flag)) break;
       const uint32_t stage = a_base + sa * kAStageBytes;

@@ -128,20 +128,19 @@ struct ClStrides {
 // The work is split in two so that a producer can put the corners of several items in flight before the first
 // blend: load_corners issues the 8 corner loads of one item (all unconditional, see the record format above),
 // blend_store consumes them.   xb_ch: channels-last fp16 staging of the clip, advanced to the item's channel.
-// pol: L2 eviction policy of the loads (the staged input is re-read by every CTA: sm100_ptx.cuh, l2_evict_last).
 __device__ __forceinline__ void load_corners(const __half* __restrict__ xb_ch, ClStrides cs, uint32_t voff,
-                                             uint32_t steps, uint4 (&c)[8], uint64_t pol) {
+                                             uint32_t steps, uint4 (&c)[8]) {
   const int dx = (steps & 1u) ? cs.dx : 0, dy = (steps & 2u) ? cs.dy : 0, dz = (steps & 4u) ? cs.dz : 0;
   const __half* p0 = xb_ch + voff;
   const __half* p1 = p0 + dz;
-  c[0] = ptx::ldg_nc_v4_hint(p0, pol);
-  c[1] = ptx::ldg_nc_v4_hint(p0 + dx, pol);
-  c[2] = ptx::ldg_nc_v4_hint(p0 + dy, pol);
-  c[3] = ptx::ldg_nc_v4_hint(p0 + dy + dx, pol);
-  c[4] = ptx::ldg_nc_v4_hint(p1, pol);
-  c[5] = ptx::ldg_nc_v4_hint(p1 + dx, pol);
-  c[6] = ptx::ldg_nc_v4_hint(p1 + dy, pol);
-  c[7] = ptx::ldg_nc_v4_hint(p1 + dy + dx, pol);
+  c[0] = ptx::ldg_nc_v4(p0);
+  c[1] = ptx::ldg_nc_v4(p0 + dx);
+  c[2] = ptx::ldg_nc_v4(p0 + dy);
+  c[3] = ptx::ldg_nc_v4(p0 + dy + dx);
+  c[4] = ptx::ldg_nc_v4(p1);
+  c[5] = ptx::ldg_nc_v4(p1 + dx);
+  c[6] = ptx::ldg_nc_v4(p1 + dy);
+  c[7] = ptx::ldg_nc_v4(p1 + dy + dx);
 }
 
 // Returns the 16 bytes it stored (a caller that also keeps the samples for the backward writes them to global).
@@ -173,18 +172,18 @@ __device__ __forceinline__ uint4 blend_store(const uint4 (&c)[8], uint4 w03, uin
 // 128-byte A row of a 32-channel unit: hi = bf16(v) at channel column c, lo = bf16(v - hi) at column 32 + c,
 // so that the MMA issuer can form a_hi*b_hi + a_lo*b_hi + a_hi*b_lo from K sub-blocks of ONE tile pair.
 __device__ __forceinline__ void load_corners_f32(const float* __restrict__ xb_ch, ClStrides cs, uint32_t voff,
-                                                 uint32_t steps, uint4 (&c)[8], uint64_t pol) {
+                                                 uint32_t steps, uint4 (&c)[8]) {
   const int dx = (steps & 1u) ? cs.dx : 0, dy = (steps & 2u) ? cs.dy : 0, dz = (steps & 4u) ? cs.dz : 0;
   const float* p0 = xb_ch + voff;
   const float* p1 = p0 + dz;
-  c[0] = ptx::ldg_nc_v4_hint(p0, pol);
-  c[1] = ptx::ldg_nc_v4_hint(p0 + dx, pol);
-  c[2] = ptx::ldg_nc_v4_hint(p0 + dy, pol);
-  c[3] = ptx::ldg_nc_v4_hint(p0 + dy + dx, pol);
-  c[4] = ptx::ldg_nc_v4_hint(p1, pol);
-  c[5] = ptx::ldg_nc_v4_hint(p1 + dx, pol);
-  c[6] = ptx::ldg_nc_v4_hint(p1 + dy, pol);
-  c[7] = ptx::ldg_nc_v4_hint(p1 + dy + dx, pol);
+  c[0] = ptx::ldg_nc_v4(p0);
+  c[1] = ptx::ldg_nc_v4(p0 + dx);
+  c[2] = ptx::ldg_nc_v4(p0 + dy);
+  c[3] = ptx::ldg_nc_v4(p0 + dy + dx);
+  c[4] = ptx::ldg_nc_v4(p1);
+  c[5] = ptx::ldg_nc_v4(p1 + dx);
+  c[6] = ptx::ldg_nc_v4(p1 + dy);
+  c[7] = ptx::ldg_nc_v4(p1 + dy + dx);
 }
 
 // w: the eight fp32 products a_j*mask (corner order 000..111, the reference's interpolation chain).

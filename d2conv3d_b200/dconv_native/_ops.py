@@ -33,6 +33,13 @@ def _new_event(stream):
     return ev
 
 
+def _will_differentiate(*tensors):
+    """Whether autograd is recording this call -- evaluated where the op is CALLED: inside Function.forward grad mode
+    is always off and ctx.needs_input_grad reports requires_grad even under torch.no_grad(), so an inference pass over
+    a model with trainable weights would otherwise look like a training pass (and keep samples it never uses)."""
+    return torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors)
+
+
 def _require(cond, expr):
     # TORCH_CHECK(expr) of the reference raises RuntimeError("Expected <expr> to be true ...")
     if not cond:
@@ -74,7 +81,7 @@ def _check_groups(input, weight, bias, groups):
 class _DeformConv3dFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, input, offset, alpha, weight, bias, sd, sh, sw, pd, ph, pw, dd, dh, dw,
-                groups, offset_groups):
+                groups, offset_groups, differentiated):
         input, offset, weight = input.contiguous(), offset.contiguous(), weight.contiguous()
         alpha = None if alpha is None else alpha.contiguous()
         bias = None if bias is None else bias.contiguous()
@@ -89,7 +96,7 @@ class _DeformConv3dFunction(torch.autograd.Function):
         with torch.cuda.device(input.device):
             y = torch.empty((input.shape[0], weight.shape[0]) + out_dims, dtype=input.dtype, device=input.device)
             ws, ws_bytes = _lib.workspace(_lib.OP_DEFORM_FWD, desc, input.device)
-            cache = _lib.SampleCache.for_forward(desc, input.device, any(ctx.needs_input_grad))
+            cache = _lib.SampleCache.for_forward(desc, input.device, differentiated)
             _lib.check(L.d2c_deform_conv3d_fwd(
                 ctypes.byref(desc), _lib.ptr(input), _lib.ptr(offset), _lib.ptr(alpha), _lib.ptr(weight),
                 _lib.ptr(bias), _lib.ptr(y), _lib.ptr(ws), ws_bytes, _lib.stream_of(input)), "deform_conv3d forward")
@@ -118,7 +125,7 @@ class _DeformConv3dFunction(torch.autograd.Function):
                 _lib.ptr(weight), _lib.ptr(gx), _lib.ptr(goff), _lib.ptr(gmask), _lib.ptr(gw), _lib.ptr(gbias),
                 _lib.ptr(ws), ws_bytes, _lib.stream_of(input), ctypes.c_void_p(ev.cuda_event)), "deform_conv3d backward")
             _BackwardState.params_ready = ev
-        return (gx, goff, gmask, gw, gbias) + (None,) * 11
+        return (gx, goff, gmask, gw, gbias) + (None,) * 12
 
 
 def deform_conv3d(input, offset, alpha, weight, bias, stride_d, stride_h, stride_w, pad_d, pad_h, pad_w,
@@ -126,12 +133,14 @@ def deform_conv3d(input, offset, alpha, weight, bias, stride_d, stride_h, stride
     """dconv_native._ops.deform_conv3d (csrc/ops/dconv3d.h:188-226)."""
     return _DeformConv3dFunction.apply(
         input, offset, alpha, weight, bias, int(stride_d), int(stride_h), int(stride_w), int(pad_d), int(pad_h),
-        int(pad_w), int(dilation_d), int(dilation_h), int(dilation_w), int(groups), int(offset_groups))
+        int(pad_w), int(dilation_d), int(dilation_h), int(dilation_w), int(groups), int(offset_groups),
+        _will_differentiate(input, offset, alpha, weight, bias))
 
 
 class _DynDilatedConv3dFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, input, size_map, alpha, weight, bias, mode, stride, padding, dilation, groups, offset_groups):
+    def forward(ctx, input, size_map, alpha, weight, bias, mode, stride, padding, dilation, groups, offset_groups,
+                differentiated):
         input, size_map, weight = input.contiguous(), size_map.contiguous(), weight.contiguous()
         alpha = None if alpha is None else alpha.contiguous()
         bias = None if bias is None else bias.contiguous()
@@ -149,7 +158,7 @@ class _DynDilatedConv3dFunction(torch.autograd.Function):
         with torch.cuda.device(input.device):
             y = torch.empty((input.shape[0], weight.shape[0]) + out_dims, dtype=input.dtype, device=input.device)
             ws, ws_bytes = _lib.workspace(_lib.OP_DYNDIL_FWD, desc, input.device)
-            cache = _lib.SampleCache.for_forward(desc, input.device, any(ctx.needs_input_grad))
+            cache = _lib.SampleCache.for_forward(desc, input.device, differentiated)
             _lib.check(L.d2c_dyn_dilated_conv3d_fwd(
                 ctypes.byref(desc), _lib.FIELD_MODES[mode], _lib.ptr(input), _lib.ptr(size_map), _lib.ptr(alpha),
                 _lib.ptr(weight), _lib.ptr(bias), _lib.ptr(y), _lib.ptr(ws), ws_bytes, _lib.stream_of(input)),
@@ -180,7 +189,7 @@ class _DynDilatedConv3dFunction(torch.autograd.Function):
                 _lib.ptr(gw), _lib.ptr(gbias), _lib.ptr(ws), ws_bytes, _lib.stream_of(input),
                 ctypes.c_void_p(ev.cuda_event)), "dyn_dilated_conv3d backward")
             _BackwardState.params_ready = ev
-        return (gx, gs, gmask, gw, gbias) + (None,) * 6
+        return (gx, gs, gmask, gw, gbias) + (None,) * 7
 
 
 def dyn_dilated_conv3d(input, size_map, alpha, weight, bias, mode, stride, padding, dilation, groups,
@@ -189,7 +198,8 @@ def dyn_dilated_conv3d(input, size_map, alpha, weight, bias, mode, stride, paddi
     the reference's compiled module: there the field is expanded to 3*K offset
     channels by offsets_from_size_map, utils/grid.py:72-98, before deform_conv3d)."""
     return _DynDilatedConv3dFunction.apply(input, size_map, alpha, weight, bias, mode, tuple(stride),
-                                           tuple(padding), tuple(dilation), int(groups), int(offset_groups))
+                                           tuple(padding), tuple(dilation), int(groups), int(offset_groups),
+                                           _will_differentiate(input, size_map, alpha, weight, bias))
 
 
 class _DeformConv1dFunction(torch.autograd.Function):
@@ -258,7 +268,7 @@ class _HeadConv3dFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, input, raw, weight, bias, field_mode, mask_channel0, mask_act, size_act, stride, padding,
-                dilation, groups, offset_groups):
+                dilation, groups, offset_groups, differentiated):
         input, raw, weight = input.contiguous(), raw.contiguous(), weight.contiguous()
         bias = None if bias is None else bias.contiguous()
         for t, nd, name in ((input, 5, "input"), (raw, 5, "deformation"), (weight, 5, "weight"), (bias, 1, "bias")):
@@ -284,7 +294,7 @@ class _HeadConv3dFunction(torch.autograd.Function):
             ws, ws_bytes = _lib.head_workspace(op, desc, head, max(fm, 0), input.device)
             args = (_lib.ptr(input), _lib.ptr(raw), _lib.ptr(weight), _lib.ptr(bias), _lib.ptr(y), _lib.ptr(ws), ws_bytes,
                     _lib.stream_of(input))
-            cache = _lib.SampleCache.for_forward(desc, input.device, any(ctx.needs_input_grad))
+            cache = _lib.SampleCache.for_forward(desc, input.device, differentiated)
             if field_mode is None:
                 rc = L.d2c_deform_conv3d_head_fwd(ctypes.byref(desc), ctypes.byref(head), *args)
             else:
@@ -319,7 +329,7 @@ class _HeadConv3dFunction(torch.autograd.Function):
                 rc = L.d2c_dyn_dilated_conv3d_head_bwd(ctypes.byref(desc), ctypes.byref(head), fm, *args)
             _lib.check(rc, "deform_conv3d (fused head) backward")
             _BackwardState.params_ready = ev
-        return (gx, graw, gw, gbias) + (None,) * 9
+        return (gx, graw, gw, gbias) + (None,) * 10
 
 
 def deform_conv3d_head(input, raw, weight, bias, field_mode, modulated, mask_act, size_act, stride, padding, dilation,
@@ -335,7 +345,8 @@ def deform_conv3d_head(input, raw, weight, bias, field_mode, modulated, mask_act
         raise RuntimeError(f"the deformation tensor must have {want} channels, got {tuple(raw.shape)}")
     return _HeadConv3dFunction.apply(input, raw, weight, bias, field_mode, geo if modulated else -1, mask_act,
                                      size_act if field_mode is not None else "linear", tuple(stride), tuple(padding),
-                                     tuple(dilation), int(groups), int(offset_groups))
+                                     tuple(dilation), int(groups), int(offset_groups),
+                                     _will_differentiate(input, raw, weight, bias))
 
 
 def deform_conv1d(input, offset, alpha, weight, bias, stride, padding, dilation, groups, offset_groups):

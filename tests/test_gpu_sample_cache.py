@@ -167,3 +167,28 @@ def test_dilation_field_layer_with_fused_head_uses_kept_samples(mode):
     tol = 1e-4 if mode == "auto" else 5e-3
     for a, b in zip(*res):
         assert (a - b).abs().max().item() <= tol * max(b.abs().max().item(), 1e-30)
+
+
+def test_inference_under_no_grad_keeps_nothing(monkeypatch):
+    """A forward under torch.no_grad() over a layer whose weights are trainable (the usual evaluation pass) must not
+    keep samples: ctx.needs_input_grad is True there, so the decision is taken where the op is called."""
+    from d2conv3d_b200 import _lib
+    from d2conv3d_b200.dconv_native import modules
+    seen = []
+    real = _lib.SampleCache.for_forward
+
+    def spy(desc, device, differentiated):
+        seen.append(bool(differentiated))
+        return real(desc, device, differentiated)
+
+    monkeypatch.setattr(_lib.SampleCache, "for_forward", staticmethod(spy))
+    layer = modules.XYZSizeConditionedMDConv3d(64, 64, 3, padding=1, offset_groups=1).cuda()
+    x = torch.randn(1, 64, 4, 8, 8, device="cuda")
+    with torch.no_grad():
+        layer(x)
+    assert seen == [False]
+    layer(x)                       # weights require grad, grad mode on: a training forward
+    assert seen == [False, True]
+    layer.requires_grad_(False)
+    layer(x)                       # nothing to differentiate
+    assert seen == [False, True, False]
