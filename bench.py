@@ -219,14 +219,14 @@ def run_reference_arm(args):
 TRAFFIC_SOURCE = "ncu --set full capture of this bench's C2 step, one launch per kernel, both math modes"
 TRAFFIC_PER_LAUNCH = {       # (phase, math mode) -> DRAM read + write bytes of one launch
     # the forward keeps its operand tiles for the weight gradient (sample cache): + 0.72 / 1.44 GB written
-    ("fwd_sm100_fused", "bf16"): 0.466e9 + 0.759e9, ("fwd_sm100_fused", "auto"): 2.197e9 + 1.657e9,
-    ("fwd_sm100_fused", "bf16x3"): 2.197e9 + 1.657e9,
-    ("bwd_sample_grad", "bf16"): 1.603e9 + 0.138e9, ("bwd_sample_grad", "auto"): 1.629e9 + 0.138e9,
-    ("bwd_sample_grad", "bf16x3"): 1.629e9 + 0.138e9,
-    ("bwd_dcol_sm100", "bf16"): 0.109e9 + 1.382e9, ("bwd_dcol_sm100", "auto"): 0.555e9 + 1.392e9,
-    ("bwd_dcol_sm100", "bf16x3"): 0.555e9 + 1.392e9,
-    ("bwd_dw_sm100_saved", "bf16"): 0.777e9 + 0.005e9, ("bwd_dw_sm100_saved", "auto"): 1.526e9 + 0.004e9,
-    ("bwd_dw_sm100_saved", "bf16x3"): 1.526e9 + 0.004e9,
+    ("fwd_sm100_fused", "bf16"): 0.411e9 + 0.762e9, ("fwd_sm100_fused", "auto"): 1.560e9 + 1.648e9,
+    ("fwd_sm100_fused", "bf16x3"): 1.560e9 + 1.648e9,
+    ("bwd_sample_grad", "bf16"): 1.603e9 + 0.137e9, ("bwd_sample_grad", "auto"): 1.630e9 + 0.137e9,
+    ("bwd_sample_grad", "bf16x3"): 1.630e9 + 0.137e9,
+    ("bwd_dcol_sm100", "bf16"): 0.112e9 + 1.383e9, ("bwd_dcol_sm100", "auto"): 0.634e9 + 1.393e9,
+    ("bwd_dcol_sm100", "bf16x3"): 0.634e9 + 1.393e9,
+    ("bwd_dw_sm100_saved", "bf16"): 0.781e9 + 0.004e9, ("bwd_dw_sm100_saved", "auto"): 1.530e9 + 0.004e9,
+    ("bwd_dw_sm100_saved", "bf16x3"): 1.530e9 + 0.004e9,
     # gather route of the weight gradient (sample cache off)
     ("bwd_dw_sm100", "bf16"): 0.430e9 + 0.073e9, ("bwd_dw_sm100", "auto"): 0.592e9 + 0.127e9,
     ("bwd_dw_sm100", "bf16x3"): 0.592e9 + 0.127e9,
