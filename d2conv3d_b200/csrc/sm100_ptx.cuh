@@ -175,10 +175,8 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src, uin
 }
 
 // L2 eviction priority for streams that are touched once (sampling records, the kept sample image): evict_first, so
-// that they do not push out the operands every CTA re-reads.  (Marking those operands evict_last was tried and taken
-// out: where the staged input is larger than L2 -- one 8x120x214 clip of 256 channels is 210 MB -- it filled L2
-// with lines that would not leave, the output tile's reductions were evicted between two touches, and the forward of
-// that layer wrote 6 GB to DRAM instead of 0.4 GB and took 30 % longer.)
+// that they do not push out the operands every CTA re-reads.  (Marking those operands evict_last as well was tried
+// and made no measurable difference; it was taken out so that an input larger than L2 cannot pin the cache.)
 __device__ __forceinline__ uint64_t l2_evict_first() {
   uint64_t pol;
   asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
