@@ -72,6 +72,7 @@ struct FwdParams {
   int tiles_per_clip, n_tiles;
   long long n_units;           // n_tiles * S
   int n_parts, part_shift;     // see cta_part_range
+  int rr;                      // 1: parts are whole tiles dealt round-robin (part r = tile r * gridDim.x + blockIdx.x)
   long long units_per_part;
   int seg_cap;                 // at most this many units accumulate in tensor memory before the partial result is
                                // added to y (see run_fwd); S = no limit
@@ -259,8 +260,13 @@ int run_fwd(const Geom& g, int math_mode, const Coords& coords, const HeadCfg& h
   const int seg_cap = x3 ? 108 : pl.S;
   // One part per clip (cta_part_range) while every CTA still gets a worthwhile range inside each clip.
   const long long units_per_clip = (long long)pl.tiles_per_clip * pl.S;
-  const int n_parts = (g.B > 1 && g.B <= 16 && units_per_clip / grid >= 4 * kMinUnitsPerCta) ? g.B : 1;
-  bool whole_tiles_only = (pl.n_tiles % grid == 0) && seg_cap >= pl.S && n_parts == 1;
+  // Many tiles per CTA: deal whole tiles round-robin (fwd_sm100_kernel, part_range) -- consecutive tiles are worked
+  // on at the same time and every tile is finished by one CTA; the last round leaves at most 1/8 of a CTA's work
+  // unbalanced.
+  const bool rr = grid == sm_count && pl.n_tiles >= 8 * grid;
+  const int n_parts = rr ? (int)((pl.n_tiles + grid - 1) / grid)
+                         : ((g.B > 1 && g.B <= 16 && units_per_clip / grid >= 4 * kMinUnitsPerCta) ? g.B : 1);
+  bool whole_tiles_only = seg_cap >= pl.S && (rr || ((pl.n_tiles % grid == 0) && n_parts == 1));
 
   // CTA pairs (deform_sm100_fwd_pair.cuh) whenever there are at least two tiles and the device can co-schedule
   // clusters of 2 with this kernel's shared memory.  Opt-in (D2C_SM100_PAIR=1): measured slower than the
@@ -326,7 +332,8 @@ int run_fwd(const Geom& g, int math_mode, const Coords& coords, const HeadCfg& h
   p.cs.dz = g.H * g.W * g.Cin; p.cs.dy = g.W * g.Cin; p.cs.dx = g.Cin;
   p.N = g.Cout; p.nh = pl.nh; p.S = pl.S; p.tiles_per_clip = pl.tiles_per_clip; p.n_tiles = pl.n_tiles;
   p.n_units = n_units;
-  p.n_parts = n_parts; p.units_per_part = n_units / n_parts; p.part_shift = (int)(grid / n_parts);
+  p.n_parts = n_parts; p.rr = rr ? 1 : 0;
+  p.units_per_part = rr ? 0 : n_units / n_parts; p.part_shift = rr ? 0 : (int)(grid / n_parts);
   p.seg_cap = seg_cap;
   p.b_stages = pl.b_stages; p.b_stage_bytes = pl.b_stage_bytes; p.tmem_cols = pl.tmem_cols;
   // keep the samples for the weight gradient when the caller bound a cache that is large enough

@@ -66,14 +66,33 @@ fwd_sm100_kernel(const FwdParams p) {
   // do no 64-bit division.
   // (unit indices fit 31 bits: checked by the host)
   int* part_tab = reinterpret_cast<int*>(base_ptr + bar_off + 256);      // [part][beg, end], then the total
+  // Large volumes (FwdParams::rr): whole tiles dealt round-robin instead -- at any time the CTAs then work on
+  // gridDim.x CONSECUTIVE tiles, whose sampling neighbourhoods overlap, so the part of the staged input they gather
+  // from is a few planes and not a few planes around 148 places spread over the whole volume (which L2 cannot hold:
+  // the stride-4 decoder layer re-fetched its 210 MB input 22 times).
+  auto part_range = [&](int part, int& beg, int& end) {
+    if (p.rr) {
+      const int tile = part * (int)gridDim.x + (int)blockIdx.x;
+      beg = tile * p.S;
+      end = tile < p.n_tiles ? beg + p.S : beg;
+    } else {
+      beg = part_tab[2 * part];
+      end = part_tab[2 * part + 1];
+    }
+  };
 
   if (threadIdx.x == 0) {
     int total = 0;
-    for (int part = 0; part < p.n_parts; ++part) {
-      long long pb, pe;
-      cta_part_range(p, part, pb, pe);
-      part_tab[2 * part] = (int)pb; part_tab[2 * part + 1] = (int)pe;
-      total += (int)(pe - pb);
+    if (p.rr) {
+      // round-robin tiles: part r is tile r * gridDim.x + blockIdx.x (computed where it is needed)
+      for (int tile = (int)blockIdx.x; tile < p.n_tiles; tile += (int)gridDim.x) total += p.S;
+    } else {
+      for (int part = 0; part < p.n_parts; ++part) {
+        long long pb, pe;
+        cta_part_range(p, part, pb, pe);
+        part_tab[2 * part] = (int)pb; part_tab[2 * part + 1] = (int)pe;
+        total += (int)(pe - pb);
+      }
     }
     part_tab[32] = total;
     for (int s = 0; s < kAStages; ++s) { ptx::mbar_init(a_full(s), kGatherWarps); ptx::mbar_init(a_empty(s), 1); }
@@ -105,7 +124,8 @@ fwd_sm100_kernel(const FwdParams p) {
     int seg = 0;
     for (int part = 0; part < p.n_parts; ++part) {
     if (*abort_flag) break;
-    const int u_beg = part_tab[2 * part], u_end = part_tab[2 * part + 1];
+    int u_beg, u_end;
+    part_range(part, u_beg, u_end);
     for (int u = u_beg; u < u_end; ++seg) {
       const int tile = u / p.S, s_beg = u % p.S;
       const int s_end = min(min(p.S, s_beg + (u_end - u)), s_beg + p.seg_cap);
@@ -203,7 +223,8 @@ fwd_sm100_kernel(const FwdParams p) {
       const uint64_t a_step = (uint64_t)(kAStageBytes >> 4), b_step = (uint64_t)(p.b_stage_bytes >> 4);
       for (int part = 0; ok && part < p.n_parts; ++part) {
       if (*abort_flag) break;
-      const int u_beg = part_tab[2 * part], u_end = part_tab[2 * part + 1];
+      int u_beg, u_end;
+    part_range(part, u_beg, u_end);
       int s_beg = u_beg % p.S;                                          // once per part
       for (int u = u_beg; ok && u < u_end; ++seg) {
         const int s_end = min(min(p.S, s_beg + (u_end - u)), s_beg + p.seg_cap);
@@ -247,7 +268,8 @@ fwd_sm100_kernel(const FwdParams p) {
       uint32_t phb = 1;                 // the wait for a FREE slot looks at the previous phase
       for (int part = 0; part < p.n_parts; ++part) {
       if (*abort_flag) break;
-      const int u_beg = part_tab[2 * part], u_end = part_tab[2 * part + 1];
+      int u_beg, u_end;
+    part_range(part, u_beg, u_end);
       int s = u_beg % p.S;              // once per part
       const uint8_t* src = p.w_sw + (long long)s * p.b_stage_bytes;
       const int n_part_units = u_end - u_beg;
@@ -284,7 +306,8 @@ fwd_sm100_kernel(const FwdParams p) {
       const uint64_t pol_stream = ptx::l2_evict_first();       // records are read once
       for (int part = 0; part < p.n_parts; ++part) {
       if (*abort_flag) break;
-      const int u_beg = part_tab[2 * part], u_end = part_tab[2 * part + 1];
+      int u_beg, u_end;
+    part_range(part, u_beg, u_end);
       int s = u_beg % p.S;
       const int tile0 = u_beg / p.S;
       int b = tile0 / p.tiles_per_clip, v0 = (tile0 % p.tiles_per_clip) * kBM;
