@@ -11,10 +11,13 @@
 // with the input staged channels-last each corner of a slice is ONE contiguous 128-byte
 // (fp16 staging) or 256-byte (fp32 staging) line.
 //
-// Work decomposition: the (tile, slice) units are cut into one contiguous range per CTA
-// (stream-K), so 203 tiles do not run as two ragged waves on 148 SMs.  A CTA whose range
-// covers a whole tile stores it; partial tiles are combined with fp32 reductions into the
-// zero-initialised output.
+// Work decomposition: the (tile, slice) units of every clip are cut into one contiguous range per CTA
+// (stream-K inside the clip), so 102 tiles per clip do not run as ragged waves on 148 SMs and all CTAs
+// gather from the same clip at the same time (one clip's staged input fits in L2, the batch does not).
+// A CTA whose range covers a whole tile stores it; partial tiles are combined with fp32 reductions into
+// the zero-initialised output.  Where a CTA has eight or more tiles (large volumes), whole tiles are
+// dealt round-robin instead: the CTAs then work on consecutive tiles, whose sampling neighbourhoods
+// overlap.
 //
 // Per CTA, 24 warps in warpgroup-aligned roles (deform_sm100_fwd_kernel.cuh):
 //   warps 0-3   epilogue: tcgen05.ld the 128 x N accumulator, add bias, store / reduce NCDHW

@@ -99,3 +99,31 @@ def test_math_mode_and_intermediate_cap(L):
     assert L.d2c_workspace_bytes(_lib.OP_DEFORM_BWD, ctypes.byref(d)) == 8 * 27 * 144 * 4
     _ops.config.set_max_intermediate_elements(default)
     assert L.d2c_workspace_bytes(_lib.OP_DEFORM_BWD, ctypes.byref(d)) == 2 * 8 * 27 * 144 * 4
+
+
+def test_sample_cache_sizes_follow_mode_cap_and_shape(L):
+    """d2c_sample_cache_bytes is pure host arithmetic: image (one 8 KB block per 64-channel slice and 64 voxels, hi and
+    lo in the fp32-parity mode) + staged input + position records; 0 wherever the call pair would not use a cache."""
+    mode0, cap0 = L.d2c_get_math_mode(), L.d2c_get_max_intermediate_elements()
+    try:
+        c2 = _desc(batch=2, in_channels=512, out_channels=512, in_d=8, in_h=30, in_w=54, offset_groups=8)
+        V, tiles = 8 * 30 * 54, 2 * 102                      # 102 tiles of 128 voxels per clip
+        pairs = 8 * 27 // 2                                  # 216 slices of 64 channels
+        pos = 2 * 8 * 27 * V * 16
+        L.d2c_set_math_mode(_lib.MATH_MODES["auto"])
+        assert L.d2c_sample_cache_bytes(ctypes.byref(c2)) == tiles * 2 * pairs * 4 * 8192 + 2 * V * 512 * 4 + pos
+        L.d2c_set_math_mode(_lib.MATH_MODES["bf16"])
+        assert L.d2c_sample_cache_bytes(ctypes.byref(c2)) == tiles * 2 * pairs * 2 * 8192 + 2 * V * 512 * 2 + pos
+        L.d2c_set_math_mode(_lib.MATH_MODES["fp32"])         # CUDA-core tier: nothing to keep
+        assert L.d2c_sample_cache_bytes(ctypes.byref(c2)) == 0
+        L.d2c_set_math_mode(_lib.MATH_MODES["auto"])
+        L.d2c_set_max_intermediate_elements(2 * 512 * 27 * V - 1)      # one element under the image's size
+        assert L.d2c_sample_cache_bytes(ctypes.byref(c2)) == 0
+        L.d2c_set_max_intermediate_elements(cap0)
+        assert L.d2c_sample_cache_bytes(ctypes.byref(_desc(dtype=1))) == 0          # float64
+        assert L.d2c_sample_cache_bytes(ctypes.byref(_desc())) == 0                 # 4 channels per group: generic tier
+        assert L.d2c_sample_cache_bytes(None) == 0
+        assert L.d2c_bind_sample_cache(None) == 0                                   # unbinding is always allowed
+    finally:
+        L.d2c_set_math_mode(mode0)
+        L.d2c_set_max_intermediate_elements(cap0)
