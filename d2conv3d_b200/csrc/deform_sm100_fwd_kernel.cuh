@@ -27,8 +27,8 @@ constexpr int kMmaWarpFwd = 4, kLoadWarpFwd = 5, kRecWarpFwd = 6, kGatherWarp0Fw
 //          a_hi*b_hi + a_lo*b_hi + a_hi*b_lo from the 16-channel K sub-blocks of the same two tiles.
 // kDual = 1 (single-pass mode only): 32 channels per offset group, a 64-channel unit spans two groups.
 // kSave = 1: the blended tiles are also written to FwdParams::sav (a forward whose backward will follow).  A template
-//          parameter, not a run-time test: values kept live for the extra stores cost the inference kernel 20-30 % on
-//          the large decoder layers when the two shared one body.
+//          parameter, not a run-time test, so that the inference kernel carries neither the stores nor the registers
+//          for their addresses.
 template <int kX3, int kDual, int kSave>
 __global__ void __launch_bounds__(kThreadsFwd, 1)
 fwd_sm100_kernel(const FwdParams p) {
